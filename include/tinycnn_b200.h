@@ -1,0 +1,460 @@
+/*
+ * tinycnn_b200.h -- C ABI of the B200 (sm_100a) training hot path for tiny-dnn.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, and returns
+ * an int status: 0 = ok, non-zero = error (text via b200_last_error()).  The C++
+ * host shim turns a non-zero status into `throw nn_error(...)`, the reference's
+ * only error convention (tiny_dnn/util/nn_error.h:19-27).
+ *
+ * Pointer convention: unless a parameter is documented as HOST memory, every
+ * float/uint8/int32 buffer is DEVICE memory on the context's GPU.  The
+ * `*_host` entry points take HOST buffers, stage them through the context's
+ * device arena and copy results back; they are what the reference-side
+ * OpKernel branches call (tensor_t rows are host vectors).
+ *
+ * Tensor layouts are the reference's own: a batch is `B` rows, each row planar
+ * CHW, index (H*c + y)*W + x (tiny_dnn/util/util.h:168-173), rows stored back to
+ * back.  Convolution weights are [(in_c*o + inc)][ky][kx]
+ * (tiny_dnn/core/kernels/conv2d_op_internal.h:41); fully-connected weights are
+ * row-major [in][out] (tiny_dnn/core/kernels/fully_connected_op_internal.h:28).
+ *
+ * Gradient convention: the reference keeps one dW/db row per sample and sums
+ * the rows later (tiny_dnn/node.h:89-103).  The device path produces the batch
+ * SUM directly (no 1/B factor: tiny_dnn/layers/layer.h:663-673 scales by 1.0).
+ */
+#ifndef TINYCNN_B200_H_
+#define TINYCNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B200_API
+#else
+#define B200_API __attribute__((visibility("default")))
+#endif
+
+/* ------------------------------------------------------------------------- */
+/* Runtime                                                                     */
+/* ------------------------------------------------------------------------- */
+
+typedef struct b200_ctx b200_ctx;
+
+/* Library version, "major.minor". */
+B200_API const char *b200_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+B200_API const char *b200_last_error(void);
+
+/* Number of CUDA devices visible; 0 when there is no usable GPU. */
+B200_API int b200_device_count(void);
+
+/*
+ * Create a context bound to `device`.  `stream` is a cudaStream_t the caller
+ * owns (NULL = the context creates its own non-blocking stream).  All work of
+ * the context is issued on that stream.  Replaces nothing in the reference
+ * (it has no device context on this path; core/framework/device.fwd.h:38-112 is
+ * the OpenCL-only analogue).
+ */
+B200_API int b200_ctx_create(int device, void *stream, b200_ctx **out);
+B200_API int b200_ctx_destroy(b200_ctx *ctx);
+B200_API int b200_ctx_set_stream(b200_ctx *ctx, void *stream);
+B200_API void *b200_ctx_stream(b200_ctx *ctx);
+B200_API int b200_ctx_sync(b200_ctx *ctx);
+
+/* Raw device memory helpers for hosts that do not link the CUDA runtime. */
+B200_API int b200_malloc(b200_ctx *ctx, size_t bytes, void **out);
+B200_API int b200_free(b200_ctx *ctx, void *ptr);
+B200_API int b200_memcpy_h2d(b200_ctx *ctx, void *dst, const void *src, size_t bytes);
+B200_API int b200_memcpy_d2h(b200_ctx *ctx, void *dst, const void *src, size_t bytes);
+B200_API int b200_memset(b200_ctx *ctx, void *dst, int value, size_t bytes);
+
+/* ------------------------------------------------------------------------- */
+/* Convolution  (a1-a3)                                                        */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Plain-C mirror of core::conv_params (tiny_dnn/core/params/conv_params.h:63-90).
+ * `tbl` is a HOST array of in_c*out_c bytes in connection_table order
+ * connected_[inc*out_c + o] (conv_params.h:52-54), or NULL for a full table.
+ */
+typedef struct b200_conv_desc {
+  int32_t in_w, in_h, in_c;     /* params.in                                  */
+  int32_t inp_w, inp_h;         /* params.in_padded (same: in + k - 1)        */
+  int32_t out_w, out_h, out_c;  /* params.out                                 */
+  int32_t k_w, k_h;             /* params.weight width/height                 */
+  int32_t stride_w, stride_h;
+  int32_t dil_w, dil_h;         /* forward only; backward ignores dilation as */
+                                /* conv2d_op_internal.h:118-123,139-160 does  */
+  int32_t has_bias;
+  int32_t pad_same;             /* padding::same = 1, padding::valid = 0      */
+  int32_t input_is_padded;      /* 1: `in`/`din` rows already have in_padded  */
+                                /* geometry, as Conv2dOp::compute receives    */
+                                /* them (convolutional_layer.h:283-299)       */
+  int32_t algo;                 /* 0 auto, 1 general kernels, 2 tiled kernels */
+  const uint8_t *tbl;           /* HOST, may be NULL                          */
+} b200_conv_desc;
+
+/*
+ * Fill a descriptor the way convolutional_layer::conv_set_params does
+ * (tiny_dnn/layers/convolutional_layer.h:404-438; conv_out_length
+ * util/util.h:329-344).
+ */
+B200_API int b200_conv_desc_init(b200_conv_desc *d, int in_w, int in_h, int in_c,
+                                 int k_w, int k_h, int out_c, int pad_same,
+                                 int has_bias, int stride_w, int stride_h,
+                                 int dil_w, int dil_h);
+
+/*
+ * out = conv(in, W) + bias.  Replaces kernels::conv2d_op_internal forward
+ * (tiny_dnn/core/kernels/conv2d_op_internal.h:13-74) as dispatched by
+ * Conv2dOp::compute (tiny_dnn/core/kernels/conv2d_op.h:23-51).  `out` is
+ * overwritten.  in: B x (in_c*in_h*in_w) (or in_padded geometry when
+ * input_is_padded); out: B x (out_c*out_h*out_w).
+ */
+B200_API int b200_conv2d_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                             const float *W, const float *bias, float *out, int batch);
+
+/*
+ * din = dX, dW (+)= sum_n dW_n, db (+)= sum_n db_n.  Replaces the backward
+ * kernels::conv2d_op_internal (conv2d_op_internal.h:78-181) as dispatched by
+ * Conv2dGradOp::compute (tiny_dnn/core/kernels/conv2d_grad_op.h:22-50).  `din`
+ * is overwritten (NULL skips dX); dW/db are overwritten when accumulate == 0
+ * and added to when accumulate != 0 (the reference never clears them,
+ * conv2d_op_internal.h:165,177).  db may be NULL when has_bias == 0.
+ */
+B200_API int b200_conv2d_bwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                             const float *W, const float *dout, float *din, float *dW,
+                             float *db, int accumulate, int batch);
+
+/* HOST-buffer forms of the two calls above (what the OpKernel branches call). */
+B200_API int b200_conv2d_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                                  const float *W, const float *bias, float *out, int batch);
+B200_API int b200_conv2d_bwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                                  const float *W, const float *dout, float *din, float *dW,
+                                  float *db, int accumulate, int batch);
+
+/* ------------------------------------------------------------------------- */
+/* Fully connected  (a4-a5)                                                    */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * out[n][i] = b[i] + sum_c W[c*out+i] * in[n][c].  Replaces
+ * kernels::fully_connected_op_internal forward
+ * (tiny_dnn/core/kernels/fully_connected_op_internal.h:15-36) as dispatched by
+ * FullyConnectedOp::compute (tiny_dnn/core/kernels/fully_connected_op.h:25-64).
+ * bias may be NULL (fully_params::has_bias_ == false).
+ */
+B200_API int b200_fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in,
+                         const float *W, const float *bias, float *out, int batch);
+
+/*
+ * din[n][c] = dot(dout[n], W[c*out..]); dW[c*out+i] (+)= sum_n dout[n][i]*in[n][c];
+ * db[i] (+)= sum_n dout[n][i].  Replaces the backward
+ * kernels::fully_connected_op_internal (fully_connected_op_internal.h:38-71) as
+ * dispatched by FullyConnectedGradOp::compute
+ * (tiny_dnn/core/kernels/fully_connected_grad_op.h:22-52).  din may be NULL.
+ */
+B200_API int b200_fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in,
+                         const float *W, const float *dout, float *din, float *dW,
+                         float *db, int accumulate, int batch);
+
+B200_API int b200_fc_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in,
+                              const float *W, const float *bias, float *out, int batch);
+B200_API int b200_fc_bwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in,
+                              const float *W, const float *dout, float *din, float *dW,
+                              float *db, int accumulate, int batch);
+
+/* ------------------------------------------------------------------------- */
+/* Pooling  (a6-a7)                                                            */
+/* ------------------------------------------------------------------------- */
+
+/* Mirror of core::maxpool_params (tiny_dnn/core/params/maxpool_params.h:17-34). */
+typedef struct b200_pool_desc {
+  int32_t in_w, in_h, in_c;
+  int32_t out_w, out_h;
+  int32_t pool_w, pool_h;
+  int32_t stride_w, stride_h;
+} b200_pool_desc;
+
+/* Output size per pool_out_length (tiny_dnn/util/util.h:346-363). */
+B200_API int b200_pool_desc_init(b200_pool_desc *d, int in_w, int in_h, int in_c,
+                                 int pool_w, int pool_h, int stride_w, int stride_h,
+                                 int ceil_mode, int pad_same);
+
+/*
+ * Max pooling forward: strict `>` scan of the (border-clipped) window in
+ * row-major order; `argmax` receives the winning in-row index (the reference's
+ * params.out2inmax).  Replaces kernels::maxpool_op_internal
+ * (tiny_dnn/core/kernels/maxpool_op_internal.h:16-39) as dispatched by
+ * MaxPoolOp::compute (tiny_dnn/core/kernels/maxpool_op.h:23-61); window tables
+ * tiny_dnn/layers/max_pooling_layer.h:195-235.
+ */
+B200_API int b200_maxpool_fwd(b200_ctx *ctx, const b200_pool_desc *d, const float *in,
+                              float *out, int32_t *argmax, int batch);
+
+/*
+ * din[i] = (argmax[in2out(i)] == i) ? dout[in2out(i)] : 0 with in2out(i) the
+ * LAST window covering i (0 when none does).  Replaces
+ * kernels::maxpool_grad_op_internal (maxpool_op_internal.h:41-57) as dispatched
+ * by MaxPoolGradOp::compute (tiny_dnn/core/kernels/maxpool_grad_op.h:22-47).
+ */
+B200_API int b200_maxpool_bwd(b200_ctx *ctx, const b200_pool_desc *d, const float *dout,
+                              const int32_t *argmax, float *din, int batch);
+
+B200_API int b200_maxpool_fwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *in,
+                                   float *out, int32_t *argmax, int batch);
+B200_API int b200_maxpool_bwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *dout,
+                                   const int32_t *argmax, float *din, int batch);
+
+/*
+ * Average pooling with the reference's trainable per-channel scale and bias:
+ * out = (sum window) * W[c] * 1/(pool_w*pool_h) + b[c].  Replaces
+ * tiny_average_pooling_kernel (tiny_dnn/layers/average_pooling_layer.h:25-55).
+ * W has pool_w*pool_h*in_c entries of which only the first in_c are used
+ * (average_pooling_layer.h:231-233; partial_connected_layer.h:24-35).
+ */
+B200_API int b200_avgpool_fwd(b200_ctx *ctx, const b200_pool_desc *d, const float *in,
+                              const float *W, const float *bias, float *out, int batch);
+
+/*
+ * din = W[c]*scale*dout[first window covering i]; dW[c] (+)= scale*sum in*dout;
+ * db[c] (+)= sum dout.  Replaces tiny_average_pooling_back_kernel
+ * (average_pooling_layer.h:58-106).  dW has pool_w*pool_h*in_c entries; entries
+ * >= in_c receive 0.
+ */
+B200_API int b200_avgpool_bwd(b200_ctx *ctx, const b200_pool_desc *d, const float *in,
+                              const float *W, const float *dout, float *din, float *dW,
+                              float *db, int accumulate, int batch);
+
+B200_API int b200_avgpool_fwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *in,
+                                   const float *W, const float *bias, float *out, int batch);
+B200_API int b200_avgpool_bwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *in,
+                                   const float *W, const float *dout, float *din, float *dW,
+                                   float *db, int accumulate, int batch);
+
+/* ------------------------------------------------------------------------- */
+/* Activations and loss gradients  (a8-a9)                                     */
+/* ------------------------------------------------------------------------- */
+
+enum { B200_ACT_NONE = 0, B200_ACT_RELU = 1, B200_ACT_TANH = 2, B200_ACT_SOFTMAX = 3 };
+
+/*
+ * y = f(x) row by row (`dim` elements per row).  Replaces
+ * relu_layer/tanh_layer/softmax_layer::forward_activation
+ * (tiny_dnn/activations/relu_layer.h:25-29, tanh_layer.h:24-28,
+ * softmax_layer.h:24-34) under activation_layer::forward_propagation
+ * (tiny_dnn/activations/activation_layer.h:74-79).
+ */
+B200_API int b200_act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int batch);
+
+/*
+ * dx from (y, dy): relu dy*(y>0), tanh dy*(1-y*y), softmax
+ * dx_j = sum_k dy_k*(k==j ? y_j(1-y_j) : -y_k*y_j).  Replaces the
+ * backward_activation members (relu_layer.h:31-39, tanh_layer.h:30-38,
+ * softmax_layer.h:36-55).
+ */
+B200_API int b200_act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx,
+                          int dim, int batch);
+
+B200_API int b200_act_fwd_host(b200_ctx *ctx, int kind, const float *x, float *y, int dim,
+                               int batch);
+B200_API int b200_act_bwd_host(b200_ctx *ctx, int kind, const float *y, const float *dy,
+                               float *dx, int dim, int batch);
+
+enum { B200_LOSS_MSE = 0, B200_LOSS_CROSS_ENTROPY = 1, B200_LOSS_CROSS_ENTROPY_MULTICLASS = 2 };
+
+/*
+ * Per-sample loss gradient dE/dy: mse 2/dim*(y-t), cross_entropy
+ * (y-t)/(y*(1-y)), multiclass -t/y.  Replaces mse::df / cross_entropy::df /
+ * cross_entropy_multiclass::df and the mini-batch loop gradient<E>
+ * (tiny_dnn/lossfunctions/loss_function.h:28-36,120-128,143-150,190-218).
+ */
+B200_API int b200_loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy,
+                            int dim, int batch);
+
+/*
+ * Sum over the batch of E::f(y_n, t_n) (loss_function.h:17-26,107-118,132-141),
+ * written to one device float.  The reference exposes it as network::get_loss.
+ */
+B200_API int b200_loss_value(b200_ctx *ctx, int kind, const float *y, const float *t,
+                             float *loss_sum, int dim, int batch);
+
+/* ------------------------------------------------------------------------- */
+/* Gradient merge + optimizer  (a10-a11)                                       */
+/* ------------------------------------------------------------------------- */
+
+enum { B200_OPT_ADAGRAD = 0, B200_OPT_ADAM = 1, B200_OPT_MOMENTUM = 2 };
+
+/* Public hyper-parameters of the reference optimizers
+ * (tiny_dnn/optimizers/optimizer.h:57-71,103-137,201-218). */
+typedef struct b200_opt_hyper {
+  float alpha;   /* learning rate (all three)                    */
+  float b1, b2;  /* adam decay terms                             */
+  float b1_t;    /* adam b1^t for THIS update call (per tensor)  */
+  float b2_t;    /* adam b2^t for THIS update call               */
+  float mu;      /* momentum                                     */
+  float lambda;  /* momentum weight decay                        */
+  float eps;     /* 1e-8 in the reference (private member)       */
+} b200_opt_hyper;
+
+/*
+ * dst[i] = sum_{r<rows} grads[r*len + i], summed in row order like
+ * edge::merge_grads (tiny_dnn/node.h:89-103).  rows may be 1.
+ */
+B200_API int b200_merge_grads(b200_ctx *ctx, const float *grads, int rows, size_t len,
+                              float *dst);
+
+/*
+ * One optimizer::update call on one parameter tensor
+ * (adagrad optimizer.h:60-66, adam :112-127, momentum :205-213).  state0 is g
+ * (adagrad), mt (adam) or dWprev (momentum); state1 is vt (adam only).  The
+ * caller advances b1_t/b2_t after each call as adam::update does (:125-126).
+ */
+B200_API int b200_opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper *h, const float *dW,
+                             float *W, float *state0, float *state1, size_t len);
+
+/*
+ * merge_grads fused with the update: dW_i = sum_r grads[r*stride + i] is formed
+ * in registers and consumed by the optimizer formula; `merged` (may be NULL)
+ * receives the sum.  Replaces the body of layer::update_weight for one
+ * trainable edge (tiny_dnn/layers/layer.h:663-682).
+ */
+B200_API int b200_merge_update(b200_ctx *ctx, int kind, const b200_opt_hyper *h,
+                               const float *grads, int rows, size_t stride, float *merged,
+                               float *W, float *state0, float *state1, size_t len);
+
+/* ------------------------------------------------------------------------- */
+/* Quantized forward  (a12-a14)                                                */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * uint8 quantized convolution forward, bit-exact with
+ * tiny_quantized_conv2d_kernel (tiny_dnn/core/kernels/tiny_quantized_conv2d_kernel.h:20-148)
+ * run per sample by tiny_backend::conv2d_q (tiny_dnn/core/backend_tiny.h:97-112):
+ * per-sample input range, filter range taken from the element subset the
+ * reference scans (:40-55), int32 accumulate, shrink-range requantize
+ * (tiny_quantization_kernel.h:145-186,230-254), dequantize to float.
+ * `in` has in_padded geometry when pad_same (the layer pads first).
+ */
+B200_API int b200_qconv2d_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                              const float *W, const float *bias, float *out, int batch);
+
+/*
+ * uint8 quantized fully-connected forward, bit-exact with
+ * tiny_quantized_fully_connected_kernel
+ * (tiny_dnn/core/kernels/tiny_quantized_fully_connected_kernel.h:22-128) run per
+ * sample as tiny_backend::fully_q would (backend_tiny.h:300-319).
+ */
+B200_API int b200_qfc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in,
+                          const float *W, const float *bias, float *out, int batch);
+
+B200_API int b200_qconv2d_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                                   const float *W, const float *bias, float *out, int batch);
+B200_API int b200_qfc_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in,
+                               const float *W, const float *bias, float *out, int batch);
+
+/* ------------------------------------------------------------------------- */
+/* Device-resident training step (driver of a1-a11)                            */
+/* ------------------------------------------------------------------------- */
+
+enum {
+  B200_LAYER_CONV = 1,
+  B200_LAYER_FC = 2,
+  B200_LAYER_MAXPOOL = 3,
+  B200_LAYER_AVGPOOL = 4,
+  B200_LAYER_RELU = 5,
+  B200_LAYER_TANH = 6,
+  B200_LAYER_SOFTMAX = 7
+};
+
+/* One layer of a network<sequential> (tiny_dnn/nodes.h:268-360). */
+typedef struct b200_layer_spec {
+  int32_t kind;
+  b200_conv_desc conv;   /* B200_LAYER_CONV                                   */
+  b200_pool_desc pool;   /* B200_LAYER_MAXPOOL / B200_LAYER_AVGPOOL           */
+  int32_t fc_in, fc_out, fc_has_bias; /* B200_LAYER_FC                        */
+} b200_layer_spec;
+
+typedef struct b200_net b200_net;
+
+/*
+ * Build a device-resident twin of a sequential network.  Parameters live in one
+ * flat buffer in network order (layer order; W before b: layer.h:663-678), and
+ * so do the batch-summed gradients (the all-reduce bucket) and optimizer state.
+ */
+B200_API int b200_net_create(b200_ctx *ctx, const b200_layer_spec *layers, int n_layers,
+                             int max_batch, b200_net **out);
+B200_API int b200_net_destroy(b200_net *net);
+
+B200_API size_t b200_net_param_count(const b200_net *net);
+B200_API int b200_net_tensor_count(const b200_net *net);
+/* offset/length of trainable tensor `i` inside the flat parameter buffer. */
+B200_API int b200_net_tensor_info(const b200_net *net, int i, size_t *offset, size_t *len);
+B200_API int b200_net_in_dim(const b200_net *net);
+B200_API int b200_net_out_dim(const b200_net *net);
+
+/* HOST <-> device copies of the flat parameter buffer. */
+B200_API int b200_net_set_params(b200_net *net, const float *host_params);
+B200_API int b200_net_get_params(b200_net *net, float *host_params);
+/* HOST copy of the flat batch-summed gradient bucket of the last backward. */
+B200_API int b200_net_get_grads(b200_net *net, float *host_grads);
+
+/* Device pointers for callers that own the collective (NCCL all-reduce). */
+B200_API float *b200_net_params_ptr(b200_net *net);
+B200_API float *b200_net_grads_ptr(b200_net *net);
+B200_API float *b200_net_output_ptr(b200_net *net);
+/* Device pointer to the output of layer `i` / its gradient (tests). */
+B200_API float *b200_net_layer_out_ptr(b200_net *net, int i);
+B200_API float *b200_net_layer_grad_ptr(b200_net *net, int i);
+
+/* network::fprop (tiny_dnn/network.h:911-926 -> nodes.h:288-303). */
+B200_API int b200_net_forward(b200_net *net, const float *x, int batch);
+/*
+ * gradient<E>(out, t) then network::bprop (loss_function.h:190-218,
+ * nodes.h:276-286); leaves the batch-summed gradients in the bucket.
+ */
+B200_API int b200_net_backward(b200_net *net, const float *t, int loss_kind);
+
+/* Reset optimizer state (optimizer::reset, optimizer.h:36-38 -- b1_t/b2_t are
+ * NOT reset by the reference; `reset_powers` != 0 restarts them for a new
+ * optimizer object). */
+B200_API int b200_net_opt_reset(b200_net *net, int reset_powers);
+
+/*
+ * nodes::update_weights (nodes.h:103-107): one optimizer update per trainable
+ * tensor in network order, Adam's powers advancing once per TENSOR
+ * (optimizer.h:125-126).  `h->b1_t/b2_t` are ignored; the net keeps its own.
+ */
+B200_API int b200_net_update(b200_net *net, int opt_kind, const b200_opt_hyper *h);
+
+/* forward + backward + update in one call; device x/t.  Uses a captured CUDA
+ * graph after the first call for a given (x, t, batch, loss, optimizer). */
+B200_API int b200_net_train_step(b200_net *net, const float *x, const float *t, int batch,
+                                 int loss_kind, int opt_kind, const b200_opt_hyper *h);
+
+/*
+ * The same step from HOST buffers (what network::train_onebatch does,
+ * network.h:911-926): x/t are copied to the device, the step runs, and the
+ * network output of the forward pass (batch x out_dim floats) is copied back
+ * to `out_host` when it is not NULL.  Pinned host memory makes the copies
+ * asynchronous; the call returns after the output has arrived.
+ */
+B200_API int b200_net_train_step_host(b200_net *net, const float *x_host, const float *t_host,
+                                      int batch, int loss_kind, int opt_kind,
+                                      const b200_opt_hyper *h, float *out_host);
+
+/* Adam powers currently held by the net (tests; T = tensor count). */
+B200_API int b200_net_adam_powers(const b200_net *net, float *b1_t, float *b2_t);
+
+/* Number of kernels this library launched on the calling process so far. */
+B200_API unsigned long long b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TINYCNN_B200_H_ */

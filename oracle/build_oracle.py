@@ -1,0 +1,83 @@
+"""Build recipe of the test oracle.
+
+`build_oracle()`      gcc  oracle/oracle.c      -> oracle/liboracle.so
+                      (plain C restatement; -ffp-contract=off so the compiler
+                      never fuses a multiply with an add)
+`build_reference()`   g++  oracle/ref_shim.cpp + oracle/ref_qfc.cpp against the
+                      reference's own headers -> oracle/_ref/libtinydnn_ref.so
+                      (only where the reference tree is present; flags follow
+                      the reference's OpenMP configuration: -O3 -fopenmp
+                      -DCNN_USE_OMP, default serialization, no AVX macros, so
+                      every kernel runs as backend_t::internal)
+
+Outputs are git-ignored build products; no reference source is copied.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent
+REF_ROOT = Path(os.environ.get("TINYDNN_REFERENCE", "/root/reference"))
+ORACLE_SO = HERE / "liboracle.so"
+REF_DIR = HERE / "_ref"
+REF_SO = REF_DIR / "libtinydnn_ref.so"
+
+
+def _run(cmd):
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("command failed: " + " ".join(map(str, cmd)) + "\n" + res.stdout + res.stderr)
+
+
+def _stale(target: Path, sources) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(s).stat().st_mtime > t for s in sources)
+
+
+def build_oracle(force: bool = False) -> Path:
+    srcs = [HERE / "oracle.c", ROOT / "include" / "tinycnn_b200.h"]
+    if force or _stale(ORACLE_SO, srcs):
+        _run(["gcc", "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-fvisibility=hidden",
+              f"-I{ROOT / 'include'}", "-o", str(ORACLE_SO), str(HERE / "oracle.c"), "-lm"])
+    return ORACLE_SO
+
+
+def reference_available() -> bool:
+    return (REF_ROOT / "tiny_dnn" / "tiny_dnn.h").exists()
+
+
+def build_reference(force: bool = False) -> Path | None:
+    """Compile the unmodified reference behind the C doors; None if it is absent."""
+    if not reference_available():
+        return REF_SO if REF_SO.exists() else None
+    REF_DIR.mkdir(exist_ok=True)
+    srcs = [HERE / "ref_shim.cpp", HERE / "ref_qfc.cpp", ROOT / "include" / "tinycnn_b200.h",
+            HERE / "ref_stub" / "tiny_dnn" / "core" / "kernels" / "tiny_quantized_matmul_kernel.h"]
+    if not (force or _stale(REF_SO, srcs)):
+        return REF_SO
+    common = ["g++", "-std=c++14", "-O3", "-fopenmp", "-DCNN_USE_OMP", "-ffp-contract=off", "-fPIC",
+              "-fvisibility=hidden", "-w", f"-I{ROOT / 'include'}"]
+    o1 = REF_DIR / "ref_shim.o"
+    o2 = REF_DIR / "ref_qfc.o"
+    p1 = subprocess.Popen(common + [f"-I{REF_ROOT}", "-c", str(HERE / "ref_shim.cpp"), "-o", str(o1)],
+                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    p2 = subprocess.Popen(common + [f"-I{HERE / 'ref_stub'}", f"-I{REF_ROOT}", "-c",
+                                    str(HERE / "ref_qfc.cpp"), "-o", str(o2)],
+                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    out1, _ = p1.communicate()
+    out2, _ = p2.communicate()
+    if p1.returncode or p2.returncode:
+        raise RuntimeError("reference build failed:\n" + out1 + out2)
+    _run(["g++", "-shared", "-fopenmp", "-o", str(REF_SO), str(o1), str(o2)])
+    return REF_SO
+
+
+if __name__ == "__main__":
+    print(build_oracle(force="-f" in sys.argv))
+    print(build_reference(force="-f" in sys.argv))

@@ -1,0 +1,534 @@
+// ref_shim.cpp -- extern "C" doors into the UNMODIFIED reference (tiny-dnn),
+// compiled from its own headers where they lie (never copied into this
+// repository) into oracle/_ref/libtinydnn_ref.so by oracle/build_oracle.py.
+//
+// TEST INFRASTRUCTURE ONLY: it pins oracle.c (the C restatement) against the
+// real implementation, generates the golden fixtures, and serves as the timed
+// CPU baseline.  Every entry point drives the reference through its own layer
+// classes / free functions with engine backend_t::internal.
+//
+// Flat-array conventions match oracle.c (B rows back to back, reference
+// layouts), so a test can call ref_X and orc_X with the same arguments.
+#include <chrono>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "tiny_dnn/tiny_dnn.h"
+#include "tinycnn_b200.h"
+
+using namespace tiny_dnn;
+
+#define REF_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+tensor_t to_tensor(const float *p, size_t rows, size_t len) {
+  tensor_t t(rows, vec_t(len));
+  if (p)
+    for (size_t r = 0; r < rows; ++r) std::copy(p + r * len, p + (r + 1) * len, t[r].begin());
+  return t;
+}
+void from_tensor(const tensor_t &t, float *p, size_t len) {
+  if (!p) return;
+  for (size_t r = 0; r < t.size(); ++r) std::copy(t[r].begin(), t[r].begin() + len, p + r * len);
+}
+
+core::connection_table make_table(const b200_conv_desc *d) {
+  if (!d->tbl) return core::connection_table();
+  std::vector<char> tmp(d->tbl, d->tbl + (size_t)d->in_c * d->out_c);
+  std::unique_ptr<bool[]> ar(new bool[tmp.size()]);
+  for (size_t i = 0; i < tmp.size(); ++i) ar[i] = tmp[i] != 0;
+  // rows = in channels, cols = out channels (examples/mnist/train.cpp:44-51)
+  return core::connection_table(ar.get(), d->in_c, d->out_c);
+}
+
+std::unique_ptr<convolutional_layer> make_conv(const b200_conv_desc *d) {
+  return std::unique_ptr<convolutional_layer>(new convolutional_layer(
+    d->in_w, d->in_h, d->k_w, d->k_h, d->in_c, d->out_c, make_table(d),
+    d->pad_same ? padding::same : padding::valid, d->has_bias != 0, d->stride_w, d->stride_h,
+    d->dil_w, d->dil_h, core::backend_t::internal));
+}
+
+}  // namespace
+
+REF_API const char *ref_version() { return "tiny-dnn reference, backend_t::internal"; }
+
+REF_API int ref_openmp_threads() {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+// ---------------------------------------------------------------- convolution
+// convolutional_layer::forward_propagation with UNPADDED input rows.
+REF_API int ref_conv2d_fwd(const b200_conv_desc *d, const float *in, const float *W,
+                           const float *bias, float *out, int B) {
+  auto l = make_conv(d);
+  size_t in_len = (size_t)d->in_c * d->in_h * d->in_w;
+  size_t out_len = (size_t)d->out_c * d->out_h * d->out_w;
+  size_t lenW = (size_t)d->out_c * d->in_c * d->k_h * d->k_w;
+  if (l->out_shape()[0].size() != out_len) return 1;
+  tensor_t tin = to_tensor(in, B, in_len), tW = to_tensor(W, 1, lenW),
+           tb = to_tensor(d->has_bias ? bias : nullptr, 1, d->out_c), tout(B, vec_t(out_len));
+  // Conv2dOp::compute reads input(2) even when has_bias is false
+  // (conv2d_op.h:29), so a bias tensor is always supplied.
+  std::vector<tensor_t *> ins = {&tin, &tW, &tb};
+  std::vector<tensor_t *> outs = {&tout};
+  l->set_parallelize(true);
+  l->forward_propagation(ins, outs);
+  from_tensor(tout, out, out_len);
+  return 0;
+}
+
+// forward then convolutional_layer::back_propagation.  din is unpadded;
+// dW / db are per-sample rows (B x len) that START FROM ZERO.
+REF_API int ref_conv2d_bwd(const b200_conv_desc *d, const float *in, const float *W,
+                           const float *dout, float *din, float *dW_rows, float *db_rows, int B) {
+  auto l = make_conv(d);
+  size_t in_len = (size_t)d->in_c * d->in_h * d->in_w;
+  size_t out_len = (size_t)d->out_c * d->out_h * d->out_w;
+  size_t lenW = (size_t)d->out_c * d->in_c * d->k_h * d->k_w;
+  tensor_t tin = to_tensor(in, B, in_len), tW = to_tensor(W, 1, lenW),
+           tb = to_tensor(nullptr, 1, d->out_c), tout(B, vec_t(out_len));
+  tensor_t gout = to_tensor(dout, B, out_len), gin(B, vec_t(in_len)), gW(B, vec_t(lenW)),
+           gb(B, vec_t(d->out_c));
+  // Conv2dGradOp::compute reads input_grad(2) unconditionally (conv2d_grad_op.h:29)
+  std::vector<tensor_t *> ins = {&tin, &tW, &tb}, gins = {&gin, &gW, &gb};
+  std::vector<tensor_t *> outs = {&tout}, gouts = {&gout};
+  l->setup(false);
+  l->set_sample_count(B);
+  l->set_parallelize(true);
+  l->forward_propagation(ins, outs);
+  l->back_propagation(ins, outs, gouts, gins);
+  from_tensor(gin, din, in_len);
+  from_tensor(gW, dW_rows, lenW);
+  if (d->has_bias) from_tensor(gb, db_rows, d->out_c);
+  return 0;
+}
+
+// ---------------------------------------------------------------- fully connected
+REF_API int ref_fc_fwd(int in_size, int out_size, const float *in, const float *W,
+                       const float *bias, float *out, int B) {
+  fully_connected_layer l(in_size, out_size, bias != nullptr, core::backend_t::internal);
+  tensor_t tin = to_tensor(in, B, in_size), tW = to_tensor(W, 1, (size_t)in_size * out_size),
+           tb = to_tensor(bias, 1, out_size), tout(B, vec_t(out_size));
+  std::vector<tensor_t *> ins = {&tin, &tW};
+  if (bias) ins.push_back(&tb);
+  std::vector<tensor_t *> outs = {&tout};
+  l.set_parallelize(true);
+  l.forward_propagation(ins, outs);
+  from_tensor(tout, out, out_size);
+  return 0;
+}
+
+REF_API int ref_fc_bwd(int in_size, int out_size, int has_bias, const float *in, const float *W,
+                       const float *dout, float *din, float *dW_rows, float *db_rows, int B) {
+  fully_connected_layer l(in_size, out_size, has_bias != 0, core::backend_t::internal);
+  size_t lenW = (size_t)in_size * out_size;
+  tensor_t tin = to_tensor(in, B, in_size), tW = to_tensor(W, 1, lenW),
+           tb = to_tensor(nullptr, 1, out_size), tout(B, vec_t(out_size));
+  tensor_t gout = to_tensor(dout, B, out_size), gin(B, vec_t(in_size)), gW(B, vec_t(lenW)),
+           gb(B, vec_t(out_size));
+  std::vector<tensor_t *> ins = {&tin, &tW}, gins = {&gin, &gW};
+  if (has_bias) {
+    ins.push_back(&tb);
+    gins.push_back(&gb);
+  }
+  std::vector<tensor_t *> outs = {&tout}, gouts = {&gout};
+  l.set_parallelize(true);
+  l.back_propagation(ins, outs, gouts, gins);
+  from_tensor(gin, din, in_size);
+  from_tensor(gW, dW_rows, lenW);
+  if (has_bias) from_tensor(gb, db_rows, out_size);
+  return 0;
+}
+
+// ---------------------------------------------------------------- pooling
+namespace {
+std::unique_ptr<max_pooling_layer> make_maxpool(const b200_pool_desc *d, int ceil_mode,
+                                                int pad_same) {
+  return std::unique_ptr<max_pooling_layer>(new max_pooling_layer(
+    d->in_w, d->in_h, d->in_c, d->pool_w, d->pool_h, d->stride_w, d->stride_h, ceil_mode != 0,
+    pad_same ? padding::same : padding::valid, core::backend_t::internal));
+}
+}  // namespace
+
+REF_API int ref_maxpool_fwd_bwd(const b200_pool_desc *d, int ceil_mode, int pad_same,
+                                const float *in, float *out, const float *dout, float *din,
+                                int B) {
+  auto l = make_maxpool(d, ceil_mode, pad_same);
+  size_t in_len = (size_t)d->in_c * d->in_h * d->in_w;
+  size_t out_len = l->out_shape()[0].size();
+  if (out_len != (size_t)d->in_c * d->out_h * d->out_w) return 1;
+  tensor_t tin = to_tensor(in, B, in_len), tout(B, vec_t(out_len));
+  std::vector<tensor_t *> ins = {&tin}, outs = {&tout};
+  l->setup(false);
+  l->set_sample_count(B);
+  l->set_parallelize(true);
+  l->forward_propagation(ins, outs);
+  from_tensor(tout, out, out_len);
+  if (dout && din) {
+    tensor_t gout = to_tensor(dout, B, out_len), gin(B, vec_t(in_len));
+    std::vector<tensor_t *> gouts = {&gout}, gins = {&gin};
+    l->back_propagation(ins, outs, gouts, gins);
+    from_tensor(gin, din, in_len);
+  }
+  return 0;
+}
+
+REF_API int ref_avgpool_fwd_bwd(const b200_pool_desc *d, const float *in, const float *W,
+                                const float *bias, float *out, const float *dout, float *din,
+                                float *dW_rows, float *db_rows, int B) {
+  average_pooling_layer l(d->in_w, d->in_h, d->in_c, d->pool_w, d->pool_h, d->stride_w,
+                          d->stride_h, false, padding::valid);
+  size_t in_len = (size_t)d->in_c * d->in_h * d->in_w;
+  size_t out_len = l.out_shape()[0].size();
+  size_t wlen = (size_t)d->pool_w * d->pool_h * d->in_c;
+  if (out_len != (size_t)d->in_c * d->out_h * d->out_w) return 1;
+  if (l.in_shape()[1].size() != wlen) return 2;
+  tensor_t tin = to_tensor(in, B, in_len), tW = to_tensor(W, 1, wlen),
+           tb = to_tensor(bias, 1, d->in_c), tout(B, vec_t(out_len));
+  std::vector<tensor_t *> ins = {&tin, &tW, &tb}, outs = {&tout};
+  l.set_parallelize(true);
+  l.forward_propagation(ins, outs);
+  from_tensor(tout, out, out_len);
+  if (dout && din) {
+    tensor_t gout = to_tensor(dout, B, out_len), gin(B, vec_t(in_len)), gW(B, vec_t(wlen)),
+             gb(B, vec_t(d->in_c));
+    std::vector<tensor_t *> gouts = {&gout}, gins = {&gin, &gW, &gb};
+    l.back_propagation(ins, outs, gouts, gins);
+    from_tensor(gin, din, in_len);
+    from_tensor(gW, dW_rows, wlen);
+    from_tensor(gb, db_rows, d->in_c);
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------- activations / loss
+namespace {
+std::unique_ptr<activation_layer> make_act(int kind, size_t dim) {
+  if (kind == B200_ACT_RELU) return std::unique_ptr<activation_layer>(new relu_layer(dim));
+  if (kind == B200_ACT_TANH) return std::unique_ptr<activation_layer>(new tanh_layer(dim));
+  return std::unique_ptr<activation_layer>(new softmax_layer(dim));
+}
+}  // namespace
+
+REF_API int ref_act_fwd_bwd(int kind, const float *x, float *y, const float *dy, float *dx,
+                            int dim, int B) {
+  auto l = make_act(kind, dim);
+  tensor_t tx = to_tensor(x, B, dim), ty(B, vec_t(dim));
+  std::vector<tensor_t *> ins = {&tx}, outs = {&ty};
+  l->forward_propagation(ins, outs);
+  from_tensor(ty, y, dim);
+  if (dy && dx) {
+    tensor_t gy = to_tensor(dy, B, dim), gx(B, vec_t(dim));
+    std::vector<tensor_t *> gouts = {&gy}, gins = {&gx};
+    l->back_propagation(ins, outs, gouts, gins);
+    from_tensor(gx, dx, dim);
+  }
+  return 0;
+}
+
+REF_API int ref_loss_grad(int kind, const float *y, const float *t, float *dy, int dim, int B) {
+  for (int n = 0; n < B; ++n) {
+    vec_t vy(y + (size_t)n * dim, y + (size_t)(n + 1) * dim);
+    vec_t vt(t + (size_t)n * dim, t + (size_t)(n + 1) * dim);
+    vec_t g = kind == B200_LOSS_MSE              ? gradient<mse>(vy, vt)
+              : kind == B200_LOSS_CROSS_ENTROPY ? gradient<cross_entropy>(vy, vt)
+                                                : gradient<cross_entropy_multiclass>(vy, vt);
+    std::copy(g.begin(), g.end(), dy + (size_t)n * dim);
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------- merge + optimizers
+// `steps` consecutive optimizer::update calls with the same gradient on one
+// tensor, exactly what test/test_optimizers.h does.
+REF_API int ref_opt_steps(int kind, const b200_opt_hyper *h, const float *dW, float *W, size_t len,
+                          int steps) {
+  vec_t vW(W, W + len), vdW(dW, dW + len);
+  if (kind == B200_OPT_ADAGRAD) {
+    adagrad o;
+    o.alpha = h->alpha;
+    for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
+  } else if (kind == B200_OPT_ADAM) {
+    adam o;
+    o.alpha = h->alpha;
+    o.b1 = h->b1;
+    o.b2 = h->b2;
+    o.b1_t = h->b1_t;
+    o.b2_t = h->b2_t;
+    for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
+  } else {
+    momentum o;
+    o.alpha = h->alpha;
+    o.mu = h->mu;
+    o.lambda = h->lambda;
+    for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
+  }
+  std::copy(vW.begin(), vW.end(), W);
+  return 0;
+}
+
+// ---------------------------------------------------------------- quantization helpers
+REF_API int64_t ref_f2q_unclamped(int bits, float input, float mn, float mx) {
+  return bits == 8 ? core::kernels::float_to_quantized_unclamped<uint8_t>(input, mn, mx)
+                   : core::kernels::float_to_quantized_unclamped<int32_t>(input, mn, mx);
+}
+REF_API int64_t ref_f2q(int bits, float input, float mn, float mx) {
+  return bits == 8 ? (int64_t)core::kernels::float_to_quantized<uint8_t>(input, mn, mx)
+                   : (int64_t)core::kernels::float_to_quantized<int32_t>(input, mn, mx);
+}
+REF_API float ref_q2f(int bits, int64_t q, float mn, float mx) {
+  return bits == 8 ? core::kernels::quantized_to_float<uint8_t>((uint8_t)q, mn, mx)
+                   : core::kernels::quantized_to_float<int32_t>((int32_t)q, mn, mx);
+}
+REF_API void ref_requantize_many_i32_u8(const int32_t *input, size_t count, float min_in,
+                                        float max_in, float min_out, float max_out,
+                                        uint8_t *output) {
+  std::vector<int32_t> tmp(input, input + count);
+  core::kernels::requantize_many_in_new_range<int32_t, uint8_t>(tmp.data(), count, min_in, max_in,
+                                                                min_out, max_out, output);
+}
+REF_API void ref_quantize_down_and_shrink_range(const int32_t *input, size_t count, float min_in,
+                                                float max_in, float *min_new, float *max_new,
+                                                uint8_t *output) {
+  std::vector<int32_t> tmp(input, input + count);
+  std::vector<uint8_t> out(count);
+  float_t mn, mx;
+  core::kernels::quantize_down_and_shrink_range<int32_t, uint8_t>(tmp, min_in, max_in, &mn, &mx,
+                                                                  &out);
+  *min_new = mn;
+  *max_new = mx;
+  std::copy(out.begin(), out.end(), output);
+}
+
+// quantized_convolutional_layer::forward_propagation, UNPADDED input rows.
+REF_API int ref_qconv2d_fwd(const b200_conv_desc *d, const float *in, const float *W,
+                            const float *bias, float *out, int B) {
+  quantized_convolutional_layer l(d->in_w, d->in_h, d->k_w, d->k_h, d->in_c, d->out_c,
+                                  d->pad_same ? padding::same : padding::valid, d->has_bias != 0,
+                                  d->stride_w, d->stride_h, core::backend_t::internal);
+  size_t in_len = (size_t)d->in_c * d->in_h * d->in_w;
+  size_t out_len = l.out_shape()[0].size();
+  if (out_len != (size_t)d->out_c * d->out_h * d->out_w) return 1;
+  size_t lenW = (size_t)d->out_c * d->in_c * d->k_h * d->k_w;
+  tensor_t tin = to_tensor(in, B, in_len), tW = to_tensor(W, 1, lenW),
+           tb = to_tensor(d->has_bias ? bias : nullptr, 1, d->out_c), tout(B, vec_t(out_len));
+  std::vector<tensor_t *> ins = {&tin, &tW, &tb}, outs = {&tout};
+  l.set_parallelize(true);
+  l.forward_propagation(ins, outs);
+  from_tensor(tout, out, out_len);
+  return 0;
+}
+
+// ---------------------------------------------------------------- whole network
+namespace {
+
+struct RefNet {
+  network<sequential> net;
+  std::vector<b200_layer_spec> specs;
+  adagrad o_adagrad;
+  adam o_adam;
+  momentum o_momentum;
+  size_t in_dim = 0, out_dim = 0, n_params = 0;
+};
+
+void add_layer(RefNet *r, const b200_layer_spec &s, size_t prev_dim) {
+  switch (s.kind) {
+    case B200_LAYER_CONV: {
+      const b200_conv_desc *d = &s.conv;
+      r->net << convolutional_layer(d->in_w, d->in_h, d->k_w, d->k_h, d->in_c, d->out_c,
+                                    make_table(d), d->pad_same ? padding::same : padding::valid,
+                                    d->has_bias != 0, d->stride_w, d->stride_h, d->dil_w, d->dil_h,
+                                    core::backend_t::internal);
+      break;
+    }
+    case B200_LAYER_FC:
+      r->net << fully_connected_layer(s.fc_in, s.fc_out, s.fc_has_bias != 0,
+                                      core::backend_t::internal);
+      break;
+    case B200_LAYER_MAXPOOL:
+      r->net << max_pooling_layer(s.pool.in_w, s.pool.in_h, s.pool.in_c, s.pool.pool_w,
+                                  s.pool.pool_h, s.pool.stride_w, s.pool.stride_h, false,
+                                  padding::valid, core::backend_t::internal);
+      break;
+    case B200_LAYER_AVGPOOL:
+      r->net << average_pooling_layer(s.pool.in_w, s.pool.in_h, s.pool.in_c, s.pool.pool_w,
+                                      s.pool.pool_h, s.pool.stride_w, s.pool.stride_h, false,
+                                      padding::valid);
+      break;
+    case B200_LAYER_RELU: r->net << relu_layer(prev_dim); break;
+    case B200_LAYER_TANH: r->net << tanh_layer(prev_dim); break;
+    case B200_LAYER_SOFTMAX: r->net << softmax_layer(prev_dim); break;
+    default: throw nn_error("unknown layer kind");
+  }
+}
+
+size_t spec_out_dim(const b200_layer_spec &s, size_t prev) {
+  switch (s.kind) {
+    case B200_LAYER_CONV: return (size_t)s.conv.out_c * s.conv.out_h * s.conv.out_w;
+    case B200_LAYER_FC: return s.fc_out;
+    case B200_LAYER_MAXPOOL:
+    case B200_LAYER_AVGPOOL: return (size_t)s.pool.in_c * s.pool.out_h * s.pool.out_w;
+    default: return prev;
+  }
+}
+
+}  // namespace
+
+REF_API void *ref_net_create(const b200_layer_spec *specs, int n_layers, unsigned seed) {
+  try {
+    RefNet *r = new RefNet();
+    r->specs.assign(specs, specs + n_layers);
+    size_t prev = 0;
+    for (int i = 0; i < n_layers; ++i) {
+      if (i == 0) {
+        const b200_layer_spec &s = specs[0];
+        r->in_dim = s.kind == B200_LAYER_CONV ? (size_t)s.conv.in_c * s.conv.in_h * s.conv.in_w
+                    : s.kind == B200_LAYER_FC ? (size_t)s.fc_in
+                                              : (size_t)s.pool.in_c * s.pool.in_h * s.pool.in_w;
+      }
+      add_layer(r, specs[i], prev);
+      prev = spec_out_dim(specs[i], prev);
+    }
+    r->out_dim = prev;
+    // deterministic weights: seed, then redraw every layer in order
+    set_random_seed(seed);
+    r->net.init_weight();
+    for (size_t i = 0; i < r->net.depth(); ++i)
+      for (auto *w : r->net[i]->weights()) r->n_params += w->size();
+    return r;
+  } catch (const std::exception &e) {
+    fprintf(stderr, "ref_net_create: %s\n", e.what());
+    return nullptr;
+  }
+}
+REF_API void ref_net_destroy(void *h) { delete static_cast<RefNet *>(h); }
+REF_API size_t ref_net_param_count(void *h) { return static_cast<RefNet *>(h)->n_params; }
+
+// flat parameters in network order (layer order; W before b)
+REF_API void ref_net_get_params(void *h, float *dst) {
+  RefNet *r = static_cast<RefNet *>(h);
+  for (size_t i = 0; i < r->net.depth(); ++i)
+    for (auto *w : r->net[i]->weights()) {
+      std::copy(w->begin(), w->end(), dst);
+      dst += w->size();
+    }
+}
+REF_API void ref_net_set_params(void *h, const float *src) {
+  RefNet *r = static_cast<RefNet *>(h);
+  for (size_t i = 0; i < r->net.depth(); ++i)
+    for (auto *w : r->net[i]->weights()) {
+      std::copy(src, src + w->size(), w->begin());
+      src += w->size();
+    }
+}
+
+REF_API int ref_net_predict(void *h, const float *x, float *out, int B) {
+  RefNet *r = static_cast<RefNet *>(h);
+  try {
+    for (int n = 0; n < B; ++n) {
+      vec_t in(x + (size_t)n * r->in_dim, x + (size_t)(n + 1) * r->in_dim);
+      vec_t o = r->net.predict(in);
+      std::copy(o.begin(), o.end(), out + (size_t)n * r->out_dim);
+    }
+  } catch (const std::exception &e) {
+    fprintf(stderr, "ref_net_predict: %s\n", e.what());
+    return 1;
+  }
+  return 0;
+}
+
+// network::fit<Loss>(optimizer, inputs, targets, batch, 1 epoch): `steps`
+// mini-batches of `batch` samples (x holds steps*batch rows).  Optimizer
+// objects persist across calls (state and Adam powers carry on).  Returns the
+// seconds spent inside fit().
+REF_API double ref_net_fit(void *h, const float *x, const float *t, int batch, int steps,
+                           int loss_kind, int opt_kind, const b200_opt_hyper *hy) {
+  RefNet *r = static_cast<RefNet *>(h);
+  size_t N = (size_t)batch * steps;
+  std::vector<vec_t> in(N), tgt(N);
+  for (size_t n = 0; n < N; ++n) {
+    in[n].assign(x + n * r->in_dim, x + (n + 1) * r->in_dim);
+    tgt[n].assign(t + n * r->out_dim, t + (n + 1) * r->out_dim);
+  }
+  r->o_adagrad.alpha = hy->alpha;
+  r->o_adam.alpha = hy->alpha;
+  r->o_adam.b1 = hy->b1;
+  r->o_adam.b2 = hy->b2;
+  r->o_momentum.alpha = hy->alpha;
+  r->o_momentum.mu = hy->mu;
+  r->o_momentum.lambda = hy->lambda;
+  auto t0 = std::chrono::steady_clock::now();
+  try {
+    auto nop = []() {};
+    // fit() calls optimizer.reset() (network.h:856), which clears the state
+    // maps but not Adam's powers (optimizer.h:36-38)
+    if (opt_kind == B200_OPT_ADAGRAD) {
+      if (loss_kind == B200_LOSS_MSE)
+        r->net.fit<mse>(r->o_adagrad, in, tgt, batch, 1, nop, nop);
+      else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
+        r->net.fit<cross_entropy>(r->o_adagrad, in, tgt, batch, 1, nop, nop);
+      else
+        r->net.fit<cross_entropy_multiclass>(r->o_adagrad, in, tgt, batch, 1, nop, nop);
+    } else if (opt_kind == B200_OPT_ADAM) {
+      if (loss_kind == B200_LOSS_MSE)
+        r->net.fit<mse>(r->o_adam, in, tgt, batch, 1, nop, nop);
+      else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
+        r->net.fit<cross_entropy>(r->o_adam, in, tgt, batch, 1, nop, nop);
+      else
+        r->net.fit<cross_entropy_multiclass>(r->o_adam, in, tgt, batch, 1, nop, nop);
+    } else {
+      if (loss_kind == B200_LOSS_MSE)
+        r->net.fit<mse>(r->o_momentum, in, tgt, batch, 1, nop, nop);
+      else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
+        r->net.fit<cross_entropy>(r->o_momentum, in, tgt, batch, 1, nop, nop);
+      else
+        r->net.fit<cross_entropy_multiclass>(r->o_momentum, in, tgt, batch, 1, nop, nop);
+    }
+  } catch (const std::exception &e) {
+    fprintf(stderr, "ref_net_fit: %s\n", e.what());
+    return -1.0;
+  }
+  auto t1 = std::chrono::steady_clock::now();
+  return std::chrono::duration<double>(t1 - t0).count();
+}
+
+REF_API void ref_net_adam_powers(void *h, float *b1_t, float *b2_t) {
+  RefNet *r = static_cast<RefNet *>(h);
+  *b1_t = r->o_adam.b1_t;
+  *b2_t = r->o_adam.b2_t;
+}
+
+// Timed layer-level passes for the CPU baseline of single-layer workloads:
+// `reps` forward (+ backward when with_bwd) passes of one convolution layer.
+REF_API double ref_time_conv(const b200_conv_desc *d, const float *in, const float *W,
+                             const float *bias, const float *dout, int B, int with_bwd, int reps) {
+  auto l = make_conv(d);
+  size_t in_len = (size_t)d->in_c * d->in_h * d->in_w;
+  size_t out_len = (size_t)d->out_c * d->out_h * d->out_w;
+  size_t lenW = (size_t)d->out_c * d->in_c * d->k_h * d->k_w;
+  tensor_t tin = to_tensor(in, B, in_len), tW = to_tensor(W, 1, lenW),
+           tb = to_tensor(d->has_bias ? bias : nullptr, 1, d->out_c), tout(B, vec_t(out_len));
+  tensor_t gout = to_tensor(dout, B, out_len), gin(B, vec_t(in_len)), gW(B, vec_t(lenW)),
+           gb(B, vec_t(d->out_c));
+  std::vector<tensor_t *> ins = {&tin, &tW, &tb}, gins = {&gin, &gW, &gb};
+  std::vector<tensor_t *> outs = {&tout}, gouts = {&gout};
+  l->setup(false);
+  l->set_sample_count(B);
+  l->set_parallelize(true);
+  auto t0 = std::chrono::steady_clock::now();
+  for (int r = 0; r < reps; ++r) {
+    l->forward_propagation(ins, outs);
+    if (with_bwd) l->back_propagation(ins, outs, gouts, gins);
+  }
+  auto t1 = std::chrono::steady_clock::now();
+  return std::chrono::duration<double>(t1 - t0).count();
+}

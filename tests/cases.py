@@ -1,0 +1,263 @@
+"""Seeded test cases shared by the golden-fixture generator, the CPU tests of the
+oracle and the GPU parity tests.  Every case regenerates its inputs from its
+seed, so a fixture only has to store the reference's outputs."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from tiny_cnn_b200._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_RELU,
+                                LAYER_SOFTMAX, LAYER_TANH, LayerSpec, OptHyper)
+from tiny_cnn_b200.network import LENET_TABLE
+from tiny_cnn_b200.ops import conv_params, hyper, maxpool_params
+
+_rng_tbl = np.random.default_rng(5)
+RANDOM_TABLE_4x6 = (_rng_tbl.random((4, 6)) > 0.4).astype(np.uint8)
+RANDOM_TABLE_4x6[0, :] = 1  # every output keeps at least one input
+
+# name -> convolution case.  w,h,c: input; k: window (kw,kh); oc: output maps
+CONV_CASES = {
+    "valid3x3": dict(w=8, h=8, c=3, kw=3, kh=3, oc=4, same=False, bias=True, B=3, seed=1),
+    "same3x3": dict(w=8, h=8, c=3, kw=3, kh=3, oc=4, same=True, bias=True, B=3, seed=2),
+    "same5x5_rect": dict(w=12, h=10, c=2, kw=5, kh=5, oc=6, same=True, bias=True, B=2, seed=3),
+    "valid5x5_tbl": dict(w=10, h=10, c=4, kw=5, kh=5, oc=6, same=False, bias=True, B=3, seed=4,
+                         table=RANDOM_TABLE_4x6),
+    "stride2": dict(w=9, h=9, c=2, kw=3, kh=3, oc=3, same=False, bias=True, B=2, seed=5, sw=2, sh=2),
+    "stride2_same": dict(w=9, h=8, c=2, kw=3, kh=3, oc=3, same=True, bias=True, B=2, seed=6, sw=2, sh=2),
+    "dilation2": dict(w=11, h=11, c=2, kw=3, kh=3, oc=3, same=False, bias=True, B=2, seed=7, dw=2, dh=2),
+    "nobias": dict(w=10, h=10, c=4, kw=5, kh=5, oc=6, same=False, bias=False, B=2, seed=8),
+    "rect_kernel": dict(w=9, h=10, c=2, kw=3, kh=2, oc=3, same=False, bias=True, B=2, seed=9),
+    "even_same": dict(w=8, h=8, c=2, kw=4, kh=4, oc=3, same=True, bias=True, B=2, seed=10),
+    "lenet_c1": dict(w=32, h=32, c=1, kw=5, kh=5, oc=6, same=False, bias=True, B=4, seed=11),
+    "lenet_c3": dict(w=14, h=14, c=6, kw=5, kh=5, oc=16, same=False, bias=True, B=4, seed=12,
+                     table=LENET_TABLE),
+    "lenet_c5": dict(w=5, h=5, c=16, kw=5, kh=5, oc=120, same=False, bias=True, B=4, seed=13),
+    "cifar_c1": dict(w=32, h=32, c=3, kw=5, kh=5, oc=32, same=True, bias=True, B=3, seed=14),
+    "cifar_c2": dict(w=16, h=16, c=32, kw=5, kh=5, oc=32, same=True, bias=True, B=3, seed=15),
+    "cifar_c3": dict(w=8, h=8, c=32, kw=5, kh=5, oc=64, same=True, bias=True, B=5, seed=16),
+    "sweep3x3_small": dict(w=14, h=14, c=16, kw=3, kh=3, oc=24, same=True, bias=True, B=2, seed=17),
+    "odd_sizes": dict(w=13, h=7, c=5, kw=3, kh=3, oc=7, same=True, bias=True, B=3, seed=18),
+    "one_sample": dict(w=6, h=6, c=1, kw=3, kh=3, oc=1, same=False, bias=True, B=1, seed=19),
+}
+
+
+def conv_desc(c, algo=0, input_is_padded=False):
+    return conv_params(c["w"], c["h"], c["c"], c["kw"], c["kh"], c["oc"], c["same"], c["bias"],
+                       c.get("sw", 1), c.get("sh", 1), c.get("dw", 1), c.get("dh", 1),
+                       c.get("table"), algo, input_is_padded)
+
+
+def gen_conv_inputs(c, d):
+    """x ~ N(0,1), W ~ U(-0.5, 0.5), b ~ U(-0.1, 0.1), dy ~ N(0,1) from the case seed."""
+    rng = np.random.default_rng(c["seed"])
+    B = c["B"]
+    x = rng.standard_normal((B, c["c"] * c["h"] * c["w"])).astype(np.float32)
+    if c.get("xrange"):
+        lo, hi = c["xrange"]
+        x = rng.uniform(lo, hi, x.shape).astype(np.float32)
+    W = rng.uniform(-0.5, 0.5, c["oc"] * c["c"] * c["kh"] * c["kw"]).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, c["oc"]).astype(np.float32) if c["bias"] else None
+    if c.get("zero_bias"):
+        b = np.zeros(c["oc"], dtype=np.float32)
+    dy = rng.standard_normal((B, d.out_c * d.out_h * d.out_w)).astype(np.float32)
+    return x, W, b, dy
+
+
+FC_CASES = {
+    "small": dict(B=3, **{"in": 7, "out": 5}, bias=True, seed=21),
+    "nobias": dict(B=2, **{"in": 9, "out": 4}, bias=False, seed=22),
+    "lenet_f6": dict(B=16, **{"in": 120, "out": 10}, bias=True, seed=23),
+    "cifar_fc1": dict(B=8, **{"in": 1024, "out": 64}, bias=True, seed=24),
+    "ragged": dict(B=5, **{"in": 130, "out": 67}, bias=True, seed=25),
+}
+
+MAXPOOL_CASES = {
+    "2x2": dict(w=8, h=8, c=3, pw=2, ph=2, sw=2, sh=2, B=3, seed=31),
+    "overlap": dict(w=7, h=7, c=2, pw=3, ph=3, sw=2, sh=2, B=2, seed=32),
+    "stride1_same": dict(w=6, h=5, c=2, pw=2, ph=2, sw=1, sh=1, same=1, B=2, seed=33),
+    "gap": dict(w=9, h=9, c=2, pw=2, ph=2, sw=3, sh=3, B=2, seed=34),
+    "ceil": dict(w=7, h=7, c=2, pw=2, ph=2, sw=2, sh=2, ceil=1, B=2, seed=35),
+    "cifar_p1": dict(w=32, h=32, c=32, pw=2, ph=2, sw=2, sh=2, B=2, seed=36),
+    "rect": dict(w=8, h=6, c=2, pw=2, ph=1, sw=2, sh=1, B=2, seed=37),
+}
+
+AVGPOOL_CASES = {
+    "2x2": dict(w=8, h=8, c=3, pw=2, ph=2, sw=2, sh=2, B=3, seed=41),
+    "lenet_s2": dict(w=28, h=28, c=6, pw=2, ph=2, sw=2, sh=2, B=4, seed=42),
+    "overlap": dict(w=6, h=6, c=2, pw=2, ph=2, sw=1, sh=1, B=2, seed=43),
+    "3x3": dict(w=9, h=9, c=2, pw=3, ph=3, sw=3, sh=3, B=2, seed=44),
+}
+
+
+def pool_desc(c):
+    return maxpool_params(c["w"], c["h"], c["c"], c["pw"], c["ph"], c["sw"], c["sh"],
+                          bool(c.get("ceil", 0)), bool(c.get("same", 0)))
+
+
+ACT_CASES = {
+    "relu": dict(kind=1, B=4, dim=37, seed=51),
+    "tanh": dict(kind=2, B=4, dim=37, seed=52, scale=2.0),
+    "softmax": dict(kind=3, B=6, dim=10, seed=53, scale=3.0),
+    "softmax_wide": dict(kind=3, B=3, dim=33, seed=54, scale=5.0),
+}
+
+# quantized forward: x ~ U[-1, 1], W ~ U[-0.5, 0.5] as the benchmark configuration states
+QCONV_CASES = {
+    "valid5x5": dict(w=12, h=12, c=4, kw=5, kh=5, oc=6, same=False, bias=True, B=3, seed=61,
+                     xrange=(-1, 1)),
+    "zero_bias": dict(w=12, h=12, c=4, kw=5, kh=5, oc=6, same=False, bias=True, B=2, seed=62,
+                      xrange=(-1, 1), zero_bias=True),
+    "stride2": dict(w=12, h=12, c=4, kw=5, kh=5, oc=8, same=False, bias=True, B=2, seed=63,
+                    xrange=(-1, 1), sw=2, sh=2),
+    "cfg5_small_batch": dict(w=28, h=28, c=32, kw=5, kh=5, oc=64, same=False, bias=True, B=2, seed=65,
+                             xrange=(-1, 1)),
+}
+
+# padding::same: the reference's quantized layer never allocates its padded
+# staging buffer (quantized_convolutional_layer.h:349-358 `init()` has no
+# caller), so it cannot be run; the kernel restatement still defines the result
+# for an already padded input.
+QCONV_ORACLE_ONLY = {
+    "same3x3": dict(w=10, h=10, c=2, kw=3, kh=3, oc=10, same=True, bias=True, B=2, seed=64,
+                    xrange=(-1, 1)),
+}
+
+QFC_CASES = {
+    "small": dict(B=3, **{"in": 40, "out": 12}, bias=True, seed=71),
+    "nobias": dict(B=2, **{"in": 33, "out": 7}, bias=False, seed=72),
+    "wide": dict(B=2, **{"in": 1152, "out": 64}, bias=True, seed=73),
+}
+
+
+def hyper_for(kind: int) -> OptHyper:
+    """Default hyper-parameters of the reference optimizers (optimizer.h:57-58,104-110,203)."""
+    if kind == 0:
+        return hyper(alpha=0.01)
+    if kind == 1:
+        return hyper(alpha=0.001, b1=0.9, b2=0.999, b1_t=0.9, b2_t=0.999)
+    return hyper(alpha=0.01, mu=0.9, lambda_=0.0)
+
+
+# ---- networks ------------------------------------------------------------------------------
+def _conv(w, h, k, c, oc, same=False, table=None):
+    s = LayerSpec()
+    s.kind = LAYER_CONV
+    d = conv_params(w, h, c, k, k, oc, same, True, table=table)
+    s.conv = d
+    return s, d
+
+
+def _fc(i, o):
+    s = LayerSpec()
+    s.kind, s.fc_in, s.fc_out, s.fc_has_bias = LAYER_FC, i, o, 1
+    return s, None
+
+
+def _pool(kind, w, h, c, p):
+    s = LayerSpec()
+    s.kind = kind
+    s.pool = maxpool_params(w, h, c, p, p, p, p)
+    return s, None
+
+
+def _act(kind):
+    s = LayerSpec()
+    s.kind = kind
+    return s, None
+
+
+def build_net_specs(name):
+    """Layer specs of a named network; returns (specs, keepalive)."""
+    if name == "lenet":
+        L = [_conv(32, 32, 5, 1, 6), _act(LAYER_TANH), _pool(LAYER_AVGPOOL, 28, 28, 6, 2), _act(LAYER_TANH),
+             _conv(14, 14, 5, 6, 16, table=LENET_TABLE), _act(LAYER_TANH),
+             _pool(LAYER_AVGPOOL, 10, 10, 16, 2), _act(LAYER_TANH),
+             _conv(5, 5, 5, 16, 120), _act(LAYER_TANH), _fc(120, 10), _act(LAYER_TANH)]
+    elif name == "cifar":
+        L = [_conv(32, 32, 5, 3, 32, True), _act(LAYER_RELU), _pool(LAYER_MAXPOOL, 32, 32, 32, 2),
+             _conv(16, 16, 5, 32, 32, True), _act(LAYER_RELU), _pool(LAYER_MAXPOOL, 16, 16, 32, 2),
+             _conv(8, 8, 5, 32, 64, True), _act(LAYER_RELU), _pool(LAYER_MAXPOOL, 8, 8, 64, 2),
+             _fc(1024, 64), _act(LAYER_RELU), _fc(64, 10), _act(LAYER_SOFTMAX)]
+    elif name == "mlp_small":
+        L = [_fc(784, 96), _act(LAYER_RELU), _fc(96, 96), _act(LAYER_RELU), _fc(96, 10),
+             _act(LAYER_SOFTMAX)]
+    elif name == "tiny_conv":
+        L = [_conv(12, 12, 3, 2, 4, True), _act(LAYER_RELU), _pool(LAYER_MAXPOOL, 12, 12, 4, 2),
+             _conv(6, 6, 3, 4, 5), _act(LAYER_TANH), _fc(80, 6), _act(LAYER_SOFTMAX)]
+    else:
+        raise KeyError(name)
+    return [s for s, _ in L], [k for _, k in L]
+
+
+NET_CASES = {
+    # LeNet-5, +-1 targets through fit<mse>, adagrad lr 0.01 (benchmark config 1, fewer steps)
+    "lenet_adagrad": dict(net="lenet", B=16, steps=4, seed=101, in_dim=1024, out_dim=10, loss=0, opt=0,
+                          t_lo=-1.0, t_hi=1.0, xgen=lambda r, s: r.uniform(-1, 1, s)),
+    # CIFAR-10 net, cross-entropy after softmax, adam lr 1e-3 (benchmark config 2, small batch)
+    "cifar_adam": dict(net="cifar", B=8, steps=3, seed=102, in_dim=3072, out_dim=10, loss=1, opt=1,
+                       t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.standard_normal(s)),
+    # MLP with momentum SGD (benchmark config 4 at reduced width)
+    "mlp_momentum": dict(net="mlp_small", B=16, steps=3, seed=103, in_dim=784, out_dim=10, loss=1, opt=2,
+                         t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.uniform(0, 1, s)),
+    "tiny_conv_adam": dict(net="tiny_conv", B=5, steps=4, seed=104, in_dim=288, out_dim=6, loss=2, opt=1,
+                           t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.standard_normal(s)),
+}
+
+
+def net_layout(specs):
+    """(offset, length, fan_in, fan_out, is_weight) of every trainable tensor in update
+    order (layer order, W before b), with the fan sizes the reference layers report
+    (convolutional_layer.h:269-277, fully_connected_layer.h:51-53,
+    partial_connected_layer.h:45-47)."""
+    out, off = [], 0
+    for s in specs:
+        if s.kind == LAYER_CONV:
+            d = s.conv
+            fi = d.k_w * d.k_h * d.in_c
+            fo = (d.k_w // d.stride_w) * (d.k_h // d.stride_h) * d.out_c
+            lens = [(d.out_c * d.in_c * d.k_h * d.k_w, True)] + ([(d.out_c, False)] if d.has_bias else [])
+        elif s.kind == LAYER_FC:
+            fi, fo = s.fc_in, s.fc_out
+            lens = [(s.fc_in * s.fc_out, True)] + ([(s.fc_out, False)] if s.fc_has_bias else [])
+        elif s.kind == LAYER_AVGPOOL:
+            fi, fo = s.pool.pool_w * s.pool.pool_h, 1
+            lens = [(s.pool.pool_w * s.pool.pool_h * s.pool.in_c, True), (s.pool.in_c, False)]
+        else:
+            continue
+        for ln, is_w in lens:
+            out.append((off, ln, fi, fo, is_w))
+            off += ln
+    return out, off
+
+
+def xavier_params(specs, seed):
+    """Flat parameter vector: weights ~ U(+-sqrt(6/(fan_in+fan_out))) (weight_init.h:37-47),
+    biases 0 (layer.h:72-73), drawn from numpy's generator."""
+    layout, n = net_layout(specs)
+    rng = np.random.default_rng(seed)
+    flat = np.zeros(n, dtype=np.float32)
+    for off, ln, fi, fo, is_w in layout:
+        if is_w:
+            b = np.sqrt(6.0 / (fi + fo))
+            flat[off:off + ln] = rng.uniform(-b, b, ln).astype(np.float32)
+    return flat
+
+
+def gen_net_data(c):
+    """(x, t) of a network case: inputs from the case's generator, one-hot targets."""
+    rng = np.random.default_rng(c["seed"] + 1000)
+    n = c["B"] * c["steps"]
+    x = c["xgen"](rng, (n, c["in_dim"])).astype(np.float32)
+    labels = rng.integers(0, c["out_dim"], n)
+    t = np.full((n, c["out_dim"]), c["t_lo"], dtype=np.float32)
+    t[np.arange(n), labels] = c["t_hi"]
+    return x, t
+
+
+def merge_rows_np(rows):
+    """edge::merge_grads (node.h:89-103): rows summed in order in float32."""
+    acc = rows[0].copy()
+    for r in rows[1:]:
+        acc += r
+    return acc

@@ -1,0 +1,197 @@
+// Activations (relu, tanh, softmax) forward/backward and the loss gradients
+// that sit between the contraction kernels on the training step.
+#include <float.h>
+
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace b200 {
+
+// relu_layer.h:25-29, tanh_layer.h:24-28 -- elementwise, float4 where aligned
+__global__ void act_fwd_kernel(int kind, const float *__restrict__ x, float *__restrict__ y,
+                               size_t n4, size_t n) {
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  size_t step = (size_t)gridDim.x * blockDim.x;
+  const float4 *x4 = reinterpret_cast<const float4 *>(x);
+  float4 *y4 = reinterpret_cast<float4 *>(y);
+  for (size_t j = i; j < n4; j += step) {
+    float4 v = x4[j];
+    v.x = apply_act(v.x, kind);
+    v.y = apply_act(v.y, kind);
+    v.z = apply_act(v.z, kind);
+    v.w = apply_act(v.w, kind);
+    y4[j] = v;
+  }
+  for (size_t j = n4 * 4 + i; j < n; j += step) y[j] = apply_act(x[j], kind);
+}
+
+// relu_layer.h:31-39 dx = dy*(y>0); tanh_layer.h:30-38 dx = dy*(1-y*y)
+__device__ __forceinline__ float act_grad(int kind, float y, float dy) {
+  if (kind == B200_ACT_RELU) return dy * (y > 0.f ? 1.f : 0.f);
+  if (kind == B200_ACT_TANH) return __fmul_rn(dy, __fsub_rn(1.f, __fmul_rn(y, y)));
+  return dy;
+}
+
+__global__ void act_bwd_kernel(int kind, const float *__restrict__ y, const float *__restrict__ dy,
+                               float *__restrict__ dx, size_t n4, size_t n) {
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  size_t step = (size_t)gridDim.x * blockDim.x;
+  const float4 *y4 = reinterpret_cast<const float4 *>(y);
+  const float4 *d4 = reinterpret_cast<const float4 *>(dy);
+  float4 *o4 = reinterpret_cast<float4 *>(dx);
+  for (size_t j = i; j < n4; j += step) {
+    float4 a = y4[j], g = d4[j], o;
+    o.x = act_grad(kind, a.x, g.x);
+    o.y = act_grad(kind, a.y, g.y);
+    o.z = act_grad(kind, a.z, g.z);
+    o.w = act_grad(kind, a.w, g.w);
+    o4[j] = o;
+  }
+  for (size_t j = n4 * 4 + i; j < n; j += step) dx[j] = act_grad(kind, y[j], dy[j]);
+}
+
+// softmax_layer.h:24-34: subtract the row max, exponentiate, divide by the sum
+// accumulated in index order.  One thread per row (rows are 10 wide here).
+__global__ void softmax_fwd_kernel(const float *__restrict__ x, float *__restrict__ y, int dim,
+                                   int B) {
+  int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= B) return;
+  const float *xr = x + (size_t)n * dim;
+  float *yr = y + (size_t)n * dim;
+  float alpha = xr[0];
+  for (int j = 1; j < dim; ++j) alpha = fmaxf(alpha, xr[j]);
+  float denom = 0.f;
+  for (int j = 0; j < dim; ++j) {
+    float e = expf(xr[j] - alpha);
+    yr[j] = e;
+    denom += e;
+  }
+  for (int j = 0; j < dim; ++j) yr[j] = yr[j] / denom;
+}
+
+// softmax_layer.h:36-55: dx_j = sum_k dy_k * (k == j ? y_j(1-y_j) : -y_k*y_j)
+__global__ void softmax_bwd_kernel(const float *__restrict__ y, const float *__restrict__ dy,
+                                   float *__restrict__ dx, int dim, int B) {
+  int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= B) return;
+  const float *yr = y + (size_t)n * dim;
+  const float *gr = dy + (size_t)n * dim;
+  float *dr = dx + (size_t)n * dim;
+  for (int j = 0; j < dim; ++j) {
+    float yj = yr[j];
+    float s = 0.f;
+    for (int k = 0; k < dim; ++k) {
+      float df = (k == j) ? __fmul_rn(yj, __fsub_rn(1.f, yj)) : __fmul_rn(-yr[k], yj);
+      s = __fadd_rn(s, __fmul_rn(gr[k], df));
+    }
+    dr[j] = s;
+  }
+}
+
+// loss_function.h:28-36 (mse), :120-128 (cross_entropy), :143-150 (multiclass)
+__global__ void loss_grad_kernel(int kind, const float *__restrict__ y, const float *__restrict__ t,
+                                 float *__restrict__ dy, int dim, size_t n) {
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  size_t step = (size_t)gridDim.x * blockDim.x;
+  const float factor = 2.0f / (float)dim;
+  for (; i < n; i += step) {
+    float yi = y[i], ti = t[i], g;
+    if (kind == B200_LOSS_MSE)
+      g = __fmul_rn(factor, __fsub_rn(yi, ti));
+    else if (kind == B200_LOSS_CROSS_ENTROPY)
+      g = __fdiv_rn(__fsub_rn(yi, ti), __fmul_rn(yi, __fsub_rn(1.f, yi)));
+    else
+      g = __fdiv_rn(-ti, yi);
+    dy[i] = g;
+  }
+}
+
+// sum over the batch of E::f (loss_function.h:17-26, :107-118, :132-141)
+__global__ void loss_value_kernel(int kind, const float *__restrict__ y, const float *__restrict__ t,
+                                  float *__restrict__ out, int dim, int B) {
+  float acc = 0.f;
+  for (int n = threadIdx.x; n < B; n += blockDim.x) {
+    const float *yr = y + (size_t)n * dim;
+    const float *tr = t + (size_t)n * dim;
+    float d = 0.f;
+    for (int j = 0; j < dim; ++j) {
+      float yi = yr[j], ti = tr[j];
+      if (kind == B200_LOSS_MSE)
+        d += (yi - ti) * (yi - ti);
+      else if (kind == B200_LOSS_CROSS_ENTROPY)
+        d += -ti * logf(yi) - (1.f - ti) * logf(1.f - yi);
+      else
+        d += -ti * logf(yi);
+    }
+    if (kind == B200_LOSS_MSE) d /= (float)dim;
+    acc += d;
+  }
+  acc = block_sum(acc);
+  if (threadIdx.x == 0) *out = acc;
+}
+
+static int grid_for(size_t total, int block, int sm_count) {
+  size_t blocks = (total + block - 1) / block;
+  size_t cap = (size_t)sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B) {
+  B200_REQUIRE(kind == B200_ACT_RELU || kind == B200_ACT_TANH || kind == B200_ACT_SOFTMAX ||
+                 kind == B200_ACT_NONE,
+               "act_fwd: unknown activation %d", kind);
+  size_t n = (size_t)dim * B;
+  if (n == 0) return 0;
+  if (kind == B200_ACT_SOFTMAX) {
+    softmax_fwd_kernel<<<ceil_div(B, 128), 128, 0, ctx->stream>>>(x, y, dim, B);
+  } else {
+    size_t n4 = (aligned16(x) && aligned16(y)) ? n / 4 : 0;
+    act_fwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(kind, x, y,
+                                                                                      n4, n);
+  }
+  B200_LAUNCHED();
+  return 0;
+}
+
+int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int B) {
+  B200_REQUIRE(kind == B200_ACT_RELU || kind == B200_ACT_TANH || kind == B200_ACT_SOFTMAX ||
+                 kind == B200_ACT_NONE,
+               "act_bwd: unknown activation %d", kind);
+  size_t n = (size_t)dim * B;
+  if (n == 0) return 0;
+  if (kind == B200_ACT_SOFTMAX) {
+    softmax_bwd_kernel<<<ceil_div(B, 128), 128, 0, ctx->stream>>>(y, dy, dx, dim, B);
+  } else {
+    size_t n4 = (aligned16(y) && aligned16(dy) && aligned16(dx)) ? n / 4 : 0;
+    act_bwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+      kind, y, dy, dx, n4, n);
+  }
+  B200_LAUNCHED();
+  return 0;
+}
+
+int loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy, int dim, int B) {
+  B200_REQUIRE(kind >= B200_LOSS_MSE && kind <= B200_LOSS_CROSS_ENTROPY_MULTICLASS,
+               "loss_grad: unknown loss %d", kind);
+  size_t n = (size_t)dim * B;
+  if (n == 0) return 0;
+  loss_grad_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(kind, y, t, dy, dim,
+                                                                             n);
+  B200_LAUNCHED();
+  return 0;
+}
+
+int loss_value(b200_ctx *ctx, int kind, const float *y, const float *t, float *loss_sum, int dim,
+               int B) {
+  B200_REQUIRE(kind >= B200_LOSS_MSE && kind <= B200_LOSS_CROSS_ENTROPY_MULTICLASS,
+               "loss_value: unknown loss %d", kind);
+  loss_value_kernel<<<1, 256, 0, ctx->stream>>>(kind, y, t, loss_sum, dim, B);
+  B200_LAUNCHED();
+  return 0;
+}
+
+}  // namespace b200

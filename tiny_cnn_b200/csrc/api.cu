@@ -1,0 +1,432 @@
+// extern "C" operator entry points: argument checks, algorithm choice, scratch
+// management, and the HOST-buffer forms used by the reference-side OpKernel
+// branches.
+#include <string.h>
+
+#include "common.cuh"
+
+using namespace b200;
+
+namespace {
+
+int check_ctx(b200_ctx *ctx) {
+  B200_REQUIRE(ctx != nullptr, "context is NULL");
+  B200_CUDA(cudaSetDevice(ctx->device));
+  return 0;
+}
+
+bool use_tiled(const b200_conv_desc *d, const ConvGeom &g) {
+  if (d->algo == 1) return false;
+  return conv_tiled_ok(g);
+}
+
+int conv_fwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                  const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(batch >= 0, "conv2d_fwd: negative batch");
+  ConvGeom g;
+  B200_TRY(conv_geom_from_desc(ctx, d, &g));
+  B200_REQUIRE(in && W && out && (bias || !g.has_bias), "conv2d_fwd: NULL buffer");
+  if (batch == 0) return 0;
+  bool tiled = use_tiled(d, g);
+  B200_REQUIRE(tiled || d->algo != 2, "conv2d_fwd: tiled kernels need stride 1, dilation 1, 3x3/5x5");
+  if (tiled) {
+    void *scratch = nullptr;
+    B200_TRY(ctx_scratch(ctx, conv_tiled_fwd_scratch(g) * sizeof(float), &scratch));
+    return conv_tiled_fwd(ctx, g, in, W, bias, out, batch, B200_ACT_NONE,
+                          static_cast<float *>(scratch));
+  }
+  return conv_general_fwd(ctx, g, in, W, bias, out, batch, B200_ACT_NONE);
+}
+
+int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                  const float *dout, float *din, float *dW, float *db, int accumulate,
+                  int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(batch >= 0, "conv2d_bwd: negative batch");
+  ConvGeom g;
+  B200_TRY(conv_geom_from_desc(ctx, d, &g));
+  B200_REQUIRE(in && W && dout && dW && (db || !g.has_bias), "conv2d_bwd: NULL buffer");
+  size_t lenW = conv_weight_len(g);
+  if (batch == 0) {
+    if (!accumulate) {
+      B200_CUDA(cudaMemsetAsync(dW, 0, lenW * sizeof(float), ctx->stream));
+      if (g.has_bias) B200_CUDA(cudaMemsetAsync(db, 0, g.OC * sizeof(float), ctx->stream));
+    }
+    return 0;
+  }
+  bool tiled = use_tiled(d, g) && g.OW <= 64;
+  B200_REQUIRE(tiled || d->algo != 2,
+               "conv2d_bwd: tiled kernels need stride 1, dilation 1, 3x3/5x5, out width <= 64");
+  if (!tiled) {
+    if (din) B200_TRY(conv_general_dx(ctx, g, W, dout, din, batch));
+    return conv_general_dw(ctx, g, in, dout, dW, db, accumulate, batch);
+  }
+  size_t n_dx = din ? conv_tiled_dx_scratch(g) : 0;
+  size_t n_dw = conv_tiled_dw_scratch(ctx, g, batch);
+  size_t n_dx_al = align_up(n_dx, 64);
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, (n_dx_al + n_dw) * sizeof(float), &scratch));
+  float *s_dx = static_cast<float *>(scratch);
+  float *s_dw = s_dx + n_dx_al;
+  if (din) B200_TRY(conv_tiled_dx(ctx, g, W, dout, din, batch, s_dx));
+  int splits = 0;
+  B200_TRY(conv_tiled_dw_partials(ctx, g, in, dout, batch, s_dw, &splits));
+  size_t row = lenW + g.OC;
+  B200_TRY(merge_rows(ctx, s_dw, splits, row, dW, lenW, accumulate, &g));
+  if (g.has_bias) B200_TRY(merge_rows(ctx, s_dw + lenW, splits, row, db, g.OC, accumulate, nullptr));
+  return 0;
+}
+
+// ---- host staging ------------------------------------------------------------
+
+// Carves the context arena into device buffers for one *_host call.
+struct Stage {
+  b200_ctx *ctx;
+  char *base = nullptr;
+  size_t used = 0, cap = 0;
+  std::vector<std::pair<size_t, size_t>> plan;  // bytes per buffer, planned first
+};
+
+struct HostBuf {
+  const void *src;  // host source to upload (nullptr: none)
+  void *dst;        // host destination to download (nullptr: none)
+  size_t bytes;
+  void *dev;
+};
+
+// Allocate all buffers of one call in the arena, upload inputs.
+int stage_in(b200_ctx *ctx, HostBuf *bufs, int n) {
+  size_t total = 0;
+  for (int i = 0; i < n; ++i) total += align_up(bufs[i].bytes ? bufs[i].bytes : 4, 256);
+  void *base = nullptr;
+  B200_TRY(ctx_arena(ctx, total, &base));
+  size_t off = 0;
+  for (int i = 0; i < n; ++i) {
+    bufs[i].dev = static_cast<char *>(base) + off;
+    off += align_up(bufs[i].bytes ? bufs[i].bytes : 4, 256);
+    if (bufs[i].src && bufs[i].bytes)
+      B200_CUDA(cudaMemcpyAsync(bufs[i].dev, bufs[i].src, bufs[i].bytes, cudaMemcpyHostToDevice,
+                                ctx->stream));
+  }
+  return 0;
+}
+
+int stage_out(b200_ctx *ctx, HostBuf *bufs, int n) {
+  for (int i = 0; i < n; ++i)
+    if (bufs[i].dst && bufs[i].bytes)
+      B200_CUDA(cudaMemcpyAsync(bufs[i].dst, bufs[i].dev, bufs[i].bytes, cudaMemcpyDeviceToHost,
+                                ctx->stream));
+  B200_CUDA(cudaStreamSynchronize(ctx->stream));
+  return 0;
+}
+
+size_t conv_in_len(const b200_conv_desc *d) {
+  bool padded = d->input_is_padded || !d->pad_same;
+  return padded ? (size_t)d->in_c * d->inp_h * d->inp_w : (size_t)d->in_c * d->in_h * d->in_w;
+}
+size_t conv_out_len(const b200_conv_desc *d) { return (size_t)d->out_c * d->out_h * d->out_w; }
+size_t conv_w_len(const b200_conv_desc *d) {
+  return (size_t)d->out_c * d->in_c * d->k_h * d->k_w;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------- convolution
+int b200_conv2d_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                    const float *bias, float *out, int batch) {
+  return conv_fwd_impl(ctx, d, in, W, bias, out, batch);
+}
+
+int b200_conv2d_bwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                    const float *dout, float *din, float *dW, float *db, int accumulate,
+                    int batch) {
+  return conv_bwd_impl(ctx, d, in, W, dout, din, dW, db, accumulate, batch);
+}
+
+int b200_conv2d_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                         const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d != nullptr && batch >= 0, "conv2d_fwd_host: bad argument");
+  size_t f = sizeof(float);
+  HostBuf b[4] = {{in, nullptr, conv_in_len(d) * batch * f, nullptr},
+                  {W, nullptr, conv_w_len(d) * f, nullptr},
+                  {d->has_bias ? bias : nullptr, nullptr, d->has_bias ? d->out_c * f : 0, nullptr},
+                  {nullptr, out, conv_out_len(d) * batch * f, nullptr}};
+  B200_TRY(stage_in(ctx, b, 4));
+  B200_TRY(conv_fwd_impl(ctx, d, (const float *)b[0].dev, (const float *)b[1].dev,
+                         (const float *)b[2].dev, (float *)b[3].dev, batch));
+  return stage_out(ctx, b, 4);
+}
+
+int b200_conv2d_bwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                         const float *dout, float *din, float *dW, float *db, int accumulate,
+                         int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d != nullptr && batch >= 0, "conv2d_bwd_host: bad argument");
+  size_t f = sizeof(float);
+  size_t nb = d->has_bias ? d->out_c * f : 0;
+  HostBuf b[6] = {{in, nullptr, conv_in_len(d) * batch * f, nullptr},
+                  {W, nullptr, conv_w_len(d) * f, nullptr},
+                  {dout, nullptr, conv_out_len(d) * batch * f, nullptr},
+                  {nullptr, din, din ? conv_in_len(d) * batch * f : 0, nullptr},
+                  {accumulate ? dW : nullptr, dW, conv_w_len(d) * f, nullptr},
+                  {accumulate && nb ? db : nullptr, nb ? db : nullptr, nb, nullptr}};
+  B200_TRY(stage_in(ctx, b, 6));
+  B200_TRY(conv_bwd_impl(ctx, d, (const float *)b[0].dev, (const float *)b[1].dev,
+                         (const float *)b[2].dev, din ? (float *)b[3].dev : nullptr,
+                         (float *)b[4].dev, nb ? (float *)b[5].dev : nullptr, accumulate, batch));
+  return stage_out(ctx, b, 6);
+}
+
+// ---------------------------------------------------------------- fully connected
+int b200_fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+                const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in_size > 0 && out_size > 0 && batch >= 0, "fc_fwd: bad size");
+  B200_REQUIRE(in && W && out, "fc_fwd: NULL buffer");
+  return fc_fwd(ctx, in_size, out_size, in, W, bias, out, batch, B200_ACT_NONE);
+}
+
+int b200_fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+                const float *dout, float *din, float *dW, float *db, int accumulate, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in_size > 0 && out_size > 0 && batch >= 0, "fc_bwd: bad size");
+  B200_REQUIRE(in && W && dout && dW, "fc_bwd: NULL buffer");
+  return fc_bwd(ctx, in_size, out_size, in, W, dout, din, dW, db, accumulate, batch);
+}
+
+int b200_fc_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+                     const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in_size > 0 && out_size > 0 && batch >= 0, "fc_fwd_host: bad size");
+  size_t f = sizeof(float);
+  HostBuf b[4] = {{in, nullptr, (size_t)in_size * batch * f, nullptr},
+                  {W, nullptr, (size_t)in_size * out_size * f, nullptr},
+                  {bias, nullptr, bias ? out_size * f : 0, nullptr},
+                  {nullptr, out, (size_t)out_size * batch * f, nullptr}};
+  B200_TRY(stage_in(ctx, b, 4));
+  B200_TRY(fc_fwd(ctx, in_size, out_size, (const float *)b[0].dev, (const float *)b[1].dev,
+                  bias ? (const float *)b[2].dev : nullptr, (float *)b[3].dev, batch,
+                  B200_ACT_NONE));
+  return stage_out(ctx, b, 4);
+}
+
+int b200_fc_bwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+                     const float *dout, float *din, float *dW, float *db, int accumulate,
+                     int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in_size > 0 && out_size > 0 && batch >= 0, "fc_bwd_host: bad size");
+  size_t f = sizeof(float);
+  size_t nw = (size_t)in_size * out_size * f, nb = db ? out_size * f : 0;
+  HostBuf b[6] = {{in, nullptr, (size_t)in_size * batch * f, nullptr},
+                  {W, nullptr, nw, nullptr},
+                  {dout, nullptr, (size_t)out_size * batch * f, nullptr},
+                  {nullptr, din, din ? (size_t)in_size * batch * f : 0, nullptr},
+                  {accumulate ? dW : nullptr, dW, nw, nullptr},
+                  {accumulate && nb ? db : nullptr, db, nb, nullptr}};
+  B200_TRY(stage_in(ctx, b, 6));
+  B200_TRY(fc_bwd(ctx, in_size, out_size, (const float *)b[0].dev, (const float *)b[1].dev,
+                  (const float *)b[2].dev, din ? (float *)b[3].dev : nullptr, (float *)b[4].dev,
+                  db ? (float *)b[5].dev : nullptr, accumulate, batch));
+  return stage_out(ctx, b, 6);
+}
+
+// ---------------------------------------------------------------- pooling
+int b200_maxpool_fwd(b200_ctx *ctx, const b200_pool_desc *d, const float *in, float *out,
+                     int32_t *argmax, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && in && out && argmax && batch >= 0, "maxpool_fwd: bad argument");
+  return maxpool_fwd(ctx, *d, in, out, argmax, batch);
+}
+int b200_maxpool_bwd(b200_ctx *ctx, const b200_pool_desc *d, const float *dout,
+                     const int32_t *argmax, float *din, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && dout && argmax && din && batch >= 0, "maxpool_bwd: bad argument");
+  return maxpool_bwd(ctx, *d, dout, argmax, din, batch);
+}
+int b200_maxpool_fwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *in, float *out,
+                          int32_t *argmax, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && batch >= 0, "maxpool_fwd_host: bad argument");
+  size_t ni = (size_t)d->in_c * d->in_h * d->in_w * batch, no = (size_t)d->in_c * d->out_h * d->out_w * batch;
+  HostBuf b[3] = {{in, nullptr, ni * 4, nullptr}, {nullptr, out, no * 4, nullptr},
+                  {nullptr, argmax, no * 4, nullptr}};
+  B200_TRY(stage_in(ctx, b, 3));
+  B200_TRY(maxpool_fwd(ctx, *d, (const float *)b[0].dev, (float *)b[1].dev, (int32_t *)b[2].dev,
+                       batch));
+  return stage_out(ctx, b, 3);
+}
+int b200_maxpool_bwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *dout,
+                          const int32_t *argmax, float *din, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && batch >= 0, "maxpool_bwd_host: bad argument");
+  size_t ni = (size_t)d->in_c * d->in_h * d->in_w * batch, no = (size_t)d->in_c * d->out_h * d->out_w * batch;
+  HostBuf b[3] = {{dout, nullptr, no * 4, nullptr}, {argmax, nullptr, no * 4, nullptr},
+                  {nullptr, din, ni * 4, nullptr}};
+  B200_TRY(stage_in(ctx, b, 3));
+  B200_TRY(maxpool_bwd(ctx, *d, (const float *)b[0].dev, (const int32_t *)b[1].dev,
+                       (float *)b[2].dev, batch));
+  return stage_out(ctx, b, 3);
+}
+
+int b200_avgpool_fwd(b200_ctx *ctx, const b200_pool_desc *d, const float *in, const float *W,
+                     const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && in && W && bias && out && batch >= 0, "avgpool_fwd: bad argument");
+  return avgpool_fwd(ctx, *d, in, W, bias, out, batch);
+}
+int b200_avgpool_bwd(b200_ctx *ctx, const b200_pool_desc *d, const float *in, const float *W,
+                     const float *dout, float *din, float *dW, float *db, int accumulate,
+                     int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && in && W && dout && dW && db && batch >= 0, "avgpool_bwd: bad argument");
+  return avgpool_bwd(ctx, *d, in, W, dout, din, dW, db, accumulate, batch);
+}
+int b200_avgpool_fwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *in, const float *W,
+                          const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && batch >= 0, "avgpool_fwd_host: bad argument");
+  size_t ni = (size_t)d->in_c * d->in_h * d->in_w * batch, no = (size_t)d->in_c * d->out_h * d->out_w * batch;
+  size_t nw = (size_t)d->pool_w * d->pool_h * d->in_c;
+  HostBuf b[4] = {{in, nullptr, ni * 4, nullptr}, {W, nullptr, nw * 4, nullptr},
+                  {bias, nullptr, (size_t)d->in_c * 4, nullptr}, {nullptr, out, no * 4, nullptr}};
+  B200_TRY(stage_in(ctx, b, 4));
+  B200_TRY(avgpool_fwd(ctx, *d, (const float *)b[0].dev, (const float *)b[1].dev,
+                       (const float *)b[2].dev, (float *)b[3].dev, batch));
+  return stage_out(ctx, b, 4);
+}
+int b200_avgpool_bwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *in, const float *W,
+                          const float *dout, float *din, float *dW, float *db, int accumulate,
+                          int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && batch >= 0, "avgpool_bwd_host: bad argument");
+  size_t ni = (size_t)d->in_c * d->in_h * d->in_w * batch, no = (size_t)d->in_c * d->out_h * d->out_w * batch;
+  size_t nw = (size_t)d->pool_w * d->pool_h * d->in_c;
+  HostBuf b[6] = {{in, nullptr, ni * 4, nullptr},
+                  {W, nullptr, nw * 4, nullptr},
+                  {dout, nullptr, no * 4, nullptr},
+                  {nullptr, din, din ? ni * 4 : 0, nullptr},
+                  {accumulate ? dW : nullptr, dW, nw * 4, nullptr},
+                  {accumulate ? db : nullptr, db, (size_t)d->in_c * 4, nullptr}};
+  B200_TRY(stage_in(ctx, b, 6));
+  B200_TRY(avgpool_bwd(ctx, *d, (const float *)b[0].dev, (const float *)b[1].dev,
+                       (const float *)b[2].dev, din ? (float *)b[3].dev : nullptr,
+                       (float *)b[4].dev, (float *)b[5].dev, accumulate, batch));
+  return stage_out(ctx, b, 6);
+}
+
+// ---------------------------------------------------------------- activations / loss
+int b200_act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(x && y && dim > 0 && batch >= 0, "act_fwd: bad argument");
+  return act_fwd(ctx, kind, x, y, dim, batch);
+}
+int b200_act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim,
+                 int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(y && dy && dx && dim > 0 && batch >= 0, "act_bwd: bad argument");
+  return act_bwd(ctx, kind, y, dy, dx, dim, batch);
+}
+int b200_act_fwd_host(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(dim > 0 && batch >= 0, "act_fwd_host: bad argument");
+  size_t n = (size_t)dim * batch * 4;
+  HostBuf b[2] = {{x, nullptr, n, nullptr}, {nullptr, y, n, nullptr}};
+  B200_TRY(stage_in(ctx, b, 2));
+  B200_TRY(act_fwd(ctx, kind, (const float *)b[0].dev, (float *)b[1].dev, dim, batch));
+  return stage_out(ctx, b, 2);
+}
+int b200_act_bwd_host(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim,
+                      int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(dim > 0 && batch >= 0, "act_bwd_host: bad argument");
+  size_t n = (size_t)dim * batch * 4;
+  HostBuf b[3] = {{y, nullptr, n, nullptr}, {dy, nullptr, n, nullptr}, {nullptr, dx, n, nullptr}};
+  B200_TRY(stage_in(ctx, b, 3));
+  B200_TRY(act_bwd(ctx, kind, (const float *)b[0].dev, (const float *)b[1].dev, (float *)b[2].dev,
+                   dim, batch));
+  return stage_out(ctx, b, 3);
+}
+
+int b200_loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy, int dim,
+                   int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(y && t && dy && dim > 0 && batch >= 0, "loss_grad: bad argument");
+  return loss_grad(ctx, kind, y, t, dy, dim, batch);
+}
+int b200_loss_value(b200_ctx *ctx, int kind, const float *y, const float *t, float *loss_sum,
+                    int dim, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(y && t && loss_sum && dim > 0 && batch >= 0, "loss_value: bad argument");
+  return loss_value(ctx, kind, y, t, loss_sum, dim, batch);
+}
+
+// ---------------------------------------------------------------- merge + optimizer
+int b200_merge_grads(b200_ctx *ctx, const float *grads, int rows, size_t len, float *dst) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(grads && dst && rows >= 1, "merge_grads: bad argument");
+  return merge_rows(ctx, grads, rows, len, dst, len, 0, nullptr);
+}
+int b200_opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper *h, const float *dW, float *W,
+                    float *state0, float *state1, size_t len) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(h && dW && W, "opt_update: NULL argument");
+  return opt_update(ctx, kind, *h, dW, 1, len, nullptr, W, state0, state1, len);
+}
+int b200_merge_update(b200_ctx *ctx, int kind, const b200_opt_hyper *h, const float *grads,
+                      int rows, size_t stride, float *merged, float *W, float *state0,
+                      float *state1, size_t len) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(h && grads && W, "merge_update: NULL argument");
+  B200_REQUIRE(rows >= 1 && (rows == 1 || stride >= len), "merge_update: bad rows/stride");
+  return opt_update(ctx, kind, *h, grads, rows, stride, merged, W, state0, state1, len);
+}
+
+// ---------------------------------------------------------------- quantized
+int b200_qconv2d_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                     const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && in && W && out && batch >= 0 && (bias || !d->has_bias),
+               "qconv2d_fwd: bad argument");
+  return qconv_fwd(ctx, d, in, W, bias, out, batch);
+}
+int b200_qfc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+                 const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in && W && out && batch >= 0, "qfc_fwd: bad argument");
+  return qfc_fwd(ctx, in_size, out_size, in, W, bias, out, batch);
+}
+int b200_qconv2d_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                          const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && batch >= 0, "qconv2d_fwd_host: bad argument");
+  size_t f = sizeof(float);
+  size_t in_len = (size_t)d->in_c * d->inp_h * d->inp_w;
+  HostBuf b[4] = {{in, nullptr, in_len * batch * f, nullptr},
+                  {W, nullptr, conv_w_len(d) * f, nullptr},
+                  {d->has_bias ? bias : nullptr, nullptr, d->has_bias ? d->out_c * f : 0, nullptr},
+                  {nullptr, out, conv_out_len(d) * batch * f, nullptr}};
+  B200_TRY(stage_in(ctx, b, 4));
+  B200_TRY(qconv_fwd(ctx, d, (const float *)b[0].dev, (const float *)b[1].dev,
+                     d->has_bias ? (const float *)b[2].dev : nullptr, (float *)b[3].dev, batch));
+  return stage_out(ctx, b, 4);
+}
+int b200_qfc_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+                      const float *bias, float *out, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in_size > 0 && out_size > 0 && batch >= 0, "qfc_fwd_host: bad argument");
+  size_t f = sizeof(float);
+  HostBuf b[4] = {{in, nullptr, (size_t)in_size * batch * f, nullptr},
+                  {W, nullptr, (size_t)in_size * out_size * f, nullptr},
+                  {bias, nullptr, bias ? out_size * f : 0, nullptr},
+                  {nullptr, out, (size_t)out_size * batch * f, nullptr}};
+  B200_TRY(stage_in(ctx, b, 4));
+  B200_TRY(qfc_fwd(ctx, in_size, out_size, (const float *)b[0].dev, (const float *)b[1].dev,
+                   bias ? (const float *)b[2].dev : nullptr, (float *)b[3].dev, batch));
+  return stage_out(ctx, b, 4);
+}
+
+}  // extern "C"

@@ -1,0 +1,189 @@
+// Shared plumbing of the B200 hot-path library: context, error reporting,
+// launch accounting and the internal launcher prototypes the C ABI and the
+// device-resident training step both use.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <atomic>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "tinycnn_b200.h"
+
+namespace b200 {
+
+// ----------------------------------------------------------------------------
+// errors
+// ----------------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+void clear_error();
+
+#define B200_CUDA(expr)                                                              \
+  do {                                                                               \
+    cudaError_t e__ = (expr);                                                        \
+    if (e__ != cudaSuccess) {                                                        \
+      ::b200::set_error("%s:%d: %s -> %s", __FILE__, __LINE__, #expr,               \
+                        cudaGetErrorString(e__));                                    \
+      return 1;                                                                      \
+    }                                                                                \
+  } while (0)
+
+#define B200_REQUIRE(cond, ...)                                                      \
+  do {                                                                               \
+    if (!(cond)) {                                                                   \
+      ::b200::set_error(__VA_ARGS__);                                                \
+      return 2;                                                                      \
+    }                                                                                \
+  } while (0)
+
+#define B200_TRY(expr)                                                               \
+  do {                                                                               \
+    int r__ = (expr);                                                                \
+    if (r__ != 0) return r__;                                                        \
+  } while (0)
+
+extern std::atomic<unsigned long long> g_launches;
+
+// Check the launch just issued and count it.
+#define B200_LAUNCHED()                                                              \
+  do {                                                                               \
+    ::b200::g_launches.fetch_add(1, std::memory_order_relaxed);                     \
+    B200_CUDA(cudaGetLastError());                                                   \
+  } while (0)
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline size_t ceil_div_sz(size_t a, size_t b) { return (a + b - 1) / b; }
+static inline size_t align_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
+
+}  // namespace b200
+
+// ----------------------------------------------------------------------------
+// context
+// ----------------------------------------------------------------------------
+struct b200_ctx {
+  int device = 0;
+  int sm_count = 148;
+  size_t smem_optin = 0;  // max dynamic shared memory per block (opt-in)
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+
+  // grow-only device scratch used by kernels that need global scratch
+  // (split partial sums, re-laid-out filters).  One op at a time per context.
+  void *scratch = nullptr;
+  size_t scratch_bytes = 0;
+
+  // grow-only device arena + pinned host buffer for the *_host entry points
+  void *arena = nullptr;
+  size_t arena_bytes = 0;
+  void *pinned = nullptr;
+  size_t pinned_bytes = 0;
+
+  // device copies of connection tables, keyed by their bytes
+  std::map<std::string, uint8_t *> tbl_cache;
+};
+
+namespace b200 {
+
+int ctx_scratch(b200_ctx *ctx, size_t bytes, void **out);
+int ctx_arena(b200_ctx *ctx, size_t bytes, void **out);
+int ctx_pinned(b200_ctx *ctx, size_t bytes, void **out);
+int ctx_device_table(b200_ctx *ctx, const uint8_t *host_tbl, size_t n, const uint8_t **out);
+
+// ----------------------------------------------------------------------------
+// convolution geometry shared by the general and the tiled kernels
+// ----------------------------------------------------------------------------
+struct ConvGeom {
+  int C, HI, WI;   // geometry of the `in` / `din` buffers
+  int OC, OH, OW;  // geometry of `out` / `dout`
+  int KH, KW, SH, SW, DH, DW;
+  int pad_t, pad_l;  // in(y) = oy*SH + wy*DH - pad_t
+  int has_bias;
+  const uint8_t *tbl;  // DEVICE connected[inc*OC + o] or nullptr
+};
+
+int conv_geom_from_desc(b200_ctx *ctx, const b200_conv_desc *d, ConvGeom *g);
+size_t conv_weight_len(const ConvGeom &g);
+
+// true when the tiled (stride 1, dilation 1, 3x3 or 5x5) kernels apply
+bool conv_tiled_ok(const ConvGeom &g);
+
+// scratch sizes (in floats) of the tiled path
+size_t conv_tiled_fwd_scratch(const ConvGeom &g);
+size_t conv_tiled_dx_scratch(const ConvGeom &g);
+size_t conv_tiled_dw_scratch(const b200_ctx *ctx, const ConvGeom &g, int B);
+
+// general kernels (any stride / dilation / table)
+int conv_general_fwd(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *W,
+                     const float *bias, float *out, int B, int act);
+int conv_general_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float *dout,
+                    float *din, int B);
+int conv_general_dw(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout,
+                    float *dW, float *db, int accumulate, int B);
+
+// tiled kernels; `scratch` must hold the matching conv_tiled_*_scratch floats
+int conv_tiled_fwd(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *W,
+                   const float *bias, float *out, int B, int act, float *scratch);
+int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float *dout,
+                  float *din, int B, float *scratch);
+// Writes `*splits` partial sums of [dW | db] (row length conv_weight_len + OC)
+// into scratch; the caller merges them in row order.
+int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in,
+                           const float *dout, int B, float *scratch, int *splits);
+
+// dst (+)= sum_r src[r*stride + i], rows summed in order; optional connection
+// mask for convolution weights (entries of unconnected pairs are left alone
+// when accumulating and zeroed otherwise).
+// `mask` (may be nullptr) names a convolution whose connection table zeroes the
+// gradient of unconnected (o, inc) pairs within the first conv_weight_len entries.
+int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *dst, size_t len,
+               int accumulate, const ConvGeom *mask);
+
+// ----------------------------------------------------------------------------
+// other ops
+// ----------------------------------------------------------------------------
+int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+           const float *bias, float *out, int B, int act);
+int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+           const float *dout, float *din, float *dW, float *db, int accumulate, int B);
+
+int maxpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, float *out,
+                int32_t *argmax, int B);
+int maxpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *dout, const int32_t *argmax,
+                float *din, int B);
+int avgpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const float *W,
+                const float *bias, float *out, int B);
+int avgpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const float *W,
+                const float *dout, float *din, float *dW, float *db, int accumulate, int B);
+
+int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B);
+int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int B);
+int loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy, int dim, int B);
+int loss_value(b200_ctx *ctx, int kind, const float *y, const float *t, float *loss_sum, int dim,
+               int B);
+
+// Per-tensor segment of the flat parameter buffer for the fused update.
+struct OptSegment {
+  unsigned long long offset;
+  unsigned long long len;
+};
+int opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *grads, int rows,
+               size_t stride, float *merged, float *W, float *s0, float *s1, size_t len);
+// All tensors in one launch; Adam powers are read per tensor from the device
+// table pow_tab[2*t] = b1_t, pow_tab[2*t+1] = b2_t and advanced afterwards by
+// opt_advance_powers (one sequential float multiply per update call, which is
+// how adam::update evolves them).
+int opt_update_segments(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *grads,
+                        float *W, float *s0, float *s1, const OptSegment *segs_dev,
+                        int n_segs, size_t total, float *pow_tab);
+int opt_advance_powers(b200_ctx *ctx, float *pow_tab, int n_tensors, float b1, float b2);
+
+int qconv_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+              const float *bias, float *out, int B);
+int qfc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
+            const float *bias, float *out, int B);
+
+}  // namespace b200

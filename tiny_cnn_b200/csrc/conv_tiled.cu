@@ -1,0 +1,766 @@
+// Tiled FP32 convolution kernels for stride 1, dilation 1, 3x3 and 5x5 filters
+// (every convolution of the LeNet, CIFAR-10 and 3x3 sweep configurations).
+//
+//   conv_core_kernel      direct convolution with a register tile of
+//                         8 output pixels x 8 output channels per thread,
+//                         input tile and re-laid-out filters staged in shared
+//                         memory with cp.async, double buffered over input
+//                         channel chunks.  Used for the forward pass and, with
+//                         flipped/transposed filters and dY as input, for dX.
+//   conv_dw_kernel        dW (+db) as a batch-reduced outer product: each
+//                         thread owns OCT output channels x all KHxKW taps of
+//                         one input channel and streams 8-pixel strips of
+//                         (X, dY) from shared memory; the batch is split over
+//                         the grid and every block writes one partial sum row.
+//
+// The math is that of kernels::conv2d_op_internal
+// (tiny_dnn/core/kernels/conv2d_op_internal.h:13-74, :91-127, :130-179) with
+// zero padding applied by predicated staging instead of a padded copy
+// (tiny_dnn/core/params/conv_params.h:106-133).
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------
+// filter re-layout
+// ---------------------------------------------------------------------------
+
+// wt[(ic*KK + tap)*COp + o] = W[(o*C + ic)*KK + tap]   (0 if o >= OC or unconnected)
+__global__ void conv_prep_wt_fwd_kernel(const float *__restrict__ W, float *__restrict__ wt,
+                                        int C, int OC, int COp, int KK,
+                                        const uint8_t *__restrict__ tbl) {
+  int total = C * KK * COp;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    int o = i % COp;
+    int r = i / COp;
+    int tap = r % KK;
+    int ic = r / KK;
+    float v = 0.f;
+    if (o < OC && (!tbl || tbl[ic * OC + o])) v = W[((size_t)o * C + ic) * KK + tap];
+    wt[i] = v;
+  }
+}
+
+// wt[(o*KK + a*KW + b)*Cp + ic] = W[(o*C + ic)*KK + (KH-1-a)*KW + (KW-1-b)]
+__global__ void conv_prep_wt_dx_kernel(const float *__restrict__ W, float *__restrict__ wt, int C,
+                                       int OC, int Cp, int KH, int KW,
+                                       const uint8_t *__restrict__ tbl) {
+  int KK = KH * KW;
+  int total = OC * KK * Cp;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    int ic = i % Cp;
+    int r = i / Cp;
+    int tap = r % KK;
+    int o = r / KK;
+    int a = tap / KW, b = tap % KW;
+    float v = 0.f;
+    if (ic < C && (!tbl || tbl[ic * OC + o]))
+      v = W[((size_t)o * C + ic) * KK + (KH - 1 - a) * KW + (KW - 1 - b)];
+    wt[i] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// direct convolution core
+// ---------------------------------------------------------------------------
+
+struct CoreCfg {
+  // problem: out[n][co][y][x] = bias[co] + sum_{ci,wy,wx} wt[ci][wy][wx][co] *
+  //                             in[n][ci][y + wy - pad_t][x + wx - pad_l]
+  const float *in;
+  const float *wt;    // [CI][KH][KW][COp]
+  const float *bias;  // [CO] or nullptr
+  float *out;
+  int B, CI, HI, WI, CO, COp, HO, WO;
+  int pad_t, pad_l, act;
+  // tiling
+  int TH, TWG, NSB, OCB, ICB;
+  int THp, PITCH;
+  int tiles_x, tiles_y, tiles_oc, tiles_n;
+  int in_tile_floats, w_tile_floats, nrows;
+  unsigned pitch_magic;
+  int log2_ocb4;
+};
+
+// v / d for v*d < 2^32 through one multiply; magic 0 encodes d == 1
+__device__ __forceinline__ unsigned fastdiv(unsigned v, unsigned magic) {
+  return magic ? __umulhi(v, magic) : v;
+}
+static unsigned make_magic(unsigned d) {
+  return d <= 1 ? 0u : (unsigned)((0x100000000ULL / d) + 1ULL);
+}
+
+template <int KH, int KW, int OCT>
+__global__ void __launch_bounds__(256, 2) conv_core_kernel(const CoreCfg p) {
+  extern __shared__ __align__(16) float smem[];
+  const int tid = threadIdx.x;
+  const int nthreads = blockDim.x;
+  constexpr int KK = KH * KW;
+
+  // ---- tile coordinates -------------------------------------------------
+  int bid = blockIdx.x;
+  const int tx_ = bid % p.tiles_x;
+  bid /= p.tiles_x;
+  const int ty_ = bid % p.tiles_y;
+  bid /= p.tiles_y;
+  const int toc = bid % p.tiles_oc;
+  const int tn = bid / p.tiles_oc;
+  const int x0 = tx_ * p.TWG * 8;
+  const int y0 = ty_ * p.TH;
+  const int o0 = toc * p.OCB;
+  const int n0 = tn * p.NSB;
+
+  // ---- shared memory carve-up --------------------------------------------
+  const int stage_floats = p.in_tile_floats + p.w_tile_floats;
+  float *stage0 = smem;
+  float *stage1 = smem + stage_floats;
+  long long *rowoff = reinterpret_cast<long long *>(smem + 2 * stage_floats);
+  int *rowic = reinterpret_cast<int *>(rowoff + p.nrows);
+
+  // row table: staged row -> offset of (n, ic, y, x=0) with ic relative to the
+  // chunk base, or -1 when the row lies outside the batch / image
+  for (int r = tid; r < p.nrows; r += nthreads) {
+    int rr = r % p.THp;
+    int q = r / p.THp;
+    int ic = q % p.ICB;
+    int s = q / p.ICB;
+    int n = n0 + s;
+    int y = y0 + rr - p.pad_t;
+    long long off = -1;
+    if (n < p.B && y >= 0 && y < p.HI)
+      off = (((long long)n * p.CI + ic) * p.HI + y) * (long long)p.WI;
+    rowoff[r] = off;
+    rowic[r] = ic;
+  }
+  __syncthreads();
+
+  const int nchunks = (p.CI + p.ICB - 1) / p.ICB;
+  const long long chan_stride = (long long)p.HI * p.WI;
+  const int ocb4 = p.OCB >> 2;
+
+  auto load_chunk = [&](int chunk, float *stage) {
+    const int c0 = chunk * p.ICB;
+    float *itile = stage;
+    float *wtile = stage + p.in_tile_floats;
+    for (int idx = tid; idx < p.in_tile_floats; idx += nthreads) {
+      int row = (int)fastdiv((unsigned)idx, p.pitch_magic);
+      int j = idx - row * p.PITCH;
+      long long off = rowoff[row];
+      int ic = rowic[row];
+      int x = x0 - p.pad_l + j;
+      bool ok = off >= 0 && (c0 + ic) < p.CI && x >= 0 && x < p.WI;
+      const float *src = ok ? p.in + off + (long long)c0 * chan_stride + x : p.in;
+      cp_async4(itile + idx, src, ok);
+    }
+    const int nq = p.ICB * KK * ocb4;
+    for (int q = tid; q < nq; q += nthreads) {
+      int row = q >> p.log2_ocb4;
+      int c4 = q & (ocb4 - 1);
+      int ic = row / KK;
+      int tap = row - ic * KK;
+      int oc = o0 + c4 * 4;
+      bool ok = (c0 + ic) < p.CI && oc < p.COp;
+      const float *src = ok ? p.wt + ((size_t)(c0 + ic) * KK + tap) * p.COp + oc : p.wt;
+      cp_async16(wtile + q * 4, src, ok);
+    }
+  };
+
+  // ---- thread coordinates -------------------------------------------------
+  const int nocg = p.OCB / OCT;
+  const int ocg = tid % nocg;
+  int pg = tid / nocg;
+  const int txg = pg % p.TWG;
+  pg /= p.TWG;
+  const int ty = pg % p.TH;
+  const int s = pg / p.TH;
+
+  float acc[OCT][8];  // [oc][px]
+#pragma unroll
+  for (int o = 0; o < OCT; ++o)
+#pragma unroll
+    for (int px = 0; px < 8; ++px) acc[o][px] = 0.f;
+
+  load_chunk(0, stage0);
+  cp_async_commit();
+
+  for (int chunk = 0; chunk < nchunks; ++chunk) {
+    float *cur = (chunk & 1) ? stage1 : stage0;
+    if (chunk + 1 < nchunks) {
+      load_chunk(chunk + 1, (chunk & 1) ? stage0 : stage1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    const float *itile = cur + ((s * p.ICB) * p.THp + ty) * p.PITCH + txg * 8;
+    const float *wtile = cur + p.in_tile_floats + ocg * OCT;
+    const int icn = min(p.ICB, p.CI - chunk * p.ICB);
+    for (int ic = 0; ic < icn; ++ic) {
+      const float *irow = itile + ic * p.THp * p.PITCH;
+      const float *wrow = wtile + ic * KK * p.OCB;
+#pragma unroll
+      for (int wy = 0; wy < KH; ++wy) {
+        float xin[12];
+        {
+          const float4 *ip = reinterpret_cast<const float4 *>(irow + wy * p.PITCH);
+          float4 a = ip[0], b = ip[1], c = ip[2];
+          xin[0] = a.x; xin[1] = a.y; xin[2] = a.z; xin[3] = a.w;
+          xin[4] = b.x; xin[5] = b.y; xin[6] = b.z; xin[7] = b.w;
+          xin[8] = c.x; xin[9] = c.y; xin[10] = c.z; xin[11] = c.w;
+        }
+#pragma unroll
+        for (int wx = 0; wx < KW; ++wx) {
+          const float4 *wp = reinterpret_cast<const float4 *>(wrow + (wy * KW + wx) * p.OCB);
+          float w[OCT];
+#pragma unroll
+          for (int h = 0; h < OCT / 4; ++h) {
+            float4 wv = wp[h];
+            w[h * 4 + 0] = wv.x;
+            w[h * 4 + 1] = wv.y;
+            w[h * 4 + 2] = wv.z;
+            w[h * 4 + 3] = wv.w;
+          }
+#pragma unroll
+          for (int o = 0; o < OCT; ++o)
+#pragma unroll
+            for (int px = 0; px < 8; ++px) acc[o][px] = fmaf(w[o], xin[px + wx], acc[o][px]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- epilogue -------------------------------------------------------------
+  const int n = n0 + s;
+  const int y = y0 + ty;
+  const int xb = x0 + txg * 8;
+  if (n >= p.B || y >= p.HO || xb >= p.WO) return;
+  const bool vec = ((p.WO & 3) == 0) && (xb + 8 <= p.WO);
+#pragma unroll
+  for (int o = 0; o < OCT; ++o) {
+    int oc = o0 + ocg * OCT + o;
+    if (oc >= p.CO) continue;
+    float bv = p.bias ? p.bias[oc] : 0.f;
+    float *op = p.out + (((size_t)n * p.CO + oc) * p.HO + y) * p.WO + xb;
+    float v[8];
+#pragma unroll
+    for (int px = 0; px < 8; ++px) v[px] = apply_act(acc[o][px] + bv, p.act);
+    if (vec) {
+      reinterpret_cast<float4 *>(op)[0] = make_float4(v[0], v[1], v[2], v[3]);
+      reinterpret_cast<float4 *>(op)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+      for (int px = 0; px < 8; ++px)
+        if (xb + px < p.WO) op[px] = v[px];
+    }
+  }
+}
+
+static int ilog2(int v) {
+  int l = 0;
+  while ((1 << l) < v) ++l;
+  return l;
+}
+
+bool conv_tiled_ok(const ConvGeom &g) {
+  if (g.SH != 1 || g.SW != 1 || g.DH != 1 || g.DW != 1) return false;
+  if (!((g.KH == 3 && g.KW == 3) || (g.KH == 5 && g.KW == 5))) return false;
+  return true;
+}
+
+static int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+// Pick the tile shape for a problem with CO output channels and HO x WO outputs.
+static int core_tiling(const b200_ctx *ctx, CoreCfg &p, int KH, int KW) {
+  // Small problems (few 8x8 register tiles per SM) use 8 px x 4 oc per thread
+  // to put more threads in flight.
+  long long tiles8 = (long long)p.B * p.HO * ceil_div(p.WO, 8) * ceil_div(p.CO, 8);
+  int OCT = tiles8 < (long long)ctx->sm_count * 512 ? 4 : 8;
+  int co_r = round_up(p.CO, 8);
+  p.OCB = co_r >= 64 ? 64 : (co_r > 16 ? 32 : co_r);  // 8, 16, 32 or 64
+  p.COp = co_r;
+  int nocg = p.OCB / OCT;
+  int target_pg = 256 / nocg;
+  int wg = ceil_div(p.WO, 8);
+  p.TWG = wg <= 8 ? wg : 4;
+  if (p.TWG > target_pg) p.TWG = target_pg;
+  p.TH = target_pg / p.TWG;
+  if (p.TH > p.HO) p.TH = p.HO;
+  if (p.TH < 1) p.TH = 1;
+  p.NSB = target_pg / (p.TWG * p.TH);
+  if (p.NSB > p.B) p.NSB = p.B;
+  if (p.NSB < 1) p.NSB = 1;
+  // Enough blocks to fill the machine twice, but never below 128 threads.
+  auto blocks = [&]() {
+    return (long long)ceil_div(p.WO, p.TWG * 8) * ceil_div(p.HO, p.TH) * ceil_div(p.CO, p.OCB) *
+           ceil_div(p.B, p.NSB);
+  };
+  auto threads = [&]() { return nocg * p.TWG * p.TH * p.NSB; };
+  while (blocks() < 2LL * ctx->sm_count && p.NSB > 1 && threads() / 2 >= 128)
+    p.NSB = (p.NSB + 1) / 2;
+  while (blocks() < 2LL * ctx->sm_count && p.TH > 1 && nocg * p.TWG * ((p.TH + 1) / 2) * p.NSB >= 128)
+    p.TH = (p.TH + 1) / 2;
+  p.ICB = p.CI < 8 ? p.CI : 8;
+  p.PITCH = round_up(p.TWG * 8 + KW - 1, 4);
+  auto smem_need = [&]() {
+    p.THp = p.TH + KH - 1;
+    p.in_tile_floats = p.NSB * p.ICB * p.THp * p.PITCH;
+    p.w_tile_floats = p.ICB * KH * KW * p.OCB;
+    p.nrows = p.NSB * p.ICB * p.THp;
+    return (size_t)2 * (p.in_tile_floats + p.w_tile_floats) * 4 + (size_t)p.nrows * 12 + 16;
+  };
+  // keep two blocks per SM resident when possible
+  size_t want = ctx->smem_optin / 2 - 2048;
+  while (smem_need() > want && p.ICB > 1) p.ICB = (p.ICB + 1) / 2;
+  p.tiles_x = ceil_div(p.WO, p.TWG * 8);
+  p.tiles_y = ceil_div(p.HO, p.TH);
+  p.tiles_oc = ceil_div(p.CO, p.OCB);
+  p.tiles_n = ceil_div(p.B, p.NSB);
+  p.pitch_magic = make_magic((unsigned)p.PITCH);
+  p.log2_ocb4 = ilog2(p.OCB / 4);
+  smem_need();
+  return OCT;
+}
+
+template <int KH, int KW, int OCT>
+static int launch_core_t(b200_ctx *ctx, const CoreCfg &p, long long blocks, int threads,
+                         size_t smem) {
+  B200_CUDA(cudaFuncSetAttribute(conv_core_kernel<KH, KW, OCT>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  conv_core_kernel<KH, KW, OCT><<<(unsigned)blocks, threads, smem, ctx->stream>>>(p);
+  B200_LAUNCHED();
+  return 0;
+}
+
+static int launch_core(b200_ctx *ctx, CoreCfg &p, int KH, int KW) {
+  int OCT = core_tiling(ctx, p, KH, KW);
+  size_t smem = (size_t)2 * (p.in_tile_floats + p.w_tile_floats) * 4 + (size_t)p.nrows * 12 + 16;
+  B200_REQUIRE(smem <= ctx->smem_optin, "conv tile needs %zu bytes of shared memory (limit %zu)",
+               smem, ctx->smem_optin);
+  int threads = (p.OCB / OCT) * p.TWG * p.TH * p.NSB;
+  B200_REQUIRE(threads >= 1 && threads <= 256, "conv tile thread count %d out of range", threads);
+  long long blocks = (long long)p.tiles_x * p.tiles_y * p.tiles_oc * p.tiles_n;
+  B200_REQUIRE(blocks > 0 && blocks < 0x7fffffffLL, "conv grid too large");
+  if (KH == 3 && OCT == 8) return launch_core_t<3, 3, 8>(ctx, p, blocks, threads, smem);
+  if (KH == 3 && OCT == 4) return launch_core_t<3, 3, 4>(ctx, p, blocks, threads, smem);
+  if (KH == 5 && OCT == 8) return launch_core_t<5, 5, 8>(ctx, p, blocks, threads, smem);
+  return launch_core_t<5, 5, 4>(ctx, p, blocks, threads, smem);
+}
+
+size_t conv_tiled_fwd_scratch(const ConvGeom &g) {
+  return (size_t)g.C * g.KH * g.KW * round_up(g.OC, 8);
+}
+size_t conv_tiled_dx_scratch(const ConvGeom &g) {
+  return (size_t)g.OC * g.KH * g.KW * round_up(g.C, 8);
+}
+
+int conv_tiled_fwd(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *W,
+                   const float *bias, float *out, int B, int act, float *scratch) {
+  if (B == 0) return 0;
+  int KK = g.KH * g.KW;
+  int COp = round_up(g.OC, 8);
+  int total = g.C * KK * COp;
+  conv_prep_wt_fwd_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(W, scratch, g.C, g.OC,
+                                                                        COp, KK, g.tbl);
+  B200_LAUNCHED();
+  CoreCfg p{};
+  p.in = in;
+  p.wt = scratch;
+  p.bias = g.has_bias ? bias : nullptr;
+  p.out = out;
+  p.B = B;
+  p.CI = g.C;
+  p.HI = g.HI;
+  p.WI = g.WI;
+  p.CO = g.OC;
+  p.HO = g.OH;
+  p.WO = g.OW;
+  p.pad_t = g.pad_t;
+  p.pad_l = g.pad_l;
+  p.act = act;
+  return launch_core(ctx, p, g.KH, g.KW);
+}
+
+int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float *dout,
+                  float *din, int B, float *scratch) {
+  if (B == 0) return 0;
+  int KK = g.KH * g.KW;
+  int Cp = round_up(g.C, 8);
+  int total = g.OC * KK * Cp;
+  conv_prep_wt_dx_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(W, scratch, g.C, g.OC, Cp,
+                                                                       g.KH, g.KW, g.tbl);
+  B200_LAUNCHED();
+  CoreCfg p{};
+  p.in = dout;
+  p.wt = scratch;
+  p.bias = nullptr;
+  p.out = din;
+  p.B = B;
+  p.CI = g.OC;
+  p.HI = g.OH;
+  p.WI = g.OW;
+  p.CO = g.C;
+  p.HO = g.HI;
+  p.WO = g.WI;
+  p.pad_t = g.KH - 1 - g.pad_t;
+  p.pad_l = g.KW - 1 - g.pad_l;
+  p.act = 0;
+  return launch_core(ctx, p, g.KH, g.KW);
+}
+
+// ---------------------------------------------------------------------------
+// dW / db
+// ---------------------------------------------------------------------------
+
+struct DwCfg {
+  const float *in;    // [B][C][HI][WI]
+  const float *dout;  // [B][OC][OH][OW]
+  float *partial;     // [splits][lenW + OC]
+  int B, C, HI, WI, OC, OH, OW, pad_t, pad_l, has_bias;
+  int OCB, ICT, SL;   // block tile: OCB out channels x ICT in channels, SL strip lanes
+  int TH, TWG, TWp;   // band rows, strips per row, staged dY row length
+  int THp, PITCHX, PSX;  // staged X rows, row pitch, plane stride
+  int OCBp;           // dY tile channel pitch
+  int tiles_oc, tiles_ic, splits, bands;
+  int x_tile_floats, dy_tile_floats;
+  unsigned magic_pitchx, magic_thp, magic_twp, magic_th;
+  size_t row_len;     // lenW + OC
+};
+
+template <int KH, int KW, int OCT>
+__global__ void __launch_bounds__(256) conv_dw_kernel(const DwCfg p) {
+  extern __shared__ __align__(16) float smem[];
+  const int tid = threadIdx.x;
+  const int nthreads = blockDim.x;
+  constexpr int KK = KH * KW;
+
+  int bid = blockIdx.x;
+  const int toc = bid % p.tiles_oc;
+  bid /= p.tiles_oc;
+  const int tic = bid % p.tiles_ic;
+  const int split = bid / p.tiles_ic;
+  const int o0 = toc * p.OCB;
+  const int c0 = tic * p.ICT;
+
+  const int stage_floats = p.x_tile_floats + p.dy_tile_floats;
+  float *stage0 = smem;
+  float *stage1 = smem + stage_floats;
+
+  const int units = p.B * p.bands;
+
+  auto load_unit = [&](int u, float *stage) {
+    const int n = u / p.bands;
+    const int y0 = (u - n * p.bands) * p.TH;
+    float *xt = stage;
+    float *dyt = stage + p.x_tile_floats;
+    // X tile: [ICT][THp][PITCHX] with plane stride PSX, zero outside the image
+    const int xcount = p.ICT * p.THp * p.PITCHX;
+    for (int idx = tid; idx < xcount; idx += nthreads) {
+      int row = (int)fastdiv((unsigned)idx, p.magic_pitchx);
+      int j = idx - row * p.PITCHX;
+      int ic = (int)fastdiv((unsigned)row, p.magic_thp);
+      int r = row - ic * p.THp;
+      int y = y0 + r - p.pad_t;
+      int x = j - p.pad_l;
+      int c = c0 + ic;
+      bool ok = c < p.C && y >= 0 && y < p.HI && x >= 0 && x < p.WI;
+      const float *src =
+        ok ? p.in + (((size_t)n * p.C + c) * p.HI + y) * (size_t)p.WI + x : p.in;
+      cp_async4(xt + ic * p.PSX + r * p.PITCHX + j, src, ok);
+    }
+    // dY tile, channel-fastest: [TH][TWp][OCBp]
+    const int dcount = p.OCB * p.TH * p.TWp;
+    for (int idx = tid; idx < dcount; idx += nthreads) {
+      int row = (int)fastdiv((unsigned)idx, p.magic_twp);
+      int x = idx - row * p.TWp;
+      int oc = (int)fastdiv((unsigned)row, p.magic_th);
+      int r = row - oc * p.TH;
+      int y = y0 + r;
+      int o = o0 + oc;
+      bool ok = o < p.OC && y < p.OH && x < p.OW;
+      const float *src =
+        ok ? p.dout + (((size_t)n * p.OC + o) * p.OH + y) * (size_t)p.OW + x : p.dout;
+      cp_async4(dyt + (r * p.TWp + x) * p.OCBp + oc, src, ok);
+    }
+  };
+
+  // thread -> (output channel group, input channel, strip lane)
+  const int nocg = p.OCB / OCT;
+  const int ocg = tid % nocg;
+  int q = tid / nocg;
+  const int icl = q % p.ICT;
+  const int sl = q / p.ICT;
+  const bool do_db = p.has_bias && tic == 0 && icl == 0;
+
+  float acc[OCT][KK];
+  float dbacc[OCT];
+#pragma unroll
+  for (int o = 0; o < OCT; ++o) {
+    dbacc[o] = 0.f;
+#pragma unroll
+    for (int t = 0; t < KK; ++t) acc[o][t] = 0.f;
+  }
+
+  const int nstrips = p.TH * p.TWG;
+  int u = split;
+  if (u < units) {
+    load_unit(u, stage0);
+  }
+  cp_async_commit();
+  int it = 0;
+  for (; u < units; u += p.splits, ++it) {
+    float *cur = (it & 1) ? stage1 : stage0;
+    int un = u + p.splits;
+    if (un < units) load_unit(un, (it & 1) ? stage0 : stage1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    const float *xt = cur + icl * p.PSX;
+    const float *dyt = cur + p.x_tile_floats + ocg * OCT;
+    for (int strip = sl; strip < nstrips; strip += p.SL) {
+      int y = strip / p.TWG;
+      int xg = strip - y * p.TWG;
+      float dy[OCT][8];
+#pragma unroll
+      for (int px = 0; px < 8; ++px) {
+        const float4 *dp =
+          reinterpret_cast<const float4 *>(dyt + (y * p.TWp + xg * 8 + px) * p.OCBp);
+#pragma unroll
+        for (int h = 0; h < OCT / 4; ++h) {
+          float4 v = dp[h];
+          dy[h * 4 + 0][px] = v.x;
+          dy[h * 4 + 1][px] = v.y;
+          dy[h * 4 + 2][px] = v.z;
+          dy[h * 4 + 3][px] = v.w;
+        }
+      }
+#pragma unroll
+      for (int wy = 0; wy < KH; ++wy) {
+        const float4 *ip = reinterpret_cast<const float4 *>(xt + (y + wy) * p.PITCHX + xg * 8);
+        float4 a = ip[0], b = ip[1], c = ip[2];
+        float xin[12] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int wx = 0; wx < KW; ++wx)
+#pragma unroll
+          for (int o = 0; o < OCT; ++o)
+#pragma unroll
+            for (int px = 0; px < 8; ++px)
+              acc[o][wy * KW + wx] = fmaf(dy[o][px], xin[px + wx], acc[o][wy * KW + wx]);
+      }
+      if (do_db) {
+#pragma unroll
+        for (int o = 0; o < OCT; ++o)
+#pragma unroll
+          for (int px = 0; px < 8; ++px) dbacc[o] += dy[o][px];
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- reduce the strip lanes through shared memory (fixed order) ----------
+  constexpr int NACC = OCT * KK + OCT;
+  if (p.SL > 1) {
+    const int ntask = nocg * p.ICT;
+    const int task = icl * nocg + ocg;
+    float *red = smem;  // [SL][ntask][NACC]
+    float *mine = red + ((size_t)sl * ntask + task) * NACC;
+#pragma unroll
+    for (int o = 0; o < OCT; ++o) {
+#pragma unroll
+      for (int t = 0; t < KK; ++t) mine[o * KK + t] = acc[o][t];
+      mine[OCT * KK + o] = dbacc[o];
+    }
+    __syncthreads();
+    if (sl == 0) {
+      for (int l = 1; l < p.SL; ++l) {
+        const float *other = red + ((size_t)l * ntask + task) * NACC;
+#pragma unroll
+        for (int o = 0; o < OCT; ++o) {
+#pragma unroll
+          for (int t = 0; t < KK; ++t) acc[o][t] += other[o * KK + t];
+          dbacc[o] += other[OCT * KK + o];
+        }
+      }
+    }
+  }
+  if (sl != 0) return;
+
+  // ---- write this block's partial row ----------------------------------------
+  float *prow = p.partial + (size_t)split * p.row_len;
+  const int c = c0 + icl;
+  if (c < p.C) {
+#pragma unroll
+    for (int o = 0; o < OCT; ++o) {
+      int oc = o0 + ocg * OCT + o;
+      if (oc >= p.OC) continue;
+      float *wp = prow + ((size_t)oc * p.C + c) * KK;
+#pragma unroll
+      for (int t = 0; t < KK; ++t) wp[t] = acc[o][t];
+    }
+  }
+  if (do_db) {
+    size_t lenW = (size_t)p.OC * p.C * KK;
+#pragma unroll
+    for (int o = 0; o < OCT; ++o) {
+      int oc = o0 + ocg * OCT + o;
+      if (oc < p.OC) prow[lenW + oc] = dbacc[o];
+    }
+  }
+}
+
+static void dw_tiling(const b200_ctx *ctx, DwCfg &p, int KH, int KW, int OCT) {
+  int oc_r = round_up(p.OC, OCT);
+  p.OCB = oc_r < 32 ? oc_r : 32;
+  int nocg = p.OCB / OCT;
+  p.ICT = 256 / nocg;
+  if (p.ICT > p.C) p.ICT = p.C;
+  p.SL = 256 / (nocg * p.ICT);
+  if (p.SL < 1) p.SL = 1;
+  if (p.SL > 8) p.SL = 8;
+  p.TWG = ceil_div(p.OW, 8);
+  p.TWp = p.TWG * 8;
+  p.PITCHX = round_up(p.TWp + KW - 1, 4);
+  p.OCBp = p.OCB + 4;
+  const int NACC = OCT * KH * KW + OCT;
+  size_t limit = ctx->smem_optin;
+  size_t want = limit / 2 - 2048;  // two resident blocks per SM when it fits
+  auto need = [&](int th) {
+    p.TH = th;
+    p.THp = th + KH - 1;
+    int plane = p.THp * p.PITCHX;
+    // plane stride with (PSX/4) odd keeps 8 consecutive channels on distinct banks
+    int ps = round_up(plane, 4);
+    if (((ps / 4) & 1) == 0) ps += 4;
+    p.PSX = ps;
+    p.x_tile_floats = p.ICT * p.PSX;
+    p.dy_tile_floats = round_up(p.TH * p.TWp * p.OCBp, 4);
+    size_t stage = (size_t)(p.x_tile_floats + p.dy_tile_floats) * 4;
+    size_t red = (size_t)p.SL * nocg * p.ICT * NACC * 4;
+    size_t tot = 2 * stage;
+    return tot > red ? tot : red;
+  };
+  int th = p.OH;
+  while (th > 1 && need(th) > want) th = (th + 1) / 2;
+  if (need(th) > limit) {
+    while (th > 1 && need(th) > limit) --th;
+  }
+  need(th);
+  p.bands = ceil_div(p.OH, p.TH);
+  p.tiles_oc = ceil_div(p.OC, p.OCB);
+  p.tiles_ic = ceil_div(p.C, p.ICT);
+  int units = p.B * p.bands;
+  int tiles = p.tiles_oc * p.tiles_ic;
+  int blocks_target = 2 * ctx->sm_count;
+  int splits = blocks_target / tiles;
+  if (splits < 1) splits = 1;
+  if (splits > units) splits = units;
+  if (splits < 1) splits = 1;
+  p.splits = splits;
+  p.magic_pitchx = make_magic((unsigned)p.PITCHX);
+  p.magic_thp = make_magic((unsigned)p.THp);
+  p.magic_twp = make_magic((unsigned)p.TWp);
+  p.magic_th = make_magic((unsigned)p.TH);
+}
+
+static void dw_fill(DwCfg &p, const ConvGeom &g, int B) {
+  p.B = B;
+  p.C = g.C;
+  p.HI = g.HI;
+  p.WI = g.WI;
+  p.OC = g.OC;
+  p.OH = g.OH;
+  p.OW = g.OW;
+  p.pad_t = g.pad_t;
+  p.pad_l = g.pad_l;
+  p.has_bias = g.has_bias;
+  p.row_len = conv_weight_len(g) + g.OC;
+}
+
+size_t conv_tiled_dw_scratch(const b200_ctx *ctx, const ConvGeom &g, int B) {
+  DwCfg p{};
+  dw_fill(p, g, B > 0 ? B : 1);
+  dw_tiling(ctx, p, g.KH, g.KW, g.KH == 3 ? 8 : 4);
+  return (size_t)p.splits * p.row_len;
+}
+
+int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout,
+                           int B, float *scratch, int *splits) {
+  B200_REQUIRE(B > 0, "conv_tiled_dw_partials: empty batch");
+  B200_REQUIRE(g.OW <= 64, "conv_tiled_dw_partials: output width %d > 64", g.OW);
+  DwCfg p{};
+  dw_fill(p, g, B);
+  const int OCT = g.KH == 3 ? 8 : 4;
+  dw_tiling(ctx, p, g.KH, g.KW, OCT);
+  p.in = in;
+  p.dout = dout;
+  p.partial = scratch;
+  const int NACC = OCT * g.KH * g.KW + OCT;
+  size_t stage = (size_t)(p.x_tile_floats + p.dy_tile_floats) * 4;
+  size_t red = (size_t)p.SL * (p.OCB / OCT) * p.ICT * NACC * 4;
+  size_t smem = 2 * stage > red ? 2 * stage : red;
+  B200_REQUIRE(smem <= ctx->smem_optin, "conv dW tile needs %zu bytes of shared memory (limit %zu)",
+               smem, ctx->smem_optin);
+  int threads = (p.OCB / OCT) * p.ICT * p.SL;
+  B200_REQUIRE(threads >= 1 && threads <= 256, "conv dW thread count %d out of range", threads);
+  int blocks = p.tiles_oc * p.tiles_ic * p.splits;
+  // rows of blocks that own no unit still write zeros, so every row is defined
+  if (g.KH == 3) {
+    B200_CUDA(cudaFuncSetAttribute(conv_dw_kernel<3, 3, 8>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    conv_dw_kernel<3, 3, 8><<<blocks, threads, smem, ctx->stream>>>(p);
+  } else {
+    B200_CUDA(cudaFuncSetAttribute(conv_dw_kernel<5, 5, 4>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    conv_dw_kernel<5, 5, 4><<<blocks, threads, smem, ctx->stream>>>(p);
+  }
+  B200_LAUNCHED();
+  *splits = p.splits;
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// merging partial rows
+// ---------------------------------------------------------------------------
+
+__global__ void merge_rows_kernel(const float *__restrict__ src, int rows, size_t stride,
+                                  float *__restrict__ dst, size_t len, int accumulate,
+                                  const uint8_t *__restrict__ tbl, int C, int OC, int KK,
+                                  size_t lenW) {
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < len; i += step) {
+    float s = src[i];
+    for (int r = 1; r < rows; ++r) s += src[(size_t)r * stride + i];
+    if (tbl && i < lenW) {
+      // unconnected (o, inc) pairs get no gradient (conv2d_op_internal.h:132)
+      size_t pair = i / KK;
+      int inc = (int)(pair % C);
+      int o = (int)(pair / C);
+      if (!tbl[inc * OC + o]) s = 0.f;
+    }
+    dst[i] = accumulate ? dst[i] + s : s;
+  }
+}
+
+int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *dst, size_t len,
+               int accumulate, const ConvGeom *mask) {
+  if (len == 0) return 0;
+  B200_REQUIRE(rows >= 1, "merge_rows: rows must be >= 1");
+  size_t blocks = ceil_div_sz(len, 256);
+  size_t cap = (size_t)ctx->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  const uint8_t *tbl = mask ? mask->tbl : nullptr;
+  merge_rows_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(
+    src, rows, stride, dst, len, accumulate, tbl, mask ? mask->C : 1, mask ? mask->OC : 1,
+    mask ? mask->KH * mask->KW : 1, mask ? conv_weight_len(*mask) : 0);
+  B200_LAUNCHED();
+  return 0;
+}
+
+}  // namespace b200

@@ -1,0 +1,81 @@
+// Small device helpers: activation epilogues, warp/block reductions, cp.async.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tinycnn_b200.h"
+
+namespace b200 {
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == B200_ACT_RELU) return fmaxf(0.f, v);
+  if (act == B200_ACT_TANH) return tanhf(v);
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block (blockDim.x a multiple of 32, at most 1024).  Result valid
+// in thread 0.  Fixed reduction tree, so repeated runs give identical bits.
+__device__ __forceinline__ float block_sum(float v) {
+  __shared__ float warp_part[32];
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // protects warp_part across back-to-back calls
+  if (lane == 0) warp_part[wid] = v;
+  __syncthreads();
+  int nw = (blockDim.x + 31) >> 5;
+  v = (threadIdx.x < nw) ? warp_part[threadIdx.x] : 0.f;
+  if (wid == 0) v = warp_sum(v);
+  return v;
+}
+
+__device__ __forceinline__ int warp_min_i(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ int warp_max_i(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// 4-byte asynchronous global->shared copy; writes 0 when !valid (src-size 0).
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gsrc, bool valid) {
+  uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  int sz = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(gsrc), "r"(sz)
+               : "memory");
+}
+// 16-byte form (both addresses 16-byte aligned).
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
+  uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc), "r"(sz)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+}  // namespace b200

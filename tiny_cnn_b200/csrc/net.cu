@@ -1,0 +1,559 @@
+// Device-resident twin of a network<sequential>: the whole training step
+// (network::train_onebatch, tiny_dnn/network.h:911-926) runs on the GPU with
+// activations, gradients, parameters and optimizer state resident in HBM.
+//
+//   forward   sequential::forward   (tiny_dnn/nodes.h:288-303)
+//   backward  gradient<E> + sequential::backward (loss_function.h:190-218, nodes.h:276-286)
+//   update    nodes::update_weights -> layer::update_weight (nodes.h:103-107, layer.h:663-682)
+//
+// Memory layout: one flat parameter buffer in network order (per layer W then
+// b), a gradient bucket and optimizer state buffers of the same shape, so the
+// data-parallel exchange is a single sum all-reduce of the bucket and the
+// update is one launch over the whole buffer.
+#include <string.h>
+
+#include "common.cuh"
+
+using namespace b200;
+
+namespace {
+
+struct Layer {
+  int kind = 0;
+  b200_conv_desc cd{};
+  ConvGeom g{};
+  b200_pool_desc pd{};
+  int fc_in = 0, fc_out = 0, fc_bias = 0;
+  size_t in_dim = 0, out_dim = 0;
+  size_t w_off = 0, w_len = 0, b_off = 0, b_len = 0;
+  float *out = nullptr;   // [max_batch][out_dim]
+  float *grad = nullptr;  // dE/d out
+  int32_t *argmax = nullptr;
+  bool tiled = false;
+  float *wt_fwd = nullptr, *wt_dx = nullptr, *dw_part = nullptr;
+  int fused_act = 0;      // activation of the NEXT layer folded into this epilogue
+  bool skipped = false;   // activation layer folded into the previous layer
+};
+
+}  // namespace
+
+struct b200_net {
+  b200_ctx *ctx = nullptr;
+  int max_batch = 0;
+  std::vector<Layer> layers;
+  std::vector<OptSegment> segs;  // trainable tensors in update order
+  size_t n_params = 0;
+  float *params = nullptr, *grads = nullptr, *state0 = nullptr, *state1 = nullptr;
+  OptSegment *segs_dev = nullptr;
+  float *pow_tab = nullptr;  // device [2*T] Adam powers per tensor
+  std::vector<float> pow_host;
+  bool pow_init = false;
+  float pow_b1 = 0.f, pow_b2 = 0.f;
+  float *in_grad = nullptr;  // dE/d input of the first layer
+  float *x_dev = nullptr, *t_dev = nullptr;  // staging for the HOST step
+  int cur_batch = 0;
+  const float *cur_x = nullptr;
+  bool fuse = true;
+  bool input_grad = true;
+  // captured step
+  cudaGraphExec_t graph = nullptr;
+  std::string graph_key;
+  int graph_seen = 0;
+  bool use_graph = true;
+};
+
+namespace {
+
+int net_alloc(void **p, size_t bytes) {
+  B200_CUDA(cudaMalloc(p, bytes ? bytes : 4));
+  B200_CUDA(cudaMemset(*p, 0, bytes ? bytes : 4));
+  return 0;
+}
+
+bool is_foldable_act(int kind) { return kind == B200_LAYER_RELU || kind == B200_LAYER_TANH; }
+int act_of_layer(int kind) {
+  if (kind == B200_LAYER_RELU) return B200_ACT_RELU;
+  if (kind == B200_LAYER_TANH) return B200_ACT_TANH;
+  if (kind == B200_LAYER_SOFTMAX) return B200_ACT_SOFTMAX;
+  return B200_ACT_NONE;
+}
+
+int net_forward_impl(b200_net *net, const float *x, int B) {
+  b200_ctx *ctx = net->ctx;
+  const float *in = x;
+  size_t n = net->layers.size();
+  for (size_t i = 0; i < n; ++i) {
+    Layer &L = net->layers[i];
+    if (L.skipped) {
+      in = L.out;  // already written by the previous layer's epilogue
+      continue;
+    }
+    float *dst = L.fused_act ? net->layers[i + 1].out : L.out;
+    const float *W = net->params + L.w_off;
+    const float *b = L.b_len ? net->params + L.b_off : nullptr;
+    switch (L.kind) {
+      case B200_LAYER_CONV:
+        if (L.tiled)
+          B200_TRY(conv_tiled_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act, L.wt_fwd));
+        else
+          B200_TRY(conv_general_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act));
+        break;
+      case B200_LAYER_FC:
+        B200_TRY(fc_fwd(ctx, L.fc_in, L.fc_out, in, W, b, dst, B, L.fused_act));
+        break;
+      case B200_LAYER_MAXPOOL:
+        B200_TRY(maxpool_fwd(ctx, L.pd, in, dst, L.argmax, B));
+        break;
+      case B200_LAYER_AVGPOOL:
+        B200_TRY(avgpool_fwd(ctx, L.pd, in, W, b, dst, B));
+        break;
+      case B200_LAYER_RELU:
+      case B200_LAYER_TANH:
+      case B200_LAYER_SOFTMAX:
+        B200_TRY(act_fwd(ctx, act_of_layer(L.kind), in, dst, (int)L.out_dim, B));
+        break;
+      default: B200_REQUIRE(false, "net_forward: unknown layer kind %d", L.kind);
+    }
+    in = dst;
+  }
+  net->cur_batch = B;
+  net->cur_x = x;
+  return 0;
+}
+
+int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
+  b200_ctx *ctx = net->ctx;
+  int B = net->cur_batch;
+  int n = (int)net->layers.size();
+  Layer &last = net->layers[n - 1];
+  B200_TRY(loss_grad(ctx, loss_kind, last.out, t, last.grad, (int)last.out_dim, B));
+  for (int i = n - 1; i >= 0; --i) {
+    Layer &L = net->layers[i];
+    const float *in = i == 0 ? net->cur_x : net->layers[i - 1].out;
+    float *din = i == 0 ? (net->input_grad ? net->in_grad : nullptr) : net->layers[i - 1].grad;
+    const float *W = net->params + L.w_off;
+    float *dW = net->grads + L.w_off;
+    float *db = L.b_len ? net->grads + L.b_off : nullptr;
+    switch (L.kind) {
+      case B200_LAYER_CONV: {
+        bool tiled_bwd = L.tiled && L.g.OW <= 64;
+        if (tiled_bwd) {
+          if (din) B200_TRY(conv_tiled_dx(ctx, L.g, W, L.grad, din, B, L.wt_dx));
+          int splits = 0;
+          B200_TRY(conv_tiled_dw_partials(ctx, L.g, in, L.grad, B, L.dw_part, &splits));
+          size_t row = L.w_len + L.g.OC;
+          B200_TRY(merge_rows(ctx, L.dw_part, splits, row, dW, L.w_len, 0, &L.g));
+          if (db) B200_TRY(merge_rows(ctx, L.dw_part + L.w_len, splits, row, db, L.b_len, 0, nullptr));
+        } else {
+          if (din) B200_TRY(conv_general_dx(ctx, L.g, W, L.grad, din, B));
+          B200_TRY(conv_general_dw(ctx, L.g, in, L.grad, dW, db, 0, B));
+        }
+        break;
+      }
+      case B200_LAYER_FC:
+        B200_TRY(fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, din, dW, db, 0, B));
+        break;
+      case B200_LAYER_MAXPOOL:
+        if (din) B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, din, B));
+        break;
+      case B200_LAYER_AVGPOOL:
+        B200_TRY(avgpool_bwd(ctx, L.pd, in, W, L.grad, din, dW, db, 0, B));
+        break;
+      case B200_LAYER_RELU:
+      case B200_LAYER_TANH:
+      case B200_LAYER_SOFTMAX:
+        if (din)
+          B200_TRY(act_bwd(ctx, act_of_layer(L.kind), L.out, L.grad, din, (int)L.out_dim, B));
+        break;
+      default: B200_REQUIRE(false, "net_backward: unknown layer kind %d", L.kind);
+    }
+  }
+  return 0;
+}
+
+// Adam powers for a fresh optimizer object: tensor j of the first step sees
+// b^(1+j), reached by j sequential float multiplies (optimizer.h:104-110,125-126).
+int net_init_powers(b200_net *net, float b1, float b2) {
+  size_t T = net->segs.size();
+  net->pow_host.assign(2 * T + 2, 0.f);
+  float p1 = b1, p2 = b2;
+  for (size_t j = 0; j < T; ++j) {
+    net->pow_host[2 * j] = p1;
+    net->pow_host[2 * j + 1] = p2;
+    p1 *= b1;
+    p2 *= b2;
+  }
+  B200_CUDA(cudaMemcpyAsync(net->pow_tab, net->pow_host.data(), sizeof(float) * 2 * T,
+                            cudaMemcpyHostToDevice, net->ctx->stream));
+  B200_CUDA(cudaStreamSynchronize(net->ctx->stream));
+  net->pow_init = true;
+  net->pow_b1 = b1;
+  net->pow_b2 = b2;
+  return 0;
+}
+
+int net_update_impl(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
+  b200_ctx *ctx = net->ctx;
+  int T = (int)net->segs.size();
+  B200_TRY(opt_update_segments(ctx, opt_kind, *h, net->grads, net->params, net->state0,
+                               net->state1, net->segs_dev, T, net->n_params, net->pow_tab));
+  if (opt_kind == B200_OPT_ADAM) B200_TRY(opt_advance_powers(ctx, net->pow_tab, T, h->b1, h->b2));
+  return 0;
+}
+
+int ensure_powers(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
+  if (opt_kind == B200_OPT_ADAM && !net->pow_init) B200_TRY(net_init_powers(net, h->b1, h->b2));
+  return 0;
+}
+
+int check_net(b200_net *net) {
+  B200_REQUIRE(net != nullptr, "net is NULL");
+  B200_CUDA(cudaSetDevice(net->ctx->device));
+  return 0;
+}
+
+int step_eager(b200_net *net, const float *x, const float *t, int B, int loss_kind, int opt_kind,
+               const b200_opt_hyper *h) {
+  B200_TRY(net_forward_impl(net, x, B));
+  B200_TRY(net_backward_impl(net, t, loss_kind));
+  return net_update_impl(net, opt_kind, h);
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, int max_batch,
+                    b200_net **out) {
+  B200_REQUIRE(ctx && specs && out && n_layers > 0 && max_batch > 0, "net_create: bad argument");
+  B200_CUDA(cudaSetDevice(ctx->device));
+  b200_net *net = new b200_net();
+  net->ctx = ctx;
+  net->max_batch = max_batch;
+  net->layers.resize(n_layers);
+  if (const char *e = getenv("B200_NET_NO_FUSE")) net->fuse = !(e[0] == '1');
+  if (const char *e = getenv("B200_NET_NO_GRAPH")) net->use_graph = !(e[0] == '1');
+  size_t off = 0;
+  size_t prev_out = 0;
+  for (int i = 0; i < n_layers; ++i) {
+    Layer &L = net->layers[i];
+    const b200_layer_spec &S = specs[i];
+    L.kind = S.kind;
+    switch (S.kind) {
+      case B200_LAYER_CONV: {
+        L.cd = S.conv;
+        L.cd.input_is_padded = 0;
+        if (int r = conv_geom_from_desc(ctx, &L.cd, &L.g)) {
+          delete net;
+          return r;
+        }
+        L.in_dim = (size_t)L.g.C * L.g.HI * L.g.WI;
+        L.out_dim = (size_t)L.g.OC * L.g.OH * L.g.OW;
+        L.w_len = conv_weight_len(L.g);
+        L.b_len = L.g.has_bias ? L.g.OC : 0;
+        L.tiled = conv_tiled_ok(L.g) && L.cd.algo != 1;
+        break;
+      }
+      case B200_LAYER_FC:
+        L.fc_in = S.fc_in;
+        L.fc_out = S.fc_out;
+        L.fc_bias = S.fc_has_bias;
+        L.in_dim = S.fc_in;
+        L.out_dim = S.fc_out;
+        L.w_len = (size_t)S.fc_in * S.fc_out;
+        L.b_len = S.fc_has_bias ? S.fc_out : 0;
+        break;
+      case B200_LAYER_MAXPOOL:
+      case B200_LAYER_AVGPOOL:
+        L.pd = S.pool;
+        L.in_dim = (size_t)S.pool.in_c * S.pool.in_h * S.pool.in_w;
+        L.out_dim = (size_t)S.pool.in_c * S.pool.out_h * S.pool.out_w;
+        if (S.kind == B200_LAYER_AVGPOOL) {
+          // weight vector has pool_w*pool_h*C entries (average_pooling_layer.h:231-233)
+          L.w_len = (size_t)S.pool.pool_w * S.pool.pool_h * S.pool.in_c;
+          L.b_len = S.pool.in_c;
+        }
+        break;
+      case B200_LAYER_RELU:
+      case B200_LAYER_TANH:
+      case B200_LAYER_SOFTMAX:
+        L.in_dim = L.out_dim = prev_out;
+        break;
+      default:
+        set_error("net_create: unknown layer kind %d at %d", S.kind, i);
+        delete net;
+        return 2;
+    }
+    if (i > 0 && L.in_dim != prev_out) {
+      set_error("net_create: layer %d expects %zu inputs, previous layer gives %zu", i, L.in_dim,
+                prev_out);
+      delete net;
+      return 2;
+    }
+    if (L.in_dim == 0 || L.out_dim == 0) {
+      set_error("net_create: layer %d has an empty shape", i);
+      delete net;
+      return 2;
+    }
+    prev_out = L.out_dim;
+    if (L.w_len) {
+      L.w_off = off;
+      net->segs.push_back({off, L.w_len});
+      off += L.w_len;
+    }
+    if (L.b_len) {
+      L.b_off = off;
+      net->segs.push_back({off, L.b_len});
+      off += L.b_len;
+    }
+  }
+  net->n_params = off;
+  // fold relu/tanh into the producing convolution / fully-connected epilogue
+  if (net->fuse) {
+    for (int i = 0; i + 1 < n_layers; ++i) {
+      Layer &L = net->layers[i];
+      Layer &N = net->layers[i + 1];
+      if ((L.kind == B200_LAYER_CONV || L.kind == B200_LAYER_FC) && is_foldable_act(N.kind)) {
+        L.fused_act = act_of_layer(N.kind);
+        N.skipped = true;
+      }
+    }
+  }
+  // device memory
+  size_t f = sizeof(float);
+  B200_TRY(net_alloc((void **)&net->params, off * f));
+  B200_TRY(net_alloc((void **)&net->grads, off * f));
+  B200_TRY(net_alloc((void **)&net->state0, off * f));
+  B200_TRY(net_alloc((void **)&net->state1, off * f));
+  B200_TRY(net_alloc((void **)&net->segs_dev, sizeof(OptSegment) * (net->segs.size() + 1)));
+  B200_CUDA(cudaMemcpy(net->segs_dev, net->segs.data(), sizeof(OptSegment) * net->segs.size(),
+                       cudaMemcpyHostToDevice));
+  B200_TRY(net_alloc((void **)&net->pow_tab, f * 2 * (net->segs.size() + 1)));
+  size_t in0 = net->layers[0].in_dim;
+  B200_TRY(net_alloc((void **)&net->in_grad, in0 * max_batch * f));
+  B200_TRY(net_alloc((void **)&net->x_dev, in0 * max_batch * f));
+  B200_TRY(net_alloc((void **)&net->t_dev, net->layers[n_layers - 1].out_dim * max_batch * f));
+  for (int i = 0; i < n_layers; ++i) {
+    Layer &L = net->layers[i];
+    B200_TRY(net_alloc((void **)&L.out, L.out_dim * max_batch * f));
+    B200_TRY(net_alloc((void **)&L.grad, L.out_dim * max_batch * f));
+    if (L.kind == B200_LAYER_MAXPOOL)
+      B200_TRY(net_alloc((void **)&L.argmax, L.out_dim * max_batch * sizeof(int32_t)));
+    if (L.kind == B200_LAYER_CONV && L.tiled) {
+      B200_TRY(net_alloc((void **)&L.wt_fwd, conv_tiled_fwd_scratch(L.g) * f));
+      B200_TRY(net_alloc((void **)&L.wt_dx, conv_tiled_dx_scratch(L.g) * f));
+      // the split count depends on the batch; size for the largest over 1..max_batch
+      size_t need = 0;
+      for (int b = 1; b <= max_batch; b = b < 8 ? b + 1 : b * 2) {
+        size_t s = conv_tiled_dw_scratch(ctx, L.g, b);
+        if (s > need) need = s;
+      }
+      size_t s = conv_tiled_dw_scratch(ctx, L.g, max_batch);
+      if (s > need) need = s;
+      // splits never exceed 2 * SM count rows
+      size_t cap = (size_t)2 * ctx->sm_count * (L.w_len + L.g.OC);
+      if (cap > need) need = cap;
+      B200_TRY(net_alloc((void **)&L.dw_part, need * f));
+    }
+  }
+  *out = net;
+  return 0;
+}
+
+int b200_net_destroy(b200_net *net) {
+  if (!net) return 0;
+  cudaSetDevice(net->ctx->device);
+  cudaStreamSynchronize(net->ctx->stream);
+  if (net->graph) cudaGraphExecDestroy(net->graph);
+  for (auto &L : net->layers) {
+    cudaFree(L.out);
+    cudaFree(L.grad);
+    cudaFree(L.argmax);
+    cudaFree(L.wt_fwd);
+    cudaFree(L.wt_dx);
+    cudaFree(L.dw_part);
+  }
+  cudaFree(net->params);
+  cudaFree(net->grads);
+  cudaFree(net->state0);
+  cudaFree(net->state1);
+  cudaFree(net->segs_dev);
+  cudaFree(net->pow_tab);
+  cudaFree(net->in_grad);
+  cudaFree(net->x_dev);
+  cudaFree(net->t_dev);
+  delete net;
+  return 0;
+}
+
+size_t b200_net_param_count(const b200_net *net) { return net ? net->n_params : 0; }
+int b200_net_tensor_count(const b200_net *net) { return net ? (int)net->segs.size() : 0; }
+int b200_net_tensor_info(const b200_net *net, int i, size_t *offset, size_t *len) {
+  B200_REQUIRE(net && i >= 0 && i < (int)net->segs.size(), "net_tensor_info: index out of range");
+  if (offset) *offset = net->segs[i].offset;
+  if (len) *len = net->segs[i].len;
+  return 0;
+}
+int b200_net_in_dim(const b200_net *net) { return net ? (int)net->layers.front().in_dim : 0; }
+int b200_net_out_dim(const b200_net *net) { return net ? (int)net->layers.back().out_dim : 0; }
+
+int b200_net_set_params(b200_net *net, const float *host_params) {
+  B200_TRY(check_net(net));
+  B200_CUDA(cudaMemcpyAsync(net->params, host_params, net->n_params * sizeof(float),
+                            cudaMemcpyHostToDevice, net->ctx->stream));
+  B200_CUDA(cudaStreamSynchronize(net->ctx->stream));
+  return 0;
+}
+int b200_net_get_params(b200_net *net, float *host_params) {
+  B200_TRY(check_net(net));
+  B200_CUDA(cudaMemcpyAsync(host_params, net->params, net->n_params * sizeof(float),
+                            cudaMemcpyDeviceToHost, net->ctx->stream));
+  B200_CUDA(cudaStreamSynchronize(net->ctx->stream));
+  return 0;
+}
+int b200_net_get_grads(b200_net *net, float *host_grads) {
+  B200_TRY(check_net(net));
+  B200_CUDA(cudaMemcpyAsync(host_grads, net->grads, net->n_params * sizeof(float),
+                            cudaMemcpyDeviceToHost, net->ctx->stream));
+  B200_CUDA(cudaStreamSynchronize(net->ctx->stream));
+  return 0;
+}
+
+float *b200_net_params_ptr(b200_net *net) { return net ? net->params : nullptr; }
+float *b200_net_grads_ptr(b200_net *net) { return net ? net->grads : nullptr; }
+float *b200_net_output_ptr(b200_net *net) { return net ? net->layers.back().out : nullptr; }
+float *b200_net_layer_out_ptr(b200_net *net, int i) {
+  if (!net || i < 0 || i >= (int)net->layers.size()) return nullptr;
+  // a layer whose activation was folded away never materialises its own output
+  if (net->layers[i].fused_act) return nullptr;
+  return net->layers[i].out;
+}
+float *b200_net_layer_grad_ptr(b200_net *net, int i) {
+  if (!net || i < -1 || i >= (int)net->layers.size()) return nullptr;
+  if (i == -1) return net->in_grad;
+  return net->layers[i].grad;
+}
+
+int b200_net_forward(b200_net *net, const float *x, int batch) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(x != nullptr, "net_forward: x is NULL");
+  B200_REQUIRE(batch >= 1 && batch <= net->max_batch, "net_forward: batch %d outside 1..%d", batch,
+               net->max_batch);
+  return net_forward_impl(net, x, batch);
+}
+
+int b200_net_backward(b200_net *net, const float *t, int loss_kind) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(t != nullptr, "net_backward: t is NULL");
+  B200_REQUIRE(net->cur_batch > 0, "net_backward: no forward pass to differentiate");
+  return net_backward_impl(net, t, loss_kind);
+}
+
+int b200_net_opt_reset(b200_net *net, int reset_powers) {
+  B200_TRY(check_net(net));
+  size_t bytes = net->n_params * sizeof(float);
+  B200_CUDA(cudaMemsetAsync(net->state0, 0, bytes, net->ctx->stream));
+  B200_CUDA(cudaMemsetAsync(net->state1, 0, bytes, net->ctx->stream));
+  if (reset_powers) net->pow_init = false;
+  return 0;
+}
+
+int b200_net_update(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(h != nullptr, "net_update: hyper-parameters are NULL");
+  B200_TRY(ensure_powers(net, opt_kind, h));
+  return net_update_impl(net, opt_kind, h);
+}
+
+int b200_net_adam_powers(const b200_net *net, float *b1_t, float *b2_t) {
+  B200_REQUIRE(net != nullptr, "net is NULL");
+  size_t T = net->segs.size();
+  std::vector<float> tab(2 * T + 2, 0.f);
+  if (net->pow_init) {
+    B200_CUDA(cudaStreamSynchronize(net->ctx->stream));
+    B200_CUDA(cudaMemcpy(tab.data(), net->pow_tab, sizeof(float) * 2 * T, cudaMemcpyDeviceToHost));
+  }
+  // entry 0 is what the NEXT update call of the first tensor will use
+  if (b1_t) *b1_t = tab[0];
+  if (b2_t) *b2_t = tab[1];
+  return 0;
+}
+
+int b200_net_train_step(b200_net *net, const float *x, const float *t, int batch, int loss_kind,
+                        int opt_kind, const b200_opt_hyper *h) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(x && t && h, "net_train_step: NULL argument");
+  B200_REQUIRE(batch >= 1 && batch <= net->max_batch, "net_train_step: batch %d outside 1..%d",
+               batch, net->max_batch);
+  B200_TRY(ensure_powers(net, opt_kind, h));
+  if (!net->use_graph) return step_eager(net, x, t, batch, loss_kind, opt_kind, h);
+
+  // key of the captured step: pointers, sizes, kinds and hyper-parameter bytes
+  std::string key;
+  key.append(reinterpret_cast<const char *>(&x), sizeof(x));
+  key.append(reinterpret_cast<const char *>(&t), sizeof(t));
+  key.append(reinterpret_cast<const char *>(&batch), sizeof(batch));
+  key.append(reinterpret_cast<const char *>(&loss_kind), sizeof(loss_kind));
+  key.append(reinterpret_cast<const char *>(&opt_kind), sizeof(opt_kind));
+  key.append(reinterpret_cast<const char *>(h), sizeof(*h));
+  if (key != net->graph_key) {
+    if (net->graph) {
+      B200_CUDA(cudaGraphExecDestroy(net->graph));
+      net->graph = nullptr;
+    }
+    net->graph_key = key;
+    net->graph_seen = 0;
+  }
+  if (net->graph) {
+    B200_CUDA(cudaGraphLaunch(net->graph, net->ctx->stream));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    net->cur_batch = batch;
+    net->cur_x = x;
+    return 0;
+  }
+  if (net->graph_seen++ == 0) {
+    // first sight of this configuration: run eagerly (sets kernel attributes,
+    // grows nothing afterwards)
+    return step_eager(net, x, t, batch, loss_kind, opt_kind, h);
+  }
+  cudaStream_t st = net->ctx->stream;
+  cudaGraph_t graph = nullptr;
+  B200_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed));
+  int r = step_eager(net, x, t, batch, loss_kind, opt_kind, h);
+  cudaError_t ce = cudaStreamEndCapture(st, &graph);
+  if (r != 0) {
+    if (graph) cudaGraphDestroy(graph);
+    return r;
+  }
+  if (ce != cudaSuccess) {
+    set_error("net_train_step: stream capture failed: %s", cudaGetErrorString(ce));
+    return 1;
+  }
+  B200_CUDA(cudaGraphInstantiate(&net->graph, graph, 0));
+  B200_CUDA(cudaGraphDestroy(graph));
+  B200_CUDA(cudaGraphLaunch(net->graph, st));
+  return 0;
+}
+
+int b200_net_train_step_host(b200_net *net, const float *x_host, const float *t_host, int batch,
+                             int loss_kind, int opt_kind, const b200_opt_hyper *h,
+                             float *out_host) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(x_host && t_host && h, "net_train_step_host: NULL argument");
+  B200_REQUIRE(batch >= 1 && batch <= net->max_batch,
+               "net_train_step_host: batch %d outside 1..%d", batch, net->max_batch);
+  cudaStream_t st = net->ctx->stream;
+  size_t in_dim = net->layers.front().in_dim, out_dim = net->layers.back().out_dim;
+  B200_CUDA(cudaMemcpyAsync(net->x_dev, x_host, in_dim * batch * sizeof(float),
+                            cudaMemcpyHostToDevice, st));
+  B200_CUDA(cudaMemcpyAsync(net->t_dev, t_host, out_dim * batch * sizeof(float),
+                            cudaMemcpyHostToDevice, st));
+  B200_TRY(b200_net_train_step(net, net->x_dev, net->t_dev, batch, loss_kind, opt_kind, h));
+  if (out_host)
+    B200_CUDA(cudaMemcpyAsync(out_host, net->layers.back().out, out_dim * batch * sizeof(float),
+                              cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,261 @@
+// Max and average pooling, forward and gradient.
+//
+// The reference drives both through index tables built once per layer
+// (max: tiny_dnn/layers/max_pooling_layer.h:195-235; average:
+// tiny_dnn/layers/average_pooling_layer.h:271-311).  Here the tables are
+// closed-form index arithmetic evaluated per thread.
+#include <float.h>
+
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace b200 {
+
+// maxpool_op_internal (tiny_dnn/core/kernels/maxpool_op_internal.h:16-39):
+// strict '>' against lowest(), window scanned dy-major, clipped at the border;
+// the winning in-row index starts at 0 as the reference's `idx` does.
+__global__ void maxpool_fwd_kernel(b200_pool_desc d, const float *__restrict__ in,
+                                   float *__restrict__ out, int32_t *__restrict__ argmax,
+                                   long long total) {
+  long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long step = (long long)gridDim.x * blockDim.x;
+  const int in_row = d.in_c * d.in_h * d.in_w;
+  for (; idx < total; idx += step) {
+    int ox = (int)(idx % d.out_w);
+    long long r = idx / d.out_w;
+    int oy = (int)(r % d.out_h);
+    r /= d.out_h;
+    int c = (int)(r % d.in_c);
+    long long n = r / d.in_c;
+    const float *ip = in + n * in_row;
+    int y0 = oy * d.stride_h, x0 = ox * d.stride_w;
+    int dymax = min(d.pool_h, d.in_h - y0);
+    int dxmax = min(d.pool_w, d.in_w - x0);
+    float best = -FLT_MAX;
+    int besti = 0;
+    for (int dy = 0; dy < dymax; ++dy)
+      for (int dx = 0; dx < dxmax; ++dx) {
+        int i = (d.in_h * c + y0 + dy) * d.in_w + x0 + dx;
+        float v = ip[i];
+        if (v > best) {
+          best = v;
+          besti = i;
+        }
+      }
+    out[idx] = best;
+    argmax[idx] = besti;
+  }
+}
+
+// maxpool_grad_op_internal (maxpool_op_internal.h:41-57).  in2out[i] is the last
+// window, in (y, x) order, that covers input i; 0 when no window does.
+__global__ void maxpool_bwd_kernel(b200_pool_desc d, const float *__restrict__ dout,
+                                   const int32_t *__restrict__ argmax, float *__restrict__ din,
+                                   long long total) {
+  long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long step = (long long)gridDim.x * blockDim.x;
+  const int in_row = d.in_c * d.in_h * d.in_w;
+  const int out_row = d.in_c * d.out_h * d.out_w;
+  for (; idx < total; idx += step) {
+    int i = (int)(idx % in_row);
+    long long n = idx / in_row;
+    int ix = i % d.in_w;
+    int r = i / d.in_w;
+    int iy = r % d.in_h;
+    int c = r / d.in_h;
+    int oy = min(iy / d.stride_h, d.out_h - 1);
+    int ox = min(ix / d.stride_w, d.out_w - 1);
+    bool covered = (iy < oy * d.stride_h + d.pool_h) && (ix < ox * d.stride_w + d.pool_w);
+    int outi = covered ? (d.out_h * c + oy) * d.out_w + ox : 0;
+    const long long ob = n * out_row;
+    din[idx] = (argmax[ob + outi] == i) ? dout[ob + outi] : 0.f;
+  }
+}
+
+// tiny_average_pooling_kernel (tiny_dnn/layers/average_pooling_layer.h:25-55):
+// windows start at multiples of the stride while they fit entirely
+// (init_connection :271-281); an output without a window is just the bias.
+__global__ void avgpool_fwd_kernel(b200_pool_desc d, const float *__restrict__ in,
+                                   const float *__restrict__ W, const float *__restrict__ bias,
+                                   float *__restrict__ out, long long total) {
+  long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long step = (long long)gridDim.x * blockDim.x;
+  const int in_row = d.in_c * d.in_h * d.in_w;
+  const float scale = 1.0f / (float)(d.pool_w * d.pool_h);
+  for (; idx < total; idx += step) {
+    int ox = (int)(idx % d.out_w);
+    long long r = idx / d.out_w;
+    int oy = (int)(r % d.out_h);
+    r /= d.out_h;
+    int c = (int)(r % d.in_c);
+    long long n = r / d.in_c;
+    const float *ip = in + n * in_row + (size_t)c * d.in_h * d.in_w;
+    int y0 = oy * d.stride_h, x0 = ox * d.stride_w;
+    float v = 0.f;
+    if (y0 + d.pool_h <= d.in_h && x0 + d.pool_w <= d.in_w) {
+      for (int dy = 0; dy < d.pool_h; ++dy)
+        for (int dx = 0; dx < d.pool_w; ++dx) v += ip[(y0 + dy) * d.in_w + x0 + dx];
+    }
+    float w = __fmul_rn(W[c], scale);
+    out[idx] = __fadd_rn(__fmul_rn(v, w), bias[c]);
+  }
+}
+
+// prev_delta of tiny_average_pooling_back_kernel (average_pooling_layer.h:78-84):
+// W[c]*scale*dout[first window covering the input].
+__global__ void avgpool_bwd_dx_kernel(b200_pool_desc d, const float *__restrict__ W,
+                                      const float *__restrict__ dout, float *__restrict__ din,
+                                      long long total) {
+  long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long step = (long long)gridDim.x * blockDim.x;
+  const int in_row = d.in_c * d.in_h * d.in_w;
+  const int out_row = d.in_c * d.out_h * d.out_w;
+  const float scale = 1.0f / (float)(d.pool_w * d.pool_h);
+  // number of windows that exist along each axis
+  const int nwy = (d.in_h - d.pool_h) / d.stride_h + 1;
+  const int nwx = (d.in_w - d.pool_w) / d.stride_w + 1;
+  for (; idx < total; idx += step) {
+    int i = (int)(idx % in_row);
+    long long n = idx / in_row;
+    int ix = i % d.in_w;
+    int r = i / d.in_w;
+    int iy = r % d.in_h;
+    int c = r / d.in_h;
+    // first window (smallest start) with start <= pos < start + pool
+    int oy = iy < d.pool_h ? 0 : (iy - d.pool_h) / d.stride_h + 1;
+    int ox = ix < d.pool_w ? 0 : (ix - d.pool_w) / d.stride_w + 1;
+    bool covered = oy < nwy && ox < nwx && oy * d.stride_h <= iy && ox * d.stride_w <= ix &&
+                   oy < d.out_h && ox < d.out_w;
+    float v = 0.f;
+    if (covered)
+      v = __fmul_rn(__fmul_rn(W[c], scale), dout[n * out_row + (d.out_h * c + oy) * d.out_w + ox]);
+    din[idx] = v;
+  }
+}
+
+// dW[c] (+)= scale * sum_{n, window, tap} in*dout ; db[c] (+)= sum dout
+// (average_pooling_layer.h:86-104).  One block per channel, fixed order.
+__global__ void avgpool_bwd_dw_kernel(b200_pool_desc d, const float *__restrict__ in,
+                                      const float *__restrict__ dout, float *__restrict__ dW,
+                                      float *__restrict__ db, int B, int accumulate) {
+  const int c = blockIdx.x;
+  const int in_row = d.in_c * d.in_h * d.in_w;
+  const int out_row = d.in_c * d.out_h * d.out_w;
+  const int oplane = d.out_h * d.out_w;
+  const float scale = 1.0f / (float)(d.pool_w * d.pool_h);
+  float sw = 0.f, sb = 0.f;
+  long long total = (long long)B * oplane;
+  for (long long t = threadIdx.x; t < total; t += blockDim.x) {
+    int n = (int)(t / oplane);
+    int o = (int)(t % oplane);
+    int oy = o / d.out_w, ox = o % d.out_w;
+    float g = dout[(size_t)n * out_row + (size_t)c * oplane + o];
+    sb += g;
+    int y0 = oy * d.stride_h, x0 = ox * d.stride_w;
+    if (y0 + d.pool_h <= d.in_h && x0 + d.pool_w <= d.in_w) {
+      const float *ip = in + (size_t)n * in_row + (size_t)c * d.in_h * d.in_w;
+      float s = 0.f;
+      for (int dy = 0; dy < d.pool_h; ++dy)
+        for (int dx = 0; dx < d.pool_w; ++dx) s += ip[(y0 + dy) * d.in_w + x0 + dx];
+      sw = fmaf(s, g, sw);
+    }
+  }
+  sw = block_sum(sw);
+  sb = block_sum(sb);
+  if (threadIdx.x == 0) {
+    float vw = sw * scale;
+    dW[c] = accumulate ? dW[c] + vw : vw;
+    db[c] = accumulate ? db[c] + sb : sb;
+  }
+}
+
+// entries in_c .. pool_w*pool_h*in_c of the weight gradient are never written
+// by the reference; a fresh (non-accumulating) gradient holds 0 there.
+__global__ void zero_tail_kernel(float *p, int from, int to) {
+  int i = from + blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < to) p[i] = 0.f;
+}
+
+static int grid_for(long long total, int block, int sm_count) {
+  long long blocks = (total + block - 1) / block;
+  long long cap = (long long)sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+static int check_pool(const b200_pool_desc &d) {
+  B200_REQUIRE(d.in_w > 0 && d.in_h > 0 && d.in_c > 0 && d.out_w > 0 && d.out_h > 0 &&
+                 d.pool_w > 0 && d.pool_h > 0 && d.stride_w > 0 && d.stride_h > 0,
+               "pool descriptor has a non-positive extent");
+  B200_REQUIRE((d.out_h - 1) * d.stride_h < d.in_h && (d.out_w - 1) * d.stride_w < d.in_w,
+               "pool descriptor: last window starts outside the input");
+  return 0;
+}
+
+int maxpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, float *out,
+                int32_t *argmax, int B) {
+  B200_TRY(check_pool(d));
+  long long total = (long long)B * d.in_c * d.out_h * d.out_w;
+  if (total == 0) return 0;
+  maxpool_fwd_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(d, in, out,
+                                                                                   argmax, total);
+  B200_LAUNCHED();
+  return 0;
+}
+
+int maxpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *dout, const int32_t *argmax,
+                float *din, int B) {
+  B200_TRY(check_pool(d));
+  long long total = (long long)B * d.in_c * d.in_h * d.in_w;
+  if (total == 0) return 0;
+  maxpool_bwd_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(d, dout, argmax,
+                                                                                   din, total);
+  B200_LAUNCHED();
+  return 0;
+}
+
+static int check_avg(const b200_pool_desc &d) {
+  B200_TRY(check_pool(d));
+  // the reference dereferences in2wo[idx][0] for every input: each input must
+  // lie in at least one window (average_pooling_layer.h:82)
+  B200_REQUIRE(d.stride_w <= d.pool_w && d.stride_h <= d.pool_h &&
+                 (d.in_w - d.pool_w) % d.stride_w == 0 && (d.in_h - d.pool_h) % d.stride_h == 0 &&
+                 d.in_w >= d.pool_w && d.in_h >= d.pool_h,
+               "average pooling: some input lies in no window (stride > pool or ragged edge)");
+  return 0;
+}
+
+int avgpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const float *W,
+                const float *bias, float *out, int B) {
+  B200_TRY(check_avg(d));
+  long long total = (long long)B * d.in_c * d.out_h * d.out_w;
+  if (total == 0) return 0;
+  avgpool_fwd_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(d, in, W, bias,
+                                                                                   out, total);
+  B200_LAUNCHED();
+  return 0;
+}
+
+int avgpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const float *W,
+                const float *dout, float *din, float *dW, float *db, int accumulate, int B) {
+  B200_TRY(check_avg(d));
+  long long total = (long long)B * d.in_c * d.in_h * d.in_w;
+  if (din && total > 0) {
+    avgpool_bwd_dx_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+      d, W, dout, din, total);
+    B200_LAUNCHED();
+  }
+  if (dW && db) {
+    avgpool_bwd_dw_kernel<<<d.in_c, 256, 0, ctx->stream>>>(d, in, dout, dW, db, B, accumulate);
+    B200_LAUNCHED();
+    int wlen = d.pool_w * d.pool_h * d.in_c;
+    if (!accumulate && wlen > d.in_c) {
+      zero_tail_kernel<<<ceil_div(wlen - d.in_c, 256), 256, 0, ctx->stream>>>(dW, d.in_c, wlen);
+      B200_LAUNCHED();
+    }
+  }
+  return 0;
+}
+
+}  // namespace b200
