@@ -1,0 +1,418 @@
+#!/usr/bin/env python
+"""Benchmark of the training hot path: CIFAR-10-style network, batch 256 per GPU,
+cross-entropy after softmax, Adam (lr 1e-3), fp32 -- training samples/s.
+
+    python bench.py --gpus 1 --steps 50 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...     # the reference's own CPU path on the host cores
+
+One JSON line is printed by rank 0.  `value` is measured with inputs resident in
+HBM; `e2e` goes through the HOST-buffer entry point (host->device copy of the
+batch and device->host copy of the network output inside the timed region).
+Data are synthetic with CIFAR-10's shapes (3x32x32 inputs ~ N(0,1), 10 classes).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (ROOT, ROOT / "tests"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+BATCH = 256
+IN_DIM, OUT_DIM = 3 * 32 * 32, 10
+WORKLOAD = "cifar10_net conv5x5(3->32,same)-relu-maxpool2 conv5x5(32->32)-relu-maxpool2 " \
+           "conv5x5(32->64)-relu-maxpool2 fc1024->64-relu fc64->10-softmax; cross_entropy; adam lr=1e-3"
+LOSS_CE, OPT_ADAM = 1, 1
+SM_COUNT, FP32_LANES = 148, 128
+
+
+def conv_flops(B, w, c, oc, k):
+    return 2.0 * B * w * w * oc * c * k * k
+
+
+# the three convolutions of the net: (name, width, in_c, out_c, k)
+CONVS = [("conv1", 32, 3, 32, 5), ("conv2", 16, 32, 32, 5), ("conv3", 8, 32, 64, 5)]
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_specs():
+    from cases import build_net_specs
+    return build_net_specs("cifar")
+
+
+def synthetic_batches(n_batches, seed):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n_batches, BATCH, IN_DIM)).astype(np.float32)
+    labels = rng.integers(0, OUT_DIM, (n_batches, BATCH))
+    t = np.zeros((n_batches, BATCH, OUT_DIM), np.float32)
+    for i in range(n_batches):
+        t[i, np.arange(BATCH), labels[i]] = 1.0
+    return x, t
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm: the unmodified reference's CPU path (OpenMP, backend_t::internal)
+# --------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    import numpy as np
+    import oracle_lib as o
+    from cases import hyper_for, xavier_params
+    specs, keep = make_specs()
+    arr = (type(specs[0]) * len(specs))(*specs)
+    x, t = synthetic_batches(1, 1000)
+    hy = hyper_for(OPT_ADAM)
+    ref = o.load_reference()
+    if ref is not None:
+        kind, cores = "reference", ref.ref_openmp_threads()
+        h = ref.ref_net_create(arr, len(specs), 42)
+        p0 = xavier_params(specs, 42)
+        ref.ref_net_set_params(h, o.p(p0))
+
+        def one_step():
+            s = ref.ref_net_fit(h, o.p(x[0]), o.p(t[0]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))
+            assert s >= 0
+            return s
+        sample = f"one mini-batch of {BATCH} samples per step through network::fit, OpenMP {cores} threads"
+        per_step = BATCH
+    else:
+        orc = o.load_oracle()
+        kind, cores = "port", 1
+        sub = 32
+        net = orc.orc_net_create(arr, len(specs), sub)
+        params = np.ctypeslib.as_array(orc.orc_net_params(net), shape=(orc.orc_net_param_count(net),))
+        params[:] = xavier_params(specs, 42)
+
+        def one_step():
+            t0 = time.perf_counter()
+            orc.orc_net_train_step(net, o.p(x[0][:sub]), o.p(t[0][:sub]), sub, LOSS_CE, OPT_ADAM, C.byref(hy))
+            return time.perf_counter() - t0
+        sample = f"{sub} samples per step through the C restatement, 1 thread"
+        per_step = sub
+    for _ in range(args.warmup):
+        one_step()
+    secs = sum(one_step() for _ in range(args.steps))
+    value = per_step * args.steps / secs
+    line = {
+        "impl": "reference", "metric": "train_samples_per_s", "value": value, "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "global_batch": BATCH * args.gpus,
+                   "parallelism": f"dp{args.gpus}", "note": "CPU reference arm runs one GPU's batch per step"},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------
+# own arm
+# --------------------------------------------------------------------------------------------
+def time_kernels(ctx, torch, ops, reps=10):
+    """CUDA-event time of every convolution kernel of the net at batch 256 (forward, dX,
+    dW+db), launched alone on the context stream; returns {name: (ms, flops)}."""
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for name, w, c, oc, k in CONVS:
+        d = ops.conv_params(w, w, c, k, k, oc, True, True)
+        x = torch.randn(BATCH, c * w * w, device="cuda", generator=g)
+        W = (torch.rand(oc * c * k * k, device="cuda", generator=g) - 0.5) * 0.2
+        b = torch.zeros(oc, device="cuda")
+        dy = torch.randn(BATCH, oc * w * w, device="cuda", generator=g)
+        y = torch.empty(BATCH, oc * w * w, device="cuda")
+        dx = torch.empty_like(x)
+        dW, db = torch.zeros_like(W), torch.zeros_like(b)
+        lib, h = ctx.lib, ctx.handle
+        from tiny_cnn_b200._lib import check, ptr
+
+        def fwd():
+            check(lib.b200_conv2d_fwd(h, C.byref(d), ptr(x), ptr(W), ptr(b), ptr(y), BATCH))
+
+        def bwd():
+            check(lib.b200_conv2d_bwd(h, C.byref(d), ptr(x), ptr(W), ptr(dy), ptr(dx), ptr(dW), ptr(db), 0, BATCH))
+
+        def bwd_nodx():
+            check(lib.b200_conv2d_bwd(h, C.byref(d), ptr(x), ptr(W), ptr(dy), None, ptr(dW), ptr(db), 0, BATCH))
+        times = {}
+        for key, fn in (("fwd", fwd), ("bwd", bwd), ("dw", bwd_nodx)):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times[key] = e0.elapsed_time(e1) / reps
+        fl = conv_flops(BATCH, w, c, oc, k)
+        out[f"{name}_fwd"] = (times["fwd"], fl)
+        out[f"{name}_dw"] = (times["dw"], fl)
+        out[f"{name}_dx"] = (max(times["bwd"] - times["dw"], 1e-6), fl)
+    return out
+
+
+def run_b200(args, rank, world, local_rank):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from tiny_cnn_b200 import network as nw
+    from tiny_cnn_b200 import ops
+    from tiny_cnn_b200._lib import load
+    from tiny_cnn_b200.parallel import DataParallel
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    lib = load()
+    ctx = ops.Context(local_rank)
+    net = nw.cifar10_net(local_rank).build(BATCH, ctx)
+    net.init_weight(np.random.default_rng(42))  # same seed on every rank: identical replicas
+    opt = nw.adam(1e-3)
+    dp = DataParallel(net)
+
+    NB = 8  # distinct resident batches rotated through the step's fixed input buffer
+    xh, th = synthetic_batches(NB, 1000 + rank)
+    x_all = torch.from_numpy(xh).cuda()
+    t_all = torch.from_numpy(th).cuda()
+    x_cur = torch.empty(BATCH, IN_DIM, device="cuda")
+    t_cur = torch.empty(BATCH, OUT_DIM, device="cuda")
+    x_pin = torch.from_numpy(xh).pin_memory()
+    t_pin = torch.from_numpy(th).pin_memory()
+    out_pin = torch.empty(BATCH, OUT_DIM).pin_memory()
+    out_dev = net.output_tensor(BATCH)
+
+    def step(i):
+        x_cur.copy_(x_all[i % NB])
+        t_cur.copy_(t_all[i % NB])
+        if world == 1:
+            net.train_onebatch(opt, x_cur, t_cur, LOSS_CE)
+        else:
+            net.forward_backward(x_cur, t_cur, LOSS_CE)
+            dp.allreduce_grads()
+            net.update(opt)
+
+    def step_e2e(i):
+        if world == 1:
+            net.train_onebatch_host(opt, x_pin[i % NB], t_pin[i % NB], LOSS_CE, out_pin)
+        else:
+            x_cur.copy_(x_pin[i % NB], non_blocking=True)
+            t_cur.copy_(t_pin[i % NB], non_blocking=True)
+            net.forward_backward(x_cur, t_cur, LOSS_CE)
+            dp.allreduce_grads()
+            net.update(opt)
+            out_pin.copy_(out_dev, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        l0 = lib.b200_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = lib.b200_launch_count() - l0
+        if world > 1:
+            tms = torch.tensor([ms], device="cuda")
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ms = float(tms[0])
+        return ms, launches
+
+    warmup = max(args.warmup, 3)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, launches = timed(step, args.steps, warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _ = timed(step_e2e, args.steps, warmup)
+
+    global_batch = BATCH * world
+    value = global_batch * args.steps / (ms * 1e-3)
+    e2e_value = global_batch * args.steps / (ms_e2e * 1e-3)
+
+    line = None
+    if rank == 0:
+        # per-kernel roofline of the convolution kernels, timed alone with CUDA events
+        kt = time_kernels(ctx, torch, ops)
+        peak_fp32 = SM_COUNT * FP32_LANES * 2 * 1.965e9 / 1e12
+        peaks = {}
+        mp = ROOT / "MEASURED_PEAKS.json"
+        if mp.exists():
+            peaks = json.loads(mp.read_text())
+        kernels = {k: {"ms": round(v[0], 4), "tflops": round(v[1] / (v[0] * 1e-3) / 1e12, 3),
+                       "frac_fp32_peak": round(v[1] / (v[0] * 1e-3) / 1e12 / peak_fp32, 4)}
+                   for k, v in kt.items()}
+        dom = max(kt, key=lambda k: kt[k][0])
+        achieved = kt[dom][1] / (kt[dom][0] * 1e-3) / 1e12
+        conv_ms = sum(v[0] for v in kt.values())
+        conv_fl = sum(v[1] for v in kt.values())
+        roofline = {
+            "kernel": dom, "bound": "fp32", "achieved": round(achieved, 3), "peak": round(peak_fp32, 2),
+            "unit": "TFLOP/s", "frac": round(achieved / peak_fp32, 4), "traffic": None,
+            "peak_source": "fp32 FFMA: 148 SMs x 128 lanes x 2 flop x clocks.max.sm 1965 MHz (no measured "
+                           "fp32 figure in MEASURED_PEAKS.json; its bf16 tensor figure is "
+                           f"{peaks.get('bf16_tflops')} TFLOP/s, hbm {peaks.get('hbm_gbs')} GB/s)",
+            "conv_fwd_bwd_all": {"ms": round(conv_ms, 4), "tflops": round(conv_fl / (conv_ms * 1e-3) / 1e12, 3),
+                                 "frac": round(conv_fl / (conv_ms * 1e-3) / 1e12 / peak_fp32, 4)},
+        }
+        cpu = cpu_baseline() if world == 1 else None
+        line = {
+            "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "global_batch": global_batch,
+                       "parallelism": f"dp{world}",
+                       "l2": "8 resident input batches rotate through the step; activations + gradients "
+                             "touched per step are about 130 MB, larger than the 126 MB L2",
+                       "step": "CUDA graph of forward+backward+update" if world == 1 else
+                               "CUDA graph of forward+backward, NCCL sum all-reduce of the gradient "
+                               "bucket, update"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": BATCH * (IN_DIM + OUT_DIM) * 4,
+                    "d2h_bytes_per_step": BATCH * OUT_DIM * 4},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+            "kernels": kernels,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def cpu_baseline():
+    """The reference's CPU path on this box's host cores, on a bounded sample of the workload."""
+    import numpy as np
+    import oracle_lib as o
+    from cases import hyper_for, xavier_params
+    specs, keep = make_specs()
+    arr = (type(specs[0]) * len(specs))(*specs)
+    x, t = synthetic_batches(1, 1000)
+    hy = hyper_for(OPT_ADAM)
+    ref = o.load_reference()
+    if ref is None:
+        orc = o.load_oracle()
+        sub = 32
+        net = orc.orc_net_create(arr, len(specs), sub)
+        params = np.ctypeslib.as_array(orc.orc_net_params(net), shape=(orc.orc_net_param_count(net),))
+        params[:] = xavier_params(specs, 42)
+        t0 = time.perf_counter()
+        n = 0
+        while time.perf_counter() - t0 < 10.0:
+            orc.orc_net_train_step(net, o.p(x[0][:sub]), o.p(t[0][:sub]), sub, LOSS_CE, OPT_ADAM, C.byref(hy))
+            n += sub
+        secs = time.perf_counter() - t0
+        return {"value": n / secs, "unit": "samples/s", "cores": 1, "kind": "port",
+                "sample": f"{n} samples in steps of {sub} through the C restatement"}
+    h = ref.ref_net_create(arr, len(specs), 42)
+    ref.ref_net_set_params(h, o.p(xavier_params(specs, 42)))
+    ref.ref_net_fit(h, o.p(x[0]), o.p(t[0]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))  # warm-up
+    secs, steps = 0.0, 0
+    while secs < 10.0 and steps < 200:
+        secs += ref.ref_net_fit(h, o.p(x[0]), o.p(t[0]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))
+        steps += 1
+    cores = ref.ref_openmp_threads()
+    return {"value": BATCH * steps / secs, "unit": "samples/s", "cores": cores, "kind": "reference",
+            "sample": f"{steps} mini-batches of {BATCH} through network::fit (backend_t::internal, "
+                      f"OpenMP, {cores} threads)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.steps is None:
+        args.steps = 50 if args.impl == "b200" else 10
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus:
+        if args.gpus != 1 or world != 1:
+            raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run); "
+                             f"WORLD_SIZE is {world}")
+    run_b200(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -438,6 +438,14 @@ B200_API int b200_net_train_step(b200_net *net, const float *x, const float *t, 
                                  int loss_kind, int opt_kind, const b200_opt_hyper *h);
 
 /*
+ * forward + backward only (captured like the whole step): what a data-parallel
+ * rank runs before the gradient bucket is all-reduced and b200_net_update is
+ * called.
+ */
+B200_API int b200_net_forward_backward(b200_net *net, const float *x, const float *t, int batch,
+                                       int loss_kind);
+
+/*
  * The same step from HOST buffers (what network::train_onebatch does,
  * network.h:911-926): x/t are copied to the device, the step runs, and the
  * network output of the forward pass (batch x out_dim floats) is copied back

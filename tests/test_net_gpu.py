@@ -1,0 +1,209 @@
+"""GPU parity tests of the device-resident training step (b200_net_*): the
+networks of the benchmark configurations are stepped through the C ABI and
+compared with the oracle's restatement of network::fit, which test_oracle.py
+ties bit for bit to the unmodified reference.
+
+Tolerances: forward outputs 1e-4, gradients and updated weights 1e-3 (relative to
+the largest reference magnitude)."""
+import ctypes as C
+import os
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as o
+from cases import NET_CASES, build_net_specs, gen_net_data, hyper_for, net_layout, xavier_params
+from test_ops_gpu import FWD_TOL, GRAD_TOL, assert_close, dev, host
+from tiny_cnn_b200 import network as nw
+from tiny_cnn_b200._lib import LayerSpec, check, ptr
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def gold():
+    return np.load(GOLD / "ref_outputs.npz")
+
+
+class DeviceNet:
+    """Thin test harness over the C ABI net built from raw layer specs."""
+
+    def __init__(self, ctx, specs, max_batch):
+        self.ctx, self.lib = ctx, ctx.lib
+        arr = (LayerSpec * len(specs))(*specs)
+        h = C.c_void_p()
+        check(self.lib.b200_net_create(ctx.handle, arr, len(specs), max_batch, C.byref(h)))
+        self.h = h
+        self.n = int(self.lib.b200_net_param_count(h))
+        self.out_dim = int(self.lib.b200_net_out_dim(h))
+
+    def set_params(self, p):
+        check(self.lib.b200_net_set_params(self.h, ptr(np.ascontiguousarray(p, dtype=np.float32))))
+
+    def params(self):
+        p = np.empty(self.n, np.float32)
+        check(self.lib.b200_net_get_params(self.h, ptr(p)))
+        return p
+
+    def grads(self):
+        g = np.empty(self.n, np.float32)
+        check(self.lib.b200_net_get_grads(self.h, ptr(g)))
+        return g
+
+    def output(self, B):
+        out = np.empty((B, self.out_dim), np.float32)
+        check(self.lib.b200_memcpy_d2h(self.ctx.handle, ptr(out), self.lib.b200_net_output_ptr(self.h),
+                                       out.nbytes))
+        return out
+
+    def close(self):
+        self.lib.b200_net_destroy(self.h)
+
+
+def orc_net_for(oracle, specs, B, p0):
+    arr = (LayerSpec * len(specs))(*specs)
+    net = oracle.orc_net_create(arr, len(specs), B)
+    n = oracle.orc_net_param_count(net)
+    params = np.ctypeslib.as_array(oracle.orc_net_params(net), shape=(n,))
+    params[:] = p0
+    return net, params
+
+
+@pytest.mark.parametrize("fuse", ["0", "1"])
+@pytest.mark.parametrize("name", list(NET_CASES))
+def test_net_steps_match_oracle(ctx, oracle, gold, name, fuse, monkeypatch):
+    """Each step: outputs, batch-summed gradients and updated weights against the oracle;
+    after the last step the weights against the reference's recorded run."""
+    monkeypatch.setenv("B200_NET_NO_FUSE", "1" if fuse == "0" else "0")
+    monkeypatch.setenv("B200_NET_NO_GRAPH", "1")
+    c = NET_CASES[name]
+    specs, keep = build_net_specs(c["net"])
+    B = c["B"]
+    p0 = xavier_params(specs, c["seed"])
+    dnet = DeviceNet(ctx, specs, B)
+    assert dnet.n == p0.size
+    dnet.set_params(p0)
+    onet, oparams = orc_net_for(oracle, specs, B, p0)
+    x, t = gen_net_data(c)
+    h = hyper_for(c["opt"])
+    n = dnet.n
+    for s in range(c["steps"]):
+        xs, ts = x[s * B:(s + 1) * B], t[s * B:(s + 1) * B]
+        dx, dt = dev(xs), dev(ts)
+        check(dnet.lib.b200_net_forward(dnet.h, ptr(dx), B))
+        oracle.orc_net_forward(onet, o.p(xs), B)
+        out_ref = np.ctypeslib.as_array(oracle.orc_net_output(onet), shape=(B, c["out_dim"])).copy()
+        assert_close(dnet.output(B), out_ref, FWD_TOL, f"{name} step {s} output")
+        check(dnet.lib.b200_net_backward(dnet.h, ptr(dt), c["loss"]))
+        oracle.orc_net_backward(onet, o.p(xs), o.p(ts), c["loss"], B)
+        g_ref = np.ctypeslib.as_array(oracle.orc_net_grads(onet), shape=(n,)).copy()
+        g = dnet.grads()
+        for off, ln, _, _, _ in net_layout(specs)[0]:
+            assert_close(g[off:off + ln], g_ref[off:off + ln], GRAD_TOL, f"{name} step {s} grad@{off}")
+        check(dnet.lib.b200_net_update(dnet.h, c["opt"], C.byref(h)))
+        oracle.orc_net_update(onet, c["opt"], C.byref(h))
+        p = dnet.params()
+        for off, ln, _, _, _ in net_layout(specs)[0]:
+            assert_close(p[off:off + ln], oparams[off:off + ln], GRAD_TOL, f"{name} step {s} weights@{off}")
+    p1 = gold[f"net/{name}/p1"]
+    p = dnet.params()
+    for off, ln, _, _, _ in net_layout(specs)[0]:
+        assert_close(p[off:off + ln], p1[off:off + ln], GRAD_TOL, f"{name} final weights@{off} vs reference")
+    if c["opt"] == 1:
+        a, b = C.c_float(), C.c_float()
+        check(dnet.lib.b200_net_adam_powers(dnet.h, C.byref(a), C.byref(b)))
+        # Adam's powers advance once per parameter tensor: identical float products
+        assert [a.value, b.value] == gold[f"net/{name}/adam_powers"].tolist()
+    dnet.close()
+    oracle.orc_net_destroy(onet)
+
+
+@pytest.mark.parametrize("name", ["lenet_adagrad", "cifar_adam"])
+def test_train_step_graph_and_host_path(ctx, oracle, gold, name, monkeypatch):
+    """b200_net_train_step (captured graph after the first two calls) and the HOST
+    entry point reach the reference's weights too, and return the forward output."""
+    monkeypatch.setenv("B200_NET_NO_FUSE", "0")
+    monkeypatch.setenv("B200_NET_NO_GRAPH", "0")
+    c = NET_CASES[name]
+    specs, keep = build_net_specs(c["net"])
+    B = c["B"]
+    p0 = xavier_params(specs, c["seed"])
+    x, t = gen_net_data(c)
+    h = hyper_for(c["opt"])
+    p1 = gold[f"net/{name}/p1"]
+    for mode in ("device", "host"):
+        dnet = DeviceNet(ctx, specs, B)
+        dnet.set_params(p0)
+        # fixed device staging so every step reuses one captured graph
+        dx = torch.empty(B, c["in_dim"], device="cuda")
+        dt = torch.empty(B, c["out_dim"], device="cuda")
+        first_out = None
+        for s in range(c["steps"]):
+            xs, ts = x[s * B:(s + 1) * B], t[s * B:(s + 1) * B]
+            if mode == "device":
+                dx.copy_(torch.from_numpy(xs))
+                dt.copy_(torch.from_numpy(ts))
+                torch.cuda.synchronize()
+                check(dnet.lib.b200_net_train_step(dnet.h, ptr(dx), ptr(dt), B, c["loss"], c["opt"],
+                                                   C.byref(h)))
+            else:
+                out = np.empty((B, c["out_dim"]), np.float32)
+                check(dnet.lib.b200_net_train_step_host(dnet.h, ptr(np.ascontiguousarray(xs)),
+                                                        ptr(np.ascontiguousarray(ts)), B, c["loss"],
+                                                        c["opt"], C.byref(h), ptr(out)))
+                if s == 0:
+                    first_out = out
+        ctx.sync()
+        p = dnet.params()
+        for off, ln, _, _, _ in net_layout(specs)[0]:
+            assert_close(p[off:off + ln], p1[off:off + ln], GRAD_TOL, f"{name} {mode} weights@{off}")
+        if mode == "host":
+            onet, _ = orc_net_for(oracle, specs, B, p0)
+            oracle.orc_net_forward(onet, o.p(x[:B]), B)
+            out_ref = np.ctypeslib.as_array(oracle.orc_net_output(onet), shape=(B, c["out_dim"]))
+            assert_close(first_out, out_ref, FWD_TOL, f"{name} host step output")
+            oracle.orc_net_destroy(onet)
+        dnet.close()
+
+
+def test_sequential_mirror_lenet_100_steps(ctx, oracle):
+    """Benchmark configuration 1 through the Python mirror of network<sequential>:
+    LeNet-5, batch 16, 100 adagrad steps on +-1 targets; weights within 1e-3 of the oracle."""
+    net = nw.lenet5().build(16, ctx)
+    rng = np.random.default_rng(1001)
+    p0 = net.init_weight(rng)
+    specs, keep = build_net_specs("lenet")
+    assert net.n_params == net_layout(specs)[1] == 52012  # incl. unused average-pool slots
+    onet, oparams = orc_net_for(oracle, specs, 16, p0)
+    x = rng.uniform(-1, 1, (1600, 1024)).astype(np.float32)
+    labels = rng.integers(0, 10, 1600)
+    t = np.full((1600, 10), -1.0, np.float32)
+    t[np.arange(1600), labels] = 1.0
+    opt = nw.adagrad(0.01)
+    net.fit(opt, x, t, 16, 1, nw.LOSS_MSE)
+    h = opt.hyper()
+    for s in range(100):
+        oracle.orc_net_train_step(onet, o.p(x[s * 16:(s + 1) * 16]), o.p(t[s * 16:(s + 1) * 16]), 16, 0, 0,
+                                  C.byref(h))
+    p = net.get_params()
+    for off, ln, _, _, _ in net_layout(specs)[0]:
+        assert_close(p[off:off + ln], oparams[off:off + ln], GRAD_TOL, f"lenet 100 steps weights@{off}")
+    oracle.orc_net_destroy(onet)
+    net.close()
+
+
+def test_net_rejects_bad_input(ctx):
+    specs, keep = build_net_specs("tiny_conv")
+    dnet = DeviceNet(ctx, specs, 4)
+    x = torch.zeros(8, 288, device="cuda")
+    with pytest.raises(Exception):
+        check(dnet.lib.b200_net_forward(dnet.h, ptr(x), 8))  # batch above max_batch
+    bad = list(specs)
+    bad[5].fc_in = 81  # does not match the 80 outputs of the layer before
+    arr = (LayerSpec * len(bad))(*bad)
+    h = C.c_void_p()
+    assert dnet.lib.b200_net_create(ctx.handle, arr, len(bad), 4, C.byref(h)) != 0
+    dnet.close()

@@ -629,7 +629,9 @@ static void dw_tiling(const b200_ctx *ctx, DwCfg &p, int KH, int KW, int OCT) {
   p.OCBp = p.OCB + 4;
   const int NACC = OCT * KH * KW + OCT;
   size_t limit = ctx->smem_optin;
-  size_t want = limit / 2 - 2048;  // two resident blocks per SM when it fits
+  // the register tile (100+ accumulators) already limits an SM to one block,
+  // so a block may take nearly all shared memory for tall bands (less halo)
+  size_t want = limit - 4096;
   auto need = [&](int th) {
     p.TH = th;
     p.THp = th + KH - 1;

@@ -55,10 +55,13 @@ struct b200_net {
   const float *cur_x = nullptr;
   bool fuse = true;
   bool input_grad = true;
-  // captured step
-  cudaGraphExec_t graph = nullptr;
-  std::string graph_key;
-  int graph_seen = 0;
+  // captured launch sequences: slot 0 = whole step, slot 1 = forward + backward
+  struct GraphSlot {
+    cudaGraphExec_t exec = nullptr;
+    std::string key;
+    int seen = 0;
+    unsigned long long kernels = 0;  // kernels recorded in the graph
+  } slots[2];
   bool use_graph = true;
 };
 
@@ -364,7 +367,8 @@ int b200_net_destroy(b200_net *net) {
   if (!net) return 0;
   cudaSetDevice(net->ctx->device);
   cudaStreamSynchronize(net->ctx->stream);
-  if (net->graph) cudaGraphExecDestroy(net->graph);
+  for (auto &slot : net->slots)
+    if (slot.exec) cudaGraphExecDestroy(slot.exec);
   for (auto &L : net->layers) {
     cudaFree(L.out);
     cudaFree(L.grad);
@@ -479,6 +483,65 @@ int b200_net_adam_powers(const b200_net *net, float *b1_t, float *b2_t) {
   return 0;
 }
 
+}  // extern "C"
+
+// Runs `body` (a sequence of launches on the context stream) directly the first
+// time a configuration `key` is seen, captures it into a CUDA graph the second
+// time, and replays the graph afterwards.
+template <typename F>
+static int run_captured(b200_net *net, int slot_idx, const std::string &key, F body) {
+  if (!net->use_graph) return body();
+  b200_net::GraphSlot &slot = net->slots[slot_idx];
+  if (key != slot.key) {
+    if (slot.exec) {
+      B200_CUDA(cudaGraphExecDestroy(slot.exec));
+      slot.exec = nullptr;
+    }
+    slot.key = key;
+    slot.seen = 0;
+  }
+  cudaStream_t st = net->ctx->stream;
+  if (slot.exec) {
+    B200_CUDA(cudaGraphLaunch(slot.exec, st));
+    g_launches.fetch_add(slot.kernels, std::memory_order_relaxed);
+    return 0;
+  }
+  if (slot.seen++ == 0) return body();  // sets kernel attributes; nothing allocates afterwards
+  cudaGraph_t graph = nullptr;
+  unsigned long long before = g_launches.load();
+  B200_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed));
+  int r = body();
+  cudaError_t ce = cudaStreamEndCapture(st, &graph);
+  unsigned long long recorded = g_launches.load() - before;
+  if (r != 0) {
+    if (graph) cudaGraphDestroy(graph);
+    return r;
+  }
+  if (ce != cudaSuccess) {
+    set_error("stream capture failed: %s", cudaGetErrorString(ce));
+    return 1;
+  }
+  B200_CUDA(cudaGraphInstantiate(&slot.exec, graph, 0));
+  B200_CUDA(cudaGraphDestroy(graph));
+  slot.kernels = recorded;
+  B200_CUDA(cudaGraphLaunch(slot.exec, st));
+  return 0;
+}
+
+static std::string step_key(const float *x, const float *t, int batch, int loss_kind, int opt_kind,
+                            const b200_opt_hyper *h) {
+  std::string key;
+  key.append(reinterpret_cast<const char *>(&x), sizeof(x));
+  key.append(reinterpret_cast<const char *>(&t), sizeof(t));
+  key.append(reinterpret_cast<const char *>(&batch), sizeof(batch));
+  key.append(reinterpret_cast<const char *>(&loss_kind), sizeof(loss_kind));
+  key.append(reinterpret_cast<const char *>(&opt_kind), sizeof(opt_kind));
+  if (h) key.append(reinterpret_cast<const char *>(h), sizeof(*h));
+  return key;
+}
+
+extern "C" {
+
 int b200_net_train_step(b200_net *net, const float *x, const float *t, int batch, int loss_kind,
                         int opt_kind, const b200_opt_hyper *h) {
   B200_TRY(check_net(net));
@@ -486,53 +549,27 @@ int b200_net_train_step(b200_net *net, const float *x, const float *t, int batch
   B200_REQUIRE(batch >= 1 && batch <= net->max_batch, "net_train_step: batch %d outside 1..%d",
                batch, net->max_batch);
   B200_TRY(ensure_powers(net, opt_kind, h));
-  if (!net->use_graph) return step_eager(net, x, t, batch, loss_kind, opt_kind, h);
-
-  // key of the captured step: pointers, sizes, kinds and hyper-parameter bytes
-  std::string key;
-  key.append(reinterpret_cast<const char *>(&x), sizeof(x));
-  key.append(reinterpret_cast<const char *>(&t), sizeof(t));
-  key.append(reinterpret_cast<const char *>(&batch), sizeof(batch));
-  key.append(reinterpret_cast<const char *>(&loss_kind), sizeof(loss_kind));
-  key.append(reinterpret_cast<const char *>(&opt_kind), sizeof(opt_kind));
-  key.append(reinterpret_cast<const char *>(h), sizeof(*h));
-  if (key != net->graph_key) {
-    if (net->graph) {
-      B200_CUDA(cudaGraphExecDestroy(net->graph));
-      net->graph = nullptr;
-    }
-    net->graph_key = key;
-    net->graph_seen = 0;
-  }
-  if (net->graph) {
-    B200_CUDA(cudaGraphLaunch(net->graph, net->ctx->stream));
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    net->cur_batch = batch;
-    net->cur_x = x;
-    return 0;
-  }
-  if (net->graph_seen++ == 0) {
-    // first sight of this configuration: run eagerly (sets kernel attributes,
-    // grows nothing afterwards)
+  int r = run_captured(net, 0, step_key(x, t, batch, loss_kind, opt_kind, h), [&]() {
     return step_eager(net, x, t, batch, loss_kind, opt_kind, h);
-  }
-  cudaStream_t st = net->ctx->stream;
-  cudaGraph_t graph = nullptr;
-  B200_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed));
-  int r = step_eager(net, x, t, batch, loss_kind, opt_kind, h);
-  cudaError_t ce = cudaStreamEndCapture(st, &graph);
-  if (r != 0) {
-    if (graph) cudaGraphDestroy(graph);
-    return r;
-  }
-  if (ce != cudaSuccess) {
-    set_error("net_train_step: stream capture failed: %s", cudaGetErrorString(ce));
-    return 1;
-  }
-  B200_CUDA(cudaGraphInstantiate(&net->graph, graph, 0));
-  B200_CUDA(cudaGraphDestroy(graph));
-  B200_CUDA(cudaGraphLaunch(net->graph, st));
-  return 0;
+  });
+  net->cur_batch = batch;
+  net->cur_x = x;
+  return r;
+}
+
+int b200_net_forward_backward(b200_net *net, const float *x, const float *t, int batch,
+                              int loss_kind) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(x && t, "net_forward_backward: NULL argument");
+  B200_REQUIRE(batch >= 1 && batch <= net->max_batch,
+               "net_forward_backward: batch %d outside 1..%d", batch, net->max_batch);
+  int r = run_captured(net, 1, step_key(x, t, batch, loss_kind, -1, nullptr), [&]() {
+    B200_TRY(net_forward_impl(net, x, batch));
+    return net_backward_impl(net, t, loss_kind);
+  });
+  net->cur_batch = batch;
+  net->cur_x = x;
+  return r;
 }
 
 int b200_net_train_step_host(b200_net *net, const float *x_host, const float *t_host, int batch,

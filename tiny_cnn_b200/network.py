@@ -242,6 +242,10 @@ class Sequential:
     def backward(self, t: torch.Tensor, loss: int):
         check(self.lib.b200_net_backward(self.handle, ptr(t), loss))
 
+    def forward_backward(self, x: torch.Tensor, t: torch.Tensor, loss: int):
+        """fprop + bprop in one (graph-captured) call; leaves the gradient bucket ready."""
+        check(self.lib.b200_net_forward_backward(self.handle, ptr(x), ptr(t), x.shape[0], loss))
+
     def update(self, opt):
         h = opt.hyper()
         check(self.lib.b200_net_update(self.handle, opt.kind, C.byref(h)))

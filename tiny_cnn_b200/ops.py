@@ -21,15 +21,25 @@ from ._lib import (ACT_NONE, ACT_RELU, ACT_SOFTMAX, ACT_TANH, LOSS_CROSS_ENTROPY
 
 
 class Context:
-    """b200_ctx bound to one GPU; work is issued on torch's current stream of that device."""
+    """b200_ctx bound to one GPU; work is issued on torch's current stream of that device.
+
+    The legacy default stream cannot be captured into a CUDA graph, so when torch's
+    current stream is the default one a new torch stream is created and made current:
+    torch copies and the library's kernels then share one ordered stream."""
 
     def __init__(self, device: int = 0, stream: Optional[int] = None):
         self.lib = L.load()
         if self.lib.b200_device_count() <= 0:
             raise B200Error("no CUDA device is visible; this library has no CPU path")
         self.device = device
+        self.torch_stream = None
         if stream is None:
-            stream = torch.cuda.current_stream(device).cuda_stream
+            ts = torch.cuda.current_stream(device)
+            if ts.cuda_stream == 0:
+                ts = torch.cuda.Stream(device)
+                torch.cuda.set_stream(ts)
+            self.torch_stream = ts
+            stream = ts.cuda_stream
         h = C.c_void_p()
         check(self.lib.b200_ctx_create(device, C.c_void_p(stream), C.byref(h)))
         self.handle = h
