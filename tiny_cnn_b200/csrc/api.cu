@@ -26,8 +26,8 @@ int conv_fwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
   B200_REQUIRE(batch >= 0, "conv2d_fwd: negative batch");
   ConvGeom g;
   B200_TRY(conv_geom_from_desc(ctx, d, &g));
+  if (batch == 0) return 0;  // empty batch: nothing to read or write
   B200_REQUIRE(in && W && out && (bias || !g.has_bias), "conv2d_fwd: NULL buffer");
-  if (batch == 0) return 0;
   bool tiled = use_tiled(d, g);
   B200_REQUIRE(tiled || d->algo != 2, "conv2d_fwd: tiled kernels need stride 1, dilation 1, 3x3/5x5");
   if (tiled) {
@@ -46,7 +46,8 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
   B200_REQUIRE(batch >= 0, "conv2d_bwd: negative batch");
   ConvGeom g;
   B200_TRY(conv_geom_from_desc(ctx, d, &g));
-  B200_REQUIRE(in && W && dout && dW && (db || !g.has_bias), "conv2d_bwd: NULL buffer");
+  B200_REQUIRE(dW && (db || !g.has_bias), "conv2d_bwd: NULL gradient buffer");
+  B200_REQUIRE(batch == 0 || (in && W && dout), "conv2d_bwd: NULL buffer");
   size_t lenW = conv_weight_len(g);
   if (batch == 0) {
     if (!accumulate) {
