@@ -131,6 +131,38 @@ B200_API int b200_conv2d_bwd(b200_ctx *ctx, const b200_conv_desc *d, const float
                              const float *W, const float *dout, float *din, float *dW,
                              float *db, int accumulate, int batch);
 
+/*
+ * Weight gradient only -- dW (+)= sum_n dW_n, db (+)= sum_n db_n, the same
+ * values b200_conv2d_bwd produces -- for callers that are not allowed to
+ * allocate device memory at call time.  It has NO counterpart in the reference.
+ *
+ * Who needs it: a host that handed all of its HBM to its own pools at start-up
+ * and has nothing left for cudaMalloc to find, or a latency-bound loop that
+ * cannot take the device-wide synchronisation cudaMalloc/cudaFree imply.  The
+ * other entry points grow a per-context scratch buffer on demand; this one
+ * takes no context and never calls cudaMalloc, cudaFree or any allocating
+ * routine.  Its scratch (the partial sums of the batch slices) is a fixed
+ * 16 MiB array compiled into the library, which every GPU that loads the
+ * library therefore carries until the process exits.
+ *
+ * Limits and rules:
+ *  - `stream` is a cudaStream_t (NULL = the default stream); all pointers are
+ *    DEVICE memory of the CURRENT device, which the caller selects beforehand.
+ *  - stride 1, dilation 1, 3x3 or 5x5 windows, output width <= 64, no
+ *    connection table (d->tbl must be NULL); anything else is refused with an
+ *    error text, as is a filter tensor whose single partial row (out_c*in_c*k*k
+ *    + out_c floats) exceeds the 4 Mi-float array.
+ *  - The first call on each device looks up the array's device address; make
+ *    that first call before any stream capture begins.
+ *  - All calls share the one array and leave their partial sums in it.  No
+ *    call depends on what an earlier call left behind (every element that is
+ *    read is written first), but two calls whose kernels overlap in time on the
+ *    same GPU -- different streams, different threads -- race on it.
+ */
+B200_API int b200_conv2d_dw_noalloc(void *stream, const b200_conv_desc *d, const float *in,
+                                    const float *dout, float *dW, float *db, int accumulate,
+                                    int batch);
+
 /* HOST-buffer forms of the two calls above (what the OpKernel branches call). */
 B200_API int b200_conv2d_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
                                   const float *W, const float *bias, float *out, int batch);

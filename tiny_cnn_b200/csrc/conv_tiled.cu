@@ -765,4 +765,143 @@ int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// weight gradient for callers that must not allocate
+// ---------------------------------------------------------------------------
+
+// Fixed scratch for b200_conv2d_dw_noalloc: 4 Mi floats (16 MiB) of partial-sum
+// rows.  It is part of the library image, so every GPU that loads the library
+// holds it from load to exit whether or not the entry point is ever called.
+constexpr size_t kNoAllocScratchFloats = (size_t)4 << 20;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+constexpr int kNoAllocMaxDevices = 64;
+struct NoAllocDevice {
+  bool ready = false;
+  float *scratch = nullptr;  // device address of g_noalloc_scratch on this GPU
+  int sm_count = 0;
+  size_t smem_optin = 0;
+};
+static NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+static std::atomic_flag g_noalloc_lock = ATOMIC_FLAG_INIT;
+
+// One-time set-up for the CURRENT device.  `g_noalloc_scratch` used as a value
+// in host code is only the host-side shadow of the symbol; the address a kernel
+// can dereference has to be asked for with cudaGetSymbolAddress.
+static int noalloc_setup(int dev, NoAllocDevice **out) {
+  B200_REQUIRE(dev >= 0 && dev < kNoAllocMaxDevices, "conv2d_dw_noalloc: device %d not supported",
+               dev);
+  while (g_noalloc_lock.test_and_set(std::memory_order_acquire)) {
+  }
+  NoAllocDevice &nd = g_noalloc_dev[dev];
+  int rc = 0;
+  if (!nd.ready) {
+    void *addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&addr, g_noalloc_scratch);
+    int sms = 0, smem = 0;
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess)
+      e = cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (e != cudaSuccess || addr == nullptr) {
+      set_error("conv2d_dw_noalloc: set-up on device %d failed: %s", dev, cudaGetErrorString(e));
+      rc = 1;
+    } else {
+      nd.scratch = static_cast<float *>(addr);
+      nd.sm_count = sms;
+      nd.smem_optin = (size_t)smem;
+      nd.ready = true;
+    }
+  }
+  g_noalloc_lock.clear(std::memory_order_release);
+  *out = &nd;
+  return rc;
+}
+
 }  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_conv2d_dw_noalloc(void *stream, const b200_conv_desc *d, const float *in,
+                                      const float *dout, float *dW, float *db, int accumulate,
+                                      int batch) {
+  B200_REQUIRE(d != nullptr, "conv2d_dw_noalloc: descriptor is NULL");
+  B200_REQUIRE(batch >= 0, "conv2d_dw_noalloc: negative batch");
+  B200_REQUIRE(d->tbl == nullptr,
+               "conv2d_dw_noalloc: connection tables are not supported (they need a device copy)");
+  int dev = -1;
+  B200_CUDA(cudaGetDevice(&dev));
+  NoAllocDevice *nd = nullptr;
+  B200_TRY(noalloc_setup(dev, &nd));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  // geometry through the same routine as every other entry point; with no
+  // table it touches nothing but the descriptor
+  b200_ctx shell;
+  shell.device = dev;
+  shell.sm_count = nd->sm_count;
+  shell.smem_optin = nd->smem_optin;
+  shell.stream = st;
+  ConvGeom g;
+  B200_TRY(conv_geom_from_desc(&shell, d, &g));
+  B200_REQUIRE(dW && (db || !g.has_bias), "conv2d_dw_noalloc: NULL gradient buffer");
+  const size_t lenW = conv_weight_len(g);
+  if (batch == 0) {
+    if (!accumulate) {
+      B200_CUDA(cudaMemsetAsync(dW, 0, lenW * sizeof(float), st));
+      if (g.has_bias) B200_CUDA(cudaMemsetAsync(db, 0, g.OC * sizeof(float), st));
+    }
+    return 0;
+  }
+  B200_REQUIRE(in && dout, "conv2d_dw_noalloc: NULL input buffer");
+  B200_REQUIRE(conv_tiled_ok(g) && g.OW <= 64,
+               "conv2d_dw_noalloc: only stride 1, dilation 1, 3x3 or 5x5 windows and output width "
+               "<= 64 are supported");
+
+  DwCfg p{};
+  dw_fill(p, g, batch);
+  const int OCT = g.KH == 3 ? 8 : 4;
+  dw_tiling(&shell, p, g.KH, g.KW, OCT);
+  // the partial rows must fit the fixed array: fewer, longer batch slices if needed
+  const size_t max_rows = kNoAllocScratchFloats / p.row_len;
+  B200_REQUIRE(max_rows >= 1,
+               "conv2d_dw_noalloc: one partial row needs %zu floats but the fixed scratch holds %zu; "
+               "use b200_conv2d_bwd for filters this large",
+               p.row_len, kNoAllocScratchFloats);
+  if ((size_t)p.splits > max_rows) p.splits = (int)max_rows;
+  p.in = in;
+  p.dout = dout;
+  p.partial = nd->scratch;
+  const int NACC = OCT * g.KH * g.KW + OCT;
+  size_t stage = (size_t)(p.x_tile_floats + p.dy_tile_floats) * 4;
+  size_t red = (size_t)p.SL * (p.OCB / OCT) * p.ICT * NACC * 4;
+  size_t smem = 2 * stage > red ? 2 * stage : red;
+  B200_REQUIRE(smem <= nd->smem_optin,
+               "conv2d_dw_noalloc: tile needs %zu bytes of shared memory (limit %zu)", smem,
+               nd->smem_optin);
+  int threads = (p.OCB / OCT) * p.ICT * p.SL;
+  int blocks = p.tiles_oc * p.tiles_ic * p.splits;
+  // Every block overwrites its whole tile of its row, so nothing left in the
+  // array by an earlier call is ever read: no clearing is needed.
+  if (g.KH == 3) {
+    B200_CUDA(cudaFuncSetAttribute(conv_dw_kernel<3, 3, 8>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    conv_dw_kernel<3, 3, 8><<<blocks, threads, smem, st>>>(p);
+  } else {
+    B200_CUDA(cudaFuncSetAttribute(conv_dw_kernel<5, 5, 4>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    conv_dw_kernel<5, 5, 4><<<blocks, threads, smem, st>>>(p);
+  }
+  B200_LAUNCHED();
+  const int mblocks = (int)((lenW + 255) / 256 < (size_t)nd->sm_count * 8 ? (lenW + 255) / 256
+                                                                          : (size_t)nd->sm_count * 8);
+  merge_rows_kernel<<<mblocks, 256, 0, st>>>(nd->scratch, p.splits, p.row_len, dW, lenW, accumulate,
+                                             nullptr, 1, 1, 1, 0);
+  B200_LAUNCHED();
+  if (g.has_bias) {
+    merge_rows_kernel<<<(g.OC + 255) / 256, 256, 0, st>>>(nd->scratch + lenW, p.splits, p.row_len,
+                                                         db, (size_t)g.OC, accumulate, nullptr, 1, 1,
+                                                         1, 0);
+    B200_LAUNCHED();
+  }
+  return 0;
+}
