@@ -188,7 +188,10 @@ int b200_fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const
   B200_TRY(check_ctx(ctx));
   B200_REQUIRE(in_size > 0 && out_size > 0 && batch >= 0, "fc_fwd: bad size");
   B200_REQUIRE(in && W && out, "fc_fwd: NULL buffer");
-  return fc_fwd(ctx, in_size, out_size, in, W, bias, out, batch, B200_ACT_NONE);
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, fc_scratch_floats(ctx, in_size, out_size, batch) * sizeof(float), &scratch));
+  return fc_fwd(ctx, in_size, out_size, in, W, bias, out, batch, B200_ACT_NONE,
+                static_cast<float *>(scratch));
 }
 
 int b200_fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
@@ -196,7 +199,10 @@ int b200_fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const
   B200_TRY(check_ctx(ctx));
   B200_REQUIRE(in_size > 0 && out_size > 0 && batch >= 0, "fc_bwd: bad size");
   B200_REQUIRE(in && W && dout && dW, "fc_bwd: NULL buffer");
-  return fc_bwd(ctx, in_size, out_size, in, W, dout, din, dW, db, accumulate, batch);
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, fc_scratch_floats(ctx, in_size, out_size, batch) * sizeof(float), &scratch));
+  return fc_bwd(ctx, in_size, out_size, in, W, dout, din, dW, db, accumulate, batch,
+                static_cast<float *>(scratch));
 }
 
 int b200_fc_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
@@ -209,9 +215,11 @@ int b200_fc_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in, 
                   {bias, nullptr, bias ? out_size * f : 0, nullptr},
                   {nullptr, out, (size_t)out_size * batch * f, nullptr}};
   B200_TRY(stage_in(ctx, b, 4));
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, fc_scratch_floats(ctx, in_size, out_size, batch) * sizeof(float), &scratch));
   B200_TRY(fc_fwd(ctx, in_size, out_size, (const float *)b[0].dev, (const float *)b[1].dev,
                   bias ? (const float *)b[2].dev : nullptr, (float *)b[3].dev, batch,
-                  B200_ACT_NONE));
+                  B200_ACT_NONE, static_cast<float *>(scratch)));
   return stage_out(ctx, b, 4);
 }
 
@@ -229,9 +237,11 @@ int b200_fc_bwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in, 
                   {accumulate ? dW : nullptr, dW, nw, nullptr},
                   {accumulate && nb ? db : nullptr, db, nb, nullptr}};
   B200_TRY(stage_in(ctx, b, 6));
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, fc_scratch_floats(ctx, in_size, out_size, batch) * sizeof(float), &scratch));
   B200_TRY(fc_bwd(ctx, in_size, out_size, (const float *)b[0].dev, (const float *)b[1].dev,
                   (const float *)b[2].dev, din ? (float *)b[3].dev : nullptr, (float *)b[4].dev,
-                  db ? (float *)b[5].dev : nullptr, accumulate, batch));
+                  db ? (float *)b[5].dev : nullptr, accumulate, batch, static_cast<float *>(scratch)));
   return stage_out(ctx, b, 6);
 }
 
@@ -369,7 +379,7 @@ int b200_loss_value(b200_ctx *ctx, int kind, const float *y, const float *t, flo
 int b200_merge_grads(b200_ctx *ctx, const float *grads, int rows, size_t len, float *dst) {
   B200_TRY(check_ctx(ctx));
   B200_REQUIRE(grads && dst && rows >= 1, "merge_grads: bad argument");
-  return merge_rows(ctx, grads, rows, len, dst, len, 0, nullptr);
+  return merge_rows(ctx, grads, rows, len, dst, len, 0, nullptr, /*in_order=*/1);
 }
 int b200_opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper *h, const float *dW, float *W,
                     float *state0, float *state1, size_t len) {

@@ -61,6 +61,11 @@ static inline size_t align_up(size_t a, size_t b) { return (a + b - 1) / b * b; 
 
 }  // namespace b200
 
+// Tile shape of the direct-convolution kernel chosen for one problem.
+struct TileChoice {
+  int OCT, OCB, TH, TWG, NSB, ICB;
+};
+
 // ----------------------------------------------------------------------------
 // context
 // ----------------------------------------------------------------------------
@@ -81,6 +86,12 @@ struct b200_ctx {
   size_t arena_bytes = 0;
   void *pinned = nullptr;
   size_t pinned_bytes = 0;
+
+  // device word a kernel sets when a bounded wait ran out; read by b200_ctx_sync
+  int *dev_err = nullptr;
+
+  // tile shapes already chosen, keyed by the problem's dimensions
+  std::map<std::string, TileChoice> tile_cache;
 
   // device copies of connection tables, keyed by their bytes
   std::map<std::string, uint8_t *> tbl_cache;
@@ -139,16 +150,22 @@ int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in,
 // when accumulating and zeroed otherwise).
 // `mask` (may be nullptr) names a convolution whose connection table zeroes the
 // gradient of unconnected (o, inc) pairs within the first conv_weight_len entries.
+// `in_order` != 0 adds the rows strictly one after the other (the order of
+// edge::merge_grads); otherwise four interleaved running sums are combined at the end.
 int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *dst, size_t len,
-               int accumulate, const ConvGeom *mask);
+               int accumulate, const ConvGeom *mask, int in_order = 0);
 
 // ----------------------------------------------------------------------------
 // other ops
 // ----------------------------------------------------------------------------
+// `scratch` (fc_scratch_floats floats, may be nullptr) holds the k-slice partial
+// sums small GEMMs are split into.
+size_t fc_scratch_floats(const b200_ctx *ctx, int in_size, int out_size, int B);
 int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
-           const float *bias, float *out, int B, int act);
+           const float *bias, float *out, int B, int act, float *scratch);
 int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
-           const float *dout, float *din, float *dW, float *db, int accumulate, int B);
+           const float *dout, float *din, float *dW, float *db, int accumulate, int B,
+           float *scratch);
 
 int maxpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, float *out,
                 int32_t *argmax, int B);

@@ -17,6 +17,8 @@
 // (tiny_dnn/core/kernels/conv2d_op_internal.h:13-74, :91-127, :130-179) with
 // zero padding applied by predicated staging instead of a padded copy
 // (tiny_dnn/core/params/conv_params.h:106-133).
+#include <algorithm>
+
 #include "common.cuh"
 #include "device_utils.cuh"
 
@@ -72,6 +74,7 @@ struct CoreCfg {
   const float *wt;    // [CI][KH][KW][COp]
   const float *bias;  // [CO] or nullptr
   float *out;
+  int *err;           // set when a bounded wait on a bulk copy runs out
   int B, CI, HI, WI, CO, COp, HO, WO;
   int pad_t, pad_l, act;
   // tiling
@@ -81,6 +84,7 @@ struct CoreCfg {
   int in_tile_floats, w_tile_floats, nrows;
   unsigned pitch_magic;
   int log2_ocb4;
+  int w_bulk;  // 1: a filter chunk is contiguous in memory and is fetched by one bulk copy
 };
 
 // v / d for v*d < 2^32 through one multiply; magic 0 encodes d == 1
@@ -91,6 +95,12 @@ static unsigned make_magic(unsigned d) {
   return d <= 1 ? 0u : (unsigned)((0x100000000ULL / d) + 1ULL);
 }
 
+// Block = one tile of (NSB samples) x (TH rows) x (TWG*8 columns) x (OCB output
+// channels); thread = 8 consecutive pixels x OCT output channels.  Input
+// channels are consumed in chunks of ICB through a two-stage shared-memory
+// pipeline: the input patch arrives by 4-byte cp.async (zero fill outside the
+// image = padding), the filter chunk by one bulk asynchronous copy signalled on
+// an mbarrier when it is contiguous in memory, else by 16-byte cp.async.
 template <int KH, int KW, int OCT>
 __global__ void __launch_bounds__(256, 2) conv_core_kernel(const CoreCfg p) {
   extern __shared__ __align__(16) float smem[];
@@ -116,8 +126,14 @@ __global__ void __launch_bounds__(256, 2) conv_core_kernel(const CoreCfg p) {
   float *stage0 = smem;
   float *stage1 = smem + stage_floats;
   long long *rowoff = reinterpret_cast<long long *>(smem + 2 * stage_floats);
-  int *rowic = reinterpret_cast<int *>(rowoff + p.nrows);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(rowoff + p.nrows);  // one per stage
+  int *rowic = reinterpret_cast<int *>(bars + 2);
 
+  if (p.w_bulk && tid == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_fence_init();
+  }
   // row table: staged row -> offset of (n, ic, y, x=0) with ic relative to the
   // chunk base, or -1 when the row lies outside the batch / image
   for (int r = tid; r < p.nrows; r += nthreads) {
@@ -139,10 +155,30 @@ __global__ void __launch_bounds__(256, 2) conv_core_kernel(const CoreCfg p) {
   const long long chan_stride = (long long)p.HI * p.WI;
   const int ocb4 = p.OCB >> 2;
 
-  auto load_chunk = [&](int chunk, float *stage) {
+  auto load_chunk = [&](int chunk, float *stage, uint64_t *bar) {
     const int c0 = chunk * p.ICB;
     float *itile = stage;
     float *wtile = stage + p.in_tile_floats;
+    if (p.w_bulk) {
+      if (tid == 0) {
+        const int icn = min(p.ICB, p.CI - c0);
+        const uint32_t bytes = (uint32_t)(icn * KK * p.COp) * 4u;
+        mbar_expect_tx(bar, bytes);
+        bulk_copy_g2s(wtile, p.wt + (size_t)c0 * KK * p.COp, bytes, bar);
+      }
+    } else {
+      const int nq = p.ICB * KK * ocb4;
+      for (int q = tid; q < nq; q += nthreads) {
+        int row = q >> p.log2_ocb4;
+        int c4 = q & (ocb4 - 1);
+        int ic = row / KK;
+        int tap = row - ic * KK;
+        int oc = o0 + c4 * 4;
+        bool ok = (c0 + ic) < p.CI && oc < p.COp;
+        const float *src = ok ? p.wt + ((size_t)(c0 + ic) * KK + tap) * p.COp + oc : p.wt;
+        cp_async16(wtile + q * 4, src, ok);
+      }
+    }
     for (int idx = tid; idx < p.in_tile_floats; idx += nthreads) {
       int row = (int)fastdiv((unsigned)idx, p.pitch_magic);
       int j = idx - row * p.PITCH;
@@ -152,17 +188,6 @@ __global__ void __launch_bounds__(256, 2) conv_core_kernel(const CoreCfg p) {
       bool ok = off >= 0 && (c0 + ic) < p.CI && x >= 0 && x < p.WI;
       const float *src = ok ? p.in + off + (long long)c0 * chan_stride + x : p.in;
       cp_async4(itile + idx, src, ok);
-    }
-    const int nq = p.ICB * KK * ocb4;
-    for (int q = tid; q < nq; q += nthreads) {
-      int row = q >> p.log2_ocb4;
-      int c4 = q & (ocb4 - 1);
-      int ic = row / KK;
-      int tap = row - ic * KK;
-      int oc = o0 + c4 * 4;
-      bool ok = (c0 + ic) < p.CI && oc < p.COp;
-      const float *src = ok ? p.wt + ((size_t)(c0 + ic) * KK + tap) * p.COp + oc : p.wt;
-      cp_async16(wtile + q * 4, src, ok);
     }
   };
 
@@ -181,19 +206,25 @@ __global__ void __launch_bounds__(256, 2) conv_core_kernel(const CoreCfg p) {
 #pragma unroll
     for (int px = 0; px < 8; ++px) acc[o][px] = 0.f;
 
-  load_chunk(0, stage0);
+  load_chunk(0, stage0, &bars[0]);
   cp_async_commit();
 
+  bool failed = false;
   for (int chunk = 0; chunk < nchunks; ++chunk) {
     float *cur = (chunk & 1) ? stage1 : stage0;
     if (chunk + 1 < nchunks) {
-      load_chunk(chunk + 1, (chunk & 1) ? stage0 : stage1);
+      load_chunk(chunk + 1, (chunk & 1) ? stage0 : stage1, &bars[(chunk + 1) & 1]);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
-    __syncthreads();
+    if (p.w_bulk) {
+      // stage (chunk & 1) completes for the (chunk >> 1)-th time
+      if (!mbar_wait_bounded(&bars[chunk & 1], (uint32_t)((chunk >> 1) & 1))) failed = true;
+    }
+    failed = __syncthreads_or(failed) != 0;  // every thread takes the same exit
+    if (failed) break;
 
     const float *itile = cur + ((s * p.ICB) * p.THp + ty) * p.PITCH + txg * 8;
     const float *wtile = cur + p.in_tile_floats + ocg * OCT;
@@ -231,6 +262,13 @@ __global__ void __launch_bounds__(256, 2) conv_core_kernel(const CoreCfg p) {
       }
     }
     __syncthreads();
+  }
+  if (failed) {
+    // a bulk copy never signalled: report, let the other copies of this block
+    // drain, and leave without writing results
+    if (p.err) atomicExch(p.err, 1);
+    cp_async_wait<0>();
+    return;
   }
 
   // ---- epilogue -------------------------------------------------------------
@@ -273,56 +311,121 @@ bool conv_tiled_ok(const ConvGeom &g) {
 
 static int round_up(int a, int b) { return (a + b - 1) / b * b; }
 
-// Pick the tile shape for a problem with CO output channels and HO x WO outputs.
-static int core_tiling(const b200_ctx *ctx, CoreCfg &p, int KH, int KW) {
-  // Small problems (few 8x8 register tiles per SM) use 8 px x 4 oc per thread
-  // to put more threads in flight.
-  long long tiles8 = (long long)p.B * p.HO * ceil_div(p.WO, 8) * ceil_div(p.CO, 8);
-  int OCT = tiles8 < (long long)ctx->sm_count * 512 ? 4 : 8;
-  int co_r = round_up(p.CO, 8);
-  p.OCB = co_r >= 64 ? 64 : (co_r > 16 ? 32 : co_r);  // 8, 16, 32 or 64
-  p.COp = co_r;
-  int nocg = p.OCB / OCT;
-  int target_pg = 256 / nocg;
-  int wg = ceil_div(p.WO, 8);
-  p.TWG = wg <= 8 ? wg : 4;
-  if (p.TWG > target_pg) p.TWG = target_pg;
-  p.TH = target_pg / p.TWG;
-  if (p.TH > p.HO) p.TH = p.HO;
-  if (p.TH < 1) p.TH = 1;
-  p.NSB = target_pg / (p.TWG * p.TH);
-  if (p.NSB > p.B) p.NSB = p.B;
-  if (p.NSB < 1) p.NSB = 1;
-  // Enough blocks to fill the machine twice, but never below 128 threads.
-  auto blocks = [&]() {
-    return (long long)ceil_div(p.WO, p.TWG * 8) * ceil_div(p.HO, p.TH) * ceil_div(p.CO, p.OCB) *
-           ceil_div(p.B, p.NSB);
-  };
-  auto threads = [&]() { return nocg * p.TWG * p.TH * p.NSB; };
-  while (blocks() < 2LL * ctx->sm_count && p.NSB > 1 && threads() / 2 >= 128)
-    p.NSB = (p.NSB + 1) / 2;
-  while (blocks() < 2LL * ctx->sm_count && p.TH > 1 && nocg * p.TWG * ((p.TH + 1) / 2) * p.NSB >= 128)
-    p.TH = (p.TH + 1) / 2;
-  p.ICB = p.CI < 8 ? p.CI : 8;
+// channel pitch of the re-laid-out filters: output channels padded to a
+// multiple of 8 (4 when there are at most 4 of them)
+static int padded_channels(int c) { return c <= 4 ? 4 : round_up(c, 8); }
+
+static size_t core_smem_bytes(const CoreCfg &p) {
+  return (size_t)2 * (p.in_tile_floats + p.w_tile_floats) * 4 + (size_t)p.nrows * 12 + 16 + 16;
+}
+
+static void core_fill_tile(CoreCfg &p, int KH, int KW) {
+  p.THp = p.TH + KH - 1;
   p.PITCH = round_up(p.TWG * 8 + KW - 1, 4);
-  auto smem_need = [&]() {
-    p.THp = p.TH + KH - 1;
-    p.in_tile_floats = p.NSB * p.ICB * p.THp * p.PITCH;
-    p.w_tile_floats = p.ICB * KH * KW * p.OCB;
-    p.nrows = p.NSB * p.ICB * p.THp;
-    return (size_t)2 * (p.in_tile_floats + p.w_tile_floats) * 4 + (size_t)p.nrows * 12 + 16;
-  };
-  // keep two blocks per SM resident when possible
-  size_t want = ctx->smem_optin / 2 - 2048;
-  while (smem_need() > want && p.ICB > 1) p.ICB = (p.ICB + 1) / 2;
+  p.in_tile_floats = p.NSB * p.ICB * p.THp * p.PITCH;
+  p.w_tile_floats = p.ICB * KH * KW * p.OCB;
+  p.nrows = p.NSB * p.ICB * p.THp;
   p.tiles_x = ceil_div(p.WO, p.TWG * 8);
   p.tiles_y = ceil_div(p.HO, p.TH);
   p.tiles_oc = ceil_div(p.CO, p.OCB);
   p.tiles_n = ceil_div(p.B, p.NSB);
   p.pitch_magic = make_magic((unsigned)p.PITCH);
   p.log2_ocb4 = ilog2(p.OCB / 4);
-  smem_need();
-  return OCT;
+  p.w_bulk = (p.OCB == p.COp) ? 1 : 0;
+}
+
+static void apply_choice(CoreCfg &p, const TileChoice &c, int KH, int KW) {
+  p.OCB = c.OCB;
+  p.TH = c.TH;
+  p.TWG = c.TWG;
+  p.NSB = c.NSB;
+  p.ICB = c.ICB;
+  core_fill_tile(p, KH, KW);
+}
+
+// Every legal tile shape with a score from a small model of the launch: blocks
+// are spread over the SMs, an SM's time is its number of blocks times the
+// instructions of a block (FMAs plus staging plus a fixed cost per chunk),
+// discounted when few warps are resident (latency is exposed) and for the 8x4
+// thread tile (more shared-memory loads per FMA); blocks that do not all fit on
+// the machine at once run in waves.  Sorted best first.
+static std::vector<std::pair<double, TileChoice>> core_candidates(const b200_ctx *ctx, CoreCfg p,
+                                                                   int KH, int KW) {
+  std::vector<std::pair<double, TileChoice>> out;
+  p.COp = padded_channels(p.CO);
+  const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  const size_t smem_sm = 233472;  // shared memory of one SM
+  const int wg = ceil_div(p.WO, 8);
+  for (int OCT = 8; OCT >= 4; OCT -= 4) {
+    if (OCT == 8 && p.COp < 8) continue;
+    // channels per block: all of them when they fit 64 (the filter chunk is then
+    // one contiguous bulk copy), else tiles of 64 or 32
+    const int ocb_opts[3] = {p.COp <= 64 ? p.COp : 0, 64, 32};
+    for (int oi = 0; oi < 3; ++oi) {
+      const int OCB = ocb_opts[oi];
+      if (OCB <= 0 || OCB > p.COp || OCB % OCT) continue;
+      if (oi > 0 && OCB == ocb_opts[0]) continue;
+      const int nocg = OCB / OCT;
+      for (int tt = 32; tt <= 256; tt <<= 1) {
+        int pgs = tt / nocg;
+        if (pgs < 1) continue;
+        TileChoice c;
+        c.OCT = OCT;
+        c.OCB = OCB;
+        c.TWG = wg <= 8 ? wg : 4;
+        if (c.TWG > pgs) c.TWG = pgs;
+        c.TH = pgs / c.TWG;
+        if (c.TH > p.HO) c.TH = p.HO;
+        if (c.TH < 1) c.TH = 1;
+        c.NSB = pgs / (c.TWG * c.TH);
+        if (c.NSB > p.B) c.NSB = p.B;
+        if (c.NSB < 1) c.NSB = 1;
+        int threads = nocg * c.TWG * c.TH * c.NSB;
+        if (threads > 256) continue;
+        for (int icb = 8; icb >= 2; icb >>= 1) {
+          c.ICB = p.CI < icb ? p.CI : icb;
+          CoreCfg q = p;
+          apply_choice(q, c, KH, KW);
+          size_t smem = core_smem_bytes(q);
+          if (smem > ctx->smem_optin) continue;
+          bool dup = false;
+          for (auto &o : out)
+            if (o.second.OCT == c.OCT && o.second.OCB == c.OCB && o.second.TH == c.TH &&
+                o.second.TWG == c.TWG && o.second.NSB == c.NSB && o.second.ICB == c.ICB)
+              dup = true;
+          if (dup) continue;
+          int warps = ceil_div(threads, 32);
+          int resident = (int)(smem_sm / (smem + 1024));
+          int by_regs = 65536 / (128 * warps * 32);
+          if (by_regs < resident) resident = by_regs;
+          if (resident > 32) resident = 32;
+          if (resident < 1) continue;
+          long long blocks = (long long)q.tiles_x * q.tiles_y * q.tiles_oc * q.tiles_n;
+          long long per_sm = (blocks + sms - 1) / sms;
+          double waves = 1.0;
+          long long conc = per_sm;  // blocks an SM runs at the same time
+          if (per_sm > resident) {
+            waves = (double)((per_sm + resident - 1) / resident);
+            conc = resident;
+          }
+          // warp instructions of one block per chunk
+          double fma = 8.0 * OCT * q.ICB * KH * KW;
+          double stage_in = 10.0 * q.in_tile_floats / threads;
+          double stage_w = q.w_bulk ? 2.0 : 8.0 * q.w_tile_floats / 4.0 / threads;
+          double per_chunk = fma * (OCT == 8 ? 1.08 : 1.18) + stage_in + stage_w + 150.0;
+          double block_cost = warps * per_chunk * ceil_div(p.CI, q.ICB);
+          double occ = 0.45 + 0.55 * (conc * warps >= 8 ? 1.0 : (conc * warps) / 8.0);
+          double t = waves * conc * block_cost / occ;
+          out.push_back({t, c});
+        }
+      }
+    }
+  }
+  std::sort(out.begin(), out.end(),
+            [](const std::pair<double, TileChoice> &a, const std::pair<double, TileChoice> &b) {
+              return a.first < b.first;
+            });
+  return out;
 }
 
 template <int KH, int KW, int OCT>
@@ -335,33 +438,103 @@ static int launch_core_t(b200_ctx *ctx, const CoreCfg &p, long long blocks, int 
   return 0;
 }
 
-static int launch_core(b200_ctx *ctx, CoreCfg &p, int KH, int KW) {
-  int OCT = core_tiling(ctx, p, KH, KW);
-  size_t smem = (size_t)2 * (p.in_tile_floats + p.w_tile_floats) * 4 + (size_t)p.nrows * 12 + 16;
+static int launch_choice(b200_ctx *ctx, CoreCfg p, const TileChoice &c, int KH, int KW) {
+  apply_choice(p, c, KH, KW);
+  p.err = ctx->dev_err;
+  size_t smem = core_smem_bytes(p);
   B200_REQUIRE(smem <= ctx->smem_optin, "conv tile needs %zu bytes of shared memory (limit %zu)",
                smem, ctx->smem_optin);
-  int threads = (p.OCB / OCT) * p.TWG * p.TH * p.NSB;
+  int threads = (p.OCB / c.OCT) * p.TWG * p.TH * p.NSB;
   B200_REQUIRE(threads >= 1 && threads <= 256, "conv tile thread count %d out of range", threads);
   long long blocks = (long long)p.tiles_x * p.tiles_y * p.tiles_oc * p.tiles_n;
   B200_REQUIRE(blocks > 0 && blocks < 0x7fffffffLL, "conv grid too large");
-  if (KH == 3 && OCT == 8) return launch_core_t<3, 3, 8>(ctx, p, blocks, threads, smem);
-  if (KH == 3 && OCT == 4) return launch_core_t<3, 3, 4>(ctx, p, blocks, threads, smem);
-  if (KH == 5 && OCT == 8) return launch_core_t<5, 5, 8>(ctx, p, blocks, threads, smem);
+  if (KH == 3 && c.OCT == 8) return launch_core_t<3, 3, 8>(ctx, p, blocks, threads, smem);
+  if (KH == 3 && c.OCT == 4) return launch_core_t<3, 3, 4>(ctx, p, blocks, threads, smem);
+  if (KH == 5 && c.OCT == 8) return launch_core_t<5, 5, 8>(ctx, p, blocks, threads, smem);
   return launch_core_t<5, 5, 4>(ctx, p, blocks, threads, smem);
 }
 
+// Tile shape for this problem: remembered per context; on first sight the best
+// candidates of the model are each timed with CUDA events on the real buffers
+// (every shape computes identical results -- the accumulation order per output
+// does not depend on the tiling) and the fastest is kept.  Inside a stream
+// capture, or with B200_AUTOTUNE=0, the model's first choice is used.
+static int launch_core(b200_ctx *ctx, CoreCfg &p, int KH, int KW) {
+  p.COp = padded_channels(p.CO);
+  char key[160];
+  snprintf(key, sizeof(key), "core %d %d %d %d %d %d %d %d %d %d", KH, p.B, p.CI, p.HI, p.WI, p.CO,
+           p.HO, p.WO, p.pad_t, p.pad_l);
+  auto it = ctx->tile_cache.find(key);
+  if (it != ctx->tile_cache.end()) return launch_choice(ctx, p, it->second, KH, KW);
+
+  auto cands = core_candidates(ctx, p, KH, KW);
+  B200_REQUIRE(!cands.empty(), "conv: no tile shape fits shared memory");
+  TileChoice pick = cands[0].second;
+  if (const char *e = getenv("B200_CONV_TILE")) {
+    // tuning override "OCT,OCB,TH,TWG,NSB,ICB" (must be one of the legal shapes)
+    int v[6];
+    if (sscanf(e, "%d,%d,%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3], &v[4], &v[5]) == 6)
+      for (auto &c : cands)
+        if (c.second.OCT == v[0] && c.second.OCB == v[1] && c.second.TH == v[2] &&
+            c.second.TWG == v[3] && c.second.NSB == v[4] && c.second.ICB == v[5])
+          pick = c.second;
+    return launch_choice(ctx, p, pick, KH, KW);
+  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  B200_CUDA(cudaStreamIsCapturing(ctx->stream, &cap));
+  const char *at = getenv("B200_AUTOTUNE");
+  bool tune = !(at && at[0] == '0') && cap == cudaStreamCaptureStatusNone && cands.size() > 1;
+  if (tune) {
+    cudaEvent_t e0, e1;
+    B200_CUDA(cudaEventCreate(&e0));
+    B200_CUDA(cudaEventCreate(&e1));
+    float best_ms = 1e30f;
+    size_t ntry = cands.size() < 24 ? cands.size() : 24;
+    for (size_t i = 0; i < ntry; ++i) {
+      const TileChoice &c = cands[i].second;
+      int r = launch_choice(ctx, p, c, KH, KW);  // warm-up (sets the kernel attribute)
+      if (r == 0) {
+        B200_CUDA(cudaEventRecord(e0, ctx->stream));
+        for (int rep = 0; rep < 3 && r == 0; ++rep) r = launch_choice(ctx, p, c, KH, KW);
+        B200_CUDA(cudaEventRecord(e1, ctx->stream));
+        B200_CUDA(cudaEventSynchronize(e1));
+      }
+      if (r != 0) {
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        return r;
+      }
+      float ms = 0.f;
+      B200_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+      if (ms < best_ms) {
+        best_ms = ms;
+        pick = c;
+      }
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (getenv("B200_TUNE_LOG"))
+      fprintf(stderr, "[b200] %s -> OCT %d OCB %d TH %d TWG %d NSB %d ICB %d (%.1f us; model pick OCT %d OCB %d TH %d TWG %d NSB %d ICB %d)\n",
+              key, pick.OCT, pick.OCB, pick.TH, pick.TWG, pick.NSB, pick.ICB, best_ms * 1000.f / 3.f,
+              cands[0].second.OCT, cands[0].second.OCB, cands[0].second.TH, cands[0].second.TWG,
+              cands[0].second.NSB, cands[0].second.ICB);
+  }
+  if (cap == cudaStreamCaptureStatusNone) ctx->tile_cache[key] = pick;
+  return launch_choice(ctx, p, pick, KH, KW);
+}
+
 size_t conv_tiled_fwd_scratch(const ConvGeom &g) {
-  return (size_t)g.C * g.KH * g.KW * round_up(g.OC, 8);
+  return (size_t)g.C * g.KH * g.KW * padded_channels(g.OC);
 }
 size_t conv_tiled_dx_scratch(const ConvGeom &g) {
-  return (size_t)g.OC * g.KH * g.KW * round_up(g.C, 8);
+  return (size_t)g.OC * g.KH * g.KW * padded_channels(g.C);
 }
 
 int conv_tiled_fwd(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *W,
                    const float *bias, float *out, int B, int act, float *scratch) {
   if (B == 0) return 0;
   int KK = g.KH * g.KW;
-  int COp = round_up(g.OC, 8);
+  int COp = padded_channels(g.OC);
   int total = g.C * KK * COp;
   conv_prep_wt_fwd_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(W, scratch, g.C, g.OC,
                                                                         COp, KK, g.tbl);
@@ -388,7 +561,7 @@ int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float 
                   float *din, int B, float *scratch) {
   if (B == 0) return 0;
   int KK = g.KH * g.KW;
-  int Cp = round_up(g.C, 8);
+  int Cp = padded_channels(g.C);
   int total = g.OC * KK * Cp;
   conv_prep_wt_dx_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(W, scratch, g.C, g.OC, Cp,
                                                                        g.KH, g.KW, g.tbl);
@@ -614,7 +787,17 @@ __global__ void __launch_bounds__(256) conv_dw_kernel(const DwCfg p) {
   }
 }
 
-static void dw_tiling(const b200_ctx *ctx, DwCfg &p, int KH, int KW, int OCT) {
+static size_t dw_smem_bytes(const DwCfg &p, int KH, int KW, int OCT) {
+  const int NACC = OCT * KH * KW + OCT;
+  size_t stage = (size_t)(p.x_tile_floats + p.dy_tile_floats) * 4;
+  size_t red = (size_t)p.SL * (p.OCB / OCT) * p.ICT * NACC * 4;
+  return 2 * stage > red ? 2 * stage : red;
+}
+
+// Fill the tiling for a band height `th` and `splits` batch slices (0 = defaults:
+// the tallest band that fits shared memory, one slice per SM).
+static void dw_tiling(const b200_ctx *ctx, DwCfg &p, int KH, int KW, int OCT, int th = 0,
+                      int splits = 0) {
   int oc_r = round_up(p.OC, OCT);
   p.OCB = oc_r < 32 ? oc_r : 32;
   int nocg = p.OCB / OCT;
@@ -627,14 +810,12 @@ static void dw_tiling(const b200_ctx *ctx, DwCfg &p, int KH, int KW, int OCT) {
   p.TWp = p.TWG * 8;
   p.PITCHX = round_up(p.TWp + KW - 1, 4);
   p.OCBp = p.OCB + 4;
-  const int NACC = OCT * KH * KW + OCT;
-  size_t limit = ctx->smem_optin;
   // the register tile (100+ accumulators) already limits an SM to one block,
-  // so a block may take nearly all shared memory for tall bands (less halo)
-  size_t want = limit - 4096;
-  auto need = [&](int th) {
-    p.TH = th;
-    p.THp = th + KH - 1;
+  // so a block may take nearly all shared memory
+  size_t limit = ctx->smem_optin;
+  auto need = [&](int h) {
+    p.TH = h;
+    p.THp = h + KH - 1;
     int plane = p.THp * p.PITCHX;
     // plane stride with (PSX/4) odd keeps 8 consecutive channels on distinct banks
     int ps = round_up(plane, 4);
@@ -642,25 +823,17 @@ static void dw_tiling(const b200_ctx *ctx, DwCfg &p, int KH, int KW, int OCT) {
     p.PSX = ps;
     p.x_tile_floats = p.ICT * p.PSX;
     p.dy_tile_floats = round_up(p.TH * p.TWp * p.OCBp, 4);
-    size_t stage = (size_t)(p.x_tile_floats + p.dy_tile_floats) * 4;
-    size_t red = (size_t)p.SL * nocg * p.ICT * NACC * 4;
-    size_t tot = 2 * stage;
-    return tot > red ? tot : red;
+    return dw_smem_bytes(p, KH, KW, OCT);
   };
-  int th = p.OH;
-  while (th > 1 && need(th) > want) th = (th + 1) / 2;
-  if (need(th) > limit) {
-    while (th > 1 && need(th) > limit) --th;
-  }
+  if (th <= 0 || th > p.OH) th = p.OH;
+  while (th > 1 && need(th) > limit) --th;
   need(th);
   p.bands = ceil_div(p.OH, p.TH);
   p.tiles_oc = ceil_div(p.OC, p.OCB);
   p.tiles_ic = ceil_div(p.C, p.ICT);
   int units = p.B * p.bands;
   int tiles = p.tiles_oc * p.tiles_ic;
-  int blocks_target = 2 * ctx->sm_count;
-  int splits = blocks_target / tiles;
-  if (splits < 1) splits = 1;
+  if (splits <= 0) splits = ctx->sm_count / tiles;
   if (splits > units) splits = units;
   if (splits < 1) splits = 1;
   p.splits = splits;
@@ -684,35 +857,22 @@ static void dw_fill(DwCfg &p, const ConvGeom &g, int B) {
   p.row_len = conv_weight_len(g) + g.OC;
 }
 
+// Upper bound of the partial rows any choice of (band height, slices) writes.
 size_t conv_tiled_dw_scratch(const b200_ctx *ctx, const ConvGeom &g, int B) {
-  DwCfg p{};
-  dw_fill(p, g, B > 0 ? B : 1);
-  dw_tiling(ctx, p, g.KH, g.KW, g.KH == 3 ? 8 : 4);
-  return (size_t)p.splits * p.row_len;
+  (void)B;
+  size_t row = conv_weight_len(g) + g.OC;
+  return (size_t)2 * ctx->sm_count * row;
 }
 
-int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout,
-                           int B, float *scratch, int *splits) {
-  B200_REQUIRE(B > 0, "conv_tiled_dw_partials: empty batch");
-  B200_REQUIRE(g.OW <= 64, "conv_tiled_dw_partials: output width %d > 64", g.OW);
-  DwCfg p{};
-  dw_fill(p, g, B);
-  const int OCT = g.KH == 3 ? 8 : 4;
-  dw_tiling(ctx, p, g.KH, g.KW, OCT);
-  p.in = in;
-  p.dout = dout;
-  p.partial = scratch;
-  const int NACC = OCT * g.KH * g.KW + OCT;
-  size_t stage = (size_t)(p.x_tile_floats + p.dy_tile_floats) * 4;
-  size_t red = (size_t)p.SL * (p.OCB / OCT) * p.ICT * NACC * 4;
-  size_t smem = 2 * stage > red ? 2 * stage : red;
+static int dw_launch(b200_ctx *ctx, const DwCfg &p, int KH, int KW, int OCT) {
+  size_t smem = dw_smem_bytes(p, KH, KW, OCT);
   B200_REQUIRE(smem <= ctx->smem_optin, "conv dW tile needs %zu bytes of shared memory (limit %zu)",
                smem, ctx->smem_optin);
   int threads = (p.OCB / OCT) * p.ICT * p.SL;
   B200_REQUIRE(threads >= 1 && threads <= 256, "conv dW thread count %d out of range", threads);
   int blocks = p.tiles_oc * p.tiles_ic * p.splits;
-  // rows of blocks that own no unit still write zeros, so every row is defined
-  if (g.KH == 3) {
+  // blocks that own no unit still write zeros, so every partial row is defined
+  if (KH == 3) {
     B200_CUDA(cudaFuncSetAttribute(conv_dw_kernel<3, 3, 8>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     conv_dw_kernel<3, 3, 8><<<blocks, threads, smem, ctx->stream>>>(p);
@@ -722,6 +882,96 @@ int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in, co
     conv_dw_kernel<5, 5, 4><<<blocks, threads, smem, ctx->stream>>>(p);
   }
   B200_LAUNCHED();
+  return 0;
+}
+
+// Band height and slice count are remembered per context; on first sight a few
+// choices are timed with CUDA events (shorter bands give more, finer units to
+// balance over the SMs at the price of more halo rows; more slices mean more
+// partial rows to merge) and the fastest is kept.  The choice only regroups the
+// partial sums; within a process a given problem always uses the same grouping.
+int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout,
+                           int B, float *scratch, int *splits) {
+  B200_REQUIRE(B > 0, "conv_tiled_dw_partials: empty batch");
+  B200_REQUIRE(g.OW <= 64, "conv_tiled_dw_partials: output width %d > 64", g.OW);
+  const int OCT = g.KH == 3 ? 8 : 4;
+  DwCfg base{};
+  dw_fill(base, g, B);
+  base.in = in;
+  base.dout = dout;
+  base.partial = scratch;
+  char key[160];
+  snprintf(key, sizeof(key), "dw %d %d %d %d %d %d %d %d %d %d", g.KH, B, g.C, g.HI, g.WI, g.OC,
+           g.OH, g.OW, g.pad_t, g.pad_l);
+  int th = 0, sp = 0;
+  auto it = ctx->tile_cache.find(key);
+  if (it != ctx->tile_cache.end()) {
+    th = it->second.TH;
+    sp = it->second.NSB;
+  } else {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    B200_CUDA(cudaStreamIsCapturing(ctx->stream, &cap));
+    const char *at = getenv("B200_AUTOTUNE");
+    bool tune = !(at && at[0] == '0') && cap == cudaStreamCaptureStatusNone;
+    if (tune) {
+      DwCfg t0 = base;
+      dw_tiling(ctx, t0, g.KH, g.KW, OCT);
+      const int th_max = t0.TH;
+      const int tiles = t0.tiles_oc * t0.tiles_ic;
+      std::vector<std::pair<int, int>> cands;
+      for (int h = th_max; h >= 1; h = h > 1 ? (h + 1) / 2 : 0)
+        for (int mult = 1; mult <= 2; ++mult) {
+          int s = mult * ctx->sm_count / tiles;
+          if (s < 1) s = 1;
+          bool dup = false;
+          for (auto &c : cands) dup = dup || (c.first == h && c.second == s);
+          if (!dup) cands.push_back({h, s});
+        }
+      cudaEvent_t e0, e1;
+      B200_CUDA(cudaEventCreate(&e0));
+      B200_CUDA(cudaEventCreate(&e1));
+      float best_ms = 1e30f;
+      for (auto &c : cands) {
+        DwCfg t = base;
+        dw_tiling(ctx, t, g.KH, g.KW, OCT, c.first, c.second);
+        int r = dw_launch(ctx, t, g.KH, g.KW, OCT);
+        if (r == 0) {
+          B200_CUDA(cudaEventRecord(e0, ctx->stream));
+          for (int rep = 0; rep < 3 && r == 0; ++rep) r = dw_launch(ctx, t, g.KH, g.KW, OCT);
+          B200_CUDA(cudaEventRecord(e1, ctx->stream));
+          B200_CUDA(cudaEventSynchronize(e1));
+        }
+        if (r != 0) {
+          cudaEventDestroy(e0);
+          cudaEventDestroy(e1);
+          return r;
+        }
+        float ms = 0.f;
+        B200_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        // the rows still have to be merged: charge them at a nominal 3 TB/s
+        ms += 3.f * (float)((double)t.splits * t.row_len * 4.0 / 3e12 * 1e3);
+        if (ms < best_ms) {
+          best_ms = ms;
+          th = t.TH;
+          sp = t.splits;
+        }
+      }
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+      if (getenv("B200_TUNE_LOG"))
+        fprintf(stderr, "[b200] %s -> band %d rows, %d slices (%.1f us incl. merge estimate)\n", key,
+                th, sp, best_ms * 1000.f / 3.f);
+    }
+    if (cap == cudaStreamCaptureStatusNone) {
+      TileChoice c{};
+      c.TH = th;
+      c.NSB = sp;
+      ctx->tile_cache[key] = c;
+    }
+  }
+  DwCfg p = base;
+  dw_tiling(ctx, p, g.KH, g.KW, OCT, th, sp);
+  B200_TRY(dw_launch(ctx, p, g.KH, g.KW, OCT));
   *splits = p.splits;
   return 0;
 }
@@ -733,12 +983,26 @@ int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in, co
 __global__ void merge_rows_kernel(const float *__restrict__ src, int rows, size_t stride,
                                   float *__restrict__ dst, size_t len, int accumulate,
                                   const uint8_t *__restrict__ tbl, int C, int OC, int KK,
-                                  size_t lenW) {
+                                  size_t lenW, int in_order = 0) {
   size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   size_t step = (size_t)gridDim.x * blockDim.x;
   for (; i < len; i += step) {
-    float s = src[i];
-    for (int r = 1; r < rows; ++r) s += src[(size_t)r * stride + i];
+    // four interleaved running sums (rows r, r+4, ...) combined at the end: a
+    // fixed order, with four independent load/add chains in flight
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int r = 0;
+    if (in_order) {  // rows added one after the other, as edge::merge_grads does
+      s0 = src[i];
+      for (r = 1; r < rows; ++r) s0 += src[(size_t)r * stride + i];
+    }
+    for (; r + 4 <= rows; r += 4) {
+      s0 += src[(size_t)(r + 0) * stride + i];
+      s1 += src[(size_t)(r + 1) * stride + i];
+      s2 += src[(size_t)(r + 2) * stride + i];
+      s3 += src[(size_t)(r + 3) * stride + i];
+    }
+    for (; r < rows; ++r) s0 += src[(size_t)r * stride + i];
+    float s = (s0 + s1) + (s2 + s3);
     if (tbl && i < lenW) {
       // unconnected (o, inc) pairs get no gradient (conv2d_op_internal.h:132)
       size_t pair = i / KK;
@@ -751,7 +1015,7 @@ __global__ void merge_rows_kernel(const float *__restrict__ src, int rows, size_
 }
 
 int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *dst, size_t len,
-               int accumulate, const ConvGeom *mask) {
+               int accumulate, const ConvGeom *mask, int in_order) {
   if (len == 0) return 0;
   B200_REQUIRE(rows >= 1, "merge_rows: rows must be >= 1");
   size_t blocks = ceil_div_sz(len, 256);
@@ -760,7 +1024,7 @@ int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *
   const uint8_t *tbl = mask ? mask->tbl : nullptr;
   merge_rows_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(
     src, rows, stride, dst, len, accumulate, tbl, mask ? mask->C : 1, mask ? mask->OC : 1,
-    mask ? mask->KH * mask->KW : 1, mask ? conv_weight_len(*mask) : 0);
+    mask ? mask->KH * mask->KW : 1, mask ? conv_weight_len(*mask) : 0, in_order);
   B200_LAUNCHED();
   return 0;
 }
@@ -871,10 +1135,7 @@ extern "C" int b200_conv2d_dw_noalloc(void *stream, const b200_conv_desc *d, con
   p.in = in;
   p.dout = dout;
   p.partial = nd->scratch;
-  const int NACC = OCT * g.KH * g.KW + OCT;
-  size_t stage = (size_t)(p.x_tile_floats + p.dy_tile_floats) * 4;
-  size_t red = (size_t)p.SL * (p.OCB / OCT) * p.ICT * NACC * 4;
-  size_t smem = 2 * stage > red ? 2 * stage : red;
+  size_t smem = dw_smem_bytes(p, g.KH, g.KW, OCT);
   B200_REQUIRE(smem <= nd->smem_optin,
                "conv2d_dw_noalloc: tile needs %zu bytes of shared memory (limit %zu)", smem,
                nd->smem_optin);

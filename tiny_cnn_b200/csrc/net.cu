@@ -31,6 +31,7 @@ struct Layer {
   int32_t *argmax = nullptr;
   bool tiled = false;
   float *wt_fwd = nullptr, *wt_dx = nullptr, *dw_part = nullptr;
+  float *fc_scratch = nullptr;  // k-slice partial sums of the small GEMMs
   int fused_act = 0;      // activation of the NEXT layer folded into this epilogue
   bool skipped = false;   // activation layer folded into the previous layer
 };
@@ -102,7 +103,7 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
           B200_TRY(conv_general_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act));
         break;
       case B200_LAYER_FC:
-        B200_TRY(fc_fwd(ctx, L.fc_in, L.fc_out, in, W, b, dst, B, L.fused_act));
+        B200_TRY(fc_fwd(ctx, L.fc_in, L.fc_out, in, W, b, dst, B, L.fused_act, L.fc_scratch));
         break;
       case B200_LAYER_MAXPOOL:
         B200_TRY(maxpool_fwd(ctx, L.pd, in, dst, L.argmax, B));
@@ -154,7 +155,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
         break;
       }
       case B200_LAYER_FC:
-        B200_TRY(fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, din, dW, db, 0, B));
+        B200_TRY(fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, din, dW, db, 0, B, L.fc_scratch));
         break;
       case B200_LAYER_MAXPOOL:
         if (din) B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, din, B));
@@ -342,20 +343,13 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
     B200_TRY(net_alloc((void **)&L.grad, L.out_dim * max_batch * f));
     if (L.kind == B200_LAYER_MAXPOOL)
       B200_TRY(net_alloc((void **)&L.argmax, L.out_dim * max_batch * sizeof(int32_t)));
+    if (L.kind == B200_LAYER_FC)
+      B200_TRY(net_alloc((void **)&L.fc_scratch,
+                         fc_scratch_floats(ctx, L.fc_in, L.fc_out, max_batch) * f));
     if (L.kind == B200_LAYER_CONV && L.tiled) {
       B200_TRY(net_alloc((void **)&L.wt_fwd, conv_tiled_fwd_scratch(L.g) * f));
       B200_TRY(net_alloc((void **)&L.wt_dx, conv_tiled_dx_scratch(L.g) * f));
-      // the split count depends on the batch; size for the largest over 1..max_batch
-      size_t need = 0;
-      for (int b = 1; b <= max_batch; b = b < 8 ? b + 1 : b * 2) {
-        size_t s = conv_tiled_dw_scratch(ctx, L.g, b);
-        if (s > need) need = s;
-      }
-      size_t s = conv_tiled_dw_scratch(ctx, L.g, max_batch);
-      if (s > need) need = s;
-      // splits never exceed 2 * SM count rows
-      size_t cap = (size_t)2 * ctx->sm_count * (L.w_len + L.g.OC);
-      if (cap > need) need = cap;
+      size_t need = conv_tiled_dw_scratch(ctx, L.g, max_batch);
       B200_TRY(net_alloc((void **)&L.dw_part, need * f));
     }
   }
@@ -376,6 +370,7 @@ int b200_net_destroy(b200_net *net) {
     cudaFree(L.wt_fwd);
     cudaFree(L.wt_dx);
     cudaFree(L.dw_part);
+    cudaFree(L.fc_scratch);
   }
   cudaFree(net->params);
   cudaFree(net->grads);

@@ -147,6 +147,8 @@ int b200_ctx_create(int device, void *stream, b200_ctx **out) {
     B200_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     c->own_stream = true;
   }
+  B200_CUDA(cudaMalloc(&c->dev_err, sizeof(int)));
+  B200_CUDA(cudaMemset(c->dev_err, 0, sizeof(int)));
   *out = c;
   return 0;
 }
@@ -158,6 +160,7 @@ int b200_ctx_destroy(b200_ctx *ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->arena) cudaFree(ctx->arena);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
+  if (ctx->dev_err) cudaFree(ctx->dev_err);
   for (auto &kv : ctx->tbl_cache) cudaFree(kv.second);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
@@ -180,6 +183,14 @@ void *b200_ctx_stream(b200_ctx *ctx) { return ctx ? (void *)ctx->stream : nullpt
 int b200_ctx_sync(b200_ctx *ctx) {
   B200_REQUIRE(ctx != nullptr, "ctx is NULL");
   B200_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (ctx->dev_err) {
+    int flag = 0;
+    B200_CUDA(cudaMemcpy(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag != 0) {
+      cudaMemset(ctx->dev_err, 0, sizeof(int));
+      B200_REQUIRE(false, "a kernel gave up a bounded wait on an asynchronous copy (code %d)", flag);
+    }
+  }
   return 0;
 }
 
