@@ -103,6 +103,10 @@ int ctx_scratch(b200_ctx *ctx, size_t bytes, void **out);
 int ctx_arena(b200_ctx *ctx, size_t bytes, void **out);
 int ctx_pinned(b200_ctx *ctx, size_t bytes, void **out);
 int ctx_device_table(b200_ctx *ctx, const uint8_t *host_tbl, size_t n, const uint8_t **out);
+// Remember a measured tile choice (and append it to the file named by the
+// environment variable B200_TUNE_CACHE, which ctx creation reads back, so a
+// later process starts with the choices already made).
+void ctx_remember_tile(b200_ctx *ctx, const std::string &key, const TileChoice &c);
 
 // ----------------------------------------------------------------------------
 // convolution geometry shared by the general and the tiled kernels
@@ -169,8 +173,12 @@ int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const floa
 
 int maxpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, float *out,
                 int32_t *argmax, int B);
+// `relu_y` (optional): output of a relu layer feeding this pooling layer; its
+// gradient mask is applied to din on the way (2x2/2 aligned layers only, see
+// maxpool_can_fuse_relu).
 int maxpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *dout, const int32_t *argmax,
-                float *din, int B);
+                float *din, int B, const float *relu_y = nullptr);
+bool maxpool_can_fuse_relu(const b200_pool_desc &d);
 int avgpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const float *W,
                 const float *bias, float *out, int B);
 int avgpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const float *W,

@@ -519,7 +519,7 @@ static int launch_core(b200_ctx *ctx, CoreCfg &p, int KH, int KW) {
               cands[0].second.OCT, cands[0].second.OCB, cands[0].second.TH, cands[0].second.TWG,
               cands[0].second.NSB, cands[0].second.ICB);
   }
-  if (cap == cudaStreamCaptureStatusNone) ctx->tile_cache[key] = pick;
+  if (cap == cudaStreamCaptureStatusNone) ctx_remember_tile(ctx, key, pick);
   return launch_choice(ctx, p, pick, KH, KW);
 }
 
@@ -966,7 +966,7 @@ int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in, co
       TileChoice c{};
       c.TH = th;
       c.NSB = sp;
-      ctx->tile_cache[key] = c;
+      ctx_remember_tile(ctx, key, c);
     }
   }
   DwCfg p = base;

@@ -34,6 +34,8 @@ struct Layer {
   float *fc_scratch = nullptr;  // k-slice partial sums of the small GEMMs
   int fused_act = 0;      // activation of the NEXT layer folded into this epilogue
   bool skipped = false;   // activation layer folded into the previous layer
+  bool relu_bwd_fused = false;   // max-pool: also applies the gradient of the relu before it
+  bool bwd_done_by_next = false; // relu: its gradient is produced by the pooling layer after it
 };
 
 }  // namespace
@@ -146,8 +148,14 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
           int splits = 0;
           B200_TRY(conv_tiled_dw_partials(ctx, L.g, in, L.grad, B, L.dw_part, &splits));
           size_t row = L.w_len + L.g.OC;
-          B200_TRY(merge_rows(ctx, L.dw_part, splits, row, dW, L.w_len, 0, &L.g));
-          if (db) B200_TRY(merge_rows(ctx, L.dw_part + L.w_len, splits, row, db, L.b_len, 0, nullptr));
+          if (db && L.b_off == L.w_off + L.w_len) {
+            // [W | b] are neighbours in the bucket as in a partial row: one merge
+            B200_TRY(merge_rows(ctx, L.dw_part, splits, row, dW, row, 0, &L.g));
+          } else {
+            B200_TRY(merge_rows(ctx, L.dw_part, splits, row, dW, L.w_len, 0, &L.g));
+            if (db)
+              B200_TRY(merge_rows(ctx, L.dw_part + L.w_len, splits, row, db, L.b_len, 0, nullptr));
+          }
         } else {
           if (din) B200_TRY(conv_general_dx(ctx, L.g, W, L.grad, din, B));
           B200_TRY(conv_general_dw(ctx, L.g, in, L.grad, dW, db, 0, B));
@@ -158,7 +166,14 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
         B200_TRY(fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, din, dW, db, 0, B, L.fc_scratch));
         break;
       case B200_LAYER_MAXPOOL:
-        if (din) B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, din, B));
+        if (L.relu_bwd_fused) {
+          // the relu before this layer was folded into the producer's epilogue: apply
+          // its gradient mask here and write straight into the producer's gradient
+          B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, net->layers[i - 2].grad, B,
+                               net->layers[i - 1].out));
+        } else if (din) {
+          B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, din, B));
+        }
         break;
       case B200_LAYER_AVGPOOL:
         B200_TRY(avgpool_bwd(ctx, L.pd, in, W, L.grad, din, dW, db, 0, B));
@@ -166,6 +181,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
       case B200_LAYER_RELU:
       case B200_LAYER_TANH:
       case B200_LAYER_SOFTMAX:
+        if (L.bwd_done_by_next) break;  // the pooling layer after it already wrote din
         if (din)
           B200_TRY(act_bwd(ctx, act_of_layer(L.kind), L.out, L.grad, din, (int)L.out_dim, B));
         break;
@@ -320,6 +336,18 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
       if ((L.kind == B200_LAYER_CONV || L.kind == B200_LAYER_FC) && is_foldable_act(N.kind)) {
         L.fused_act = act_of_layer(N.kind);
         N.skipped = true;
+      }
+    }
+  }
+  // relu -> 2x2 max-pool: the pooling gradient kernel applies the relu mask itself
+  if (net->fuse) {
+    for (int i = 2; i < n_layers; ++i) {
+      Layer &P = net->layers[i];
+      Layer &R = net->layers[i - 1];
+      if (P.kind == B200_LAYER_MAXPOOL && R.kind == B200_LAYER_RELU && R.skipped &&
+          maxpool_can_fuse_relu(P.pd)) {
+        P.relu_bwd_fused = true;
+        R.bwd_done_by_next = true;
       }
     }
   }

@@ -72,6 +72,93 @@ __global__ void maxpool_bwd_kernel(b200_pool_desc d, const float *__restrict__ d
   }
 }
 
+// 2x2 windows with stride 2 on an even-width plane (every pooling layer of the
+// benchmark networks): one thread owns two neighbouring outputs, reads the two
+// input rows as float4 and writes float2 / int2.  Same scan order and strict
+// '>' as the general kernel.
+__global__ void maxpool2x2_fwd_kernel(int in_w, int in_h, int out_w, int out_h, long long planes,
+                                      const float *__restrict__ in, float *__restrict__ out,
+                                      int32_t *__restrict__ argmax, int in_c) {
+  const int ow2 = out_w >> 1;  // output pairs per row
+  long long total = planes * out_h * ow2;
+  long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long step = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += step) {
+    int xp = (int)(idx % ow2);
+    long long r = idx / ow2;
+    int oy = (int)(r % out_h);
+    long long plane = r / out_h;  // n * in_c + c
+    int c = (int)(plane % in_c);
+    const float *ip = in + (plane * in_h + 2 * oy) * in_w + 4 * xp;
+    float4 a = *reinterpret_cast<const float4 *>(ip);
+    float4 b = *reinterpret_cast<const float4 *>(ip + in_w);
+    // in-row index (c, y, x) of the window's first element
+    int base = (in_h * c + 2 * oy) * in_w + 4 * xp;
+    float best0 = -FLT_MAX, best1 = -FLT_MAX;
+    int i0 = 0, i1 = 0;
+    if (a.x > best0) { best0 = a.x; i0 = base; }
+    if (a.y > best0) { best0 = a.y; i0 = base + 1; }
+    if (b.x > best0) { best0 = b.x; i0 = base + in_w; }
+    if (b.y > best0) { best0 = b.y; i0 = base + in_w + 1; }
+    if (a.z > best1) { best1 = a.z; i1 = base + 2; }
+    if (a.w > best1) { best1 = a.w; i1 = base + 3; }
+    if (b.z > best1) { best1 = b.z; i1 = base + in_w + 2; }
+    if (b.w > best1) { best1 = b.w; i1 = base + in_w + 3; }
+    long long o = (plane * out_h + oy) * out_w + 2 * xp;
+    *reinterpret_cast<float2 *>(out + o) = make_float2(best0, best1);
+    *reinterpret_cast<int2 *>(argmax + o) = make_int2(i0, i1);
+  }
+}
+
+// Gradient of the same layer; with `relu_y` != nullptr the gradient of a relu
+// that precedes the pooling layer is applied on the way (relu_y is that relu's
+// output, i.e. this layer's input): din = (y > 0) ? pooled gradient : 0.
+__global__ void maxpool2x2_bwd_kernel(int in_w, int in_h, int out_w, int out_h, long long planes,
+                                      const float *__restrict__ dout,
+                                      const int32_t *__restrict__ argmax,
+                                      const float *__restrict__ relu_y, float *__restrict__ din,
+                                      int in_c) {
+  const int ow2 = out_w >> 1;
+  long long total = planes * out_h * ow2;
+  long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long step = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += step) {
+    int xp = (int)(idx % ow2);
+    long long r = idx / ow2;
+    int oy = (int)(r % out_h);
+    long long plane = r / out_h;
+    int c = (int)(plane % in_c);
+    long long o = (plane * out_h + oy) * out_w + 2 * xp;
+    float2 g = *reinterpret_cast<const float2 *>(dout + o);
+    int2 am = *reinterpret_cast<const int2 *>(argmax + o);
+    int base = (in_h * c + 2 * oy) * in_w + 4 * xp;
+    float4 a, b;
+    a.x = am.x == base ? g.x : 0.f;
+    a.y = am.x == base + 1 ? g.x : 0.f;
+    b.x = am.x == base + in_w ? g.x : 0.f;
+    b.y = am.x == base + in_w + 1 ? g.x : 0.f;
+    a.z = am.y == base + 2 ? g.y : 0.f;
+    a.w = am.y == base + 3 ? g.y : 0.f;
+    b.z = am.y == base + in_w + 2 ? g.y : 0.f;
+    b.w = am.y == base + in_w + 3 ? g.y : 0.f;
+    long long ioff = (plane * in_h + 2 * oy) * in_w + 4 * xp;
+    if (relu_y) {
+      float4 ya = *reinterpret_cast<const float4 *>(relu_y + ioff);
+      float4 yb = *reinterpret_cast<const float4 *>(relu_y + ioff + in_w);
+      a.x = ya.x > 0.f ? a.x : 0.f;
+      a.y = ya.y > 0.f ? a.y : 0.f;
+      a.z = ya.z > 0.f ? a.z : 0.f;
+      a.w = ya.w > 0.f ? a.w : 0.f;
+      b.x = yb.x > 0.f ? b.x : 0.f;
+      b.y = yb.y > 0.f ? b.y : 0.f;
+      b.z = yb.z > 0.f ? b.z : 0.f;
+      b.w = yb.w > 0.f ? b.w : 0.f;
+    }
+    *reinterpret_cast<float4 *>(din + ioff) = a;
+    *reinterpret_cast<float4 *>(din + ioff + in_w) = b;
+  }
+}
+
 // tiny_average_pooling_kernel (tiny_dnn/layers/average_pooling_layer.h:25-55):
 // windows start at multiples of the stride while they fit entirely
 // (init_connection :271-281); an output without a window is just the bias.
@@ -193,22 +280,50 @@ static int check_pool(const b200_pool_desc &d) {
   return 0;
 }
 
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// 2x2/2 pooling of planes whose width is a multiple of 4 and whose height is even
+static bool pool2x2_fast(const b200_pool_desc &d) {
+  return d.pool_w == 2 && d.pool_h == 2 && d.stride_w == 2 && d.stride_h == 2 && (d.in_w % 4) == 0 &&
+         (d.in_h % 2) == 0 && d.out_w * 2 == d.in_w && d.out_h * 2 == d.in_h;
+}
+
 int maxpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, float *out,
                 int32_t *argmax, int B) {
   B200_TRY(check_pool(d));
   long long total = (long long)B * d.in_c * d.out_h * d.out_w;
   if (total == 0) return 0;
+  if (pool2x2_fast(d) && aligned16(in) && aligned16(out) && aligned16(argmax)) {
+    long long planes = (long long)B * d.in_c;
+    maxpool2x2_fwd_kernel<<<grid_for(total / 2, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+      d.in_w, d.in_h, d.out_w, d.out_h, planes, in, out, argmax, d.in_c);
+    B200_LAUNCHED();
+    return 0;
+  }
   maxpool_fwd_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(d, in, out,
                                                                                    argmax, total);
   B200_LAUNCHED();
   return 0;
 }
 
+bool maxpool_can_fuse_relu(const b200_pool_desc &d) { return pool2x2_fast(d); }
+
 int maxpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *dout, const int32_t *argmax,
-                float *din, int B) {
+                float *din, int B, const float *relu_y) {
   B200_TRY(check_pool(d));
   long long total = (long long)B * d.in_c * d.in_h * d.in_w;
   if (total == 0) return 0;
+  bool fast = pool2x2_fast(d) && aligned16(dout) && aligned16(din) && aligned16(argmax) &&
+              (!relu_y || aligned16(relu_y));
+  B200_REQUIRE(fast || !relu_y, "maxpool_bwd: relu fusion needs the 2x2/2 aligned path");
+  if (fast) {
+    long long planes = (long long)B * d.in_c;
+    long long work = planes * d.out_h * (d.out_w / 2);
+    maxpool2x2_bwd_kernel<<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+      d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, relu_y, din, d.in_c);
+    B200_LAUNCHED();
+    return 0;
+  }
   maxpool_bwd_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(d, dout, argmax,
                                                                                    din, total);
   B200_LAUNCHED();

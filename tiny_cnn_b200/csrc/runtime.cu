@@ -73,6 +73,33 @@ int ctx_device_table(b200_ctx *ctx, const uint8_t *host_tbl, size_t n, const uin
   return 0;
 }
 
+void ctx_remember_tile(b200_ctx *ctx, const std::string &key, const TileChoice &c) {
+  ctx->tile_cache[key] = c;
+  if (const char *path = getenv("B200_TUNE_CACHE")) {
+    if (FILE *f = fopen(path, "a")) {
+      fprintf(f, "%s|%d %d %d %d %d %d\n", key.c_str(), c.OCT, c.OCB, c.TH, c.TWG, c.NSB, c.ICB);
+      fclose(f);
+    }
+  }
+}
+
+static void ctx_load_tiles(b200_ctx *ctx) {
+  const char *path = getenv("B200_TUNE_CACHE");
+  if (!path) return;
+  FILE *f = fopen(path, "r");
+  if (!f) return;
+  char line[512];
+  while (fgets(line, sizeof(line), f)) {
+    char *bar = strchr(line, '|');
+    if (!bar) continue;
+    *bar = 0;
+    TileChoice c{};
+    if (sscanf(bar + 1, "%d %d %d %d %d %d", &c.OCT, &c.OCB, &c.TH, &c.TWG, &c.NSB, &c.ICB) == 6)
+      ctx->tile_cache[line] = c;
+  }
+  fclose(f);
+}
+
 int conv_geom_from_desc(b200_ctx *ctx, const b200_conv_desc *d, ConvGeom *g) {
   B200_REQUIRE(d != nullptr, "conv descriptor is NULL");
   B200_REQUIRE(d->in_w > 0 && d->in_h > 0 && d->in_c > 0 && d->out_c > 0 && d->k_w > 0 &&
@@ -147,6 +174,7 @@ int b200_ctx_create(int device, void *stream, b200_ctx **out) {
     B200_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     c->own_stream = true;
   }
+  ctx_load_tiles(c);
   B200_CUDA(cudaMalloc(&c->dev_err, sizeof(int)));
   B200_CUDA(cudaMemset(c->dev_err, 0, sizeof(int)));
   *out = c;
