@@ -78,6 +78,35 @@ def build_reference(force: bool = False) -> Path | None:
     return REF_SO
 
 
+OVERLAY_DIR = REF_DIR / "overlay"
+BACKEND_TEST = REF_DIR / "bin" / "test_backend_b200"
+
+
+def build_backend_test(force: bool = False) -> Path | None:
+    """Generate the backend_t::b200 overlay from the reference tree and compile the
+    C++ A/B test (tests/cpp/test_backend_b200.cpp) against it; None if the reference
+    is absent.  The binary links tiny_cnn_b200/csrc/libtinycnn_b200.so by relative rpath."""
+    if not reference_available():
+        return BACKEND_TEST if BACKEND_TEST.exists() else None
+    import sys as _sys
+    _sys.path.insert(0, str(ROOT))
+    from tiny_cnn_b200.host.make_overlay import make_overlay
+    src = ROOT / "tests" / "cpp" / "test_backend_b200.cpp"
+    host = ROOT / "tiny_cnn_b200" / "host"
+    deps = [src, host / "b200_glue.h", host / "b200_backend.h", host / "make_overlay.py",
+            ROOT / "include" / "tinycnn_b200.h"]
+    if not (force or _stale(BACKEND_TEST, deps)):
+        return BACKEND_TEST
+    make_overlay(REF_ROOT, OVERLAY_DIR)
+    BACKEND_TEST.parent.mkdir(parents=True, exist_ok=True)
+    libdir = ROOT / "tiny_cnn_b200" / "csrc"
+    _run(["g++", "-std=c++14", "-O2", "-fopenmp", "-DCNN_USE_OMP", "-w", f"-I{OVERLAY_DIR}", f"-I{REF_ROOT}",
+          f"-I{ROOT / 'include'}", str(src), "-o", str(BACKEND_TEST), f"-L{libdir}", "-ltinycnn_b200",
+          "-Wl,-rpath,$ORIGIN/../../../tiny_cnn_b200/csrc", "-ldl", "-lpthread", "-lrt"])
+    return BACKEND_TEST
+
+
 if __name__ == "__main__":
     print(build_oracle(force="-f" in sys.argv))
     print(build_reference(force="-f" in sys.argv))
+    print(build_backend_test(force="-f" in sys.argv))

@@ -1,0 +1,239 @@
+// A/B test of the engine core::backend_t::b200 inside tiny-dnn itself.
+//
+// Compiled against the overlay produced by tiny_cnn_b200/host/make_overlay.py
+// placed before the tiny-dnn tree on the include path, and linked with
+// libtinycnn_b200.so.  The same layer objects and networks are run with
+// backend_t::internal (the reference's CPU kernels) and with backend_t::b200,
+// following the reference's own engine A/B tests
+// (test/test_convolutional_layer.h:257-497).  Tolerances: forward 1e-4,
+// gradients and weights 1e-3, relative to the largest magnitude; the
+// quantized layer is compared bit for bit.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <random>
+
+#include "tiny_dnn/tiny_dnn.h"
+
+using namespace tiny_dnn;
+
+static int g_fail = 0;
+
+static double max_abs(const vec_t &v) {
+  double m = 0;
+  for (auto x : v) m = std::max(m, (double)std::fabs(x));
+  return m;
+}
+
+static bool close_vec(const vec_t &a, const vec_t &b, double tol, const char *what) {
+  if (a.size() != b.size()) {
+    printf("FAIL %s: size %zu vs %zu\n", what, a.size(), b.size());
+    ++g_fail;
+    return false;
+  }
+  double scale = std::max(max_abs(b), 1e-30), worst = 0;
+  for (size_t i = 0; i < a.size(); ++i) {
+    double err = std::fabs((double)a[i] - (double)b[i]);
+    if (err > tol * (std::fabs((double)b[i]) + scale)) {
+      printf("FAIL %s: [%zu] got %.9g want %.9g (scale %g)\n", what, i, a[i], b[i], scale);
+      ++g_fail;
+      return false;
+    }
+    worst = std::max(worst, err / scale);
+  }
+  printf("ok   %s (max rel err %.2e)\n", what, worst);
+  return true;
+}
+
+static vec_t sum_rows(const tensor_t &t) {
+  vec_t s(t[0].size(), 0);
+  for (auto &r : t)
+    for (size_t i = 0; i < s.size(); ++i) s[i] += r[i];
+  return s;
+}
+
+static void fill_normal(tensor_t &t, std::mt19937 &g) {
+  std::normal_distribution<float> d(0.f, 1.f);
+  for (auto &r : t)
+    for (auto &x : r) x = d(g);
+}
+static void fill_uniform(vec_t &v, std::mt19937 &g, float lo, float hi) {
+  std::uniform_real_distribution<float> d(lo, hi);
+  for (auto &x : v) x = d(g);
+}
+
+// Run one layer forward + backward on B samples with the engine given.
+struct LayerRun {
+  tensor_t out, din, dW, db;
+};
+
+template <typename L>
+static LayerRun run_layer(L &l, core::backend_t engine, const tensor_t &x, const vec_t &W, const vec_t &b,
+                          const tensor_t &dy, bool has_weights) {
+  const size_t B = x.size();
+  l.set_backend_type(engine);
+  tensor_t tx = x, tW(1, W), tb(1, b), tout(B, vec_t(l.out_shape()[0].size()));
+  tensor_t gx(B, vec_t(x[0].size())), gW(B, vec_t(W.size())), gb(B, vec_t(b.size())), gout = dy;
+  std::vector<tensor_t *> ins = {&tx}, outs = {&tout}, gins = {&gx}, gouts = {&gout};
+  if (has_weights) {
+    ins.push_back(&tW);
+    ins.push_back(&tb);
+    gins.push_back(&gW);
+    gins.push_back(&gb);
+  }
+  l.setup(false);
+  l.set_sample_count(B);
+  l.set_parallelize(true);
+  l.forward_propagation(ins, outs);
+  l.back_propagation(ins, outs, gouts, gins);
+  return {tout, gx, gW, gb};
+}
+
+static vec_t flat(const tensor_t &t) {
+  vec_t f;
+  for (auto &r : t) f.insert(f.end(), r.begin(), r.end());
+  return f;
+}
+
+template <typename L>
+static void ab_layer(const char *name, L &l, size_t B, bool has_weights, unsigned seed) {
+  std::mt19937 g(seed);
+  tensor_t x(B, vec_t(l.in_shape()[0].size())), dy(B, vec_t(l.out_shape()[0].size()));
+  fill_normal(x, g);
+  fill_normal(dy, g);
+  vec_t W(has_weights ? l.in_shape()[1].size() : 0), b(has_weights ? l.in_shape()[2].size() : 0);
+  fill_uniform(W, g, -0.5f, 0.5f);
+  fill_uniform(b, g, -0.1f, 0.1f);
+  LayerRun a = run_layer(l, core::backend_t::internal, x, W, b, dy, has_weights);
+  LayerRun c = run_layer(l, core::backend_t::b200, x, W, b, dy, has_weights);
+  char what[128];
+  snprintf(what, sizeof(what), "%s forward", name);
+  close_vec(flat(c.out), flat(a.out), 1e-4, what);
+  snprintf(what, sizeof(what), "%s dX", name);
+  close_vec(flat(c.din), flat(a.din), 1e-3, what);
+  if (has_weights) {
+    snprintf(what, sizeof(what), "%s dW (merged)", name);
+    close_vec(sum_rows(c.dW), sum_rows(a.dW), 1e-3, what);
+    snprintf(what, sizeof(what), "%s db (merged)", name);
+    close_vec(sum_rows(c.db), sum_rows(a.db), 1e-3, what);
+  }
+}
+
+static void build_net(network<sequential> &nn, core::backend_t e) {
+  using conv = convolutional_layer;
+  using pool = max_pooling_layer;
+  using fc = fully_connected_layer;
+  nn << conv(16, 16, 5, 3, 8, padding::same, true, 1, 1, 1, 1, e) << relu_layer()
+     << pool(16, 16, 8, 2, false, e)
+     << conv(8, 8, 3, 8, 12, padding::valid, true, 1, 1, 1, 1, e) << tanh_layer()
+     << pool(6, 6, 12, 2, false, e) << fc(3 * 3 * 12, 10, true, e) << softmax_layer(10);
+}
+
+static void ab_network() {
+  network<sequential> a, c;
+  build_net(a, core::backend_t::internal);
+  build_net(c, core::backend_t::b200);
+  set_random_seed(7);
+  a.init_weight();
+  // same starting weights
+  for (size_t i = 0; i < a.depth(); ++i) {
+    auto wa = a[i]->weights();
+    auto wc = c[i]->weights();
+    for (size_t k = 0; k < wa.size(); ++k) *wc[k] = *wa[k];
+  }
+  c.init_weight();  // marks layers initialised; restore the weights afterwards
+  for (size_t i = 0; i < a.depth(); ++i) {
+    auto wa = a[i]->weights();
+    auto wc = c[i]->weights();
+    for (size_t k = 0; k < wa.size(); ++k) *wc[k] = *wa[k];
+  }
+  std::mt19937 g(11);
+  const size_t B = 8, steps = 3;
+  std::vector<vec_t> x(B * steps, vec_t(16 * 16 * 3)), t(B * steps, vec_t(10, 0.f));
+  std::normal_distribution<float> nd(0.f, 1.f);
+  for (auto &v : x)
+    for (auto &e : v) e = nd(g);
+  for (auto &v : t) v[g() % 10] = 1.f;
+  adam oa, oc;
+  a.fit<cross_entropy>(oa, x, t, B, 1);
+  c.fit<cross_entropy>(oc, x, t, B, 1);
+  for (size_t i = 0; i < a.depth(); ++i) {
+    auto wa = a[i]->weights();
+    auto wc = c[i]->weights();
+    for (size_t k = 0; k < wa.size(); ++k) {
+      char what[128];
+      snprintf(what, sizeof(what), "network fit: layer %zu tensor %zu after %zu adam steps", i, k, steps);
+      close_vec(*wc[k], *wa[k], 1e-3, what);
+    }
+  }
+  vec_t pa = a.predict(x[0]), pc = c.predict(x[0]);
+  close_vec(pc, pa, 1e-4, "network predict");
+}
+
+static void ab_quantized() {
+  std::mt19937 g(3);
+  const size_t B = 3;
+  quantized_convolutional_layer qa(12, 12, 5, 5, 4, 6, padding::valid, true, 1, 1, core::backend_t::internal);
+  quantized_convolutional_layer qc(12, 12, 5, 5, 4, 6, padding::valid, true, 1, 1, core::backend_t::b200);
+  tensor_t x(B, vec_t(4 * 12 * 12)), W(1, vec_t(6 * 4 * 25)), b(1, vec_t(6));
+  for (auto &r : x) fill_uniform(r, g, -1.f, 1.f);
+  fill_uniform(W[0], g, -0.5f, 0.5f);
+  fill_uniform(b[0], g, -0.1f, 0.1f);
+  tensor_t oa(B, vec_t(6 * 8 * 8)), oc(B, vec_t(6 * 8 * 8));
+  std::vector<tensor_t *> ins = {&x, &W, &b}, outa = {&oa}, outc = {&oc};
+  qa.set_parallelize(true);
+  qa.forward_propagation(ins, outa);
+  qc.forward_propagation(ins, outc);
+  bool same = true;
+  for (size_t s = 0; s < B; ++s) same = same && std::memcmp(oa[s].data(), oc[s].data(), oa[s].size() * sizeof(float)) == 0;
+  if (same) {
+    printf("ok   quantized convolution bit-exact\n");
+  } else {
+    printf("FAIL quantized convolution differs\n");
+    ++g_fail;
+  }
+}
+
+int main() {
+  try {
+    {
+      convolutional_layer l(12, 10, 5, 5, 2, 6, padding::same, true, 1, 1, 1, 1, core::backend_t::internal);
+      ab_layer("conv 5x5 same", l, 3, true, 1);
+    }
+    {
+      convolutional_layer l(9, 9, 3, 3, 2, 3, padding::valid, true, 2, 2, 1, 1, core::backend_t::internal);
+      ab_layer("conv 3x3 stride 2", l, 2, true, 2);
+    }
+    {
+      bool tbl[] = {true, false, true, true, true, false, false, true, true, true, true, false};  // 3 in x 4 out
+      convolutional_layer l(10, 10, 5, 3, 4, core::connection_table(tbl, 3, 4), padding::valid, true, 1, 1, 1, 1,
+                            core::backend_t::internal);
+      ab_layer("conv 5x5 connection table", l, 3, true, 3);
+    }
+    {
+      fully_connected_layer l(130, 67, true, core::backend_t::internal);
+      ab_layer("fully connected", l, 5, true, 4);
+    }
+    {
+      max_pooling_layer l(8, 8, 3, 2, 2, false, core::backend_t::internal);
+      ab_layer("max pool 2x2", l, 3, false, 5);
+    }
+    {
+      max_pooling_layer l(7, 7, 2, 3, 3, 2, 2, false, padding::valid, core::backend_t::internal);
+      ab_layer("max pool 3x3 stride 2", l, 2, false, 6);
+    }
+    ab_network();
+    ab_quantized();
+    std::ostringstream os;
+    os << core::backend_t::b200;
+    if (os.str() != "B200") {
+      printf("FAIL operator<< gives %s\n", os.str().c_str());
+      ++g_fail;
+    }
+  } catch (const std::exception &e) {
+    printf("FAIL exception: %s\n", e.what());
+    return 2;
+  }
+  printf(g_fail ? "RESULT: %d FAILED\n" : "RESULT: all passed\n", g_fail);
+  return g_fail ? 1 : 0;
+}

@@ -1,0 +1,176 @@
+// b200_glue.h -- C++14 host side of the B200 engine for tiny-dnn.
+//
+// Included by the patched operator dispatchers (Conv2dOp, Conv2dGradOp,
+// FullyConnectedOp, FullyConnectedGradOp, MaxPoolOp, MaxPoolGradOp) that
+// make_overlay.py derives from the reference headers.  It turns the
+// reference's tensor_t rows (one heap vector per sample) into the contiguous
+// buffers of the C ABI (include/tinycnn_b200.h) and back, and turns a non-zero
+// status into nn_error, the reference's error convention
+// (tiny_dnn/util/nn_error.h:19-27).  There is no CPU fallback: if the library
+// cannot create a context the call throws.
+#pragma once
+
+#include <algorithm>
+#include <cstdint>
+#include <vector>
+
+#include "tinycnn_b200.h"
+
+namespace tiny_dnn {
+namespace b200 {
+
+inline void check(int status) {
+  if (status != 0) throw nn_error(std::string("b200: ") + b200_last_error());
+}
+
+// one context per process: device 0, its own stream
+inline b200_ctx *ctx() {
+  static b200_ctx *c = [] {
+    b200_ctx *p = nullptr;
+    check(b200_ctx_create(0, nullptr, &p));
+    return p;
+  }();
+  return c;
+}
+
+inline std::vector<float> pack(const tensor_t &t) {
+  std::vector<float> flat;
+  if (t.empty()) return flat;
+  const size_t n = t[0].size();
+  flat.resize(t.size() * n);
+  for (size_t r = 0; r < t.size(); ++r) std::copy(t[r].begin(), t[r].end(), flat.begin() + r * n);
+  return flat;
+}
+
+inline void unpack(const std::vector<float> &flat, tensor_t &t) {
+  if (t.empty()) return;
+  const size_t n = t[0].size();
+  for (size_t r = 0; r < t.size(); ++r)
+    std::copy(flat.begin() + r * n, flat.begin() + (r + 1) * n, t[r].begin());
+}
+
+// core::conv_params (tiny_dnn/core/params/conv_params.h:63-90) -> b200_conv_desc.
+// The op kernels receive rows that the layer has already padded
+// (convolutional_layer.h:283-299), hence input_is_padded = 1.
+inline b200_conv_desc conv_desc(const core::conv_params &p, std::vector<uint8_t> &tbl) {
+  b200_conv_desc d{};
+  d.in_w = static_cast<int32_t>(p.in.width_);
+  d.in_h = static_cast<int32_t>(p.in.height_);
+  d.in_c = static_cast<int32_t>(p.in.depth_);
+  d.inp_w = static_cast<int32_t>(p.in_padded.width_);
+  d.inp_h = static_cast<int32_t>(p.in_padded.height_);
+  d.out_w = static_cast<int32_t>(p.out.width_);
+  d.out_h = static_cast<int32_t>(p.out.height_);
+  d.out_c = static_cast<int32_t>(p.out.depth_);
+  d.k_w = static_cast<int32_t>(p.weight.width_);
+  d.k_h = static_cast<int32_t>(p.weight.height_);
+  d.stride_w = static_cast<int32_t>(p.w_stride);
+  d.stride_h = static_cast<int32_t>(p.h_stride);
+  d.dil_w = static_cast<int32_t>(p.w_dilation);
+  d.dil_h = static_cast<int32_t>(p.h_dilation);
+  d.has_bias = p.has_bias ? 1 : 0;
+  d.pad_same = p.pad_type == padding::same ? 1 : 0;
+  d.input_is_padded = 1;
+  if (!p.tbl.is_empty()) {  // connected_[inc*cols + o] (conv_params.h:52-54)
+    tbl.assign(p.tbl.connected_.begin(), p.tbl.connected_.end());
+    d.tbl = tbl.data();
+  }
+  return d;
+}
+
+inline b200_pool_desc pool_desc(const core::maxpool_params &p) {
+  b200_pool_desc d{};
+  d.in_w = static_cast<int32_t>(p.in.width_);
+  d.in_h = static_cast<int32_t>(p.in.height_);
+  d.in_c = static_cast<int32_t>(p.in.depth_);
+  d.out_w = static_cast<int32_t>(p.out.width_);
+  d.out_h = static_cast<int32_t>(p.out.height_);
+  d.pool_w = static_cast<int32_t>(p.pool_size_x);
+  d.pool_h = static_cast<int32_t>(p.pool_size_y);
+  d.stride_w = static_cast<int32_t>(p.stride_x);
+  d.stride_h = static_cast<int32_t>(p.stride_y);
+  return d;
+}
+
+// Conv2dOp::compute branch: replaces kernels::conv2d_op_internal forward
+// (tiny_dnn/core/kernels/conv2d_op_internal.h:13-74).
+inline void conv2d_op(const tensor_t &in_data, const vec_t &W, const vec_t &bias,
+                      tensor_t &out_data, const core::conv_params &params) {
+  std::vector<uint8_t> tbl;
+  b200_conv_desc d = conv_desc(params, tbl);
+  std::vector<float> in = pack(in_data), out(out_data.size() * out_data[0].size());
+  check(b200_conv2d_fwd_host(ctx(), &d, in.data(), W.data(), params.has_bias ? bias.data() : nullptr,
+                             out.data(), static_cast<int>(in_data.size())));
+  unpack(out, out_data);
+}
+
+// Conv2dGradOp::compute branch: replaces the backward kernels::conv2d_op_internal
+// (conv2d_op_internal.h:78-181).  The reference adds one dW/db row per sample and
+// sums the rows in edge::merge_grads (tiny_dnn/node.h:89-103); the device returns
+// the batch sum, which is added to row 0, so the merged gradient is the same.
+inline void conv2d_grad_op(const tensor_t &prev_out, const vec_t &W, tensor_t &dW, tensor_t &db,
+                           tensor_t &curr_delta, tensor_t &prev_delta,
+                           const core::conv_params &params) {
+  std::vector<uint8_t> tbl;
+  b200_conv_desc d = conv_desc(params, tbl);
+  std::vector<float> x = pack(prev_out), dy = pack(curr_delta);
+  std::vector<float> dx(prev_delta.size() * prev_delta[0].size());
+  check(b200_conv2d_bwd_host(ctx(), &d, x.data(), W.data(), dy.data(), dx.data(), dW[0].data(),
+                             params.has_bias ? db[0].data() : nullptr, /*accumulate=*/1,
+                             static_cast<int>(prev_out.size())));
+  unpack(dx, prev_delta);
+}
+
+// FullyConnectedOp::compute branch (fully_connected_op_internal.h:15-36)
+inline void fully_connected_op(const tensor_t &in_data, const vec_t &W, const vec_t &bias,
+                               tensor_t &out_data, const core::fully_params &params) {
+  std::vector<float> in = pack(in_data), out(out_data.size() * params.out_size_);
+  check(b200_fc_fwd_host(ctx(), static_cast<int>(params.in_size_), static_cast<int>(params.out_size_),
+                         in.data(), W.data(), params.has_bias_ ? bias.data() : nullptr, out.data(),
+                         static_cast<int>(in_data.size())));
+  unpack(out, out_data);
+}
+
+// FullyConnectedGradOp::compute branch (fully_connected_op_internal.h:38-71)
+inline void fully_connected_grad_op(const tensor_t &prev_out, const vec_t &W, tensor_t &dW,
+                                    tensor_t &db, tensor_t &curr_delta, tensor_t &prev_delta,
+                                    const core::fully_params &params) {
+  std::vector<float> x = pack(prev_out), dy = pack(curr_delta);
+  std::vector<float> dx(prev_delta.size() * params.in_size_);
+  check(b200_fc_bwd_host(ctx(), static_cast<int>(params.in_size_), static_cast<int>(params.out_size_),
+                         x.data(), W.data(), dy.data(), dx.data(), dW[0].data(),
+                         params.has_bias_ ? db[0].data() : nullptr, /*accumulate=*/1,
+                         static_cast<int>(prev_out.size())));
+  unpack(dx, prev_delta);
+}
+
+// MaxPoolOp::compute branch (maxpool_op_internal.h:16-39); the winning indices
+// go back into params.out2inmax, which MaxPoolGradOp reads.
+inline void maxpool_op(const tensor_t &in_data, tensor_t &out_data, core::maxpool_params &params) {
+  b200_pool_desc d = pool_desc(params);
+  const size_t B = in_data.size(), n_out = params.out.size();
+  std::vector<float> in = pack(in_data), out(B * n_out);
+  std::vector<int32_t> arg(B * n_out);
+  check(b200_maxpool_fwd_host(ctx(), &d, in.data(), out.data(), arg.data(), static_cast<int>(B)));
+  unpack(out, out_data);
+  for (size_t s = 0; s < B; ++s) {
+    params.out2inmax[s].resize(n_out);
+    for (size_t i = 0; i < n_out; ++i) params.out2inmax[s][i] = static_cast<size_t>(arg[s * n_out + i]);
+  }
+}
+
+// MaxPoolGradOp::compute branch (maxpool_op_internal.h:41-57)
+inline void maxpool_grad_op(tensor_t &prev_delta, const tensor_t &curr_delta,
+                            core::maxpool_params &params) {
+  b200_pool_desc d = pool_desc(params);
+  const size_t B = prev_delta.size(), n_out = params.out.size();
+  std::vector<float> dy = pack(curr_delta), dx(B * params.in.size());
+  std::vector<int32_t> arg(B * n_out);
+  for (size_t s = 0; s < B; ++s)
+    for (size_t i = 0; i < n_out; ++i) arg[s * n_out + i] = static_cast<int32_t>(params.out2inmax[s][i]);
+  check(b200_maxpool_bwd_host(ctx(), &d, dy.data(), arg.data(), dx.data(), static_cast<int>(B)));
+  unpack(dx, prev_delta);
+}
+
+}  // namespace b200
+}  // namespace tiny_dnn
