@@ -66,6 +66,14 @@ B200_API int b200_ctx_set_stream(b200_ctx *ctx, void *stream);
 B200_API void *b200_ctx_stream(b200_ctx *ctx);
 B200_API int b200_ctx_sync(b200_ctx *ctx);
 
+/*
+ * Context options.  "fc_tensor_cores": 0 = fully-connected GEMMs always on the
+ * fp32 FFMA kernels, 1 (default) = large ones on the tensor cores with the
+ * 3xTF32 split (fp32-level accuracy), 2 = every GEMM the tensor-core kernel can
+ * take.  Unknown names are an error.
+ */
+B200_API int b200_ctx_set_option(b200_ctx *ctx, const char *name, int value);
+
 /* Raw device memory helpers for hosts that do not link the CUDA runtime. */
 B200_API int b200_malloc(b200_ctx *ctx, size_t bytes, void **out);
 B200_API int b200_free(b200_ctx *ctx, void *ptr);

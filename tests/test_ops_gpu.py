@@ -209,6 +209,34 @@ def test_fc_mlp_layer_size(ctx, oracle):
     assert_close(host(db), db_ref, GRAD_TOL, "mlp db")
 
 
+@pytest.mark.parametrize("B,I,O", [(128, 784, 4096), (200, 4096, 330), (256, 1024, 64)])
+def test_fc_tensor_core_path(ctx, oracle, B, I, O):
+    """The 3xTF32 tensor-core GEMMs (forced on) against the oracle at the forward /
+    gradient tolerances, ragged extents included."""
+    rng = np.random.default_rng(17)
+    x = rng.uniform(0, 1, (B, I)).astype(np.float32)
+    W = rng.uniform(-0.05, 0.05, I * O).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, O).astype(np.float32)
+    dy = rng.standard_normal((B, O)).astype(np.float32)
+    y_ref = o.f32(B, O)
+    oracle.orc_fc_fwd(I, O, o.p(x), o.p(W), o.p(b), o.p(y_ref), B)
+    dx_ref, dW_ref, db_ref = o.f32(B, I), o.f32(I * O), o.f32(O)
+    oracle.orc_fc_bwd(I, O, o.p(x), o.p(W), o.p(dy), o.p(dx_ref), o.p(dW_ref), o.p(db_ref), 0, B)
+    check(ctx.lib.b200_ctx_set_option(ctx.handle, b"fc_tensor_cores", 2))
+    try:
+        y = ops.fully_connected_op(ctx, I, O, dev(x), dev(W), dev(b))
+        dx, dW, db = ops.fully_connected_grad_op(ctx, I, O, dev(x), dev(W), dev(dy))
+        ctx.sync()
+    finally:
+        check(ctx.lib.b200_ctx_set_option(ctx.handle, b"fc_tensor_cores", 1))
+    assert_close(host(y), y_ref, FWD_TOL, "tc fwd")
+    assert_close(host(dx), dx_ref, GRAD_TOL, "tc dx")
+    assert_close(host(dW), dW_ref, GRAD_TOL, "tc dW")
+    assert_close(host(db), db_ref, GRAD_TOL, "tc db")
+    # the hi/lo split keeps fp32-level accuracy: a single-pass TF32 product would sit near 1e-3
+    assert np.abs(host(y) - y_ref).max() <= 5e-5 * np.abs(y_ref).max()
+
+
 # --------------------------------------------------------------------------- pooling
 @pytest.mark.parametrize("name", list(MAXPOOL_CASES))
 def test_maxpool(ctx, oracle, gold, name):

@@ -79,6 +79,7 @@ SIGNATURES = {
     "b200_ctx_create": (_i, [_i, _vp, C.POINTER(_vp)]),
     "b200_ctx_destroy": (_i, [_vp]),
     "b200_ctx_set_stream": (_i, [_vp, _vp]),
+    "b200_ctx_set_option": (_i, [_vp, C.c_char_p, _i]),
     "b200_ctx_stream": (_vp, [_vp]),
     "b200_ctx_sync": (_i, [_vp]),
     "b200_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),

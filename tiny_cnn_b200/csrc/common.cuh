@@ -90,6 +90,9 @@ struct b200_ctx {
   // device word a kernel sets when a bounded wait ran out; read by b200_ctx_sync
   int *dev_err = nullptr;
 
+  // fully-connected GEMMs on the tensor cores (3xTF32): 0 never, 1 when large, 2 whenever legal
+  int fc_tensor_cores = 1;
+
   // tile shapes already chosen, keyed by the problem's dimensions
   std::map<std::string, TileChoice> tile_cache;
 
@@ -162,8 +165,15 @@ int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *
 // ----------------------------------------------------------------------------
 // other ops
 // ----------------------------------------------------------------------------
+// tensor-core GEMM (gemm_tc.cu): D[M][N] (+)= A * Bt^T, operands split into TF32 hi/lo
+// pairs in `scratch` (gemm_tc_scratch_floats floats)
+size_t gemm_tc_scratch_floats(int M, int N, int K);
+int gemm_tc(b200_ctx *ctx, int M, int N, int K, const float *src_a, long long lda, bool a_transposed,
+            const float *src_b, long long ldb, bool b_transposed, float *D, const float *bias,
+            int accumulate, int act, float *scratch);
+
 // `scratch` (fc_scratch_floats floats, may be nullptr) holds the k-slice partial
-// sums small GEMMs are split into.
+// sums small GEMMs are split into, or the split operands of the tensor-core path.
 size_t fc_scratch_floats(const b200_ctx *ctx, int in_size, int out_size, int B);
 int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
            const float *bias, float *out, int B, int act, float *scratch);

@@ -110,11 +110,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll already blocks for a
-// hardware-defined interval) and reports failure instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int limit = 1 << 22) {
-  for (int i = 0; i < limit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait: polls until the phase completes or about two seconds of wall
+// time (the device's nanosecond timer) have passed, and reports which.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
+                                                  unsigned long long limit_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+  do {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
+  } while (t1 - t0 < limit_ns);
   return false;
 }
 

@@ -171,10 +171,26 @@ static GemmPlan plan_gemm(const b200_ctx *ctx, int M, int N, int K) {
   return p;
 }
 
+// A GEMM goes to the tensor cores when the context allows it and it is big enough
+// to pay for splitting its operands.
+static bool use_tc(const b200_ctx *ctx, int M, int N, int K) {
+  if (ctx->fc_tensor_cores == 0) return false;
+  if (M < 128 || N < 64 || K < 32) return false;  // at least one full tile in every direction
+  if (ctx->fc_tensor_cores >= 2) return true;
+  return (long long)M * N * K >= (1LL << 26);
+}
+
 // Upper bound, monotone in B, of the scratch any of the three GEMMs of a layer
-// needs: slices * M * N <= (2*SMs/tiles32 + 1) * M * N <= 2*SMs*1024 + M*N.
+// needs: slices * M * N <= (2*SMs/tiles32 + 1) * M * N <= 2*SMs*1024 + M*N; the
+// tensor-core path needs the split operands instead.
 size_t fc_scratch_floats(const b200_ctx *ctx, int in_size, int out_size, int B) {
   size_t need = 0;
+  if (ctx->fc_tensor_cores != 0) {
+    size_t t[3] = {gemm_tc_scratch_floats(B, out_size, in_size), gemm_tc_scratch_floats(B, in_size, out_size),
+                   gemm_tc_scratch_floats(in_size, out_size, B)};
+    for (size_t v : t)
+      if (v > need) need = v;
+  }
   size_t mn[3] = {(size_t)B * out_size, (size_t)B * in_size, (size_t)in_size * out_size};
   for (size_t v : mn) {
     size_t n = (size_t)2 * ctx->sm_count * 1024 + v;
@@ -214,6 +230,10 @@ static int run_gemm(b200_ctx *ctx, int M, int N, int K, const float *A, long lon
 
 int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
            const float *bias, float *out, int B, int act, float *scratch) {
+  if (scratch && use_tc(ctx, B, out_size, in_size))
+    // A = in [B][in]; Bt = W^T: W is [in][out], i.e. K x N, transposed while splitting
+    return gemm_tc(ctx, B, out_size, in_size, in, in_size, false, W, out_size, true, out, bias, 0,
+                   act, scratch);
   // M = B, N = out, K = in; A = in (k fast), Bm = W[k][n] (n fast)
   return run_gemm<true, true>(ctx, B, out_size, in_size, in, in_size, 1, W, out_size, 1, out, bias,
                               0, act, scratch);
@@ -222,13 +242,21 @@ int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const floa
 int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
            const float *dout, float *din, float *dW, float *db, int accumulate, int B,
            float *scratch) {
-  if (din) {
+  if (din && scratch && use_tc(ctx, B, in_size, out_size)) {
+    // din[B][in] = dout[B][out] * W^T: A = dout; Bt[n = c][k = o] = W[c*out + o] as stored
+    B200_TRY(gemm_tc(ctx, B, in_size, out_size, dout, out_size, false, W, out_size, false, din,
+                     nullptr, 0, 0, scratch));
+  } else if (din) {
     // din[B][in] = dout[B][out] * W^T : M = B, N = in, K = out;
     // Bm(k = o, n = c) = W[c*out + o] -> b_k = 1, b_n = out (k fast)
     B200_TRY((run_gemm<true, false>(ctx, B, in_size, out_size, dout, out_size, 1, W, 1, out_size,
                                     din, nullptr, 0, 0, scratch)));
   }
-  if (dW) {
+  if (dW && scratch && use_tc(ctx, in_size, out_size, B)) {
+    // dW[in][out] (+)= in^T * dout: A = in^T (in is B x in = K x M), Bt = dout^T (K x N)
+    B200_TRY(gemm_tc(ctx, in_size, out_size, B, in, in_size, true, dout, out_size, true, dW, nullptr,
+                     accumulate, 0, scratch));
+  } else if (dW) {
     // dW[in][out] (+)= in^T * dout : M = in, N = out, K = B;
     // A(m = c, k = n) = in[n*in + c] -> a_m = 1, a_k = in (m fast)
     B200_TRY((run_gemm<false, true>(ctx, in_size, out_size, B, in, 1, in_size, dout, out_size, 1,

@@ -206,6 +206,17 @@ int b200_ctx_set_stream(b200_ctx *ctx, void *stream) {
   return 0;
 }
 
+int b200_ctx_set_option(b200_ctx *ctx, const char *name, int value) {
+  B200_REQUIRE(ctx != nullptr && name != nullptr, "ctx_set_option: NULL argument");
+  if (strcmp(name, "fc_tensor_cores") == 0) {
+    B200_REQUIRE(value >= 0 && value <= 2, "fc_tensor_cores must be 0, 1 or 2");
+    ctx->fc_tensor_cores = value;
+    return 0;
+  }
+  B200_REQUIRE(false, "ctx_set_option: unknown option '%s'", name);
+  return 0;
+}
+
 void *b200_ctx_stream(b200_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 
 int b200_ctx_sync(b200_ctx *ctx) {
