@@ -70,7 +70,10 @@ B200_API int b200_ctx_sync(b200_ctx *ctx);
  * Context options.  "fc_tensor_cores": 0 = fully-connected GEMMs always on the
  * fp32 FFMA kernels, 1 (default) = large ones on the tensor cores with the
  * 3xTF32 split (fp32-level accuracy), 2 = every GEMM the tensor-core kernel can
- * take.  Unknown names are an error.
+ * take.  "conv_tensor_cores": 0 = convolutions never on the tensor cores,
+ * 1 (default) = the passes of stride-1 layers whose contracted side has at least
+ * 16 channels, 2 = every pass the tensor-core kernels can take (stride 1,
+ * dilation 1, windows up to 8x8, at most 256 channels).  Unknown names are an error.
  */
 B200_API int b200_ctx_set_option(b200_ctx *ctx, const char *name, int value);
 
@@ -103,7 +106,7 @@ typedef struct b200_conv_desc {
   int32_t input_is_padded;      /* 1: `in`/`din` rows already have in_padded  */
                                 /* geometry, as Conv2dOp::compute receives    */
                                 /* them (convolutional_layer.h:283-299)       */
-  int32_t algo;                 /* 0 auto, 1 general kernels, 2 tiled kernels */
+  int32_t algo;                 /* 0 auto, 1 general kernels, 2 tiled FFMA kernels, 3 tensor-core kernels */
   const uint8_t *tbl;           /* HOST, may be NULL                          */
 } b200_conv_desc;
 

@@ -58,12 +58,19 @@ def tiled_applies(c):
 
 
 # --------------------------------------------------------------------------- convolution
-@pytest.mark.parametrize("algo", [1, 2])
+def tensor_core_applies(c):
+    return (c.get("sw", 1) == 1 and c.get("sh", 1) == 1 and c.get("dw", 1) == 1 and c.get("dh", 1) == 1
+            and c["kw"] <= 8 and c["kh"] <= 8)
+
+
+@pytest.mark.parametrize("algo", [1, 2, 3])
 @pytest.mark.parametrize("name", list(CONV_CASES))
 def test_conv_fwd_bwd(ctx, oracle, gold, name, algo):
     c = CONV_CASES[name]
     if algo == 2 and not tiled_applies(c):
         pytest.skip("tiled kernels take stride 1, dilation 1, 3x3/5x5 only")
+    if algo == 3 and not tensor_core_applies(c):
+        pytest.skip("tensor-core kernels take stride 1, dilation 1, windows up to 8x8 only")
     d = conv_desc(c, algo=algo)
     x, W, b, dy = gen_conv_inputs(c, d)
     y_ref, dx_ref, dW_ref, db_ref = orc_conv(oracle, d, x, W, b, dy, per_sample=0)
@@ -147,13 +154,14 @@ def test_conv_tiled_vs_general_full_size(ctx):
         b = torch.rand(oc, device="cuda", generator=g) - 0.5
         dy = torch.randn(B, oc * w * w, device="cuda", generator=g)
         res = []
-        for algo in (1, 2):
+        for algo in (1, 2, 3) if oc <= 64 else (1, 2):  # wider layers do not fit the tensor-core tiles
             d = ops.conv_params(w, w, c, k, k, oc, True, True, algo=algo)
             y = ops.conv2d_op(ctx, d, x, W, b)
             dx, dW, db = ops.conv2d_grad_op(ctx, d, x, W, dy)
             res.append([host(t) for t in (y, dx, dW, db)])
-        for a, bb, tol, nm in zip(res[0], res[1], (FWD_TOL, GRAD_TOL, GRAD_TOL, GRAD_TOL), "y dx dW db".split()):
-            assert_close(bb, a, tol, f"{w}x{w}x{c}->{oc} {nm} tiled vs general")
+        for other, label in list(zip(res[1:], ("tiled", "tensor-core"))):
+            for a, bb, tol, nm in zip(res[0], other, (FWD_TOL, GRAD_TOL, GRAD_TOL, GRAD_TOL), "y dx dW db".split()):
+                assert_close(bb, a, tol, f"{w}x{w}x{c}->{oc} {nm} {label} vs general")
 
 
 def test_conv_linearity_full_size(ctx):

@@ -28,6 +28,17 @@ int conv_fwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
   B200_TRY(conv_geom_from_desc(ctx, d, &g));
   if (batch == 0) return 0;  // empty batch: nothing to read or write
   B200_REQUIRE(in && W && out && (bias || !g.has_bias), "conv2d_fwd: NULL buffer");
+  ConvTcUse tc = conv_tc_use(ctx, g, d->algo);
+  B200_REQUIRE(d->algo != 3 || tc.fwd,
+               "conv2d_fwd: tensor-core kernels need stride 1, dilation 1, windows <= 8x8, <= 256 channels");
+  if (tc.fwd) {
+    size_t n_x = align_up(conv_tc_tall_floats(g, batch, 0), 64);
+    void *scratch = nullptr;
+    B200_TRY(ctx_scratch(ctx, (n_x + conv_tc_filter_floats(g, 0)) * sizeof(float), &scratch));
+    float *xs = static_cast<float *>(scratch);
+    B200_TRY(conv_tc_tall_x(ctx, g, in, batch, xs));
+    return conv_tc_fwd(ctx, g, xs, W, bias, out, batch, B200_ACT_NONE, xs + n_x);
+  }
   bool tiled = use_tiled(d, g);
   B200_REQUIRE(tiled || d->algo != 2, "conv2d_fwd: tiled kernels need stride 1, dilation 1, 3x3/5x5");
   if (tiled) {
@@ -56,21 +67,49 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
     }
     return 0;
   }
+  ConvTcUse tc = conv_tc_use(ctx, g, d->algo);
+  B200_REQUIRE(d->algo != 3 || tc.dw,
+               "conv2d_bwd: tensor-core kernels need stride 1, dilation 1, windows <= 8x8, <= 256 channels");
+  if (!din) tc.dx = false;
   bool tiled = use_tiled(d, g) && g.OW <= 64;
   B200_REQUIRE(tiled || d->algo != 2,
                "conv2d_bwd: tiled kernels need stride 1, dilation 1, 3x3/5x5, out width <= 64");
-  if (!tiled) {
-    if (din) B200_TRY(conv_general_dx(ctx, g, W, dout, din, batch));
-    return conv_general_dw(ctx, g, in, dout, dW, db, accumulate, batch);
-  }
-  size_t n_dx = din ? conv_tiled_dx_scratch(g) : 0;
-  size_t n_dw = conv_tiled_dw_scratch(ctx, g, batch);
-  size_t n_dx_al = align_up(n_dx, 64);
+  // one carve-up of the context scratch for every pass of this call
+  const bool need_dys = tc.dx || tc.dw;
+  size_t n_dys = need_dys ? align_up(conv_tc_tall_floats(g, batch, 1), 64) : 0;
+  int bs_rows = tc.dw && g.has_bias ? conv_tc_bsum_rows(g, batch) : 0;
+  size_t n_bs = align_up((size_t)bs_rows * g.OC, 64);
+  size_t n_xs = tc.dw ? align_up(conv_tc_tall_floats(g, batch, 0), 64) : 0;
+  size_t n_wdx = tc.dx ? align_up(conv_tc_filter_floats(g, 1), 64) : 0;
+  size_t n_part = tc.dw ? align_up(conv_tc_dw_floats(ctx, g, batch), 64) : 0;
+  size_t n_tdx = (din && !tc.dx && tiled) ? align_up(conv_tiled_dx_scratch(g), 64) : 0;
+  size_t n_tdw = (!tc.dw && tiled) ? conv_tiled_dw_scratch(ctx, g, batch) : 0;
   void *scratch = nullptr;
-  B200_TRY(ctx_scratch(ctx, (n_dx_al + n_dw) * sizeof(float), &scratch));
-  float *s_dx = static_cast<float *>(scratch);
-  float *s_dw = s_dx + n_dx_al;
-  if (din) B200_TRY(conv_tiled_dx(ctx, g, W, dout, din, batch, s_dx));
+  B200_TRY(ctx_scratch(ctx, (n_dys + n_bs + n_xs + n_wdx + n_part + n_tdx + n_tdw + 64) * sizeof(float),
+                       &scratch));
+  float *dys = static_cast<float *>(scratch);
+  float *bs = dys + n_dys, *xs = bs + n_bs, *wdx = xs + n_xs, *part = wdx + n_wdx;
+  float *s_dx = part + n_part, *s_dw = s_dx + n_tdx;
+  if (need_dys) B200_TRY(conv_tc_tall_dy(ctx, g, dout, batch, dys, bs_rows ? bs : nullptr));
+  // dX
+  if (din) {
+    if (tc.dx)
+      B200_TRY(conv_tc_dx(ctx, g, dys, W, din, batch, wdx));
+    else if (tiled)
+      B200_TRY(conv_tiled_dx(ctx, g, W, dout, din, batch, s_dx));
+    else
+      B200_TRY(conv_general_dx(ctx, g, W, dout, din, batch));
+  }
+  // dW, db
+  if (tc.dw) {
+    B200_TRY(conv_tc_tall_x(ctx, g, in, batch, xs));
+    int splits = 0;
+    B200_TRY(conv_tc_dw(ctx, g, xs, dys, batch, part, &splits));
+    B200_TRY(merge_rows(ctx, part, splits, lenW, dW, lenW, accumulate, &g));
+    if (g.has_bias) B200_TRY(merge_rows(ctx, bs, bs_rows, g.OC, db, g.OC, accumulate, nullptr));
+    return 0;
+  }
+  if (!tiled) return conv_general_dw(ctx, g, in, dout, dW, db, accumulate, batch);
   int splits = 0;
   B200_TRY(conv_tiled_dw_partials(ctx, g, in, dout, batch, s_dw, &splits));
   size_t row = lenW + g.OC;

@@ -92,6 +92,9 @@ struct b200_ctx {
 
   // fully-connected GEMMs on the tensor cores (3xTF32): 0 never, 1 when large, 2 whenever legal
   int fc_tensor_cores = 1;
+  // convolutions on the tensor cores: 0 never, 1 for layers with at least 16 channels on the
+  // contracted side, 2 whenever the geometry allows
+  int conv_tensor_cores = 1;
 
   // tile shapes already chosen, keyed by the problem's dimensions
   std::map<std::string, TileChoice> tile_cache;
@@ -151,6 +154,29 @@ int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float 
 // into scratch; the caller merges them in row order.
 int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in,
                            const float *dout, int B, float *scratch, int *splits);
+
+// tensor-core path (conv_tc.cu): stride 1, dilation 1, windows up to 8x8, at most 256 channels
+// either side.  The passes read "tall" split copies of the input (xs) and of dY (dys) that
+// conv_tc_tall_x / conv_tc_tall_dy write; sizes in floats from the *_floats functions.
+bool conv_tc_ok(const b200_ctx *ctx, const ConvGeom &g);
+// which passes of a layer run on the tensor cores: `algo` 3 = all (when conv_tc_ok), 1 / 2 =
+// none, 0 = by the context's conv_tensor_cores option
+struct ConvTcUse {
+  bool fwd, dx, dw;
+};
+ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo);
+size_t conv_tc_tall_floats(const ConvGeom &g, int B, int which);  // 0: input, 1: dY
+size_t conv_tc_filter_floats(const ConvGeom &g, int for_dx);
+int conv_tc_bsum_rows(const ConvGeom &g, int B);
+size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B);
+int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs);
+int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, float *dys, float *bsum);
+int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,
+                float *out, int B, int act, float *wt);
+int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *W, float *din, int B,
+               float *wt);
+int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *dys, int B, float *part,
+               int *splits);
 
 // dst (+)= sum_r src[r*stride + i], rows summed in order; optional connection
 // mask for convolution weights (entries of unconnected pairs are left alone

@@ -1,0 +1,727 @@
+// Stride-1 convolution on the 5th-generation tensor cores (tcgen05), fp32-accurate
+// through the 3xTF32 split (x = hi + lo; lo*hi + hi*lo + hi*hi accumulated in fp32 in
+// tensor memory).  Replaces the loops of kernels::conv2d_op_internal and
+// kernels::conv2d_grad_op_internal (tiny_dnn/core/kernels/conv2d_op_internal.h:13-74,
+// :91-127 dX, :130-169 dW, :172-179 db) for layers with enough channels to feed the
+// tensor pipe; the FFMA kernels of conv_tiled.cu keep the rest.
+//
+// Operand layout ("tall" pixel-major split tensors, made by to_tall_kernel):
+//   P[hi|lo][t][x][c]   c < Cp (channels padded to 32: one 128-byte row per pixel),
+//   t = b*period + y    every image is followed by `period - H` rows of zeros, which serve
+//                       as the bottom padding of image b and the top padding of image b+1;
+//                       left/right padding and the rows before the first image come from
+//                       the zero fill of out-of-range TMA coordinates.
+//
+// Forward / dX (conv_tc_kernel): implicit GEMM, M = 128 output pixels (16 tall rows x 8
+//   columns), N = output channels, K = 32 input channels per filter tap.  One TMA load
+//   brings the haloed input tile (16+KH-1 rows x 16 columns x 32 channels) into shared
+//   memory once; every tap's A operand is the same tile addressed at a row offset
+//   (ky*16 + kx rows) -- the 128-byte swizzle is a function of the absolute address, so
+//   no im2col copy is made.  Filters stream through a ring of per-tap tiles.
+// dW (conv_dw_tc_kernel): K = pixels.  Both operands are MN-major (rows = pixels):
+//   A = dY with the kx shifts stacked along M (blocks one pixel row = 128 bytes apart),
+//   B = X with the ky shifts stacked along N (blocks one tile row apart), so one MMA chain
+//   computes 4 x KH taps of a 32 x 32 channel block.  The batch is cut into slices whose
+//   partial sums are merged in fixed order (the device form of edge::merge_grads).
+// Warp roles in both kernels: warps 0-3 epilogue (one TMEM lane per thread), warp 4 TMEM
+// allocation + TMA producer, warp 5 MMA issuer.  No multicast; every wait is bounded and a
+// timeout sets the context's error word, frees tensor memory and returns.
+#include <stdlib.h>
+
+#include "tc_utils.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int TCV_THREADS = 192;
+constexpr int TCV_TILE_ROWS = 16;  // tall rows per output tile
+constexpr int TCV_TILE_COLS = 8;   // columns per output tile (one group of 8 MMA rows)
+constexpr int TCV_HALO_W = 16;     // columns of the haloed tile in shared memory
+
+// geometry of the tall tensors of one convolution
+struct TallGeom {
+  int pad_b, pad_r;        // implied bottom / right padding
+  int period;              // tall rows per image
+  int Cp, OCp;             // channels padded to 32
+  long long rows;          // B * period
+};
+
+TallGeom tall_geom(const ConvGeom &g, int B) {
+  TallGeom t;
+  t.pad_b = g.OH + g.KH - 1 - g.pad_t - g.HI;
+  t.pad_r = g.OW + g.KW - 1 - g.pad_l - g.WI;
+  int pv = g.pad_t > t.pad_b ? g.pad_t : t.pad_b;
+  if (pv < 0) pv = 0;
+  t.period = g.HI + pv;
+  t.Cp = (g.C + 31) / 32 * 32;
+  t.OCp = (g.OC + 31) / 32 * 32;
+  t.rows = (long long)B * t.period;
+  return t;
+}
+
+// rows per image of the tall form of dY as the dX pass needs it (padding KH-1-pad on each side)
+int dy_period(const ConvGeom &g) {
+  TallGeom t = tall_geom(g, 1);
+  int a = g.KH - 1 - g.pad_t, b = g.KH - 1 - t.pad_b;
+  int pv = a > b ? a : b;
+  if (pv < 0) pv = 0;
+  return g.OH + pv;
+}
+
+// ---- CHW rows -> tall split tensors ---------------------------------------------------
+
+// One block converts `rb` tall rows of one image: src[b][c][y][x] -> hi/lo[t][x][c],
+// zero for padded channels and for the rows between images.  With `bsum` the block also
+// writes the per-channel sum of what it read (bias gradient partials, fixed order).
+__global__ void __launch_bounds__(256) to_tall_kernel(const float *__restrict__ src, int C, int H, int W,
+                                                      int Cp, int period, int rb, long long rows_total,
+                                                      float *__restrict__ hi, float *__restrict__ lo,
+                                                      float *__restrict__ bsum) {
+  extern __shared__ float tile[];  // [rb*W][Cp+1]
+  const int chunks = (period + rb - 1) / rb;
+  const int b = blockIdx.x / chunks, r0 = (blockIdx.x % chunks) * rb;
+  const int nr = min(rb, period - r0);
+  const int npx = nr * W, pitch = Cp + 1;
+  const int valid_rows = max(0, min(nr, H - r0));
+  for (int i = threadIdx.x; i < C * npx; i += blockDim.x) {
+    int c = i / npx, p = i % npx;
+    int ry = p / W;
+    float v = 0.f;
+    if (ry < valid_rows) v = src[((size_t)(b * C + c) * H + r0) * W + p];
+    tile[p * pitch + c] = v;
+  }
+  __syncthreads();
+  const size_t base = ((size_t)b * period + r0) * W * Cp;
+  for (int i = threadIdx.x; i < npx * Cp; i += blockDim.x) {
+    int p = i / Cp, c = i % Cp;
+    float h = 0.f, l = 0.f;
+    if (c < C) split_tf32_rn(tile[p * pitch + c], h, l);
+    hi[base + i] = h;
+    lo[base + i] = l;
+  }
+  if (bsum != nullptr && threadIdx.x < C) {
+    float s = 0.f;
+    for (int p = 0; p < valid_rows * W; ++p) s += tile[p * pitch + threadIdx.x];
+    bsum[(size_t)blockIdx.x * C + threadIdx.x] = s;
+  }
+}
+
+// ---- filter matrices ----------------------------------------------------------------------
+
+// Forward: F[tap][slab][n][k] = W[o = n][inc = slab*32 + k][ky][kx]            (tap = ky*KW + kx)
+// dX:      F[tap][slab][n][k] = W[o = slab*32 + k][inc = n][KH-1-ky][KW-1-kx]
+// n < Np rows of 32 floats; zero beyond the real channels and for unconnected pairs.
+__global__ void tc_filter_prep_kernel(const float *__restrict__ W, const uint8_t *__restrict__ tbl, int C,
+                                      int OC, int KH, int KW, int Np, int slabs, int for_dx,
+                                      float *__restrict__ hi, float *__restrict__ lo) {
+  const long long total = (long long)KH * KW * slabs * Np * 32;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    int k = (int)(i % 32);
+    long long r = i / 32;
+    int n = (int)(r % Np);
+    r /= Np;
+    int slab = (int)(r % slabs);
+    int tap = (int)(r / slabs);
+    int ky = tap / KW, kx = tap % KW;
+    int o, inc;
+    if (for_dx) {
+      o = slab * 32 + k;
+      inc = n;
+      ky = KH - 1 - ky;
+      kx = KW - 1 - kx;
+    } else {
+      o = n;
+      inc = slab * 32 + k;
+    }
+    float h = 0.f, l = 0.f;
+    if (o < OC && inc < C && (tbl == nullptr || tbl[inc * OC + o]))
+      split_tf32_rn(W[((size_t)(o * C + inc) * KH + ky) * KW + kx], h, l);
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+}  // namespace
+
+// ---- forward / dX: implicit GEMM over a haloed pixel tile ----------------------------------
+
+namespace {
+
+struct TcConvArgs {
+  float *out;          // [B][N][OH][OW]
+  const float *bias;   // N values or nullptr
+  int *err;
+  int B, period;       // images, tall rows per image (input and output share the row index)
+  int OH, OW, N, Np;   // output extent, real / padded output channels
+  int slabs;           // 32-channel slabs of the input
+  int KH, KW, pad_t, pad_l;
+  int tiles_x, ntiles;
+  int act;
+  int nf;              // filter ring stages
+  int acc_stride;      // TMEM columns per accumulator (multiple of 32)
+  int tmem_cols;       // allocated columns (power of two >= 2*acc_stride)
+};
+
+__global__ void __launch_bounds__(TCV_THREADS, 1)
+  conv_tc_kernel(const __grid_constant__ CUtensorMap in_hi, const __grid_constant__ CUtensorMap in_lo,
+                 const __grid_constant__ CUtensorMap f_hi, const __grid_constant__ CUtensorMap f_lo,
+                 const TcConvArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t HB = TCV_HALO_W * (TCV_TILE_ROWS + a.KH - 1) * 128u;  // one halo tile (hi or lo)
+  const uint32_t FB = (uint32_t)a.Np * 128u;                           // one filter tile (hi or lo)
+  uint8_t *halo = smem;             // [2][hi | lo]
+  uint8_t *filt = smem + 4 * HB;    // [nf][hi | lo]
+  uint64_t *halo_full = reinterpret_cast<uint64_t *>(filt + (size_t)a.nf * 2 * FB);
+  uint64_t *halo_empty = halo_full + 2;
+  uint64_t *acc_full = halo_empty + 2;
+  uint64_t *acc_empty = acc_full + 2;
+  uint64_t *filt_full = acc_empty + 2;
+  uint64_t *filt_empty = filt_full + a.nf;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(filt_empty + a.nf);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&halo_full[i], 1);
+      mbar_init(&halo_empty[i], 1);
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);
+    }
+    for (int i = 0; i < a.nf; ++i) {
+      mbar_init(&filt_full[i], 1);
+      mbar_init(&filt_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 4) tmem_alloc(tmem_slot, (uint32_t)a.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int taps = a.KH * a.KW;
+  bool failed = false;
+
+  if (warp == 4 && lane == 0) {
+    // ---- TMA producer -----------------------------------------------------------------
+    uint32_t u = 0, f = 0;
+    for (int tile = blockIdx.x; tile < a.ntiles && !failed; tile += gridDim.x) {
+      const int x0 = (tile % a.tiles_x) * TCV_TILE_COLS, t0 = (tile / a.tiles_x) * TCV_TILE_ROWS;
+      for (int slab = 0; slab < a.slabs && !failed; ++slab, ++u) {
+        const uint32_t hb = u & 1, use = u >> 1;
+        if (use > 0 && !mbar_wait_bounded(&halo_empty[hb], (use - 1) & 1)) {
+          failed = true;
+          break;
+        }
+        uint8_t *h = halo + hb * 2 * HB;
+        mbar_expect_tx(&halo_full[hb], 2 * HB);
+        tma_load_3d(h, &in_hi, slab * 32, x0 - a.pad_l, t0 - a.pad_t, &halo_full[hb]);
+        tma_load_3d(h + HB, &in_lo, slab * 32, x0 - a.pad_l, t0 - a.pad_t, &halo_full[hb]);
+        for (int tap = 0; tap < taps; ++tap, ++f) {
+          const uint32_t fs = f % a.nf, fuse = f / a.nf;
+          if (fuse > 0 && !mbar_wait_bounded(&filt_empty[fs], (fuse - 1) & 1)) {
+            failed = true;
+            break;
+          }
+          uint8_t *ft = filt + (size_t)fs * 2 * FB;
+          const int row = (tap * a.slabs + slab) * a.Np;
+          mbar_expect_tx(&filt_full[fs], 2 * FB);
+          tma_load_2d(ft, &f_hi, 0, row, &filt_full[fs]);
+          tma_load_2d(ft + FB, &f_lo, 0, row, &filt_full[fs]);
+        }
+      }
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ---- MMA issuer -----------------------------------------------------------------------
+    const uint32_t idesc = umma_idesc_tf32(128, a.Np);
+    uint32_t u = 0, f = 0, it = 0;
+    for (int tile = blockIdx.x; tile < a.ntiles && !failed; tile += gridDim.x, ++it) {
+      const uint32_t ab = it & 1, ause = it >> 1;
+      if (ause > 0 && !mbar_wait_bounded(&acc_empty[ab], (ause - 1) & 1)) {
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + ab * (uint32_t)a.acc_stride;
+      uint32_t accumulate = 0;
+      for (int slab = 0; slab < a.slabs && !failed; ++slab, ++u) {
+        const uint32_t hb = u & 1;
+        if (!mbar_wait_bounded(&halo_full[hb], (u >> 1) & 1)) {
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t hbase = smem_u32(halo + hb * 2 * HB);
+        for (int tap = 0; tap < taps; ++tap, ++f) {
+          const uint32_t fs = f % a.nf;
+          if (!mbar_wait_bounded(&filt_full[fs], (f / a.nf) & 1)) {
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const int ky = tap / a.KW, kx = tap - ky * a.KW;
+          // the tap's A operand: the halo tile addressed (ky, kx) pixels further on
+          const uint32_t abase = hbase + (uint32_t)(ky * TCV_HALO_W + kx) * 128u;
+          const uint32_t bbase = smem_u32(filt + (size_t)fs * 2 * FB);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint64_t ahi = umma_desc(abase + k4 * 32, 16, TCV_HALO_W * 128, 2);
+            const uint64_t alo = umma_desc(abase + HB + k4 * 32, 16, TCV_HALO_W * 128, 2);
+            const uint64_t bhi = umma_desc(bbase + k4 * 32, 16, 1024, 2);
+            const uint64_t blo = umma_desc(bbase + FB + k4 * 32, 16, 1024, 2);
+            umma_tf32(tmem_d, alo, bhi, idesc, accumulate);
+            umma_tf32(tmem_d, ahi, blo, idesc, 1);
+            umma_tf32(tmem_d, ahi, bhi, idesc, 1);
+            accumulate = 1;
+          }
+          umma_commit(&filt_empty[fs]);
+        }
+        if (!failed) umma_commit(&halo_empty[hb]);
+      }
+      if (!failed) umma_commit(&acc_full[ab]);
+    }
+  } else if (warp < 4) {
+    // ---- epilogue ------------------------------------------------------------------------
+    uint32_t it = 0;
+    const int m = warp * 32 + lane, dt = m >> 3, dx = m & 7;
+    for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x, ++it) {
+      const uint32_t ab = it & 1;
+      if (!mbar_wait_bounded(&acc_full[ab], (it >> 1) & 1)) {
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+      const int x = (tile % a.tiles_x) * TCV_TILE_COLS + dx;
+      const int t = (tile / a.tiles_x) * TCV_TILE_ROWS + dt;
+      const int b = t / a.period, y = t - b * a.period;
+      const bool valid = b < a.B && y < a.OH && x < a.OW;
+      float *obase = a.out + ((size_t)b * a.N * a.OH + y) * a.OW + x;
+      const size_t plane = (size_t)a.OH * a.OW;
+      for (int c0 = 0; c0 < a.Np; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + ab * (uint32_t)a.acc_stride + (uint32_t)c0, v);
+        if (valid) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int oc = c0 + j;
+            if (oc < a.N) {
+              float r = v[j];
+              if (a.bias) r += a.bias[oc];
+              obase[oc * plane] = apply_act(r, a.act);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[ab]);
+    }
+  }
+  if (failed && a.err) atomicExch(a.err, 3);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
+}
+
+}  // namespace
+
+// ---- dW: pixels are the contraction ----------------------------------------------------------
+
+namespace {
+
+constexpr int TCW_ROWS = 16;    // tall rows per stage
+constexpr int TCW_STAGES = 2;
+
+struct TcDwArgs {
+  float *part;            // [ksplits][row_stride] partial weight gradients, reference order
+  int *err;
+  int KH, KW, pad_t, pad_l, C, OC;
+  int groups_x;           // groups of 8 input columns
+  int nstages;            // row blocks x column groups
+  int ic_slabs;
+  int ksplits;
+  int tmem_cols;
+  long long row_stride;
+};
+
+// dW[o][inc][ky][kx] = sum over pixels u of X dY[t][u + pad_l - kx] * X[t + ky - pad_t][u]
+__global__ void __launch_bounds__(TCV_THREADS, 1)
+  conv_dw_tc_kernel(const __grid_constant__ CUtensorMap dy_hi, const __grid_constant__ CUtensorMap dy_lo,
+                    const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ CUtensorMap x_lo,
+                    const TcDwArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t DYB = 16u * TCW_ROWS * 128u;                 // dY tile: 16 columns x rows (hi or lo)
+  const uint32_t XB = 8u * (TCW_ROWS + a.KH - 1) * 128u;      // X tile: 8 columns x (rows + KH-1)
+  const uint32_t STAGE = 2 * DYB + 2 * XB;
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + TCW_STAGES * STAGE);
+  uint64_t *empty = full + TCW_STAGES;
+  uint64_t *accum = empty + TCW_STAGES;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ocs = blockIdx.y / a.ic_slabs, ics = blockIdx.y % a.ic_slabs;
+  const int s_begin = (int)((long long)blockIdx.x * a.nstages / a.ksplits);
+  const int s_end = (int)((long long)(blockIdx.x + 1) * a.nstages / a.ksplits);
+  const int chunks = (a.KW + 3) / 4;
+  const int N = a.KH * 32;
+
+  if (tid == 0) {
+    for (int s = 0; s < TCW_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    mbar_fence_init();
+  }
+  if (warp == 4) tmem_alloc(tmem_slot, (uint32_t)a.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool failed = false;
+
+  if (warp == 4 && lane == 0) {
+    for (int s = s_begin; s < s_end; ++s) {
+      const uint32_t i = s - s_begin, st = i % TCW_STAGES, use = i / TCW_STAGES;
+      if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
+        failed = true;
+        break;
+      }
+      const int t0 = (s / a.groups_x) * TCW_ROWS, u0 = (s % a.groups_x) * 8;
+      uint8_t *p = smem + st * STAGE;
+      mbar_expect_tx(&full[st], STAGE);
+      tma_load_3d(p, &dy_hi, ocs * 32, u0 + a.pad_l - (a.KW - 1), t0, &full[st]);
+      tma_load_3d(p + DYB, &dy_lo, ocs * 32, u0 + a.pad_l - (a.KW - 1), t0, &full[st]);
+      tma_load_3d(p + 2 * DYB, &x_hi, ics * 32, u0, t0 - a.pad_t, &full[st]);
+      tma_load_3d(p + 2 * DYB + XB, &x_lo, ics * 32, u0, t0 - a.pad_t, &full[st]);
+    }
+  } else if (warp == 5 && lane == 0) {
+    const uint32_t idesc = umma_idesc_tf32_major(128, N, 1, 1);
+    uint32_t accumulate = 0;
+    for (int s = s_begin; s < s_end && !failed; ++s) {
+      const uint32_t i = s - s_begin, st = i % TCW_STAGES;
+      if (!mbar_wait_bounded(&full[st], (i / TCW_STAGES) & 1)) {
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t base = smem_u32(smem + st * STAGE);
+      for (int r = 0; r < TCW_ROWS; ++r) {
+        // B: X rows r .. r+KH-1 of this 8-column strip, one 32 x 8-pixel block per ky
+        const uint32_t xb = base + 2 * DYB + (uint32_t)r * 1024u;
+        const uint64_t bhi = umma_desc(xb, 1024, 512, 1);
+        const uint64_t blo = umma_desc(xb + XB, 1024, 512, 1);
+        for (int ch = 0; ch < chunks; ++ch) {
+          // A: dY pixels shifted by j = 4*ch .. 4*ch+3 columns (kx = KW-1-j), one block per shift
+          const uint32_t ab = base + (uint32_t)(r * 16 + ch * 4) * 128u;
+          const uint64_t ahi = umma_desc(ab, 128, 512, 1);
+          const uint64_t alo = umma_desc(ab + DYB, 128, 512, 1);
+          const uint32_t d = tmem_base + (uint32_t)(ch * N);
+          umma_tf32(d, alo, bhi, idesc, accumulate);
+          umma_tf32(d, ahi, blo, idesc, 1);
+          umma_tf32(d, ahi, bhi, idesc, 1);
+        }
+        accumulate = 1;
+      }
+      umma_commit(&empty[st]);
+    }
+    if (!failed) umma_commit(accum);
+  } else if (warp < 4) {
+    float *row = a.part + (size_t)blockIdx.x * a.row_stride;
+    const int oc = ocs * 32 + lane;
+    if (s_end > s_begin) {
+      if (!mbar_wait_bounded(accum, 0)) failed = true;
+      tc_fence_after();
+    }
+    if (!failed) {
+      for (int ch = 0; ch < chunks; ++ch) {
+        const int kx = a.KW - 1 - (ch * 4 + warp);
+        for (int c0 = 0; c0 < N; c0 += 32) {
+          float v[32];
+          if (s_end > s_begin) {
+            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(ch * N + c0), v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+          const int ky = c0 >> 5;
+          if (kx >= 0 && oc < a.OC) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int inc = ics * 32 + j;
+              if (inc < a.C) row[((size_t)(oc * a.C + inc) * a.KH + ky) * a.KW + kx] = v[j];
+            }
+          }
+        }
+      }
+    }
+  }
+  if (failed && a.err) atomicExch(a.err, 4);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
+}
+
+}  // namespace
+
+// ---- host side -----------------------------------------------------------------------------
+
+namespace {
+
+int pow2_at_least(int v) {
+  int p = 32;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+int pad16(int n) { return (n + 15) / 16 * 16; }
+
+// filter ring stages that fit beside the two halo buffers (0: does not fit)
+int conv_tc_ring(const b200_ctx *ctx, int KH, int Np) {
+  size_t HB = (size_t)TCV_HALO_W * (TCV_TILE_ROWS + KH - 1) * 128, FB = (size_t)Np * 128;
+  size_t fixed = 1024 + 4 * HB + 512;
+  if (ctx->smem_optin < fixed + 2 * 2 * FB) return 0;
+  size_t nf = (ctx->smem_optin - fixed) / (2 * FB);
+  return (int)(nf > 12 ? 12 : nf);
+}
+
+size_t conv_tc_smem(int KH, int Np, int nf) {
+  size_t HB = (size_t)TCV_HALO_W * (TCV_TILE_ROWS + KH - 1) * 128, FB = (size_t)Np * 128;
+  return 1024 + 4 * HB + (size_t)nf * 2 * FB + (8 + 2 * nf) * 8 + 16;
+}
+
+size_t dw_tc_smem(int KH) {
+  size_t st = 2 * (16 * TCW_ROWS * 128) + 2 * (8 * (TCW_ROWS + KH - 1) * 128);
+  return 1024 + TCW_STAGES * st + (2 * TCW_STAGES + 1) * 8 + 16;
+}
+
+int make_map_rows(CUtensorMap *m, const float *base, uint64_t rows, uint32_t box_rows) {
+  return make_map_2d(m, base, 32, rows, 32, box_rows);
+}
+
+int to_tall(b200_ctx *ctx, const float *src, int C, int H, int W, int Cp, int period, int B, float *dst,
+            float *bsum, int *blocks_out) {
+  int px = 16384 / (Cp + 1);
+  if (px > 256) px = 256;
+  int rb = px / W;
+  if (rb < 1) rb = 1;
+  if (rb > period) rb = period;
+  size_t smem = (size_t)rb * W * (Cp + 1) * sizeof(float);
+  if (smem > 48 * 1024)
+    B200_CUDA(cudaFuncSetAttribute(to_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int chunks = ceil_div(period, rb);
+  long long rows = (long long)B * period;
+  size_t one = (size_t)rows * W * Cp;
+  to_tall_kernel<<<B * chunks, 256, smem, ctx->stream>>>(src, C, H, W, Cp, period, rb, rows, dst, dst + one,
+                                                         bsum);
+  B200_LAUNCHED();
+  if (blocks_out) *blocks_out = B * chunks;
+  return 0;
+}
+
+int to_tall_blocks(int W, int Cp, int period, int B) {
+  int px = 16384 / (Cp + 1);
+  if (px > 256) px = 256;
+  int rb = px / W;
+  if (rb < 1) rb = 1;
+  if (rb > period) rb = period;
+  return B * ceil_div(period, rb);
+}
+
+// shared launcher of the forward and dX passes
+int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long rows, int period,
+                   const float *wt, int KH, int KW, int pad_t, int pad_l, int N, float *out, int OH, int OW,
+                   const float *bias, int act, int B) {
+  const int Np = pad16(N), slabs = Cp / 32, taps = KH * KW;
+  const int nf = conv_tc_ring(ctx, KH, Np);
+  B200_REQUIRE(nf >= 2, "tensor-core convolution: tiles do not fit shared memory (KH %d, N %d)", KH, N);
+  CUtensorMap in_hi, in_lo, f_hi, f_lo;
+  const size_t one = (size_t)rows * Win * Cp;
+  B200_TRY(make_map_3d(&in_hi, tall, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS + KH - 1,
+                       CU_TENSOR_MAP_SWIZZLE_128B));
+  B200_TRY(make_map_3d(&in_lo, tall + one, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS + KH - 1,
+                       CU_TENSOR_MAP_SWIZZLE_128B));
+  const size_t frows = (size_t)taps * slabs * Np;
+  B200_TRY(make_map_rows(&f_hi, wt, frows, Np));
+  B200_TRY(make_map_rows(&f_lo, wt + frows * 32, frows, Np));
+  TcConvArgs a;
+  a.out = out;
+  a.bias = bias;
+  a.err = ctx->dev_err;
+  a.B = B;
+  a.period = period;
+  a.OH = OH;
+  a.OW = OW;
+  a.N = N;
+  a.Np = Np;
+  a.slabs = slabs;
+  a.KH = KH;
+  a.KW = KW;
+  a.pad_t = pad_t;
+  a.pad_l = pad_l;
+  a.tiles_x = ceil_div(OW, TCV_TILE_COLS);
+  a.ntiles = a.tiles_x * (int)((rows + TCV_TILE_ROWS - 1) / TCV_TILE_ROWS);
+  a.act = act;
+  a.nf = nf;
+  a.acc_stride = (Np + 31) / 32 * 32;
+  a.tmem_cols = pow2_at_least(2 * a.acc_stride);
+  const size_t smem = conv_tc_smem(KH, Np, nf);
+  B200_CUDA(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int grid = a.ntiles < ctx->sm_count ? a.ntiles : ctx->sm_count;
+  conv_tc_kernel<<<grid, TCV_THREADS, smem, ctx->stream>>>(in_hi, in_lo, f_hi, f_lo, a);
+  B200_LAUNCHED();
+  return 0;
+}
+
+int filter_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, int Np, int slabs, int for_dx, float *wt) {
+  long long total = (long long)g.KH * g.KW * slabs * Np * 32;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  tc_filter_prep_kernel<<<blocks, 256, 0, ctx->stream>>>(W, g.tbl, g.C, g.OC, g.KH, g.KW, Np, slabs, for_dx,
+                                                         wt, wt + total);
+  B200_LAUNCHED();
+  return 0;
+}
+
+}  // namespace
+
+bool conv_tc_ok(const b200_ctx *ctx, const ConvGeom &g) {
+  if (g.SH != 1 || g.SW != 1 || g.DH != 1 || g.DW != 1) return false;
+  if (g.KH > 8 || g.KW > 8 || g.OC > 256 || g.C > 256) return false;
+  TallGeom t = tall_geom(g, 1);
+  if (g.pad_t < 0 || g.pad_l < 0 || t.pad_b < 0 || t.pad_r < 0) return false;
+  if (g.pad_t > g.KH - 1 || t.pad_b > g.KH - 1 || g.pad_l > g.KW - 1 || t.pad_r > g.KW - 1) return false;
+  if (g.WI > 256 || g.OW > 256) return false;
+  if (conv_tc_ring(ctx, g.KH, pad16(g.OC)) < 2 || conv_tc_ring(ctx, g.KH, pad16(g.C)) < 2) return false;
+  if (dw_tc_smem(g.KH) > ctx->smem_optin) return false;
+  size_t tall_smem = (size_t)(g.WI > g.OW ? g.WI : g.OW) * ((t.Cp > t.OCp ? t.Cp : t.OCp) + 1) * 4;
+  return tall_smem <= ctx->smem_optin;
+}
+
+ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo) {
+  ConvTcUse u = {false, false, false};
+  if (algo == 1 || algo == 2 || !conv_tc_ok(ctx, g)) return u;
+  if (algo != 3 && ctx->conv_tensor_cores == 0) return u;
+  if (algo == 3 || ctx->conv_tensor_cores >= 2) {
+    u.fwd = u.dx = u.dw = true;
+  } else {
+    // a pass pays off when the contracted channel count fills most of a 32-wide slab
+    u.fwd = g.C >= 16;
+    u.dx = g.OC >= 16;
+    u.dw = g.C >= 16 && g.OC >= 16;
+  }
+  if (algo != 3) {
+    if (const char *e = getenv("B200_CONV_TC")) {  // bit 0 forward, bit 1 dX, bit 2 dW
+      int m = atoi(e);
+      u.fwd = (m & 1) != 0;
+      u.dx = (m & 2) != 0;
+      u.dw = (m & 4) != 0;
+    }
+  }
+  return u;
+}
+
+// floats of the tall split form (hi + lo) of the input (which = 0) or of dY (which = 1)
+size_t conv_tc_tall_floats(const ConvGeom &g, int B, int which) {
+  TallGeom t = tall_geom(g, B);
+  if (which == 0) return (size_t)2 * t.rows * g.WI * t.Cp;
+  return (size_t)2 * B * dy_period(g) * g.OW * t.OCp;
+}
+
+size_t conv_tc_filter_floats(const ConvGeom &g, int for_dx) {
+  TallGeom t = tall_geom(g, 1);
+  int Np = for_dx ? pad16(g.C) : pad16(g.OC), slabs = (for_dx ? t.OCp : t.Cp) / 32;
+  return (size_t)2 * g.KH * g.KW * slabs * Np * 32;
+}
+
+// rows of per-block bias-gradient partials the dY conversion writes
+int conv_tc_bsum_rows(const ConvGeom &g, int B) {
+  TallGeom t = tall_geom(g, 1);
+  return to_tall_blocks(g.OW, t.OCp, dy_period(g), B);
+}
+
+int conv_tc_dw_splits(const b200_ctx *ctx, const ConvGeom &g, int B) {
+  TallGeom t = tall_geom(g, B);
+  int units = (t.Cp / 32) * (t.OCp / 32);
+  long long nstages = (t.rows + TCW_ROWS - 1) / TCW_ROWS * ceil_div(g.WI, 8);
+  int k = ctx->sm_count / units;
+  if (k < 1) k = 1;
+  if (k > nstages) k = (int)nstages;
+  return k;
+}
+
+// floats of scratch of the dW pass: the partial rows
+size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B) {
+  return (size_t)conv_tc_dw_splits(ctx, g, B) * conv_weight_len(g);
+}
+
+int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs) {
+  TallGeom t = tall_geom(g, B);
+  return to_tall(ctx, in, g.C, g.HI, g.WI, t.Cp, t.period, B, xs, nullptr, nullptr);
+}
+
+// dY -> tall split form; bsum (conv_tc_bsum_rows x OC floats, may be nullptr) receives the
+// per-block channel sums whose in-order total is the bias gradient
+int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, float *dys, float *bsum) {
+  TallGeom t = tall_geom(g, B);
+  return to_tall(ctx, dout, g.OC, g.OH, g.OW, t.OCp, dy_period(g), B, dys, bsum, nullptr);
+}
+
+int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,
+                float *out, int B, int act, float *wt) {
+  TallGeom t = tall_geom(g, B);
+  B200_TRY(filter_prep(ctx, g, W, pad16(g.OC), t.Cp / 32, 0, wt));
+  return launch_conv_tc(ctx, xs, t.Cp, g.WI, t.rows, t.period, wt, g.KH, g.KW, g.pad_t, g.pad_l, g.OC, out,
+                        g.OH, g.OW, g.has_bias ? bias : nullptr, act, B);
+}
+
+int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *W, float *din, int B,
+               float *wt) {
+  TallGeom t = tall_geom(g, B);
+  const int period = dy_period(g);
+  B200_TRY(filter_prep(ctx, g, W, pad16(g.C), t.OCp / 32, 1, wt));
+  return launch_conv_tc(ctx, dys, t.OCp, g.OW, (long long)B * period, period, wt, g.KH, g.KW,
+                        g.KH - 1 - g.pad_t, g.KW - 1 - g.pad_l, g.C, din, g.HI, g.WI, nullptr, B200_ACT_NONE,
+                        B);
+}
+
+// partial weight gradients: *splits rows of conv_weight_len floats in `part`
+int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *dys, int B, float *part,
+               int *splits) {
+  TallGeom t = tall_geom(g, B);
+  B200_REQUIRE(dy_period(g) == t.period, "tensor-core dW: input and gradient row periods differ");
+  CUtensorMap dy_hi, dy_lo, x_hi, x_lo;
+  const size_t one_dy = (size_t)t.rows * g.OW * t.OCp, one_x = (size_t)t.rows * g.WI * t.Cp;
+  const CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+  B200_TRY(make_map_3d(&dy_hi, dys, t.OCp, g.OW, t.rows, 32, 16, TCW_ROWS, swz));
+  B200_TRY(make_map_3d(&dy_lo, dys + one_dy, t.OCp, g.OW, t.rows, 32, 16, TCW_ROWS, swz));
+  B200_TRY(make_map_3d(&x_hi, xs, t.Cp, g.WI, t.rows, 32, 8, TCW_ROWS + g.KH - 1, swz));
+  B200_TRY(make_map_3d(&x_lo, xs + one_x, t.Cp, g.WI, t.rows, 32, 8, TCW_ROWS + g.KH - 1, swz));
+  TcDwArgs a;
+  a.part = part;
+  a.err = ctx->dev_err;
+  a.KH = g.KH;
+  a.KW = g.KW;
+  a.pad_t = g.pad_t;
+  a.pad_l = g.pad_l;
+  a.C = g.C;
+  a.OC = g.OC;
+  a.groups_x = ceil_div(g.WI, 8);
+  a.nstages = (int)((t.rows + TCW_ROWS - 1) / TCW_ROWS) * a.groups_x;
+  a.ic_slabs = t.Cp / 32;
+  a.ksplits = conv_tc_dw_splits(ctx, g, B);
+  a.tmem_cols = pow2_at_least(((g.KW + 3) / 4) * g.KH * 32);
+  a.row_stride = (long long)conv_weight_len(g);
+  const size_t smem = dw_tc_smem(g.KH);
+  B200_CUDA(cudaFuncSetAttribute(conv_dw_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(a.ksplits, a.ic_slabs * (t.OCp / 32));
+  conv_dw_tc_kernel<<<grid, TCV_THREADS, smem, ctx->stream>>>(dy_hi, dy_lo, x_hi, x_lo, a);
+  B200_LAUNCHED();
+  *splits = a.ksplits;
+  return 0;
+}
+
+}  // namespace b200

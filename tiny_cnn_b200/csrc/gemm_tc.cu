@@ -19,10 +19,7 @@
 //                        activation / accumulate, stores to D
 // No multicast is used anywhere; every wait is bounded and a timeout sets the
 // context's error word, releases TMEM and returns.
-#include <cuda.h>
-
-#include "common.cuh"
-#include "device_utils.cuh"
+#include "tc_utils.cuh"
 
 namespace b200 {
 
@@ -32,11 +29,6 @@ constexpr int TC_STAGES = 3;
 constexpr int TC_THREADS = 192;
 
 // ---- operand preparation -----------------------------------------------------
-
-__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
-  hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);  // keep the 10 TF32 mantissa bits
-  lo = x - hi;                                              // exact in fp32
-}
 
 // hi/lo[r][c] = split(src[r*ld + c]) for c < cols, 0 for cols <= c < pitch
 __global__ void tc_split_kernel(const float *__restrict__ src, int rows, int cols, long long ld,
@@ -74,78 +66,6 @@ __global__ void tc_split_transpose_kernel(const float *__restrict__ src, int row
       lo[(long long)c * pitch + r] = l;
     }
   }
-}
-
-// ---- tcgen05 / TMA wrappers ------------------------------------------------------
-
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int c0, int c1,
-                                            uint64_t *bar) {
-  asm volatile(
-    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
-      smem_u32(smem_dst)),
-    "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-    : "memory");
-}
-
-// shared-memory matrix descriptor: K-major tile whose rows are 128 bytes, 128-byte
-// swizzle, groups of 8 rows 1024 bytes apart
-__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);  // start address
-  d |= (uint64_t)1 << 16;                       // leading byte offset (unused for this layout)
-  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                       // 128-byte swizzle
-  return d;
-}
-
-// instruction descriptor: TF32 x TF32 -> F32, both operands K-major, M x N tile
-__host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N) {
-  return (1u << 4)                    // D format F32
-         | (2u << 7)                  // A format TF32
-         | (2u << 10)                 // B format TF32
-         | ((uint32_t)(N >> 3) << 17) // N / 8
-         | ((uint32_t)(M >> 4) << 24); // M / 16
-}
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-    "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-    " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-    "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-    : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
-                 smem_u32(bar))
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
-  uint32_t r[32];
-  asm volatile(
-    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-      "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-      "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-      "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-    : "r"(taddr)
-    : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 }
 
 struct TcArgs {
@@ -275,23 +195,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 }
 
 // ---- host side ---------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
 
 // 2D fp32 tensor [rows][pitch]; box = 32 floats x box_rows, 128-byte swizzle, zero fill
 static int make_map(CUtensorMap *m, const float *base, int rows, int cols, int pitch, int box_rows) {

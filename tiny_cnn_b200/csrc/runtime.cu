@@ -213,6 +213,11 @@ int b200_ctx_set_option(b200_ctx *ctx, const char *name, int value) {
     ctx->fc_tensor_cores = value;
     return 0;
   }
+  if (strcmp(name, "conv_tensor_cores") == 0) {
+    B200_REQUIRE(value >= 0 && value <= 2, "conv_tensor_cores must be 0, 1 or 2");
+    ctx->conv_tensor_cores = value;
+    return 0;
+  }
   B200_REQUIRE(false, "ctx_set_option: unknown option '%s'", name);
   return 0;
 }
