@@ -59,8 +59,9 @@ def tiled_applies(c):
 
 # --------------------------------------------------------------------------- convolution
 def tensor_core_applies(c):
+    widest = (max(c["c"], c["oc"]) + 15) // 16 * 16
     return (c.get("sw", 1) == 1 and c.get("sh", 1) == 1 and c.get("dw", 1) == 1 and c.get("dh", 1) == 1
-            and c["kw"] <= 8 and c["kh"] <= 8)
+            and c["kw"] <= 8 and c["kh"] <= 8 and c["kh"] * widest <= 512)
 
 
 @pytest.mark.parametrize("algo", [1, 2, 3])
@@ -70,7 +71,7 @@ def test_conv_fwd_bwd(ctx, oracle, gold, name, algo):
     if algo == 2 and not tiled_applies(c):
         pytest.skip("tiled kernels take stride 1, dilation 1, 3x3/5x5 only")
     if algo == 3 and not tensor_core_applies(c):
-        pytest.skip("tensor-core kernels take stride 1, dilation 1, windows up to 8x8 only")
+        pytest.skip("tensor-core kernels take stride 1, dilation 1, windows up to 8x8, window height x channels <= 512")
     d = conv_desc(c, algo=algo)
     x, W, b, dy = gen_conv_inputs(c, d)
     y_ref, dx_ref, dW_ref, db_ref = orc_conv(oracle, d, x, W, b, dy, per_sample=0)

@@ -34,7 +34,7 @@ int conv_fwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
   if (tc.fwd) {
     size_t n_x = align_up(conv_tc_tall_floats(g, batch, 0), 64);
     void *scratch = nullptr;
-    B200_TRY(ctx_scratch(ctx, (n_x + conv_tc_filter_floats(g, 0)) * sizeof(float), &scratch));
+    B200_TRY(ctx_scratch(ctx, (n_x + conv_tc_filter_floats(ctx, g, 0)) * sizeof(float), &scratch));
     float *xs = static_cast<float *>(scratch);
     B200_TRY(conv_tc_tall_x(ctx, g, in, batch, xs));
     return conv_tc_fwd(ctx, g, xs, W, bias, out, batch, B200_ACT_NONE, xs + n_x);
@@ -80,7 +80,7 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
   int bs_rows = tc.dw && g.has_bias ? conv_tc_bsum_rows(g, batch) : 0;
   size_t n_bs = align_up((size_t)bs_rows * g.OC, 64);
   size_t n_xs = tc.dw ? align_up(conv_tc_tall_floats(g, batch, 0), 64) : 0;
-  size_t n_wdx = tc.dx ? align_up(conv_tc_filter_floats(g, 1), 64) : 0;
+  size_t n_wdx = tc.dx ? align_up(conv_tc_filter_floats(ctx, g, 1), 64) : 0;
   size_t n_part = tc.dw ? align_up(conv_tc_dw_floats(ctx, g, batch), 64) : 0;
   size_t n_tdx = (din && !tc.dx && tiled) ? align_up(conv_tiled_dx_scratch(g), 64) : 0;
   size_t n_tdw = (!tc.dw && tiled) ? conv_tiled_dw_scratch(ctx, g, batch) : 0;
@@ -106,7 +106,7 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
     int splits = 0;
     B200_TRY(conv_tc_dw(ctx, g, xs, dys, batch, part, &splits));
     B200_TRY(merge_rows(ctx, part, splits, lenW, dW, lenW, accumulate, &g));
-    if (g.has_bias) B200_TRY(merge_rows(ctx, bs, bs_rows, g.OC, db, g.OC, accumulate, nullptr));
+    if (g.has_bias) B200_TRY(conv_tc_bias_grad(ctx, g, bs, batch, db, accumulate));
     return 0;
   }
   if (!tiled) return conv_general_dw(ctx, g, in, dout, dW, db, accumulate, batch);

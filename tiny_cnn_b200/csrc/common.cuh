@@ -92,8 +92,8 @@ struct b200_ctx {
 
   // fully-connected GEMMs on the tensor cores (3xTF32): 0 never, 1 when large, 2 whenever legal
   int fc_tensor_cores = 1;
-  // convolutions on the tensor cores: 0 never, 1 for layers with at least 16 channels on the
-  // contracted side, 2 whenever the geometry allows
+  // convolutions on the tensor cores: 0 never, 1 for layers with at least 16 channels on
+  // both sides, 2 whenever the geometry allows
   int conv_tensor_cores = 1;
 
   // tile shapes already chosen, keyed by the problem's dimensions
@@ -166,8 +166,9 @@ struct ConvTcUse {
 };
 ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo);
 size_t conv_tc_tall_floats(const ConvGeom &g, int B, int which);  // 0: input, 1: dY
-size_t conv_tc_filter_floats(const ConvGeom &g, int for_dx);
+size_t conv_tc_filter_floats(const b200_ctx *ctx, const ConvGeom &g, int for_dx);
 int conv_tc_bsum_rows(const ConvGeom &g, int B);
+int conv_tc_bias_grad(b200_ctx *ctx, const ConvGeom &g, const float *bsum, int B, float *db, int accumulate);
 size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B);
 int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs);
 int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, float *dys, float *bsum);

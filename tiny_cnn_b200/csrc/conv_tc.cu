@@ -74,65 +74,84 @@ int dy_period(const ConvGeom &g) {
 // One block converts `rb` tall rows of one image: src[b][c][y][x] -> hi/lo[t][x][c],
 // zero for padded channels and for the rows between images.  With `bsum` the block also
 // writes the per-channel sum of what it read (bias gradient partials, fixed order).
+// Shared tile [c][pixel] with an odd pitch: scalar, coalesced loads along x; 16-byte
+// stores of four channels of one pixel.
 __global__ void __launch_bounds__(256) to_tall_kernel(const float *__restrict__ src, int C, int H, int W,
-                                                      int Cp, int period, int rb, long long rows_total,
+                                                      int Cp, int period, int rb, int pitch,
                                                       float *__restrict__ hi, float *__restrict__ lo,
                                                       float *__restrict__ bsum) {
-  extern __shared__ float tile[];  // [rb*W][Cp+1]
+  extern __shared__ float tile[];  // [C][pitch]
   const int chunks = (period + rb - 1) / rb;
   const int b = blockIdx.x / chunks, r0 = (blockIdx.x % chunks) * rb;
   const int nr = min(rb, period - r0);
-  const int npx = nr * W, pitch = Cp + 1;
-  const int valid_rows = max(0, min(nr, H - r0));
-  for (int i = threadIdx.x; i < C * npx; i += blockDim.x) {
-    int c = i / npx, p = i % npx;
-    int ry = p / W;
-    float v = 0.f;
-    if (ry < valid_rows) v = src[((size_t)(b * C + c) * H + r0) * W + p];
-    tile[p * pitch + c] = v;
+  const int npx = nr * W;
+  const int valid_px = max(0, min(nr, H - r0)) * W;
+  const float *img = src + ((size_t)b * C * H + r0) * W;
+  const size_t plane = (size_t)H * W;
+  const int total = C * npx;
+#pragma unroll 8
+  for (int i = threadIdx.x; i < total; i += 256) {
+    int c = i / npx, p = i - c * npx;
+    tile[c * pitch + p] = p < valid_px ? img[c * plane + p] : 0.f;
   }
   __syncthreads();
   const size_t base = ((size_t)b * period + r0) * W * Cp;
-  for (int i = threadIdx.x; i < npx * Cp; i += blockDim.x) {
-    int p = i / Cp, c = i % Cp;
-    float h = 0.f, l = 0.f;
-    if (c < C) split_tf32_rn(tile[p * pitch + c], h, l);
-    hi[base + i] = h;
-    lo[base + i] = l;
+  const int Cq = Cp >> 2, total2 = npx * Cq;
+  float4 *hi4 = reinterpret_cast<float4 *>(hi + base), *lo4 = reinterpret_cast<float4 *>(lo + base);
+#pragma unroll 4
+  for (int i = threadIdx.x; i < total2; i += 256) {
+    int p = i / Cq, c = (i - p * Cq) * 4;
+    float h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      h[j] = l[j] = 0.f;
+      if (c + j < C) split_tf32_rn(tile[(c + j) * pitch + p], h[j], l[j]);
+    }
+    hi4[i] = make_float4(h[0], h[1], h[2], h[3]);
+    lo4[i] = make_float4(l[0], l[1], l[2], l[3]);
   }
-  if (bsum != nullptr && threadIdx.x < C) {
-    float s = 0.f;
-    for (int p = 0; p < valid_rows * W; ++p) s += tile[p * pitch + threadIdx.x];
-    bsum[(size_t)blockIdx.x * C + threadIdx.x] = s;
+  if (bsum != nullptr) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c = warp; c < C; c += 8) {
+      float s = 0.f;
+      for (int p = lane; p < valid_px; p += 32) s += tile[c * pitch + p];
+      s = warp_sum(s);
+      if (lane == 0) bsum[(size_t)blockIdx.x * C + c] = s;
+    }
   }
 }
 
 // ---- filter matrices ----------------------------------------------------------------------
 
-// Forward: F[tap][slab][n][k] = W[o = n][inc = slab*32 + k][ky][kx]            (tap = ky*KW + kx)
-// dX:      F[tap][slab][n][k] = W[o = slab*32 + k][inc = n][KH-1-ky][KW-1-kx]
-// n < Np rows of 32 floats; zero beyond the real channels and for unconnected pairs.
+// One tile per (slab, kx, group): rows n = ky*gs + j (j < gs output channels of the group),
+// 32 floats (the slab's contracted channels) each.
+// Forward: F[slab][kx][grp][ky][j][k] = W[o = grp*gs + j][inc = slab*32 + k][ky][kx]
+// dX:      F[slab][kx][grp][ky][j][k] = W[o = slab*32 + k][inc = grp*gs + j][KH-1-ky][KW-1-kx]
+// zero beyond the real channels and for unconnected pairs.
 __global__ void tc_filter_prep_kernel(const float *__restrict__ W, const uint8_t *__restrict__ tbl, int C,
-                                      int OC, int KH, int KW, int Np, int slabs, int for_dx,
+                                      int OC, int KH, int KW, int gs, int groups, int slabs, int for_dx,
                                       float *__restrict__ hi, float *__restrict__ lo) {
-  const long long total = (long long)KH * KW * slabs * Np * 32;
+  const long long total = (long long)slabs * KW * groups * KH * gs * 32;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     int k = (int)(i % 32);
     long long r = i / 32;
-    int n = (int)(r % Np);
-    r /= Np;
-    int slab = (int)(r % slabs);
-    int tap = (int)(r / slabs);
-    int ky = tap / KW, kx = tap % KW;
+    int j = (int)(r % gs);
+    r /= gs;
+    int ky = (int)(r % KH);
+    r /= KH;
+    int grp = (int)(r % groups);
+    r /= groups;
+    int kx = (int)(r % KW);
+    int slab = (int)(r / KW);
     int o, inc;
     if (for_dx) {
       o = slab * 32 + k;
-      inc = n;
+      inc = grp * gs + j;
       ky = KH - 1 - ky;
       kx = KW - 1 - kx;
     } else {
-      o = n;
+      o = grp * gs + j;
       inc = slab * 32 + k;
     }
     float h = 0.f, l = 0.f;
@@ -145,23 +164,35 @@ __global__ void tc_filter_prep_kernel(const float *__restrict__ W, const uint8_t
 
 }  // namespace
 
-// ---- forward / dX: implicit GEMM over a haloed pixel tile ----------------------------------
+// ---- forward / dX: implicit GEMM with the window rows stacked along N -------------------------
+//
+// For a tile of 16 tall input rows r and 8 columns x the tensor cores compute
+//   D[(r, x)][(ky, o)] = sum over kx, c of  X[r][x + kx - pad_l][c] * W[o][c][ky][kx]
+// (M = 128 pixels, N = KH * channels of the group, K = 32 channels per kx step; the kx shift is a
+// row offset into the haloed tile in shared memory), and the epilogue adds the KH row-shifted
+// column blocks:  out[t][x][o] = sum over ky of D[(t + ky - pad_t, x)][(ky, o)], which yields
+// 16 - (KH-1) output rows per tile.  Stacking ky along N makes every MMA instruction KH times
+// wider; an instruction narrower than about 128 columns runs at a fixed cost.
 
 namespace {
+
+constexpr int TCV_EPI_FLOATS = 2 * 128 * 16;  // row exchange buffer of the epilogue (two halves)
 
 struct TcConvArgs {
   float *out;          // [B][N][OH][OW]
   const float *bias;   // N values or nullptr
   int *err;
   int B, period;       // images, tall rows per image (input and output share the row index)
-  int OH, OW, N, Np;   // output extent, real / padded output channels
+  int OH, OW, N;       // output extent and channels
   int slabs;           // 32-channel slabs of the input
+  int groups, gs;      // output-channel groups, channels per group (multiple of 16)
   int KH, KW, pad_t, pad_l;
   int tiles_x, ntiles;
   int act;
+  int nh;              // haloed-tile buffers (1 or 2)
   int nf;              // filter ring stages
-  int acc_stride;      // TMEM columns per accumulator (multiple of 32)
-  int tmem_cols;       // allocated columns (power of two >= 2*acc_stride)
+  int nb;              // accumulator buffers in tensor memory (1 or 2)
+  int tmem_cols;       // allocated columns (power of two >= nb * groups * KH * gs)
 };
 
 __global__ void __launch_bounds__(TCV_THREADS, 1)
@@ -170,11 +201,14 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
                  const TcConvArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const uint32_t HB = TCV_HALO_W * (TCV_TILE_ROWS + a.KH - 1) * 128u;  // one halo tile (hi or lo)
-  const uint32_t FB = (uint32_t)a.Np * 128u;                           // one filter tile (hi or lo)
-  uint8_t *halo = smem;             // [2][hi | lo]
-  uint8_t *filt = smem + 4 * HB;    // [nf][hi | lo]
-  uint64_t *halo_full = reinterpret_cast<uint64_t *>(filt + (size_t)a.nf * 2 * FB);
+  constexpr uint32_t HB = TCV_HALO_W * TCV_TILE_ROWS * 128u;  // one haloed tile (hi or lo): 32 KiB
+  const int Ng = a.KH * a.gs;                                 // MMA width
+  const uint32_t FB = (uint32_t)Ng * 128u;                    // one filter tile (hi or lo)
+  const int CB = a.groups * Ng;                               // accumulator columns per buffer
+  uint8_t *halo = smem;                                       // [nh][hi | lo]
+  uint8_t *filt = halo + (size_t)a.nh * 2 * HB;               // [nf][hi | lo]
+  float *xch = reinterpret_cast<float *>(filt + (size_t)a.nf * 2 * FB);
+  uint64_t *halo_full = reinterpret_cast<uint64_t *>(xch + TCV_EPI_FLOATS);
   uint64_t *halo_empty = halo_full + 2;
   uint64_t *acc_full = halo_empty + 2;
   uint64_t *acc_empty = acc_full + 2;
@@ -201,32 +235,33 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int taps = a.KH * a.KW;
+  const int TR = TCV_TILE_ROWS - (a.KH - 1);  // output rows per tile
   bool failed = false;
 
   if (warp == 4 && lane == 0) {
     // ---- TMA producer -----------------------------------------------------------------
     uint32_t u = 0, f = 0;
     for (int tile = blockIdx.x; tile < a.ntiles && !failed; tile += gridDim.x) {
-      const int x0 = (tile % a.tiles_x) * TCV_TILE_COLS, t0 = (tile / a.tiles_x) * TCV_TILE_ROWS;
+      const int x0 = (tile % a.tiles_x) * TCV_TILE_COLS, r0 = (tile / a.tiles_x) * TR - a.pad_t;
       for (int slab = 0; slab < a.slabs && !failed; ++slab, ++u) {
-        const uint32_t hb = u & 1, use = u >> 1;
+        const uint32_t hb = u % a.nh, use = u / a.nh;
         if (use > 0 && !mbar_wait_bounded(&halo_empty[hb], (use - 1) & 1)) {
           failed = true;
           break;
         }
-        uint8_t *h = halo + hb * 2 * HB;
+        uint8_t *h = halo + (size_t)hb * 2 * HB;
         mbar_expect_tx(&halo_full[hb], 2 * HB);
-        tma_load_3d(h, &in_hi, slab * 32, x0 - a.pad_l, t0 - a.pad_t, &halo_full[hb]);
-        tma_load_3d(h + HB, &in_lo, slab * 32, x0 - a.pad_l, t0 - a.pad_t, &halo_full[hb]);
-        for (int tap = 0; tap < taps; ++tap, ++f) {
+        tma_load_3d(h, &in_hi, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
+        tma_load_3d(h + HB, &in_lo, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
+        const int nst = a.KW * a.groups;
+        for (int s = 0; s < nst; ++s, ++f) {
           const uint32_t fs = f % a.nf, fuse = f / a.nf;
           if (fuse > 0 && !mbar_wait_bounded(&filt_empty[fs], (fuse - 1) & 1)) {
             failed = true;
             break;
           }
           uint8_t *ft = filt + (size_t)fs * 2 * FB;
-          const int row = (tap * a.slabs + slab) * a.Np;
+          const int row = (slab * nst + s) * Ng;
           mbar_expect_tx(&filt_full[fs], 2 * FB);
           tma_load_2d(ft, &f_hi, 0, row, &filt_full[fs]);
           tma_load_2d(ft + FB, &f_lo, 0, row, &filt_full[fs]);
@@ -235,81 +270,121 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     }
   } else if (warp == 5 && lane == 0) {
     // ---- MMA issuer -----------------------------------------------------------------------
-    const uint32_t idesc = umma_idesc_tf32(128, a.Np);
+    const uint32_t idesc = umma_idesc_tf32(128, Ng);
     uint32_t u = 0, f = 0, it = 0;
     for (int tile = blockIdx.x; tile < a.ntiles && !failed; tile += gridDim.x, ++it) {
-      const uint32_t ab = it & 1, ause = it >> 1;
+      const uint32_t ab = it % a.nb, ause = it / a.nb;
       if (ause > 0 && !mbar_wait_bounded(&acc_empty[ab], (ause - 1) & 1)) {
         failed = true;
         break;
       }
       tc_fence_after();
-      const uint32_t tmem_d = tmem_base + ab * (uint32_t)a.acc_stride;
-      uint32_t accumulate = 0;
+      const uint32_t tmem_d = tmem_base + ab * (uint32_t)CB;
       for (int slab = 0; slab < a.slabs && !failed; ++slab, ++u) {
-        const uint32_t hb = u & 1;
-        if (!mbar_wait_bounded(&halo_full[hb], (u >> 1) & 1)) {
+        const uint32_t hb = u % a.nh;
+        if (!mbar_wait_bounded(&halo_full[hb], (u / a.nh) & 1)) {
           failed = true;
           break;
         }
         tc_fence_after();
-        const uint32_t hbase = smem_u32(halo + hb * 2 * HB);
-        for (int tap = 0; tap < taps; ++tap, ++f) {
-          const uint32_t fs = f % a.nf;
-          if (!mbar_wait_bounded(&filt_full[fs], (f / a.nf) & 1)) {
-            failed = true;
-            break;
-          }
-          tc_fence_after();
-          const int ky = tap / a.KW, kx = tap - ky * a.KW;
-          // the tap's A operand: the halo tile addressed (ky, kx) pixels further on
-          const uint32_t abase = hbase + (uint32_t)(ky * TCV_HALO_W + kx) * 128u;
-          const uint32_t bbase = smem_u32(filt + (size_t)fs * 2 * FB);
+        const uint32_t hbase = smem_u32(halo + (size_t)hb * 2 * HB);
+        for (int kx = 0; kx < a.KW && !failed; ++kx) {
+          for (int grp = 0; grp < a.groups; ++grp, ++f) {
+            const uint32_t fs = f % a.nf;
+            if (!mbar_wait_bounded(&filt_full[fs], (f / a.nf) & 1)) {
+              failed = true;
+              break;
+            }
+            tc_fence_after();
+            // A: the haloed tile addressed kx pixels (rows of 128 bytes) further on
+            const uint32_t abase = hbase + (uint32_t)kx * 128u;
+            const uint32_t bbase = smem_u32(filt + (size_t)fs * 2 * FB);
+            const uint32_t d = tmem_d + (uint32_t)(grp * Ng);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            const uint64_t ahi = umma_desc(abase + k4 * 32, 16, TCV_HALO_W * 128, 2);
-            const uint64_t alo = umma_desc(abase + HB + k4 * 32, 16, TCV_HALO_W * 128, 2);
-            const uint64_t bhi = umma_desc(bbase + k4 * 32, 16, 1024, 2);
-            const uint64_t blo = umma_desc(bbase + FB + k4 * 32, 16, 1024, 2);
-            umma_tf32(tmem_d, alo, bhi, idesc, accumulate);
-            umma_tf32(tmem_d, ahi, blo, idesc, 1);
-            umma_tf32(tmem_d, ahi, bhi, idesc, 1);
-            accumulate = 1;
+            for (int k4 = 0; k4 < 4; ++k4) {
+              const uint64_t ahi = umma_desc(abase + k4 * 32, 16, TCV_HALO_W * 128, 2);
+              const uint64_t alo = umma_desc(abase + HB + k4 * 32, 16, TCV_HALO_W * 128, 2);
+              const uint64_t bhi = umma_desc(bbase + k4 * 32, 16, 1024, 2);
+              const uint64_t blo = umma_desc(bbase + FB + k4 * 32, 16, 1024, 2);
+              umma_tf32(d, alo, bhi, idesc, (slab | kx | k4) != 0);
+              umma_tf32(d, ahi, blo, idesc, 1);
+              umma_tf32(d, ahi, bhi, idesc, 1);
+            }
+            umma_commit(&filt_empty[fs]);
           }
-          umma_commit(&filt_empty[fs]);
         }
         if (!failed) umma_commit(&halo_empty[hb]);
       }
       if (!failed) umma_commit(&acc_full[ab]);
     }
   } else if (warp < 4) {
-    // ---- epilogue ------------------------------------------------------------------------
+    // ---- epilogue: sum the KH row-shifted column blocks, bias, activation, store -------------
     uint32_t it = 0;
-    const int m = warp * 32 + lane, dt = m >> 3, dx = m & 7;
+    const int m = warp * 32 + lane, r = m >> 3, dx = m & 7;
+    const size_t plane = (size_t)a.OH * a.OW;
+    uint32_t half = 0;  // exchange buffer half in use
     for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x, ++it) {
-      const uint32_t ab = it & 1;
-      if (!mbar_wait_bounded(&acc_full[ab], (it >> 1) & 1)) {
-        failed = true;
-        break;
+      const uint32_t ab = it % a.nb;
+      if (!mbar_wait_bounded(&acc_full[ab], (it / a.nb) & 1)) failed = true;
+      // every epilogue thread takes part in the named barriers below, so leave together
+      {
+        int any;
+        asm volatile(
+          "{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n bar.red.or.pred q, 1, 128, p;\n selp.u32 %0, 1, 0, q;\n}\n"
+          : "=r"(any)
+          : "r"((int)failed)
+          : "memory");
+        if (any) {
+          failed = true;
+          break;
+        }
       }
       tc_fence_after();
       const int x = (tile % a.tiles_x) * TCV_TILE_COLS + dx;
-      const int t = (tile / a.tiles_x) * TCV_TILE_ROWS + dt;
+      const int t = (tile / a.tiles_x) * TR + r;  // output tall row this thread owns (if r < TR)
       const int b = t / a.period, y = t - b * a.period;
-      const bool valid = b < a.B && y < a.OH && x < a.OW;
+      const bool valid = r < TR && b < a.B && y < a.OH && x < a.OW;
       float *obase = a.out + ((size_t)b * a.N * a.OH + y) * a.OW + x;
-      const size_t plane = (size_t)a.OH * a.OW;
-      for (int c0 = 0; c0 < a.Np; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + ab * (uint32_t)a.acc_stride + (uint32_t)c0, v);
-        if (valid) {
+      const uint32_t tbase = tmem_base + ((uint32_t)(warp * 32) << 16) + ab * (uint32_t)CB;
+      for (int grp = 0; grp < a.groups; ++grp) {
+        for (int c0 = 0; c0 < a.gs; c0 += 16) {
+          float acc[16];
+          tmem_ld16(tbase + (uint32_t)(grp * Ng + c0), acc);
+          for (int ky = 1; ky < a.KH; ++ky) {
+            float v[16];
+            tmem_ld16(tbase + (uint32_t)(grp * Ng + ky * a.gs + c0), v);
+            // hand the block to the thread ky rows up: 64-byte rows, 16-byte chunks swizzled
+            float4 *row = reinterpret_cast<float4 *>(xch + half * (TCV_EPI_FLOATS / 2) + m * 16);
+            const int sw = (m >> 1) & 3;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int oc = c0 + j;
-            if (oc < a.N) {
-              float r = v[j];
-              if (a.bias) r += a.bias[oc];
-              obase[oc * plane] = apply_act(r, a.act);
+            for (int q = 0; q < 4; ++q)
+              row[q ^ sw] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            const int src = m + 8 * ky;
+            if (src < 128) {
+              const float4 *srow =
+                reinterpret_cast<const float4 *>(xch + half * (TCV_EPI_FLOATS / 2) + src * 16);
+              const int ssw = (src >> 1) & 3;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float4 w = srow[q ^ ssw];
+                acc[4 * q] += w.x;
+                acc[4 * q + 1] += w.y;
+                acc[4 * q + 2] += w.z;
+                acc[4 * q + 3] += w.w;
+              }
+            }
+            half ^= 1;
+          }
+          if (valid) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int oc = grp * a.gs + c0 + j;
+              if (oc < a.N) {
+                float res = acc[j];
+                if (a.bias) res += a.bias[oc];
+                obase[oc * plane] = apply_act(res, a.act);
+              }
             }
           }
         }
@@ -479,18 +554,38 @@ int pow2_at_least(int v) {
 
 int pad16(int n) { return (n + 15) / 16 * 16; }
 
-// filter ring stages that fit beside the two halo buffers (0: does not fit)
-int conv_tc_ring(const b200_ctx *ctx, int KH, int Np) {
-  size_t HB = (size_t)TCV_HALO_W * (TCV_TILE_ROWS + KH - 1) * 128, FB = (size_t)Np * 128;
-  size_t fixed = 1024 + 4 * HB + 512;
-  if (ctx->smem_optin < fixed + 2 * 2 * FB) return 0;
-  size_t nf = (ctx->smem_optin - fixed) / (2 * FB);
-  return (int)(nf > 12 ? 12 : nf);
-}
+// tiling of the forward / dX kernel for a window height and an output channel count
+struct TcPlan {
+  bool ok;
+  int groups, gs;   // output-channel groups and channels per group
+  int nh, nf, nb;   // haloed-tile buffers, filter ring stages, accumulator buffers
+  int tmem_cols;
+  size_t smem;
+};
 
-size_t conv_tc_smem(int KH, int Np, int nf) {
-  size_t HB = (size_t)TCV_HALO_W * (TCV_TILE_ROWS + KH - 1) * 128, FB = (size_t)Np * 128;
-  return 1024 + 4 * HB + (size_t)nf * 2 * FB + (8 + 2 * nf) * 8 + 16;
+TcPlan conv_tc_plan(const b200_ctx *ctx, int KH, int n_out) {
+  TcPlan p = {};
+  const int c16 = pad16(n_out);
+  const int gmax = 256 / KH / 16 * 16;
+  if (gmax < 16) return p;
+  p.groups = (c16 + gmax - 1) / gmax;
+  p.gs = pad16((c16 + p.groups - 1) / p.groups);
+  const int CB = p.groups * KH * p.gs;
+  if (CB > 512) return p;
+  p.nb = 2 * CB <= 512 ? 2 : 1;
+  p.tmem_cols = pow2_at_least(p.nb * CB);
+  const size_t HB = (size_t)TCV_HALO_W * TCV_TILE_ROWS * 128, stage = (size_t)2 * KH * p.gs * 128;
+  const size_t fixed = 1024 + (size_t)TCV_EPI_FLOATS * 4 + 512;
+  for (p.nh = 2; p.nh >= 1; --p.nh) {
+    size_t need = fixed + (size_t)p.nh * 2 * HB;
+    if (ctx->smem_optin < need + 2 * stage) continue;
+    size_t nf = (ctx->smem_optin - need) / stage;
+    p.nf = (int)(nf > 6 ? 6 : nf);
+    p.smem = need + (size_t)p.nf * stage;
+    p.ok = true;
+    return p;
+  }
+  return p;
 }
 
 size_t dw_tc_smem(int KH) {
@@ -502,51 +597,51 @@ int make_map_rows(CUtensorMap *m, const float *base, uint64_t rows, uint32_t box
   return make_map_2d(m, base, 32, rows, 32, box_rows);
 }
 
-int to_tall(b200_ctx *ctx, const float *src, int C, int H, int W, int Cp, int period, int B, float *dst,
-            float *bsum, int *blocks_out) {
-  int px = 16384 / (Cp + 1);
-  if (px > 256) px = 256;
+// rows of one image a conversion block takes
+int to_tall_rows(int C, int W, int period) {
+  int px = 4096 / (C > 0 ? C : 1);  // about 16 KiB of tile: several blocks per SM
+  if (px > 512) px = 512;
   int rb = px / W;
   if (rb < 1) rb = 1;
   if (rb > period) rb = period;
-  size_t smem = (size_t)rb * W * (Cp + 1) * sizeof(float);
+  // even out the chunks of one image
+  int chunks = ceil_div(period, rb);
+  return ceil_div(period, chunks);
+}
+
+int to_tall_blocks(int C, int W, int period, int B) { return B * ceil_div(period, to_tall_rows(C, W, period)); }
+
+int to_tall(b200_ctx *ctx, const float *src, int C, int H, int W, int Cp, int period, int B, float *dst,
+            float *bsum) {
+  const int rb = to_tall_rows(C, W, period);
+  const int pitch = ((rb * W + 7) & ~7) + 1;
+  size_t smem = (size_t)C * pitch * sizeof(float);
   if (smem > 48 * 1024)
     B200_CUDA(cudaFuncSetAttribute(to_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int chunks = ceil_div(period, rb);
-  long long rows = (long long)B * period;
-  size_t one = (size_t)rows * W * Cp;
-  to_tall_kernel<<<B * chunks, 256, smem, ctx->stream>>>(src, C, H, W, Cp, period, rb, rows, dst, dst + one,
+  size_t one = (size_t)B * period * W * Cp;
+  to_tall_kernel<<<B * chunks, 256, smem, ctx->stream>>>(src, C, H, W, Cp, period, rb, pitch, dst, dst + one,
                                                          bsum);
   B200_LAUNCHED();
-  if (blocks_out) *blocks_out = B * chunks;
   return 0;
-}
-
-int to_tall_blocks(int W, int Cp, int period, int B) {
-  int px = 16384 / (Cp + 1);
-  if (px > 256) px = 256;
-  int rb = px / W;
-  if (rb < 1) rb = 1;
-  if (rb > period) rb = period;
-  return B * ceil_div(period, rb);
 }
 
 // shared launcher of the forward and dX passes
 int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long rows, int period,
                    const float *wt, int KH, int KW, int pad_t, int pad_l, int N, float *out, int OH, int OW,
                    const float *bias, int act, int B) {
-  const int Np = pad16(N), slabs = Cp / 32, taps = KH * KW;
-  const int nf = conv_tc_ring(ctx, KH, Np);
-  B200_REQUIRE(nf >= 2, "tensor-core convolution: tiles do not fit shared memory (KH %d, N %d)", KH, N);
+  const TcPlan p = conv_tc_plan(ctx, KH, N);
+  B200_REQUIRE(p.ok, "tensor-core convolution: tiles do not fit (window height %d, %d channels)", KH, N);
+  const int slabs = Cp / 32, Ng = KH * p.gs;
   CUtensorMap in_hi, in_lo, f_hi, f_lo;
   const size_t one = (size_t)rows * Win * Cp;
-  B200_TRY(make_map_3d(&in_hi, tall, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS + KH - 1,
+  B200_TRY(make_map_3d(&in_hi, tall, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS,
                        CU_TENSOR_MAP_SWIZZLE_128B));
-  B200_TRY(make_map_3d(&in_lo, tall + one, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS + KH - 1,
+  B200_TRY(make_map_3d(&in_lo, tall + one, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS,
                        CU_TENSOR_MAP_SWIZZLE_128B));
-  const size_t frows = (size_t)taps * slabs * Np;
-  B200_TRY(make_map_rows(&f_hi, wt, frows, Np));
-  B200_TRY(make_map_rows(&f_lo, wt + frows * 32, frows, Np));
+  const size_t frows = (size_t)slabs * KW * p.groups * Ng;
+  B200_TRY(make_map_rows(&f_hi, wt, frows, Ng));
+  B200_TRY(make_map_rows(&f_lo, wt + frows * 32, frows, Ng));
   TcConvArgs a;
   a.out = out;
   a.bias = bias;
@@ -556,34 +651,56 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long 
   a.OH = OH;
   a.OW = OW;
   a.N = N;
-  a.Np = Np;
   a.slabs = slabs;
+  a.groups = p.groups;
+  a.gs = p.gs;
   a.KH = KH;
   a.KW = KW;
   a.pad_t = pad_t;
   a.pad_l = pad_l;
+  const int TR = TCV_TILE_ROWS - (KH - 1);
   a.tiles_x = ceil_div(OW, TCV_TILE_COLS);
-  a.ntiles = a.tiles_x * (int)((rows + TCV_TILE_ROWS - 1) / TCV_TILE_ROWS);
+  a.ntiles = a.tiles_x * (int)((rows + TR - 1) / TR);
   a.act = act;
-  a.nf = nf;
-  a.acc_stride = (Np + 31) / 32 * 32;
-  a.tmem_cols = pow2_at_least(2 * a.acc_stride);
-  const size_t smem = conv_tc_smem(KH, Np, nf);
-  B200_CUDA(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  a.nh = p.nh;
+  a.nf = p.nf;
+  a.nb = p.nb;
+  a.tmem_cols = p.tmem_cols;
+  B200_CUDA(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
   int grid = a.ntiles < ctx->sm_count ? a.ntiles : ctx->sm_count;
-  conv_tc_kernel<<<grid, TCV_THREADS, smem, ctx->stream>>>(in_hi, in_lo, f_hi, f_lo, a);
+  conv_tc_kernel<<<grid, TCV_THREADS, p.smem, ctx->stream>>>(in_hi, in_lo, f_hi, f_lo, a);
   B200_LAUNCHED();
   return 0;
 }
 
-int filter_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, int Np, int slabs, int for_dx, float *wt) {
-  long long total = (long long)g.KH * g.KW * slabs * Np * 32;
+int filter_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, int n_out, int slabs, int for_dx, float *wt) {
+  const TcPlan p = conv_tc_plan(ctx, g.KH, n_out);
+  long long total = (long long)slabs * g.KW * p.groups * g.KH * p.gs * 32;
   int blocks = (int)((total + 255) / 256);
   if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-  tc_filter_prep_kernel<<<blocks, 256, 0, ctx->stream>>>(W, g.tbl, g.C, g.OC, g.KH, g.KW, Np, slabs, for_dx,
-                                                         wt, wt + total);
+  tc_filter_prep_kernel<<<blocks, 256, 0, ctx->stream>>>(W, g.tbl, g.C, g.OC, g.KH, g.KW, p.gs, p.groups, slabs,
+                                                         for_dx, wt, wt + total);
   B200_LAUNCHED();
   return 0;
+}
+
+// dst[c] (+)= sum over rows of src[r*len + c] for a tall, narrow matrix (many partial rows of a
+// short vector): 32 row lanes per column, each adding its rows in order, combined in fixed order.
+__global__ void __launch_bounds__(1024) sum_rows_narrow_kernel(const float *__restrict__ src, int rows, int len,
+                                                              float *__restrict__ dst, int accumulate) {
+  __shared__ float part[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x, rg = threadIdx.y;
+  float s = 0.f;
+  if (c < len)
+    for (int r = rg; r < rows; r += 32) s += src[(size_t)r * len + c];
+  part[rg][threadIdx.x] = s;
+  __syncthreads();
+  if (rg == 0 && c < len) {
+    float t = part[0][threadIdx.x];
+#pragma unroll
+    for (int i = 1; i < 32; ++i) t += part[i][threadIdx.x];
+    dst[c] = accumulate ? dst[c] + t : t;
+  }
 }
 
 }  // namespace
@@ -595,9 +712,9 @@ bool conv_tc_ok(const b200_ctx *ctx, const ConvGeom &g) {
   if (g.pad_t < 0 || g.pad_l < 0 || t.pad_b < 0 || t.pad_r < 0) return false;
   if (g.pad_t > g.KH - 1 || t.pad_b > g.KH - 1 || g.pad_l > g.KW - 1 || t.pad_r > g.KW - 1) return false;
   if (g.WI > 256 || g.OW > 256) return false;
-  if (conv_tc_ring(ctx, g.KH, pad16(g.OC)) < 2 || conv_tc_ring(ctx, g.KH, pad16(g.C)) < 2) return false;
+  if (!conv_tc_plan(ctx, g.KH, g.OC).ok || !conv_tc_plan(ctx, g.KH, g.C).ok) return false;
   if (dw_tc_smem(g.KH) > ctx->smem_optin) return false;
-  size_t tall_smem = (size_t)(g.WI > g.OW ? g.WI : g.OW) * ((t.Cp > t.OCp ? t.Cp : t.OCp) + 1) * 4;
+  size_t tall_smem = (size_t)((g.WI > g.OW ? g.WI : g.OW) + 9) * (g.C > g.OC ? g.C : g.OC) * 4;
   return tall_smem <= ctx->smem_optin;
 }
 
@@ -608,10 +725,8 @@ ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo) {
   if (algo == 3 || ctx->conv_tensor_cores >= 2) {
     u.fwd = u.dx = u.dw = true;
   } else {
-    // a pass pays off when the contracted channel count fills most of a 32-wide slab
-    u.fwd = g.C >= 16;
-    u.dx = g.OC >= 16;
-    u.dw = g.C >= 16 && g.OC >= 16;
+    // a pass pays off when both channel counts fill a good part of a 32-wide slab / MMA width
+    u.fwd = u.dx = u.dw = g.C >= 16 && g.OC >= 16;
   }
   if (algo != 3) {
     if (const char *e = getenv("B200_CONV_TC")) {  // bit 0 forward, bit 1 dX, bit 2 dW
@@ -631,16 +746,25 @@ size_t conv_tc_tall_floats(const ConvGeom &g, int B, int which) {
   return (size_t)2 * B * dy_period(g) * g.OW * t.OCp;
 }
 
-size_t conv_tc_filter_floats(const ConvGeom &g, int for_dx) {
+size_t conv_tc_filter_floats(const b200_ctx *ctx, const ConvGeom &g, int for_dx) {
   TallGeom t = tall_geom(g, 1);
-  int Np = for_dx ? pad16(g.C) : pad16(g.OC), slabs = (for_dx ? t.OCp : t.Cp) / 32;
-  return (size_t)2 * g.KH * g.KW * slabs * Np * 32;
+  const TcPlan p = conv_tc_plan(ctx, g.KH, for_dx ? g.C : g.OC);
+  int slabs = (for_dx ? t.OCp : t.Cp) / 32;
+  return (size_t)2 * slabs * g.KW * p.groups * g.KH * p.gs * 32;
 }
 
 // rows of per-block bias-gradient partials the dY conversion writes
 int conv_tc_bsum_rows(const ConvGeom &g, int B) {
   TallGeom t = tall_geom(g, 1);
-  return to_tall_blocks(g.OW, t.OCp, dy_period(g), B);
+  return to_tall_blocks(g.OC, g.OW, dy_period(g), B);
+}
+
+// bias gradient from the per-block channel sums of conv_tc_tall_dy
+int conv_tc_bias_grad(b200_ctx *ctx, const ConvGeom &g, const float *bsum, int B, float *db, int accumulate) {
+  sum_rows_narrow_kernel<<<ceil_div(g.OC, 32), dim3(32, 32), 0, ctx->stream>>>(bsum, conv_tc_bsum_rows(g, B),
+                                                                              g.OC, db, accumulate);
+  B200_LAUNCHED();
+  return 0;
 }
 
 int conv_tc_dw_splits(const b200_ctx *ctx, const ConvGeom &g, int B) {
@@ -660,20 +784,20 @@ size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B) {
 
 int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs) {
   TallGeom t = tall_geom(g, B);
-  return to_tall(ctx, in, g.C, g.HI, g.WI, t.Cp, t.period, B, xs, nullptr, nullptr);
+  return to_tall(ctx, in, g.C, g.HI, g.WI, t.Cp, t.period, B, xs, nullptr);
 }
 
 // dY -> tall split form; bsum (conv_tc_bsum_rows x OC floats, may be nullptr) receives the
 // per-block channel sums whose in-order total is the bias gradient
 int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, float *dys, float *bsum) {
   TallGeom t = tall_geom(g, B);
-  return to_tall(ctx, dout, g.OC, g.OH, g.OW, t.OCp, dy_period(g), B, dys, bsum, nullptr);
+  return to_tall(ctx, dout, g.OC, g.OH, g.OW, t.OCp, dy_period(g), B, dys, bsum);
 }
 
 int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,
                 float *out, int B, int act, float *wt) {
   TallGeom t = tall_geom(g, B);
-  B200_TRY(filter_prep(ctx, g, W, pad16(g.OC), t.Cp / 32, 0, wt));
+  B200_TRY(filter_prep(ctx, g, W, g.OC, t.Cp / 32, 0, wt));
   return launch_conv_tc(ctx, xs, t.Cp, g.WI, t.rows, t.period, wt, g.KH, g.KW, g.pad_t, g.pad_l, g.OC, out,
                         g.OH, g.OW, g.has_bias ? bias : nullptr, act, B);
 }
@@ -682,7 +806,7 @@ int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *
                float *wt) {
   TallGeom t = tall_geom(g, B);
   const int period = dy_period(g);
-  B200_TRY(filter_prep(ctx, g, W, pad16(g.C), t.OCp / 32, 1, wt));
+  B200_TRY(filter_prep(ctx, g, W, g.C, t.OCp / 32, 1, wt));
   return launch_conv_tc(ctx, dys, t.OCp, g.OW, (long long)B * period, period, wt, g.KH, g.KW,
                         g.KH - 1 - g.pad_t, g.KW - 1 - g.pad_l, g.C, din, g.HI, g.WI, nullptr, B200_ACT_NONE,
                         B);

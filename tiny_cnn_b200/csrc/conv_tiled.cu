@@ -1014,6 +1014,43 @@ __global__ void merge_rows_kernel(const float *__restrict__ src, int rows, size_
   }
 }
 
+// Same sum for many partial rows: 8 row lanes per output element (lane k adds rows k, k+8, ...
+// in order, two chains in flight), combined in lane order -- a fixed order, 8x the loads in flight.
+__global__ void __launch_bounds__(256)
+  merge_rows_lanes_kernel(const float *__restrict__ src, int rows, size_t stride, float *__restrict__ dst,
+                          size_t len, int accumulate, const uint8_t *__restrict__ tbl, int C, int OC, int KK,
+                          size_t lenW) {
+  __shared__ float part[8][33];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  for (size_t base = (size_t)blockIdx.x * 32; base < len; base += (size_t)gridDim.x * 32) {
+    const size_t i = base + tx;
+    float s0 = 0.f, s1 = 0.f;
+    if (i < len) {
+      int r = ty;
+      for (; r + 8 < rows; r += 16) {
+        s0 += src[(size_t)r * stride + i];
+        s1 += src[(size_t)(r + 8) * stride + i];
+      }
+      if (r < rows) s0 += src[(size_t)r * stride + i];
+    }
+    part[ty][tx] = s0 + s1;
+    __syncthreads();
+    if (ty == 0 && i < len) {
+      float s = part[0][tx];
+#pragma unroll
+      for (int k = 1; k < 8; ++k) s += part[k][tx];
+      if (tbl && i < lenW) {
+        size_t pair = i / KK;
+        int inc = (int)(pair % C);
+        int o = (int)(pair / C);
+        if (!tbl[inc * OC + o]) s = 0.f;
+      }
+      dst[i] = accumulate ? dst[i] + s : s;
+    }
+    __syncthreads();
+  }
+}
+
 int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *dst, size_t len,
                int accumulate, const ConvGeom *mask, int in_order) {
   if (len == 0) return 0;
@@ -1022,6 +1059,15 @@ int merge_rows(b200_ctx *ctx, const float *src, int rows, size_t stride, float *
   size_t cap = (size_t)ctx->sm_count * 8;
   if (blocks > cap) blocks = cap;
   const uint8_t *tbl = mask ? mask->tbl : nullptr;
+  if (!in_order && rows >= 16) {
+    size_t lb = ceil_div_sz(len, 32);
+    if (lb > cap * 4) lb = cap * 4;
+    merge_rows_lanes_kernel<<<(unsigned)lb, dim3(32, 8), 0, ctx->stream>>>(
+      src, rows, stride, dst, len, accumulate, tbl, mask ? mask->C : 1, mask ? mask->OC : 1,
+      mask ? mask->KH * mask->KW : 1, mask ? conv_weight_len(*mask) : 0);
+    B200_LAUNCHED();
+    return 0;
+  }
   merge_rows_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(
     src, rows, stride, dst, len, accumulate, tbl, mask ? mask->C : 1, mask ? mask->OC : 1,
     mask ? mask->KH * mask->KW : 1, mask ? conv_weight_len(*mask) : 0, in_order);

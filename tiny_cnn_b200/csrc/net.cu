@@ -31,6 +31,11 @@ struct Layer {
   int32_t *argmax = nullptr;
   bool tiled = false;
   float *wt_fwd = nullptr, *wt_dx = nullptr, *dw_part = nullptr;
+  // tensor-core passes: tall split copies of the input and of dY, per-block bias partials,
+  // filter matrices, partial weight gradients
+  ConvTcUse tc = {false, false, false};
+  float *tc_xs = nullptr, *tc_dys = nullptr, *tc_bsum = nullptr;
+  float *tc_wt_fwd = nullptr, *tc_wt_dx = nullptr, *tc_part = nullptr;
   float *fc_scratch = nullptr;  // k-slice partial sums of the small GEMMs
   int fused_act = 0;      // activation of the NEXT layer folded into this epilogue
   bool skipped = false;   // activation layer folded into the previous layer
@@ -99,7 +104,10 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
     const float *b = L.b_len ? net->params + L.b_off : nullptr;
     switch (L.kind) {
       case B200_LAYER_CONV:
-        if (L.tiled)
+        if (L.tc.fwd) {
+          B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
+          B200_TRY(conv_tc_fwd(ctx, L.g, L.tc_xs, W, b, dst, B, L.fused_act, L.tc_wt_fwd));
+        } else if (L.tiled)
           B200_TRY(conv_tiled_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act, L.wt_fwd));
         else
           B200_TRY(conv_general_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act));
@@ -143,8 +151,24 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
     switch (L.kind) {
       case B200_LAYER_CONV: {
         bool tiled_bwd = L.tiled && L.g.OW <= 64;
-        if (tiled_bwd) {
-          if (din) B200_TRY(conv_tiled_dx(ctx, L.g, W, L.grad, din, B, L.wt_dx));
+        const bool tc_dx = L.tc.dx && din != nullptr;
+        if (tc_dx || L.tc.dw)
+          B200_TRY(conv_tc_tall_dy(ctx, L.g, L.grad, B, L.tc_dys, L.tc.dw && db ? L.tc_bsum : nullptr));
+        if (din) {
+          if (tc_dx)
+            B200_TRY(conv_tc_dx(ctx, L.g, L.tc_dys, W, din, B, L.tc_wt_dx));
+          else if (tiled_bwd)
+            B200_TRY(conv_tiled_dx(ctx, L.g, W, L.grad, din, B, L.wt_dx));
+          else
+            B200_TRY(conv_general_dx(ctx, L.g, W, L.grad, din, B));
+        }
+        if (L.tc.dw) {
+          if (!L.tc.fwd) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
+          int splits = 0;
+          B200_TRY(conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits));
+          B200_TRY(merge_rows(ctx, L.tc_part, splits, L.w_len, dW, L.w_len, 0, &L.g));
+          if (db) B200_TRY(conv_tc_bias_grad(ctx, L.g, L.tc_bsum, B, db, 0));
+        } else if (tiled_bwd) {
           int splits = 0;
           B200_TRY(conv_tiled_dw_partials(ctx, L.g, in, L.grad, B, L.dw_part, &splits));
           size_t row = L.w_len + L.g.OC;
@@ -157,7 +181,6 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
               B200_TRY(merge_rows(ctx, L.dw_part + L.w_len, splits, row, db, L.b_len, 0, nullptr));
           }
         } else {
-          if (din) B200_TRY(conv_general_dx(ctx, L.g, W, L.grad, din, B));
           B200_TRY(conv_general_dw(ctx, L.g, in, L.grad, dW, db, 0, B));
         }
         break;
@@ -272,6 +295,7 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
         L.w_len = conv_weight_len(L.g);
         L.b_len = L.g.has_bias ? L.g.OC : 0;
         L.tiled = conv_tiled_ok(L.g) && L.cd.algo != 1;
+        L.tc = conv_tc_use(ctx, L.g, L.cd.algo);
         break;
       }
       case B200_LAYER_FC:
@@ -380,6 +404,18 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
       size_t need = conv_tiled_dw_scratch(ctx, L.g, max_batch);
       B200_TRY(net_alloc((void **)&L.dw_part, need * f));
     }
+    if (L.kind == B200_LAYER_CONV && (L.tc.fwd || L.tc.dx || L.tc.dw)) {
+      if (L.tc.fwd || L.tc.dw)
+        B200_TRY(net_alloc((void **)&L.tc_xs, conv_tc_tall_floats(L.g, max_batch, 0) * f));
+      if (L.tc.dx || L.tc.dw)
+        B200_TRY(net_alloc((void **)&L.tc_dys, conv_tc_tall_floats(L.g, max_batch, 1) * f));
+      if (L.tc.fwd) B200_TRY(net_alloc((void **)&L.tc_wt_fwd, conv_tc_filter_floats(ctx, L.g, 0) * f));
+      if (L.tc.dx) B200_TRY(net_alloc((void **)&L.tc_wt_dx, conv_tc_filter_floats(ctx, L.g, 1) * f));
+      if (L.tc.dw) {
+        B200_TRY(net_alloc((void **)&L.tc_part, conv_tc_dw_floats(ctx, L.g, max_batch) * f));
+        B200_TRY(net_alloc((void **)&L.tc_bsum, (size_t)conv_tc_bsum_rows(L.g, max_batch) * L.g.OC * f + 64));
+      }
+    }
   }
   *out = net;
   return 0;
@@ -398,6 +434,12 @@ int b200_net_destroy(b200_net *net) {
     cudaFree(L.wt_fwd);
     cudaFree(L.wt_dx);
     cudaFree(L.dw_part);
+    cudaFree(L.tc_xs);
+    cudaFree(L.tc_dys);
+    cudaFree(L.tc_bsum);
+    cudaFree(L.tc_wt_fwd);
+    cudaFree(L.tc_wt_dx);
+    cudaFree(L.tc_part);
     cudaFree(L.fc_scratch);
   }
   cudaFree(net->params);
