@@ -105,7 +105,7 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
     B200_TRY(conv_tc_tall_x(ctx, g, in, batch, xs));
     int splits = 0;
     B200_TRY(conv_tc_dw(ctx, g, xs, dys, batch, part, &splits));
-    B200_TRY(merge_rows(ctx, part, splits, lenW, dW, lenW, accumulate, &g));
+    B200_TRY(conv_tc_dw_finish(ctx, g, part, splits, dW, accumulate));
     if (g.has_bias) B200_TRY(conv_tc_bias_grad(ctx, g, bs, batch, db, accumulate));
     return 0;
   }

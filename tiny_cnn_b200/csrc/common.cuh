@@ -178,6 +178,7 @@ int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *
                float *wt);
 int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *dys, int B, float *part,
                int *splits);
+int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate);
 
 // dst (+)= sum_r src[r*stride + i], rows summed in order; optional connection
 // mask for convolution weights (entries of unconnected pairs are left alone

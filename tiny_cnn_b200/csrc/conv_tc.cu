@@ -24,7 +24,7 @@
 //   computes 4 x KH taps of a 32 x 32 channel block.  The batch is cut into slices whose
 //   partial sums are merged in fixed order (the device form of edge::merge_grads).
 // Warp roles in both kernels: warps 0-3 epilogue (one TMEM lane per thread), warp 4 TMEM
-// allocation + TMA producer, warp 5 MMA issuer.  No multicast; every wait is bounded and a
+// allocation + TMA producer, warp 5 MMA issuer.  Every load is CTA-local; every wait is bounded and a
 // timeout sets the context's error word, frees tensor memory and returns.
 #include <stdlib.h>
 
@@ -193,6 +193,7 @@ struct TcConvArgs {
   int nf;              // filter ring stages
   int nb;              // accumulator buffers in tensor memory (1 or 2)
   int tmem_cols;       // allocated columns (power of two >= nb * groups * KH * gs)
+  long long *dbg;      // optional [grid][8] cycle counters (B200_TC_TIMING=1), else nullptr
 };
 
 __global__ void __launch_bounds__(TCV_THREADS, 1)
@@ -206,8 +207,8 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   const uint32_t FB = (uint32_t)Ng * 128u;                    // one filter tile (hi or lo)
   const int CB = a.groups * Ng;                               // accumulator columns per buffer
   uint8_t *halo = smem;                                       // [nh][hi | lo]
-  uint8_t *filt = halo + (size_t)a.nh * 2 * HB;               // [nf][hi | lo]
-  float *xch = reinterpret_cast<float *>(filt + (size_t)a.nf * 2 * FB);
+  uint8_t *filt = halo + (size_t)a.nh * 2 * HB;               // [nf] filter tiles (hi and lo alternate)
+  float *xch = reinterpret_cast<float *>(filt + (size_t)a.nf * FB);
   uint64_t *halo_full = reinterpret_cast<uint64_t *>(xch + TCV_EPI_FLOATS);
   uint64_t *halo_empty = halo_full + 2;
   uint64_t *acc_full = halo_empty + 2;
@@ -254,17 +255,15 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
         tma_load_3d(h, &in_hi, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
         tma_load_3d(h + HB, &in_lo, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
         const int nst = a.KW * a.groups;
-        for (int s = 0; s < nst; ++s, ++f) {
+        for (int s = 0; s < 2 * nst; ++s, ++f) {  // per (kx, group): the hi tile, then the lo tile
           const uint32_t fs = f % a.nf, fuse = f / a.nf;
           if (fuse > 0 && !mbar_wait_bounded(&filt_empty[fs], (fuse - 1) & 1)) {
             failed = true;
             break;
           }
-          uint8_t *ft = filt + (size_t)fs * 2 * FB;
-          const int row = (slab * nst + s) * Ng;
-          mbar_expect_tx(&filt_full[fs], 2 * FB);
-          tma_load_2d(ft, &f_hi, 0, row, &filt_full[fs]);
-          tma_load_2d(ft + FB, &f_lo, 0, row, &filt_full[fs]);
+          const int row = (slab * nst + (s >> 1)) * Ng;
+          mbar_expect_tx(&filt_full[fs], FB);
+          tma_load_2d(filt + (size_t)fs * FB, (s & 1) ? &f_lo : &f_hi, 0, row, &filt_full[fs]);
         }
       }
     }
@@ -272,50 +271,68 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     // ---- MMA issuer -----------------------------------------------------------------------
     const uint32_t idesc = umma_idesc_tf32(128, Ng);
     uint32_t u = 0, f = 0, it = 0;
+    long long w_acc = 0, w_halo = 0, w_filt = 0, t_begin = clock64(), tq;
     for (int tile = blockIdx.x; tile < a.ntiles && !failed; tile += gridDim.x, ++it) {
       const uint32_t ab = it % a.nb, ause = it / a.nb;
+      tq = clock64();
       if (ause > 0 && !mbar_wait_bounded(&acc_empty[ab], (ause - 1) & 1)) {
         failed = true;
         break;
       }
+      w_acc += clock64() - tq;
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + ab * (uint32_t)CB;
       for (int slab = 0; slab < a.slabs && !failed; ++slab, ++u) {
         const uint32_t hb = u % a.nh;
+        tq = clock64();
         if (!mbar_wait_bounded(&halo_full[hb], (u / a.nh) & 1)) {
           failed = true;
           break;
         }
+        w_halo += clock64() - tq;
         tc_fence_after();
         const uint32_t hbase = smem_u32(halo + (size_t)hb * 2 * HB);
         for (int kx = 0; kx < a.KW && !failed; ++kx) {
-          for (int grp = 0; grp < a.groups; ++grp, ++f) {
-            const uint32_t fs = f % a.nf;
-            if (!mbar_wait_bounded(&filt_full[fs], (f / a.nf) & 1)) {
-              failed = true;
-              break;
-            }
-            tc_fence_after();
+          for (int grp = 0; grp < a.groups && !failed; ++grp) {
             // A: the haloed tile addressed kx pixels (rows of 128 bytes) further on
             const uint32_t abase = hbase + (uint32_t)kx * 128u;
-            const uint32_t bbase = smem_u32(filt + (size_t)fs * 2 * FB);
             const uint32_t d = tmem_d + (uint32_t)(grp * Ng);
+            for (int part = 0; part < 2; ++part, ++f) {  // the hi filter tile, then the lo tile
+              const uint32_t fs = f % a.nf;
+              tq = clock64();
+              if (!mbar_wait_bounded(&filt_full[fs], (f / a.nf) & 1)) {
+                failed = true;
+                break;
+              }
+              w_filt += clock64() - tq;
+              tc_fence_after();
+              const uint32_t bbase = smem_u32(filt + (size_t)fs * FB);
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) {
-              const uint64_t ahi = umma_desc(abase + k4 * 32, 16, TCV_HALO_W * 128, 2);
-              const uint64_t alo = umma_desc(abase + HB + k4 * 32, 16, TCV_HALO_W * 128, 2);
-              const uint64_t bhi = umma_desc(bbase + k4 * 32, 16, 1024, 2);
-              const uint64_t blo = umma_desc(bbase + FB + k4 * 32, 16, 1024, 2);
-              umma_tf32(d, alo, bhi, idesc, (slab | kx | k4) != 0);
-              umma_tf32(d, ahi, blo, idesc, 1);
-              umma_tf32(d, ahi, bhi, idesc, 1);
+              for (int k4 = 0; k4 < 4; ++k4) {
+                const uint64_t ahi = umma_desc(abase + k4 * 32, 16, TCV_HALO_W * 128, 2);
+                const uint64_t b = umma_desc(bbase + k4 * 32, 16, 1024, 2);
+                if (part == 0) {
+                  const uint64_t alo = umma_desc(abase + HB + k4 * 32, 16, TCV_HALO_W * 128, 2);
+                  umma_tf32(d, alo, b, idesc, (slab | kx | k4) != 0);
+                  umma_tf32(d, ahi, b, idesc, 1);
+                } else {
+                  umma_tf32(d, ahi, b, idesc, 1);
+                }
+              }
+              umma_commit(&filt_empty[fs]);
             }
-            umma_commit(&filt_empty[fs]);
           }
         }
         if (!failed) umma_commit(&halo_empty[hb]);
       }
       if (!failed) umma_commit(&acc_full[ab]);
+    }
+    if (a.dbg) {
+      long long *d = a.dbg + (size_t)blockIdx.x * 8;
+      d[0] = clock64() - t_begin;
+      d[1] = w_acc;
+      d[2] = w_halo;
+      d[3] = w_filt;
     }
   } else if (warp < 4) {
     // ---- epilogue: sum the KH row-shifted column blocks, bias, activation, store -------------
@@ -323,9 +340,12 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     const int m = warp * 32 + lane, r = m >> 3, dx = m & 7;
     const size_t plane = (size_t)a.OH * a.OW;
     uint32_t half = 0;  // exchange buffer half in use
+    long long w_full = 0, t_begin = clock64(), tq;
     for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x, ++it) {
       const uint32_t ab = it % a.nb;
+      tq = clock64();
       if (!mbar_wait_bounded(&acc_full[ab], (it / a.nb) & 1)) failed = true;
+      w_full += clock64() - tq;
       // every epilogue thread takes part in the named barriers below, so leave together
       {
         int any;
@@ -393,6 +413,11 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[ab]);
     }
+    if (a.dbg && tid == 0) {
+      long long *d = a.dbg + (size_t)blockIdx.x * 8;
+      d[4] = clock64() - t_begin;
+      d[5] = w_full;
+    }
   }
   if (failed && a.err) atomicExch(a.err, 3);
   tc_fence_before();
@@ -419,6 +444,7 @@ struct TcDwArgs {
   int ksplits;
   int tmem_cols;
   long long row_stride;
+  long long *dbg;  // optional [blocks][8] cycle counters (B200_TC_TIMING=1), else nullptr
 };
 
 // dW[o][inc][ky][kx] = sum over pixels u of X dY[t][u + pad_l - kx] * X[t + ky - pad_t][u]
@@ -457,6 +483,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool failed = false;
+  long long t_begin = 0, t_acc = 0;
 
   if (warp == 4 && lane == 0) {
     for (int s = s_begin; s < s_end; ++s) {
@@ -476,12 +503,15 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   } else if (warp == 5 && lane == 0) {
     const uint32_t idesc = umma_idesc_tf32_major(128, N, 1, 1);
     uint32_t accumulate = 0;
+    long long w_full = 0, t_begin = clock64(), tq;
     for (int s = s_begin; s < s_end && !failed; ++s) {
       const uint32_t i = s - s_begin, st = i % TCW_STAGES;
+      tq = clock64();
       if (!mbar_wait_bounded(&full[st], (i / TCW_STAGES) & 1)) {
         failed = true;
         break;
       }
+      w_full += clock64() - tq;
       tc_fence_after();
       const uint32_t base = smem_u32(smem + st * STAGE);
       for (int r = 0; r < TCW_ROWS; ++r) {
@@ -504,35 +534,46 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
       umma_commit(&empty[st]);
     }
     if (!failed) umma_commit(accum);
+    if (a.dbg) {
+      long long *d = a.dbg + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
+      d[0] = clock64() - t_begin;
+      d[1] = w_full;
+      d[2] = s_end - s_begin;
+    }
   } else if (warp < 4) {
-    float *row = a.part + (size_t)blockIdx.x * a.row_stride;
-    const int oc = ocs * 32 + lane;
+    // partial row in the kernel's own order [unit][j][ky][inc][o] (o fastest: one 128-byte line per
+    // store instruction); conv_tc_dw_finish sums the rows and reorders to the reference layout
+    float *row = a.part + (size_t)blockIdx.x * a.row_stride + (size_t)blockIdx.y * a.KW * N * 32;
+    t_begin = clock64();
     if (s_end > s_begin) {
       if (!mbar_wait_bounded(accum, 0)) failed = true;
       tc_fence_after();
     }
+    t_acc = clock64();
     if (!failed) {
       for (int ch = 0; ch < chunks; ++ch) {
-        const int kx = a.KW - 1 - (ch * 4 + warp);
+        const int j = ch * 4 + warp;
         for (int c0 = 0; c0 < N; c0 += 32) {
           float v[32];
           if (s_end > s_begin) {
             tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(ch * N + c0), v);
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            for (int q = 0; q < 32; ++q) v[q] = 0.f;
           }
-          const int ky = c0 >> 5;
-          if (kx >= 0 && oc < a.OC) {
+          if (j < a.KW) {
+            float *dst = row + ((size_t)j * N + c0) * 32 + lane;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int inc = ics * 32 + j;
-              if (inc < a.C) row[((size_t)(oc * a.C + inc) * a.KH + ky) * a.KW + kx] = v[j];
-            }
+            for (int q = 0; q < 32; ++q) dst[q * 32] = v[q];
           }
         }
       }
     }
+  }
+  if (a.dbg && tid == 0) {
+    long long *d = a.dbg + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
+    d[3] = t_acc - t_begin;
+    d[4] = clock64() - t_acc;
   }
   if (failed && a.err) atomicExch(a.err, 4);
   tc_fence_before();
@@ -574,13 +615,13 @@ TcPlan conv_tc_plan(const b200_ctx *ctx, int KH, int n_out) {
   if (CB > 512) return p;
   p.nb = 2 * CB <= 512 ? 2 : 1;
   p.tmem_cols = pow2_at_least(p.nb * CB);
-  const size_t HB = (size_t)TCV_HALO_W * TCV_TILE_ROWS * 128, stage = (size_t)2 * KH * p.gs * 128;
+  const size_t HB = (size_t)TCV_HALO_W * TCV_TILE_ROWS * 128, stage = (size_t)KH * p.gs * 128;
   const size_t fixed = 1024 + (size_t)TCV_EPI_FLOATS * 4 + 512;
   for (p.nh = 2; p.nh >= 1; --p.nh) {
     size_t need = fixed + (size_t)p.nh * 2 * HB;
     if (ctx->smem_optin < need + 2 * stage) continue;
     size_t nf = (ctx->smem_optin - need) / stage;
-    p.nf = (int)(nf > 6 ? 6 : nf);
+    p.nf = (int)(nf > 12 ? 12 : nf);
     p.smem = need + (size_t)p.nf * stage;
     p.ok = true;
     return p;
@@ -666,10 +707,26 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long 
   a.nf = p.nf;
   a.nb = p.nb;
   a.tmem_cols = p.tmem_cols;
+  a.dbg = nullptr;
   B200_CUDA(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
   int grid = a.ntiles < ctx->sm_count ? a.ntiles : ctx->sm_count;
+  static const bool timing = getenv("B200_TC_TIMING") != nullptr;
+  if (timing) B200_CUDA(cudaMalloc(&a.dbg, (size_t)grid * 8 * sizeof(long long)));
   conv_tc_kernel<<<grid, TCV_THREADS, p.smem, ctx->stream>>>(in_hi, in_lo, f_hi, f_lo, a);
   B200_LAUNCHED();
+  if (timing) {  // diagnostic: where the MMA and epilogue roles spent their cycles, averaged over blocks
+    std::vector<long long> h((size_t)grid * 8);
+    B200_CUDA(cudaStreamSynchronize(ctx->stream));
+    B200_CUDA(cudaMemcpy(h.data(), a.dbg, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+    B200_CUDA(cudaFree(a.dbg));
+    double s[8] = {0};
+    for (int i = 0; i < grid; ++i)
+      for (int k = 0; k < 8; ++k) s[k] += (double)h[(size_t)i * 8 + k] / grid;
+    fprintf(stderr,
+            "[tc-timing] tiles %d grid %d N %d: mma total %.0f clk, waits acc %.0f halo %.0f filt %.0f | "
+            "epilogue total %.0f, wait full %.0f\n",
+            a.ntiles, grid, KH * p.gs, s[0], s[1], s[2], s[3], s[4], s[5]);
+  }
   return 0;
 }
 
@@ -682,6 +739,25 @@ int filter_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, int n_out, int
                                                          for_dx, wt, wt + total);
   B200_LAUNCHED();
   return 0;
+}
+
+// merged weight gradient in the dW kernel's order [unit][j][ky][inc][o] -> reference order
+// dW[o][inc][ky][kx] (kx = KW-1-j); unconnected pairs get no gradient
+__global__ void dw_tc_permute_kernel(const float *__restrict__ src, float *__restrict__ dW, int C, int OC,
+                                     int KH, int KW, int ic_slabs, const uint8_t *__restrict__ tbl,
+                                     int accumulate) {
+  const int total = OC * C * KH * KW;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    int kx = i % KW, r = i / KW;
+    int ky = r % KH;
+    r /= KH;
+    int inc = r % C, o = r / C;
+    int unit = (o >> 5) * ic_slabs + (inc >> 5);
+    size_t n = ((((size_t)unit * KW + (KW - 1 - kx)) * KH + ky) * 32 + (inc & 31)) * 32 + (o & 31);
+    float v = src[n];
+    if (tbl && !tbl[inc * OC + o]) v = 0.f;
+    dW[i] = accumulate ? dW[i] + v : v;
+  }
 }
 
 // dst[c] (+)= sum over rows of src[r*len + c] for a tall, narrow matrix (many partial rows of a
@@ -777,9 +853,28 @@ int conv_tc_dw_splits(const b200_ctx *ctx, const ConvGeom &g, int B) {
   return k;
 }
 
-// floats of scratch of the dW pass: the partial rows
+// floats of one partial row of the dW kernel (its own order, channels padded to 32)
+static size_t dw_tc_row(const ConvGeom &g) {
+  TallGeom t = tall_geom(g, 1);
+  return (size_t)(t.Cp / 32) * (t.OCp / 32) * g.KW * g.KH * 32 * 32;
+}
+
+// floats of scratch of the dW pass: the partial rows and their sum
 size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B) {
-  return (size_t)conv_tc_dw_splits(ctx, g, B) * conv_weight_len(g);
+  return ((size_t)conv_tc_dw_splits(ctx, g, B) + 1) * dw_tc_row(g);
+}
+
+// sum the partial rows conv_tc_dw wrote (fixed order) and store them in the reference layout
+int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate) {
+  const size_t row = dw_tc_row(g);
+  float *sum = part + (size_t)splits * row;
+  B200_TRY(merge_rows(ctx, part, splits, row, sum, row, 0, nullptr));
+  TallGeom t = tall_geom(g, 1);
+  const int total = (int)conv_weight_len(g);
+  dw_tc_permute_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(sum, dW, g.C, g.OC, g.KH, g.KW, t.Cp / 32,
+                                                                      g.tbl, accumulate);
+  B200_LAUNCHED();
+  return 0;
 }
 
 int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs) {
@@ -812,7 +907,7 @@ int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *
                         B);
 }
 
-// partial weight gradients: *splits rows of conv_weight_len floats in `part`
+// partial weight gradients: *splits rows in `part` (conv_tc_dw_floats floats), finished by conv_tc_dw_finish
 int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *dys, int B, float *part,
                int *splits) {
   TallGeom t = tall_geom(g, B);
@@ -838,12 +933,29 @@ int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *d
   a.ic_slabs = t.Cp / 32;
   a.ksplits = conv_tc_dw_splits(ctx, g, B);
   a.tmem_cols = pow2_at_least(((g.KW + 3) / 4) * g.KH * 32);
-  a.row_stride = (long long)conv_weight_len(g);
+  a.row_stride = (long long)dw_tc_row(g);
   const size_t smem = dw_tc_smem(g.KH);
   B200_CUDA(cudaFuncSetAttribute(conv_dw_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(a.ksplits, a.ic_slabs * (t.OCp / 32));
+  a.dbg = nullptr;
+  static const bool timing = getenv("B200_TC_TIMING") != nullptr;
+  const int nblk = (int)(grid.x * grid.y);
+  if (timing) B200_CUDA(cudaMalloc(&a.dbg, (size_t)nblk * 8 * sizeof(long long)));
   conv_dw_tc_kernel<<<grid, TCV_THREADS, smem, ctx->stream>>>(dy_hi, dy_lo, x_hi, x_lo, a);
   B200_LAUNCHED();
+  if (timing) {  // diagnostic: cycles of the MMA role and of the epilogue, averaged over blocks
+    std::vector<long long> h((size_t)nblk * 8);
+    B200_CUDA(cudaStreamSynchronize(ctx->stream));
+    B200_CUDA(cudaMemcpy(h.data(), a.dbg, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+    B200_CUDA(cudaFree(a.dbg));
+    double s[8] = {0};
+    for (int i = 0; i < nblk; ++i)
+      for (int k = 0; k < 8; ++k) s[k] += (double)h[(size_t)i * 8 + k] / nblk;
+    fprintf(stderr,
+            "[tc-timing] dW blocks %d stages/block %.2f: mma total %.0f clk, wait full %.0f | epilogue wait %.0f, "
+            "store %.0f\n",
+            nblk, s[2], s[0], s[1], s[3], s[4]);
+  }
   *splits = a.ksplits;
   return 0;
 }

@@ -17,7 +17,7 @@
 //                        frees the stage / publishes the accumulator
 //   warps 0-3            epilogue: tcgen05.ld of their 32 TMEM lanes, bias /
 //                        activation / accumulate, stores to D
-// No multicast is used anywhere; every wait is bounded and a timeout sets the
+// Every load is CTA-local; every wait is bounded and a timeout sets the
 // context's error word, releases TMEM and returns.
 #include "tc_utils.cuh"
 

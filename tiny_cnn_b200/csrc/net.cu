@@ -166,7 +166,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
           if (!L.tc.fwd) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
           int splits = 0;
           B200_TRY(conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits));
-          B200_TRY(merge_rows(ctx, L.tc_part, splits, L.w_len, dW, L.w_len, 0, &L.g));
+          B200_TRY(conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0));
           if (db) B200_TRY(conv_tc_bias_grad(ctx, L.g, L.tc_bsum, B, db, 0));
         } else if (tiled_bwd) {
           int splits = 0;

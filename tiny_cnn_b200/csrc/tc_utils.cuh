@@ -1,6 +1,6 @@
 // tcgen05 (5th-generation tensor core), tensor-memory and TMA wrappers shared by the
 // tensor-core GEMM and convolution kernels.  Everything here is inline PTX for sm_100a;
-// no load uses cluster multicast.
+// every load is CTA-local.
 #pragma once
 
 #include <cuda.h>
