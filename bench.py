@@ -167,11 +167,15 @@ def run_reference(args, rank, world):
 # --------------------------------------------------------------------------------------------
 # own arm
 # --------------------------------------------------------------------------------------------
-def time_kernels(ctx, torch, ops, reps=10):
-    """CUDA-event time of every convolution kernel of the net at batch 256 (forward, dX,
-    dW+db), launched alone on the context stream; returns {name: (ms, flops)}."""
+def time_kernels(ctx, torch, ops, reps=20):
+    """Per convolution pass of the net at batch 256 (forward, dX, dW): CUDA-event time of the
+    pass's main kernel alone (b200_conv2d_time_pass: operand copies and filter matrices prepared
+    outside the timed region) and of the whole operator call (every launch the pass needs).
+    Returns {name: {"ms", "op_ms", "flops", "tensor"}}."""
+    from tiny_cnn_b200._lib import check, ptr
     out = {}
     g = torch.Generator(device="cuda").manual_seed(3)
+    lib, h = ctx.lib, ctx.handle
     for name, w, c, oc, k in CONVS:
         d = ops.conv_params(w, w, c, k, k, oc, True, True)
         x = torch.randn(BATCH, c * w * w, device="cuda", generator=g)
@@ -181,8 +185,6 @@ def time_kernels(ctx, torch, ops, reps=10):
         y = torch.empty(BATCH, oc * w * w, device="cuda")
         dx = torch.empty_like(x)
         dW, db = torch.zeros_like(W), torch.zeros_like(b)
-        lib, h = ctx.lib, ctx.handle
-        from tiny_cnn_b200._lib import check, ptr
 
         def fwd():
             check(lib.b200_conv2d_fwd(h, C.byref(d), ptr(x), ptr(W), ptr(b), ptr(y), BATCH))
@@ -192,7 +194,7 @@ def time_kernels(ctx, torch, ops, reps=10):
 
         def bwd_nodx():
             check(lib.b200_conv2d_bwd(h, C.byref(d), ptr(x), ptr(W), ptr(dy), None, ptr(dW), ptr(db), 0, BATCH))
-        times = {}
+        op = {}
         for key, fn in (("fwd", fwd), ("bwd", bwd), ("dw", bwd_nodx)):
             for _ in range(3):
                 fn()
@@ -203,12 +205,61 @@ def time_kernels(ctx, torch, ops, reps=10):
                 fn()
             e1.record()
             torch.cuda.synchronize()
-            times[key] = e0.elapsed_time(e1) / reps
+            op[key] = e0.elapsed_time(e1) / reps
+        op["dx"] = max(op["bwd"] - op["dw"], 1e-6)
         fl = conv_flops(BATCH, w, c, oc, k)
-        out[f"{name}_fwd"] = (times["fwd"], fl)
-        out[f"{name}_dw"] = (times["dw"], fl)
-        out[f"{name}_dx"] = (max(times["bwd"] - times["dw"], 1e-6), fl)
+        for pi, key in enumerate(("fwd", "dx", "dw")):
+            ms, tc = C.c_float(0), C.c_int(0)
+            check(lib.b200_conv2d_time_pass(h, C.byref(d), ptr(x), ptr(W), ptr(dy), BATCH, pi, reps,
+                                            C.byref(ms), C.byref(tc)))
+            out[f"{name}_{key}"] = {"ms": ms.value, "op_ms": op[key], "flops": fl, "tensor": bool(tc.value)}
     return out
+
+
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; None where no capture of that launch exists
+NCU_DRAM_BYTES = {"conv2_fwd": 19.13e6}
+
+
+def conv_rooflines(kt, peaks):
+    """Per-kernel table and the roofline object of the dominant kernel.  Tensor-core passes
+    compute every fp32 product as three TF32 products, so their ceiling in algorithmic
+    (fp32-equivalent) flop/s is the TF32 rate / 3 = the measured bf16 rate / 6."""
+    peak_fp32 = SM_COUNT * FP32_LANES * 2 * 1.965e9 / 1e12
+    bf16 = peaks.get("bf16_tflops")
+    peak_tc = (bf16 if bf16 else 1590.0) / 6.0
+    src = "of measured" if bf16 else "of fallback"
+    kernels = {}
+    for k, v in kt.items():
+        tf = v["flops"] / (v["ms"] * 1e-3) / 1e12
+        peak = peak_tc if v["tensor"] else peak_fp32
+        kernels[k] = {"ms": round(v["ms"], 4), "op_ms": round(v["op_ms"], 4), "tflops": round(tf, 3),
+                      "engine": "tcgen05 3xTF32" if v["tensor"] else "fp32 FFMA",
+                      "frac_of_peak": round(tf / peak, 4)}
+    # the kernel function with the largest share of the step: conv_tc_kernel runs the forward and
+    # dX passes of every tensor-core layer; report its longest launch
+    fam = [k for k, v in kt.items() if v["tensor"] and not k.endswith("_dw")]
+    pool = fam if fam else list(kt)
+    dom = max(pool, key=lambda k: (round(kt[k]["ms"], 3), k.endswith("_fwd")))
+    v = kt[dom]
+    tf = v["flops"] / (v["ms"] * 1e-3) / 1e12
+    tensor = v["tensor"]
+    peak = peak_tc if tensor else peak_fp32
+    conv_ms = sum(x["ms"] for x in kt.values())
+    conv_fl = sum(x["flops"] for x in kt.values())
+    roofline = {
+        "kernel": ("conv_tc_kernel" if tensor else "conv FFMA kernel") + f" ({dom})",
+        "bound": "tensor" if tensor else "fp32",
+        "achieved": round(tf, 3), "peak": round(peak, 2), "unit": "TFLOP/s", "frac": round(tf / peak, 4),
+        "traffic": NCU_DRAM_BYTES.get(dom),
+        "peak_source": (f"algorithmic fp32 flop/s; ceiling = bf16 tensor peak {bf16} TFLOP/s {src} / 2 (TF32 rate) "
+                        "/ 3 (three TF32 products per fp32 product)") if tensor else
+                       "fp32 FFMA: 148 SMs x 128 lanes x 2 flop x clocks.max.sm 1965 MHz (no measured fp32 figure)",
+        "tensor_pipe_tflops": round(3 * tf, 1) if tensor else None,
+        "conv_main_kernels_all": {"ms": round(conv_ms, 4), "tflops": round(conv_fl / (conv_ms * 1e-3) / 1e12, 3)},
+        "fp32_ffma_peak": round(peak_fp32, 2), "hbm_gbs": peaks.get("hbm_gbs"),
+    }
+    return kernels, roofline
 
 
 def run_b200(args, rank, world, local_rank):
@@ -304,27 +355,11 @@ def run_b200(args, rank, world, local_rank):
     if rank == 0:
         # per-kernel roofline of the convolution kernels, timed alone with CUDA events
         kt = time_kernels(ctx, torch, ops)
-        peak_fp32 = SM_COUNT * FP32_LANES * 2 * 1.965e9 / 1e12
         peaks = {}
         mp = ROOT / "MEASURED_PEAKS.json"
         if mp.exists():
             peaks = json.loads(mp.read_text())
-        kernels = {k: {"ms": round(v[0], 4), "tflops": round(v[1] / (v[0] * 1e-3) / 1e12, 3),
-                       "frac_fp32_peak": round(v[1] / (v[0] * 1e-3) / 1e12 / peak_fp32, 4)}
-                   for k, v in kt.items()}
-        dom = max(kt, key=lambda k: kt[k][0])
-        achieved = kt[dom][1] / (kt[dom][0] * 1e-3) / 1e12
-        conv_ms = sum(v[0] for v in kt.values())
-        conv_fl = sum(v[1] for v in kt.values())
-        roofline = {
-            "kernel": dom, "bound": "fp32", "achieved": round(achieved, 3), "peak": round(peak_fp32, 2),
-            "unit": "TFLOP/s", "frac": round(achieved / peak_fp32, 4), "traffic": None,
-            "peak_source": "fp32 FFMA: 148 SMs x 128 lanes x 2 flop x clocks.max.sm 1965 MHz (no measured "
-                           "fp32 figure in MEASURED_PEAKS.json; its bf16 tensor figure is "
-                           f"{peaks.get('bf16_tflops')} TFLOP/s, hbm {peaks.get('hbm_gbs')} GB/s)",
-            "conv_fwd_bwd_all": {"ms": round(conv_ms, 4), "tflops": round(conv_fl / (conv_ms * 1e-3) / 1e12, 3),
-                                 "frac": round(conv_fl / (conv_ms * 1e-3) / 1e12 / peak_fp32, 4)},
-        }
+        kernels, roofline = conv_rooflines(kt, peaks)
         cpu = cpu_baseline() if world == 1 else None
         line = {
             "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
@@ -333,6 +368,8 @@ def run_b200(args, rank, world, local_rank):
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "global_batch": global_batch,
                        "parallelism": f"dp{world}",
+                       "arithmetic": "fp32 results; conv2/conv3 passes on tcgen05 tensor cores as 3xTF32 "
+                                     "(hi/lo split, fp32 accumulation), conv1 and the rest fp32 FFMA",
                        "l2": "8 resident input batches rotate through the step; activations + gradients "
                              "touched per step are about 130 MB, larger than the 126 MB L2",
                        "step": "CUDA graph of forward+backward+update" if world == 1 else

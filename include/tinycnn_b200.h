@@ -143,6 +143,20 @@ B200_API int b200_conv2d_bwd(b200_ctx *ctx, const b200_conv_desc *d, const float
                              float *db, int accumulate, int batch);
 
 /*
+ * Measurement hook (no counterpart in the reference): average device time in
+ * milliseconds of the MAIN kernel of one convolution pass -- pass 0 forward,
+ * 1 dX, 2 dW -- over `reps` launches, timed with CUDA events on the context's
+ * stream.  The operand copies and filter matrices a pass needs are prepared
+ * once, outside the timed region; the small prepare / merge kernels are not
+ * part of the figure (on the tiled FFMA path the filter re-layout kernel is,
+ * because that launcher issues both).  `*on_tensor_cores` reports which kernel
+ * family ran.  All pointers are DEVICE memory.
+ */
+B200_API int b200_conv2d_time_pass(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                                   const float *W, const float *dout, int batch, int pass, int reps,
+                                   float *ms, int *on_tensor_cores);
+
+/*
  * Weight gradient only -- dW (+)= sum_n dW_n, db (+)= sum_n db_n, the same
  * values b200_conv2d_bwd produces -- for callers that are not allowed to
  * allocate device memory at call time.  It has NO counterpart in the reference.

@@ -91,6 +91,7 @@ SIGNATURES = {
     "b200_conv2d_fwd": (_i, [_vp, _cd, _vp, _vp, _vp, _vp, _i]),
     "b200_conv2d_bwd": (_i, [_vp, _cd, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "b200_conv2d_dw_noalloc": (_i, [_vp, _cd, _vp, _vp, _vp, _vp, _i, _i]),
+    "b200_conv2d_time_pass": (_i, [_vp, _cd, _vp, _vp, _vp, _i, _i, _i, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "b200_conv2d_fwd_host": (_i, [_vp, _cd, _vp, _vp, _vp, _vp, _i]),
     "b200_conv2d_bwd_host": (_i, [_vp, _cd, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "b200_fc_fwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i]),

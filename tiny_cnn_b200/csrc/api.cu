@@ -118,6 +118,62 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
   return 0;
 }
 
+// Device time of the main kernel of one pass (see b200_conv2d_time_pass).
+int conv_time_pass_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                        const float *dout, int batch, int pass, int reps, float *ms, int *on_tc) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(batch >= 1 && reps >= 1 && pass >= 0 && pass <= 2 && ms, "conv2d_time_pass: bad argument");
+  ConvGeom g;
+  B200_TRY(conv_geom_from_desc(ctx, d, &g));
+  B200_REQUIRE(in && W && (dout || pass == 0), "conv2d_time_pass: NULL buffer");
+  ConvTcUse tc = conv_tc_use(ctx, g, d->algo);
+  const bool tiled = use_tiled(d, g) && (pass == 0 || g.OW <= 64);
+  const bool use_tc = pass == 0 ? tc.fwd : pass == 1 ? tc.dx : tc.dw;
+  B200_REQUIRE(use_tc || tiled, "conv2d_time_pass: only the tensor-core and the tiled kernels are timed");
+  const size_t in_len = (size_t)batch * g.C * g.HI * g.WI, out_len = (size_t)batch * g.OC * g.OH * g.OW;
+  size_t n_res = align_up(in_len > out_len ? in_len : out_len, 64);
+  size_t n_xs = align_up(conv_tc_tall_floats(g, batch, 0), 64), n_dys = align_up(conv_tc_tall_floats(g, batch, 1), 64);
+  size_t n_wt = align_up(use_tc ? conv_tc_filter_floats(ctx, g, pass == 1) : 0, 64);
+  size_t n_part = use_tc ? align_up(conv_tc_dw_floats(ctx, g, batch), 64) : 0;
+  size_t n_tiled = 0;
+  if (!use_tc)
+    n_tiled = pass == 0 ? conv_tiled_fwd_scratch(g) : pass == 1 ? conv_tiled_dx_scratch(g)
+                                                                 : conv_tiled_dw_scratch(ctx, g, batch);
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, (n_res + n_xs + n_dys + n_wt + n_part + n_tiled + 64) * sizeof(float), &scratch));
+  float *res = static_cast<float *>(scratch), *xs = res + n_res, *dys = xs + n_xs, *wt = dys + n_dys;
+  float *part = wt + n_wt, *ts = part + n_part;
+  cudaEvent_t e0, e1;
+  B200_CUDA(cudaEventCreate(&e0));
+  B200_CUDA(cudaEventCreate(&e1));
+  int splits = 0, rc = 0;
+  auto run = [&](int prep) -> int {
+    if (use_tc) {
+      if (pass == 0) return conv_tc_fwd(ctx, g, xs, W, nullptr, res, batch, B200_ACT_NONE, wt, prep);
+      if (pass == 1) return conv_tc_dx(ctx, g, dys, W, res, batch, wt, prep);
+      return conv_tc_dw(ctx, g, xs, dys, batch, part, &splits);
+    }
+    if (pass == 0) return conv_tiled_fwd(ctx, g, in, W, nullptr, res, batch, B200_ACT_NONE, ts);
+    if (pass == 1) return conv_tiled_dx(ctx, g, W, dout, res, batch, ts);
+    return conv_tiled_dw_partials(ctx, g, in, dout, batch, ts, &splits);
+  };
+  if (use_tc && pass != 1) rc = conv_tc_tall_x(ctx, g, in, batch, xs);
+  if (!rc && use_tc && pass != 0) rc = conv_tc_tall_dy(ctx, g, dout, batch, dys, nullptr);
+  if (!rc) rc = run(1);  // warm-up, filter matrices, tile choice
+  if (!rc) rc = cudaEventRecord(e0, ctx->stream) == cudaSuccess ? 0 : 1;
+  for (int i = 0; i < reps && !rc; ++i) rc = run(0);
+  if (!rc) rc = cudaEventRecord(e1, ctx->stream) == cudaSuccess ? 0 : 1;
+  if (!rc) rc = cudaEventSynchronize(e1) == cudaSuccess ? 0 : 1;
+  float t = 0.f;
+  if (!rc) rc = cudaEventElapsedTime(&t, e0, e1) == cudaSuccess ? 0 : 1;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  B200_REQUIRE(rc == 0, "conv2d_time_pass: a launch or an event call failed (%s)", b200_last_error());
+  *ms = t / reps;
+  if (on_tc) *on_tc = use_tc ? 1 : 0;
+  return 0;
+}
+
 // ---- host staging ------------------------------------------------------------
 
 // Carves the context arena into device buffers for one *_host call.
@@ -184,6 +240,11 @@ int b200_conv2d_bwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, con
                     const float *dout, float *din, float *dW, float *db, int accumulate,
                     int batch) {
   return conv_bwd_impl(ctx, d, in, W, dout, din, dW, db, accumulate, batch);
+}
+
+int b200_conv2d_time_pass(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                          const float *dout, int batch, int pass, int reps, float *ms, int *on_tensor_cores) {
+  return conv_time_pass_impl(ctx, d, in, W, dout, batch, pass, reps, ms, on_tensor_cores);
 }
 
 int b200_conv2d_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,

@@ -172,10 +172,11 @@ int conv_tc_bias_grad(b200_ctx *ctx, const ConvGeom &g, const float *bsum, int B
 size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B);
 int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs);
 int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, float *dys, float *bsum);
+// `prep` = 0 reuses the filter matrices an earlier call left in `wt` (same weights)
 int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,
-                float *out, int B, int act, float *wt);
+                float *out, int B, int act, float *wt, int prep = 1);
 int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *W, float *din, int B,
-               float *wt);
+               float *wt, int prep = 1);
 int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *dys, int B, float *part,
                int *splits);
 int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate);

@@ -397,14 +397,17 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
             half ^= 1;
           }
           if (valid) {
+            // bias first, all at once: loads interleaved with the stores would wait on each of them
+            float bv[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int oc = grp * a.gs + c0 + j;
-              if (oc < a.N) {
-                float res = acc[j];
-                if (a.bias) res += a.bias[oc];
-                obase[oc * plane] = apply_act(res, a.act);
-              }
+              bv[j] = (a.bias != nullptr && oc < a.N) ? __ldg(a.bias + oc) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int oc = grp * a.gs + c0 + j;
+              if (oc < a.N) obase[oc * plane] = apply_act(acc[j] + bv[j], a.act);
             }
           }
         }
@@ -890,18 +893,18 @@ int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, 
 }
 
 int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,
-                float *out, int B, int act, float *wt) {
+                float *out, int B, int act, float *wt, int prep) {
   TallGeom t = tall_geom(g, B);
-  B200_TRY(filter_prep(ctx, g, W, g.OC, t.Cp / 32, 0, wt));
+  if (prep) B200_TRY(filter_prep(ctx, g, W, g.OC, t.Cp / 32, 0, wt));
   return launch_conv_tc(ctx, xs, t.Cp, g.WI, t.rows, t.period, wt, g.KH, g.KW, g.pad_t, g.pad_l, g.OC, out,
                         g.OH, g.OW, g.has_bias ? bias : nullptr, act, B);
 }
 
 int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *W, float *din, int B,
-               float *wt) {
+               float *wt, int prep) {
   TallGeom t = tall_geom(g, B);
   const int period = dy_period(g);
-  B200_TRY(filter_prep(ctx, g, W, g.C, t.OCp / 32, 1, wt));
+  if (prep) B200_TRY(filter_prep(ctx, g, W, g.C, t.OCp / 32, 1, wt));
   return launch_conv_tc(ctx, dys, t.OCp, g.OW, (long long)B * period, period, wt, g.KH, g.KW,
                         g.KH - 1 - g.pad_t, g.KW - 1 - g.pad_l, g.C, din, g.HI, g.WI, nullptr, B200_ACT_NONE,
                         B);

@@ -170,16 +170,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
         if (row < a.M) {
           float *drow = a.D + (size_t)row * a.N + n0 + c0;
+          // all loads before the stores: interleaved, every load would wait for the store before it
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             int col = n0 + c0 + j;
             if (col < a.N) {
-              float x = v[j];
-              if (a.bias) x += a.bias[col];
-              if (a.accumulate) x += drow[j];
-              drow[j] = apply_act(x, a.act);
+              if (a.bias) v[j] += __ldg(a.bias + col);
+              if (a.accumulate) v[j] += drow[j];
             }
           }
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (n0 + c0 + j < a.N) drow[j] = apply_act(v[j], a.act);
         }
       }
     }
