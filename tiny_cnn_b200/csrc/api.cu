@@ -68,7 +68,7 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
     return 0;
   }
   ConvTcUse tc = conv_tc_use(ctx, g, d->algo);
-  B200_REQUIRE(d->algo != 3 || tc.dw,
+  B200_REQUIRE(d->algo != 3 || tc.dw || tc.dw_small,
                "conv2d_bwd: tensor-core kernels need stride 1, dilation 1, windows <= 8x8, <= 256 channels");
   if (!din) tc.dx = false;
   bool tiled = use_tiled(d, g) && g.OW <= 64;
@@ -83,13 +83,15 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
   size_t n_wdx = tc.dx ? align_up(conv_tc_filter_floats(ctx, g, 1), 64) : 0;
   size_t n_part = tc.dw ? align_up(conv_tc_dw_floats(ctx, g, batch), 64) : 0;
   size_t n_tdx = (din && !tc.dx && tiled) ? align_up(conv_tiled_dx_scratch(g), 64) : 0;
-  size_t n_tdw = (!tc.dw && tiled) ? conv_tiled_dw_scratch(ctx, g, batch) : 0;
+  size_t n_small = tc.dw_small ? align_up(conv_dw_small_floats(ctx, g, batch), 64) : 0;
+  size_t n_tdw = (!tc.dw && !tc.dw_small && tiled) ? conv_tiled_dw_scratch(ctx, g, batch) : 0;
   void *scratch = nullptr;
-  B200_TRY(ctx_scratch(ctx, (n_dys + n_bs + n_xs + n_wdx + n_part + n_tdx + n_tdw + 64) * sizeof(float),
+  B200_TRY(ctx_scratch(ctx, (n_dys + n_bs + n_xs + n_wdx + n_part + n_small + n_tdx + n_tdw + 64) * sizeof(float),
                        &scratch));
   float *dys = static_cast<float *>(scratch);
   float *bs = dys + n_dys, *xs = bs + n_bs, *wdx = xs + n_xs, *part = wdx + n_wdx;
-  float *s_dx = part + n_part, *s_dw = s_dx + n_tdx;
+  float *small = part + n_part;
+  float *s_dx = small + n_small, *s_dw = s_dx + n_tdx;
   if (need_dys) B200_TRY(conv_tc_tall_dy(ctx, g, dout, batch, dys, bs_rows ? bs : nullptr));
   // dX
   if (din) {
@@ -109,6 +111,7 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
     if (g.has_bias) B200_TRY(conv_tc_bias_grad(ctx, g, bs, batch, db, accumulate));
     return 0;
   }
+  if (tc.dw_small) return conv_dw_small(ctx, g, in, dout, batch, small, dW, db, accumulate);
   if (!tiled) return conv_general_dw(ctx, g, in, dout, dW, db, accumulate, batch);
   int splits = 0;
   B200_TRY(conv_tiled_dw_partials(ctx, g, in, dout, batch, s_dw, &splits));
@@ -128,13 +131,14 @@ int conv_time_pass_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
   B200_REQUIRE(in && W && (dout || pass == 0), "conv2d_time_pass: NULL buffer");
   ConvTcUse tc = conv_tc_use(ctx, g, d->algo);
   const bool tiled = use_tiled(d, g) && (pass == 0 || g.OW <= 64);
-  const bool use_tc = pass == 0 ? tc.fwd : pass == 1 ? tc.dx : tc.dw;
+  const bool use_tc = pass == 0 ? tc.fwd : pass == 1 ? tc.dx : (tc.dw || tc.dw_small);
   B200_REQUIRE(use_tc || tiled, "conv2d_time_pass: only the tensor-core and the tiled kernels are timed");
   const size_t in_len = (size_t)batch * g.C * g.HI * g.WI, out_len = (size_t)batch * g.OC * g.OH * g.OW;
   size_t n_res = align_up(in_len > out_len ? in_len : out_len, 64);
   size_t n_xs = align_up(conv_tc_tall_floats(g, batch, 0), 64), n_dys = align_up(conv_tc_tall_floats(g, batch, 1), 64);
   size_t n_wt = align_up(use_tc ? conv_tc_filter_floats(ctx, g, pass == 1) : 0, 64);
-  size_t n_part = use_tc ? align_up(conv_tc_dw_floats(ctx, g, batch), 64) : 0;
+  size_t n_part = use_tc ? align_up(tc.dw_small ? conv_dw_small_floats(ctx, g, batch) + conv_weight_len(g) + g.OC
+                                               : conv_tc_dw_floats(ctx, g, batch), 64) : 0;
   size_t n_tiled = 0;
   if (!use_tc)
     n_tiled = pass == 0 ? conv_tiled_fwd_scratch(g) : pass == 1 ? conv_tiled_dx_scratch(g)
@@ -151,14 +155,19 @@ int conv_time_pass_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
     if (use_tc) {
       if (pass == 0) return conv_tc_fwd(ctx, g, xs, W, nullptr, res, batch, B200_ACT_NONE, wt, prep);
       if (pass == 1) return conv_tc_dx(ctx, g, dys, W, res, batch, wt, prep);
+      if (tc.dw_small) {  // includes its merge and permute launches
+        float *gw = part + conv_dw_small_floats(ctx, g, batch);
+        return conv_dw_small(ctx, g, in, dout, batch, part, gw, gw + conv_weight_len(g), 0);
+      }
       return conv_tc_dw(ctx, g, xs, dys, batch, part, &splits);
     }
     if (pass == 0) return conv_tiled_fwd(ctx, g, in, W, nullptr, res, batch, B200_ACT_NONE, ts);
     if (pass == 1) return conv_tiled_dx(ctx, g, W, dout, res, batch, ts);
     return conv_tiled_dw_partials(ctx, g, in, dout, batch, ts, &splits);
   };
-  if (use_tc && pass != 1) rc = conv_tc_tall_x(ctx, g, in, batch, xs);
-  if (!rc && use_tc && pass != 0) rc = conv_tc_tall_dy(ctx, g, dout, batch, dys, nullptr);
+  const bool slab = use_tc && !(pass == 2 && tc.dw_small);
+  if (slab && pass != 1) rc = conv_tc_tall_x(ctx, g, in, batch, xs);
+  if (!rc && slab && pass != 0) rc = conv_tc_tall_dy(ctx, g, dout, batch, dys, nullptr);
   if (!rc) rc = run(1);  // warm-up, filter matrices, tile choice
   if (!rc) rc = cudaEventRecord(e0, ctx->stream) == cudaSuccess ? 0 : 1;
   for (int i = 0; i < reps && !rc; ++i) rc = run(0);

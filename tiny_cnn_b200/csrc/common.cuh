@@ -163,6 +163,7 @@ bool conv_tc_ok(const b200_ctx *ctx, const ConvGeom &g);
 // none, 0 = by the context's conv_tensor_cores option
 struct ConvTcUse {
   bool fwd, dx, dw;
+  bool dw_small;  // dW through the im2col form for layers with few input channels (conv_dw_small)
 };
 ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo);
 size_t conv_tc_tall_floats(const ConvGeom &g, int B, int which);  // 0: input, 1: dY
@@ -180,6 +181,12 @@ int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *
 int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *dys, int B, float *part,
                int *splits);
 int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate);
+
+// dW of stride-1 layers with in_c*KH*KW <= 128 on the tensor cores, straight from the CHW tensors
+bool conv_dw_small_ok(const b200_ctx *ctx, const ConvGeom &g);
+size_t conv_dw_small_floats(const b200_ctx *ctx, const ConvGeom &g, int B);
+int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout, int B, float *part,
+                  float *dW, float *db, int accumulate);
 
 // dst (+)= sum_r src[r*stride + i], rows summed in order; optional connection
 // mask for convolution weights (entries of unconnected pairs are left alone

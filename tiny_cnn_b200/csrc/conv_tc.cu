@@ -798,21 +798,32 @@ bool conv_tc_ok(const b200_ctx *ctx, const ConvGeom &g) {
 }
 
 ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo) {
-  ConvTcUse u = {false, false, false};
-  if (algo == 1 || algo == 2 || !conv_tc_ok(ctx, g)) return u;
+  ConvTcUse u = {false, false, false, false};
+  if (algo == 1 || algo == 2) return u;
   if (algo != 3 && ctx->conv_tensor_cores == 0) return u;
-  if (algo == 3 || ctx->conv_tensor_cores >= 2) {
-    u.fwd = u.dx = u.dw = true;
-  } else {
-    // a pass pays off when both channel counts fill a good part of a 32-wide slab / MMA width
-    u.fwd = u.dx = u.dw = g.C >= 16 && g.OC >= 16;
+  if (conv_tc_ok(ctx, g)) {
+    if (algo == 3 || ctx->conv_tensor_cores >= 2) {
+      u.fwd = u.dx = u.dw = true;
+    } else {
+      // a pass pays off when both channel counts fill a good part of a 32-wide slab / MMA width
+      u.fwd = u.dx = u.dw = g.C >= 16 && g.OC >= 16;
+    }
+    if (algo != 3) {
+      if (const char *e = getenv("B200_CONV_TC")) {  // bit 0 forward, bit 1 dX, bit 2 dW
+        int m = atoi(e);
+        u.fwd = (m & 1) != 0;
+        u.dx = (m & 2) != 0;
+        u.dw = (m & 4) != 0;
+      }
+    }
   }
-  if (algo != 3) {
-    if (const char *e = getenv("B200_CONV_TC")) {  // bit 0 forward, bit 1 dX, bit 2 dW
-      int m = atoi(e);
-      u.fwd = (m & 1) != 0;
-      u.dx = (m & 2) != 0;
-      u.dw = (m & 4) != 0;
+  // few input channels: the im2col form of dW instead of the slab form
+  if (conv_dw_small_ok(ctx, g) && (!u.dw || g.C < 16)) {
+    bool want = true;
+    if (const char *e = getenv("B200_CONV_TC")) want = algo == 3 || (atoi(e) & 8) != 0;
+    if (want) {
+      u.dw = false;
+      u.dw_small = true;
     }
   }
   return u;
@@ -960,6 +971,399 @@ int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *d
             nblk, s[2], s[0], s[1], s[3], s[4]);
   }
   *splits = a.ksplits;
+  return 0;
+}
+
+// ---- dW of layers with few input channels: explicit transposed im2col operand -----------------
+//
+// When in_c * KH * KW <= 128 (the first layer of a network: 3 x 5 x 5 = 75) a 32-channel slab would
+// be almost all padding.  Here the contraction still runs over pixels, but both operands are
+// K-major with 32 consecutive pixels of one output row per 128-byte row:
+//   B[o][p]  = dY[b][o][y][x0 + p]                  a TMA tile straight from the CHW gradient
+//   A[k][p]  = Xpad[b][c][y + ky][x0 + p + kx]      k = (c*KH + ky)*KW + kx, written by the four
+//              converter warps from the raw input rows (one TMA tile) as TF32 hi / lo tiles
+//   D[k][o] += A * B^T                              M = 128 (k padded), N = out channels, 4 k-steps
+// so dW needs 12 MMAs per 32 pixels.  The converter warps also split B into hi / lo in place and
+// keep the bias-gradient sums.  Per-CTA partial results are merged in fixed order afterwards.
+
+namespace {
+
+constexpr int TCS_MAX_STAGES = 6;
+constexpr int TCS_PX = 32;          // pixels per step (one 128-byte operand row)
+constexpr int TCS_GROUPS = 4;       // converter groups; group g converts the steps i with i % 4 == g
+constexpr int TCS_GROUP_WARPS = 2;
+constexpr int TCS_CONV_WARPS = TCS_GROUPS * TCS_GROUP_WARPS;  // then one TMA warp and one MMA warp
+constexpr int TCS_THREADS = (TCS_CONV_WARPS + 2) * 32;
+
+struct TcDwSmallArgs {
+  float *part;          // [ksplits][row] with row = 128 * OCp (D[k][o]) + OCp (bias sums)
+  int *err;
+  int C, OC, OCp, KH, KW, pad_t, pad_l;
+  int OH, OW, nxb;      // output extent, 32-pixel blocks per output row
+  int Kreal;            // C * KH * KW
+  int bw;               // floats per raw input row in shared memory
+  int nsteps, ksplits;
+  int nst;              // pipeline stages
+  int tmem_cols;
+  long long row;
+  long long *dbg;       // optional [blocks][8] cycle counters (B200_TC_TIMING=1), else nullptr
+};
+
+__global__ void __launch_bounds__(TCS_THREADS, 1)
+  conv_dw_small_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap dy_map,
+                          const TcDwSmallArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t AB = 128u * 128u;                      // A tile (hi or lo): 128 rows of 128 bytes
+  const uint32_t BB = (uint32_t)a.OCp * 128u;           // B tile (hi or lo)
+  const uint32_t XB = ((uint32_t)(a.C * a.KH * a.bw * 4) + 1023u) & ~1023u;  // raw input rows
+  const uint32_t STAGE = 2 * AB + 2 * BB + XB;
+  uint64_t *tma_full = reinterpret_cast<uint64_t *>(smem + (size_t)a.nst * STAGE);
+  uint64_t *op_full = tma_full + TCS_MAX_STAGES;
+  uint64_t *op_empty = op_full + TCS_MAX_STAGES;
+  uint64_t *accum = op_empty + TCS_MAX_STAGES;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum + 1);
+  float *bsum_s = reinterpret_cast<float *>(tmem_slot + 4);   // [group][8 pixel quads][OCp] bias partials
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int s_begin = (int)((long long)blockIdx.x * a.nsteps / a.ksplits);
+  const int s_end = (int)((long long)(blockIdx.x + 1) * a.nsteps / a.ksplits);
+  if (tid == 0) {
+    for (int s = 0; s < a.nst; ++s) {
+      mbar_init(&tma_full[s], 1);
+      mbar_init(&op_full[s], TCS_GROUP_WARPS);
+      mbar_init(&op_empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    mbar_fence_init();
+  }
+  if (warp == TCS_CONV_WARPS) tmem_alloc(tmem_slot, (uint32_t)a.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool failed = false;
+
+  if (warp == TCS_CONV_WARPS && lane == 0) {
+    // ---- TMA producer: raw input rows and the gradient tile of each step ----------------------
+    long long w = 0, t0 = clock64(), tq;
+    for (int s = s_begin; s < s_end; ++s) {
+      const uint32_t i = s - s_begin, st = i % a.nst, use = i / a.nst;
+      tq = clock64();
+      if (use > 0 && !mbar_wait_bounded(&op_empty[st], (use - 1) & 1)) {
+        failed = true;
+        break;
+      }
+      w += clock64() - tq;
+      if (a.dbg && s == s_end - 1) {
+        a.dbg[blockIdx.x * 8 + 0] = clock64() - t0;
+        a.dbg[blockIdx.x * 8 + 1] = w;
+      }
+      const int xb = s % a.nxb, by = s / a.nxb, y = by % a.OH, b = by / a.OH;
+      const int x0 = xb * TCS_PX;
+      const int xs = (x0 - a.pad_l) & ~3;  // aligned start column of the raw rows (floor to 4)
+      uint8_t *p = smem + (size_t)st * STAGE;
+      mbar_expect_tx(&tma_full[st], BB + (uint32_t)(a.C * a.KH * a.bw * 4));
+      tma_load_4d(p + 2 * AB, &dy_map, x0, 0, y, b, &tma_full[st]);
+      tma_load_4d(p + 2 * AB + 2 * BB, &x_map, xs, y - a.pad_t, 0, b, &tma_full[st]);
+    }
+  } else if (warp == TCS_CONV_WARPS + 1 && lane == 0) {
+    // ---- MMA issuer ---------------------------------------------------------------------------
+    // the hi and lo gradient tiles are neighbours in shared memory: A_hi * [B_hi | B_lo] is one
+    // instruction of width 2*OCp (columns OCp.. hold the A_hi*B_lo part, added in the epilogue)
+    const uint32_t idesc1 = umma_idesc_tf32(128, a.OCp), idesc2 = umma_idesc_tf32(128, 2 * a.OCp);
+    long long w = 0, t0 = clock64(), tq;
+    for (int s = s_begin; s < s_end && !failed; ++s) {
+      const uint32_t i = s - s_begin, st = i % a.nst;
+      tq = clock64();
+      if (!mbar_wait_bounded(&op_full[st], (i / a.nst) & 1)) {
+        failed = true;
+        break;
+      }
+      w += clock64() - tq;
+      if (a.dbg && s == s_end - 1) {
+        a.dbg[blockIdx.x * 8 + 2] = clock64() - t0;
+        a.dbg[blockIdx.x * 8 + 3] = w;
+      }
+      tc_fence_after();
+      const uint32_t base = smem_u32(smem + (size_t)st * STAGE);
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        const uint64_t ahi = umma_desc(base + k4 * 32, 16, 1024, 2);
+        const uint64_t alo = umma_desc(base + AB + k4 * 32, 16, 1024, 2);
+        const uint64_t b = umma_desc(base + 2 * AB + k4 * 32, 16, 1024, 2);
+        umma_tf32(tmem_base, ahi, b, idesc2, (i | k4) != 0);
+        umma_tf32(tmem_base, alo, b, idesc1, 1);
+      }
+      umma_commit(&op_empty[st]);
+    }
+    if (!failed) umma_commit(accum);
+  } else if (warp < TCS_CONV_WARPS) {
+    // ---- converters: im2col rows and the hi / lo split, then the epilogue ----------------------
+    const int KK = a.KH * a.KW;
+    const int grp = warp / TCS_GROUP_WARPS, gtid = tid - grp * (TCS_GROUP_WARPS * 32);
+    constexpr int NCT = TCS_GROUP_WARPS * 32;  // threads of one group
+    constexpr int NI = 128 * 8 / NCT;          // (row k, pixel quad) items per thread: 128 rows x 8 quads per step
+    // The items a thread converts are the same in every step: their source and destination offsets
+    // are computed once.  Rows beyond the real taps are zeroed once (by group 0).
+    int soff[NI];       // floats into the raw rows (without the step's column offset), -1: no tap
+    uint32_t doff[NI];  // bytes into the A tile
+#pragma unroll
+    for (int j = 0; j < NI; ++j) {
+      const int it = gtid + NCT * j, k = it >> 3, quad = it & 7;
+      doff[j] = (uint32_t)k * 128u + (uint32_t)((quad ^ (k & 7)) << 4);
+      if (k < a.Kreal) {
+        const int c = k / KK, r = k - c * KK, ky = r / a.KW, kx = r - ky * a.KW;
+        soff[j] = (c * a.KH + ky) * a.bw + kx + quad * 4;
+      } else {
+        soff[j] = -1;
+        if (grp == 0) {
+          for (int st = 0; st < a.nst; ++st) {
+            *reinterpret_cast<float4 *>(smem + (size_t)st * STAGE + doff[j]) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(smem + (size_t)st * STAGE + AB + doff[j]) = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+      }
+    }
+    // all groups wait until the zero rows are in place and published to the tensor core's proxy
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TCS_CONV_WARPS * 32) : "memory");
+    constexpr int NB = 128 * 8 / NCT;  // at most 128 out channels x 8 quads per step
+    float bacc[NB];                    // bias partials of the (o, quad) items this thread owns
+#pragma unroll
+    for (int q = 0; q < NB; ++q) bacc[q] = 0.f;
+    long long w = 0, t0 = clock64(), tq;
+    for (int s = s_begin + grp; s < s_end; s += TCS_GROUPS) {
+      const uint32_t i = s - s_begin, st = i % a.nst;
+      tq = clock64();
+      if (!mbar_wait_bounded(&tma_full[st], (i / a.nst) & 1)) {
+        failed = true;
+        break;
+      }
+      w += clock64() - tq;
+      uint8_t *p = smem + (size_t)st * STAGE;
+      const int x0 = (s % a.nxb) * TCS_PX;
+      const int d = (x0 - a.pad_l) - ((x0 - a.pad_l) & ~3);  // offset of the first needed column
+      const float *xr = reinterpret_cast<const float *>(p + 2 * AB + 2 * BB) + d;
+#pragma unroll
+      for (int j = 0; j < NI; ++j) {
+        if (soff[j] >= 0) {
+          const float *src = xr + soff[j];
+          float h[4], l[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) split_tf32_rn(src[q], h[q], l[q]);
+          *reinterpret_cast<float4 *>(p + doff[j]) = make_float4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<float4 *>(p + AB + doff[j]) = make_float4(l[0], l[1], l[2], l[3]);
+        }
+      }
+      // B: split the gradient tile in place (hi) and into the lo tile; bias partial sums
+#pragma unroll
+      for (int slot = 0; slot < NB; ++slot) {
+        const int it = gtid + NCT * slot;
+        if (it < a.OCp * 8) {
+          const int o = it >> 3, quad = it & 7;
+          const uint32_t off = (uint32_t)o * 128u + (uint32_t)((quad ^ (o & 7)) << 4);
+          float4 v = *reinterpret_cast<float4 *>(p + 2 * AB + off);
+          float h[4], l[4];
+          split_tf32_rn(v.x, h[0], l[0]);
+          split_tf32_rn(v.y, h[1], l[1]);
+          split_tf32_rn(v.z, h[2], l[2]);
+          split_tf32_rn(v.w, h[3], l[3]);
+          *reinterpret_cast<float4 *>(p + 2 * AB + off) = make_float4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<float4 *>(p + 2 * AB + BB + off) = make_float4(l[0], l[1], l[2], l[3]);
+          bacc[slot] += (v.x + v.y) + (v.z + v.w);
+        }
+      }
+      // generic-proxy writes -> visible to the tensor core (async proxy), then hand over
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&op_full[st]);
+    }
+    if (a.dbg && tid == 0) {
+      a.dbg[blockIdx.x * 8 + 4] = clock64() - t0;
+      a.dbg[blockIdx.x * 8 + 5] = w;
+    }
+    // ---- epilogue ------------------------------------------------------------------------------
+    float *row = a.part + (size_t)blockIdx.x * a.row;
+#pragma unroll
+    for (int slot = 0; slot < NB; ++slot) {
+      const int it = gtid + NCT * slot;
+      if (it < a.OCp * 8) bsum_s[(grp * 8 + (it & 7)) * a.OCp + (it >> 3)] = bacc[slot];
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TCS_CONV_WARPS * 32) : "memory");
+    for (int o = tid; o < a.OCp; o += TCS_CONV_WARPS * 32) {
+      float t = bsum_s[o];
+#pragma unroll
+      for (int q = 1; q < TCS_GROUPS * 8; ++q) t += bsum_s[q * a.OCp + o];
+      row[(size_t)128 * a.OCp + o] = t;
+    }
+    if (warp < 4 && s_end > s_begin && !failed) {
+      if (!mbar_wait_bounded(accum, 0)) failed = true;
+      tc_fence_after();
+    }
+    if (warp < 4 && !failed) {  // one warp per TMEM lane quadrant
+      const int k = warp * 32 + lane;
+      for (int c0 = 0; c0 < a.OCp; c0 += 16) {
+        float v[16];
+        if (s_end > s_begin) {
+          float w[16];
+          tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+          tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(a.OCp + c0), w);
+#pragma unroll
+          for (int q = 0; q < 16; ++q) v[q] += w[q];
+        } else {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) v[q] = 0.f;
+        }
+        float4 *dst = reinterpret_cast<float4 *>(row + (size_t)k * a.OCp + c0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      }
+    }
+  }
+  if (failed && a.err) atomicExch(a.err, 5);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == TCS_CONV_WARPS) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
+}
+
+// sum of the partial rows -> reference layout: dW[o][k] = sum[k*OCp + o], db[o] = sum[128*OCp + o]
+__global__ void dw_small_permute_kernel(const float *__restrict__ src, float *__restrict__ dW, float *__restrict__ db,
+                                        int C, int OC, int OCp, int KK, const uint8_t *__restrict__ tbl,
+                                        int accumulate) {
+  const int K = C * KK, total = OC * K + (db ? OC : 0);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    if (i < OC * K) {
+      int o = i / K, k = i - o * K;
+      float v = src[(size_t)k * OCp + o];
+      if (tbl && !tbl[(k / KK) * OC + o]) v = 0.f;
+      dW[i] = accumulate ? dW[i] + v : v;
+    } else {
+      int o = i - OC * K;
+      float v = src[(size_t)128 * OCp + o];
+      db[o] = accumulate ? db[o] + v : v;
+    }
+  }
+}
+
+size_t dw_small_stage(const ConvGeom &g, int OCp, int bw) {
+  size_t XB = ((size_t)g.C * g.KH * bw * 4 + 1023) & ~(size_t)1023;
+  return 2 * 128 * 128 + 2 * (size_t)OCp * 128 + XB;
+}
+
+size_t dw_small_fixed(int OCp) {
+  return 1024 + (3 * TCS_MAX_STAGES + 1) * 8 + 32 + (size_t)TCS_GROUPS * 8 * OCp * 4 + 64;
+}
+
+// pipeline stages that fit (0: the kernel does not fit)
+int dw_small_stages(const b200_ctx *ctx, const ConvGeom &g, int OCp, int bw) {
+  size_t fixed = dw_small_fixed(OCp), stage = dw_small_stage(g, OCp, bw);
+  if (ctx->smem_optin < fixed + 2 * stage) return 0;
+  size_t n = (ctx->smem_optin - fixed) / stage;
+  return (int)(n > TCS_MAX_STAGES ? TCS_MAX_STAGES : n);
+}
+
+int dw_small_bw(const ConvGeom &g) { return (TCS_PX + g.KW - 1 + 3 + 3) & ~3; }
+
+}  // namespace
+
+// true when the small-input-channel dW kernel applies
+bool conv_dw_small_ok(const b200_ctx *ctx, const ConvGeom &g) {
+  if (g.SH != 1 || g.SW != 1 || g.DH != 1 || g.DW != 1) return false;
+  if (g.C * g.KH * g.KW > 128 || g.OC > 128) return false;
+  if ((g.WI & 3) || (g.OW & 3)) return false;                 // TMA strides are multiples of 16 bytes
+  if (((size_t)g.HI * g.WI) & 3 || ((size_t)g.OH * g.OW) & 3) return false;
+  TallGeom t = tall_geom(g, 1);
+  if (g.pad_t < 0 || g.pad_l < 0 || t.pad_b < 0 || t.pad_r < 0) return false;
+  const int OCp = (g.OC + 15) / 16 * 16;
+  return dw_small_stages(ctx, g, OCp, dw_small_bw(g)) >= 2;
+}
+
+int conv_dw_small_splits(const b200_ctx *ctx, const ConvGeom &g, int B) {
+  long long nsteps = (long long)B * g.OH * ceil_div(g.OW, TCS_PX);
+  return (int)(nsteps < ctx->sm_count ? nsteps : ctx->sm_count);
+}
+
+size_t conv_dw_small_floats(const b200_ctx *ctx, const ConvGeom &g, int B) {
+  const int OCp = (g.OC + 15) / 16 * 16;
+  return ((size_t)conv_dw_small_splits(ctx, g, B) + 1) * ((size_t)129 * OCp);
+}
+
+// dW (+ db when the layer has a bias) from the CHW input and gradient; `part` holds conv_dw_small_floats
+int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout, int B, float *part,
+                  float *dW, float *db, int accumulate) {
+  const int OCp = (g.OC + 15) / 16 * 16, bw = dw_small_bw(g);
+  EncodeTiledFn fn = encode_fn();
+  B200_REQUIRE(fn != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
+  CUtensorMap x_map, dy_map;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)g.WI, (cuuint64_t)g.HI, (cuuint64_t)g.C, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)g.WI * 4, (cuuint64_t)g.HI * g.WI * 4, (cuuint64_t)g.C * g.HI * g.WI * 4};
+    cuuint32_t box[4] = {(cuuint32_t)bw, (cuuint32_t)g.KH, (cuuint32_t)g.C, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(in), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (%d) for the input rows", (int)r);
+  }
+  {
+    // dimensions ordered (x, o, y, b) so that one box is the K-major tile [o][32 pixels]
+    cuuint64_t dims[4] = {(cuuint64_t)g.OW, (cuuint64_t)g.OC, (cuuint64_t)g.OH, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)g.OH * g.OW * 4, (cuuint64_t)g.OW * 4, (cuuint64_t)g.OC * g.OH * g.OW * 4};
+    cuuint32_t box[4] = {TCS_PX, (cuuint32_t)OCp, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(&dy_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(dout), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (%d) for the gradient tiles", (int)r);
+  }
+  TcDwSmallArgs a;
+  a.part = part;
+  a.err = ctx->dev_err;
+  a.C = g.C;
+  a.OC = g.OC;
+  a.OCp = OCp;
+  a.KH = g.KH;
+  a.KW = g.KW;
+  a.pad_t = g.pad_t;
+  a.pad_l = g.pad_l;
+  a.OH = g.OH;
+  a.OW = g.OW;
+  a.nxb = ceil_div(g.OW, TCS_PX);
+  a.Kreal = g.C * g.KH * g.KW;
+  a.bw = bw;
+  a.nsteps = B * g.OH * a.nxb;
+  a.ksplits = conv_dw_small_splits(ctx, g, B);
+  a.nst = dw_small_stages(ctx, g, OCp, bw);
+  B200_REQUIRE(a.nst >= 2, "conv_dw_small: the tiles do not fit shared memory");
+  a.tmem_cols = pow2_at_least(2 * OCp);
+  a.row = (long long)129 * OCp;
+  const size_t smem = dw_small_fixed(OCp) + (size_t)a.nst * dw_small_stage(g, OCp, bw);
+  B200_CUDA(cudaFuncSetAttribute(conv_dw_small_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  a.dbg = nullptr;
+  static const bool timing = getenv("B200_TC_TIMING") != nullptr;
+  if (timing) B200_CUDA(cudaMalloc(&a.dbg, (size_t)a.ksplits * 8 * sizeof(long long)));
+  conv_dw_small_tc_kernel<<<a.ksplits, TCS_THREADS, smem, ctx->stream>>>(x_map, dy_map, a);
+  B200_LAUNCHED();
+  if (timing) {  // diagnostic: cycles of the three roles and of their waits, averaged over blocks
+    std::vector<long long> h((size_t)a.ksplits * 8);
+    B200_CUDA(cudaStreamSynchronize(ctx->stream));
+    B200_CUDA(cudaMemcpy(h.data(), a.dbg, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+    B200_CUDA(cudaFree(a.dbg));
+    double s[8] = {0};
+    for (int i = 0; i < a.ksplits; ++i)
+      for (int k = 0; k < 8; ++k) s[k] += (double)h[(size_t)i * 8 + k] / a.ksplits;
+    fprintf(stderr,
+            "[tc-timing] dW small: steps/block %.1f stages %d: producer %.0f clk (wait %.0f), mma %.0f (wait %.0f), "
+            "converter group 0 %.0f (wait %.0f)\n",
+            (double)a.nsteps / a.ksplits, a.nst, s[0], s[1], s[2], s[3], s[4], s[5]);
+  }
+  float *sum = part + (size_t)a.ksplits * a.row;
+  B200_TRY(merge_rows(ctx, part, a.ksplits, (size_t)a.row, sum, (size_t)a.row, 0, nullptr));
+  const int total = g.OC * a.Kreal + (g.has_bias && db ? g.OC : 0);
+  dw_small_permute_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(
+    sum, dW, g.has_bias ? db : nullptr, g.C, g.OC, OCp, g.KH * g.KW, g.tbl, accumulate);
+  B200_LAUNCHED();
   return 0;
 }
 

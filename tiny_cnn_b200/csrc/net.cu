@@ -33,9 +33,9 @@ struct Layer {
   float *wt_fwd = nullptr, *wt_dx = nullptr, *dw_part = nullptr;
   // tensor-core passes: tall split copies of the input and of dY, per-block bias partials,
   // filter matrices, partial weight gradients
-  ConvTcUse tc = {false, false, false};
+  ConvTcUse tc = {false, false, false, false};
   float *tc_xs = nullptr, *tc_dys = nullptr, *tc_bsum = nullptr;
-  float *tc_wt_fwd = nullptr, *tc_wt_dx = nullptr, *tc_part = nullptr;
+  float *tc_wt_fwd = nullptr, *tc_wt_dx = nullptr, *tc_part = nullptr, *tc_small_part = nullptr;
   float *fc_scratch = nullptr;  // k-slice partial sums of the small GEMMs
   int fused_act = 0;      // activation of the NEXT layer folded into this epilogue
   bool skipped = false;   // activation layer folded into the previous layer
@@ -168,6 +168,8 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
           B200_TRY(conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits));
           B200_TRY(conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0));
           if (db) B200_TRY(conv_tc_bias_grad(ctx, L.g, L.tc_bsum, B, db, 0));
+        } else if (L.tc.dw_small) {
+          B200_TRY(conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0));
         } else if (tiled_bwd) {
           int splits = 0;
           B200_TRY(conv_tiled_dw_partials(ctx, L.g, in, L.grad, B, L.dw_part, &splits));
@@ -404,6 +406,8 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
       size_t need = conv_tiled_dw_scratch(ctx, L.g, max_batch);
       B200_TRY(net_alloc((void **)&L.dw_part, need * f));
     }
+    if (L.kind == B200_LAYER_CONV && L.tc.dw_small)
+      B200_TRY(net_alloc((void **)&L.tc_small_part, conv_dw_small_floats(ctx, L.g, max_batch) * f));
     if (L.kind == B200_LAYER_CONV && (L.tc.fwd || L.tc.dx || L.tc.dw)) {
       if (L.tc.fwd || L.tc.dw)
         B200_TRY(net_alloc((void **)&L.tc_xs, conv_tc_tall_floats(L.g, max_batch, 0) * f));
@@ -440,6 +444,7 @@ int b200_net_destroy(b200_net *net) {
     cudaFree(L.tc_wt_fwd);
     cudaFree(L.tc_wt_dx);
     cudaFree(L.tc_part);
+    cudaFree(L.tc_small_part);
     cudaFree(L.fc_scratch);
   }
   cudaFree(net->params);

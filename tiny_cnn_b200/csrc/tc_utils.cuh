@@ -89,6 +89,15 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
     : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *map, int c0, int c1,
+                                            int c2, int c3, uint64_t *bar) {
+  asm volatile(
+    "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n" ::"r"(
+      smem_u32(smem_dst)),
+    "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+    : "memory");
+}
+
 // General shared-memory matrix descriptor.  `layout`: 2 = 128-byte swizzle of 16-byte chunks
 // (K-major operands: rows of 32 floats, `sbo` bytes between groups of 8 rows), 1 = 128-byte
 // swizzle of 32-byte chunks (the form 32-bit MN-major operands need: rows are 32 floats along
