@@ -73,7 +73,7 @@ B200_API int b200_ctx_sync(b200_ctx *ctx);
  * take.  "conv_tensor_cores": 0 = convolutions never on the tensor cores,
  * 1 (default) = stride-1 layers with at least 16 input and 16 output
  * channels, 2 = every pass the tensor-core kernels can take (stride 1,
- * dilation 1, windows up to 8x8, at most 256 channels).  Unknown names are an error.
+ * dilation 1, windows up to 8x8, at most 256 channels either side).  Unknown names are an error.
  */
 B200_API int b200_ctx_set_option(b200_ctx *ctx, const char *name, int value);
 

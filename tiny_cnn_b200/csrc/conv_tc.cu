@@ -205,7 +205,8 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   constexpr uint32_t HB = TCV_HALO_W * TCV_TILE_ROWS * 128u;  // one haloed tile (hi or lo): 32 KiB
   const int Ng = a.KH * a.gs;                                 // MMA width
   const uint32_t FB = (uint32_t)Ng * 128u;                    // one filter tile (hi or lo)
-  const int CB = a.groups * Ng;                               // accumulator columns per buffer
+  const int CB = Ng;                                          // accumulator columns per buffer
+  const int nunits = a.ntiles * a.groups;                     // work unit = (pixel tile, channel group)
   uint8_t *halo = smem;                                       // [nh][hi | lo]
   uint8_t *filt = halo + (size_t)a.nh * 2 * HB;               // [nf] filter tiles (hi and lo alternate)
   float *xch = reinterpret_cast<float *>(filt + (size_t)a.nf * FB);
@@ -242,7 +243,8 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   if (warp == 4 && lane == 0) {
     // ---- TMA producer -----------------------------------------------------------------
     uint32_t u = 0, f = 0;
-    for (int tile = blockIdx.x; tile < a.ntiles && !failed; tile += gridDim.x) {
+    for (int unit = blockIdx.x; unit < nunits && !failed; unit += gridDim.x) {
+      const int tile = unit / a.groups, grp = unit - tile * a.groups;
       const int x0 = (tile % a.tiles_x) * TCV_TILE_COLS, r0 = (tile / a.tiles_x) * TR - a.pad_t;
       for (int slab = 0; slab < a.slabs && !failed; ++slab, ++u) {
         const uint32_t hb = u % a.nh, use = u / a.nh;
@@ -254,14 +256,13 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
         mbar_expect_tx(&halo_full[hb], 2 * HB);
         tma_load_3d(h, &in_hi, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
         tma_load_3d(h + HB, &in_lo, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
-        const int nst = a.KW * a.groups;
-        for (int s = 0; s < 2 * nst; ++s, ++f) {  // per (kx, group): the hi tile, then the lo tile
+        for (int s = 0; s < 2 * a.KW; ++s, ++f) {  // per kx: the hi tile, then the lo tile
           const uint32_t fs = f % a.nf, fuse = f / a.nf;
           if (fuse > 0 && !mbar_wait_bounded(&filt_empty[fs], (fuse - 1) & 1)) {
             failed = true;
             break;
           }
-          const int row = (slab * nst + (s >> 1)) * Ng;
+          const int row = ((slab * a.KW + (s >> 1)) * a.groups + grp) * Ng;
           mbar_expect_tx(&filt_full[fs], FB);
           tma_load_2d(filt + (size_t)fs * FB, (s & 1) ? &f_lo : &f_hi, 0, row, &filt_full[fs]);
         }
@@ -272,7 +273,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     const uint32_t idesc = umma_idesc_tf32(128, Ng);
     uint32_t u = 0, f = 0, it = 0;
     long long w_acc = 0, w_halo = 0, w_filt = 0, t_begin = clock64(), tq;
-    for (int tile = blockIdx.x; tile < a.ntiles && !failed; tile += gridDim.x, ++it) {
+    for (int unit = blockIdx.x; unit < nunits && !failed; unit += gridDim.x, ++it) {
       const uint32_t ab = it % a.nb, ause = it / a.nb;
       tq = clock64();
       if (ause > 0 && !mbar_wait_bounded(&acc_empty[ab], (ause - 1) & 1)) {
@@ -293,10 +294,10 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
         tc_fence_after();
         const uint32_t hbase = smem_u32(halo + (size_t)hb * 2 * HB);
         for (int kx = 0; kx < a.KW && !failed; ++kx) {
-          for (int grp = 0; grp < a.groups && !failed; ++grp) {
+          {
             // A: the haloed tile addressed kx pixels (rows of 128 bytes) further on
             const uint32_t abase = hbase + (uint32_t)kx * 128u;
-            const uint32_t d = tmem_d + (uint32_t)(grp * Ng);
+            const uint32_t d = tmem_d;
             for (int part = 0; part < 2; ++part, ++f) {  // the hi filter tile, then the lo tile
               const uint32_t fs = f % a.nf;
               tq = clock64();
@@ -341,7 +342,8 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     const size_t plane = (size_t)a.OH * a.OW;
     uint32_t half = 0;  // exchange buffer half in use
     long long w_full = 0, t_begin = clock64(), tq;
-    for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x, ++it) {
+    for (int unit = blockIdx.x; unit < nunits; unit += gridDim.x, ++it) {
+      const int tile = unit / a.groups, grp = unit - tile * a.groups;
       const uint32_t ab = it % a.nb;
       tq = clock64();
       if (!mbar_wait_bounded(&acc_full[ab], (it / a.nb) & 1)) failed = true;
@@ -366,13 +368,13 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
       const bool valid = r < TR && b < a.B && y < a.OH && x < a.OW;
       float *obase = a.out + ((size_t)b * a.N * a.OH + y) * a.OW + x;
       const uint32_t tbase = tmem_base + ((uint32_t)(warp * 32) << 16) + ab * (uint32_t)CB;
-      for (int grp = 0; grp < a.groups; ++grp) {
+      {
         for (int c0 = 0; c0 < a.gs; c0 += 16) {
           float acc[16];
-          tmem_ld16(tbase + (uint32_t)(grp * Ng + c0), acc);
+          tmem_ld16(tbase + (uint32_t)c0, acc);
           for (int ky = 1; ky < a.KH; ++ky) {
             float v[16];
-            tmem_ld16(tbase + (uint32_t)(grp * Ng + ky * a.gs + c0), v);
+            tmem_ld16(tbase + (uint32_t)(ky * a.gs + c0), v);
             // hand the block to the thread ky rows up: 64-byte rows, 16-byte chunks swizzled
             float4 *row = reinterpret_cast<float4 *>(xch + half * (TCV_EPI_FLOATS / 2) + m * 16);
             const int sw = (m >> 1) & 3;
@@ -614,8 +616,7 @@ TcPlan conv_tc_plan(const b200_ctx *ctx, int KH, int n_out) {
   if (gmax < 16) return p;
   p.groups = (c16 + gmax - 1) / gmax;
   p.gs = pad16((c16 + p.groups - 1) / p.groups);
-  const int CB = p.groups * KH * p.gs;
-  if (CB > 512) return p;
+  const int CB = KH * p.gs;  // accumulator columns of one (tile, group) unit
   p.nb = 2 * CB <= 512 ? 2 : 1;
   p.tmem_cols = pow2_at_least(p.nb * CB);
   const size_t HB = (size_t)TCV_HALO_W * TCV_TILE_ROWS * 128, stage = (size_t)KH * p.gs * 128;
@@ -712,7 +713,8 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long 
   a.tmem_cols = p.tmem_cols;
   a.dbg = nullptr;
   B200_CUDA(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
-  int grid = a.ntiles < ctx->sm_count ? a.ntiles : ctx->sm_count;
+  const int units = a.ntiles * a.groups;
+  int grid = units < ctx->sm_count ? units : ctx->sm_count;
   static const bool timing = getenv("B200_TC_TIMING") != nullptr;
   if (timing) B200_CUDA(cudaMalloc(&a.dbg, (size_t)grid * 8 * sizeof(long long)));
   conv_tc_kernel<<<grid, TCV_THREADS, p.smem, ctx->stream>>>(in_hi, in_lo, f_hi, f_lo, a);
