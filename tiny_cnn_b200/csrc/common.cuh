@@ -173,6 +173,12 @@ int conv_tc_bias_grad(b200_ctx *ctx, const ConvGeom &g, const float *bsum, int B
 size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B);
 int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs);
 int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, float *dys, float *bsum);
+// the same conversions fused with the 2x2/2 max-pooling layer before the convolution (forward) and
+// with the gradient of the pooling layer (and relu) after it (backward)
+int conv_tc_tall_x_pool(b200_ctx *ctx, const ConvGeom &g, const float *in, float *pooled, int32_t *argmax, int B,
+                        float *xs);
+int conv_tc_tall_dy_unpool(b200_ctx *ctx, const ConvGeom &g, const float *gpool, const int32_t *argmax,
+                           const float *relu_y, float *dout_chw, int B, float *dys, float *bsum);
 // `prep` = 0 reuses the filter matrices an earlier call left in `wt` (same weights)
 int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,
                 float *out, int B, int act, float *wt, int prep = 1);

@@ -26,6 +26,7 @@
 // Warp roles in both kernels: warps 0-3 epilogue (one TMEM lane per thread), warp 4 TMEM
 // allocation + TMA producer, warp 5 MMA issuer.  Every load is CTA-local; every wait is bounded and a
 // timeout sets the context's error word, frees tensor memory and returns.
+#include <float.h>
 #include <stdlib.h>
 
 #include "tc_utils.cuh"
@@ -71,28 +72,83 @@ int dy_period(const ConvGeom &g) {
 
 // ---- CHW rows -> tall split tensors ---------------------------------------------------
 
+// Where the CHW values to convert come from.  mode 0: a CHW tensor.  mode 1: the 2x2/2 max-pool of
+// `a` (planes in_h x in_w = 2H x 2W): the pooled values and their argmax are also written, CHW, as
+// maxpool2x2_fwd_kernel would (strict '>' in window order).  mode 2: the gradient of a 2x2/2
+// max-pool (pooled gradient `a`, argmax `am`), masked by the relu whose output is `relu_y` when
+// given; the CHW gradient is also written to `out_chw`.
+struct TallSrc {
+  int mode;
+  const float *a;
+  const int32_t *am;
+  const float *relu_y;
+  float *out_chw;
+  int32_t *out_am;
+};
+
 // One block converts `rb` tall rows of one image: src[b][c][y][x] -> hi/lo[t][x][c],
 // zero for padded channels and for the rows between images.  With `bsum` the block also
 // writes the per-channel sum of what it read (bias gradient partials, fixed order).
 // Shared tile [c][pixel] with an odd pitch: scalar, coalesced loads along x; 16-byte
 // stores of four channels of one pixel.
-__global__ void __launch_bounds__(256) to_tall_kernel(const float *__restrict__ src, int C, int H, int W,
-                                                      int Cp, int period, int rb, int pitch,
-                                                      float *__restrict__ hi, float *__restrict__ lo,
-                                                      float *__restrict__ bsum) {
+__global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, int H, int W, int Cp, int period,
+                                                      int rb, int pitch, float *__restrict__ hi,
+                                                      float *__restrict__ lo, float *__restrict__ bsum) {
   extern __shared__ float tile[];  // [C][pitch]
   const int chunks = (period + rb - 1) / rb;
   const int b = blockIdx.x / chunks, r0 = (blockIdx.x % chunks) * rb;
   const int nr = min(rb, period - r0);
   const int npx = nr * W;
   const int valid_px = max(0, min(nr, H - r0)) * W;
-  const float *img = src + ((size_t)b * C * H + r0) * W;
   const size_t plane = (size_t)H * W;
   const int total = C * npx;
+  if (src.mode == 0) {
+    const float *img = src.a + ((size_t)b * C * H + r0) * W;
 #pragma unroll 8
-  for (int i = threadIdx.x; i < total; i += 256) {
-    int c = i / npx, p = i - c * npx;
-    tile[c * pitch + p] = p < valid_px ? img[c * plane + p] : 0.f;
+    for (int i = threadIdx.x; i < total; i += 256) {
+      int c = i / npx, p = i - c * npx;
+      tile[c * pitch + p] = p < valid_px ? img[c * plane + p] : 0.f;
+    }
+  } else if (src.mode == 1) {
+    const int in_w = 2 * W, in_h = 2 * H;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < total; i += 256) {
+      int c = i / npx, p = i - c * npx;
+      float best = 0.f;
+      if (p < valid_px) {
+        const int ry = p / W, x = p - ry * W, y = r0 + ry;
+        const float *ip = src.a + (((size_t)b * C + c) * in_h + 2 * y) * in_w + 2 * x;
+        const float2 u = *reinterpret_cast<const float2 *>(ip);
+        const float2 v = *reinterpret_cast<const float2 *>(ip + in_w);
+        const int base = (in_h * c + 2 * y) * in_w + 2 * x;
+        int idx = 0;
+        best = -FLT_MAX;
+        if (u.x > best) { best = u.x; idx = base; }
+        if (u.y > best) { best = u.y; idx = base + 1; }
+        if (v.x > best) { best = v.x; idx = base + in_w; }
+        if (v.y > best) { best = v.y; idx = base + in_w + 1; }
+        const size_t o = ((size_t)b * C + c) * plane + (size_t)y * W + x;
+        src.out_chw[o] = best;
+        src.out_am[o] = idx;
+      }
+      tile[c * pitch + p] = best;
+    }
+  } else {
+    const int pw = W >> 1, ph = H >> 1;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < total; i += 256) {
+      int c = i / npx, p = i - c * npx;
+      float v = 0.f;
+      if (p < valid_px) {
+        const int ry = p / W, x = p - ry * W, y = r0 + ry;
+        const size_t po = (((size_t)b * C + c) * ph + (y >> 1)) * pw + (x >> 1);
+        const size_t o = ((size_t)b * C + c) * plane + (size_t)y * W + x;
+        v = src.am[po] == (H * c + y) * W + x ? src.a[po] : 0.f;
+        if (src.relu_y != nullptr && !(src.relu_y[o] > 0.f)) v = 0.f;
+        if (src.out_chw != nullptr) src.out_chw[o] = v;
+      }
+      tile[c * pitch + p] = v;
+    }
   }
   __syncthreads();
   const size_t base = ((size_t)b * period + r0) * W * Cp;
@@ -656,7 +712,7 @@ int to_tall_rows(int C, int W, int period) {
 
 int to_tall_blocks(int C, int W, int period, int B) { return B * ceil_div(period, to_tall_rows(C, W, period)); }
 
-int to_tall(b200_ctx *ctx, const float *src, int C, int H, int W, int Cp, int period, int B, float *dst,
+int to_tall(b200_ctx *ctx, const TallSrc &src, int C, int H, int W, int Cp, int period, int B, float *dst,
             float *bsum) {
   const int rb = to_tall_rows(C, W, period);
   const int pitch = ((rb * W + 7) & ~7) + 1;
@@ -895,14 +951,35 @@ int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits,
 
 int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs) {
   TallGeom t = tall_geom(g, B);
-  return to_tall(ctx, in, g.C, g.HI, g.WI, t.Cp, t.period, B, xs, nullptr);
+  const TallSrc src = {0, in, nullptr, nullptr, nullptr, nullptr};
+  return to_tall(ctx, src, g.C, g.HI, g.WI, t.Cp, t.period, B, xs, nullptr);
 }
 
 // dY -> tall split form; bsum (conv_tc_bsum_rows x OC floats, may be nullptr) receives the
 // per-block channel sums whose in-order total is the bias gradient
 int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, float *dys, float *bsum) {
   TallGeom t = tall_geom(g, B);
-  return to_tall(ctx, dout, g.OC, g.OH, g.OW, t.OCp, dy_period(g), B, dys, bsum);
+  const TallSrc src = {0, dout, nullptr, nullptr, nullptr, nullptr};
+  return to_tall(ctx, src, g.OC, g.OH, g.OW, t.OCp, dy_period(g), B, dys, bsum);
+}
+
+// 2x2/2 max-pooling fused with the conversion: `in` is the pooling layer's input (planes 2*HI x 2*WI),
+// `pooled` / `argmax` receive what maxpool_fwd would write, `xs` the tall split copy of the pooled values
+int conv_tc_tall_x_pool(b200_ctx *ctx, const ConvGeom &g, const float *in, float *pooled, int32_t *argmax, int B,
+                        float *xs) {
+  TallGeom t = tall_geom(g, B);
+  const TallSrc src = {1, in, nullptr, nullptr, pooled, argmax};
+  return to_tall(ctx, src, g.C, g.HI, g.WI, t.Cp, t.period, B, xs, nullptr);
+}
+
+// gradient of a 2x2/2 max-pooling layer (pooled gradient `gpool`, its `argmax`) that follows this
+// convolution -- through the relu in between when `relu_y` (the relu's output) is given -- written as
+// the tall split copy of dY, as the CHW gradient `dout_chw` (may be nullptr) and as bias partials
+int conv_tc_tall_dy_unpool(b200_ctx *ctx, const ConvGeom &g, const float *gpool, const int32_t *argmax,
+                           const float *relu_y, float *dout_chw, int B, float *dys, float *bsum) {
+  TallGeom t = tall_geom(g, B);
+  const TallSrc src = {2, gpool, argmax, relu_y, dout_chw, nullptr};
+  return to_tall(ctx, src, g.OC, g.OH, g.OW, t.OCp, dy_period(g), B, dys, bsum);
 }
 
 int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,

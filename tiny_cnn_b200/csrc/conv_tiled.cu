@@ -557,6 +557,191 @@ int conv_tiled_fwd(b200_ctx *ctx, const ConvGeom &g, const float *in, const floa
   return launch_core(ctx, p, g.KH, g.KW);
 }
 
+// ---------------------------------------------------------------------------
+// direct convolution with at most four output channels (dX of a first layer)
+// ---------------------------------------------------------------------------
+//
+// out[n][co][y][x] = sum_{ci,wy,wx} wt[ci][wy][wx][co(4)] * in[n][ci][y + wy - pad_t][x + wx - pad_l]
+// With so few output channels a thread cannot reuse an input value across channels, so it reuses
+// it across the window instead: each thread owns a 2 x 4 pixel patch for all NOUT channels, reads
+// its (2+KH-1) x (4+KW-1) input window of one input channel into registers (16-byte loads) and
+// applies all KH*KW taps to it; the NOUT weights of a tap come from shared memory in one
+// broadcast load.  A block covers a 32 x 8 output tile of one image; input channels are staged
+// four at a time with zero-filled cp.async, double buffered, and each of the four thread groups
+// of a block takes one of them (more warps in flight); the groups' sums are added in group order.
+
+constexpr int FO_TILE = 32, FO_TILE_H = 8, FO_PX = 4, FO_PY = 2, FO_ICB = 4;  // 32 x 8 output tile: many small blocks
+constexpr int FO_PATCHES = (FO_TILE / FO_PX) * (FO_TILE_H / FO_PY);  // 8 x 4 patches of 4 x 2 pixels
+constexpr int FO_THREADS = FO_PATCHES * FO_ICB;       // one thread group per staged input channel
+
+struct FewOutCfg {
+  const float *in;   // [B][CI][HI][WI]
+  const float *wt;   // [CI][KH*KW][4]
+  float *out;        // [B][CO][HO][WO]
+  int CI, HI, WI, CO, HO, WO, pad_t, pad_l, tiles_x;
+};
+
+template <int KH, int KW, int NOUT>
+__global__ void __launch_bounds__(FO_THREADS) conv_fewout_kernel(const FewOutCfg p) {
+  constexpr int KK = KH * KW;
+  constexpr int TH = FO_TILE_H + KH - 1;               // staged rows
+  constexpr int PITCH = (FO_TILE + KW - 1 + 3) & ~3;   // staged row pitch (floats, 16-byte rows)
+  constexpr int WR = FO_PY + KH - 1, WC = FO_PX + KW - 1;  // register window
+  constexpr int WC4 = (WC + 3) / 4;                    // 16-byte loads per window row
+  extern __shared__ __align__(16) float fo_smem[];
+  float *wsm = fo_smem;                                // [CI][KK][4]
+  float *xs = fo_smem + ((p.CI * KK * 4 + 3) & ~3);     // [2][FO_ICB][TH][PITCH]
+  const int tid = threadIdx.x, z = tid / FO_PATCHES, t = tid - z * FO_PATCHES, tx = t & 7, ty = t >> 3;
+  const int b = blockIdx.y, tile = blockIdx.x;
+  const int x0 = (tile % p.tiles_x) * FO_TILE, y0 = (tile / p.tiles_x) * FO_TILE_H;
+  for (int i = tid; i < p.CI * KK; i += FO_THREADS)
+    reinterpret_cast<float4 *>(wsm)[i] = reinterpret_cast<const float4 *>(p.wt)[i];
+  const float *img = p.in + (size_t)b * p.CI * p.HI * p.WI;
+  const int nchunks = (p.CI + FO_ICB - 1) / FO_ICB;
+  // The elements a thread stages are at the same tile positions in every chunk: their source
+  // offsets (relative to the chunk's first channel) and validity are computed once.
+  constexpr int NEL = FO_ICB * TH * PITCH;
+  constexpr int NST = (NEL + FO_THREADS - 1) / FO_THREADS;
+  int soff[NST];       // float offset from the first channel of the chunk, -1: padding (zero fill)
+  int schan[NST];      // channel within the chunk
+#pragma unroll
+  for (int k = 0; k < NST; ++k) {
+    const int i = tid + k * FO_THREADS;
+    const int col = i % PITCH, r = i / PITCH, row = r % TH, c = r / TH;
+    const int gy = y0 + row - p.pad_t, gx = x0 + col - p.pad_l;
+    const bool ok = i < NEL && gy >= 0 && gy < p.HI && gx >= 0 && gx < p.WI;
+    soff[k] = ok ? (c * p.HI + gy) * p.WI + gx : -1;
+    schan[k] = i < NEL ? c : FO_ICB;
+  }
+  auto stage = [&](int chunk, int buf) {
+    float *dst = xs + (size_t)buf * NEL;
+    const int c0 = chunk * FO_ICB;
+    const float *src = img + (size_t)c0 * p.HI * p.WI;
+#pragma unroll
+    for (int k = 0; k < NST; ++k) {
+      if (schan[k] < FO_ICB) {
+        const bool ok = soff[k] >= 0 && c0 + schan[k] < p.CI;
+        cp_async4(dst + tid + k * FO_THREADS, ok ? src + soff[k] : img, ok);
+      }
+    }
+    cp_async_commit();
+  };
+  float acc[NOUT][FO_PY][FO_PX];
+#pragma unroll
+  for (int n = 0; n < NOUT; ++n)
+#pragma unroll
+    for (int i = 0; i < FO_PY; ++i)
+#pragma unroll
+      for (int j = 0; j < FO_PX; ++j) acc[n][i][j] = 0.f;
+  stage(0, 0);
+  for (int chunk = 0; chunk < nchunks; ++chunk) {
+    if (chunk + 1 < nchunks) {
+      stage(chunk + 1, (chunk + 1) & 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const float *xb = xs + (size_t)(chunk & 1) * FO_ICB * TH * PITCH;
+    {
+      const int c = z, ci = chunk * FO_ICB + c;
+      if (ci < p.CI) {
+      float win[WR][WC4 * 4];
+      const float *wp = xb + ((size_t)c * TH + ty * FO_PY) * PITCH + tx * FO_PX;
+#pragma unroll
+      for (int r = 0; r < WR; ++r)
+#pragma unroll
+        for (int q = 0; q < WC4; ++q) {
+          const float4 v = *reinterpret_cast<const float4 *>(wp + r * PITCH + 4 * q);
+          win[r][4 * q] = v.x;
+          win[r][4 * q + 1] = v.y;
+          win[r][4 * q + 2] = v.z;
+          win[r][4 * q + 3] = v.w;
+        }
+      const float4 *wc = reinterpret_cast<const float4 *>(wsm) + (size_t)ci * KK;
+#pragma unroll
+      for (int wy = 0; wy < KH; ++wy)
+#pragma unroll
+        for (int wx = 0; wx < KW; ++wx) {
+          const float4 w4 = wc[wy * KW + wx];
+          const float w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+          for (int n = 0; n < NOUT; ++n)
+#pragma unroll
+            for (int i = 0; i < FO_PY; ++i)
+#pragma unroll
+              for (int j = 0; j < FO_PX; ++j) acc[n][i][j] = fmaf(w[n], win[i + wy][j + wx], acc[n][i][j]);
+        }
+    }
+    }
+    __syncthreads();
+  }
+  // add the groups' partial sums in group order (the staging buffers are free now)
+  float *red = xs;  // [FO_ICB - 1][NOUT * FO_PY * FO_PX][FO_PATCHES]
+  if (z > 0) {
+#pragma unroll
+    for (int n = 0; n < NOUT; ++n)
+#pragma unroll
+      for (int i = 0; i < FO_PY; ++i)
+#pragma unroll
+        for (int j = 0; j < FO_PX; ++j)
+          red[((size_t)(z - 1) * NOUT * FO_PY * FO_PX + (n * FO_PY + i) * FO_PX + j) * FO_PATCHES + t] = acc[n][i][j];
+  }
+  __syncthreads();
+  if (z > 0) return;
+#pragma unroll
+  for (int g = 0; g < FO_ICB - 1; ++g)
+#pragma unroll
+    for (int n = 0; n < NOUT; ++n)
+#pragma unroll
+      for (int i = 0; i < FO_PY; ++i)
+#pragma unroll
+        for (int j = 0; j < FO_PX; ++j)
+          acc[n][i][j] += red[((size_t)g * NOUT * FO_PY * FO_PX + (n * FO_PY + i) * FO_PX + j) * FO_PATCHES + t];
+  const int ox = x0 + tx * FO_PX, oy = y0 + ty * FO_PY;
+#pragma unroll
+  for (int n = 0; n < NOUT; ++n) {
+    if (n >= p.CO) break;
+#pragma unroll
+    for (int i = 0; i < FO_PY; ++i) {
+      if (oy + i >= p.HO) continue;
+      float *o = p.out + (((size_t)b * p.CO + n) * p.HO + oy + i) * p.WO + ox;
+      if (ox + FO_PX <= p.WO && (p.WO & 3) == 0) {
+        *reinterpret_cast<float4 *>(o) = make_float4(acc[n][i][0], acc[n][i][1], acc[n][i][2], acc[n][i][3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < FO_PX; ++j)
+          if (ox + j < p.WO) o[j] = acc[n][i][j];
+      }
+    }
+  }
+}
+
+static size_t fewout_smem(int CI, int KH, int KW) {
+  size_t TH = FO_TILE_H + KH - 1, PITCH = (FO_TILE + KW - 1 + 3) & ~3;
+  size_t stages = 2 * FO_ICB * TH * PITCH * 4, red = (size_t)(FO_ICB - 1) * 4 * FO_PY * FO_PX * FO_PATCHES * 4;
+  return (((size_t)CI * KH * KW * 4 + 3) & ~(size_t)3) * 4 + (stages > red ? stages : red);
+}
+
+template <int KH, int KW>
+static int launch_fewout(b200_ctx *ctx, const FewOutCfg &p, int B) {
+  size_t smem = fewout_smem(p.CI, KH, KW);
+  dim3 grid(p.tiles_x * ceil_div(p.HO, FO_TILE_H), B);
+#define B200_FEWOUT(N)                                                                                   \
+  do {                                                                                                   \
+    B200_CUDA(cudaFuncSetAttribute(conv_fewout_kernel<KH, KW, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                   (int)smem));                                                          \
+    conv_fewout_kernel<KH, KW, N><<<grid, FO_THREADS, smem, ctx->stream>>>(p);                           \
+  } while (0)
+  if (p.CO == 1) B200_FEWOUT(1);
+  else if (p.CO == 2) B200_FEWOUT(2);
+  else if (p.CO == 3) B200_FEWOUT(3);
+  else B200_FEWOUT(4);
+#undef B200_FEWOUT
+  B200_LAUNCHED();
+  return 0;
+}
+
 int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float *dout,
                   float *din, int B, float *scratch) {
   if (B == 0) return 0;
@@ -566,6 +751,24 @@ int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float 
   conv_prep_wt_dx_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(W, scratch, g.C, g.OC, Cp,
                                                                        g.KH, g.KW, g.tbl);
   B200_LAUNCHED();
+  if (g.C <= 4 && Cp == 4 && fewout_smem(g.OC, g.KH, g.KW) <= ctx->smem_optin) {
+    // few input channels: dX is a convolution with few OUTPUT channels
+    FewOutCfg f{};
+    f.in = dout;
+    f.wt = scratch;
+    f.out = din;
+    f.CI = g.OC;
+    f.HI = g.OH;
+    f.WI = g.OW;
+    f.CO = g.C;
+    f.HO = g.HI;
+    f.WO = g.WI;
+    f.pad_t = g.KH - 1 - g.pad_t;
+    f.pad_l = g.KW - 1 - g.pad_l;
+    f.tiles_x = ceil_div(g.WI, FO_TILE);
+    if (g.KH == 5 && g.KW == 5) return launch_fewout<5, 5>(ctx, f, B);
+    if (g.KH == 3 && g.KW == 3) return launch_fewout<3, 3>(ctx, f, B);
+  }
   CoreCfg p{};
   p.in = dout;
   p.wt = scratch;

@@ -41,6 +41,11 @@ struct Layer {
   bool skipped = false;   // activation layer folded into the previous layer
   bool relu_bwd_fused = false;   // max-pool: also applies the gradient of the relu before it
   bool bwd_done_by_next = false; // relu: its gradient is produced by the pooling layer after it
+  // 2x2 max-pool next to a tensor-core convolution: the pooling kernels also write the tall split
+  // copies that convolution reads (its input in the forward pass, its dY in the backward pass)
+  int feeds_conv = -1;     // max-pool: convolution layer whose input copy it writes
+  int grad_to_conv = -1;   // max-pool: convolution layer whose dY copy it writes
+  bool xs_from_pool = false, dys_from_pool = false;  // convolution: copies come from the pooling layers
 };
 
 }  // namespace
@@ -105,7 +110,7 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
     switch (L.kind) {
       case B200_LAYER_CONV:
         if (L.tc.fwd) {
-          B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
+          if (!L.xs_from_pool) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
           B200_TRY(conv_tc_fwd(ctx, L.g, L.tc_xs, W, b, dst, B, L.fused_act, L.tc_wt_fwd));
         } else if (L.tiled)
           B200_TRY(conv_tiled_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act, L.wt_fwd));
@@ -116,7 +121,12 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
         B200_TRY(fc_fwd(ctx, L.fc_in, L.fc_out, in, W, b, dst, B, L.fused_act, L.fc_scratch));
         break;
       case B200_LAYER_MAXPOOL:
-        B200_TRY(maxpool_fwd(ctx, L.pd, in, dst, L.argmax, B));
+        if (L.feeds_conv >= 0) {
+          Layer &Cv = net->layers[L.feeds_conv];
+          B200_TRY(conv_tc_tall_x_pool(ctx, Cv.g, in, dst, L.argmax, B, Cv.tc_xs));
+        } else {
+          B200_TRY(maxpool_fwd(ctx, L.pd, in, dst, L.argmax, B));
+        }
         break;
       case B200_LAYER_AVGPOOL:
         B200_TRY(avgpool_fwd(ctx, L.pd, in, W, b, dst, B));
@@ -152,7 +162,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
       case B200_LAYER_CONV: {
         bool tiled_bwd = L.tiled && L.g.OW <= 64;
         const bool tc_dx = L.tc.dx && din != nullptr;
-        if (tc_dx || L.tc.dw)
+        if ((tc_dx || L.tc.dw) && !L.dys_from_pool)
           B200_TRY(conv_tc_tall_dy(ctx, L.g, L.grad, B, L.tc_dys, L.tc.dw && db ? L.tc_bsum : nullptr));
         if (din) {
           if (tc_dx)
@@ -163,7 +173,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
             B200_TRY(conv_general_dx(ctx, L.g, W, L.grad, din, B));
         }
         if (L.tc.dw) {
-          if (!L.tc.fwd) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
+          if (!L.tc.fwd && !L.xs_from_pool) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
           int splits = 0;
           B200_TRY(conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits));
           B200_TRY(conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0));
@@ -191,7 +201,14 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
         B200_TRY(fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, din, dW, db, 0, B, L.fc_scratch));
         break;
       case B200_LAYER_MAXPOOL:
-        if (L.relu_bwd_fused) {
+        if (L.grad_to_conv >= 0) {
+          // gradient of this layer (and of the relu before it) written straight into the forms the
+          // tensor-core convolution reads: tall split copy, CHW gradient, bias partials
+          Layer &Cv = net->layers[L.grad_to_conv];
+          B200_TRY(conv_tc_tall_dy_unpool(ctx, Cv.g, L.grad, L.argmax,
+                                          L.relu_bwd_fused ? net->layers[i - 1].out : nullptr, Cv.grad, B,
+                                          Cv.tc_dys, Cv.tc.dw && Cv.b_len ? Cv.tc_bsum : nullptr));
+        } else if (L.relu_bwd_fused) {
           // the relu before this layer was folded into the producer's epilogue: apply
           // its gradient mask here and write straight into the producer's gradient
           B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, net->layers[i - 2].grad, B,
@@ -374,6 +391,31 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
           maxpool_can_fuse_relu(P.pd)) {
         P.relu_bwd_fused = true;
         R.bwd_done_by_next = true;
+      }
+    }
+  }
+  // 2x2 max-pool beside a tensor-core convolution: fuse the tall conversions into the pooling kernels
+  if (net->fuse) {
+    for (int i = 0; i < n_layers; ++i) {
+      Layer &P = net->layers[i];
+      if (P.kind != B200_LAYER_MAXPOOL || !maxpool_can_fuse_relu(P.pd)) continue;
+      if (i + 1 < n_layers) {
+        Layer &N = net->layers[i + 1];
+        if (N.kind == B200_LAYER_CONV && (N.tc.fwd || N.tc.dw) && N.g.C == P.pd.in_c &&
+            N.g.HI == P.pd.out_h && N.g.WI == P.pd.out_w) {
+          P.feeds_conv = i + 1;
+          N.xs_from_pool = true;
+        }
+      }
+      int j = P.relu_bwd_fused ? i - 2 : i - 1;
+      if (j >= 0 && (P.relu_bwd_fused || !net->layers[i - 1].skipped)) {
+        Layer &Cv = net->layers[j];
+        if (Cv.kind == B200_LAYER_CONV && (Cv.tc.dx || Cv.tc.dw) && Cv.g.OC == P.pd.in_c &&
+            Cv.g.OH == P.pd.in_h && Cv.g.OW == P.pd.in_w && (P.relu_bwd_fused || j == i - 1) &&
+            (P.relu_bwd_fused || Cv.fused_act == 0)) {
+          P.grad_to_conv = j;
+          Cv.dys_from_pool = true;
+        }
       }
     }
   }
