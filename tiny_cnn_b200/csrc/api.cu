@@ -107,8 +107,7 @@ int conv_bwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
     B200_TRY(conv_tc_tall_x(ctx, g, in, batch, xs));
     int splits = 0;
     B200_TRY(conv_tc_dw(ctx, g, xs, dys, batch, part, &splits));
-    B200_TRY(conv_tc_dw_finish(ctx, g, part, splits, dW, accumulate));
-    if (g.has_bias) B200_TRY(conv_tc_bias_grad(ctx, g, bs, batch, db, accumulate));
+    B200_TRY(conv_tc_dw_finish(ctx, g, part, splits, dW, accumulate, g.has_bias ? bs : nullptr, batch, db));
     return 0;
   }
   if (tc.dw_small) return conv_dw_small(ctx, g, in, dout, batch, small, dW, db, accumulate);
@@ -155,7 +154,7 @@ int conv_time_pass_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
     if (use_tc) {
       if (pass == 0) return conv_tc_fwd(ctx, g, xs, W, nullptr, res, batch, B200_ACT_NONE, wt, prep);
       if (pass == 1) return conv_tc_dx(ctx, g, dys, W, res, batch, wt, prep);
-      if (tc.dw_small) {  // includes its merge and permute launches
+      if (tc.dw_small) {  // includes its finishing launch
         float *gw = part + conv_dw_small_floats(ctx, g, batch);
         return conv_dw_small(ctx, g, in, dout, batch, part, gw, gw + conv_weight_len(g), 0);
       }

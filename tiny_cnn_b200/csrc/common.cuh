@@ -169,7 +169,6 @@ ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo);
 size_t conv_tc_tall_floats(const ConvGeom &g, int B, int which);  // 0: input, 1: dY
 size_t conv_tc_filter_floats(const b200_ctx *ctx, const ConvGeom &g, int for_dx);
 int conv_tc_bsum_rows(const ConvGeom &g, int B);
-int conv_tc_bias_grad(b200_ctx *ctx, const ConvGeom &g, const float *bsum, int B, float *db, int accumulate);
 size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B);
 int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs);
 int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, float *dys, float *bsum);
@@ -179,6 +178,8 @@ int conv_tc_tall_x_pool(b200_ctx *ctx, const ConvGeom &g, const float *in, float
                         float *xs);
 int conv_tc_tall_dy_unpool(b200_ctx *ctx, const ConvGeom &g, const float *gpool, const int32_t *argmax,
                            const float *relu_y, float *dout_chw, int B, float *dys, float *bsum);
+// filter matrices of the forward and / or dX pass (either may be nullptr) in one launch
+int conv_tc_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, float *wt_fwd, float *wt_dx);
 // `prep` = 0 reuses the filter matrices an earlier call left in `wt` (same weights)
 int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,
                 float *out, int B, int act, float *wt, int prep = 1);
@@ -186,7 +187,9 @@ int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *
                float *wt, int prep = 1);
 int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *dys, int B, float *part,
                int *splits);
-int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate);
+// finish: fixed-order sum of the partial rows into the reference layout, and (with bsum / db) the bias gradient
+int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate,
+                      const float *bsum, int B, float *db);
 
 // dW of stride-1 layers with in_c*KH*KW <= 128 on the tensor cores, straight from the CHW tensors
 bool conv_dw_small_ok(const b200_ctx *ctx, const ConvGeom &g);

@@ -184,9 +184,17 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
 // Forward: F[slab][kx][grp][ky][j][k] = W[o = grp*gs + j][inc = slab*32 + k][ky][kx]
 // dX:      F[slab][kx][grp][ky][j][k] = W[o = slab*32 + k][inc = grp*gs + j][KH-1-ky][KW-1-kx]
 // zero beyond the real channels and for unconnected pairs.
+struct FilterPrepOne {
+  int gs, groups, slabs, for_dx;
+  float *hi, *lo;
+};
+
+// blockIdx.y selects the matrix set: both the forward and the dX matrices of a layer in one launch
 __global__ void tc_filter_prep_kernel(const float *__restrict__ W, const uint8_t *__restrict__ tbl, int C,
-                                      int OC, int KH, int KW, int gs, int groups, int slabs, int for_dx,
-                                      float *__restrict__ hi, float *__restrict__ lo) {
+                                      int OC, int KH, int KW, const FilterPrepOne m0, const FilterPrepOne m1) {
+  const FilterPrepOne m = blockIdx.y == 0 ? m0 : m1;
+  const int gs = m.gs, groups = m.groups, slabs = m.slabs, for_dx = m.for_dx;
+  float *__restrict__ hi = m.hi, *__restrict__ lo = m.lo;
   const long long total = (long long)slabs * KW * groups * KH * gs * 32;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -791,53 +799,137 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long 
   return 0;
 }
 
-int filter_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, int n_out, int slabs, int for_dx, float *wt) {
-  const TcPlan p = conv_tc_plan(ctx, g.KH, n_out);
-  long long total = (long long)slabs * g.KW * p.groups * g.KH * p.gs * 32;
+FilterPrepOne filter_prep_one(const b200_ctx *ctx, const ConvGeom &g, int for_dx, float *wt, long long *total) {
+  TallGeom t = tall_geom(g, 1);
+  const TcPlan p = conv_tc_plan(ctx, g.KH, for_dx ? g.C : g.OC);
+  FilterPrepOne m;
+  m.gs = p.gs;
+  m.groups = p.groups;
+  m.slabs = (for_dx ? t.OCp : t.Cp) / 32;
+  m.for_dx = for_dx;
+  *total = (long long)m.slabs * g.KW * p.groups * g.KH * p.gs * 32;
+  m.hi = wt;
+  m.lo = wt + *total;
+  return m;
+}
+
+}  // namespace
+
+// filter matrices of the forward pass (wt_fwd) and / or of the dX pass (wt_dx) in one launch
+int conv_tc_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, float *wt_fwd, float *wt_dx) {
+  if (!wt_fwd && !wt_dx) return 0;
+  long long t0 = 0, t1 = 0;
+  FilterPrepOne m0 = filter_prep_one(ctx, g, wt_fwd ? 0 : 1, wt_fwd ? wt_fwd : wt_dx, &t0);
+  FilterPrepOne m1 = m0;
+  int sets = 1;
+  if (wt_fwd && wt_dx) {
+    m1 = filter_prep_one(ctx, g, 1, wt_dx, &t1);
+    sets = 2;
+  }
+  long long total = t0 > t1 ? t0 : t1;
   int blocks = (int)((total + 255) / 256);
   if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-  tc_filter_prep_kernel<<<blocks, 256, 0, ctx->stream>>>(W, g.tbl, g.C, g.OC, g.KH, g.KW, p.gs, p.groups, slabs,
-                                                         for_dx, wt, wt + total);
+  tc_filter_prep_kernel<<<dim3(blocks, sets), 256, 0, ctx->stream>>>(W, g.tbl, g.C, g.OC, g.KH, g.KW, m0, m1);
   B200_LAUNCHED();
   return 0;
 }
 
-// merged weight gradient in the dW kernel's order [unit][j][ky][inc][o] -> reference order
-// dW[o][inc][ky][kx] (kx = KW-1-j); unconnected pairs get no gradient
-__global__ void dw_tc_permute_kernel(const float *__restrict__ src, float *__restrict__ dW, int C, int OC,
-                                     int KH, int KW, int ic_slabs, const uint8_t *__restrict__ tbl,
-                                     int accumulate) {
-  const int total = OC * C * KH * KW;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    int kx = i % KW, r = i / KW;
-    int ky = r % KH;
-    r /= KH;
-    int inc = r % C, o = r / C;
-    int unit = (o >> 5) * ic_slabs + (inc >> 5);
-    size_t n = ((((size_t)unit * KW + (KW - 1 - kx)) * KH + ky) * 32 + (inc & 31)) * 32 + (o & 31);
-    float v = src[n];
-    if (tbl && !tbl[inc * OC + o]) v = 0.f;
-    dW[i] = accumulate ? dW[i] + v : v;
+namespace {
+
+// One launch that finishes a tensor-core dW pass: sums the partial rows in fixed order (8 row
+// lanes per element, lane k adds rows k, k+8, ... in order, lanes combined in order) and stores
+// the totals in the reference layout.  Elements [0, row_w) are weight-gradient entries in the
+// producing kernel's own order; `layout` says which: 0 = [unit][j][ky][inc][o] of
+// conv_dw_tc_kernel (kx = KW-1-j), 1 = [k][o] of conv_dw_small_tc_kernel.  Elements
+// [row_w, row_w + OC) are bias-gradient sums taken from `bsrc` (bs_rows rows of bs_stride floats,
+// entry bs_off + o of each).  Unconnected pairs get no gradient.
+struct DwFinishArgs {
+  const float *part;
+  long long part_stride;
+  int splits;
+  const float *bsrc;
+  long long bs_stride, bs_off;
+  int bs_rows;
+  float *dW, *db;
+  int layout, row_w;
+  int C, OC, OCp, KH, KW, ic_slabs;
+  const uint8_t *tbl;
+  int accumulate;
+};
+
+__global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) {
+  __shared__ float lanes[8][33];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int total = a.row_w + (a.db != nullptr ? a.OC : 0);
+  for (int base = blockIdx.x * 32; base < total; base += gridDim.x * 32) {
+    const int e = base + tx;
+    float s0 = 0.f, s1 = 0.f;
+    if (e < a.row_w) {
+      const float *src = a.part + e;
+      int r = ty;
+      for (; r + 8 < a.splits; r += 16) {
+        s0 += src[(size_t)r * a.part_stride];
+        s1 += src[(size_t)(r + 8) * a.part_stride];
+      }
+      if (r < a.splits) s0 += src[(size_t)r * a.part_stride];
+    } else if (e < total) {
+      const float *src = a.bsrc + a.bs_off + (e - a.row_w);
+      int r = ty;
+      for (; r + 8 < a.bs_rows; r += 16) {
+        s0 += src[(size_t)r * a.bs_stride];
+        s1 += src[(size_t)(r + 8) * a.bs_stride];
+      }
+      if (r < a.bs_rows) s0 += src[(size_t)r * a.bs_stride];
+    }
+    lanes[ty][tx] = s0 + s1;
+    __syncthreads();
+    if (ty == 0 && e < total) {
+      float s = lanes[0][tx];
+#pragma unroll
+      for (int k = 1; k < 8; ++k) s += lanes[k][tx];
+      if (e >= a.row_w) {
+        float *d = a.db + (e - a.row_w);
+        *d = a.accumulate ? *d + s : s;
+      } else {
+        int o, inc, ky, kx;
+        if (a.layout == 0) {
+          int r = e;
+          const int ol = r & 31;
+          r >>= 5;
+          const int il = r & 31;
+          r >>= 5;
+          ky = r % a.KH;
+          r /= a.KH;
+          const int j = r % a.KW, unit = r / a.KW;
+          kx = a.KW - 1 - j;
+          o = (unit / a.ic_slabs) * 32 + ol;
+          inc = (unit % a.ic_slabs) * 32 + il;
+        } else {
+          const int k = e / a.OCp, KK = a.KH * a.KW;
+          o = e - k * a.OCp;
+          inc = k / KK;
+          const int t = k - inc * KK;
+          ky = t / a.KW;
+          kx = t - ky * a.KW;
+        }
+        if (o < a.OC && inc < a.C) {
+          if (a.tbl && !a.tbl[inc * a.OC + o]) s = 0.f;
+          float *d = a.dW + (((size_t)o * a.C + inc) * a.KH + ky) * a.KW + kx;
+          *d = a.accumulate ? *d + s : s;
+        }
+      }
+    }
+    __syncthreads();
   }
 }
 
-// dst[c] (+)= sum over rows of src[r*len + c] for a tall, narrow matrix (many partial rows of a
-// short vector): 32 row lanes per column, each adding its rows in order, combined in fixed order.
-__global__ void __launch_bounds__(1024) sum_rows_narrow_kernel(const float *__restrict__ src, int rows, int len,
-                                                              float *__restrict__ dst, int accumulate) {
-  __shared__ float part[32][33];
-  const int c = blockIdx.x * 32 + threadIdx.x, rg = threadIdx.y;
-  float s = 0.f;
-  if (c < len)
-    for (int r = rg; r < rows; r += 32) s += src[(size_t)r * len + c];
-  part[rg][threadIdx.x] = s;
-  __syncthreads();
-  if (rg == 0 && c < len) {
-    float t = part[0][threadIdx.x];
-#pragma unroll
-    for (int i = 1; i < 32; ++i) t += part[i][threadIdx.x];
-    dst[c] = accumulate ? dst[c] + t : t;
-  }
+int launch_dw_finish(b200_ctx *ctx, const DwFinishArgs &a) {
+  const int total = a.row_w + (a.db != nullptr ? a.OC : 0);
+  int blocks = ceil_div(total, 32);
+  if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+  dw_finish_kernel<<<blocks, dim3(32, 8), 0, ctx->stream>>>(a);
+  B200_LAUNCHED();
+  return 0;
 }
 
 }  // namespace
@@ -907,14 +999,6 @@ int conv_tc_bsum_rows(const ConvGeom &g, int B) {
   return to_tall_blocks(g.OC, g.OW, dy_period(g), B);
 }
 
-// bias gradient from the per-block channel sums of conv_tc_tall_dy
-int conv_tc_bias_grad(b200_ctx *ctx, const ConvGeom &g, const float *bsum, int B, float *db, int accumulate) {
-  sum_rows_narrow_kernel<<<ceil_div(g.OC, 32), dim3(32, 32), 0, ctx->stream>>>(bsum, conv_tc_bsum_rows(g, B),
-                                                                              g.OC, db, accumulate);
-  B200_LAUNCHED();
-  return 0;
-}
-
 int conv_tc_dw_splits(const b200_ctx *ctx, const ConvGeom &g, int B) {
   TallGeom t = tall_geom(g, B);
   int units = (t.Cp / 32) * (t.OCp / 32);
@@ -936,17 +1020,32 @@ size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B) {
   return ((size_t)conv_tc_dw_splits(ctx, g, B) + 1) * dw_tc_row(g);
 }
 
-// sum the partial rows conv_tc_dw wrote (fixed order) and store them in the reference layout
-int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate) {
-  const size_t row = dw_tc_row(g);
-  float *sum = part + (size_t)splits * row;
-  B200_TRY(merge_rows(ctx, part, splits, row, sum, row, 0, nullptr));
+// sum the partial rows conv_tc_dw wrote (fixed order) and store them in the reference layout; with
+// `bsum` (the per-block channel sums of conv_tc_tall_dy) and `db` also the bias gradient
+int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate,
+                      const float *bsum, int B, float *db) {
   TallGeom t = tall_geom(g, 1);
-  const int total = (int)conv_weight_len(g);
-  dw_tc_permute_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(sum, dW, g.C, g.OC, g.KH, g.KW, t.Cp / 32,
-                                                                      g.tbl, accumulate);
-  B200_LAUNCHED();
-  return 0;
+  DwFinishArgs a;
+  a.part = part;
+  a.part_stride = (long long)dw_tc_row(g);
+  a.splits = splits;
+  a.bsrc = bsum;
+  a.bs_stride = g.OC;
+  a.bs_off = 0;
+  a.bs_rows = bsum ? conv_tc_bsum_rows(g, B) : 0;
+  a.dW = dW;
+  a.db = (bsum && g.has_bias) ? db : nullptr;
+  a.layout = 0;
+  a.row_w = (int)dw_tc_row(g);
+  a.C = g.C;
+  a.OC = g.OC;
+  a.OCp = t.OCp;
+  a.KH = g.KH;
+  a.KW = g.KW;
+  a.ic_slabs = t.Cp / 32;
+  a.tbl = g.tbl;
+  a.accumulate = accumulate;
+  return launch_dw_finish(ctx, a);
 }
 
 int conv_tc_tall_x(b200_ctx *ctx, const ConvGeom &g, const float *in, int B, float *xs) {
@@ -985,7 +1084,7 @@ int conv_tc_tall_dy_unpool(b200_ctx *ctx, const ConvGeom &g, const float *gpool,
 int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *W, const float *bias,
                 float *out, int B, int act, float *wt, int prep) {
   TallGeom t = tall_geom(g, B);
-  if (prep) B200_TRY(filter_prep(ctx, g, W, g.OC, t.Cp / 32, 0, wt));
+  if (prep) B200_TRY(conv_tc_prep(ctx, g, W, wt, nullptr));
   return launch_conv_tc(ctx, xs, t.Cp, g.WI, t.rows, t.period, wt, g.KH, g.KW, g.pad_t, g.pad_l, g.OC, out,
                         g.OH, g.OW, g.has_bias ? bias : nullptr, act, B);
 }
@@ -994,7 +1093,7 @@ int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *
                float *wt, int prep) {
   TallGeom t = tall_geom(g, B);
   const int period = dy_period(g);
-  if (prep) B200_TRY(filter_prep(ctx, g, W, g.C, t.OCp / 32, 1, wt));
+  if (prep) B200_TRY(conv_tc_prep(ctx, g, W, nullptr, wt));
   return launch_conv_tc(ctx, dys, t.OCp, g.OW, (long long)B * period, period, wt, g.KH, g.KW,
                         g.KH - 1 - g.pad_t, g.KW - 1 - g.pad_l, g.C, din, g.HI, g.WI, nullptr, B200_ACT_NONE,
                         B);
@@ -1306,25 +1405,6 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
   if (warp == TCS_CONV_WARPS) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
 }
 
-// sum of the partial rows -> reference layout: dW[o][k] = sum[k*OCp + o], db[o] = sum[128*OCp + o]
-__global__ void dw_small_permute_kernel(const float *__restrict__ src, float *__restrict__ dW, float *__restrict__ db,
-                                        int C, int OC, int OCp, int KK, const uint8_t *__restrict__ tbl,
-                                        int accumulate) {
-  const int K = C * KK, total = OC * K + (db ? OC : 0);
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    if (i < OC * K) {
-      int o = i / K, k = i - o * K;
-      float v = src[(size_t)k * OCp + o];
-      if (tbl && !tbl[(k / KK) * OC + o]) v = 0.f;
-      dW[i] = accumulate ? dW[i] + v : v;
-    } else {
-      int o = i - OC * K;
-      float v = src[(size_t)128 * OCp + o];
-      db[o] = accumulate ? db[o] + v : v;
-    }
-  }
-}
-
 size_t dw_small_stage(const ConvGeom &g, int OCp, int bw) {
   size_t XB = ((size_t)g.C * g.KH * bw * 4 + 1023) & ~(size_t)1023;
   return 2 * 128 * 128 + 2 * (size_t)OCp * 128 + XB;
@@ -1437,12 +1517,27 @@ int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float
             "converter group 0 %.0f (wait %.0f)\n",
             (double)a.nsteps / a.ksplits, a.nst, s[0], s[1], s[2], s[3], s[4], s[5]);
   }
-  float *sum = part + (size_t)a.ksplits * a.row;
-  B200_TRY(merge_rows(ctx, part, a.ksplits, (size_t)a.row, sum, (size_t)a.row, 0, nullptr));
-  const int total = g.OC * a.Kreal + (g.has_bias && db ? g.OC : 0);
-  dw_small_permute_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(
-    sum, dW, g.has_bias ? db : nullptr, g.C, g.OC, OCp, g.KH * g.KW, g.tbl, accumulate);
-  B200_LAUNCHED();
+  DwFinishArgs f;
+  f.part = part;
+  f.part_stride = a.row;
+  f.splits = a.ksplits;
+  f.bsrc = part;            // the bias sums are the last OCp entries of every partial row
+  f.bs_stride = a.row;
+  f.bs_off = (long long)128 * OCp;
+  f.bs_rows = a.ksplits;
+  f.dW = dW;
+  f.db = g.has_bias ? db : nullptr;
+  f.layout = 1;
+  f.row_w = 128 * OCp;
+  f.C = g.C;
+  f.OC = g.OC;
+  f.OCp = OCp;
+  f.KH = g.KH;
+  f.KW = g.KW;
+  f.ic_slabs = 1;
+  f.tbl = g.tbl;
+  f.accumulate = accumulate;
+  B200_TRY(launch_dw_finish(ctx, f));
   return 0;
 }
 

@@ -111,7 +111,9 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
       case B200_LAYER_CONV:
         if (L.tc.fwd) {
           if (!L.xs_from_pool) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
-          B200_TRY(conv_tc_fwd(ctx, L.g, L.tc_xs, W, b, dst, B, L.fused_act, L.tc_wt_fwd));
+          // the dX pass of this step reads the same weights: both filter matrices in one launch
+          B200_TRY(conv_tc_prep(ctx, L.g, W, L.tc_wt_fwd, L.tc.dx ? L.tc_wt_dx : nullptr));
+          B200_TRY(conv_tc_fwd(ctx, L.g, L.tc_xs, W, b, dst, B, L.fused_act, L.tc_wt_fwd, 0));
         } else if (L.tiled)
           B200_TRY(conv_tiled_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act, L.wt_fwd));
         else
@@ -166,7 +168,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
           B200_TRY(conv_tc_tall_dy(ctx, L.g, L.grad, B, L.tc_dys, L.tc.dw && db ? L.tc_bsum : nullptr));
         if (din) {
           if (tc_dx)
-            B200_TRY(conv_tc_dx(ctx, L.g, L.tc_dys, W, din, B, L.tc_wt_dx));
+            B200_TRY(conv_tc_dx(ctx, L.g, L.tc_dys, W, din, B, L.tc_wt_dx, L.tc.fwd ? 0 : 1));
           else if (tiled_bwd)
             B200_TRY(conv_tiled_dx(ctx, L.g, W, L.grad, din, B, L.wt_dx));
           else
@@ -176,8 +178,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
           if (!L.tc.fwd && !L.xs_from_pool) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
           int splits = 0;
           B200_TRY(conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits));
-          B200_TRY(conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0));
-          if (db) B200_TRY(conv_tc_bias_grad(ctx, L.g, L.tc_bsum, B, db, 0));
+          B200_TRY(conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db));
         } else if (L.tc.dw_small) {
           B200_TRY(conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0));
         } else if (tiled_bwd) {
