@@ -101,53 +101,91 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
   const int npx = nr * W;
   const int valid_px = max(0, min(nr, H - r0)) * W;
   const size_t plane = (size_t)H * W;
-  const int total = C * npx;
+  // phase 1: one warp per channel (channels w, w+8, ...), lanes along the pixels of the chunk
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (src.mode == 0) {
     const float *img = src.a + ((size_t)b * C * H + r0) * W;
-#pragma unroll 8
-    for (int i = threadIdx.x; i < total; i += 256) {
-      int c = i / npx, p = i - c * npx;
-      tile[c * pitch + p] = p < valid_px ? img[c * plane + p] : 0.f;
+    for (int c = warp; c < C; c += 8) {
+      const float *ch = img + c * plane;
+      float *trow = tile + c * pitch;
+#pragma unroll 4
+      for (int p = lane; p < npx; p += 32) trow[p] = p < valid_px ? ch[p] : 0.f;
     }
   } else if (src.mode == 1) {
-    const int in_w = 2 * W, in_h = 2 * H;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < total; i += 256) {
-      int c = i / npx, p = i - c * npx;
-      float best = 0.f;
-      if (p < valid_px) {
-        const int ry = p / W, x = p - ry * W, y = r0 + ry;
-        const float *ip = src.a + (((size_t)b * C + c) * in_h + 2 * y) * in_w + 2 * x;
-        const float2 u = *reinterpret_cast<const float2 *>(ip);
-        const float2 v = *reinterpret_cast<const float2 *>(ip + in_w);
-        const int base = (in_h * c + 2 * y) * in_w + 2 * x;
-        int idx = 0;
-        best = -FLT_MAX;
-        if (u.x > best) { best = u.x; idx = base; }
-        if (u.y > best) { best = u.y; idx = base + 1; }
-        if (v.x > best) { best = v.x; idx = base + in_w; }
-        if (v.y > best) { best = v.y; idx = base + in_w + 1; }
-        const size_t o = ((size_t)b * C + c) * plane + (size_t)y * W + x;
-        src.out_chw[o] = best;
-        src.out_am[o] = idx;
+    // two pooled pixels per lane: 16-byte loads of the two input rows, 8-byte stores
+    const int in_w = 2 * W, in_h = 2 * H, W2 = W >> 1;
+    for (int c = warp; c < C; c += 8) {
+      float *trow = tile + c * pitch;
+      const size_t cplane = ((size_t)b * C + c) * plane;
+      const float *cin = src.a + ((size_t)b * C + c) * in_h * in_w;
+#pragma unroll 2
+      for (int q = lane; q < (npx >> 1); q += 32) {
+        const int ry = q / W2, x = (q - ry * W2) * 2, y = r0 + ry, p = ry * W + x;
+        float best0 = 0.f, best1 = 0.f;
+        if (p < valid_px) {
+          const float *ip = cin + (size_t)(2 * y) * in_w + 2 * x;
+          const float4 u = *reinterpret_cast<const float4 *>(ip);
+          const float4 v = *reinterpret_cast<const float4 *>(ip + in_w);
+          const int base = (in_h * c + 2 * y) * in_w + 2 * x;
+          int i0 = 0, i1 = 0;
+          best0 = best1 = -FLT_MAX;
+          if (u.x > best0) { best0 = u.x; i0 = base; }
+          if (u.y > best0) { best0 = u.y; i0 = base + 1; }
+          if (v.x > best0) { best0 = v.x; i0 = base + in_w; }
+          if (v.y > best0) { best0 = v.y; i0 = base + in_w + 1; }
+          if (u.z > best1) { best1 = u.z; i1 = base + 2; }
+          if (u.w > best1) { best1 = u.w; i1 = base + 3; }
+          if (v.z > best1) { best1 = v.z; i1 = base + in_w + 2; }
+          if (v.w > best1) { best1 = v.w; i1 = base + in_w + 3; }
+          const size_t o = cplane + (size_t)y * W + x;
+          *reinterpret_cast<float2 *>(src.out_chw + o) = make_float2(best0, best1);
+          *reinterpret_cast<int2 *>(src.out_am + o) = make_int2(i0, i1);
+        }
+        trow[p] = best0;
+        trow[p + 1] = best1;
       }
-      tile[c * pitch + p] = best;
     }
   } else {
+    // one pooled pixel per lane: its gradient goes to the one input position argmax names
     const int pw = W >> 1, ph = H >> 1;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < total; i += 256) {
-      int c = i / npx, p = i - c * npx;
-      float v = 0.f;
-      if (p < valid_px) {
-        const int ry = p / W, x = p - ry * W, y = r0 + ry;
-        const size_t po = (((size_t)b * C + c) * ph + (y >> 1)) * pw + (x >> 1);
-        const size_t o = ((size_t)b * C + c) * plane + (size_t)y * W + x;
-        v = src.am[po] == (H * c + y) * W + x ? src.a[po] : 0.f;
-        if (src.relu_y != nullptr && !(src.relu_y[o] > 0.f)) v = 0.f;
-        if (src.out_chw != nullptr) src.out_chw[o] = v;
+    for (int c = warp; c < C; c += 8) {
+      float *trow = tile + c * pitch;
+      const size_t cplane = ((size_t)b * C + c) * plane;
+      const size_t pplane = ((size_t)b * C + c) * ph * pw;
+#pragma unroll 2
+      for (int q = lane; q < ((nr + 1) >> 1) * pw; q += 32) {
+        const int pry = q / pw, prx = q - pry * pw, ry = 2 * pry, x = 2 * prx, y = r0 + ry;
+        float v00 = 0.f, v01 = 0.f, v10 = 0.f, v11 = 0.f;
+        if (y < H) {
+          const size_t po = pplane + (size_t)(y >> 1) * pw + prx;
+          const float gval = src.a[po];
+          const int am = src.am[po] - ((H * c + y) * W + x);  // offset inside the window: 0, 1, W, W+1
+          v00 = am == 0 ? gval : 0.f;
+          v01 = am == 1 ? gval : 0.f;
+          v10 = am == W ? gval : 0.f;
+          v11 = am == W + 1 ? gval : 0.f;
+          const size_t o = cplane + (size_t)y * W + x;
+          if (src.relu_y != nullptr) {
+            const float2 r0v = *reinterpret_cast<const float2 *>(src.relu_y + o);
+            const float2 r1v = *reinterpret_cast<const float2 *>(src.relu_y + o + W);
+            if (!(r0v.x > 0.f)) v00 = 0.f;
+            if (!(r0v.y > 0.f)) v01 = 0.f;
+            if (!(r1v.x > 0.f)) v10 = 0.f;
+            if (!(r1v.y > 0.f)) v11 = 0.f;
+          }
+          if (src.out_chw != nullptr) {
+            *reinterpret_cast<float2 *>(src.out_chw + o) = make_float2(v00, v01);
+            *reinterpret_cast<float2 *>(src.out_chw + o + W) = make_float2(v10, v11);
+          }
+        }
+        const int p = ry * W + x;
+        trow[p] = v00;
+        trow[p + 1] = v01;
+        if (ry + 1 < nr) {
+          trow[p + W] = v10;
+          trow[p + W + 1] = v11;
+        }
       }
-      tile[c * pitch + p] = v;
     }
   }
   __syncthreads();
@@ -167,7 +205,6 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
     lo4[i] = make_float4(l[0], l[1], l[2], l[3]);
   }
   if (bsum != nullptr) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int c = warp; c < C; c += 8) {
       float s = 0.f;
       for (int p = lane; p < valid_px; p += 32) s += tile[c * pitch + p];
@@ -715,14 +752,20 @@ int to_tall_rows(int C, int W, int period) {
   if (rb > period) rb = period;
   // even out the chunks of one image
   int chunks = ceil_div(period, rb);
-  return ceil_div(period, chunks);
+  rb = ceil_div(period, chunks);
+  if ((rb & 1) && rb < period) ++rb;  // even chunks: the pooling gradient is produced two rows at a time
+  return rb;
 }
 
-int to_tall_blocks(int C, int W, int period, int B) { return B * ceil_div(period, to_tall_rows(C, W, period)); }
+int to_tall_blocks(int C, int W, int period, int B) {
+  return B * ceil_div(period, to_tall_rows(C, W, period));
+}
 
 int to_tall(b200_ctx *ctx, const TallSrc &src, int C, int H, int W, int Cp, int period, int B, float *dst,
             float *bsum) {
   const int rb = to_tall_rows(C, W, period);
+  B200_REQUIRE(src.mode != 2 || (((rb & 1) == 0 || rb == period) && (H & 1) == 0),
+               "tall conversion: the pooling gradient needs even row counts");
   const int pitch = ((rb * W + 7) & ~7) + 1;
   size_t smem = (size_t)C * pitch * sizeof(float);
   if (smem > 48 * 1024)
