@@ -513,6 +513,20 @@ B200_API int b200_net_train_step_host(b200_net *net, const float *x_host, const 
                                       int batch, int loss_kind, int opt_kind,
                                       const b200_opt_hyper *h, float *out_host);
 
+/*
+ * network::fit over HOST arrays (tiny_dnn/network.h:840-879): `epochs` passes
+ * over n_samples rows of x_host [n_samples][in_dim] / t_host [n_samples][out_dim]
+ * in mini-batches of `batch` (the last one of a pass may be smaller, as in the
+ * reference), one training step each.  The upload of the next mini-batch runs
+ * on a second stream while the current step computes (pinned host memory makes
+ * that overlap real).  With `out_host` [n_samples][out_dim] not NULL the
+ * forward output of every step is copied back to its rows (the last epoch's
+ * values remain).  Returns after everything has finished.
+ */
+B200_API int b200_net_fit_host(b200_net *net, const float *x_host, const float *t_host,
+                               long long n_samples, int batch, int epochs, int loss_kind,
+                               int opt_kind, const b200_opt_hyper *h, float *out_host);
+
 /* Adam powers currently held by the net (tests; T = tensor count). */
 B200_API int b200_net_adam_powers(const b200_net *net, float *b1_t, float *b2_t);
 

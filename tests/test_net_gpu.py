@@ -195,6 +195,39 @@ def test_sequential_mirror_lenet_100_steps(ctx, oracle):
     net.close()
 
 
+def test_fit_host_equals_step_by_step(ctx):
+    """b200_net_fit_host (uploads overlapped with the steps, ragged last mini-batch, two epochs)
+    ends with exactly the weights of one b200_net_train_step_host call per mini-batch, and
+    returns every step's forward output."""
+    specs, keep = build_net_specs("cifar")
+    B, n = 8, 28  # 3 full mini-batches and one of 4 per epoch
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((n, 3072)).astype(np.float32)
+    t = np.zeros((n, 10), np.float32)
+    t[np.arange(n), rng.integers(0, 10, n)] = 1.0
+    p0 = xavier_params(specs, 11)
+    h = hyper_for(1)
+    a, b = DeviceNet(ctx, specs, B), DeviceNet(ctx, specs, B)
+    a.set_params(p0)
+    b.set_params(p0)
+    outs_a = np.zeros((n, 10), np.float32)
+    outs_b = np.zeros((n, 10), np.float32)
+    xp, tp = torch.from_numpy(x).pin_memory(), torch.from_numpy(t).pin_memory()
+    check(a.lib.b200_net_fit_host(a.h, ptr(xp), ptr(tp), n, B, 2, 1, 1, C.byref(h), ptr(outs_a)))
+    for epoch in range(2):
+        for i in range(0, n, B):
+            nb = min(B, n - i)
+            out = np.empty((nb, 10), np.float32)
+            check(b.lib.b200_net_train_step_host(b.h, ptr(np.ascontiguousarray(x[i:i + nb])),
+                                                 ptr(np.ascontiguousarray(t[i:i + nb])), nb, 1, 1, C.byref(h),
+                                                 ptr(out)))
+            outs_b[i:i + nb] = out
+    assert np.array_equal(a.params(), b.params())
+    assert np.array_equal(outs_a, outs_b)
+    a.close()
+    b.close()
+
+
 def test_net_rejects_bad_input(ctx):
     specs, keep = build_net_specs("tiny_conv")
     dnet = DeviceNet(ctx, specs, 4)

@@ -64,6 +64,10 @@ struct b200_net {
   float pow_b1 = 0.f, pow_b2 = 0.f;
   float *in_grad = nullptr;  // dE/d input of the first layer
   float *x_dev = nullptr, *t_dev = nullptr;  // staging for the HOST step
+  // b200_net_fit_host: uploads of the next mini-batch overlap the step of the current one
+  cudaStream_t copy_stream = nullptr;
+  float *x_stage[2] = {nullptr, nullptr}, *t_stage[2] = {nullptr, nullptr};
+  cudaEvent_t up_done[2] = {nullptr, nullptr}, stage_free[2] = {nullptr, nullptr};
   int cur_batch = 0;
   const float *cur_x = nullptr;
   bool fuse = true;
@@ -497,6 +501,13 @@ int b200_net_destroy(b200_net *net) {
   cudaFree(net->segs_dev);
   cudaFree(net->pow_tab);
   cudaFree(net->in_grad);
+  for (int i = 0; i < 2; ++i) {
+    cudaFree(net->x_stage[i]);
+    cudaFree(net->t_stage[i]);
+    if (net->up_done[i]) cudaEventDestroy(net->up_done[i]);
+    if (net->stage_free[i]) cudaEventDestroy(net->stage_free[i]);
+  }
+  if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
   cudaFree(net->x_dev);
   cudaFree(net->t_dev);
   delete net;
@@ -702,6 +713,56 @@ int b200_net_train_step_host(b200_net *net, const float *x_host, const float *t_
   if (out_host)
     B200_CUDA(cudaMemcpyAsync(out_host, net->layers.back().out, out_dim * batch * sizeof(float),
                               cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  return 0;
+}
+
+int b200_net_fit_host(b200_net *net, const float *x_host, const float *t_host, long long n_samples,
+                      int batch, int epochs, int loss_kind, int opt_kind, const b200_opt_hyper *h,
+                      float *out_host) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(x_host && t_host && h, "net_fit_host: NULL argument");
+  B200_REQUIRE(batch >= 1 && batch <= net->max_batch, "net_fit_host: batch %d outside 1..%d", batch,
+               net->max_batch);
+  B200_REQUIRE(n_samples >= 0 && epochs >= 0, "net_fit_host: negative count");
+  cudaStream_t st = net->ctx->stream;
+  const size_t in_dim = net->layers.front().in_dim, out_dim = net->layers.back().out_dim;
+  if (!net->copy_stream) {
+    B200_CUDA(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      B200_TRY(net_alloc((void **)&net->x_stage[i], in_dim * net->max_batch * sizeof(float)));
+      B200_TRY(net_alloc((void **)&net->t_stage[i], out_dim * net->max_batch * sizeof(float)));
+      B200_CUDA(cudaEventCreateWithFlags(&net->up_done[i], cudaEventDisableTiming));
+      B200_CUDA(cudaEventCreateWithFlags(&net->stage_free[i], cudaEventDisableTiming));
+    }
+  }
+  // whatever the compute stream has queued so far must not be overtaken by the first upload's
+  // consumer; the staging buffers themselves are free (every earlier fit ended with a sync)
+  long long step = 0;
+  for (int e = 0; e < epochs; ++e) {
+    for (long long i = 0; i < n_samples; i += batch, ++step) {
+      const int nb = (int)((n_samples - i) < batch ? (n_samples - i) : batch);  // ragged last batch
+      const int buf = (int)(step & 1);
+      if (step >= 2) B200_CUDA(cudaStreamWaitEvent(net->copy_stream, net->stage_free[buf], 0));
+      B200_CUDA(cudaMemcpyAsync(net->x_stage[buf], x_host + (size_t)i * in_dim, in_dim * nb * sizeof(float),
+                                cudaMemcpyHostToDevice, net->copy_stream));
+      B200_CUDA(cudaMemcpyAsync(net->t_stage[buf], t_host + (size_t)i * out_dim, out_dim * nb * sizeof(float),
+                                cudaMemcpyHostToDevice, net->copy_stream));
+      B200_CUDA(cudaEventRecord(net->up_done[buf], net->copy_stream));
+      B200_CUDA(cudaStreamWaitEvent(st, net->up_done[buf], 0));
+      // the captured step reads fixed buffers: hand the mini-batch over with a device copy
+      B200_CUDA(cudaMemcpyAsync(net->x_dev, net->x_stage[buf], in_dim * nb * sizeof(float),
+                                cudaMemcpyDeviceToDevice, st));
+      B200_CUDA(cudaMemcpyAsync(net->t_dev, net->t_stage[buf], out_dim * nb * sizeof(float),
+                                cudaMemcpyDeviceToDevice, st));
+      B200_CUDA(cudaEventRecord(net->stage_free[buf], st));
+      B200_TRY(b200_net_train_step(net, net->x_dev, net->t_dev, nb, loss_kind, opt_kind, h));
+      if (out_host)
+        B200_CUDA(cudaMemcpyAsync(out_host + (size_t)i * out_dim, net->layers.back().out,
+                                  out_dim * nb * sizeof(float), cudaMemcpyDeviceToHost, st));
+    }
+  }
+  B200_CUDA(cudaStreamSynchronize(net->copy_stream));
   B200_CUDA(cudaStreamSynchronize(st));
   return 0;
 }

@@ -263,12 +263,13 @@ class Sequential:
                                                 x_host.shape[0], loss, opt.kind, C.byref(h),
                                                 ptr(out_host)))
 
-    def fit(self, opt, inputs, targets, batch_size: int, epochs: int, loss: int):
-        """network::fit (tiny_dnn/network.h:840-879) over HOST arrays [N][dim]."""
-        n = inputs.shape[0]
-        for _ in range(epochs):
-            for i in range(0, n, batch_size):
-                self.train_onebatch_host(opt, inputs[i:i + batch_size], targets[i:i + batch_size], loss)
+    def fit(self, opt, inputs, targets, batch_size: int, epochs: int, loss: int, outputs=None):
+        """network::fit (tiny_dnn/network.h:840-879) over HOST arrays [N][dim]: one library call,
+        uploads overlapped with the steps.  `outputs` [N][out_dim] receives every step's forward
+        output."""
+        h = opt.hyper()
+        check(self.lib.b200_net_fit_host(self.handle, ptr(inputs), ptr(targets), inputs.shape[0],
+                                         batch_size, epochs, loss, opt.kind, C.byref(h), ptr(outputs)))
 
     def adam_powers(self):
         a, b = C.c_float(), C.c_float()
