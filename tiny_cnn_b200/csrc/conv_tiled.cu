@@ -530,6 +530,129 @@ size_t conv_tiled_dx_scratch(const ConvGeom &g) {
   return (size_t)g.OC * g.KH * g.KW * padded_channels(g.C);
 }
 
+// ---------------------------------------------------------------------------
+// direct convolution with at most four input channels (forward of a first layer)
+// ---------------------------------------------------------------------------
+//
+// out[n][co][y][x] = act(bias[co] + sum_{ci,wy,wx} wt[ci][wy][wx][co] * in[n][ci][y+wy-pad_t][x+wx-pad_l])
+// A block covers a 32 x 8 output tile of one image for all output channels: thread = (2 x 4 pixel
+// patch, group of 8 output channels), 64 accumulators.  The whole input tile (all <= 4 channels)
+// is staged once; per input channel a thread reads its (2+KH-1) x (4+KW-1) window into registers
+// and applies all taps, fetching the 8 weights of a tap with two broadcast 16-byte loads.
+
+constexpr int FI_TILE_W = 32, FI_TILE_H = 8, FI_PX = 4, FI_PY = 2, FI_OCG = 8;
+constexpr int FI_PATCHES = (FI_TILE_W / FI_PX) * (FI_TILE_H / FI_PY);  // 32: one warp per channel group
+
+struct FewInCfg {
+  const float *in;    // [B][CI][HI][WI]
+  const float *wt;    // [CI][KH*KW][COp]  (COp a multiple of 8)
+  const float *bias;  // CO values or nullptr
+  float *out;         // [B][CO][HO][WO]
+  int CI, HI, WI, CO, COp, HO, WO, pad_t, pad_l, tiles_x, act;
+};
+
+template <int KH, int KW>
+__global__ void __launch_bounds__(256) conv_fewin_kernel(const FewInCfg p) {
+  constexpr int KK = KH * KW;
+  constexpr int TH = FI_TILE_H + KH - 1;
+  constexpr int PITCH = (FI_TILE_W + KW - 1 + 3) & ~3;
+  constexpr int WC = FI_PX + KW - 1, WC4 = (WC + 3) / 4;
+  extern __shared__ __align__(16) float fi_smem[];
+  float *wsm = fi_smem;                          // [CI][KK][COp]
+  float *xs = fi_smem + p.CI * KK * p.COp;       // [CI][TH][PITCH]
+  const int tid = threadIdx.x, grp = tid / FI_PATCHES, t = tid - grp * FI_PATCHES, tx = t & 7, ty = t >> 3;
+  const int b = blockIdx.y, tile = blockIdx.x;
+  const int x0 = (tile % p.tiles_x) * FI_TILE_W, y0 = (tile / p.tiles_x) * FI_TILE_H;
+  const int nthreads = blockDim.x;
+  for (int i = tid; i < p.CI * KK * p.COp / 4; i += nthreads)
+    reinterpret_cast<float4 *>(wsm)[i] = reinterpret_cast<const float4 *>(p.wt)[i];
+  const float *img = p.in + (size_t)b * p.CI * p.HI * p.WI;
+  for (int i = tid; i < p.CI * TH * PITCH; i += nthreads) {
+    const int col = i % PITCH, r = i / PITCH, row = r % TH, c = r / TH;
+    const int gy = y0 + row - p.pad_t, gx = x0 + col - p.pad_l;
+    const bool ok = gy >= 0 && gy < p.HI && gx >= 0 && gx < p.WI;
+    cp_async4(xs + i, ok ? img + ((size_t)c * p.HI + gy) * p.WI + gx : img, ok);
+  }
+  cp_async_commit();
+  float acc[FI_OCG][FI_PY][FI_PX];
+#pragma unroll
+  for (int n = 0; n < FI_OCG; ++n)
+#pragma unroll
+    for (int i = 0; i < FI_PY; ++i)
+#pragma unroll
+      for (int j = 0; j < FI_PX; ++j) acc[n][i][j] = 0.f;
+  cp_async_wait<0>();
+  __syncthreads();
+  // one (input channel, window row) per iteration: a loop body of KW * 64 FFMAs stays in the
+  // instruction cache, which the fully unrolled KH*KW body does not
+#pragma unroll 1
+  for (int it = 0; it < p.CI * KH; ++it) {
+    const int ci = it / KH, wy = it - ci * KH;
+    float win[FI_PY][WC4 * 4];
+    const float *wp = xs + ((size_t)ci * TH + ty * FI_PY + wy) * PITCH + tx * FI_PX;
+#pragma unroll
+    for (int r = 0; r < FI_PY; ++r)
+#pragma unroll
+      for (int q = 0; q < WC4; ++q) {
+        const float4 v = *reinterpret_cast<const float4 *>(wp + r * PITCH + 4 * q);
+        win[r][4 * q] = v.x;
+        win[r][4 * q + 1] = v.y;
+        win[r][4 * q + 2] = v.z;
+        win[r][4 * q + 3] = v.w;
+      }
+    const float *wc = wsm + ((size_t)ci * KK + wy * KW) * p.COp + grp * FI_OCG;
+#pragma unroll
+    for (int wx = 0; wx < KW; ++wx) {
+      const float4 wa = *reinterpret_cast<const float4 *>(wc + wx * p.COp);
+      const float4 wb = *reinterpret_cast<const float4 *>(wc + wx * p.COp + 4);
+      const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+      for (int n = 0; n < FI_OCG; ++n)
+#pragma unroll
+        for (int i = 0; i < FI_PY; ++i)
+#pragma unroll
+          for (int j = 0; j < FI_PX; ++j) acc[n][i][j] = fmaf(w[n], win[i][j + wx], acc[n][i][j]);
+    }
+  }
+  const int ox = x0 + tx * FI_PX, oy = y0 + ty * FI_PY;
+#pragma unroll
+  for (int n = 0; n < FI_OCG; ++n) {
+    const int co = grp * FI_OCG + n;
+    if (co >= p.CO) break;
+    const float bv = p.bias ? __ldg(p.bias + co) : 0.f;
+#pragma unroll
+    for (int i = 0; i < FI_PY; ++i) {
+      if (oy + i >= p.HO) continue;
+      float *o = p.out + (((size_t)b * p.CO + co) * p.HO + oy + i) * p.WO + ox;
+      float v[FI_PX];
+#pragma unroll
+      for (int j = 0; j < FI_PX; ++j) v[j] = apply_act(acc[n][i][j] + bv, p.act);
+      if (ox + FI_PX <= p.WO && (p.WO & 3) == 0) {
+        *reinterpret_cast<float4 *>(o) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < FI_PX; ++j)
+          if (ox + j < p.WO) o[j] = v[j];
+      }
+    }
+  }
+}
+
+static size_t fewin_smem(int CI, int COp, int KH, int KW) {
+  size_t TH = FI_TILE_H + KH - 1, PITCH = (FI_TILE_W + KW - 1 + 3) & ~3;
+  return ((size_t)CI * KH * KW * COp + (size_t)CI * TH * PITCH) * 4;
+}
+
+template <int KH, int KW>
+static int launch_fewin(b200_ctx *ctx, const FewInCfg &p, int B) {
+  size_t smem = fewin_smem(p.CI, p.COp, KH, KW);
+  dim3 grid(p.tiles_x * ceil_div(p.HO, FI_TILE_H), B);
+  B200_CUDA(cudaFuncSetAttribute(conv_fewin_kernel<KH, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  conv_fewin_kernel<KH, KW><<<grid, FI_PATCHES * (p.COp / FI_OCG), smem, ctx->stream>>>(p);
+  B200_LAUNCHED();
+  return 0;
+}
+
 int conv_tiled_fwd(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *W,
                    const float *bias, float *out, int B, int act, float *scratch) {
   if (B == 0) return 0;
@@ -539,6 +662,26 @@ int conv_tiled_fwd(b200_ctx *ctx, const ConvGeom &g, const float *in, const floa
   conv_prep_wt_fwd_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(W, scratch, g.C, g.OC,
                                                                         COp, KK, g.tbl);
   B200_LAUNCHED();
+  if (g.C <= 4 && COp % 8 == 0 && COp <= 64 && fewin_smem(g.C, COp, g.KH, g.KW) <= ctx->smem_optin) {
+    FewInCfg f{};
+    f.in = in;
+    f.wt = scratch;
+    f.bias = g.has_bias ? bias : nullptr;
+    f.out = out;
+    f.CI = g.C;
+    f.HI = g.HI;
+    f.WI = g.WI;
+    f.CO = g.OC;
+    f.COp = COp;
+    f.HO = g.OH;
+    f.WO = g.OW;
+    f.pad_t = g.pad_t;
+    f.pad_l = g.pad_l;
+    f.tiles_x = ceil_div(g.OW, FI_TILE_W);
+    f.act = act;
+    if (g.KH == 5 && g.KW == 5) return launch_fewin<5, 5>(ctx, f, B);
+    if (g.KH == 3 && g.KW == 3) return launch_fewin<3, 3>(ctx, f, B);
+  }
   CoreCfg p{};
   p.in = in;
   p.wt = scratch;
@@ -586,7 +729,7 @@ __global__ void __launch_bounds__(FO_THREADS) conv_fewout_kernel(const FewOutCfg
   constexpr int KK = KH * KW;
   constexpr int TH = FO_TILE_H + KH - 1;               // staged rows
   constexpr int PITCH = (FO_TILE + KW - 1 + 3) & ~3;   // staged row pitch (floats, 16-byte rows)
-  constexpr int WR = FO_PY + KH - 1, WC = FO_PX + KW - 1;  // register window
+  constexpr int WC = FO_PX + KW - 1;                   // register window columns
   constexpr int WC4 = (WC + 3) / 4;                    // 16-byte loads per window row
   extern __shared__ __align__(16) float fo_smem[];
   float *wsm = fo_smem;                                // [CI][KK][4]
@@ -646,21 +789,22 @@ __global__ void __launch_bounds__(FO_THREADS) conv_fewout_kernel(const FewOutCfg
     {
       const int c = z, ci = chunk * FO_ICB + c;
       if (ci < p.CI) {
-      float win[WR][WC4 * 4];
-      const float *wp = xb + ((size_t)c * TH + ty * FO_PY) * PITCH + tx * FO_PX;
-#pragma unroll
-      for (int r = 0; r < WR; ++r)
-#pragma unroll
-        for (int q = 0; q < WC4; ++q) {
-          const float4 v = *reinterpret_cast<const float4 *>(wp + r * PITCH + 4 * q);
-          win[r][4 * q] = v.x;
-          win[r][4 * q + 1] = v.y;
-          win[r][4 * q + 2] = v.z;
-          win[r][4 * q + 3] = v.w;
-        }
       const float4 *wc = reinterpret_cast<const float4 *>(wsm) + (size_t)ci * KK;
+      // one window row per iteration keeps the loop body inside the instruction cache
+#pragma unroll 1
+      for (int wy = 0; wy < KH; ++wy) {
+        float win[FO_PY][WC4 * 4];
+        const float *wp = xb + ((size_t)c * TH + ty * FO_PY + wy) * PITCH + tx * FO_PX;
 #pragma unroll
-      for (int wy = 0; wy < KH; ++wy)
+        for (int r = 0; r < FO_PY; ++r)
+#pragma unroll
+          for (int q = 0; q < WC4; ++q) {
+            const float4 v = *reinterpret_cast<const float4 *>(wp + r * PITCH + 4 * q);
+            win[r][4 * q] = v.x;
+            win[r][4 * q + 1] = v.y;
+            win[r][4 * q + 2] = v.z;
+            win[r][4 * q + 3] = v.w;
+          }
 #pragma unroll
         for (int wx = 0; wx < KW; ++wx) {
           const float4 w4 = wc[wy * KW + wx];
@@ -670,8 +814,9 @@ __global__ void __launch_bounds__(FO_THREADS) conv_fewout_kernel(const FewOutCfg
 #pragma unroll
             for (int i = 0; i < FO_PY; ++i)
 #pragma unroll
-              for (int j = 0; j < FO_PX; ++j) acc[n][i][j] = fmaf(w[n], win[i + wy][j + wx], acc[n][i][j]);
+              for (int j = 0; j < FO_PX; ++j) acc[n][i][j] = fmaf(w[n], win[i][j + wx], acc[n][i][j]);
         }
+      }
     }
     }
     __syncthreads();
