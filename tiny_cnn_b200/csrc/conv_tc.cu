@@ -901,7 +901,8 @@ struct DwFinishArgs {
 };
 
 __global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) {
-  __shared__ float lanes[8][33];
+  constexpr int RL = 8;  // row lanes
+  __shared__ float lanes[RL][33];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int total = a.row_w + (a.db != nullptr ? a.OC : 0);
   for (int base = blockIdx.x * 32; base < total; base += gridDim.x * 32) {
@@ -910,17 +911,17 @@ __global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) {
     if (e < a.row_w) {
       const float *src = a.part + e;
       int r = ty;
-      for (; r + 8 < a.splits; r += 16) {
+      for (; r + RL < a.splits; r += 2 * RL) {
         s0 += src[(size_t)r * a.part_stride];
-        s1 += src[(size_t)(r + 8) * a.part_stride];
+        s1 += src[(size_t)(r + RL) * a.part_stride];
       }
       if (r < a.splits) s0 += src[(size_t)r * a.part_stride];
     } else if (e < total) {
       const float *src = a.bsrc + a.bs_off + (e - a.row_w);
       int r = ty;
-      for (; r + 8 < a.bs_rows; r += 16) {
+      for (; r + RL < a.bs_rows; r += 2 * RL) {
         s0 += src[(size_t)r * a.bs_stride];
-        s1 += src[(size_t)(r + 8) * a.bs_stride];
+        s1 += src[(size_t)(r + RL) * a.bs_stride];
       }
       if (r < a.bs_rows) s0 += src[(size_t)r * a.bs_stride];
     }
@@ -929,7 +930,7 @@ __global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) {
     if (ty == 0 && e < total) {
       float s = lanes[0][tx];
 #pragma unroll
-      for (int k = 1; k < 8; ++k) s += lanes[k][tx];
+      for (int k = 1; k < RL; ++k) s += lanes[k][tx];
       if (e >= a.row_w) {
         float *d = a.db + (e - a.row_w);
         *d = a.accumulate ? *d + s : s;
@@ -1209,10 +1210,11 @@ int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *d
 
 namespace {
 
-constexpr int TCS_MAX_STAGES = 6;
+constexpr int TCS_MAX_STAGES = 3;     // three are enough to hide the loads and leave shared memory for a co-resident kernel
 constexpr int TCS_PX = 32;          // pixels per step (one 128-byte operand row)
-constexpr int TCS_GROUPS = 4;       // converter groups; group g converts the steps i with i % 4 == g
-constexpr int TCS_GROUP_WARPS = 2;
+constexpr int TCS_GROUPS = 2;       // converter groups; group g converts the steps i with i % 2 == g
+constexpr int TCS_GROUP_WARPS = 4;
+static_assert(TCS_GROUPS <= 2, "a group's first step must be the first use of its stage: stages >= groups");
 constexpr int TCS_CONV_WARPS = TCS_GROUPS * TCS_GROUP_WARPS;  // then one TMA warp and one MMA warp
 constexpr int TCS_THREADS = (TCS_CONV_WARPS + 2) * 32;
 
@@ -1252,7 +1254,7 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
   if (tid == 0) {
     for (int s = 0; s < a.nst; ++s) {
       mbar_init(&tma_full[s], 1);
-      mbar_init(&op_full[s], TCS_GROUP_WARPS);
+      mbar_init(&op_full[s], TCS_CONV_WARPS);
       mbar_init(&op_empty[s], 1);
     }
     mbar_init(accum, 1);
@@ -1354,7 +1356,10 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
 #pragma unroll
     for (int q = 0; q < NB; ++q) bacc[q] = 0.f;
     long long w = 0, t0 = clock64(), tq;
-    for (int s = s_begin + grp; s < s_end; s += TCS_GROUPS) {
+    // Every converter warp observes every step's barrier, in order, and takes part in the
+    // hand-over, although only the step's group converts: a warp that skipped phases of an
+    // mbarrier could no longer tell one phase from the one two later (the wait is by parity).
+    for (int s = s_begin; s < s_end; ++s) {
       const uint32_t i = s - s_begin, st = i % a.nst;
       tq = clock64();
       if (!mbar_wait_bounded(&tma_full[st], (i / a.nst) & 1)) {
@@ -1362,6 +1367,11 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
         break;
       }
       w += clock64() - tq;
+      if ((int)(i % TCS_GROUPS) != grp) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&op_full[st]);
+        continue;
+      }
       uint8_t *p = smem + (size_t)st * STAGE;
       const int x0 = (s % a.nxb) * TCS_PX;
       const int d = (x0 - a.pad_l) - ((x0 - a.pad_l) & ~3);  // offset of the first needed column
@@ -1460,7 +1470,9 @@ size_t dw_small_fixed(int OCp) {
 // pipeline stages that fit (0: the kernel does not fit)
 int dw_small_stages(const b200_ctx *ctx, const ConvGeom &g, int OCp, int bw) {
   size_t fixed = dw_small_fixed(OCp), stage = dw_small_stage(g, OCp, bw);
-  if (ctx->smem_optin < fixed + 2 * stage) return 0;
+  // at least as many stages as converter groups: a group waiting for the second use of a stage
+  // before its first use has happened would see the barrier's parity as already satisfied
+  if (ctx->smem_optin < fixed + TCS_GROUPS * stage) return 0;
   size_t n = (ctx->smem_optin - fixed) / stage;
   return (int)(n > TCS_MAX_STAGES ? TCS_MAX_STAGES : n);
 }
@@ -1478,7 +1490,7 @@ bool conv_dw_small_ok(const b200_ctx *ctx, const ConvGeom &g) {
   TallGeom t = tall_geom(g, 1);
   if (g.pad_t < 0 || g.pad_l < 0 || t.pad_b < 0 || t.pad_r < 0) return false;
   const int OCp = (g.OC + 15) / 16 * 16;
-  return dw_small_stages(ctx, g, OCp, dw_small_bw(g)) >= 2;
+  return dw_small_stages(ctx, g, OCp, dw_small_bw(g)) >= TCS_GROUPS;
 }
 
 int conv_dw_small_splits(const b200_ctx *ctx, const ConvGeom &g, int B) {
@@ -1537,7 +1549,7 @@ int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float
   a.nsteps = B * g.OH * a.nxb;
   a.ksplits = conv_dw_small_splits(ctx, g, B);
   a.nst = dw_small_stages(ctx, g, OCp, bw);
-  B200_REQUIRE(a.nst >= 2, "conv_dw_small: the tiles do not fit shared memory");
+  B200_REQUIRE(a.nst >= TCS_GROUPS, "conv_dw_small: the tiles do not fit shared memory");
   a.tmem_cols = pow2_at_least(2 * OCp);
   a.row = (long long)129 * OCp;
   const size_t smem = dw_small_fixed(OCp) + (size_t)a.nst * dw_small_stage(g, OCp, bw);

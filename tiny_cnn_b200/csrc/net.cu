@@ -64,6 +64,10 @@ struct b200_net {
   float pow_b1 = 0.f, pow_b2 = 0.f;
   float *in_grad = nullptr;  // dE/d input of the first layer
   float *x_dev = nullptr, *t_dev = nullptr;  // staging for the HOST step
+  // side stream for independent work of one layer's backward pass (a tensor-core dW beside an
+  // FFMA dX use different units of the SM and share it)
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   // b200_net_fit_host: uploads of the next mini-batch overlap the step of the current one
   cudaStream_t copy_stream = nullptr;
   float *x_stage[2] = {nullptr, nullptr}, *t_stage[2] = {nullptr, nullptr};
@@ -170,6 +174,20 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
         const bool tc_dx = L.tc.dx && din != nullptr;
         if ((tc_dx || L.tc.dw) && !L.dys_from_pool)
           B200_TRY(conv_tc_tall_dy(ctx, L.g, L.grad, B, L.tc_dys, L.tc.dw && db ? L.tc_bsum : nullptr));
+        // An FFMA dX and the tensor-core dW of a layer with few input channels keep different
+        // units busy: the dW branch goes to the side stream, first, so that its one block per SM
+        // is resident when the many small dX blocks arrive, and both share the SMs.
+        const bool dw_on_side = L.tc.dw_small && din != nullptr && !tc_dx && net->side != nullptr;
+        cudaStream_t main_stream = ctx->stream;
+        if (dw_on_side) {
+          B200_CUDA(cudaEventRecord(net->ev_fork, main_stream));
+          B200_CUDA(cudaStreamWaitEvent(net->side, net->ev_fork, 0));
+          ctx->stream = net->side;
+          int rc = conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0);
+          ctx->stream = main_stream;
+          B200_TRY(rc);
+          B200_CUDA(cudaEventRecord(net->ev_join, net->side));
+        }
         if (din) {
           if (tc_dx)
             B200_TRY(conv_tc_dx(ctx, L.g, L.tc_dys, W, din, B, L.tc_wt_dx, L.tc.fwd ? 0 : 1));
@@ -177,6 +195,10 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
             B200_TRY(conv_tiled_dx(ctx, L.g, W, L.grad, din, B, L.wt_dx));
           else
             B200_TRY(conv_general_dx(ctx, L.g, W, L.grad, din, B));
+        }
+        if (dw_on_side) {
+          B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_join, 0));
+          break;
         }
         if (L.tc.dw) {
           if (!L.tc.fwd && !L.xs_from_pool) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
@@ -300,6 +322,11 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
   net->layers.resize(n_layers);
   if (const char *e = getenv("B200_NET_NO_FUSE")) net->fuse = !(e[0] == '1');
   if (const char *e = getenv("B200_NET_NO_GRAPH")) net->use_graph = !(e[0] == '1');
+  if (!getenv("B200_NET_NO_SIDE")) {
+    cudaStreamCreateWithFlags(&net->side, cudaStreamNonBlocking);
+    cudaEventCreateWithFlags(&net->ev_fork, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&net->ev_join, cudaEventDisableTiming);
+  }
   size_t off = 0;
   size_t prev_out = 0;
   for (int i = 0; i < n_layers; ++i) {
@@ -508,6 +535,9 @@ int b200_net_destroy(b200_net *net) {
     if (net->stage_free[i]) cudaEventDestroy(net->stage_free[i]);
   }
   if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+  if (net->side) cudaStreamDestroy(net->side);
+  if (net->ev_fork) cudaEventDestroy(net->ev_fork);
+  if (net->ev_join) cudaEventDestroy(net->ev_join);
   cudaFree(net->x_dev);
   cudaFree(net->t_dev);
   delete net;
