@@ -51,13 +51,36 @@ __global__ void act_bwd_kernel(int kind, const float *__restrict__ y, const floa
 }
 
 // softmax_layer.h:24-34: subtract the row max, exponentiate, divide by the sum
-// accumulated in index order.  One thread per row (rows are 10 wide here).
+// accumulated in index order.  One thread per row (rows are 10 wide here); rows of at most
+// SM_REG values are kept in registers between the passes.
+constexpr int SM_REG = 16;
+
 __global__ void softmax_fwd_kernel(const float *__restrict__ x, float *__restrict__ y, int dim,
                                    int B) {
   int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= B) return;
   const float *xr = x + (size_t)n * dim;
   float *yr = y + (size_t)n * dim;
+  if (dim <= SM_REG) {
+    float v[SM_REG];
+#pragma unroll
+    for (int j = 0; j < SM_REG; ++j) v[j] = j < dim ? xr[j] : 0.f;
+    float alpha = v[0];
+#pragma unroll
+    for (int j = 1; j < SM_REG; ++j)
+      if (j < dim) alpha = fmaxf(alpha, v[j]);
+    float denom = 0.f;
+#pragma unroll
+    for (int j = 0; j < SM_REG; ++j)
+      if (j < dim) {
+        v[j] = expf(v[j] - alpha);
+        denom += v[j];
+      }
+#pragma unroll
+    for (int j = 0; j < SM_REG; ++j)
+      if (j < dim) yr[j] = v[j] / denom;
+    return;
+  }
   float alpha = xr[0];
   for (int j = 1; j < dim; ++j) alpha = fmaxf(alpha, xr[j]);
   float denom = 0.f;
@@ -69,14 +92,55 @@ __global__ void softmax_fwd_kernel(const float *__restrict__ x, float *__restric
   for (int j = 0; j < dim; ++j) yr[j] = yr[j] / denom;
 }
 
+__device__ __forceinline__ float loss_grad_one(int kind, float yi, float ti, float factor) {
+  if (kind == B200_LOSS_MSE) return __fmul_rn(factor, __fsub_rn(yi, ti));
+  if (kind == B200_LOSS_CROSS_ENTROPY)
+    return __fdiv_rn(__fsub_rn(yi, ti), __fmul_rn(yi, __fsub_rn(1.f, yi)));
+  return __fdiv_rn(-ti, yi);
+}
+
 // softmax_layer.h:36-55: dx_j = sum_k dy_k * (k == j ? y_j(1-y_j) : -y_k*y_j)
-__global__ void softmax_bwd_kernel(const float *__restrict__ y, const float *__restrict__ dy,
-                                   float *__restrict__ dx, int dim, int B) {
+// With `t` != nullptr the incoming gradient is first computed as the loss gradient of (y, t)
+// (loss_function.h) and stored to dy: the loss-gradient and softmax-gradient kernels in one.
+__global__ void softmax_bwd_kernel(const float *__restrict__ y, float *__restrict__ dy,
+                                   float *__restrict__ dx, int dim, int B, const float *__restrict__ t,
+                                   int loss_kind) {
   int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= B) return;
   const float *yr = y + (size_t)n * dim;
-  const float *gr = dy + (size_t)n * dim;
+  float *gr = dy + (size_t)n * dim;
   float *dr = dx + (size_t)n * dim;
+  const float factor = 2.0f / (float)dim;
+  if (dim <= SM_REG) {
+    float yv[SM_REG], gv[SM_REG];
+#pragma unroll
+    for (int j = 0; j < SM_REG; ++j) {
+      yv[j] = j < dim ? yr[j] : 0.f;
+      if (t != nullptr) {
+        gv[j] = j < dim ? loss_grad_one(loss_kind, yv[j], t[(size_t)n * dim + j], factor) : 0.f;
+        if (j < dim) gr[j] = gv[j];
+      } else {
+        gv[j] = j < dim ? gr[j] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < SM_REG; ++j) {
+      if (j < dim) {
+        const float yj = yv[j];
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < SM_REG; ++k)
+          if (k < dim) {
+            float df = (k == j) ? __fmul_rn(yj, __fsub_rn(1.f, yj)) : __fmul_rn(-yv[k], yj);
+            s = __fadd_rn(s, __fmul_rn(gv[k], df));
+          }
+        dr[j] = s;
+      }
+    }
+    return;
+  }
+  if (t != nullptr)
+    for (int j = 0; j < dim; ++j) gr[j] = loss_grad_one(loss_kind, yr[j], t[(size_t)n * dim + j], factor);
   for (int j = 0; j < dim; ++j) {
     float yj = yr[j];
     float s = 0.f;
@@ -95,14 +159,7 @@ __global__ void loss_grad_kernel(int kind, const float *__restrict__ y, const fl
   size_t step = (size_t)gridDim.x * blockDim.x;
   const float factor = 2.0f / (float)dim;
   for (; i < n; i += step) {
-    float yi = y[i], ti = t[i], g;
-    if (kind == B200_LOSS_MSE)
-      g = __fmul_rn(factor, __fsub_rn(yi, ti));
-    else if (kind == B200_LOSS_CROSS_ENTROPY)
-      g = __fdiv_rn(__fsub_rn(yi, ti), __fmul_rn(yi, __fsub_rn(1.f, yi)));
-    else
-      g = __fdiv_rn(-ti, yi);
-    dy[i] = g;
+    dy[i] = loss_grad_one(kind, y[i], t[i], factor);
   }
 }
 
@@ -147,7 +204,7 @@ int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B) {
   size_t n = (size_t)dim * B;
   if (n == 0) return 0;
   if (kind == B200_ACT_SOFTMAX) {
-    softmax_fwd_kernel<<<ceil_div(B, 128), 128, 0, ctx->stream>>>(x, y, dim, B);
+    softmax_fwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(x, y, dim, B);
   } else {
     size_t n4 = (aligned16(x) && aligned16(y)) ? n / 4 : 0;
     act_fwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(kind, x, y,
@@ -164,7 +221,7 @@ int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx,
   size_t n = (size_t)dim * B;
   if (n == 0) return 0;
   if (kind == B200_ACT_SOFTMAX) {
-    softmax_bwd_kernel<<<ceil_div(B, 128), 128, 0, ctx->stream>>>(y, dy, dx, dim, B);
+    softmax_bwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(y, const_cast<float *>(dy), dx, dim, B, nullptr, 0);
   } else {
     size_t n4 = (aligned16(y) && aligned16(dy) && aligned16(dx)) ? n / 4 : 0;
     act_bwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
@@ -181,6 +238,17 @@ int loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy
   if (n == 0) return 0;
   loss_grad_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(kind, y, t, dy, dim,
                                                                              n);
+  B200_LAUNCHED();
+  return 0;
+}
+
+// loss gradient of (y, t) into dy, then the softmax gradient into dx: one launch
+int softmax_loss_bwd(b200_ctx *ctx, int loss_kind, const float *y, const float *t, float *dy, float *dx, int dim,
+                     int B) {
+  B200_REQUIRE(loss_kind >= B200_LOSS_MSE && loss_kind <= B200_LOSS_CROSS_ENTROPY_MULTICLASS,
+               "softmax_loss_bwd: unknown loss %d", loss_kind);
+  if ((size_t)dim * B == 0) return 0;
+  softmax_bwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(y, dy, dx, dim, B, t, loss_kind);
   B200_LAUNCHED();
   return 0;
 }

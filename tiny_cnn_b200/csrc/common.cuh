@@ -242,6 +242,9 @@ int avgpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const f
 int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B);
 int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int B);
 int loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy, int dim, int B);
+// loss gradient (into dy) and the gradient of a softmax layer whose output is y (into dx) in one launch
+int softmax_loss_bwd(b200_ctx *ctx, int loss_kind, const float *y, const float *t, float *dy, float *dx, int dim,
+                     int B);
 int loss_value(b200_ctx *ctx, int kind, const float *y, const float *t, float *loss_sum, int dim,
                int B);
 

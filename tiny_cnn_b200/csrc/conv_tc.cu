@@ -903,74 +903,75 @@ struct DwFinishArgs {
 __global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) {
   constexpr int RL = 8;  // row lanes
   __shared__ float lanes[RL][33];
+  __shared__ float tree[256];
   const int tx = threadIdx.x, ty = threadIdx.y;
-  const int total = a.row_w + (a.db != nullptr ? a.OC : 0);
-  for (int base = blockIdx.x * 32; base < total; base += gridDim.x * 32) {
-    const int e = base + tx;
-    float s0 = 0.f, s1 = 0.f;
-    if (e < a.row_w) {
-      const float *src = a.part + e;
-      int r = ty;
-      for (; r + RL < a.splits; r += 2 * RL) {
-        s0 += src[(size_t)r * a.part_stride];
-        s1 += src[(size_t)(r + RL) * a.part_stride];
-      }
-      if (r < a.splits) s0 += src[(size_t)r * a.part_stride];
-    } else if (e < total) {
-      const float *src = a.bsrc + a.bs_off + (e - a.row_w);
-      int r = ty;
-      for (; r + RL < a.bs_rows; r += 2 * RL) {
-        s0 += src[(size_t)r * a.bs_stride];
-        s1 += src[(size_t)(r + RL) * a.bs_stride];
-      }
-      if (r < a.bs_rows) s0 += src[(size_t)r * a.bs_stride];
-    }
-    lanes[ty][tx] = s0 + s1;
+  const int wblocks = (a.row_w + 31) / 32;
+  if ((int)blockIdx.x >= wblocks) {
+    // bias gradient: one block per output channel; its many short partial rows are spread over
+    // all 256 threads (thread k adds rows k, k+256, ... in order), combined by a fixed tree
+    const int o = blockIdx.x - wblocks, t = ty * 32 + tx;
+    if (a.db == nullptr || o >= a.OC) return;
+    const float *src = a.bsrc + a.bs_off + o;
+    float s = 0.f;
+    for (int r = t; r < a.bs_rows; r += 256) s += src[(size_t)r * a.bs_stride];
+    tree[t] = s;
     __syncthreads();
-    if (ty == 0 && e < total) {
-      float s = lanes[0][tx];
 #pragma unroll
-      for (int k = 1; k < RL; ++k) s += lanes[k][tx];
-      if (e >= a.row_w) {
-        float *d = a.db + (e - a.row_w);
-        *d = a.accumulate ? *d + s : s;
-      } else {
-        int o, inc, ky, kx;
-        if (a.layout == 0) {
-          int r = e;
-          const int ol = r & 31;
-          r >>= 5;
-          const int il = r & 31;
-          r >>= 5;
-          ky = r % a.KH;
-          r /= a.KH;
-          const int j = r % a.KW, unit = r / a.KW;
-          kx = a.KW - 1 - j;
-          o = (unit / a.ic_slabs) * 32 + ol;
-          inc = (unit % a.ic_slabs) * 32 + il;
-        } else {
-          const int k = e / a.OCp, KK = a.KH * a.KW;
-          o = e - k * a.OCp;
-          inc = k / KK;
-          const int t = k - inc * KK;
-          ky = t / a.KW;
-          kx = t - ky * a.KW;
-        }
-        if (o < a.OC && inc < a.C) {
-          if (a.tbl && !a.tbl[inc * a.OC + o]) s = 0.f;
-          float *d = a.dW + (((size_t)o * a.C + inc) * a.KH + ky) * a.KW + kx;
-          *d = a.accumulate ? *d + s : s;
-        }
-      }
+    for (int w = 128; w > 0; w >>= 1) {
+      if (t < w) tree[t] += tree[t + w];
+      __syncthreads();
     }
-    __syncthreads();
+    if (t == 0) a.db[o] = a.accumulate ? a.db[o] + tree[0] : tree[0];
+    return;
+  }
+  const int e = blockIdx.x * 32 + tx;
+  float s0 = 0.f, s1 = 0.f;
+  if (e < a.row_w) {
+    const float *src = a.part + e;
+    int r = ty;
+    for (; r + RL < a.splits; r += 2 * RL) {
+      s0 += src[(size_t)r * a.part_stride];
+      s1 += src[(size_t)(r + RL) * a.part_stride];
+    }
+    if (r < a.splits) s0 += src[(size_t)r * a.part_stride];
+  }
+  lanes[ty][tx] = s0 + s1;
+  __syncthreads();
+  if (ty == 0 && e < a.row_w) {
+    float s = lanes[0][tx];
+#pragma unroll
+    for (int k = 1; k < RL; ++k) s += lanes[k][tx];
+    int o, inc, ky, kx;
+    if (a.layout == 0) {
+      int r = e;
+      const int ol = r & 31;
+      r >>= 5;
+      const int il = r & 31;
+      r >>= 5;
+      ky = r % a.KH;
+      r /= a.KH;
+      const int j = r % a.KW, unit = r / a.KW;
+      kx = a.KW - 1 - j;
+      o = (unit / a.ic_slabs) * 32 + ol;
+      inc = (unit % a.ic_slabs) * 32 + il;
+    } else {
+      const int k = e / a.OCp, KK = a.KH * a.KW;
+      o = e - k * a.OCp;
+      inc = k / KK;
+      const int t = k - inc * KK;
+      ky = t / a.KW;
+      kx = t - ky * a.KW;
+    }
+    if (o < a.OC && inc < a.C) {
+      if (a.tbl && !a.tbl[inc * a.OC + o]) s = 0.f;
+      float *d = a.dW + (((size_t)o * a.C + inc) * a.KH + ky) * a.KW + kx;
+      *d = a.accumulate ? *d + s : s;
+    }
   }
 }
 
 int launch_dw_finish(b200_ctx *ctx, const DwFinishArgs &a) {
-  const int total = a.row_w + (a.db != nullptr ? a.OC : 0);
-  int blocks = ceil_div(total, 32);
-  if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+  const int blocks = (a.row_w + 31) / 32 + (a.db != nullptr ? a.OC : 0);
   dw_finish_kernel<<<blocks, dim3(32, 8), 0, ctx->stream>>>(a);
   B200_LAUNCHED();
   return 0;

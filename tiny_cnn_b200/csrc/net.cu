@@ -160,8 +160,13 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
   int B = net->cur_batch;
   int n = (int)net->layers.size();
   Layer &last = net->layers[n - 1];
-  B200_TRY(loss_grad(ctx, loss_kind, last.out, t, last.grad, (int)last.out_dim, B));
-  for (int i = n - 1; i >= 0; --i) {
+  // a softmax output layer: loss gradient and softmax gradient in one launch
+  const bool tail_fused = net->fuse && last.kind == B200_LAYER_SOFTMAX && n >= 2;
+  if (tail_fused)
+    B200_TRY(softmax_loss_bwd(ctx, loss_kind, last.out, t, last.grad, net->layers[n - 2].grad, (int)last.out_dim, B));
+  else
+    B200_TRY(loss_grad(ctx, loss_kind, last.out, t, last.grad, (int)last.out_dim, B));
+  for (int i = tail_fused ? n - 2 : n - 1; i >= 0; --i) {
     Layer &L = net->layers[i];
     const float *in = i == 0 ? net->cur_x : net->layers[i - 1].out;
     float *din = i == 0 ? (net->input_grad ? net->in_grad : nullptr) : net->layers[i - 1].grad;
