@@ -37,6 +37,7 @@ struct Layer {
   float *tc_xs = nullptr, *tc_dys = nullptr, *tc_bsum = nullptr;
   float *tc_wt_fwd = nullptr, *tc_wt_dx = nullptr, *tc_part = nullptr, *tc_small_part = nullptr;
   float *fc_scratch = nullptr;  // k-slice partial sums of the small GEMMs
+  float *fc_scratch_side = nullptr;  // the same for the dW GEMM when it runs on the side stream
   int fused_act = 0;      // activation of the NEXT layer folded into this epilogue
   bool skipped = false;   // activation layer folded into the previous layer
   bool relu_bwd_fused = false;   // max-pool: also applies the gradient of the relu before it
@@ -166,33 +167,62 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
     B200_TRY(softmax_loss_bwd(ctx, loss_kind, last.out, t, last.grad, net->layers[n - 2].grad, (int)last.out_dim, B));
   else
     B200_TRY(loss_grad(ctx, loss_kind, last.out, t, last.grad, (int)last.out_dim, B));
-  for (int i = tail_fused ? n - 2 : n - 1; i >= 0; --i) {
+  // The gradients with respect to the weights are leaves of the backward pass: nothing in it
+  // reads them.  They go to the side stream, so the chain of dX kernels -- the critical path --
+  // does not wait for them, and kernels that leave SMs idle overlap.  One join at the end.
+  cudaStream_t main_stream = ctx->stream;
+  bool side_used = false;
+  int rc_side = 0;
+  auto fork = [&]() -> int {
+    B200_CUDA(cudaEventRecord(net->ev_fork, main_stream));
+    B200_CUDA(cudaStreamWaitEvent(net->side, net->ev_fork, 0));
+    ctx->stream = net->side;
+    side_used = true;
+    return 0;
+  };
+  for (int i = tail_fused ? n - 2 : n - 1; i >= 0 && rc_side == 0; --i) {
     Layer &L = net->layers[i];
     const float *in = i == 0 ? net->cur_x : net->layers[i - 1].out;
     float *din = i == 0 ? (net->input_grad ? net->in_grad : nullptr) : net->layers[i - 1].grad;
     const float *W = net->params + L.w_off;
     float *dW = net->grads + L.w_off;
     float *db = L.b_len ? net->grads + L.b_off : nullptr;
+    const bool can_fork = net->side != nullptr && din != nullptr;
     switch (L.kind) {
       case B200_LAYER_CONV: {
         bool tiled_bwd = L.tiled && L.g.OW <= 64;
         const bool tc_dx = L.tc.dx && din != nullptr;
         if ((tc_dx || L.tc.dw) && !L.dys_from_pool)
           B200_TRY(conv_tc_tall_dy(ctx, L.g, L.grad, B, L.tc_dys, L.tc.dw && db ? L.tc_bsum : nullptr));
-        // An FFMA dX and the tensor-core dW of a layer with few input channels keep different
-        // units busy: the dW branch goes to the side stream, first, so that its one block per SM
-        // is resident when the many small dX blocks arrive, and both share the SMs.
-        const bool dw_on_side = L.tc.dw_small && din != nullptr && !tc_dx && net->side != nullptr;
-        cudaStream_t main_stream = ctx->stream;
-        if (dw_on_side) {
-          B200_CUDA(cudaEventRecord(net->ev_fork, main_stream));
-          B200_CUDA(cudaStreamWaitEvent(net->side, net->ev_fork, 0));
-          ctx->stream = net->side;
-          int rc = conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0);
-          ctx->stream = main_stream;
-          B200_TRY(rc);
-          B200_CUDA(cudaEventRecord(net->ev_join, net->side));
+        // dW first: its launch precedes the dX launch, so a one-block-per-SM dW kernel is resident
+        // when the small blocks of an FFMA dX arrive and both share the SMs
+        const bool forked = can_fork && (L.tc.dw || L.tc.dw_small);
+        if (forked) B200_TRY(fork());
+        if (L.tc.dw) {
+          if (!L.tc.fwd && !L.xs_from_pool) rc_side = conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs);
+          int splits = 0;
+          if (!rc_side) rc_side = conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits);
+          if (!rc_side)
+            rc_side = conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db);
+        } else if (L.tc.dw_small) {
+          rc_side = conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0);
+        } else if (tiled_bwd) {
+          int splits = 0;
+          rc_side = conv_tiled_dw_partials(ctx, L.g, in, L.grad, B, L.dw_part, &splits);
+          size_t row = L.w_len + L.g.OC;
+          if (!rc_side && db && L.b_off == L.w_off + L.w_len) {
+            // [W | b] are neighbours in the bucket as in a partial row: one merge
+            rc_side = merge_rows(ctx, L.dw_part, splits, row, dW, row, 0, &L.g);
+          } else if (!rc_side) {
+            rc_side = merge_rows(ctx, L.dw_part, splits, row, dW, L.w_len, 0, &L.g);
+            if (!rc_side && db)
+              rc_side = merge_rows(ctx, L.dw_part + L.w_len, splits, row, db, L.b_len, 0, nullptr);
+          }
+        } else {
+          rc_side = conv_general_dw(ctx, L.g, in, L.grad, dW, db, 0, B);
         }
+        ctx->stream = main_stream;
+        if (rc_side) break;
         if (din) {
           if (tc_dx)
             B200_TRY(conv_tc_dx(ctx, L.g, L.tc_dys, W, din, B, L.tc_wt_dx, L.tc.fwd ? 0 : 1));
@@ -201,36 +231,18 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
           else
             B200_TRY(conv_general_dx(ctx, L.g, W, L.grad, din, B));
         }
-        if (dw_on_side) {
-          B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_join, 0));
-          break;
-        }
-        if (L.tc.dw) {
-          if (!L.tc.fwd && !L.xs_from_pool) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
-          int splits = 0;
-          B200_TRY(conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits));
-          B200_TRY(conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db));
-        } else if (L.tc.dw_small) {
-          B200_TRY(conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0));
-        } else if (tiled_bwd) {
-          int splits = 0;
-          B200_TRY(conv_tiled_dw_partials(ctx, L.g, in, L.grad, B, L.dw_part, &splits));
-          size_t row = L.w_len + L.g.OC;
-          if (db && L.b_off == L.w_off + L.w_len) {
-            // [W | b] are neighbours in the bucket as in a partial row: one merge
-            B200_TRY(merge_rows(ctx, L.dw_part, splits, row, dW, row, 0, &L.g));
-          } else {
-            B200_TRY(merge_rows(ctx, L.dw_part, splits, row, dW, L.w_len, 0, &L.g));
-            if (db)
-              B200_TRY(merge_rows(ctx, L.dw_part + L.w_len, splits, row, db, L.b_len, 0, nullptr));
-          }
-        } else {
-          B200_TRY(conv_general_dw(ctx, L.g, in, L.grad, dW, db, 0, B));
-        }
         break;
       }
       case B200_LAYER_FC:
-        B200_TRY(fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, din, dW, db, 0, B, L.fc_scratch));
+        if (can_fork && L.fc_scratch_side) {
+          B200_TRY(fork());
+          rc_side = fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, nullptr, dW, db, 0, B, L.fc_scratch_side);
+          ctx->stream = main_stream;
+          if (rc_side) break;
+          B200_TRY(fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, din, nullptr, nullptr, 0, B, L.fc_scratch));
+        } else {
+          B200_TRY(fc_bwd(ctx, L.fc_in, L.fc_out, in, W, L.grad, din, dW, db, 0, B, L.fc_scratch));
+        }
         break;
       case B200_LAYER_MAXPOOL:
         if (L.grad_to_conv >= 0) {
@@ -262,7 +274,12 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
       default: B200_REQUIRE(false, "net_backward: unknown layer kind %d", L.kind);
     }
   }
-  return 0;
+  ctx->stream = main_stream;
+  if (side_used) {  // the optimizer (or the caller's all-reduce) follows on the main stream
+    B200_CUDA(cudaEventRecord(net->ev_join, net->side));
+    B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_join, 0));
+  }
+  return rc_side;
 }
 
 // Adam powers for a fresh optimizer object: tensor j of the first step sees
@@ -476,9 +493,13 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
     B200_TRY(net_alloc((void **)&L.grad, L.out_dim * max_batch * f));
     if (L.kind == B200_LAYER_MAXPOOL)
       B200_TRY(net_alloc((void **)&L.argmax, L.out_dim * max_batch * sizeof(int32_t)));
-    if (L.kind == B200_LAYER_FC)
+    if (L.kind == B200_LAYER_FC) {
       B200_TRY(net_alloc((void **)&L.fc_scratch,
                          fc_scratch_floats(ctx, L.fc_in, L.fc_out, max_batch) * f));
+      if (net->side)
+        B200_TRY(net_alloc((void **)&L.fc_scratch_side,
+                           fc_scratch_floats(ctx, L.fc_in, L.fc_out, max_batch) * f));
+    }
     if (L.kind == B200_LAYER_CONV && L.tiled) {
       B200_TRY(net_alloc((void **)&L.wt_fwd, conv_tiled_fwd_scratch(L.g) * f));
       B200_TRY(net_alloc((void **)&L.wt_dx, conv_tiled_dx_scratch(L.g) * f));
@@ -517,6 +538,7 @@ int b200_net_destroy(b200_net *net) {
     cudaFree(L.wt_fwd);
     cudaFree(L.wt_dx);
     cudaFree(L.dw_part);
+    cudaFree(L.fc_scratch_side);
     cudaFree(L.tc_xs);
     cudaFree(L.tc_dys);
     cudaFree(L.tc_bsum);
