@@ -44,6 +44,7 @@ struct Layer {
   bool bwd_done_by_next = false; // relu: its gradient is produced by the pooling layer after it
   // 2x2 max-pool next to a tensor-core convolution: the pooling kernels also write the tall split
   // copies that convolution reads (its input in the forward pass, its dY in the backward pass)
+  cudaEvent_t ev_prep = nullptr;  // tensor-core convolution: its filter matrices are ready (side stream)
   int feeds_conv = -1;     // max-pool: convolution layer whose input copy it writes
   int grad_to_conv = -1;   // max-pool: convolution layer whose dY copy it writes
   bool xs_from_pool = false, dys_from_pool = false;  // convolution: copies come from the pooling layers
@@ -107,6 +108,26 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
   b200_ctx *ctx = net->ctx;
   const float *in = x;
   size_t n = net->layers.size();
+  // The filter matrices of the tensor-core layers depend on the weights only: they are made on the
+  // side stream while the first layers compute; each layer waits for its own.
+  bool prep_on_side = false;
+  if (net->side) {
+    cudaStream_t main_stream = ctx->stream;
+    for (size_t i = 0; i < n; ++i) {
+      Layer &L = net->layers[i];
+      if (L.kind != B200_LAYER_CONV || !L.tc.fwd || !L.ev_prep) continue;
+      if (!prep_on_side) {
+        B200_CUDA(cudaEventRecord(net->ev_fork, main_stream));
+        B200_CUDA(cudaStreamWaitEvent(net->side, net->ev_fork, 0));
+        prep_on_side = true;
+      }
+      ctx->stream = net->side;
+      int rc = conv_tc_prep(ctx, L.g, net->params + L.w_off, L.tc_wt_fwd, L.tc.dx ? L.tc_wt_dx : nullptr);
+      ctx->stream = main_stream;
+      B200_TRY(rc);
+      B200_CUDA(cudaEventRecord(L.ev_prep, net->side));
+    }
+  }
   for (size_t i = 0; i < n; ++i) {
     Layer &L = net->layers[i];
     if (L.skipped) {
@@ -121,7 +142,10 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
         if (L.tc.fwd) {
           if (!L.xs_from_pool) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
           // the dX pass of this step reads the same weights: both filter matrices in one launch
-          B200_TRY(conv_tc_prep(ctx, L.g, W, L.tc_wt_fwd, L.tc.dx ? L.tc_wt_dx : nullptr));
+          if (prep_on_side && L.ev_prep)
+            B200_CUDA(cudaStreamWaitEvent(ctx->stream, L.ev_prep, 0));
+          else
+            B200_TRY(conv_tc_prep(ctx, L.g, W, L.tc_wt_fwd, L.tc.dx ? L.tc_wt_dx : nullptr));
           B200_TRY(conv_tc_fwd(ctx, L.g, L.tc_xs, W, b, dst, B, L.fused_act, L.tc_wt_fwd, 0));
         } else if (L.tiled)
           B200_TRY(conv_tiled_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act, L.wt_fwd));
@@ -508,6 +532,8 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
     }
     if (L.kind == B200_LAYER_CONV && L.tc.dw_small)
       B200_TRY(net_alloc((void **)&L.tc_small_part, conv_dw_small_floats(ctx, L.g, max_batch) * f));
+    if (L.kind == B200_LAYER_CONV && L.tc.fwd && net->side)
+      B200_CUDA(cudaEventCreateWithFlags(&L.ev_prep, cudaEventDisableTiming));
     if (L.kind == B200_LAYER_CONV && (L.tc.fwd || L.tc.dx || L.tc.dw)) {
       if (L.tc.fwd || L.tc.dw)
         B200_TRY(net_alloc((void **)&L.tc_xs, conv_tc_tall_floats(L.g, max_batch, 0) * f));
@@ -537,6 +563,7 @@ int b200_net_destroy(b200_net *net) {
     cudaFree(L.argmax);
     cudaFree(L.wt_fwd);
     cudaFree(L.wt_dx);
+    if (L.ev_prep) cudaEventDestroy(L.ev_prep);
     cudaFree(L.dw_part);
     cudaFree(L.fc_scratch_side);
     cudaFree(L.tc_xs);
