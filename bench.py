@@ -393,9 +393,10 @@ def run_b200(args, rank, world, local_rank):
                                      "(hi/lo split, fp32 accumulation), conv1 and the rest fp32 FFMA",
                        "l2": "8 resident input batches rotate through the step; activations + gradients "
                              "touched per step are about 130 MB, larger than the 126 MB L2",
-                       "step": "CUDA graph of forward+backward+update" if world == 1 else
-                               "CUDA graph of forward+backward, NCCL sum all-reduce of the gradient "
-                               "bucket, update"},
+                       "step": ("CUDA graph of forward+backward+update" if world == 1 else
+                                "CUDA graph of forward+backward, NCCL sum all-reduce of the gradient bucket, update")
+                               + "; inside the graph the weight-gradient kernels and the filter matrices run on a "
+                                 "side branch beside the forward / dX chain"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "api": "Sequential.fit -> b200_net_fit_host: uploads of the next mini-batch overlap the "

@@ -1,6 +1,8 @@
-"""Single-layer timing of the convolution kernels through the C ABI.
+"""Single-layer timing of the kernels through the C ABI.
 
     python -m tiny_cnn_b200.kernel_bench --layer conv2 --batch 256 --reps 5 --passes fwd,bwd
+    python -m tiny_cnn_b200.kernel_bench --layer fc4096 --batch 1024        (MLP configuration layers)
+    python -m tiny_cnn_b200.kernel_bench --layer qconv --batch 128          (quantized configuration)
 
 Prints one JSON line with the CUDA-event time per pass and the achieved
 TFLOP/s (2*B*oh*ow*oc*ic*kh*kw flop per pass: forward, dX and dW each).
@@ -25,18 +27,73 @@ LAYERS = {
 }
 
 
+# name -> (in, out) of the fully-connected layers of the MLP configuration
+FC_LAYERS = {"fc784": (784, 4096), "fc4096": (4096, 4096), "fc10": (4096, 10)}
+
+
+def timed(fn, reps, warmup):
+    for _ in range(warmup):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def other_layers(args, ctx):
+    """Fully-connected layers of the MLP configuration and the quantized forward layers."""
+    B = args.batch
+    g = torch.Generator(device="cuda").manual_seed(2)
+    out = {"layer": args.layer, "batch": B}
+    if args.layer in FC_LAYERS:
+        I, O = FC_LAYERS[args.layer]
+        x = torch.rand(B, I, device="cuda", generator=g)
+        W = (torch.rand(I * O, device="cuda", generator=g) - 0.5) * 0.05
+        b = torch.zeros(O, device="cuda")
+        dy = torch.randn(B, O, device="cuda", generator=g)
+        y = torch.empty(B, O, device="cuda")
+        dW, db = torch.empty_like(W), torch.empty_like(b)
+        flop = 2.0 * B * I * O
+        ms = timed(lambda: ops.fully_connected_op(ctx, I, O, x, W, b, out=y), args.reps, args.warmup)
+        out["fwd"] = {"ms": round(ms, 4), "tflops": round(flop / ms / 1e9, 3)}
+        ms = timed(lambda: ops.fully_connected_grad_op(ctx, I, O, x, W, dy, dW=dW, db=db), args.reps, args.warmup)
+        out["bwd"] = {"ms": round(ms, 4), "tflops": round(2 * flop / ms / 1e9, 3)}
+    elif args.layer == "qconv":  # 32 x 28 x 28 -> 64 maps, 5x5, valid (stride from --stride)
+        d = ops.conv_params(28, 28, 32, 5, 5, 64, False, True, args.stride, args.stride)
+        x = torch.rand(B, 32 * 28 * 28, device="cuda", generator=g) * 2 - 1
+        W = torch.rand(64 * 32 * 25, device="cuda", generator=g) - 0.5
+        b = torch.zeros(64, device="cuda")
+        ms = timed(lambda: ops.quantized_conv2d(ctx, d, x, W, b), args.reps, args.warmup)
+        macs = B * 64 * d.out_w * d.out_h * 32 * 25
+        out["fwd"] = {"ms": round(ms, 4), "int_tops": round(2.0 * macs / ms / 1e9, 3)}
+    else:  # qfc 9216 -> 256
+        x = torch.rand(B, 9216, device="cuda", generator=g) * 2 - 1
+        W = torch.rand(9216 * 256, device="cuda", generator=g) - 0.5
+        b = torch.zeros(256, device="cuda")
+        ms = timed(lambda: ops.quantized_fully_connected(ctx, 9216, 256, x, W, b), args.reps, args.warmup)
+        out["fwd"] = {"ms": round(ms, 4), "int_tops": round(2.0 * B * 9216 * 256 / ms / 1e9, 3)}
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--layer", default="conv2", choices=sorted(LAYERS))
+    ap.add_argument("--layer", default="conv2", choices=sorted(LAYERS) + sorted(FC_LAYERS) + ["qconv", "qfc"])
+    ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--passes", default="fwd,bwd")
     ap.add_argument("--algo", type=int, default=0)
     args = ap.parse_args()
+    ctx = ops.Context(0)
+    if args.layer not in LAYERS:
+        return other_layers(args, ctx)
     w, c, oc, k = LAYERS[args.layer]
     B = args.batch
-    ctx = ops.Context(0)
     d = ops.conv_params(w, w, c, k, k, oc, True, True, algo=args.algo)
     g = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randn(B, c * w * w, device="cuda", generator=g)
