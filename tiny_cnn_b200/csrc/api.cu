@@ -29,8 +29,9 @@ int conv_fwd_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const
   if (batch == 0) return 0;  // empty batch: nothing to read or write
   B200_REQUIRE(in && W && out && (bias || !g.has_bias), "conv2d_fwd: NULL buffer");
   ConvTcUse tc = conv_tc_use(ctx, g, d->algo);
-  B200_REQUIRE(d->algo != 3 || tc.fwd,
+  B200_REQUIRE(d->algo != 3 || tc.fwd || tc.fwd_small,
                "conv2d_fwd: tensor-core kernels need stride 1, dilation 1, windows <= 8x8, <= 256 channels");
+  if (tc.fwd_small) return conv_fwd_small(ctx, g, in, W, bias, out, batch, B200_ACT_NONE);
   if (tc.fwd) {
     size_t n_x = align_up(conv_tc_tall_floats(g, batch, 0), 64);
     void *scratch = nullptr;
@@ -130,7 +131,7 @@ int conv_time_pass_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
   B200_REQUIRE(in && W && (dout || pass == 0), "conv2d_time_pass: NULL buffer");
   ConvTcUse tc = conv_tc_use(ctx, g, d->algo);
   const bool tiled = use_tiled(d, g) && (pass == 0 || g.OW <= 64);
-  const bool use_tc = pass == 0 ? tc.fwd : pass == 1 ? tc.dx : (tc.dw || tc.dw_small);
+  const bool use_tc = pass == 0 ? (tc.fwd || tc.fwd_small) : pass == 1 ? tc.dx : (tc.dw || tc.dw_small);
   B200_REQUIRE(use_tc || tiled, "conv2d_time_pass: only the tensor-core and the tiled kernels are timed");
   const size_t in_len = (size_t)batch * g.C * g.HI * g.WI, out_len = (size_t)batch * g.OC * g.OH * g.OW;
   size_t n_res = align_up(in_len > out_len ? in_len : out_len, 64);
@@ -152,6 +153,7 @@ int conv_time_pass_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
   int splits = 0, rc = 0;
   auto run = [&](int prep) -> int {
     if (use_tc) {
+      if (pass == 0 && tc.fwd_small) return conv_fwd_small(ctx, g, in, W, nullptr, res, batch, B200_ACT_NONE);
       if (pass == 0) return conv_tc_fwd(ctx, g, xs, W, nullptr, res, batch, B200_ACT_NONE, wt, prep);
       if (pass == 1) return conv_tc_dx(ctx, g, dys, W, res, batch, wt, prep);
       if (tc.dw_small) {  // includes its finishing launch
@@ -164,7 +166,7 @@ int conv_time_pass_impl(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
     if (pass == 1) return conv_tiled_dx(ctx, g, W, dout, res, batch, ts);
     return conv_tiled_dw_partials(ctx, g, in, dout, batch, ts, &splits);
   };
-  const bool slab = use_tc && !(pass == 2 && tc.dw_small);
+  const bool slab = use_tc && !(pass == 2 && tc.dw_small) && !(pass == 0 && tc.fwd_small);
   if (slab && pass != 1) rc = conv_tc_tall_x(ctx, g, in, batch, xs);
   if (!rc && slab && pass != 0) rc = conv_tc_tall_dy(ctx, g, dout, batch, dys, nullptr);
   if (!rc) rc = run(1);  // warm-up, filter matrices, tile choice

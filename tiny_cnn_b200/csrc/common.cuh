@@ -163,8 +163,13 @@ bool conv_tc_ok(const b200_ctx *ctx, const ConvGeom &g);
 // none, 0 = by the context's conv_tensor_cores option
 struct ConvTcUse {
   bool fwd, dx, dw;
-  bool dw_small;  // dW through the im2col form for layers with few input channels (conv_dw_small)
+  bool dw_small;   // dW through the im2col form for layers with few input channels (conv_dw_small)
+  bool fwd_small;  // forward through the im2col form for the same layers (conv_fwd_small)
 };
+// forward of layers with few input channels (in_c*KH*KW <= 96, <= 64 out channels) from the CHW input
+bool conv_fwd_small_ok(const b200_ctx *ctx, const ConvGeom &g);
+int conv_fwd_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *W, const float *bias, float *out,
+                   int B, int act);
 ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo);
 size_t conv_tc_tall_floats(const ConvGeom &g, int B, int which);  // 0: input, 1: dY
 size_t conv_tc_filter_floats(const b200_ctx *ctx, const ConvGeom &g, int for_dx);

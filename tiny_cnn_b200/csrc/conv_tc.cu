@@ -993,7 +993,7 @@ bool conv_tc_ok(const b200_ctx *ctx, const ConvGeom &g) {
 }
 
 ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo) {
-  ConvTcUse u = {false, false, false, false};
+  ConvTcUse u = {false, false, false, false, false};
   if (algo == 1 || algo == 2) return u;
   if (algo != 3 && ctx->conv_tensor_cores == 0) return u;
   if (conv_tc_ok(ctx, g)) {
@@ -1019,6 +1019,15 @@ ConvTcUse conv_tc_use(const b200_ctx *ctx, const ConvGeom &g, int algo) {
     if (want) {
       u.dw = false;
       u.dw_small = true;
+    }
+  }
+  // and the im2col form of the forward pass (bit 4 of B200_CONV_TC)
+  if (conv_fwd_small_ok(ctx, g) && (!u.fwd || g.C < 16)) {
+    bool want = true;
+    if (const char *e = getenv("B200_CONV_TC")) want = algo == 3 || (atoi(e) & 16) != 0;
+    if (want) {
+      u.fwd = false;
+      u.fwd_small = true;
     }
   }
   return u;

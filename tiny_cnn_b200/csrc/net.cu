@@ -147,7 +147,9 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
           else
             B200_TRY(conv_tc_prep(ctx, L.g, W, L.tc_wt_fwd, L.tc.dx ? L.tc_wt_dx : nullptr));
           B200_TRY(conv_tc_fwd(ctx, L.g, L.tc_xs, W, b, dst, B, L.fused_act, L.tc_wt_fwd, 0));
-        } else if (L.tiled)
+        } else if (L.tc.fwd_small)
+          B200_TRY(conv_fwd_small(ctx, L.g, in, W, b, dst, B, L.fused_act));
+        else if (L.tiled)
           B200_TRY(conv_tiled_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act, L.wt_fwd));
         else
           B200_TRY(conv_general_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act));

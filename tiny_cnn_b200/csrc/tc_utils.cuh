@@ -126,11 +126,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
                : "memory");
 }
 
-// round to the nearest TF32 (10 explicit mantissa bits); lo = x - hi is exact in fp32
+// round to the nearest TF32 (10 explicit mantissa bits, ties away from zero); lo = x - hi is exact
+// in fp32.  Integer form of cvt.rna.tf32.f32 (same bits for every finite input): that instruction
+// issues on the conversion pipe, a quarter-rate unit that a kernel converting an im2col tile in
+// its inner loop saturates, while an add and a mask run at full rate.
 __device__ __forceinline__ void split_tf32_rn(float x, float &hi, float &lo) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(u) : "f"(x));
-  hi = __uint_as_float(u);
+  hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
   lo = x - hi;
 }
 
@@ -159,6 +160,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// the same load without the wait: issue several, then tmem_ld_wait() once before the values are used
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+      "=r"(r[15])
+    : "r"(taddr)
+    : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
