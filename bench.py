@@ -390,7 +390,7 @@ def run_b200(args, rank, world, local_rank):
             "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "global_batch": global_batch,
                        "parallelism": f"dp{world}",
                        "arithmetic": "fp32 results; conv2/conv3 passes on tcgen05 tensor cores as 3xTF32 "
-                                     "(hi/lo split, fp32 accumulation), conv1 and the rest fp32 FFMA",
+                                     "(hi/lo split, fp32 accumulation) -- also conv1 forward and dW; conv1 dX and the rest fp32 FFMA",
                        "l2": "8 resident input batches rotate through the step; activations + gradients "
                              "touched per step are about 130 MB, larger than the 126 MB L2",
                        "step": ("CUDA graph of forward+backward+update" if world == 1 else
