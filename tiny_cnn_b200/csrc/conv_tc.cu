@@ -86,6 +86,19 @@ struct TallSrc {
   int32_t *out_am;
 };
 
+// one 2x2 window as maxpool2x2_fwd_kernel takes it: strict '>' in window order from -FLT_MAX, the
+// index of the winner in the sample's CHW numbering (0 when nothing exceeds -FLT_MAX)
+__device__ __forceinline__ void pool_window(float a, float b, float c, float d, int base, int in_w, float &best,
+                                            int &idx) {
+  best = -FLT_MAX;
+  int code = -1;
+  if (a > best) { best = a; code = 0; }
+  if (b > best) { best = b; code = 1; }
+  if (c > best) { best = c; code = 2; }
+  if (d > best) { best = d; code = 3; }
+  idx = code < 0 ? 0 : base + (code & 1) + (code >> 1) * in_w;
+}
+
 // One block converts `rb` tall rows of one image: src[b][c][y][x] -> hi/lo[t][x][c],
 // zero for padded channels and for the rows between images.  With `bsum` the block also
 // writes the per-channel sum of what it read (bias gradient partials, fixed order).
@@ -112,78 +125,105 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
       for (int p = lane; p < npx; p += 32) trow[p] = p < valid_px ? ch[p] : 0.f;
     }
   } else if (src.mode == 1) {
-    // two pooled pixels per lane: 16-byte loads of the two input rows, 8-byte stores
-    const int in_w = 2 * W, in_h = 2 * H, W2 = W >> 1;
-    for (int c = warp; c < C; c += 8) {
-      float *trow = tile + c * pitch;
-      const size_t cplane = ((size_t)b * C + c) * plane;
-      const float *cin = src.a + ((size_t)b * C + c) * in_h * in_w;
-#pragma unroll 2
-      for (int q = lane; q < (npx >> 1); q += 32) {
-        const int ry = q / W2, x = (q - ry * W2) * 2, y = r0 + ry, p = ry * W + x;
-        float best0 = 0.f, best1 = 0.f;
-        if (p < valid_px) {
-          const float *ip = cin + (size_t)(2 * y) * in_w + 2 * x;
-          const float4 u = *reinterpret_cast<const float4 *>(ip);
-          const float4 v = *reinterpret_cast<const float4 *>(ip + in_w);
-          const int base = (in_h * c + 2 * y) * in_w + 2 * x;
-          int i0 = 0, i1 = 0;
-          best0 = best1 = -FLT_MAX;
-          if (u.x > best0) { best0 = u.x; i0 = base; }
-          if (u.y > best0) { best0 = u.y; i0 = base + 1; }
-          if (v.x > best0) { best0 = v.x; i0 = base + in_w; }
-          if (v.y > best0) { best0 = v.y; i0 = base + in_w + 1; }
-          if (u.z > best1) { best1 = u.z; i1 = base + 2; }
-          if (u.w > best1) { best1 = u.w; i1 = base + 3; }
-          if (v.z > best1) { best1 = v.z; i1 = base + in_w + 2; }
-          if (v.w > best1) { best1 = v.w; i1 = base + in_w + 3; }
-          const size_t o = cplane + (size_t)y * W + x;
-          *reinterpret_cast<float2 *>(src.out_chw + o) = make_float2(best0, best1);
-          *reinterpret_cast<int2 *>(src.out_am + o) = make_int2(i0, i1);
+    // two pooled pixels per lane: 16-byte loads of the two input rows, 8-byte stores.  Two channels
+    // per pass, so that four loads are in flight per lane; the pair's place in the chunk does not
+    // depend on the channel.
+    const int in_w = 2 * W, in_h = 2 * H, W2 = W >> 1, nq = npx >> 1;
+    const int w2s = (W2 & (W2 - 1)) == 0 ? 31 - __clz(W2) : -1;
+    const size_t iplane = (size_t)in_h * in_w;
+    for (int q = lane; q < nq; q += 32) {
+      const int ry = w2s >= 0 ? q >> w2s : q / W2, x = (q - ry * W2) * 2, y = r0 + ry, pp = ry * W + x;
+      const bool live = pp < valid_px;
+      const size_t ioff = (size_t)(2 * y) * in_w + 2 * x, ooff = (size_t)y * W + x;
+      for (int c = warp; c < C; c += 16) {
+        const int c2 = c + 8;
+        const bool two = c2 < C;
+        float b00 = 0.f, b01 = 0.f, b10 = 0.f, b11 = 0.f;
+        if (live) {
+          const float *ip0 = src.a + ((size_t)b * C + c) * iplane + ioff;
+          const float *ip1 = src.a + ((size_t)b * C + (two ? c2 : c)) * iplane + ioff;
+          const float4 u0 = *reinterpret_cast<const float4 *>(ip0);
+          const float4 v0 = *reinterpret_cast<const float4 *>(ip0 + in_w);
+          const float4 u1 = *reinterpret_cast<const float4 *>(ip1);
+          const float4 v1 = *reinterpret_cast<const float4 *>(ip1 + in_w);
+          int i00, i01, i10, i11;
+          pool_window(u0.x, u0.y, v0.x, v0.y, (in_h * c + 2 * y) * in_w + 2 * x, in_w, b00, i00);
+          pool_window(u0.z, u0.w, v0.z, v0.w, (in_h * c + 2 * y) * in_w + 2 * x + 2, in_w, b01, i01);
+          const size_t o0 = ((size_t)b * C + c) * plane + ooff;
+          *reinterpret_cast<float2 *>(src.out_chw + o0) = make_float2(b00, b01);
+          *reinterpret_cast<int2 *>(src.out_am + o0) = make_int2(i00, i01);
+          if (two) {
+            pool_window(u1.x, u1.y, v1.x, v1.y, (in_h * c2 + 2 * y) * in_w + 2 * x, in_w, b10, i10);
+            pool_window(u1.z, u1.w, v1.z, v1.w, (in_h * c2 + 2 * y) * in_w + 2 * x + 2, in_w, b11, i11);
+            const size_t o1 = ((size_t)b * C + c2) * plane + ooff;
+            *reinterpret_cast<float2 *>(src.out_chw + o1) = make_float2(b10, b11);
+            *reinterpret_cast<int2 *>(src.out_am + o1) = make_int2(i10, i11);
+          }
         }
-        trow[p] = best0;
-        trow[p + 1] = best1;
+        tile[c * pitch + pp] = b00;
+        tile[c * pitch + pp + 1] = b01;
+        if (two) {
+          tile[c2 * pitch + pp] = b10;
+          tile[c2 * pitch + pp + 1] = b11;
+        }
       }
     }
   } else {
-    // one pooled pixel per lane: its gradient goes to the one input position argmax names
-    const int pw = W >> 1, ph = H >> 1;
-    for (int c = warp; c < C; c += 8) {
-      float *trow = tile + c * pitch;
-      const size_t cplane = ((size_t)b * C + c) * plane;
-      const size_t pplane = ((size_t)b * C + c) * ph * pw;
-#pragma unroll 2
-      for (int q = lane; q < ((nr + 1) >> 1) * pw; q += 32) {
-        const int pry = q / pw, prx = q - pry * pw, ry = 2 * pry, x = 2 * prx, y = r0 + ry;
-        float v00 = 0.f, v01 = 0.f, v10 = 0.f, v11 = 0.f;
-        if (y < H) {
-          const size_t po = pplane + (size_t)(y >> 1) * pw + prx;
-          const float gval = src.a[po];
-          const int am = src.am[po] - ((H * c + y) * W + x);  // offset inside the window: 0, 1, W, W+1
-          v00 = am == 0 ? gval : 0.f;
-          v01 = am == 1 ? gval : 0.f;
-          v10 = am == W ? gval : 0.f;
-          v11 = am == W + 1 ? gval : 0.f;
-          const size_t o = cplane + (size_t)y * W + x;
-          if (src.relu_y != nullptr) {
-            const float2 r0v = *reinterpret_cast<const float2 *>(src.relu_y + o);
-            const float2 r1v = *reinterpret_cast<const float2 *>(src.relu_y + o + W);
-            if (!(r0v.x > 0.f)) v00 = 0.f;
-            if (!(r0v.y > 0.f)) v01 = 0.f;
-            if (!(r1v.x > 0.f)) v10 = 0.f;
-            if (!(r1v.y > 0.f)) v11 = 0.f;
+    // one pooled pixel per lane: its gradient goes to the one input position argmax names.  The
+    // pixel's place in the chunk does not depend on the channel; two channels per pass.
+    const int pw = W >> 1, ph = H >> 1, nq = ((nr + 1) >> 1) * pw;
+    const int pws = (pw & (pw - 1)) == 0 ? 31 - __clz(pw) : -1;
+    for (int q = lane; q < nq; q += 32) {
+      const int pry = pws >= 0 ? q >> pws : q / pw, prx = q - pry * pw, ry = 2 * pry, x = 2 * prx, y = r0 + ry;
+      const bool live = y < H, second = ry + 1 < nr;
+      const size_t poff = (size_t)(y >> 1) * pw + prx, ooff = (size_t)y * W + x;
+      const int pp = ry * W + x;
+      for (int c = warp; c < C; c += 16) {
+        const int c2 = c + 8;
+        const bool two = c2 < C;
+        float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        if (live) {
+          const int cc[2] = {c, two ? c2 : c};
+          float gval[2];
+          int am[2];
+          float2 ra[2], rb2[2];
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const size_t po = ((size_t)b * C + cc[k]) * ph * pw + poff;
+            gval[k] = src.a[po];
+            am[k] = src.am[po] - ((H * cc[k] + y) * W + x);  // offset inside the window: 0, 1, W, W+1
+            if (src.relu_y != nullptr) {
+              const size_t o = ((size_t)b * C + cc[k]) * plane + ooff;
+              ra[k] = *reinterpret_cast<const float2 *>(src.relu_y + o);
+              rb2[k] = *reinterpret_cast<const float2 *>(src.relu_y + o + W);
+            } else {
+              ra[k] = rb2[k] = make_float2(1.f, 1.f);
+            }
           }
-          if (src.out_chw != nullptr) {
-            *reinterpret_cast<float2 *>(src.out_chw + o) = make_float2(v00, v01);
-            *reinterpret_cast<float2 *>(src.out_chw + o + W) = make_float2(v10, v11);
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            if (k == 1 && !two) break;
+            v[k][0] = (am[k] == 0 && ra[k].x > 0.f) ? gval[k] : 0.f;
+            v[k][1] = (am[k] == 1 && ra[k].y > 0.f) ? gval[k] : 0.f;
+            v[k][2] = (am[k] == W && rb2[k].x > 0.f) ? gval[k] : 0.f;
+            v[k][3] = (am[k] == W + 1 && rb2[k].y > 0.f) ? gval[k] : 0.f;
+            if (src.out_chw != nullptr) {
+              const size_t o = ((size_t)b * C + cc[k]) * plane + ooff;
+              *reinterpret_cast<float2 *>(src.out_chw + o) = make_float2(v[k][0], v[k][1]);
+              *reinterpret_cast<float2 *>(src.out_chw + o + W) = make_float2(v[k][2], v[k][3]);
+            }
           }
         }
-        const int p = ry * W + x;
-        trow[p] = v00;
-        trow[p + 1] = v01;
-        if (ry + 1 < nr) {
-          trow[p + W] = v10;
-          trow[p + W + 1] = v11;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (k == 1 && !two) break;
+          float *trow = tile + (k ? c2 : c) * pitch;
+          trow[pp] = v[k][0];
+          trow[pp + 1] = v[k][1];
+          if (second) {
+            trow[pp + W] = v[k][2];
+            trow[pp + W + 1] = v[k][3];
+          }
         }
       }
     }
@@ -192,17 +232,35 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
   const size_t base = ((size_t)b * period + r0) * W * Cp;
   const int Cq = Cp >> 2, total2 = npx * Cq;
   float4 *hi4 = reinterpret_cast<float4 *>(hi + base), *lo4 = reinterpret_cast<float4 *>(lo + base);
+  if (256 % Cq == 0) {
+    // the channel quad of a thread is the same for every pixel it stores: no division per item
+    const int c = (threadIdx.x % Cq) * 4, pstep = 256 / Cq;
+    const float *t0 = tile + c * pitch;
+    const bool k0 = c < C, k1 = c + 1 < C, k2 = c + 2 < C, k3 = c + 3 < C;
+    int i = threadIdx.x;
 #pragma unroll 4
-  for (int i = threadIdx.x; i < total2; i += 256) {
-    int p = i / Cq, c = (i - p * Cq) * 4;
-    float h[4], l[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      h[j] = l[j] = 0.f;
-      if (c + j < C) split_tf32_rn(tile[(c + j) * pitch + p], h[j], l[j]);
+    for (int p = threadIdx.x / Cq; p < npx; p += pstep, i += 256) {
+      float h[4], l[4];
+      split_tf32_rn(k0 ? t0[p] : 0.f, h[0], l[0]);
+      split_tf32_rn(k1 ? t0[pitch + p] : 0.f, h[1], l[1]);
+      split_tf32_rn(k2 ? t0[2 * pitch + p] : 0.f, h[2], l[2]);
+      split_tf32_rn(k3 ? t0[3 * pitch + p] : 0.f, h[3], l[3]);
+      hi4[i] = make_float4(h[0], h[1], h[2], h[3]);
+      lo4[i] = make_float4(l[0], l[1], l[2], l[3]);
     }
-    hi4[i] = make_float4(h[0], h[1], h[2], h[3]);
-    lo4[i] = make_float4(l[0], l[1], l[2], l[3]);
+  } else {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < total2; i += 256) {
+      int p = i / Cq, c = (i - p * Cq) * 4;
+      float h[4], l[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        h[j] = l[j] = 0.f;
+        if (c + j < C) split_tf32_rn(tile[(c + j) * pitch + p], h[j], l[j]);
+      }
+      hi4[i] = make_float4(h[0], h[1], h[2], h[3]);
+      lo4[i] = make_float4(l[0], l[1], l[2], l[3]);
+    }
   }
   if (bsum != nullptr) {
     for (int c = warp; c < C; c += 8) {
@@ -1223,7 +1281,7 @@ namespace {
 constexpr int TCS_MAX_STAGES = 3;     // three are enough to hide the loads and leave shared memory for a co-resident kernel
 constexpr int TCS_PX = 32;          // pixels per step (one 128-byte operand row)
 constexpr int TCS_GROUPS = 2;       // converter groups; group g converts the steps i with i % 2 == g
-constexpr int TCS_GROUP_WARPS = 4;
+constexpr int TCS_GROUP_WARPS = 8;
 static_assert(TCS_GROUPS <= 2, "a group's first step must be the first use of its stage: stages >= groups");
 constexpr int TCS_CONV_WARPS = TCS_GROUPS * TCS_GROUP_WARPS;  // then one TMA warp and one MMA warp
 constexpr int TCS_THREADS = (TCS_CONV_WARPS + 2) * 32;

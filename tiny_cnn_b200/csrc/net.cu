@@ -199,6 +199,9 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
   cudaStream_t main_stream = ctx->stream;
   bool side_used = false;
   int rc_side = 0;
+  // One side branch, not one per layer: the large kernels of both branches each fill the SMs, so
+  // more branches only interleave them and delay the dX chain (measured: two branches 0.387 ms
+  // against 0.374 ms with one).
   auto fork = [&]() -> int {
     B200_CUDA(cudaEventRecord(net->ev_fork, main_stream));
     B200_CUDA(cudaStreamWaitEvent(net->side, net->ev_fork, 0));
@@ -305,6 +308,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
     B200_CUDA(cudaEventRecord(net->ev_join, net->side));
     B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_join, 0));
   }
+
   return rc_side;
 }
 

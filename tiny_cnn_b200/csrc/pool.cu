@@ -93,7 +93,7 @@ __global__ void maxpool2x2_fwd_kernel(int in_w, int in_h, int out_w, int out_h, 
     float4 a = *reinterpret_cast<const float4 *>(ip);
     float4 b = *reinterpret_cast<const float4 *>(ip + in_w);
     // in-row index (c, y, x) of the window's first element
-    int base = (in_h * c + 2 * oy) * in_w + 4 * xp;
+    int base = (in_h * c + 2 * (int)oy) * in_w + 4 * (int)xp;
     float best0 = -FLT_MAX, best1 = -FLT_MAX;
     int i0 = 0, i1 = 0;
     if (a.x > best0) { best0 = a.x; i0 = base; }
@@ -113,25 +113,28 @@ __global__ void maxpool2x2_fwd_kernel(int in_w, int in_h, int out_w, int out_h, 
 // Gradient of the same layer; with `relu_y` != nullptr the gradient of a relu
 // that precedes the pooling layer is applied on the way (relu_y is that relu's
 // output, i.e. this layer's input): din = (y > 0) ? pooled gradient : 0.
+// I = unsigned when every index fits 32 bits (the usual case: the 64-bit divisions of the general
+// form cost more than the memory traffic of this kernel), long long otherwise.
+template <typename I>
 __global__ void maxpool2x2_bwd_kernel(int in_w, int in_h, int out_w, int out_h, long long planes,
                                       const float *__restrict__ dout,
                                       const int32_t *__restrict__ argmax,
                                       const float *__restrict__ relu_y, float *__restrict__ din,
                                       int in_c) {
-  const int ow2 = out_w >> 1;
-  long long total = planes * out_h * ow2;
-  long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  long long step = (long long)gridDim.x * blockDim.x;
+  const I ow2 = (I)(out_w >> 1), oh = (I)out_h, ic = (I)in_c;
+  const I total = (I)planes * oh * ow2;
+  I idx = (I)blockIdx.x * (I)blockDim.x + (I)threadIdx.x;
+  const I step = (I)gridDim.x * (I)blockDim.x;
   for (; idx < total; idx += step) {
-    int xp = (int)(idx % ow2);
-    long long r = idx / ow2;
-    int oy = (int)(r % out_h);
-    long long plane = r / out_h;
-    int c = (int)(plane % in_c);
-    long long o = (plane * out_h + oy) * out_w + 2 * xp;
+    const I xp = idx % ow2;
+    const I r = idx / ow2;
+    const I oy = r % oh;
+    const I plane = r / oh;
+    const int c = (int)(plane % ic);
+    const I o = (plane * oh + oy) * (I)out_w + 2 * xp;
     float2 g = *reinterpret_cast<const float2 *>(dout + o);
     int2 am = *reinterpret_cast<const int2 *>(argmax + o);
-    int base = (in_h * c + 2 * oy) * in_w + 4 * xp;
+    int base = (in_h * c + 2 * (int)oy) * in_w + 4 * (int)xp;
     float4 a, b;
     a.x = am.x == base ? g.x : 0.f;
     a.y = am.x == base + 1 ? g.x : 0.f;
@@ -141,7 +144,7 @@ __global__ void maxpool2x2_bwd_kernel(int in_w, int in_h, int out_w, int out_h, 
     a.w = am.y == base + 3 ? g.y : 0.f;
     b.z = am.y == base + in_w + 2 ? g.y : 0.f;
     b.w = am.y == base + in_w + 3 ? g.y : 0.f;
-    long long ioff = (plane * in_h + 2 * oy) * in_w + 4 * xp;
+    const I ioff = (plane * (I)in_h + 2 * oy) * (I)in_w + 4 * xp;
     if (relu_y) {
       float4 ya = *reinterpret_cast<const float4 *>(relu_y + ioff);
       float4 yb = *reinterpret_cast<const float4 *>(relu_y + ioff + in_w);
@@ -319,8 +322,12 @@ int maxpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *dout, const
   if (fast) {
     long long planes = (long long)B * d.in_c;
     long long work = planes * d.out_h * (d.out_w / 2);
-    maxpool2x2_bwd_kernel<<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
-      d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, relu_y, din, d.in_c);
+    if (planes * d.in_h * d.in_w < (1LL << 31))
+      maxpool2x2_bwd_kernel<unsigned><<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+        d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, relu_y, din, d.in_c);
+    else
+      maxpool2x2_bwd_kernel<long long><<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+        d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, relu_y, din, d.in_c);
     B200_LAUNCHED();
     return 0;
   }
