@@ -57,15 +57,6 @@ struct TcFwdSmallArgs {
   long long *dbg;  // optional [blocks][12] cycle counters (B200_TC_TIMING=1), else nullptr
 };
 
-__device__ __forceinline__ void umma_tf32_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-    "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-    " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
-    "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-    : "memory");
-}
-
 // four consecutive TMEM columns of the warp's 32 lanes
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, float a, float b, float c, float d) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(taddr),

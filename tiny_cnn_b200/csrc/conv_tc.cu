@@ -1270,15 +1270,17 @@ int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *d
 // be almost all padding.  Here the contraction still runs over pixels, but both operands are
 // K-major with 32 consecutive pixels of one output row per 128-byte row:
 //   B[o][p]  = dY[b][o][y][x0 + p]                  a TMA tile straight from the CHW gradient
-//   A[k][p]  = Xpad[b][c][y + ky][x0 + p + kx]      k = (c*KH + ky)*KW + kx, written by the four
-//              converter warps from the raw input rows (one TMA tile) as TF32 hi / lo tiles
+//   A[k][p]  = Xpad[b][c][y + ky][x0 + p + kx]      k = (c*KH + ky)*KW + kx: a converter thread owns
+//              tap k, gathers its pixels from the raw input rows (one TMA tile), splits them and
+//              writes hi / lo into TMEM lane k (tcgen05.st); the MMAs take A from tensor memory, so
+//              the im2col rows never pass through shared memory
 //   D[k][o] += A * B^T                              M = 128 (k padded), N = out channels, 4 k-steps
-// so dW needs 12 MMAs per 32 pixels.  The converter warps also split B into hi / lo in place and
+// so dW needs 8 MMAs per 32 pixels.  The converter warps also split B into hi / lo in place and
 // keep the bias-gradient sums.  Per-CTA partial results are merged in fixed order afterwards.
 
 namespace {
 
-constexpr int TCS_MAX_STAGES = 3;     // three are enough to hide the loads and leave shared memory for a co-resident kernel
+constexpr int TCS_MAX_STAGES = 4;     // gradient tile + raw input rows per stage: a few KB each
 constexpr int TCS_PX = 32;          // pixels per step (one 128-byte operand row)
 constexpr int TCS_GROUPS = 2;       // converter groups; group g converts the steps i with i % 2 == g
 constexpr int TCS_GROUP_WARPS = 8;
@@ -1295,7 +1297,7 @@ struct TcDwSmallArgs {
   int bw;               // floats per raw input row in shared memory
   int nsteps, ksplits;
   int nst;              // pipeline stages
-  int tmem_cols;
+  int tmem_cols;        // accumulator 2*OCp, then two A buffers of 32 hi + 32 lo columns
   long long row;
   long long *dbg;       // optional [blocks][8] cycle counters (B200_TC_TIMING=1), else nullptr
 };
@@ -1305,14 +1307,14 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
                           const TcDwSmallArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const uint32_t AB = 128u * 128u;                      // A tile (hi or lo): 128 rows of 128 bytes
   const uint32_t BB = (uint32_t)a.OCp * 128u;           // B tile (hi or lo)
   const uint32_t XB = ((uint32_t)(a.C * a.KH * a.bw * 4) + 1023u) & ~1023u;  // raw input rows
-  const uint32_t STAGE = 2 * AB + 2 * BB + XB;
+  const uint32_t STAGE = 2 * BB + XB;
   uint64_t *tma_full = reinterpret_cast<uint64_t *>(smem + (size_t)a.nst * STAGE);
   uint64_t *op_full = tma_full + TCS_MAX_STAGES;
   uint64_t *op_empty = op_full + TCS_MAX_STAGES;
-  uint64_t *accum = op_empty + TCS_MAX_STAGES;
+  uint64_t *a_empty = op_empty + TCS_MAX_STAGES;   // [2] A buffers in tensor memory, one per converter group
+  uint64_t *accum = a_empty + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum + 1);
   float *bsum_s = reinterpret_cast<float *>(tmem_slot + 4);   // [group][8 pixel quads][OCp] bias partials
 
@@ -1325,6 +1327,8 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
       mbar_init(&op_full[s], TCS_CONV_WARPS);
       mbar_init(&op_empty[s], 1);
     }
+    mbar_init(&a_empty[0], 1);
+    mbar_init(&a_empty[1], 1);
     mbar_init(accum, 1);
     mbar_fence_init();
   }
@@ -1333,6 +1337,7 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_a = tmem_base + 2u * (uint32_t)a.OCp;   // A buffer of group g: 64 columns from tmem_a + 64 g
   bool failed = false;
 
   if (warp == TCS_CONV_WARPS && lane == 0) {
@@ -1355,8 +1360,8 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
       const int xs = (x0 - a.pad_l) & ~3;  // aligned start column of the raw rows (floor to 4)
       uint8_t *p = smem + (size_t)st * STAGE;
       mbar_expect_tx(&tma_full[st], BB + (uint32_t)(a.C * a.KH * a.bw * 4));
-      tma_load_4d(p + 2 * AB, &dy_map, x0, 0, y, b, &tma_full[st]);
-      tma_load_4d(p + 2 * AB + 2 * BB, &x_map, xs, y - a.pad_t, 0, b, &tma_full[st]);
+      tma_load_4d(p, &dy_map, x0, 0, y, b, &tma_full[st]);
+      tma_load_4d(p + 2 * BB, &x_map, xs, y - a.pad_t, 0, b, &tma_full[st]);
     }
   } else if (warp == TCS_CONV_WARPS + 1 && lane == 0) {
     // ---- MMA issuer ---------------------------------------------------------------------------
@@ -1378,15 +1383,15 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
       }
       tc_fence_after();
       const uint32_t base = smem_u32(smem + (size_t)st * STAGE);
+      const uint32_t ta = tmem_a + (i & 1u) * 64u;
 #pragma unroll
       for (int k4 = 0; k4 < 4; ++k4) {
-        const uint64_t ahi = umma_desc(base + k4 * 32, 16, 1024, 2);
-        const uint64_t alo = umma_desc(base + AB + k4 * 32, 16, 1024, 2);
-        const uint64_t b = umma_desc(base + 2 * AB + k4 * 32, 16, 1024, 2);
-        umma_tf32(tmem_base, ahi, b, idesc2, (i | k4) != 0);
-        umma_tf32(tmem_base, alo, b, idesc1, 1);
+        const uint64_t b = umma_desc(base + k4 * 32, 16, 1024, 2);
+        umma_tf32_ta(tmem_base, ta + k4 * 8, b, idesc2, (i | k4) != 0);
+        umma_tf32_ta(tmem_base, ta + 32 + k4 * 8, b, idesc1, 1);
       }
       umma_commit(&op_empty[st]);
+      umma_commit(&a_empty[i & 1u]);
     }
     if (!failed) umma_commit(accum);
   } else if (warp < TCS_CONV_WARPS) {
@@ -1394,31 +1399,16 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
     const int KK = a.KH * a.KW;
     const int grp = warp / TCS_GROUP_WARPS, gtid = tid - grp * (TCS_GROUP_WARPS * 32);
     constexpr int NCT = TCS_GROUP_WARPS * 32;  // threads of one group
-    constexpr int NI = 128 * 8 / NCT;          // (row k, pixel quad) items per thread: 128 rows x 8 quads per step
-    // The items a thread converts are the same in every step: their source and destination offsets
-    // are computed once.  Rows beyond the real taps are zeroed once (by group 0).
-    int soff[NI];       // floats into the raw rows (without the step's column offset), -1: no tap
-    uint32_t doff[NI];  // bytes into the A tile
-#pragma unroll
-    for (int j = 0; j < NI; ++j) {
-      const int it = gtid + NCT * j, k = it >> 3, quad = it & 7;
-      doff[j] = (uint32_t)k * 128u + (uint32_t)((quad ^ (k & 7)) << 4);
-      if (k < a.Kreal) {
-        const int c = k / KK, r = k - c * KK, ky = r / a.KW, kx = r - ky * a.KW;
-        soff[j] = (c * a.KH + ky) * a.bw + kx + quad * 4;
-      } else {
-        soff[j] = -1;
-        if (grp == 0) {
-          for (int st = 0; st < a.nst; ++st) {
-            *reinterpret_cast<float4 *>(smem + (size_t)st * STAGE + doff[j]) = make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4 *>(smem + (size_t)st * STAGE + AB + doff[j]) = make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
-      }
+    // A: this thread owns tap k = its TMEM lane and half of the step's 32 pixels (two warps of a
+    // group share a lane quadrant); taps beyond the real ones are written as zeros
+    static_assert(TCS_GROUP_WARPS == 8, "two warps per TMEM lane quadrant in every converter group");
+    const int k = 32 * (warp & 3) + lane, phalf = ((warp - grp * TCS_GROUP_WARPS) >> 2) * 16;
+    int soff = -1;  // floats into the raw rows (without the step's column offset)
+    if (k < a.Kreal) {
+      const int c = k / KK, r = k - c * KK, ky = r / a.KW, kx = r - ky * a.KW;
+      soff = (c * a.KH + ky) * a.bw + kx + phalf;
     }
-    // all groups wait until the zero rows are in place and published to the tensor core's proxy
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    asm volatile("bar.sync 1, %0;\n" ::"n"(TCS_CONV_WARPS * 32) : "memory");
+    const uint32_t ta_thread = tmem_a + (uint32_t)grp * 64u + ((uint32_t)(warp & 3) << 21) + (uint32_t)phalf;
     constexpr int NB = 128 * 8 / NCT;  // at most 128 out channels x 8 quads per step
     float bacc[NB];                    // bias partials of the (o, quad) items this thread owns
 #pragma unroll
@@ -1440,20 +1430,27 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
         if (lane == 0) mbar_arrive(&op_full[st]);
         continue;
       }
+      // this group's A buffer was read by the MMAs of its previous step
+      if (i >= 2 && !mbar_wait_bounded(&a_empty[grp], ((i >> 1) - 1) & 1)) {
+        failed = true;
+        break;
+      }
+      tc_fence_after();
       uint8_t *p = smem + (size_t)st * STAGE;
       const int x0 = (s % a.nxb) * TCS_PX;
       const int d = (x0 - a.pad_l) - ((x0 - a.pad_l) & ~3);  // offset of the first needed column
-      const float *xr = reinterpret_cast<const float *>(p + 2 * AB + 2 * BB) + d;
+      const float *xr = reinterpret_cast<const float *>(p + 2 * BB) + d;
+      {
+        uint32_t h[16], l[16];
 #pragma unroll
-      for (int j = 0; j < NI; ++j) {
-        if (soff[j] >= 0) {
-          const float *src = xr + soff[j];
-          float h[4], l[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) split_tf32_rn(src[q], h[q], l[q]);
-          *reinterpret_cast<float4 *>(p + doff[j]) = make_float4(h[0], h[1], h[2], h[3]);
-          *reinterpret_cast<float4 *>(p + AB + doff[j]) = make_float4(l[0], l[1], l[2], l[3]);
+        for (int q = 0; q < 16; ++q) {
+          float hv, lv;
+          split_tf32_rn(soff >= 0 ? xr[soff + q] : 0.f, hv, lv);
+          h[q] = __float_as_uint(hv);
+          l[q] = __float_as_uint(lv);
         }
+        tmem_st16(ta_thread, h);
+        tmem_st16(ta_thread + 32, l);
       }
       // B: split the gradient tile in place (hi) and into the lo tile; bias partial sums
 #pragma unroll
@@ -1462,19 +1459,22 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
         if (it < a.OCp * 8) {
           const int o = it >> 3, quad = it & 7;
           const uint32_t off = (uint32_t)o * 128u + (uint32_t)((quad ^ (o & 7)) << 4);
-          float4 v = *reinterpret_cast<float4 *>(p + 2 * AB + off);
+          float4 v = *reinterpret_cast<float4 *>(p + off);
           float h[4], l[4];
           split_tf32_rn(v.x, h[0], l[0]);
           split_tf32_rn(v.y, h[1], l[1]);
           split_tf32_rn(v.z, h[2], l[2]);
           split_tf32_rn(v.w, h[3], l[3]);
-          *reinterpret_cast<float4 *>(p + 2 * AB + off) = make_float4(h[0], h[1], h[2], h[3]);
-          *reinterpret_cast<float4 *>(p + 2 * AB + BB + off) = make_float4(l[0], l[1], l[2], l[3]);
+          *reinterpret_cast<float4 *>(p + off) = make_float4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<float4 *>(p + BB + off) = make_float4(l[0], l[1], l[2], l[3]);
           bacc[slot] += (v.x + v.y) + (v.z + v.w);
         }
       }
-      // generic-proxy writes -> visible to the tensor core (async proxy), then hand over
+      // generic-proxy writes -> visible to the tensor core (async proxy); the TMEM stores have
+      // landed; then hand over
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&op_full[st]);
     }
@@ -1528,11 +1528,11 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
 
 size_t dw_small_stage(const ConvGeom &g, int OCp, int bw) {
   size_t XB = ((size_t)g.C * g.KH * bw * 4 + 1023) & ~(size_t)1023;
-  return 2 * 128 * 128 + 2 * (size_t)OCp * 128 + XB;
+  return 2 * (size_t)OCp * 128 + XB;
 }
 
 size_t dw_small_fixed(int OCp) {
-  return 1024 + (3 * TCS_MAX_STAGES + 1) * 8 + 32 + (size_t)TCS_GROUPS * 8 * OCp * 4 + 64;
+  return 1024 + (3 * TCS_MAX_STAGES + 3) * 8 + 32 + (size_t)TCS_GROUPS * 8 * OCp * 4 + 64;
 }
 
 // pipeline stages that fit (0: the kernel does not fit)
@@ -1618,7 +1618,7 @@ int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float
   a.ksplits = conv_dw_small_splits(ctx, g, B);
   a.nst = dw_small_stages(ctx, g, OCp, bw);
   B200_REQUIRE(a.nst >= TCS_GROUPS, "conv_dw_small: the tiles do not fit shared memory");
-  a.tmem_cols = pow2_at_least(2 * OCp);
+  a.tmem_cols = pow2_at_least(2 * OCp + 128);
   a.row = (long long)129 * OCp;
   const size_t smem = dw_small_fixed(OCp) + (size_t)a.nst * dw_small_stage(g, OCp, bw);
   B200_CUDA(cudaFuncSetAttribute(conv_dw_small_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

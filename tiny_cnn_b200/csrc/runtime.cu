@@ -171,7 +171,8 @@ int b200_ctx_create(int device, void *stream, b200_ctx **out) {
     c->stream = (cudaStream_t)stream;
     c->own_stream = false;
   } else {
-    B200_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    // above the default priority: a net's side branch runs at the default one and yields to this stream
+    B200_CUDA(cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, -1));
     c->own_stream = true;
   }
   ctx_load_tiles(c);

@@ -36,7 +36,9 @@ class Context:
         if stream is None:
             ts = torch.cuda.current_stream(device)
             if ts.cuda_stream == 0:
-                ts = torch.cuda.Stream(device)
+                # above the default priority: the net's side branch (default priority) then yields the
+                # SMs to the kernels of this stream, which carry the critical path of a step
+                ts = torch.cuda.Stream(device, priority=-1)
                 torch.cuda.set_stream(ts)
             self.torch_stream = ts
             stream = ts.cuda_stream
