@@ -281,6 +281,9 @@ def run_b200(args, rank, world, local_rank):
     net.init_weight(np.random.default_rng(42))  # same seed on every rank: identical replicas
     opt = nw.adam(1e-3)
     dp = DataParallel(net)
+    # replicas: the bucket is summed over NVLink by the library's own kernel inside the step's graph;
+    # NCCL only when the peer mapping is unavailable (or B200_DP_NCCL=1)
+    peer = world > 1 and os.environ.get("B200_DP_NCCL") != "1" and dp.enable_peer_reduce()
 
     NB = 8  # distinct resident batches rotated through the step's fixed input buffer
     xh, th = synthetic_batches(NB, 1000 + rank)
@@ -296,7 +299,7 @@ def run_b200(args, rank, world, local_rank):
     def step(i):
         x_cur.copy_(x_all[i % NB])
         t_cur.copy_(t_all[i % NB])
-        if world == 1:
+        if world == 1 or peer:
             net.train_onebatch(opt, x_cur, t_cur, LOSS_CE)
         else:
             net.forward_backward(x_cur, t_cur, LOSS_CE)
@@ -326,9 +329,12 @@ def run_b200(args, rank, world, local_rank):
         else:
             x_cur.copy_(x_pin[i % NB], non_blocking=True)
             t_cur.copy_(t_pin[i % NB], non_blocking=True)
-            net.forward_backward(x_cur, t_cur, LOSS_CE)
-            dp.allreduce_grads()
-            net.update(opt)
+            if peer:
+                net.train_onebatch(opt, x_cur, t_cur, LOSS_CE)
+            else:
+                net.forward_backward(x_cur, t_cur, LOSS_CE)
+                dp.allreduce_grads()
+                net.update(opt)
             out_pin.copy_(out_dev, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
@@ -394,13 +400,16 @@ def run_b200(args, rank, world, local_rank):
                        "l2": "8 resident input batches rotate through the step; activations + gradients "
                              "touched per step are about 130 MB, larger than the 126 MB L2",
                        "step": ("CUDA graph of forward+backward+update" if world == 1 else
+                                "one CUDA graph: forward+backward, sum of the gradient bucket over the ranks by the "
+                                "library's peer-memory kernel (NVLink stores, rank-ordered adds), update" if peer else
                                 "CUDA graph of forward+backward, NCCL sum all-reduce of the gradient bucket, update")
                                + "; inside the graph the weight-gradient kernels and the filter matrices run on a "
                                  "side branch beside the forward / dX chain"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "api": "Sequential.fit -> b200_net_fit_host: uploads of the next mini-batch overlap the "
-                           "current step" if world == 1 else "per-step copies, forward_backward, all-reduce, update",
+                           "current step" if world == 1 else ("per-step copies, train_onebatch (peer-memory reduction inside the graph)"
+                                                             if peer else "per-step copies, forward_backward, all-reduce, update"),
                     "h2d_bytes_per_step": BATCH * (IN_DIM + OUT_DIM) * 4,
                     "d2h_bytes_per_step": BATCH * OUT_DIM * 4},
             "gpu_launches": int(launches),

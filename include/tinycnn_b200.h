@@ -503,6 +503,24 @@ B200_API int b200_net_forward_backward(b200_net *net, const float *x, const floa
                                        int loss_kind);
 
 /*
+ * Data-parallel replicas (one process per GPU, the mini-batch sharded over them): the
+ * device form of edge::merge_grads (network.h:880-906) across GPUs.  Every rank provides
+ * a zero-filled buffer of b200_net_peer_reduce_bytes() bytes that all ranks have mapped
+ * (peer / symmetric memory) and passes the `world` base addresses, as mapped in its own
+ * process, to b200_net_peer_reduce_init.  From then on b200_net_train_step sums the
+ * gradient bucket over the ranks between the backward pass and the update, inside its
+ * captured graph: one kernel per GPU pushes its bucket into every rank's buffer over
+ * NVLink, waits (bounded) for the others' and adds the `world` copies in rank order, so
+ * the replicas stay bit-identical.  No 1/world factor.  Every rank must call the step the
+ * same number of times.  b200_net_peer_reduce is the reduction alone (after
+ * b200_net_forward_backward, before b200_net_update).
+ */
+B200_API size_t b200_net_peer_reduce_bytes(b200_net *net, int world);
+B200_API int b200_net_peer_reduce_init(b200_net *net, int rank, int world,
+                                       const unsigned long long *buffers);
+B200_API int b200_net_peer_reduce(b200_net *net);
+
+/*
  * The same step from HOST buffers (what network::train_onebatch does,
  * network.h:911-926): x/t are copied to the device, the step runs, and the
  * network output of the forward pass (batch x out_dim floats) is copied back

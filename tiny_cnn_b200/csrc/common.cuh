@@ -227,6 +227,19 @@ int gemm_tc(b200_ctx *ctx, int M, int N, int K, const float *src_a, long long ld
 size_t fc_scratch_floats(const b200_ctx *ctx, int in_size, int out_size, int B);
 int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
            const float *bias, float *out, int B, int act, float *scratch);
+// sum of a bucket over the ranks of a data-parallel job through peer memory (peer_reduce.cu)
+struct PeerReduce {
+  int rank = 0, world = 0;
+  long long n = 0;
+  float **bases_dev = nullptr;   // [world] every rank's buffer as mapped in this process
+  unsigned *step_dev = nullptr;  // reductions done so far
+};
+size_t peer_reduce_bytes(long long n, int world);
+int peer_reduce_init(b200_ctx *ctx, PeerReduce *pr, long long n, int rank, int world,
+                     const unsigned long long *bases);
+void peer_reduce_free(PeerReduce *pr);
+int peer_reduce_run(b200_ctx *ctx, const PeerReduce *pr, float *grads);
+
 int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
            const float *dout, float *din, float *dW, float *db, int accumulate, int B,
            float *scratch);

@@ -78,6 +78,7 @@ struct b200_net {
   const float *cur_x = nullptr;
   bool fuse = true;
   bool input_grad = true;
+  PeerReduce peer;  // data-parallel replicas: the gradient bucket is summed over the ranks inside the step
   // captured launch sequences: slot 0 = whole step, slot 1 = forward + backward
   struct GraphSlot {
     cudaGraphExec_t exec = nullptr;
@@ -357,6 +358,7 @@ int step_eager(b200_net *net, const float *x, const float *t, int B, int loss_ki
                const b200_opt_hyper *h) {
   B200_TRY(net_forward_impl(net, x, B));
   B200_TRY(net_backward_impl(net, t, loss_kind));
+  if (net->peer.world > 1) B200_TRY(peer_reduce_run(net->ctx, &net->peer, net->grads));
   return net_update_impl(net, opt_kind, h);
 }
 
@@ -595,6 +597,7 @@ int b200_net_destroy(b200_net *net) {
     if (net->stage_free[i]) cudaEventDestroy(net->stage_free[i]);
   }
   if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+  peer_reduce_free(&net->peer);
   if (net->side) cudaStreamDestroy(net->side);
   if (net->ev_fork) cudaEventDestroy(net->ev_fork);
   if (net->ev_join) cudaEventDestroy(net->ev_join);
@@ -674,6 +677,25 @@ int b200_net_opt_reset(b200_net *net, int reset_powers) {
   B200_CUDA(cudaMemsetAsync(net->state1, 0, bytes, net->ctx->stream));
   if (reset_powers) net->pow_init = false;
   return 0;
+}
+
+size_t b200_net_peer_reduce_bytes(b200_net *net, int world) {
+  if (!net || world < 2) return 0;
+  return peer_reduce_bytes((long long)net->n_params, world);
+}
+
+int b200_net_peer_reduce_init(b200_net *net, int rank, int world, const unsigned long long *buffers) {
+  B200_TRY(check_net(net));
+  B200_TRY(peer_reduce_init(net->ctx, &net->peer, (long long)net->n_params, rank, world, buffers));
+  // the step's launch sequence changes: captured graphs are rebuilt
+  for (auto &slot : net->slots) slot.key.clear();
+  return 0;
+}
+
+int b200_net_peer_reduce(b200_net *net) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(net->peer.world > 1, "net_peer_reduce: b200_net_peer_reduce_init was not called");
+  return peer_reduce_run(net->ctx, &net->peer, net->grads);
 }
 
 int b200_net_update(b200_net *net, int opt_kind, const b200_opt_hyper *h) {

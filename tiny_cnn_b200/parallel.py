@@ -7,6 +7,12 @@ bit-identical without a parameter broadcast after step 0.
 
 `torch.distributed` is the plumbing (NCCL over NVLink on GPUs, gloo in CPU
 tests); the collective operates in place on the net's flat gradient bucket.
+
+On GPUs `enable_peer_reduce()` moves the sum into the step itself: every rank
+maps every rank's exchange buffer (torch symmetric memory does the rendezvous),
+and the library's own kernel pushes the bucket over NVLink and adds the copies in
+rank order inside the captured graph of `train_onebatch`, which is then one graph
+launch per step with no collective call between two graphs.
 """
 from __future__ import annotations
 
@@ -36,14 +42,58 @@ class DataParallel:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.bucket = net.grads_tensor()
+        self.peer = False
+        self._symm = None  # keeps the exchange buffer and its rendezvous handle alive
+
+    def enable_peer_reduce(self) -> bool:
+        """Map every rank's exchange buffer into every rank and hand the addresses to the net
+        (b200_net_peer_reduce_init).  Returns True when EVERY rank succeeded; otherwise all
+        ranks keep the NCCL all-reduce.  Collective: every rank must call it."""
+        if self.world <= 1 or not self.bucket.is_cuda:
+            return False
+        import ctypes as C
+
+        from ._lib import check
+        ok, why = 1, ""
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            lib, h = self.net.lib, self.net.handle
+            nbytes = int(lib.b200_net_peer_reduce_bytes(h, self.world))
+            buf = symm_mem.empty((nbytes + 3) // 4, dtype=torch.float32, device=self.bucket.device)
+            buf.zero_()
+            grp = self.group if self.group is not None else dist.group.WORLD
+            hdl = symm_mem.rendezvous(buf, grp)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            torch.cuda.synchronize()
+        except Exception as e:  # no peer mapping on this system: stay with NCCL
+            ok, why = 0, f"{type(e).__name__}: {e}"
+        flag = torch.tensor([ok], device=self.bucket.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)  # also: every buffer is zeroed
+        if int(flag.item()) != 1:
+            if why and self.rank == 0:
+                print(f"[tiny_cnn_b200] peer reduce unavailable, using NCCL ({why})", flush=True)
+            return False
+        arr = (C.c_ulonglong * self.world)(*ptrs)
+        check(lib.b200_net_peer_reduce_init(h, self.rank, self.world, arr))
+        self._symm = (buf, hdl)
+        self.peer = True
+        return True
 
     def allreduce_grads(self):
         """In-place SUM over ranks of the gradient bucket (no averaging)."""
         if self.world > 1:
-            dist.all_reduce(self.bucket, op=dist.ReduceOp.SUM, group=self.group)
+            if self.peer:
+                from ._lib import check
+                check(self.net.lib.b200_net_peer_reduce(self.net.handle))
+            else:
+                dist.all_reduce(self.bucket, op=dist.ReduceOp.SUM, group=self.group)
 
     def train_onebatch(self, opt, x_shard, t_shard, loss: int):
         """One data-parallel step on this rank's shard."""
+        if self.peer and hasattr(self.net, "train_onebatch"):
+            # the reduction is part of the net's captured step: one graph launch
+            self.net.train_onebatch(opt, x_shard, t_shard, loss)
+            return
         self.net.forward(x_shard)
         self.net.backward(t_shard, loss)
         self.allreduce_grads()
