@@ -71,7 +71,8 @@ class DataParallel:
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)  # also: every buffer is zeroed
         if int(flag.item()) != 1:
             if why and self.rank == 0:
-                print(f"[tiny_cnn_b200] peer reduce unavailable, using NCCL ({why})", flush=True)
+                import sys
+                print(f"[tiny_cnn_b200] peer reduce unavailable, using NCCL ({why})", file=sys.stderr, flush=True)
             return False
         arr = (C.c_ulonglong * self.world)(*ptrs)
         check(lib.b200_net_peer_reduce_init(h, self.rank, self.world, arr))
