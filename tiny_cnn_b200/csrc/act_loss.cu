@@ -92,6 +92,23 @@ __global__ void softmax_fwd_kernel(const float *__restrict__ x, float *__restric
   for (int j = 0; j < dim; ++j) yr[j] = yr[j] / denom;
 }
 
+// Rows of at most 16 values, sixteen lanes per row: lane j exponentiates x_j, every lane adds the
+// exponentials in index order (fetched from their lanes), so the result has the bits of the
+// one-thread form above.
+__global__ void __launch_bounds__(256) softmax_fwd16_kernel(const float *__restrict__ x, float *__restrict__ y, int dim,
+                                                            int B) {
+  const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 4, j = threadIdx.x & 15;
+  const int base = threadIdx.x & 16;
+  const bool live = n < B && j < dim;
+  const float xj = live ? x[(size_t)n * dim + j] : 0.f;
+  float alpha = __shfl_sync(0xffffffffu, xj, base);
+  for (int k = 1; k < dim; ++k) alpha = fmaxf(alpha, __shfl_sync(0xffffffffu, xj, base + k));
+  const float ej = expf(xj - alpha);
+  float denom = 0.f;
+  for (int k = 0; k < dim; ++k) denom += __shfl_sync(0xffffffffu, ej, base + k);
+  if (live) y[(size_t)n * dim + j] = ej / denom;
+}
+
 __device__ __forceinline__ float loss_grad_one(int kind, float yi, float ti, float factor) {
   if (kind == B200_LOSS_MSE) return __fmul_rn(factor, __fsub_rn(yi, ti));
   if (kind == B200_LOSS_CROSS_ENTROPY)
@@ -102,6 +119,36 @@ __device__ __forceinline__ float loss_grad_one(int kind, float yi, float ti, flo
 // softmax_layer.h:36-55: dx_j = sum_k dy_k * (k == j ? y_j(1-y_j) : -y_k*y_j)
 // With `t` != nullptr the incoming gradient is first computed as the loss gradient of (y, t)
 // (loss_function.h) and stored to dy: the loss-gradient and softmax-gradient kernels in one.
+// The same for rows of at most 16 values with sixteen lanes per row: lane j computes dx_j, fetching y_k
+// and the incoming gradient g_k from lane k; the sum over k runs in index order as in the one-thread
+// form below, so both give the same bits.
+__global__ void __launch_bounds__(256) softmax_bwd16_kernel(const float *__restrict__ y, float *__restrict__ dy,
+                                                            float *__restrict__ dx, int dim, int B,
+                                                            const float *__restrict__ t, int loss_kind) {
+  const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 4, j = threadIdx.x & 15;
+  const int base = threadIdx.x & 16;  // first lane of this row's group inside the warp
+  const bool live = n < B && j < dim;
+  const float factor = 2.0f / (float)dim;
+  float yj = 0.f, gj = 0.f;
+  if (live) {
+    yj = y[(size_t)n * dim + j];
+    if (t != nullptr) {
+      gj = loss_grad_one(loss_kind, yj, t[(size_t)n * dim + j], factor);
+      dy[(size_t)n * dim + j] = gj;
+    } else {
+      gj = dy[(size_t)n * dim + j];
+    }
+  }
+  float s = 0.f;
+  for (int k = 0; k < dim; ++k) {
+    const float yk = __shfl_sync(0xffffffffu, yj, base + k);
+    const float gk = __shfl_sync(0xffffffffu, gj, base + k);
+    const float df = (k == j) ? __fmul_rn(yj, __fsub_rn(1.f, yj)) : __fmul_rn(-yk, yj);
+    s = __fadd_rn(s, __fmul_rn(gk, df));
+  }
+  if (live) dx[(size_t)n * dim + j] = s;
+}
+
 __global__ void softmax_bwd_kernel(const float *__restrict__ y, float *__restrict__ dy,
                                    float *__restrict__ dx, int dim, int B, const float *__restrict__ t,
                                    int loss_kind) {
@@ -204,7 +251,10 @@ int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B) {
   size_t n = (size_t)dim * B;
   if (n == 0) return 0;
   if (kind == B200_ACT_SOFTMAX) {
-    softmax_fwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(x, y, dim, B);
+    if (dim <= 16)
+      softmax_fwd16_kernel<<<ceil_div(B * 16, 256), 256, 0, ctx->stream>>>(x, y, dim, B);
+    else
+      softmax_fwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(x, y, dim, B);
   } else {
     size_t n4 = (aligned16(x) && aligned16(y)) ? n / 4 : 0;
     act_fwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(kind, x, y,
@@ -221,7 +271,11 @@ int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx,
   size_t n = (size_t)dim * B;
   if (n == 0) return 0;
   if (kind == B200_ACT_SOFTMAX) {
-    softmax_bwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(y, const_cast<float *>(dy), dx, dim, B, nullptr, 0);
+    if (dim <= 16)
+      softmax_bwd16_kernel<<<ceil_div(B * 16, 256), 256, 0, ctx->stream>>>(y, const_cast<float *>(dy), dx, dim, B,
+                                                                           nullptr, 0);
+    else
+      softmax_bwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(y, const_cast<float *>(dy), dx, dim, B, nullptr, 0);
   } else {
     size_t n4 = (aligned16(y) && aligned16(dy) && aligned16(dx)) ? n / 4 : 0;
     act_bwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
@@ -248,7 +302,10 @@ int softmax_loss_bwd(b200_ctx *ctx, int loss_kind, const float *y, const float *
   B200_REQUIRE(loss_kind >= B200_LOSS_MSE && loss_kind <= B200_LOSS_CROSS_ENTROPY_MULTICLASS,
                "softmax_loss_bwd: unknown loss %d", loss_kind);
   if ((size_t)dim * B == 0) return 0;
-  softmax_bwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(y, dy, dx, dim, B, t, loss_kind);
+  if (dim <= 16)
+    softmax_bwd16_kernel<<<ceil_div(B * 16, 256), 256, 0, ctx->stream>>>(y, dy, dx, dim, B, t, loss_kind);
+  else
+    softmax_bwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(y, dy, dx, dim, B, t, loss_kind);
   B200_LAUNCHED();
   return 0;
 }
