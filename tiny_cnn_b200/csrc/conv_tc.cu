@@ -169,62 +169,42 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
       }
     }
   } else {
-    // one pooled pixel per lane: its gradient goes to the one input position argmax names.  The
-    // pixel's place in the chunk does not depend on the channel; two channels per pass.
+    // one pooled pixel of one channel per thread: its gradient goes to the one input position
+    // argmax names.  (channel, pixel) pairs are spread over the whole block, so that narrow images
+    // (a handful of pooled pixels per chunk) still fill the lanes; consecutive threads read
+    // consecutive pooled pixels, and consecutive channel planes are neighbours in memory.
     const int pw = W >> 1, ph = H >> 1, nq = ((nr + 1) >> 1) * pw;
     const int pws = (pw & (pw - 1)) == 0 ? 31 - __clz(pw) : -1;
-    for (int q = lane; q < nq; q += 32) {
+    for (int it = threadIdx.x; it < C * nq; it += 256) {
+      const int c = it / nq, q = it - c * nq;
       const int pry = pws >= 0 ? q >> pws : q / pw, prx = q - pry * pw, ry = 2 * pry, x = 2 * prx, y = r0 + ry;
-      const bool live = y < H, second = ry + 1 < nr;
-      const size_t poff = (size_t)(y >> 1) * pw + prx, ooff = (size_t)y * W + x;
       const int pp = ry * W + x;
-      for (int c = warp; c < C; c += 16) {
-        const int c2 = c + 8;
-        const bool two = c2 < C;
-        float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        if (live) {
-          const int cc[2] = {c, two ? c2 : c};
-          float gval[2];
-          int am[2];
-          float2 ra[2], rb2[2];
-#pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            const size_t po = ((size_t)b * C + cc[k]) * ph * pw + poff;
-            gval[k] = src.a[po];
-            am[k] = src.am[po] - ((H * cc[k] + y) * W + x);  // offset inside the window: 0, 1, W, W+1
-            if (src.relu_y != nullptr) {
-              const size_t o = ((size_t)b * C + cc[k]) * plane + ooff;
-              ra[k] = *reinterpret_cast<const float2 *>(src.relu_y + o);
-              rb2[k] = *reinterpret_cast<const float2 *>(src.relu_y + o + W);
-            } else {
-              ra[k] = rb2[k] = make_float2(1.f, 1.f);
-            }
-          }
-#pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            if (k == 1 && !two) break;
-            v[k][0] = (am[k] == 0 && ra[k].x > 0.f) ? gval[k] : 0.f;
-            v[k][1] = (am[k] == 1 && ra[k].y > 0.f) ? gval[k] : 0.f;
-            v[k][2] = (am[k] == W && rb2[k].x > 0.f) ? gval[k] : 0.f;
-            v[k][3] = (am[k] == W + 1 && rb2[k].y > 0.f) ? gval[k] : 0.f;
-            if (src.out_chw != nullptr) {
-              const size_t o = ((size_t)b * C + cc[k]) * plane + ooff;
-              *reinterpret_cast<float2 *>(src.out_chw + o) = make_float2(v[k][0], v[k][1]);
-              *reinterpret_cast<float2 *>(src.out_chw + o + W) = make_float2(v[k][2], v[k][3]);
-            }
-          }
+      float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+      if (y < H) {
+        const size_t po = ((size_t)b * C + c) * ph * pw + (size_t)(y >> 1) * pw + prx;
+        const size_t o = ((size_t)b * C + c) * plane + (size_t)y * W + x;
+        const float gval = src.a[po];
+        const int am = src.am[po] - ((H * c + y) * W + x);  // offset inside the window: 0, 1, W, W+1
+        float2 ra = make_float2(1.f, 1.f), rb2 = make_float2(1.f, 1.f);
+        if (src.relu_y != nullptr) {
+          ra = *reinterpret_cast<const float2 *>(src.relu_y + o);
+          rb2 = *reinterpret_cast<const float2 *>(src.relu_y + o + W);
         }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          if (k == 1 && !two) break;
-          float *trow = tile + (k ? c2 : c) * pitch;
-          trow[pp] = v[k][0];
-          trow[pp + 1] = v[k][1];
-          if (second) {
-            trow[pp + W] = v[k][2];
-            trow[pp + W + 1] = v[k][3];
-          }
+        v0 = (am == 0 && ra.x > 0.f) ? gval : 0.f;
+        v1 = (am == 1 && ra.y > 0.f) ? gval : 0.f;
+        v2 = (am == W && rb2.x > 0.f) ? gval : 0.f;
+        v3 = (am == W + 1 && rb2.y > 0.f) ? gval : 0.f;
+        if (src.out_chw != nullptr) {
+          *reinterpret_cast<float2 *>(src.out_chw + o) = make_float2(v0, v1);
+          *reinterpret_cast<float2 *>(src.out_chw + o + W) = make_float2(v2, v3);
         }
+      }
+      float *trow = tile + c * pitch;
+      trow[pp] = v0;
+      trow[pp + 1] = v1;
+      if (ry + 1 < nr) {
+        trow[pp + W] = v2;
+        trow[pp + W + 1] = v3;
       }
     }
   }
