@@ -34,6 +34,22 @@ def test_shard_bounds_cover_the_batch():
         shard_bounds(4, 2, 2)
 
 
+def test_peer_reduce_is_off_without_gpus():
+    """On CPU buckets (and for a single rank) the peer-memory reduction declines without touching
+    the library or the process group; the driver keeps the all-reduce of torch.distributed."""
+    from tiny_cnn_b200.parallel import DataParallel
+
+    class Net:
+        def grads_tensor(self):
+            return torch.zeros(8)
+
+    dp = DataParallel(Net())
+    assert dp.world == 1 and dp.peer is False
+    assert dp.enable_peer_reduce() is False and dp.peer is False
+    dp.world = 2  # a CPU bucket never takes the peer path either
+    assert dp.enable_peer_reduce() is False and dp.peer is False
+
+
 class OracleNet:
     """The oracle's CPU network behind the interface DataParallel drives."""
 
