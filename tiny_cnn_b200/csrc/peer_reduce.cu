@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(PR_THREADS) peer_reduce_kernel(const PeerArgs 
   __syncthreads();
   if (tid < a.world) {
     unsigned *flag = reinterpret_cast<unsigned *>(a.bases[tid] + flag_off) + half * PR_CHUNKS + b;
+    __threadfence_system();  // the signalling thread itself orders the block's stores (seen through the barrier) before the flag
     atomicAdd_system(flag, 1u);
   }
   // 3. wait for every rank's chunk (bounded: about two seconds of wall time)
