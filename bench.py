@@ -10,6 +10,13 @@ One JSON line is printed by rank 0.  `value` is measured with inputs resident in
 HBM; `e2e` goes through the HOST-buffer entry point (host->device copy of the
 batch and device->host copy of the network output inside the timed region).
 Data are synthetic with CIFAR-10's shapes (3x32x32 inputs ~ N(0,1), 10 classes).
+
+A block of `--steps` steps is timed with CUDA events between barriers, and the
+block is repeated until at least one second has been timed; the line reports the
+median block (`ms_per_step`) with the fastest and slowest beside it.  With more
+than one rank the line also carries `parity`: the replicas' parameters compared
+bit for bit after the timed steps, and two data-parallel steps compared with the
+same two steps of ONE GPU on the concatenated mini-batch.
 """
 from __future__ import annotations
 
@@ -29,7 +36,10 @@ for p in (ROOT, ROOT / "tests"):
         sys.path.insert(0, str(p))
 
 BATCH = 256
+NB = 8  # distinct mini-batches rotated through the step
 IN_DIM, OUT_DIM = 3 * 32 * 32, 10
+MIN_TIMED_MS = 1000.0  # the block of --steps steps is repeated until this much has been timed
+MAX_BLOCKS = 400
 WORKLOAD = "cifar10_net conv5x5(3->32,same)-relu-maxpool2 conv5x5(32->32)-relu-maxpool2 " \
            "conv5x5(32->64)-relu-maxpool2 fc1024->64-relu fc64->10-softmax; cross_entropy; adam lr=1e-3"
 LOSS_CE, OPT_ADAM = 1, 1
@@ -109,6 +119,13 @@ def synthetic_batches(n_batches, seed):
 # --------------------------------------------------------------------------------------------
 # reference arm: the unmodified reference's CPU path (OpenMP, backend_t::internal)
 # --------------------------------------------------------------------------------------------
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -117,17 +134,21 @@ def run_reference(args, rank, world):
     from cases import hyper_for, xavier_params
     specs, keep = make_specs()
     arr = (type(specs[0]) * len(specs))(*specs)
-    x, t = synthetic_batches(1, 1000)
+    x, t = synthetic_batches(NB, 1000)
     hy = hyper_for(OPT_ADAM)
     ref = o.load_reference()
+    count = [0]
     if ref is not None:
-        kind, cores = "reference", ref.ref_openmp_threads()
+        # all host cores, whatever OMP_NUM_THREADS the launcher exported (torch.distributed.run sets 1)
+        kind, cores = "reference", ref.ref_set_threads(host_cores())
         h = ref.ref_net_create(arr, len(specs), 42)
         p0 = xavier_params(specs, 42)
         ref.ref_net_set_params(h, o.p(p0))
 
         def one_step():
-            s = ref.ref_net_fit(h, o.p(x[0]), o.p(t[0]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))
+            i = count[0] % NB
+            count[0] += 1
+            s = ref.ref_net_fit(h, o.p(x[i]), o.p(t[i]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))
             assert s >= 0
             return s
         sample = f"one mini-batch of {BATCH} samples per step through network::fit, OpenMP {cores} threads"
@@ -141,8 +162,11 @@ def run_reference(args, rank, world):
         params[:] = xavier_params(specs, 42)
 
         def one_step():
+            i = count[0] % NB
+            count[0] += 1
+            xs, ts = np.ascontiguousarray(x[i][:sub]), np.ascontiguousarray(t[i][:sub])
             t0 = time.perf_counter()
-            orc.orc_net_train_step(net, o.p(x[0][:sub]), o.p(t[0][:sub]), sub, LOSS_CE, OPT_ADAM, C.byref(hy))
+            orc.orc_net_train_step(net, o.p(xs), o.p(ts), sub, LOSS_CE, OPT_ADAM, C.byref(hy))
             return time.perf_counter() - t0
         sample = f"{sub} samples per step through the C restatement, 1 thread"
         per_step = sub
@@ -155,13 +179,21 @@ def run_reference(args, rank, world):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "global_batch": BATCH * args.gpus,
-                   "parallelism": f"dp{args.gpus}", "note": "CPU reference arm runs one GPU's batch per step"},
+        "config": bench_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "note": "the CPU reference runs one GPU's mini-batch per step on rank 0's host cores",
     }
     print(json.dumps(line), flush=True)
+
+
+def bench_config(world):
+    """The `config` object, identical in both arms."""
+    return {"workload": WORKLOAD, "per_gpu_batch": BATCH, "global_batch": BATCH * world,
+            "parallelism": f"dp{world}",
+            "l2": f"{NB} distinct mini-batches rotate through the step; the activations and gradients a step "
+                  "touches are about 130 MB, larger than the 126 MB L2, so no flush is needed"}
 
 
 # --------------------------------------------------------------------------------------------
@@ -269,7 +301,7 @@ def run_b200(args, rank, world, local_rank):
 
     from tiny_cnn_b200 import network as nw
     from tiny_cnn_b200 import ops
-    from tiny_cnn_b200._lib import load
+    from tiny_cnn_b200._lib import check, load
     from tiny_cnn_b200.parallel import DataParallel
 
     torch.cuda.set_device(local_rank)
@@ -278,14 +310,13 @@ def run_b200(args, rank, world, local_rank):
     lib = load()
     ctx = ops.Context(local_rank)
     net = nw.cifar10_net(local_rank).build(BATCH, ctx)
-    net.init_weight(np.random.default_rng(42))  # same seed on every rank: identical replicas
+    p0 = net.init_weight(np.random.default_rng(42))  # same seed on every rank: identical replicas
     opt = nw.adam(1e-3)
     dp = DataParallel(net)
-    # replicas: the bucket is summed over NVLink by the library's own kernel inside the step's graph;
+    # replicas: the bucket is summed over NVLink by the library's own kernels inside the step's graph;
     # NCCL only when the peer mapping is unavailable (or B200_DP_NCCL=1)
     peer = world > 1 and os.environ.get("B200_DP_NCCL") != "1" and dp.enable_peer_reduce()
 
-    NB = 8  # distinct resident batches rotated through the step's fixed input buffer
     xh, th = synthetic_batches(NB, 1000 + rank)
     x_all = torch.from_numpy(xh).cuda()
     t_all = torch.from_numpy(th).cuda()
@@ -296,83 +327,102 @@ def run_b200(args, rank, world, local_rank):
     out_pin = torch.empty(BATCH, OUT_DIM).pin_memory()
     out_dev = net.output_tensor(BATCH)
 
-    def step(i):
-        x_cur.copy_(x_all[i % NB])
-        t_cur.copy_(t_all[i % NB])
+    def dp_step(x, t):
         if world == 1 or peer:
-            net.train_onebatch(opt, x_cur, t_cur, LOSS_CE)
+            net.train_onebatch(opt, x, t, LOSS_CE)
         else:
-            net.forward_backward(x_cur, t_cur, LOSS_CE)
+            net.forward_backward(x, t, LOSS_CE)
             dp.allreduce_grads()
             net.update(opt)
 
-    def fit_e2e(steps):
-        """`steps` mini-batches through network::fit's counterpart: every step's inputs come from
-        pinned host memory and its forward output goes back to the host, inside the call."""
-        idx = [(warmup_base + i) % NB for i in range(steps)]
-        xs = torch.cat([x_pin[j] for j in idx]).pin_memory()
-        ts = torch.cat([t_pin[j] for j in idx]).pin_memory()
-        outs = torch.empty(steps * BATCH, OUT_DIM).pin_memory()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        net.fit(opt, xs, ts, BATCH, 1, LOSS_CE, outs)   # returns after the last output has arrived
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1)
-
-    warmup_base = 0
-
-    def step_e2e(i):
-        if world == 1:
-            net.train_onebatch_host(opt, x_pin[i % NB], t_pin[i % NB], LOSS_CE, out_pin)
-        else:
-            x_cur.copy_(x_pin[i % NB], non_blocking=True)
-            t_cur.copy_(t_pin[i % NB], non_blocking=True)
-            if peer:
-                net.train_onebatch(opt, x_cur, t_cur, LOSS_CE)
-            else:
-                net.forward_backward(x_cur, t_cur, LOSS_CE)
-                dp.allreduce_grads()
-                net.update(opt)
-            out_pin.copy_(out_dev, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+    def step(i):
+        x_cur.copy_(x_all[i % NB])
+        t_cur.copy_(t_all[i % NB])
+        dp_step(x_cur, t_cur)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup):
-        for i in range(warmup):
-            fn(i)
+    def max_over_ranks(ms):
+        if world > 1:
+            tms = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ms = float(tms[0])
+        return ms
+
+    def timed_block(run_steps, steps):
+        """barrier, event, `steps` steps, event, barrier; device time, max over ranks."""
         barrier()
         l0 = lib.b200_launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(steps):
-            fn(warmup + i)
+        run_steps(steps)
         e1.record()
         barrier()
-        ms = e0.elapsed_time(e1)
-        launches = lib.b200_launch_count() - l0
-        if world > 1:
-            tms = torch.tensor([ms], device="cuda")
-            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-            ms = float(tms[0])
-        return ms, launches
+        return max_over_ranks(e0.elapsed_time(e1)), lib.b200_launch_count() - l0
+
+    def repeat_blocks(run_steps, steps):
+        """Repeat the block until MIN_TIMED_MS have been timed (every rank sees the same max-reduced
+        times, so every rank stops after the same block)."""
+        times, launches = [], 0
+        while (sum(times) < MIN_TIMED_MS or len(times) < 3) and len(times) < MAX_BLOCKS:
+            ms, launches = timed_block(run_steps, steps)
+            times.append(ms)
+        return times, launches
+
+    # ---- inputs resident in HBM ------------------------------------------------------------
+    counter = [0]
+
+    def run_device(steps):
+        for _ in range(steps):
+            step(counter[0])
+            counter[0] += 1
 
     warmup = max(args.warmup, 3)
+    run_device(warmup)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms, launches = timed(step, args.steps, warmup)
+    blocks, launches = repeat_blocks(run_device, args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    if world == 1:
-        fit_e2e(warmup)
-        ms_e2e = fit_e2e(args.steps)
-    else:
-        ms_e2e, _ = timed(step_e2e, args.steps, warmup)
+    ctx.sync()  # raises if a kernel gave up a bounded wait (a peer reduction that timed out)
+    ms = statistics.median(blocks)
+
+    # ---- end to end: every step's inputs from pinned host memory, its output back to the host ----
+    fit_ok = world == 1 or peer
+
+    def run_e2e(steps):
+        base = counter[0]
+        counter[0] += steps
+        if fit_ok:
+            # network::fit's counterpart: one library call; the upload of mini-batch i+1 runs on a copy
+            # stream beside step i (with several ranks the reduction over the replicas is inside the step)
+            net.fit(opt, xs_fit[:steps * BATCH], ts_fit[:steps * BATCH], BATCH, 1, LOSS_CE, outs_fit[:steps * BATCH])
+            return
+        for i in range(base, base + steps):
+            x_cur.copy_(x_pin[i % NB], non_blocking=True)
+            t_cur.copy_(t_pin[i % NB], non_blocking=True)
+            dp_step(x_cur, t_cur)
+            out_pin.copy_(out_dev, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    n_fit = max(args.steps, warmup)
+    if fit_ok:
+        idx = [i % NB for i in range(n_fit)]
+        xs_fit = torch.cat([x_pin[j] for j in idx]).pin_memory()
+        ts_fit = torch.cat([t_pin[j] for j in idx]).pin_memory()
+        outs_fit = torch.empty(n_fit * BATCH, OUT_DIM).pin_memory()
+    run_e2e(warmup)
+    blocks_e2e, _ = repeat_blocks(run_e2e, args.steps)
+    ctx.sync()
+    ms_e2e = statistics.median(blocks_e2e)
+
+    # ---- replicas against each other and against one GPU on the concatenated mini-batch ----
+    parity = None
+    if world > 1:
+        parity = dp_parity(torch, dist, np, nw, ops, net, opt, dp_step, p0, rank, world, local_rank, ctx)
 
     global_batch = BATCH * world
     value = global_batch * args.steps / (ms * 1e-3)
@@ -388,34 +438,43 @@ def run_b200(args, rank, world, local_rank):
             peaks = json.loads(mp.read_text())
         kernels, roofline = conv_rooflines(kt, peaks)
         cpu = cpu_baseline() if world == 1 else None
+        per = 1.0 / args.steps
         line = {
             "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
-            "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms * per,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "global_batch": global_batch,
-                       "parallelism": f"dp{world}",
-                       "arithmetic": "fp32 results; conv2/conv3 passes on tcgen05 tensor cores as 3xTF32 "
-                                     "(hi/lo split, fp32 accumulation) -- also conv1 forward and dW; conv1 dX and the rest fp32 FFMA",
-                       "l2": "8 resident input batches rotate through the step; activations + gradients "
-                             "touched per step are about 130 MB, larger than the 126 MB L2",
-                       "step": ("CUDA graph of forward+backward+update" if world == 1 else
-                                "one CUDA graph: forward+backward, sum of the gradient bucket over the ranks by the "
-                                "library's peer-memory kernel (NVLink stores, rank-ordered adds), update" if peer else
-                                "CUDA graph of forward+backward, NCCL sum all-reduce of the gradient bucket, update")
-                               + "; inside the graph the weight-gradient kernels and the filter matrices run on a "
-                                 "side branch beside the forward / dX chain"},
+            "config": bench_config(world),
+            "timing": {"blocks": len(blocks), "timed_ms": round(sum(blocks), 2),
+                       "ms_per_step_median": ms * per, "ms_per_step_min": min(blocks) * per,
+                       "ms_per_step_max": max(blocks) * per,
+                       "how": f"blocks of {args.steps} steps between barriers, CUDA events, max over ranks, "
+                              f"repeated until {MIN_TIMED_MS:.0f} ms were timed; the median block is reported"},
+            "notes": {
+                "arithmetic": "fp32 results; conv2/conv3 passes on tcgen05 tensor cores as 3xTF32 (hi/lo split, fp32 "
+                              "accumulation) -- also conv1 forward and dW; conv1 dX and the rest fp32 FFMA",
+                "step": ("CUDA graph of forward+backward+update" if world == 1 else
+                         "one CUDA graph: forward+backward with the gradients of all layers but the first pushed to the "
+                         "peers over NVLink from a side branch as soon as they exist, then first-layer push + "
+                         "rank-ordered sum (the library's peer-memory kernels), update" if peer else
+                         "CUDA graph of forward+backward, NCCL sum all-reduce of the gradient bucket, update")
+                        + "; inside the graph the weight-gradient kernels and the filter matrices run on a "
+                          "side branch beside the forward / dX chain"},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
-                    "api": "Sequential.fit -> b200_net_fit_host: uploads of the next mini-batch overlap the "
-                           "current step" if world == 1 else ("per-step copies, train_onebatch (peer-memory reduction inside the graph)"
-                                                             if peer else "per-step copies, forward_backward, all-reduce, update"),
+            "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e * per,
+                    "ms_per_step_min": min(blocks_e2e) * per, "ms_per_step_max": max(blocks_e2e) * per,
+                    "blocks": len(blocks_e2e),
+                    "api": ("Sequential.fit -> b200_net_fit_host on every rank: uploads of the next mini-batch overlap "
+                            "the current step" + ("" if world == 1 else "; the reduction over the replicas is inside the step"))
+                           if fit_ok else "per-step copies, forward_backward, NCCL all-reduce, update",
                     "h2d_bytes_per_step": BATCH * (IN_DIM + OUT_DIM) * 4,
                     "d2h_bytes_per_step": BATCH * OUT_DIM * 4},
             "gpu_launches": int(launches),
             "roofline": roofline,
             "kernels": kernels,
         }
+        if parity is not None:
+            line["parity"] = parity
         if cpu is not None:
             line["cpu_baseline"] = cpu
     if world > 1:
@@ -425,14 +484,68 @@ def run_b200(args, rank, world, local_rank):
         print(json.dumps(line), flush=True)
 
 
+def dp_parity(torch, dist, np, nw, ops, net, opt, dp_step, p0, rank, world, local_rank, ctx):
+    """Outside any timed region.  (a) After the timed steps every replica must hold the same
+    parameters, bit for bit.  (b) Two data-parallel steps from the initial weights against the same
+    two steps of a single GPU (rank 0) on the concatenated mini-batch of world x BATCH samples:
+    largest difference of any parameter tensor relative to its largest magnitude."""
+    from tiny_cnn_b200._lib import check
+    p_mine = torch.from_numpy(net.get_params()).cuda()
+    gathered = [torch.empty_like(p_mine) for _ in range(world)]
+    dist.all_gather(gathered, p_mine)
+    identical = all(torch.equal(gathered[0], g) for g in gathered)
+    # (b) restart every replica from the initial weights with a fresh optimizer
+    steps = 2
+    net.set_params(p0)
+    check(net.lib.b200_net_opt_reset(net.handle, 1))
+    xs, ts = synthetic_batches(steps, 7000 + rank)
+    x_d, t_d = torch.from_numpy(xs).cuda(), torch.from_numpy(ts).cuda()
+    x_buf, t_buf = torch.empty(BATCH, IN_DIM, device="cuda"), torch.empty(BATCH, OUT_DIM, device="cuda")
+    for s in range(steps):
+        x_buf.copy_(x_d[s])
+        t_buf.copy_(t_d[s])
+        dp_step(x_buf, t_buf)
+    ctx.sync()
+    p_dp = net.get_params()
+    p_all = torch.from_numpy(p_dp).cuda()
+    gathered = [torch.empty_like(p_all) for _ in range(world)]
+    dist.all_gather(gathered, p_all)
+    identical = identical and all(torch.equal(gathered[0], g) for g in gathered)
+    worst = None
+    if rank == 0:
+        big = nw.cifar10_net(local_rank).build(BATCH * world, ctx)
+        big.set_params(p0)
+        parts = [synthetic_batches(steps, 7000 + r) for r in range(world)]
+        for s in range(steps):
+            x = torch.from_numpy(np.concatenate([pr[0][s] for pr in parts])).cuda()
+            t = torch.from_numpy(np.concatenate([pr[1][s] for pr in parts])).cuda()
+            big.train_onebatch(opt, x, t, LOSS_CE)
+        ctx.sync()
+        p_one = big.get_params()
+        worst = 0.0
+        for off, ln in big.tensors():
+            a, b = p_dp[off:off + ln], p_one[off:off + ln]
+            worst = max(worst, float(np.abs(a - b).max() / max(float(np.abs(b).max()), 1e-30)))
+        big.close()
+    dist.barrier()
+    return {"replicas_identical": bool(identical), "vs_single_gpu": worst, "vs_single_gpu_tol": 1e-3,
+            "steps": steps,
+            "how": f"{steps} data-parallel adam steps from the initial weights on {world} x {BATCH} samples against "
+                   f"the same steps of one GPU on the concatenated {world * BATCH}-sample mini-batch: largest "
+                   "|difference| of a parameter tensor / its largest magnitude; replicas compared bit for bit "
+                   "after the timed steps and after these"}
+
+
 def cpu_baseline():
-    """The reference's CPU path on this box's host cores, on a bounded sample of the workload."""
+    """The reference's CPU path on this box's host cores, on a bounded sample of the workload:
+    backend_t::internal (the parity target) for about 10 s and, as an informational second column,
+    the reference's AVX kernels (backend_t::avx: its fastest shipped path for 5x5 convolutions)."""
     import numpy as np
     import oracle_lib as o
     from cases import hyper_for, xavier_params
     specs, keep = make_specs()
     arr = (type(specs[0]) * len(specs))(*specs)
-    x, t = synthetic_batches(1, 1000)
+    x, t = synthetic_batches(NB, 1000)
     hy = hyper_for(OPT_ADAM)
     ref = o.load_reference()
     if ref is None:
@@ -441,25 +554,39 @@ def cpu_baseline():
         net = orc.orc_net_create(arr, len(specs), sub)
         params = np.ctypeslib.as_array(orc.orc_net_params(net), shape=(orc.orc_net_param_count(net),))
         params[:] = xavier_params(specs, 42)
+        xs, ts = np.ascontiguousarray(x[0][:sub]), np.ascontiguousarray(t[0][:sub])
         t0 = time.perf_counter()
         n = 0
         while time.perf_counter() - t0 < 10.0:
-            orc.orc_net_train_step(net, o.p(x[0][:sub]), o.p(t[0][:sub]), sub, LOSS_CE, OPT_ADAM, C.byref(hy))
+            orc.orc_net_train_step(net, o.p(xs), o.p(ts), sub, LOSS_CE, OPT_ADAM, C.byref(hy))
             n += sub
         secs = time.perf_counter() - t0
         return {"value": n / secs, "unit": "samples/s", "cores": 1, "kind": "port",
                 "sample": f"{n} samples in steps of {sub} through the C restatement"}
-    h = ref.ref_net_create(arr, len(specs), 42)
-    ref.ref_net_set_params(h, o.p(xavier_params(specs, 42)))
-    ref.ref_net_fit(h, o.p(x[0]), o.p(t[0]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))  # warm-up
-    secs, steps = 0.0, 0
-    while secs < 10.0 and steps < 200:
-        secs += ref.ref_net_fit(h, o.p(x[0]), o.p(t[0]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))
-        steps += 1
-    cores = ref.ref_openmp_threads()
-    return {"value": BATCH * steps / secs, "unit": "samples/s", "cores": cores, "kind": "reference",
-            "sample": f"{steps} mini-batches of {BATCH} through network::fit (backend_t::internal, "
-                      f"OpenMP, {cores} threads)"}
+
+    def timed(lib, budget_s):
+        cores = lib.ref_set_threads(host_cores())
+        h = lib.ref_net_create(arr, len(specs), 42)
+        lib.ref_net_set_params(h, o.p(xavier_params(specs, 42)))
+        lib.ref_net_fit(h, o.p(x[0]), o.p(t[0]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))  # warm-up
+        secs, steps = 0.0, 0
+        while secs < budget_s and steps < 200:
+            i = (steps + 1) % NB
+            secs += lib.ref_net_fit(h, o.p(x[i]), o.p(t[i]), BATCH, 1, LOSS_CE, OPT_ADAM, C.byref(hy))
+            steps += 1
+        lib.ref_net_destroy(h)
+        return BATCH * steps / secs, steps, cores
+    value, steps, cores = timed(ref, 10.0)
+    out = {"value": value, "unit": "samples/s", "cores": cores, "kind": "reference",
+           "sample": f"{steps} mini-batches of {BATCH} through network::fit (backend_t::internal, "
+                     f"OpenMP, {cores} threads)"}
+    avx = o.load_reference_avx()
+    if avx is not None:
+        v, n, c = timed(avx, 5.0)
+        out["avx"] = {"value": v, "unit": "samples/s", "cores": c,
+                      "sample": f"{n} mini-batches of {BATCH} through network::fit, built -DCNN_USE_SSE -DCNN_USE_AVX "
+                                "-mavx with backend_t::avx (informational: not the parity target)"}
+    return out
 
 
 def main():

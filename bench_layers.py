@@ -1,8 +1,8 @@
 """Single-layer timing of the kernels through the C ABI.
 
-    python -m tiny_cnn_b200.kernel_bench --layer conv2 --batch 256 --reps 5 --passes fwd,bwd
-    python -m tiny_cnn_b200.kernel_bench --layer fc4096 --batch 1024        (MLP configuration layers)
-    python -m tiny_cnn_b200.kernel_bench --layer qconv --batch 128          (quantized configuration)
+    python bench_layers.py --layer conv2 --batch 256 --reps 5 --passes fwd,bwd
+    python bench_layers.py --layer fc4096 --batch 1024        (MLP configuration layers)
+    python bench_layers.py --layer qconv --batch 128          (quantized configuration)
 
 Prints one JSON line with the CUDA-event time per pass and the achieved
 TFLOP/s (2*B*oh*ow*oc*ic*kh*kw flop per pass: forward, dX and dW each).
@@ -16,8 +16,8 @@ import json
 
 import torch
 
-from . import ops
-from ._lib import check, ptr
+from tiny_cnn_b200 import ops
+from tiny_cnn_b200._lib import check, ptr
 
 # name -> (width, in_c, out_c, window), all stride 1, padding same
 LAYERS = {

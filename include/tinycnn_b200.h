@@ -178,7 +178,11 @@ B200_API int b200_conv2d_time_pass(b200_ctx *ctx, const b200_conv_desc *d, const
  *    error text, as is a filter tensor whose single partial row (out_c*in_c*k*k
  *    + out_c floats) exceeds the 4 Mi-float array.
  *  - The first call on each device looks up the array's device address; make
- *    that first call before any stream capture begins.
+ *    that first call before any stream capture begins.  With lazy module loading
+ *    (the default since CUDA 12.2) the library's device code, this array included,
+ *    is only placed on a GPU when it is first used there, so that first call is
+ *    also when the 16 MiB are taken: make it before the host hands the rest of
+ *    the memory to its own pools (or run with CUDA_MODULE_LOADING=EAGER).
  *  - All calls share the one array and leave their partial sums in it.  No
  *    call depends on what an earlier call left behind (every element that is
  *    read is written first), but two calls whose kernels overlap in time on the
@@ -508,17 +512,32 @@ B200_API int b200_net_forward_backward(b200_net *net, const float *x, const floa
  * a zero-filled buffer of b200_net_peer_reduce_bytes() bytes that all ranks have mapped
  * (peer / symmetric memory) and passes the `world` base addresses, as mapped in its own
  * process, to b200_net_peer_reduce_init.  From then on b200_net_train_step sums the
- * gradient bucket over the ranks between the backward pass and the update, inside its
- * captured graph: one kernel per GPU pushes its bucket into every rank's buffer over
- * NVLink, waits (bounded) for the others' and adds the `world` copies in rank order, so
- * the replicas stay bit-identical.  No 1/world factor.  Every rank must call the step the
- * same number of times.  b200_net_peer_reduce is the reduction alone (after
- * b200_net_forward_backward, before b200_net_update).
+ * gradient bucket over the ranks inside its captured graph: the gradients of every layer
+ * but the first one with parameters are pushed into every rank's buffer over NVLink from a
+ * side branch as soon as the backward pass has produced them; after the backward pass one
+ * kernel per GPU pushes the first layer's, waits (bounded) for the other ranks' pushes and
+ * adds the `world` copies in rank order, so the replicas stay bit-identical.  No 1/world
+ * factor.  Every rank must call the step the same number of times.
+ *
+ * `timeout_ms` bounds every wait for another rank (0 = 10 s).  A wait that runs out sets the
+ * context's error word (b200_ctx_sync then returns an error naming code 7) and the update
+ * of that step changes nothing on this rank; the other ranks may have finished the step, so
+ * the replicas differ from then on and the buffers' arrival counters are out of step: a
+ * timeout is terminal for this group of ranks (rebuild the nets, reload a checkpoint).
+ *
+ * b200_net_peer_reduce is the reduction alone (after b200_net_forward_backward, before
+ * b200_net_update).  b200_net_peer_push / b200_net_peer_sum are its two halves -- push the
+ * whole bucket to every rank without waiting; wait for every rank's push and sum -- for a
+ * caller that runs several ranks of one GPU one after the other (tests): kernels that wait
+ * for one another must never be separate launches on one GPU, so there every rank pushes
+ * before any rank sums.
  */
 B200_API size_t b200_net_peer_reduce_bytes(b200_net *net, int world);
 B200_API int b200_net_peer_reduce_init(b200_net *net, int rank, int world,
-                                       const unsigned long long *buffers);
+                                       const unsigned long long *buffers, int timeout_ms);
 B200_API int b200_net_peer_reduce(b200_net *net);
+B200_API int b200_net_peer_push(b200_net *net);
+B200_API int b200_net_peer_sum(b200_net *net);
 
 /*
  * The same step from HOST buffers (what network::train_onebatch does,

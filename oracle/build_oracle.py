@@ -9,6 +9,11 @@
                       the reference's OpenMP configuration: -O3 -fopenmp
                       -DCNN_USE_OMP, default serialization, no AVX macros, so
                       every kernel runs as backend_t::internal)
+                      and, from the same ref_shim.cpp with -DCNN_USE_SSE
+                      -DCNN_USE_AVX -mavx -DREF_ENGINE=core::backend_t::avx,
+                      oracle/_ref/libtinydnn_ref_avx.so: the reference's AVX
+                      kernels (5x5 convolutions, fully connected), only ever
+                      timed as an informational CPU column, never a parity target
 
 Outputs are git-ignored build products; no reference source is copied.
 """
@@ -21,10 +26,12 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent
-REF_ROOT = Path(os.environ.get("TINYDNN_REFERENCE", "/root/reference"))
+# the reference tree: beside this repository unless TINYDNN_REFERENCE says otherwise
+REF_ROOT = Path(os.environ.get("TINYDNN_REFERENCE", str(ROOT.parent / "reference")))
 ORACLE_SO = HERE / "liboracle.so"
 REF_DIR = HERE / "_ref"
 REF_SO = REF_DIR / "libtinydnn_ref.so"
+REF_AVX_SO = REF_DIR / "libtinydnn_ref_avx.so"
 
 
 def _run(cmd):
@@ -59,7 +66,7 @@ def build_reference(force: bool = False) -> Path | None:
     REF_DIR.mkdir(exist_ok=True)
     srcs = [HERE / "ref_shim.cpp", HERE / "ref_qfc.cpp", ROOT / "include" / "tinycnn_b200.h",
             HERE / "ref_stub" / "tiny_dnn" / "core" / "kernels" / "tiny_quantized_matmul_kernel.h"]
-    if not (force or _stale(REF_SO, srcs)):
+    if not (force or _stale(REF_SO, srcs) or _stale(REF_AVX_SO, srcs)):
         return REF_SO
     common = ["g++", "-std=c++14", "-O3", "-fopenmp", "-DCNN_USE_OMP", "-ffp-contract=off", "-fPIC",
               "-fvisibility=hidden", "-w", f"-I{ROOT / 'include'}"]
@@ -70,11 +77,18 @@ def build_reference(force: bool = False) -> Path | None:
     p2 = subprocess.Popen(common + [f"-I{HERE / 'ref_stub'}", f"-I{REF_ROOT}", "-c",
                                     str(HERE / "ref_qfc.cpp"), "-o", str(o2)],
                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    o3 = REF_DIR / "ref_shim_avx.o"
+    p3 = subprocess.Popen(common + ["-DCNN_USE_SSE", "-DCNN_USE_AVX", "-mavx",
+                                    "-DREF_ENGINE=core::backend_t::avx", f"-I{REF_ROOT}", "-c",
+                                    str(HERE / "ref_shim.cpp"), "-o", str(o3)],
+                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     out1, _ = p1.communicate()
     out2, _ = p2.communicate()
-    if p1.returncode or p2.returncode:
-        raise RuntimeError("reference build failed:\n" + out1 + out2)
+    out3, _ = p3.communicate()
+    if p1.returncode or p2.returncode or p3.returncode:
+        raise RuntimeError("reference build failed:\n" + out1 + out2 + out3)
     _run(["g++", "-shared", "-fopenmp", "-o", str(REF_SO), str(o1), str(o2)])
+    _run(["g++", "-shared", "-fopenmp", "-o", str(REF_AVX_SO), str(o3)])
     return REF_SO
 
 

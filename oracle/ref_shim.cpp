@@ -5,7 +5,8 @@
 // TEST INFRASTRUCTURE ONLY: it pins oracle.c (the C restatement) against the
 // real implementation, generates the golden fixtures, and serves as the timed
 // CPU baseline.  Every entry point drives the reference through its own layer
-// classes / free functions with engine backend_t::internal.
+// classes / free functions with engine REF_ENGINE (backend_t::internal unless
+// the build says otherwise).
 //
 // Flat-array conventions match oracle.c (B rows back to back, reference
 // layouts), so a test can call ref_X and orc_X with the same arguments.
@@ -23,6 +24,15 @@
 using namespace tiny_dnn;
 
 #define REF_API extern "C" __attribute__((visibility("default")))
+
+// Engine every layer is constructed with.  The default build is the parity
+// target, backend_t::internal; oracle/build_oracle.py compiles this file a
+// second time with -DREF_ENGINE=core::backend_t::avx (and the reference's AVX
+// macros) into a separate library that is only ever TIMED, as the reference's
+// fastest shipped CPU path for 5x5 convolutions (conv2d_op_avx.h:451-468).
+#ifndef REF_ENGINE
+#define REF_ENGINE core::backend_t::internal
+#endif
 
 namespace {
 
@@ -50,17 +60,32 @@ std::unique_ptr<convolutional_layer> make_conv(const b200_conv_desc *d) {
   return std::unique_ptr<convolutional_layer>(new convolutional_layer(
     d->in_w, d->in_h, d->k_w, d->k_h, d->in_c, d->out_c, make_table(d),
     d->pad_same ? padding::same : padding::valid, d->has_bias != 0, d->stride_w, d->stride_h,
-    d->dil_w, d->dil_h, core::backend_t::internal));
+    d->dil_w, d->dil_h, REF_ENGINE));
 }
 
 }  // namespace
 
-REF_API const char *ref_version() { return "tiny-dnn reference, backend_t::internal"; }
+#define REF_STR2(x) #x
+#define REF_STR(x) REF_STR2(x)
+REF_API const char *ref_version() { return "tiny-dnn reference, " REF_STR(REF_ENGINE); }
 
 REF_API int ref_openmp_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();
 #else
+  return 1;
+#endif
+}
+
+// Thread count of the OpenMP runtime inside this library.  A launcher may have
+// exported OMP_NUM_THREADS=1 (torch.distributed.run does); the timed baseline
+// asks for the host's cores explicitly instead of inheriting that.
+REF_API int ref_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
   return 1;
 #endif
 }
@@ -115,7 +140,7 @@ REF_API int ref_conv2d_bwd(const b200_conv_desc *d, const float *in, const float
 // ---------------------------------------------------------------- fully connected
 REF_API int ref_fc_fwd(int in_size, int out_size, const float *in, const float *W,
                        const float *bias, float *out, int B) {
-  fully_connected_layer l(in_size, out_size, bias != nullptr, core::backend_t::internal);
+  fully_connected_layer l(in_size, out_size, bias != nullptr, REF_ENGINE);
   tensor_t tin = to_tensor(in, B, in_size), tW = to_tensor(W, 1, (size_t)in_size * out_size),
            tb = to_tensor(bias, 1, out_size), tout(B, vec_t(out_size));
   std::vector<tensor_t *> ins = {&tin, &tW};
@@ -129,7 +154,7 @@ REF_API int ref_fc_fwd(int in_size, int out_size, const float *in, const float *
 
 REF_API int ref_fc_bwd(int in_size, int out_size, int has_bias, const float *in, const float *W,
                        const float *dout, float *din, float *dW_rows, float *db_rows, int B) {
-  fully_connected_layer l(in_size, out_size, has_bias != 0, core::backend_t::internal);
+  fully_connected_layer l(in_size, out_size, has_bias != 0, REF_ENGINE);
   size_t lenW = (size_t)in_size * out_size;
   tensor_t tin = to_tensor(in, B, in_size), tW = to_tensor(W, 1, lenW),
            tb = to_tensor(nullptr, 1, out_size), tout(B, vec_t(out_size));
@@ -155,7 +180,7 @@ std::unique_ptr<max_pooling_layer> make_maxpool(const b200_pool_desc *d, int cei
                                                 int pad_same) {
   return std::unique_ptr<max_pooling_layer>(new max_pooling_layer(
     d->in_w, d->in_h, d->in_c, d->pool_w, d->pool_h, d->stride_w, d->stride_h, ceil_mode != 0,
-    pad_same ? padding::same : padding::valid, core::backend_t::internal));
+    pad_same ? padding::same : padding::valid, REF_ENGINE));
 }
 }  // namespace
 
@@ -314,7 +339,7 @@ REF_API int ref_qconv2d_fwd(const b200_conv_desc *d, const float *in, const floa
                             const float *bias, float *out, int B) {
   quantized_convolutional_layer l(d->in_w, d->in_h, d->k_w, d->k_h, d->in_c, d->out_c,
                                   d->pad_same ? padding::same : padding::valid, d->has_bias != 0,
-                                  d->stride_w, d->stride_h, core::backend_t::internal);
+                                  d->stride_w, d->stride_h, REF_ENGINE);
   size_t in_len = (size_t)d->in_c * d->in_h * d->in_w;
   size_t out_len = l.out_shape()[0].size();
   if (out_len != (size_t)d->out_c * d->out_h * d->out_w) return 1;
@@ -347,17 +372,17 @@ void add_layer(RefNet *r, const b200_layer_spec &s, size_t prev_dim) {
       r->net << convolutional_layer(d->in_w, d->in_h, d->k_w, d->k_h, d->in_c, d->out_c,
                                     make_table(d), d->pad_same ? padding::same : padding::valid,
                                     d->has_bias != 0, d->stride_w, d->stride_h, d->dil_w, d->dil_h,
-                                    core::backend_t::internal);
+                                    REF_ENGINE);
       break;
     }
     case B200_LAYER_FC:
       r->net << fully_connected_layer(s.fc_in, s.fc_out, s.fc_has_bias != 0,
-                                      core::backend_t::internal);
+                                      REF_ENGINE);
       break;
     case B200_LAYER_MAXPOOL:
       r->net << max_pooling_layer(s.pool.in_w, s.pool.in_h, s.pool.in_c, s.pool.pool_w,
                                   s.pool.pool_h, s.pool.stride_w, s.pool.stride_h, false,
-                                  padding::valid, core::backend_t::internal);
+                                  padding::valid, REF_ENGINE);
       break;
     case B200_LAYER_AVGPOOL:
       r->net << average_pooling_layer(s.pool.in_w, s.pool.in_h, s.pool.in_c, s.pool.pool_w,
@@ -499,6 +524,94 @@ REF_API double ref_net_fit(void *h, const float *x, const float *t, int batch, i
   }
   auto t1 = std::chrono::steady_clock::now();
   return std::chrono::duration<double>(t1 - t0).count();
+}
+
+// Batch-summed gradients of `n` samples computed `chunk` samples at a time, the
+// protocol for mini-batches whose per-sample weight gradients do not fit in
+// host memory (B x len(W) floats): every chunk goes through the network's own
+// fprop / bprop<Loss>, its per-sample rows are merged by the reference's
+// edge::merge_grads (node.h:89-103), the merged chunks are added in sample
+// order, and the gradient tensors are cleared as layer::update_weight does
+// (layer.h:680).  With chunk == n this is exactly what train_onebatch hands
+// to the optimizer.  grads_out: flat, network order (W before b per layer);
+// out_out (optional): forward outputs of all n samples.  No weight changes.
+REF_API int ref_net_grads_chunked(void *h, const float *x, const float *t, int n, int chunk,
+                                  int loss_kind, float *grads_out, float *out_out) {
+  RefNet *r = static_cast<RefNet *>(h);
+  try {
+    r->net.set_netphase(net_phase::train);
+    for (size_t i = 0; i < r->net.depth(); ++i) r->net[i]->set_parallelize(true);
+    std::vector<vec_t> acc;
+    bool first = true;
+    vec_t diff;
+    for (int c0 = 0; c0 < n; c0 += chunk) {
+      int nb = std::min(chunk, n - c0);
+      // network::fprop / bprop index their arguments [sample][channel][feature] (nodes.h:288-303)
+      std::vector<tensor_t> in(nb, tensor_t(1)), tgt(nb, tensor_t(1));
+      for (int s = 0; s < nb; ++s) {
+        in[s][0].assign(x + (size_t)(c0 + s) * r->in_dim, x + (size_t)(c0 + s + 1) * r->in_dim);
+        tgt[s][0].assign(t + (size_t)(c0 + s) * r->out_dim, t + (size_t)(c0 + s + 1) * r->out_dim);
+      }
+      std::vector<tensor_t> out = r->net.fprop(in);
+      if (out_out)
+        for (int s = 0; s < nb; ++s)
+          std::copy(out[s][0].begin(), out[s][0].end(), out_out + (size_t)(c0 + s) * r->out_dim);
+      if (loss_kind == B200_LOSS_MSE)
+        r->net.bprop<mse>(out, tgt, std::vector<tensor_t>());
+      else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
+        r->net.bprop<cross_entropy>(out, tgt, std::vector<tensor_t>());
+      else
+        r->net.bprop<cross_entropy_multiclass>(out, tgt, std::vector<tensor_t>());
+      size_t k = 0;
+      for (size_t i = 0; i < r->net.depth(); ++i) {
+        layer *l = r->net[i];
+        auto types = l->in_types();
+        for (size_t j = 0; j < types.size(); ++j) {
+          if (!is_trainable_weight(types[j])) continue;
+          // a mini-batch smaller than an earlier one leaves stale (cleared) rows behind: harmless zeros
+          l->prev()[j]->merge_grads(&diff);
+          if (first) acc.push_back(diff);
+          else
+            for (size_t e = 0; e < diff.size(); ++e) acc[k][e] += diff[e];
+          ++k;
+        }
+        l->clear_grads();
+      }
+      first = false;
+    }
+    for (auto &a : acc) {
+      std::copy(a.begin(), a.end(), grads_out);
+      grads_out += a.size();
+    }
+  } catch (const std::exception &e) {
+    fprintf(stderr, "ref_net_grads_chunked: %s\n", e.what());
+    return 1;
+  }
+  return 0;
+}
+
+// optimizer::update per parameter tensor in network order with a flat gradient
+// (what nodes::update_weights -> layer::update_weight does after the merge).
+// The optimizer objects are the net's persistent ones (state carries on).
+REF_API int ref_net_apply_update(void *h, const float *grads, int opt_kind, const b200_opt_hyper *hy) {
+  RefNet *r = static_cast<RefNet *>(h);
+  r->o_adagrad.alpha = hy->alpha;
+  r->o_adam.alpha = hy->alpha;
+  r->o_adam.b1 = hy->b1;
+  r->o_adam.b2 = hy->b2;
+  r->o_momentum.alpha = hy->alpha;
+  r->o_momentum.mu = hy->mu;
+  r->o_momentum.lambda = hy->lambda;
+  optimizer *o = opt_kind == B200_OPT_ADAGRAD ? static_cast<optimizer *>(&r->o_adagrad)
+                 : opt_kind == B200_OPT_ADAM  ? static_cast<optimizer *>(&r->o_adam)
+                                              : static_cast<optimizer *>(&r->o_momentum);
+  for (size_t i = 0; i < r->net.depth(); ++i)
+    for (auto *w : r->net[i]->weights()) {
+      vec_t g(grads, grads + w->size());
+      o->update(g, *w, w->size() >= 512);  // layer.h:676
+      grads += w->size();
+    }
+  return 0;
 }
 
 REF_API void ref_net_adam_powers(void *h, float *b1_t, float *b2_t) {

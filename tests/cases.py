@@ -9,8 +9,60 @@ import numpy as np
 
 from tiny_cnn_b200._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_RELU,
                                 LAYER_SOFTMAX, LAYER_TANH, LayerSpec, OptHyper)
+from tiny_cnn_b200._lib import ConvDesc, PoolDesc
 from tiny_cnn_b200.network import LENET_TABLE
-from tiny_cnn_b200.ops import conv_params, hyper, maxpool_params
+
+
+# Descriptor arithmetic restated in Python, so that the fixture generator, the oracle tests and the
+# benchmark's CPU legs describe a network without loading the CUDA library (tests/test_abi.py checks
+# these against b200_conv_desc_init / b200_pool_desc_init).
+def _conv_out_length(n, k, stride, dil, same):
+    """conv_out_length (tiny_dnn/util/util.h:329-344)."""
+    return -(-n // stride) if same else -(-(n - dil * k + dil) // stride)
+
+
+def conv_params(in_w, in_h, in_c, k_w, k_h, out_c, pad_same=False, has_bias=True, stride_w=1,
+                stride_h=1, dil_w=1, dil_h=1, table=None, algo=0, input_is_padded=False) -> ConvDesc:
+    """conv_set_params (tiny_dnn/layers/convolutional_layer.h:404-438) into a b200_conv_desc."""
+    d = ConvDesc()
+    d.in_w, d.in_h, d.in_c = in_w, in_h, in_c
+    d.inp_w = in_w + k_w - 1 if pad_same else in_w
+    d.inp_h = in_h + k_h - 1 if pad_same else in_h
+    d.out_w = _conv_out_length(in_w, k_w, stride_w, dil_w, pad_same)
+    d.out_h = _conv_out_length(in_h, k_h, stride_h, dil_h, pad_same)
+    d.out_c, d.k_w, d.k_h = out_c, k_w, k_h
+    d.stride_w, d.stride_h, d.dil_w, d.dil_h = stride_w, stride_h, dil_w, dil_h
+    d.has_bias, d.pad_same = int(has_bias), int(pad_same)
+    d.algo, d.input_is_padded = algo, int(input_is_padded)
+    assert d.out_w > 0 and d.out_h > 0
+    if table is not None:
+        t = np.ascontiguousarray(np.asarray(table, dtype=np.uint8).reshape(in_c, out_c))
+        d._table_keepalive = t
+        d.tbl = t.ctypes.data_as(C.POINTER(C.c_uint8))
+    return d
+
+
+def maxpool_params(in_w, in_h, in_c, pool_w, pool_h=None, stride_w=None, stride_h=None,
+                   ceil_mode=False, pad_same=False) -> PoolDesc:
+    """pool_out_length (tiny_dnn/util/util.h:346-363) into a b200_pool_desc."""
+    pool_h = pool_w if pool_h is None else pool_h
+    stride_w = pool_w if stride_w is None else stride_w
+    stride_h = pool_h if stride_h is None else stride_h
+
+    def out_len(n, win, stride):
+        ln = n if pad_same else n - win + 1
+        tmp = np.float32(ln + stride - 1) / np.float32(stride)
+        return int(np.ceil(tmp) if ceil_mode else np.floor(tmp))
+    d = PoolDesc()
+    d.in_w, d.in_h, d.in_c = in_w, in_h, in_c
+    d.pool_w, d.pool_h, d.stride_w, d.stride_h = pool_w, pool_h, stride_w, stride_h
+    d.out_w, d.out_h = out_len(in_w, pool_w, stride_w), out_len(in_h, pool_h, stride_h)
+    assert d.out_w > 0 and d.out_h > 0
+    return d
+
+
+def hyper(alpha=0.01, b1=0.9, b2=0.999, b1_t=0.9, b2_t=0.999, mu=0.9, lambda_=0.0, eps=1e-8) -> OptHyper:
+    return OptHyper(alpha, b1, b2, b1_t, b2_t, mu, lambda_, eps)
 
 _rng_tbl = np.random.default_rng(5)
 RANDOM_TABLE_4x6 = (_rng_tbl.random((4, 6)) > 0.4).astype(np.uint8)
@@ -182,6 +234,9 @@ def build_net_specs(name):
     elif name == "mlp_small":
         L = [_fc(784, 96), _act(LAYER_RELU), _fc(96, 96), _act(LAYER_RELU), _fc(96, 10),
              _act(LAYER_SOFTMAX)]
+    elif name == "mlp":
+        L = [_fc(784, 4096), _act(LAYER_RELU), _fc(4096, 4096), _act(LAYER_RELU), _fc(4096, 10),
+             _act(LAYER_SOFTMAX)]
     elif name == "tiny_conv":
         L = [_conv(12, 12, 3, 2, 4, True), _act(LAYER_RELU), _pool(LAYER_MAXPOOL, 12, 12, 4, 2),
              _conv(6, 6, 3, 4, 5), _act(LAYER_TANH), _fc(80, 6), _act(LAYER_SOFTMAX)]
@@ -261,3 +316,89 @@ def merge_rows_np(rows):
     for r in rows[1:]:
         acc += r
     return acc
+
+
+# ---- benchmark configurations at their stated sizes -------------------------------------------
+# The reference's outputs for these are too large to commit whole; tests/golden/ref_fullsize.npz
+# keeps a digest of every tensor (strided samples, float64 sum, sum of magnitudes, largest
+# magnitude, per-row float64 sums) made by tests/golden/make_golden_fullsize.py.
+FULL_CONV_CASES = {  # single-layer sweep: 3x3, stride 1, same padding, batch 256
+    "sweep_56x56x64": dict(w=56, h=56, c=64, kw=3, kh=3, oc=64, same=True, bias=True, B=256, seed=301),
+    "sweep_28x28x128": dict(w=28, h=28, c=128, kw=3, kh=3, oc=128, same=True, bias=True, B=256, seed=302),
+    "sweep_14x14x256": dict(w=14, h=14, c=256, kw=3, kh=3, oc=256, same=True, bias=True, B=256, seed=303),
+}
+
+
+def gen_full_conv_inputs(c, d):
+    """x ~ N(0,1), W xavier-uniform, b ~ U(-0.1, 0.1), dy ~ N(0,1), drawn in float32."""
+    rng = np.random.default_rng(c["seed"])
+    B = c["B"]
+    x = rng.standard_normal((B, c["c"] * c["h"] * c["w"]), dtype=np.float32)
+    fan_in, fan_out = c["kw"] * c["kh"] * c["c"], c["kw"] * c["kh"] * c["oc"]
+    bound = np.float32(np.sqrt(6.0 / (fan_in + fan_out)))
+    W = (rng.random(c["oc"] * c["c"] * c["kh"] * c["kw"], dtype=np.float32) * 2 - 1) * bound
+    b = (rng.random(c["oc"], dtype=np.float32) * 2 - 1) * np.float32(0.1)
+    dy = rng.standard_normal((B, d.out_c * d.out_h * d.out_w), dtype=np.float32)
+    return x, W, b, dy
+
+
+FULL_NET_CASES = {
+    # CIFAR-10 net at the benchmarked batch, 3 adam steps
+    "cifar_adam_b256": dict(net="cifar", B=256, steps=3, seed=202, in_dim=3072, out_dim=10, loss=1, opt=1,
+                            t_lo=0.0, t_hi=1.0, chunk=256, xgen=lambda r, s: r.standard_normal(s)),
+    # MLP 784 -> 4096 -> 4096 -> 10, batch 1024, momentum; the reference cannot hold the per-sample
+    # weight gradients of one such mini-batch (1024 x 16.8 M floats), so its gradients are computed
+    # 16 samples at a time and the merged chunks added in order
+    "mlp_momentum_b1024": dict(net="mlp", B=1024, steps=2, seed=204, in_dim=784, out_dim=10, loss=1, opt=2,
+                               t_lo=0.0, t_hi=1.0, chunk=16, xgen=lambda r, s: r.uniform(0, 1, s)),
+}
+
+FULL_Q_CASE = dict(w=28, h=28, c=32, kw=5, kh=5, oc=64, B=128, seed=505, fc_out=256)
+
+
+def gen_full_q_inputs():
+    """Quantized-inference configuration: x ~ U[-1,1], conv W ~ U[-0.5,0.5], conv bias zero or
+    U[-0.1,0.1], fc W ~ U[-0.5,0.5], fc bias ~ U[-0.1,0.1]."""
+    c = FULL_Q_CASE
+    rng = np.random.default_rng(c["seed"])
+    x = rng.uniform(-1, 1, (c["B"], c["c"] * c["h"] * c["w"])).astype(np.float32)
+    W = rng.uniform(-0.5, 0.5, c["oc"] * c["c"] * c["kh"] * c["kw"]).astype(np.float32)
+    biases = {"bias0": np.zeros(c["oc"], np.float32),
+              "bias_u": rng.uniform(-0.1, 0.1, c["oc"]).astype(np.float32)}
+    Wf = rng.uniform(-0.5, 0.5, 9216 * c["fc_out"]).astype(np.float32)
+    bf = rng.uniform(-0.1, 0.1, c["fc_out"]).astype(np.float32)
+    return x, W, biases, Wf, bf
+
+
+def digest(a, stride=101):
+    """What the full-size fixture keeps of a tensor."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    flat = a.ravel()
+    d64 = flat.astype(np.float64)
+    out = {"samples": flat[::stride].copy(),
+           "stats": np.array([d64.sum(), np.abs(d64).sum(), np.abs(d64).max() if flat.size else 0.0])}
+    if a.ndim == 2 and a.shape[0] > 1:
+        out["row_sums"] = a.astype(np.float64).sum(axis=1)
+    return out
+
+
+def check_digest(got, gold, key, tol, stride=101):
+    """Compare a tensor with its stored digest: samples within tol of the tensor's largest
+    magnitude, total and per-row sums within tol of the corresponding sum of magnitudes."""
+    got = np.ascontiguousarray(got, dtype=np.float32)
+    samples, stats = gold[f"{key}/samples"], gold[f"{key}/stats"]
+    s, abs_s, mx = (float(v) for v in stats)
+    mine = got.ravel()[::stride]
+    assert mine.shape == samples.shape, f"{key}: {mine.shape} samples vs {samples.shape}"
+    err = np.abs(mine.astype(np.float64) - samples.astype(np.float64))
+    worst = float(err.max()) if err.size else 0.0
+    assert worst <= tol * max(mx, 1e-30), f"{key}: sample off by {worst:g} (largest magnitude {mx:g}, tol {tol:g})"
+    g64 = got.astype(np.float64)
+    assert abs(float(g64.sum()) - s) <= tol * max(abs_s, 1e-30), \
+        f"{key}: sum {float(g64.sum())!r} vs {s!r} (sum of magnitudes {abs_s:g})"
+    if f"{key}/row_sums" in gold:
+        rows = gold[f"{key}/row_sums"]
+        row_abs = np.abs(g64).sum(axis=1)
+        bad = np.abs(g64.sum(axis=1) - rows) > tol * np.maximum(row_abs, 1e-30)
+        assert not bad.any(), f"{key}: {int(bad.sum())} row sums differ beyond {tol:g}"
+    return worst / max(mx, 1e-30)

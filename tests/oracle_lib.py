@@ -62,6 +62,7 @@ ORACLE_SIGS = {
 REF_SIGS = {
     "ref_version": (C.c_char_p, []),
     "ref_openmp_threads": (_i, []),
+    "ref_set_threads": (_i, [_i]),
     "ref_conv2d_fwd": (_i, [_cd, _vp, _vp, _vp, _vp, _i]),
     "ref_conv2d_bwd": (_i, [_cd, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "ref_fc_fwd": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i]),
@@ -86,6 +87,8 @@ REF_SIGS = {
     "ref_net_predict": (_i, [_vp, _vp, _vp, _i]),
     "ref_net_fit": (C.c_double, [_vp, _vp, _vp, _i, _i, _i, _i, _oh]),
     "ref_net_adam_powers": (None, [_vp, _fp, _fp]),
+    "ref_net_grads_chunked": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
+    "ref_net_apply_update": (_i, [_vp, _vp, _i, _oh]),
     "ref_time_conv": (C.c_double, [_cd, _vp, _vp, _vp, _vp, _i, _i, _i]),
 }
 
@@ -124,6 +127,21 @@ def load_reference():
             return None
         _ref = _bind(path, REF_SIGS)
     return _ref
+
+
+_ref_avx = None
+
+
+def load_reference_avx():
+    """The reference compiled with its AVX kernels and backend_t::avx (timed only), or None."""
+    global _ref_avx
+    if _ref_avx is None:
+        path = ROOT / "oracle" / "_ref" / "libtinydnn_ref_avx.so"
+        if not path.exists():
+            return None
+        sigs = {k: v for k, v in REF_SIGS.items() if k != "ref_qfc_fwd"}
+        _ref_avx = _bind(path, sigs)
+    return _ref_avx
 
 
 def p(a):

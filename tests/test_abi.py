@@ -65,6 +65,30 @@ def test_pool_descriptor_matches_reference_shape_rules():
     assert (d.out_w, d.out_h) == (3, 3)
 
 
+def test_python_descriptor_restatement_equals_the_library():
+    """tests/cases.py restates the descriptor arithmetic so that fixtures and CPU baselines need no
+    CUDA library; it must agree with b200_conv_desc_init / b200_pool_desc_init field for field."""
+    import cases
+    lib = L.load()
+    skip = {"tbl", "algo", "input_is_padded"}
+    for c in list(cases.CONV_CASES.values()) + list(cases.QCONV_CASES.values()):
+        d = L.ConvDesc()
+        assert lib.b200_conv_desc_init(C.byref(d), c["w"], c["h"], c["c"], c["kw"], c["kh"], c["oc"],
+                                       int(c["same"]), int(c["bias"]), c.get("sw", 1), c.get("sh", 1),
+                                       c.get("dw", 1), c.get("dh", 1)) == 0
+        p = cases.conv_desc(c)
+        for name, _ in L.ConvDesc._fields_:
+            if name not in skip:
+                assert getattr(d, name) == getattr(p, name), (c, name)
+    for c in list(cases.MAXPOOL_CASES.values()) + list(cases.AVGPOOL_CASES.values()):
+        d = L.PoolDesc()
+        assert lib.b200_pool_desc_init(C.byref(d), c["w"], c["h"], c["c"], c["pw"], c["ph"], c["sw"], c["sh"],
+                                       int(c.get("ceil", 0)), int(c.get("same", 0))) == 0
+        p = cases.pool_desc(c)
+        for name, _ in L.PoolDesc._fields_:
+            assert getattr(d, name) == getattr(p, name), (c, name)
+
+
 def test_no_cpu_fallback():
     """Without a GPU the context cannot be created and says why."""
     lib = L.load()

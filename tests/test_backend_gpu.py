@@ -27,7 +27,8 @@ def test_backend_b200_inside_tiny_dnn():
 
 def test_overlay_patches_fit_the_reference(tmp_path):
     """Where the reference tree is present, every anchored edit of the overlay applies."""
-    ref = Path("/root/reference")
+    import os
+    ref = Path(os.environ.get("TINYDNN_REFERENCE", str(ROOT.parent / "reference")))
     if not (ref / "tiny_dnn" / "tiny_dnn.h").exists():
         pytest.skip("reference tree not present")
     from tiny_cnn_b200.host.make_overlay import PATCHES, make_overlay

@@ -1,0 +1,59 @@
+"""The C restatement against the reference's digests at the benchmarked size: the CIFAR-10 net at
+batch 256, first adam step -- forward outputs, batch-summed gradients and updated weights equal the
+unmodified reference's bit for bit (the samples the fixture keeps), and the quantized
+configuration at batch 128 (stride 2 + fully connected) byte for byte."""
+import ctypes as C
+import hashlib
+from pathlib import Path
+
+import numpy as np
+
+import oracle_lib as o
+from cases import (FULL_NET_CASES, FULL_Q_CASE, build_net_specs, conv_params, gen_full_q_inputs, gen_net_data,
+                   hyper_for, net_layout, xavier_params)
+from tiny_cnn_b200._lib import LayerSpec
+
+GOLD = Path(__file__).parent / "golden"
+
+
+def test_oracle_cifar_batch256_first_step_equals_reference(oracle):
+    full = np.load(GOLD / "ref_fullsize.npz")
+    name = "cifar_adam_b256"
+    c = FULL_NET_CASES[name]
+    specs, keep = build_net_specs(c["net"])
+    layout, n = net_layout(specs)
+    B = c["B"]
+    arr = (LayerSpec * len(specs))(*specs)
+    net = oracle.orc_net_create(arr, len(specs), B)
+    params = np.ctypeslib.as_array(oracle.orc_net_params(net), shape=(n,))
+    params[:] = xavier_params(specs, c["seed"])
+    x, t = gen_net_data(c)
+    xs, ts = np.ascontiguousarray(x[:B]), np.ascontiguousarray(t[:B])
+    h = hyper_for(c["opt"])
+    oracle.orc_net_forward(net, o.p(xs), B)
+    out = np.ctypeslib.as_array(oracle.orc_net_output(net), shape=(B, c["out_dim"])).copy()
+    assert np.array_equal(out, full[f"net/{name}/step0/out"])
+    oracle.orc_net_backward(net, o.p(xs), o.p(ts), c["loss"], B)
+    g = np.ctypeslib.as_array(oracle.orc_net_grads(net), shape=(n,)).copy()
+    oracle.orc_net_update(net, c["opt"], C.byref(h))
+    for ti, (off, ln, _, _, _) in enumerate(layout):
+        assert np.array_equal(g[off:off + ln][::3], full[f"net/{name}/step0/grad{ti}/samples"]), f"grad {ti}"
+        assert np.array_equal(params[off:off + ln][::3], full[f"net/{name}/step0/param{ti}/samples"]), f"param {ti}"
+    oracle.orc_net_destroy(net)
+
+
+def test_oracle_quantized_batch128_equals_reference(oracle):
+    full = np.load(GOLD / "ref_fullsize.npz")
+    c = FULL_Q_CASE
+    x, W, biases, Wf, bf = gen_full_q_inputs()
+    B = c["B"]
+    bias = biases["bias_u"]
+    d = conv_params(c["w"], c["h"], c["c"], c["kw"], c["kh"], c["oc"], False, True, 2, 2)
+    y = o.f32(B, d.out_c * d.out_h * d.out_w)
+    assert oracle.orc_qconv2d_fwd(C.byref(d), o.p(x), o.p(W), o.p(bias), o.p(y), B, None, None) == 0
+    sha = np.frombuffer(hashlib.sha256(y.tobytes()).digest(), dtype=np.uint8)
+    assert np.array_equal(sha, full["quant/bias_u/conv_s2/sha256"])
+    z = o.f32(B, c["fc_out"])
+    assert oracle.orc_qfc_fwd(9216, c["fc_out"], o.p(y), o.p(Wf), o.p(bf), o.p(z), B) == 0
+    sha = np.frombuffer(hashlib.sha256(z.tobytes()).digest(), dtype=np.uint8)
+    assert np.array_equal(sha, full["quant/bias_u/fc/sha256"])

@@ -142,8 +142,10 @@ SIGNATURES = {
     "b200_net_train_step": (_i, [_vp, _vp, _vp, _i, _i, _i, _oh]),
     "b200_net_forward_backward": (_i, [_vp, _vp, _vp, _i, _i]),
     "b200_net_peer_reduce_bytes": (_sz, [_vp, _i]),
-    "b200_net_peer_reduce_init": (_i, [_vp, _i, _i, C.POINTER(C.c_ulonglong)]),
+    "b200_net_peer_reduce_init": (_i, [_vp, _i, _i, C.POINTER(C.c_ulonglong), _i]),
     "b200_net_peer_reduce": (_i, [_vp]),
+    "b200_net_peer_push": (_i, [_vp]),
+    "b200_net_peer_sum": (_i, [_vp]),
     "b200_net_train_step_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _oh, _vp]),
     "b200_net_fit_host": (_i, [_vp, _vp, _vp, C.c_longlong, _i, _i, _i, _i, _oh, _vp]),
     "b200_net_adam_powers": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),

@@ -231,13 +231,19 @@ int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const floa
 struct PeerReduce {
   int rank = 0, world = 0;
   long long n = 0;
+  long long split = 0;           // [split, n) is pushed early, [0, split) by the summing kernel
+  unsigned long long timeout_ns = 0;
   float **bases_dev = nullptr;   // [world] every rank's buffer as mapped in this process
   unsigned *step_dev = nullptr;  // reductions done so far
 };
 size_t peer_reduce_bytes(long long n, int world);
-int peer_reduce_init(b200_ctx *ctx, PeerReduce *pr, long long n, int rank, int world,
-                     const unsigned long long *bases);
+// `timeout_ms` bounds every wait of the summing kernel (0 = 10 s)
+int peer_reduce_init(b200_ctx *ctx, PeerReduce *pr, long long n, long long split, int rank, int world,
+                     const unsigned long long *bases, int timeout_ms);
 void peer_reduce_free(PeerReduce *pr);
+int peer_reduce_push_early(b200_ctx *ctx, const PeerReduce *pr, float *grads);
+int peer_reduce_push_all(b200_ctx *ctx, const PeerReduce *pr, float *grads);
+int peer_reduce_finish(b200_ctx *ctx, const PeerReduce *pr, float *grads, int late_pushed);
 int peer_reduce_run(b200_ctx *ctx, const PeerReduce *pr, float *grads);
 
 int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
@@ -277,10 +283,13 @@ int opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *gr
 // table pow_tab[2*t] = b1_t, pow_tab[2*t+1] = b2_t and advanced afterwards by
 // opt_advance_powers (one sequential float multiply per update call, which is
 // how adam::update evolves them).
+// `skip_if` (may be nullptr): device word; when it is non-zero as the kernel starts, nothing is
+// changed (a reduction over the replicas that gave up leaves the parameters of the step before).
 int opt_update_segments(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *grads,
                         float *W, float *s0, float *s1, const OptSegment *segs_dev,
-                        int n_segs, size_t total, float *pow_tab);
-int opt_advance_powers(b200_ctx *ctx, float *pow_tab, int n_tensors, float b1, float b2);
+                        int n_segs, size_t total, float *pow_tab, const int *skip_if = nullptr);
+int opt_advance_powers(b200_ctx *ctx, float *pow_tab, int n_tensors, float b1, float b2,
+                       const int *skip_if = nullptr);
 
 int qconv_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
               const float *bias, float *out, int B);

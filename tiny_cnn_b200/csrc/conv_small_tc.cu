@@ -146,19 +146,19 @@ __global__ void __launch_bounds__(TFS_THREADS, 1)
 
   if (warp == W_TMA && lane == 0) {
     // ---- TMA producer: the raw input rows of each step -------------------------------------------
-    long long w = 0, t0 = clock64(), tq;
+    long long w = 0, t0 = tc_clock(), tq;
     StepPos pos;
     pos.init(s_begin, a.nxb, a.nyb);
     for (int s = s_begin; s < s_end; ++s, pos.next(a.nxb, a.nyb)) {
       const uint32_t i = s - s_begin, st = i % TFS_STAGES, use = i / TFS_STAGES;
-      tq = clock64();
+      tq = tc_clock();
       if (use > 0 && !mbar_wait_bounded(&raw_empty[st], (use - 1) & 1)) {
         failed = true;
         break;
       }
-      w += clock64() - tq;
+      w += tc_clock() - tq;
       if (a.dbg && s == s_end - 1) {
-        a.dbg[blockIdx.x * 12 + 0] = clock64() - t0;
+        a.dbg[blockIdx.x * 12 + 0] = tc_clock() - t0;
         a.dbg[blockIdx.x * 12 + 1] = w;
       }
       const int xs = (pos.xb * TFS_PX - a.pad_l) & ~3;  // aligned start column (floor to a multiple of 4)
@@ -170,23 +170,23 @@ __global__ void __launch_bounds__(TFS_THREADS, 1)
     // ---- MMA issuer ------------------------------------------------------------------------------
     const uint32_t idesc1 = umma_idesc_tf32(128, a.OCp), idesc2 = umma_idesc_tf32(128, 2 * a.OCp);
     const uint64_t b0 = umma_desc(smem_u32(wt), 16, 1024, 2);
-    long long w = 0, w2 = 0, t0 = clock64(), tq;
+    long long w = 0, w2 = 0, t0 = tc_clock(), tq;
     for (int s = s_begin; s < s_end; ++s) {
       const uint32_t i = s - s_begin, ab = i & 1;
-      tq = clock64();
+      tq = tc_clock();
       if (!mbar_wait_bounded(&a_full[ab], (i >> 1) & 1)) {
         failed = true;
         break;
       }
-      w += clock64() - tq;
-      tq = clock64();
+      w += tc_clock() - tq;
+      tq = tc_clock();
       if (i >= 2 && !mbar_wait_bounded(&acc_empty[ab], ((i >> 1) - 1) & 1)) {
         failed = true;
         break;
       }
-      w2 += clock64() - tq;
+      w2 += tc_clock() - tq;
       if (a.dbg && s == s_end - 1) {
-        a.dbg[blockIdx.x * 12 + 2] = clock64() - t0;
+        a.dbg[blockIdx.x * 12 + 2] = tc_clock() - t0;
         a.dbg[blockIdx.x * 12 + 3] = w;
         a.dbg[blockIdx.x * 12 + 4] = w2;
       }
@@ -243,22 +243,22 @@ __global__ void __launch_bounds__(TFS_THREADS, 1)
       const int kq = part + j * NPART;
       ko[j] = kq < nkq ? *reinterpret_cast<const int4 *>(koff + kq * 4) : make_int4(-1, -1, -1, -1);
     }
-    long long w = 0, w2 = 0, t0 = clock64(), tq;
+    long long w = 0, w2 = 0, t0 = tc_clock(), tq;
     int xb = s_begin % a.nxb;
     for (int s = s_begin; s < s_end; ++s, xb = (xb + 1 == a.nxb) ? 0 : xb + 1) {
       const uint32_t i = s - s_begin, st = i % TFS_STAGES, use = i / TFS_STAGES, ab = i & 1;
-      tq = clock64();
+      tq = tc_clock();
       if (!mbar_wait_bounded(&tma_full[st], use & 1)) {
         failed = true;
         break;
       }
-      w += clock64() - tq;
-      tq = clock64();
+      w += tc_clock() - tq;
+      tq = tc_clock();
       if (i >= 2 && !mbar_wait_bounded(&a_empty[ab], ((i >> 1) - 1) & 1)) {
         failed = true;
         break;
       }
-      w2 += clock64() - tq;
+      w2 += tc_clock() - tq;
       tc_fence_after();
       uint8_t *sp = stage0 + (size_t)st * STAGE;
       const int x0 = xb * TFS_PX;
@@ -296,26 +296,26 @@ __global__ void __launch_bounds__(TFS_THREADS, 1)
       }
     }
     if (a.dbg && ct == 0) {
-      a.dbg[blockIdx.x * 12 + 5] = clock64() - t0;
+      a.dbg[blockIdx.x * 12 + 5] = tc_clock() - t0;
       a.dbg[blockIdx.x * 12 + 6] = w;
       a.dbg[blockIdx.x * 12 + 7] = w2;
     }
   } else if (warp < TFS_EPI_WARPS) {
     // ---- epilogue: hi + lo parts, bias, activation, store ------------------------------------------
     const size_t plane = (size_t)a.OH * a.OW;
-    long long w = 0, wl = 0, t0 = clock64(), tq;
+    long long w = 0, wl = 0, t0 = tc_clock(), tq;
     StepPos pos;
     pos.init(s_begin, a.nxb, a.nyb);
     for (int s = s_begin; s < s_end; ++s, pos.next(a.nxb, a.nyb)) {
       const uint32_t i = s - s_begin, ab = i & 1;
-      tq = clock64();
+      tq = tc_clock();
       if (!mbar_wait_bounded(&acc_full[ab], (i >> 1) & 1)) {
         failed = true;
         break;
       }
-      w += clock64() - tq;
+      w += tc_clock() - tq;
       if (a.dbg && tid == 0 && s == s_end - 1) {
-        a.dbg[blockIdx.x * 12 + 8] = clock64() - t0;
+        a.dbg[blockIdx.x * 12 + 8] = tc_clock() - t0;
         a.dbg[blockIdx.x * 12 + 9] = w;
       }
       tc_fence_after();
@@ -331,7 +331,7 @@ __global__ void __launch_bounds__(TFS_THREADS, 1)
       }
       for (int c0 = cfirst; c0 < a.OCp; c0 += 32) {
         uint32_t v[16], w[16];
-        tq = clock64();
+        tq = tc_clock();
         tmem_ld16_nowait(tacc + (uint32_t)c0, v);
         tmem_ld16_nowait(tacc + (uint32_t)(a.OCp + c0), w);
         tmem_ld_wait();
@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(TFS_THREADS, 1)
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[ab]);
         }
-        wl += clock64() - tq;
+        wl += tc_clock() - tq;
         float bv[16];
 #pragma unroll
         for (int q = 0; q < 4; ++q)
@@ -450,10 +450,13 @@ int conv_fwd_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const floa
   B200_REQUIRE(smem <= (size_t)ctx->smem_optin, "conv_fwd_small: the tiles do not fit shared memory");
   B200_CUDA(cudaFuncSetAttribute(conv_fwd_small_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   a.dbg = nullptr;
+#ifdef B200_TC_TIMING
   static const bool timing = getenv("B200_TC_TIMING") != nullptr;
   if (timing) B200_CUDA(cudaMalloc(&a.dbg, (size_t)a.nblocks * 12 * sizeof(long long)));
+#endif
   conv_fwd_small_tc_kernel<<<a.nblocks, TFS_THREADS, smem, ctx->stream>>>(x_map, a);
   B200_LAUNCHED();
+#ifdef B200_TC_TIMING
   if (timing) {  // diagnostic: cycles of the four roles and of their waits, averaged over blocks
     std::vector<long long> h((size_t)a.nblocks * 12);
     B200_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -467,6 +470,7 @@ int conv_fwd_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const floa
             "accumulator %.0f), converter %.0f (wait tma %.0f, tile free %.0f), epilogue %.0f (wait %.0f, tmem loads %.0f)\n",
             (double)a.nsteps / a.nblocks, s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], s[8], s[9], s[10]);
   }
+#endif
   return 0;
 }
 

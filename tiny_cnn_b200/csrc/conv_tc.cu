@@ -332,7 +332,14 @@ struct TcConvArgs {
   int nf;              // filter ring stages
   int nb;              // accumulator buffers in tensor memory (1 or 2)
   int tmem_cols;       // allocated columns (power of two >= nb * groups * KH * gs)
-  long long *dbg;      // optional [grid][8] cycle counters (B200_TC_TIMING=1), else nullptr
+  // Image-aligned tiles (images whose height H divides the 16 tile rows and equals the output
+  // height): a tile holds the H rows of 16 / H whole images, loaded through a 4D tensor map that
+  // skips the zero rows between images, and the epilogue leaves out the window rows that fall
+  // outside the image instead of reading zeros.  Every one of the 16 tile rows is then an output
+  // row -- no tile overlap, no padding rows through the tensor cores.
+  int aligned;         // 0: tiles of 16 - (KH-1) output rows that overlap by KH-1 input rows
+  int img_h, ipt;      // aligned: rows per image, images per tile
+  long long *dbg;      // [grid][8] cycle counters in a build with -DB200_TC_TIMING, else nullptr
 };
 
 __global__ void __launch_bounds__(TCV_THREADS, 1)
@@ -385,6 +392,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     for (int unit = blockIdx.x; unit < nunits && !failed; unit += gridDim.x) {
       const int tile = unit / a.groups, grp = unit - tile * a.groups;
       const int x0 = (tile % a.tiles_x) * TCV_TILE_COLS, r0 = (tile / a.tiles_x) * TR - a.pad_t;
+      const int img0 = (tile / a.tiles_x) * a.ipt;  // aligned tiles: first image of the tile
       for (int slab = 0; slab < a.slabs && !failed; ++slab, ++u) {
         const uint32_t hb = u % a.nh, use = u / a.nh;
         if (use > 0 && !mbar_wait_bounded(&halo_empty[hb], (use - 1) & 1)) {
@@ -393,8 +401,13 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
         }
         uint8_t *h = halo + (size_t)hb * 2 * HB;
         mbar_expect_tx(&halo_full[hb], 2 * HB);
-        tma_load_3d(h, &in_hi, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
-        tma_load_3d(h + HB, &in_lo, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
+        if (a.aligned) {
+          tma_load_4d(h, &in_hi, slab * 32, x0 - a.pad_l, 0, img0, &halo_full[hb]);
+          tma_load_4d(h + HB, &in_lo, slab * 32, x0 - a.pad_l, 0, img0, &halo_full[hb]);
+        } else {
+          tma_load_3d(h, &in_hi, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
+          tma_load_3d(h + HB, &in_lo, slab * 32, x0 - a.pad_l, r0, &halo_full[hb]);
+        }
         for (int s = 0; s < 2 * a.KW; ++s, ++f) {  // per kx: the hi tile, then the lo tile
           const uint32_t fs = f % a.nf, fuse = f / a.nf;
           if (fuse > 0 && !mbar_wait_bounded(&filt_empty[fs], (fuse - 1) & 1)) {
@@ -411,25 +424,25 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     // ---- MMA issuer -----------------------------------------------------------------------
     const uint32_t idesc = umma_idesc_tf32(128, Ng);
     uint32_t u = 0, f = 0, it = 0;
-    long long w_acc = 0, w_halo = 0, w_filt = 0, t_begin = clock64(), tq;
+    long long w_acc = 0, w_halo = 0, w_filt = 0, t_begin = tc_clock(), tq;
     for (int unit = blockIdx.x; unit < nunits && !failed; unit += gridDim.x, ++it) {
       const uint32_t ab = it % a.nb, ause = it / a.nb;
-      tq = clock64();
+      tq = tc_clock();
       if (ause > 0 && !mbar_wait_bounded(&acc_empty[ab], (ause - 1) & 1)) {
         failed = true;
         break;
       }
-      w_acc += clock64() - tq;
+      w_acc += tc_clock() - tq;
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + ab * (uint32_t)CB;
       for (int slab = 0; slab < a.slabs && !failed; ++slab, ++u) {
         const uint32_t hb = u % a.nh;
-        tq = clock64();
+        tq = tc_clock();
         if (!mbar_wait_bounded(&halo_full[hb], (u / a.nh) & 1)) {
           failed = true;
           break;
         }
-        w_halo += clock64() - tq;
+        w_halo += tc_clock() - tq;
         tc_fence_after();
         const uint32_t hbase = smem_u32(halo + (size_t)hb * 2 * HB);
         for (int kx = 0; kx < a.KW && !failed; ++kx) {
@@ -439,12 +452,12 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
             const uint32_t d = tmem_d;
             for (int part = 0; part < 2; ++part, ++f) {  // the hi filter tile, then the lo tile
               const uint32_t fs = f % a.nf;
-              tq = clock64();
+              tq = tc_clock();
               if (!mbar_wait_bounded(&filt_full[fs], (f / a.nf) & 1)) {
                 failed = true;
                 break;
               }
-              w_filt += clock64() - tq;
+              w_filt += tc_clock() - tq;
               tc_fence_after();
               const uint32_t bbase = smem_u32(filt + (size_t)fs * FB);
 #pragma unroll
@@ -469,7 +482,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     }
     if (a.dbg) {
       long long *d = a.dbg + (size_t)blockIdx.x * 8;
-      d[0] = clock64() - t_begin;
+      d[0] = tc_clock() - t_begin;
       d[1] = w_acc;
       d[2] = w_halo;
       d[3] = w_filt;
@@ -480,13 +493,13 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     const int m = warp * 32 + lane, r = m >> 3, dx = m & 7;
     const size_t plane = (size_t)a.OH * a.OW;
     uint32_t half = 0;  // exchange buffer half in use
-    long long w_full = 0, t_begin = clock64(), tq;
+    long long w_full = 0, t_begin = tc_clock(), tq;
     for (int unit = blockIdx.x; unit < nunits; unit += gridDim.x, ++it) {
       const int tile = unit / a.groups, grp = unit - tile * a.groups;
       const uint32_t ab = it % a.nb;
-      tq = clock64();
+      tq = tc_clock();
       if (!mbar_wait_bounded(&acc_full[ab], (it / a.nb) & 1)) failed = true;
-      w_full += clock64() - tq;
+      w_full += tc_clock() - tq;
       // every epilogue thread takes part in the named barriers below, so leave together
       {
         int any;
@@ -502,33 +515,54 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
       }
       tc_fence_after();
       const int x = (tile % a.tiles_x) * TCV_TILE_COLS + dx;
-      const int t = (tile / a.tiles_x) * TR + r;  // output tall row this thread owns (if r < TR)
-      const int b = t / a.period, y = t - b * a.period;
-      const bool valid = r < TR && b < a.B && y < a.OH && x < a.OW;
+      // the output row this thread owns, and the tile rows [row_lo, row_hi) whose window-row
+      // blocks may be added to it
+      int b, y, row_lo, row_hi, ky_own;
+      bool valid;
+      if (a.aligned) {
+        const int bi = r / a.img_h;
+        y = r - bi * a.img_h;
+        b = (tile / a.tiles_x) * a.ipt + bi;
+        valid = b < a.B && x < a.OW;
+        row_lo = bi * a.img_h;          // rows of other images (or outside the image) are not read:
+        row_hi = row_lo + a.img_h;      // they stand for the zero padding above and below
+        ky_own = a.pad_t;               // input row r itself carries window row pad_t of output row r
+      } else {
+        const int t = (tile / a.tiles_x) * TR + r;  // output tall row (if r < TR)
+        b = t / a.period;
+        y = t - b * a.period;
+        valid = r < TR && b < a.B && y < a.OH && x < a.OW;
+        row_lo = 0;
+        row_hi = TCV_TILE_ROWS;
+        ky_own = 0;
+      }
       float *obase = a.out + ((size_t)b * a.N * a.OH + y) * a.OW + x;
       const uint32_t tbase = tmem_base + ((uint32_t)(warp * 32) << 16) + ab * (uint32_t)CB;
       {
         for (int c0 = 0; c0 < a.gs; c0 += 16) {
           float acc[16];
-          tmem_ld16(tbase + (uint32_t)c0, acc);
-          for (int ky = 1; ky < a.KH; ++ky) {
+          tmem_ld16(tbase + (uint32_t)(ky_own * a.gs + c0), acc);
+          for (int ky = 0; ky < a.KH; ++ky) {
+            if (ky == ky_own) continue;
             float v[16];
             tmem_ld16(tbase + (uint32_t)(ky * a.gs + c0), v);
-            // hand the block to the thread ky rows up: 64-byte rows, 16-byte chunks swizzled
+            // hand the block to the thread that owns the output row it belongs to (ky - ky_own rows
+            // up): 64-byte rows, 16-byte chunks swizzled
             float4 *row = reinterpret_cast<float4 *>(xch + half * (TCV_EPI_FLOATS / 2) + m * 16);
             const int sw = (m >> 1) & 3;
 #pragma unroll
             for (int q = 0; q < 4; ++q)
               row[q ^ sw] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             asm volatile("bar.sync 1, 128;\n" ::: "memory");
-            const int src = m + 8 * ky;
-            if (src < 128) {
-              const float4 *srow =
+            const int srow = r + ky - ky_own;
+            if (srow >= row_lo && srow < row_hi) {
+              const int src = m + 8 * (ky - ky_own);
+              const float4 *srow4 =
                 reinterpret_cast<const float4 *>(xch + half * (TCV_EPI_FLOATS / 2) + src * 16);
               const int ssw = (src >> 1) & 3;
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                float4 w = srow[q ^ ssw];
+                float4 w = srow4[q ^ ssw];
                 acc[4 * q] += w.x;
                 acc[4 * q + 1] += w.y;
                 acc[4 * q + 2] += w.z;
@@ -559,7 +593,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     }
     if (a.dbg && tid == 0) {
       long long *d = a.dbg + (size_t)blockIdx.x * 8;
-      d[4] = clock64() - t_begin;
+      d[4] = tc_clock() - t_begin;
       d[5] = w_full;
     }
   }
@@ -588,7 +622,7 @@ struct TcDwArgs {
   int ksplits;
   int tmem_cols;
   long long row_stride;
-  long long *dbg;  // optional [blocks][8] cycle counters (B200_TC_TIMING=1), else nullptr
+  long long *dbg;  // [blocks][8] cycle counters in a build with -DB200_TC_TIMING, else nullptr
 };
 
 // dW[o][inc][ky][kx] = sum over pixels u of X dY[t][u + pad_l - kx] * X[t + ky - pad_t][u]
@@ -647,15 +681,15 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   } else if (warp == 5 && lane == 0) {
     const uint32_t idesc = umma_idesc_tf32_major(128, N, 1, 1);
     uint32_t accumulate = 0;
-    long long w_full = 0, t_begin = clock64(), tq;
+    long long w_full = 0, t_begin = tc_clock(), tq;
     for (int s = s_begin; s < s_end && !failed; ++s) {
       const uint32_t i = s - s_begin, st = i % TCW_STAGES;
-      tq = clock64();
+      tq = tc_clock();
       if (!mbar_wait_bounded(&full[st], (i / TCW_STAGES) & 1)) {
         failed = true;
         break;
       }
-      w_full += clock64() - tq;
+      w_full += tc_clock() - tq;
       tc_fence_after();
       const uint32_t base = smem_u32(smem + st * STAGE);
       for (int r = 0; r < TCW_ROWS; ++r) {
@@ -680,7 +714,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     if (!failed) umma_commit(accum);
     if (a.dbg) {
       long long *d = a.dbg + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
-      d[0] = clock64() - t_begin;
+      d[0] = tc_clock() - t_begin;
       d[1] = w_full;
       d[2] = s_end - s_begin;
     }
@@ -688,12 +722,12 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     // partial row in the kernel's own order [unit][j][ky][inc][o] (o fastest: one 128-byte line per
     // store instruction); conv_tc_dw_finish sums the rows and reorders to the reference layout
     float *row = a.part + (size_t)blockIdx.x * a.row_stride + (size_t)blockIdx.y * a.KW * N * 32;
-    t_begin = clock64();
+    t_begin = tc_clock();
     if (s_end > s_begin) {
       if (!mbar_wait_bounded(accum, 0)) failed = true;
       tc_fence_after();
     }
-    t_acc = clock64();
+    t_acc = tc_clock();
     if (!failed) {
       for (int ch = 0; ch < chunks; ++ch) {
         const int j = ch * 4 + warp;
@@ -717,7 +751,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   if (a.dbg && tid == 0) {
     long long *d = a.dbg + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8;
     d[3] = t_acc - t_begin;
-    d[4] = clock64() - t_acc;
+    d[4] = tc_clock() - t_acc;
   }
   if (failed && a.err) atomicExch(a.err, 4);
   tc_fence_before();
@@ -817,7 +851,8 @@ int to_tall(b200_ctx *ctx, const TallSrc &src, int C, int H, int W, int Cp, int 
 }
 
 // shared launcher of the forward and dX passes
-int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long rows, int period,
+// `Hin` = rows per image of the tall tensor (its images are `period` rows apart)
+int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, int Hin, long long rows, int period,
                    const float *wt, int KH, int KW, int pad_t, int pad_l, int N, float *out, int OH, int OW,
                    const float *bias, int act, int B) {
   const TcPlan p = conv_tc_plan(ctx, KH, N);
@@ -825,10 +860,21 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long 
   const int slabs = Cp / 32, Ng = KH * p.gs;
   CUtensorMap in_hi, in_lo, f_hi, f_lo;
   const size_t one = (size_t)rows * Win * Cp;
-  B200_TRY(make_map_3d(&in_hi, tall, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS,
-                       CU_TENSOR_MAP_SWIZZLE_128B));
-  B200_TRY(make_map_3d(&in_lo, tall + one, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS,
-                       CU_TENSOR_MAP_SWIZZLE_128B));
+  // image-aligned tiles: whole images per tile (see TcConvArgs)
+  static const bool no_aligned = getenv("B200_CONV_TC_NO_ALIGNED") != nullptr;
+  const bool aligned = !no_aligned && Hin == OH && Hin >= 1 && TCV_TILE_ROWS % Hin == 0 && pad_t <= KH - 1;
+  const int ipt = aligned ? TCV_TILE_ROWS / Hin : 1;
+  if (aligned) {
+    B200_TRY(make_map_4d(&in_hi, tall, Cp, Win, Hin, B, (uint64_t)period * Win * Cp, 32, TCV_HALO_W, Hin, ipt,
+                         CU_TENSOR_MAP_SWIZZLE_128B));
+    B200_TRY(make_map_4d(&in_lo, tall + one, Cp, Win, Hin, B, (uint64_t)period * Win * Cp, 32, TCV_HALO_W, Hin,
+                         ipt, CU_TENSOR_MAP_SWIZZLE_128B));
+  } else {
+    B200_TRY(make_map_3d(&in_hi, tall, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS,
+                         CU_TENSOR_MAP_SWIZZLE_128B));
+    B200_TRY(make_map_3d(&in_lo, tall + one, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS,
+                         CU_TENSOR_MAP_SWIZZLE_128B));
+  }
   const size_t frows = (size_t)slabs * KW * p.groups * Ng;
   B200_TRY(make_map_rows(&f_hi, wt, frows, Ng));
   B200_TRY(make_map_rows(&f_lo, wt + frows * 32, frows, Ng));
@@ -850,7 +896,10 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long 
   a.pad_l = pad_l;
   const int TR = TCV_TILE_ROWS - (KH - 1);
   a.tiles_x = ceil_div(OW, TCV_TILE_COLS);
-  a.ntiles = a.tiles_x * (int)((rows + TR - 1) / TR);
+  a.ntiles = a.tiles_x * (aligned ? ceil_div(B, ipt) : (int)((rows + TR - 1) / TR));
+  a.aligned = aligned ? 1 : 0;
+  a.img_h = Hin;
+  a.ipt = ipt;
   a.act = act;
   a.nh = p.nh;
   a.nf = p.nf;
@@ -860,10 +909,13 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long 
   B200_CUDA(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
   const int units = a.ntiles * a.groups;
   int grid = units < ctx->sm_count ? units : ctx->sm_count;
+#ifdef B200_TC_TIMING
   static const bool timing = getenv("B200_TC_TIMING") != nullptr;
   if (timing) B200_CUDA(cudaMalloc(&a.dbg, (size_t)grid * 8 * sizeof(long long)));
+#endif
   conv_tc_kernel<<<grid, TCV_THREADS, p.smem, ctx->stream>>>(in_hi, in_lo, f_hi, f_lo, a);
   B200_LAUNCHED();
+#ifdef B200_TC_TIMING
   if (timing) {  // diagnostic: where the MMA and epilogue roles spent their cycles, averaged over blocks
     std::vector<long long> h((size_t)grid * 8);
     B200_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -877,6 +929,7 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, long long 
             "epilogue total %.0f, wait full %.0f\n",
             a.ntiles, grid, KH * p.gs, s[0], s[1], s[2], s[3], s[4], s[5]);
   }
+#endif
   return 0;
 }
 
@@ -1177,7 +1230,7 @@ int conv_tc_fwd(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *
                 float *out, int B, int act, float *wt, int prep) {
   TallGeom t = tall_geom(g, B);
   if (prep) B200_TRY(conv_tc_prep(ctx, g, W, wt, nullptr));
-  return launch_conv_tc(ctx, xs, t.Cp, g.WI, t.rows, t.period, wt, g.KH, g.KW, g.pad_t, g.pad_l, g.OC, out,
+  return launch_conv_tc(ctx, xs, t.Cp, g.WI, g.HI, t.rows, t.period, wt, g.KH, g.KW, g.pad_t, g.pad_l, g.OC, out,
                         g.OH, g.OW, g.has_bias ? bias : nullptr, act, B);
 }
 
@@ -1186,7 +1239,7 @@ int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *
   TallGeom t = tall_geom(g, B);
   const int period = dy_period(g);
   if (prep) B200_TRY(conv_tc_prep(ctx, g, W, nullptr, wt));
-  return launch_conv_tc(ctx, dys, t.OCp, g.OW, (long long)B * period, period, wt, g.KH, g.KW,
+  return launch_conv_tc(ctx, dys, t.OCp, g.OW, g.OH, (long long)B * period, period, wt, g.KH, g.KW,
                         g.KH - 1 - g.pad_t, g.KW - 1 - g.pad_l, g.C, din, g.HI, g.WI, nullptr, B200_ACT_NONE,
                         B);
 }
@@ -1222,11 +1275,14 @@ int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *d
   B200_CUDA(cudaFuncSetAttribute(conv_dw_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(a.ksplits, a.ic_slabs * (t.OCp / 32));
   a.dbg = nullptr;
-  static const bool timing = getenv("B200_TC_TIMING") != nullptr;
   const int nblk = (int)(grid.x * grid.y);
+#ifdef B200_TC_TIMING
+  static const bool timing = getenv("B200_TC_TIMING") != nullptr;
   if (timing) B200_CUDA(cudaMalloc(&a.dbg, (size_t)nblk * 8 * sizeof(long long)));
+#endif
   conv_dw_tc_kernel<<<grid, TCV_THREADS, smem, ctx->stream>>>(dy_hi, dy_lo, x_hi, x_lo, a);
   B200_LAUNCHED();
+#ifdef B200_TC_TIMING
   if (timing) {  // diagnostic: cycles of the MMA role and of the epilogue, averaged over blocks
     std::vector<long long> h((size_t)nblk * 8);
     B200_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -1240,6 +1296,7 @@ int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *d
             "store %.0f\n",
             nblk, s[2], s[0], s[1], s[3], s[4]);
   }
+#endif
   *splits = a.ksplits;
   return 0;
 }
@@ -1279,7 +1336,7 @@ struct TcDwSmallArgs {
   int nst;              // pipeline stages
   int tmem_cols;        // accumulator 2*OCp, then two A buffers of 32 hi + 32 lo columns
   long long row;
-  long long *dbg;       // optional [blocks][8] cycle counters (B200_TC_TIMING=1), else nullptr
+  long long *dbg;       // [blocks][8] cycle counters in a build with -DB200_TC_TIMING, else nullptr
 };
 
 __global__ void __launch_bounds__(TCS_THREADS, 1)
@@ -1322,17 +1379,17 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
 
   if (warp == TCS_CONV_WARPS && lane == 0) {
     // ---- TMA producer: raw input rows and the gradient tile of each step ----------------------
-    long long w = 0, t0 = clock64(), tq;
+    long long w = 0, t0 = tc_clock(), tq;
     for (int s = s_begin; s < s_end; ++s) {
       const uint32_t i = s - s_begin, st = i % a.nst, use = i / a.nst;
-      tq = clock64();
+      tq = tc_clock();
       if (use > 0 && !mbar_wait_bounded(&op_empty[st], (use - 1) & 1)) {
         failed = true;
         break;
       }
-      w += clock64() - tq;
+      w += tc_clock() - tq;
       if (a.dbg && s == s_end - 1) {
-        a.dbg[blockIdx.x * 8 + 0] = clock64() - t0;
+        a.dbg[blockIdx.x * 8 + 0] = tc_clock() - t0;
         a.dbg[blockIdx.x * 8 + 1] = w;
       }
       const int xb = s % a.nxb, by = s / a.nxb, y = by % a.OH, b = by / a.OH;
@@ -1348,17 +1405,17 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
     // the hi and lo gradient tiles are neighbours in shared memory: A_hi * [B_hi | B_lo] is one
     // instruction of width 2*OCp (columns OCp.. hold the A_hi*B_lo part, added in the epilogue)
     const uint32_t idesc1 = umma_idesc_tf32(128, a.OCp), idesc2 = umma_idesc_tf32(128, 2 * a.OCp);
-    long long w = 0, t0 = clock64(), tq;
+    long long w = 0, t0 = tc_clock(), tq;
     for (int s = s_begin; s < s_end && !failed; ++s) {
       const uint32_t i = s - s_begin, st = i % a.nst;
-      tq = clock64();
+      tq = tc_clock();
       if (!mbar_wait_bounded(&op_full[st], (i / a.nst) & 1)) {
         failed = true;
         break;
       }
-      w += clock64() - tq;
+      w += tc_clock() - tq;
       if (a.dbg && s == s_end - 1) {
-        a.dbg[blockIdx.x * 8 + 2] = clock64() - t0;
+        a.dbg[blockIdx.x * 8 + 2] = tc_clock() - t0;
         a.dbg[blockIdx.x * 8 + 3] = w;
       }
       tc_fence_after();
@@ -1393,18 +1450,18 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
     float bacc[NB];                    // bias partials of the (o, quad) items this thread owns
 #pragma unroll
     for (int q = 0; q < NB; ++q) bacc[q] = 0.f;
-    long long w = 0, t0 = clock64(), tq;
+    long long w = 0, t0 = tc_clock(), tq;
     // Every converter warp observes every step's barrier, in order, and takes part in the
     // hand-over, although only the step's group converts: a warp that skipped phases of an
     // mbarrier could no longer tell one phase from the one two later (the wait is by parity).
     for (int s = s_begin; s < s_end; ++s) {
       const uint32_t i = s - s_begin, st = i % a.nst;
-      tq = clock64();
+      tq = tc_clock();
       if (!mbar_wait_bounded(&tma_full[st], (i / a.nst) & 1)) {
         failed = true;
         break;
       }
-      w += clock64() - tq;
+      w += tc_clock() - tq;
       if ((int)(i % TCS_GROUPS) != grp) {
         __syncwarp();
         if (lane == 0) mbar_arrive(&op_full[st]);
@@ -1459,7 +1516,7 @@ __global__ void __launch_bounds__(TCS_THREADS, 1)
       if (lane == 0) mbar_arrive(&op_full[st]);
     }
     if (a.dbg && tid == 0) {
-      a.dbg[blockIdx.x * 8 + 4] = clock64() - t0;
+      a.dbg[blockIdx.x * 8 + 4] = tc_clock() - t0;
       a.dbg[blockIdx.x * 8 + 5] = w;
     }
     // ---- epilogue ------------------------------------------------------------------------------
@@ -1603,10 +1660,13 @@ int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float
   const size_t smem = dw_small_fixed(OCp) + (size_t)a.nst * dw_small_stage(g, OCp, bw);
   B200_CUDA(cudaFuncSetAttribute(conv_dw_small_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   a.dbg = nullptr;
+#ifdef B200_TC_TIMING
   static const bool timing = getenv("B200_TC_TIMING") != nullptr;
   if (timing) B200_CUDA(cudaMalloc(&a.dbg, (size_t)a.ksplits * 8 * sizeof(long long)));
+#endif
   conv_dw_small_tc_kernel<<<a.ksplits, TCS_THREADS, smem, ctx->stream>>>(x_map, dy_map, a);
   B200_LAUNCHED();
+#ifdef B200_TC_TIMING
   if (timing) {  // diagnostic: cycles of the three roles and of their waits, averaged over blocks
     std::vector<long long> h((size_t)a.ksplits * 8);
     B200_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -1620,6 +1680,7 @@ int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float
             "converter group 0 %.0f (wait %.0f)\n",
             (double)a.nsteps / a.ksplits, a.nst, s[0], s[1], s[2], s[3], s[4], s[5]);
   }
+#endif
   DwFinishArgs f;
   f.part = part;
   f.part_stride = a.row;

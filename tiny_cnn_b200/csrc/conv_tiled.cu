@@ -1233,11 +1233,15 @@ static int dw_launch(b200_ctx *ctx, const DwCfg &p, int KH, int KW, int OCT) {
   return 0;
 }
 
-// Band height and slice count are remembered per context; on first sight a few
-// choices are timed with CUDA events (shorter bands give more, finer units to
-// balance over the SMs at the price of more halo rows; more slices mean more
-// partial rows to merge) and the fastest is kept.  The choice only regroups the
-// partial sums; within a process a given problem always uses the same grouping.
+// Band height and slice count regroup the partial sums, so they decide the fp32
+// summation order of dW.  By default they are a fixed function of the problem
+// and the SM count (tallest band, one slice per SM and tile): the same inputs
+// give the same bits in every process.  With B200_AUTOTUNE=1 a few choices are
+// timed with CUDA events on first sight (shorter bands give more, finer units
+// to balance over the SMs at the price of more halo rows; more slices mean more
+// partial rows to merge), the fastest is kept per context and, through
+// B200_TUNE_CACHE, across processes; results are then reproducible only for
+// one tuning outcome.
 int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout,
                            int B, float *scratch, int *splits) {
   B200_REQUIRE(B > 0, "conv_tiled_dw_partials: empty batch");
@@ -1254,13 +1258,15 @@ int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in, co
   int th = 0, sp = 0;
   auto it = ctx->tile_cache.find(key);
   if (it != ctx->tile_cache.end()) {
-    th = it->second.TH;
-    sp = it->second.NSB;
+    // an entry read from a tuning file may come from another GPU or an edited file: the scratch
+    // holds 2 * sm_count partial rows, a band cannot be taller than the output
+    th = it->second.TH < 0 ? 0 : it->second.TH > g.OH ? g.OH : it->second.TH;
+    sp = it->second.NSB < 0 ? 0 : it->second.NSB > 2 * ctx->sm_count ? 2 * ctx->sm_count : it->second.NSB;
   } else {
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     B200_CUDA(cudaStreamIsCapturing(ctx->stream, &cap));
     const char *at = getenv("B200_AUTOTUNE");
-    bool tune = !(at && at[0] == '0') && cap == cudaStreamCaptureStatusNone;
+    bool tune = at && at[0] == '1' && cap == cudaStreamCaptureStatusNone;
     if (tune) {
       DwCfg t0 = base;
       dw_tiling(ctx, t0, g.KH, g.KW, OCT);
@@ -1534,6 +1540,7 @@ extern "C" int b200_conv2d_dw_noalloc(void *stream, const b200_conv_desc *d, con
                "conv2d_dw_noalloc: tile needs %zu bytes of shared memory (limit %zu)", smem,
                nd->smem_optin);
   int threads = (p.OCB / OCT) * p.ICT * p.SL;
+  B200_REQUIRE(threads >= 1 && threads <= 256, "conv2d_dw_noalloc: thread count %d out of range", threads);
   int blocks = p.tiles_oc * p.tiles_ic * p.splits;
   // Every block overwrites its whole tile of its row, so nothing left in the
   // array by an earlier call is ever read: no clearing is needed.

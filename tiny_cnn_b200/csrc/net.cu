@@ -79,13 +79,30 @@ struct b200_net {
   bool fuse = true;
   bool input_grad = true;
   PeerReduce peer;  // data-parallel replicas: the gradient bucket is summed over the ranks inside the step
-  // captured launch sequences: slot 0 = whole step, slot 1 = forward + backward
-  struct GraphSlot {
+  // the layers after `peer_early_layer` (inclusive) own bucket entries [peer.split, n): once their weight
+  // gradients exist they are pushed to the peers from `comm`, beside the rest of the backward pass
+  int peer_early_layer = -1;
+  cudaStream_t comm = nullptr;
+  cudaEvent_t ev_comm_main = nullptr, ev_comm_side = nullptr, ev_comm_done = nullptr;
+  // captured launch sequences: slot 0 = whole step, slot 1 = forward + backward.  A slot keeps
+  // the graphs of the last few configurations (buffers, batch size, hyper-parameters), so the
+  // ragged last mini-batch of an epoch does not evict the graph of the full ones.
+  struct GraphEntry {
     cudaGraphExec_t exec = nullptr;
-    std::string key;
     int seen = 0;
     unsigned long long kernels = 0;  // kernels recorded in the graph
+    unsigned long long last_use = 0;
+  };
+  struct GraphSlot {
+    std::map<std::string, GraphEntry> entries;
+    unsigned long long clock = 0;
+    void clear() {
+      for (auto &kv : entries)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+      entries.clear();
+    }
   } slots[2];
+  static constexpr size_t kGraphsPerSlot = 4;
   bool use_graph = true;
 };
 
@@ -183,7 +200,7 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
   return 0;
 }
 
-int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
+int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in_step = false) {
   b200_ctx *ctx = net->ctx;
   int B = net->cur_batch;
   int n = (int)net->layers.size();
@@ -198,7 +215,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
   // reads them.  They go to the side stream, so the chain of dX kernels -- the critical path --
   // does not wait for them, and kernels that leave SMs idle overlap.  One join at the end.
   cudaStream_t main_stream = ctx->stream;
-  bool side_used = false;
+  bool side_used = false, comm_used = false;
   int rc_side = 0;
   // One side branch, not one per layer: the large kernels of both branches each fill the SMs, so
   // more branches only interleave them and delay the dX chain (measured: two branches 0.387 ms
@@ -303,12 +320,29 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind) {
         break;
       default: B200_REQUIRE(false, "net_backward: unknown layer kind %d", L.kind);
     }
+    if (peer_in_step && i == net->peer_early_layer && rc_side == 0 && net->comm) {
+      // every weight gradient of layers i.. has been issued (main or side stream): send them to
+      // the peers now, from a third stream, while the remaining layers still compute
+      B200_CUDA(cudaEventRecord(net->ev_comm_main, main_stream));
+      B200_CUDA(cudaStreamWaitEvent(net->comm, net->ev_comm_main, 0));
+      if (side_used) {
+        B200_CUDA(cudaEventRecord(net->ev_comm_side, net->side));
+        B200_CUDA(cudaStreamWaitEvent(net->comm, net->ev_comm_side, 0));
+      }
+      ctx->stream = net->comm;
+      int rc = peer_reduce_push_early(ctx, &net->peer, net->grads);
+      ctx->stream = main_stream;
+      B200_TRY(rc);
+      B200_CUDA(cudaEventRecord(net->ev_comm_done, net->comm));
+      comm_used = true;
+    }
   }
   ctx->stream = main_stream;
   if (side_used) {  // the optimizer (or the caller's all-reduce) follows on the main stream
     B200_CUDA(cudaEventRecord(net->ev_join, net->side));
     B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_join, 0));
   }
+  if (comm_used) B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_comm_done, 0));
 
   return rc_side;
 }
@@ -337,9 +371,11 @@ int net_init_powers(b200_net *net, float b1, float b2) {
 int net_update_impl(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
   b200_ctx *ctx = net->ctx;
   int T = (int)net->segs.size();
+  // after a reduction over the replicas whose wait ran out the update changes nothing
+  const int *skip_if = net->peer.world > 1 ? ctx->dev_err : nullptr;
   B200_TRY(opt_update_segments(ctx, opt_kind, *h, net->grads, net->params, net->state0,
-                               net->state1, net->segs_dev, T, net->n_params, net->pow_tab));
-  if (opt_kind == B200_OPT_ADAM) B200_TRY(opt_advance_powers(ctx, net->pow_tab, T, h->b1, h->b2));
+                               net->state1, net->segs_dev, T, net->n_params, net->pow_tab, skip_if));
+  if (opt_kind == B200_OPT_ADAM) B200_TRY(opt_advance_powers(ctx, net->pow_tab, T, h->b1, h->b2, skip_if));
   return 0;
 }
 
@@ -357,8 +393,13 @@ int check_net(b200_net *net) {
 int step_eager(b200_net *net, const float *x, const float *t, int B, int loss_kind, int opt_kind,
                const b200_opt_hyper *h) {
   B200_TRY(net_forward_impl(net, x, B));
-  B200_TRY(net_backward_impl(net, t, loss_kind));
-  if (net->peer.world > 1) B200_TRY(peer_reduce_run(net->ctx, &net->peer, net->grads));
+  const bool peer = net->peer.world > 1;
+  const bool early = peer && net->comm && net->peer_early_layer >= 0 && net->peer.split < net->peer.n;
+  B200_TRY(net_backward_impl(net, t, loss_kind, early));
+  if (peer) {
+    if (!early) B200_TRY(peer_reduce_push_early(net->ctx, &net->peer, net->grads));
+    B200_TRY(peer_reduce_finish(net->ctx, &net->peer, net->grads, 0));
+  }
   return net_update_impl(net, opt_kind, h);
 }
 
@@ -563,8 +604,7 @@ int b200_net_destroy(b200_net *net) {
   if (!net) return 0;
   cudaSetDevice(net->ctx->device);
   cudaStreamSynchronize(net->ctx->stream);
-  for (auto &slot : net->slots)
-    if (slot.exec) cudaGraphExecDestroy(slot.exec);
+  for (auto &slot : net->slots) slot.clear();
   for (auto &L : net->layers) {
     cudaFree(L.out);
     cudaFree(L.grad);
@@ -598,6 +638,10 @@ int b200_net_destroy(b200_net *net) {
   }
   if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
   peer_reduce_free(&net->peer);
+  if (net->comm) cudaStreamDestroy(net->comm);
+  if (net->ev_comm_main) cudaEventDestroy(net->ev_comm_main);
+  if (net->ev_comm_side) cudaEventDestroy(net->ev_comm_side);
+  if (net->ev_comm_done) cudaEventDestroy(net->ev_comm_done);
   if (net->side) cudaStreamDestroy(net->side);
   if (net->ev_fork) cudaEventDestroy(net->ev_fork);
   if (net->ev_join) cudaEventDestroy(net->ev_join);
@@ -684,11 +728,34 @@ size_t b200_net_peer_reduce_bytes(b200_net *net, int world) {
   return peer_reduce_bytes((long long)net->n_params, world);
 }
 
-int b200_net_peer_reduce_init(b200_net *net, int rank, int world, const unsigned long long *buffers) {
+int b200_net_peer_reduce_init(b200_net *net, int rank, int world, const unsigned long long *buffers,
+                              int timeout_ms) {
   B200_TRY(check_net(net));
-  B200_TRY(peer_reduce_init(net->ctx, &net->peer, (long long)net->n_params, rank, world, buffers));
+  // The first layer with parameters finishes its gradients last; everything after it in the
+  // bucket can leave early.  The boundary is rounded up to 16 bytes (entries below it that are
+  // ready early simply travel with the late part).
+  int first = -1, second = -1;
+  for (int i = 0; i < (int)net->layers.size(); ++i) {
+    if (net->layers[i].w_len == 0 && net->layers[i].b_len == 0) continue;
+    if (first < 0) first = i;
+    else if (second < 0) second = i;
+  }
+  long long n = (long long)net->n_params, split = n;
+  if (second >= 0) {
+    const Layer &L = net->layers[second];
+    split = (long long)((L.w_len ? L.w_off : L.b_off) + 3) / 4 * 4;
+    if (split > n) split = n;
+  }
+  net->peer_early_layer = split < n ? second : -1;
+  B200_TRY(peer_reduce_init(net->ctx, &net->peer, n, split, rank, world, buffers, timeout_ms));
+  if (!net->comm) {
+    B200_CUDA(cudaStreamCreateWithFlags(&net->comm, cudaStreamNonBlocking));
+    B200_CUDA(cudaEventCreateWithFlags(&net->ev_comm_main, cudaEventDisableTiming));
+    B200_CUDA(cudaEventCreateWithFlags(&net->ev_comm_side, cudaEventDisableTiming));
+    B200_CUDA(cudaEventCreateWithFlags(&net->ev_comm_done, cudaEventDisableTiming));
+  }
   // the step's launch sequence changes: captured graphs are rebuilt
-  for (auto &slot : net->slots) slot.key.clear();
+  for (auto &slot : net->slots) slot.clear();
   return 0;
 }
 
@@ -696,6 +763,18 @@ int b200_net_peer_reduce(b200_net *net) {
   B200_TRY(check_net(net));
   B200_REQUIRE(net->peer.world > 1, "net_peer_reduce: b200_net_peer_reduce_init was not called");
   return peer_reduce_run(net->ctx, &net->peer, net->grads);
+}
+
+int b200_net_peer_push(b200_net *net) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(net->peer.world > 1, "net_peer_push: b200_net_peer_reduce_init was not called");
+  return peer_reduce_push_all(net->ctx, &net->peer, net->grads);
+}
+
+int b200_net_peer_sum(b200_net *net) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(net->peer.world > 1, "net_peer_sum: b200_net_peer_reduce_init was not called");
+  return peer_reduce_finish(net->ctx, &net->peer, net->grads, 1);
 }
 
 int b200_net_update(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
@@ -727,15 +806,20 @@ int b200_net_adam_powers(const b200_net *net, float *b1_t, float *b2_t) {
 template <typename F>
 static int run_captured(b200_net *net, int slot_idx, const std::string &key, F body) {
   if (!net->use_graph) return body();
-  b200_net::GraphSlot &slot = net->slots[slot_idx];
-  if (key != slot.key) {
-    if (slot.exec) {
-      B200_CUDA(cudaGraphExecDestroy(slot.exec));
-      slot.exec = nullptr;
+  b200_net::GraphSlot &table = net->slots[slot_idx];
+  auto it = table.entries.find(key);
+  if (it == table.entries.end()) {
+    if (table.entries.size() >= b200_net::kGraphsPerSlot) {  // drop the configuration used longest ago
+      auto victim = table.entries.begin();
+      for (auto e = table.entries.begin(); e != table.entries.end(); ++e)
+        if (e->second.last_use < victim->second.last_use) victim = e;
+      if (victim->second.exec) B200_CUDA(cudaGraphExecDestroy(victim->second.exec));
+      table.entries.erase(victim);
     }
-    slot.key = key;
-    slot.seen = 0;
+    it = table.entries.emplace(key, b200_net::GraphEntry()).first;
   }
+  b200_net::GraphEntry &slot = it->second;
+  slot.last_use = ++table.clock;
   cudaStream_t st = net->ctx->stream;
   if (slot.exec) {
     B200_CUDA(cudaGraphLaunch(slot.exec, st));

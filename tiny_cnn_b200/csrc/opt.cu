@@ -64,7 +64,9 @@ __global__ void opt_update_segments_kernel(int kind, OptParams h, const float *_
                                            float *__restrict__ W, float *__restrict__ s0,
                                            float *__restrict__ s1,
                                            const OptSegment *__restrict__ segs, int n_segs,
-                                           size_t total, const float *__restrict__ pow_tab) {
+                                           size_t total, const float *__restrict__ pow_tab,
+                                           const int *__restrict__ skip_if) {
+  if (skip_if && *skip_if != 0) return;
   size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   size_t step = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += step) {
@@ -95,7 +97,9 @@ __global__ void opt_update_segments_kernel(int kind, OptParams h, const float *_
 // power after t further multiplies, and every entry then moves on by n_tensors
 // sequential float multiplies -- the same products, in the same order, that
 // `b1_t *= b1` produces on the host.
-__global__ void opt_advance_powers_kernel(float *pow_tab, int n_tensors, float b1, float b2) {
+__global__ void opt_advance_powers_kernel(float *pow_tab, int n_tensors, float b1, float b2,
+                                          const int *__restrict__ skip_if) {
+  if (skip_if && *skip_if != 0) return;
   int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_tensors) return;
   float p1 = pow_tab[2 * t], p2 = pow_tab[2 * t + 1];
@@ -143,19 +147,20 @@ int opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *gr
 
 int opt_update_segments(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *grads,
                         float *W, float *s0, float *s1, const OptSegment *segs_dev, int n_segs,
-                        size_t total, float *pow_tab) {
+                        size_t total, float *pow_tab, const int *skip_if) {
   B200_REQUIRE(kind >= B200_OPT_ADAGRAD && kind <= B200_OPT_MOMENTUM, "unknown optimizer %d", kind);
   if (total == 0) return 0;
   opt_update_segments_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
-    kind, to_params(h), grads, W, s0, s1, segs_dev, n_segs, total, pow_tab);
+    kind, to_params(h), grads, W, s0, s1, segs_dev, n_segs, total, pow_tab, skip_if);
   B200_LAUNCHED();
   return 0;
 }
 
-int opt_advance_powers(b200_ctx *ctx, float *pow_tab, int n_tensors, float b1, float b2) {
+int opt_advance_powers(b200_ctx *ctx, float *pow_tab, int n_tensors, float b1, float b2,
+                       const int *skip_if) {
   if (n_tensors == 0) return 0;
   opt_advance_powers_kernel<<<ceil_div(n_tensors, 64), 64, 0, ctx->stream>>>(pow_tab, n_tensors, b1,
-                                                                            b2);
+                                                                            b2, skip_if);
   B200_LAUNCHED();
   return 0;
 }

@@ -233,7 +233,10 @@ int b200_ctx_sync(b200_ctx *ctx) {
     B200_CUDA(cudaMemcpy(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag != 0) {
       cudaMemset(ctx->dev_err, 0, sizeof(int));
-      B200_REQUIRE(false, "a kernel gave up a bounded wait on an asynchronous copy (code %d)", flag);
+      B200_REQUIRE(false, "a kernel gave up a bounded wait (code %d: %s)", flag,
+                   flag == 7 ? "the sum of the gradients over the replicas timed out waiting for another rank; this rank "
+                               "skipped the update, the replicas differ from now on"
+                             : "an asynchronous copy or tensor-core operation did not complete");
     }
   }
   return 0;

@@ -197,6 +197,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
     : "memory");
 }
 
+// Cycle counter of the role-timing diagnostics.  They exist only in a build with
+// -DB200_TC_TIMING (python -m tiny_cnn_b200.build --tc-timing); otherwise this is a constant and
+// every counter update folds away.
+__device__ __forceinline__ long long tc_clock() {
+#ifdef B200_TC_TIMING
+  return clock64();
+#else
+  return 0;
+#endif
+}
+
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
 }
@@ -255,6 +266,26 @@ static inline int make_map_3d(CUtensorMap *m, const float *base, uint64_t d0, ui
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B200_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (%d) for a %llu x %llu x %llu tensor",
                (int)r, (unsigned long long)d2, (unsigned long long)d1, (unsigned long long)d0);
+  return 0;
+}
+
+// fp32 tensor [d3][d2][d1][d0] whose outermost dimension is `stride3` floats apart (the others are
+// dense); box b0 x b1 x b2 x b3, zero fill
+static inline int make_map_4d(CUtensorMap *m, const float *base, uint64_t d0, uint64_t d1, uint64_t d2,
+                              uint64_t d3, uint64_t stride3, uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3,
+                              CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_fn();
+  B200_REQUIRE(fn != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {d0 * sizeof(float), d0 * d1 * sizeof(float), stride3 * sizeof(float)};
+  cuuint32_t box[4] = {b0, b1, b2, b3};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (%d) for a %llu x %llu x %llu x %llu tensor",
+               (int)r, (unsigned long long)d3, (unsigned long long)d2, (unsigned long long)d1,
+               (unsigned long long)d0);
   return 0;
 }
 

@@ -45,10 +45,12 @@ class DataParallel:
         self.peer = False
         self._symm = None  # keeps the exchange buffer and its rendezvous handle alive
 
-    def enable_peer_reduce(self) -> bool:
+    def enable_peer_reduce(self, timeout_ms: int = 0) -> bool:
         """Map every rank's exchange buffer into every rank and hand the addresses to the net
         (b200_net_peer_reduce_init).  Returns True when EVERY rank succeeded; otherwise all
-        ranks keep the NCCL all-reduce.  Collective: every rank must call it."""
+        ranks keep the NCCL all-reduce.  Collective: every rank must call it.  `timeout_ms` bounds
+        every wait of the reduction for another rank (0 = the library's default, 10 s); call
+        `check()` now and then to learn of a wait that ran out."""
         if self.world <= 1 or not self.bucket.is_cuda:
             return False
         import ctypes as C
@@ -75,10 +77,17 @@ class DataParallel:
                 print(f"[tiny_cnn_b200] peer reduce unavailable, using NCCL ({why})", file=sys.stderr, flush=True)
             return False
         arr = (C.c_ulonglong * self.world)(*ptrs)
-        check(lib.b200_net_peer_reduce_init(h, self.rank, self.world, arr))
+        check(lib.b200_net_peer_reduce_init(h, self.rank, self.world, arr, int(timeout_ms)))
         self._symm = (buf, hdl)
         self.peer = True
         return True
+
+    def check(self):
+        """Wait for this rank's queued work and raise if a kernel gave up a bounded wait (a reduction
+        over the replicas that timed out: this rank skipped the update, the replicas now differ)."""
+        ctx = getattr(self.net, "ctx", None)
+        if ctx is not None:
+            ctx.sync()
 
     def allreduce_grads(self):
         """In-place SUM over ranks of the gradient bucket (no averaging)."""
