@@ -278,17 +278,24 @@ def conv_rooflines(kt, peaks):
     tensor = v["tensor"]
     peak = peak_tc if tensor else peak_fp32
     conv_ms = sum(x["ms"] for x in kt.values())
+    conv_op_ms = sum(x["op_ms"] for x in kt.values())
     conv_fl = sum(x["flops"] for x in kt.values())
+    op_tf = v["flops"] / (v["op_ms"] * 1e-3) / 1e12
     roofline = {
         "kernel": ("conv_tc_kernel" if tensor else "conv FFMA kernel") + f" ({dom})",
         "bound": "tensor" if tensor else "fp32",
         "achieved": round(tf, 3), "peak": round(peak, 2), "unit": "TFLOP/s", "frac": round(tf / peak, 4),
+        # the same pass as the operator call issues it: the main kernel plus the layout kernels it needs
+        # (tall hi/lo copies, filter matrices, partial-row merges)
+        "achieved_op": round(op_tf, 3), "frac_op": round(op_tf / peak, 4),
         "traffic": NCU_DRAM_BYTES.get(dom),
         "peak_source": (f"algorithmic fp32 flop/s; ceiling = bf16 tensor peak {bf16} TFLOP/s {src} / 2 (TF32 rate) "
                         "/ 3 (three TF32 products per fp32 product)") if tensor else
                        "fp32 FFMA: 148 SMs x 128 lanes x 2 flop x clocks.max.sm 1965 MHz (no measured fp32 figure)",
         "tensor_pipe_tflops": round(3 * tf, 1) if tensor else None,
         "conv_main_kernels_all": {"ms": round(conv_ms, 4), "tflops": round(conv_fl / (conv_ms * 1e-3) / 1e12, 3)},
+        "conv_operator_calls_all": {"ms": round(conv_op_ms, 4),
+                                    "tflops": round(conv_fl / (conv_op_ms * 1e-3) / 1e12, 3)},
         "fp32_ffma_peak": round(peak_fp32, 2), "hbm_gbs": peaks.get("hbm_gbs"),
     }
     return kernels, roofline
@@ -438,6 +445,7 @@ def run_b200(args, rank, world, local_rank):
             peaks = json.loads(mp.read_text())
         kernels, roofline = conv_rooflines(kt, peaks)
         cpu = cpu_baseline() if world == 1 else None
+        cpp = e2e_cpp(max(4 * args.steps, 200)) if world == 1 else None
         per = 1.0 / args.steps
         line = {
             "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
@@ -477,6 +485,8 @@ def run_b200(args, rank, world, local_rank):
             line["parity"] = parity
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if cpp is not None:
+            line["e2e_cpp"] = cpp
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -534,6 +544,26 @@ def dp_parity(torch, dist, np, nw, ops, net, opt, dp_step, p0, rank, world, loca
                    f"the same steps of one GPU on the concatenated {world * BATCH}-sample mini-batch: largest "
                    "|difference| of a parameter tensor / its largest magnitude; replicas compared bit for bit "
                    "after the timed steps and after these"}
+
+
+def e2e_cpp(steps):
+    """network<sequential>::fit of the same net under engine backend_t::b200, timed inside a C++
+    program around the fit call (tiny_cnn_b200/host/bench_fit.cpp, built by oracle/build_oracle.py
+    where the tiny-dnn tree is present): std::vector<vec_t> in pageable memory in, trained weights in
+    the layer objects out.  None when the binary was not built."""
+    exe = ROOT / "oracle" / "_ref" / "bin" / "bench_fit_b200"
+    if not exe.exists():
+        return None
+    try:
+        res = subprocess.run([str(exe), str(steps), str(BATCH)], capture_output=True, text=True, timeout=300)
+        line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1]
+        d = json.loads(line)
+    except Exception as e:  # a diagnostic figure: its absence must not cost the bench line
+        return {"error": f"{type(e).__name__}: {e}"}
+    return {"value": d["samples_per_s"], "unit": "samples/s", "ms_per_step": d["ms_per_step"], "steps": d["steps"],
+            "device_fit": d["device_fit"],
+            "api": "tiny_dnn::network<sequential>::fit<cross_entropy>(adam, std::vector<vec_t>, ...) with every "
+                   "layer on core::backend_t::b200, wall clock around the call"}
 
 
 def cpu_baseline():

@@ -83,6 +83,13 @@ B200_API int b200_free(b200_ctx *ctx, void *ptr);
 B200_API int b200_memcpy_h2d(b200_ctx *ctx, void *dst, const void *src, size_t bytes);
 B200_API int b200_memcpy_d2h(b200_ctx *ctx, void *dst, const void *src, size_t bytes);
 B200_API int b200_memset(b200_ctx *ctx, void *dst, int value, size_t bytes);
+/*
+ * Page-locked host memory (cudaHostAlloc) for callers without the CUDA headers: the *_host entry
+ * points and b200_net_fit_host copy asynchronously, and overlap uploads with compute, only from
+ * such memory.  It replaces the std::vector<vec_t> staging of network::fit (network.h:911-926).
+ */
+B200_API int b200_host_alloc(size_t bytes, void **out);
+B200_API int b200_host_free(void *ptr);
 
 /* ------------------------------------------------------------------------- */
 /* Convolution  (a1-a3)                                                        */
@@ -564,8 +571,22 @@ B200_API int b200_net_fit_host(b200_net *net, const float *x_host, const float *
                                long long n_samples, int batch, int epochs, int loss_kind,
                                int opt_kind, const b200_opt_hyper *h, float *out_host);
 
-/* Adam powers currently held by the net (tests; T = tensor count). */
+/* Adam powers currently held by the net: what the next update of the FIRST tensor will use,
+ * i.e. the b1_t / b2_t members of the reference's adam object at that moment (optimizer.h:129-133). */
 B200_API int b200_net_adam_powers(const b200_net *net, float *b1_t, float *b2_t);
+
+/*
+ * Hand-off of the optimizer between the host objects of the reference and the device
+ * (network::save / load move the weights, network.h:676-728; the optimizer's state lives in
+ * stateful_optimizer::E_, optimizer.h:34-48, and in adam's public b1_t / b2_t).
+ * State buffer 0 is adagrad's g, adam's mt, momentum's dWprev; buffer 1 is adam's vt.  Both are
+ * flat in network parameter order, like b200_net_get_params.  b200_net_set_adam_powers makes the
+ * next step continue from an adam object whose powers currently are (b1_t, b2_t); a fresh object
+ * has (b1, b2), which is also what a net starts from when this is never called.
+ */
+B200_API int b200_net_get_opt_state(b200_net *net, int which, float *host_state);
+B200_API int b200_net_set_opt_state(b200_net *net, int which, const float *host_state);
+B200_API int b200_net_set_adam_powers(b200_net *net, float b1, float b2, float b1_t, float b2_t);
 
 /* Number of kernels this library launched on the calling process so far. */
 B200_API unsigned long long b200_launch_count(void);

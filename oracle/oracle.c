@@ -1022,6 +1022,15 @@ ORC_API void orc_net_update(orc_net *net, int opt_kind, const b200_opt_hyper *h)
   }
 }
 
+/* network::fit calls optimizer.reset() (network.h:856): stateful_optimizer::reset clears the
+ * per-weight state (optimizer.h:36-38) but adam's powers b1_t / b2_t carry on.  `keep_powers` = 0
+ * also restarts the powers (a new optimizer object). */
+ORC_API void orc_net_opt_reset(orc_net *net, int keep_powers) {
+  memset(net->s0, 0, net->n_params * sizeof(float));
+  memset(net->s1, 0, net->n_params * sizeof(float));
+  if (!keep_powers) net->powers_init = 0;
+}
+
 ORC_API void orc_net_adam_powers(const orc_net *net, float *b1_t, float *b2_t) {
   *b1_t = net->b1_t;
   *b2_t = net->b2_t;

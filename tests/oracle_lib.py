@@ -56,6 +56,7 @@ ORACLE_SIGS = {
     "orc_net_backward": (None, [_vp, _vp, _vp, _i, _i]),
     "orc_net_update": (None, [_vp, _i, _oh]),
     "orc_net_adam_powers": (None, [_vp, _fp, _fp]),
+    "orc_net_opt_reset": (None, [_vp, _i]),
     "orc_net_train_step": (None, [_vp, _vp, _vp, _i, _i, _i, _oh]),
 }
 

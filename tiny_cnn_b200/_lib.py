@@ -82,6 +82,8 @@ SIGNATURES = {
     "b200_ctx_set_option": (_i, [_vp, C.c_char_p, _i]),
     "b200_ctx_stream": (_vp, [_vp]),
     "b200_ctx_sync": (_i, [_vp]),
+    "b200_host_alloc": (_i, [_sz, C.POINTER(_vp)]),
+    "b200_host_free": (_i, [_vp]),
     "b200_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "b200_free": (_i, [_vp, _vp]),
     "b200_memcpy_h2d": (_i, [_vp, _vp, _vp, _sz]),
@@ -149,6 +151,9 @@ SIGNATURES = {
     "b200_net_train_step_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _oh, _vp]),
     "b200_net_fit_host": (_i, [_vp, _vp, _vp, C.c_longlong, _i, _i, _i, _i, _oh, _vp]),
     "b200_net_adam_powers": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "b200_net_get_opt_state": (_i, [_vp, _i, _vp]),
+    "b200_net_set_opt_state": (_i, [_vp, _i, _vp]),
+    "b200_net_set_adam_powers": (_i, [_vp, C.c_float, C.c_float, C.c_float, C.c_float]),
 }
 
 _lib = None

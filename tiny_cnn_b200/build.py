@@ -40,14 +40,23 @@ def _newest_header() -> float:
     return max(h.stat().st_mtime for h in hs)
 
 
-def _compile(src: Path, verbose: bool, ptxas_info: bool) -> Path:
-    obj = src.with_suffix(".o")
+# Role-timing diagnostics of the tensor-core kernels (cycle counters per warp role, printed when
+# the environment variable B200_TC_TIMING is set) exist only in a library built with
+# `python -m tiny_cnn_b200.build --tc-timing`, which goes to csrc/libtinycnn_b200_timing.so; load it
+# with TINYCNN_B200_LIB.  The default library carries none of it.
+TIMING_LIB_PATH = CSRC / "libtinycnn_b200_timing.so"
+
+
+def _compile(src: Path, verbose: bool, ptxas_info: bool, tc_timing: bool = False) -> Path:
+    obj = src.with_suffix(".timing.o" if tc_timing else ".o")
     newest = max(src.stat().st_mtime, _newest_header(), Path(__file__).stat().st_mtime)
     if obj.exists() and obj.stat().st_mtime >= newest:
         return obj
     cmd = [_nvcc(), *ARCH_FLAGS, *COMMON_FLAGS, "-c", str(src), "-o", str(obj)]
     if src.name in NO_FMAD:
         cmd.append("-fmad=false")
+    if tc_timing:
+        cmd.append("-DB200_TC_TIMING")
     if ptxas_info:
         cmd += ["-Xptxas", "-v"]
     if verbose:
@@ -60,32 +69,34 @@ def _compile(src: Path, verbose: bool, ptxas_info: bool) -> Path:
     return obj
 
 
-def build_native(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
+def build_native(verbose: bool = False, force: bool = False, ptxas_info: bool = False,
+                 tc_timing: bool = False) -> Path:
     """Compile and link the CUDA library; returns the path of the .so."""
+    lib_path = TIMING_LIB_PATH if tc_timing else LIB_PATH
     srcs = sorted(CSRC.glob("*.cu"))
     if not srcs:
         raise RuntimeError(f"no CUDA sources under {CSRC}")
     if force:
         for s in srcs:
-            o = s.with_suffix(".o")
+            o = s.with_suffix(".timing.o" if tc_timing else ".o")
             if o.exists():
                 o.unlink()
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        objs = list(ex.map(lambda s: _compile(s, verbose, ptxas_info), srcs))
+        objs = list(ex.map(lambda s: _compile(s, verbose, ptxas_info, tc_timing), srcs))
     newest_obj = max(o.stat().st_mtime for o in objs)
-    if LIB_PATH.exists() and LIB_PATH.stat().st_mtime >= newest_obj and not force:
-        return LIB_PATH
-    cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *map(str, objs),
+    if lib_path.exists() and lib_path.stat().st_mtime >= newest_obj and not force:
+        return lib_path
+    cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-o", str(lib_path), *map(str, objs),
            "-Xcompiler", "-fPIC", "-cudart", "static"]
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
     p = build_native(verbose="-v" in sys.argv, force="-f" in sys.argv,
-                     ptxas_info="--ptxas" in sys.argv)
+                     ptxas_info="--ptxas" in sys.argv, tc_timing="--tc-timing" in sys.argv)
     print(p)

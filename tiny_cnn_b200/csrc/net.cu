@@ -70,6 +70,11 @@ struct b200_net {
   // FFMA dX use different units of the SM and share it)
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  // third stream for the short kernels that finish a tensor-core weight gradient (fixed-order sum of
+  // the partial rows, reorder, bias gradient): the next layer's weight-gradient kernel on the side
+  // stream does not queue behind them
+  cudaStream_t fin = nullptr;
+  cudaEvent_t ev_fin_fork = nullptr, ev_fin_join = nullptr;
   // b200_net_fit_host: uploads of the next mini-batch overlap the step of the current one
   cudaStream_t copy_stream = nullptr;
   float *x_stage[2] = {nullptr, nullptr}, *t_stage[2] = {nullptr, nullptr};
@@ -215,7 +220,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
   // reads them.  They go to the side stream, so the chain of dX kernels -- the critical path --
   // does not wait for them, and kernels that leave SMs idle overlap.  One join at the end.
   cudaStream_t main_stream = ctx->stream;
-  bool side_used = false, comm_used = false;
+  bool side_used = false, comm_used = false, fin_used = false;
   int rc_side = 0;
   // One side branch, not one per layer: the large kernels of both branches each fill the SMs, so
   // more branches only interleave them and delay the dX chain (measured: two branches 0.387 ms
@@ -249,8 +254,18 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
           if (!L.tc.fwd && !L.xs_from_pool) rc_side = conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs);
           int splits = 0;
           if (!rc_side) rc_side = conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits);
-          if (!rc_side)
+          if (!rc_side && forked && net->fin) {
+            // the finishing launch leaves the side stream, whose next kernel is the next layer's dW
+            B200_CUDA(cudaEventRecord(net->ev_fin_fork, net->side));
+            B200_CUDA(cudaStreamWaitEvent(net->fin, net->ev_fin_fork, 0));
+            ctx->stream = net->fin;
             rc_side = conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db);
+            ctx->stream = net->side;
+            B200_CUDA(cudaEventRecord(net->ev_fin_join, net->fin));
+            fin_used = true;
+          } else if (!rc_side) {
+            rc_side = conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db);
+          }
         } else if (L.tc.dw_small) {
           rc_side = conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0);
         } else if (tiled_bwd) {
@@ -329,6 +344,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
         B200_CUDA(cudaEventRecord(net->ev_comm_side, net->side));
         B200_CUDA(cudaStreamWaitEvent(net->comm, net->ev_comm_side, 0));
       }
+      if (fin_used) B200_CUDA(cudaStreamWaitEvent(net->comm, net->ev_fin_join, 0));
       ctx->stream = net->comm;
       int rc = peer_reduce_push_early(ctx, &net->peer, net->grads);
       ctx->stream = main_stream;
@@ -342,17 +358,19 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
     B200_CUDA(cudaEventRecord(net->ev_join, net->side));
     B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_join, 0));
   }
+  if (fin_used) B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_fin_join, 0));
   if (comm_used) B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_comm_done, 0));
 
   return rc_side;
 }
 
-// Adam powers for a fresh optimizer object: tensor j of the first step sees
-// b^(1+j), reached by j sequential float multiplies (optimizer.h:104-110,125-126).
-int net_init_powers(b200_net *net, float b1, float b2) {
+// Adam powers: an optimizer object whose powers currently are (b1_t, b2_t) -- a fresh one has
+// (b1, b2) -- gives tensor j of the next step b1_t * b1^j, reached by j sequential float
+// multiplies (optimizer.h:104-110,125-126).
+int net_init_powers(b200_net *net, float b1, float b2, float b1_t, float b2_t) {
   size_t T = net->segs.size();
   net->pow_host.assign(2 * T + 2, 0.f);
-  float p1 = b1, p2 = b2;
+  float p1 = b1_t, p2 = b2_t;
   for (size_t j = 0; j < T; ++j) {
     net->pow_host[2 * j] = p1;
     net->pow_host[2 * j + 1] = p2;
@@ -380,7 +398,7 @@ int net_update_impl(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
 }
 
 int ensure_powers(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
-  if (opt_kind == B200_OPT_ADAM && !net->pow_init) B200_TRY(net_init_powers(net, h->b1, h->b2));
+  if (opt_kind == B200_OPT_ADAM && !net->pow_init) B200_TRY(net_init_powers(net, h->b1, h->b2, h->b1, h->b2));
   return 0;
 }
 
@@ -421,6 +439,11 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
     cudaStreamCreateWithFlags(&net->side, cudaStreamNonBlocking);
     cudaEventCreateWithFlags(&net->ev_fork, cudaEventDisableTiming);
     cudaEventCreateWithFlags(&net->ev_join, cudaEventDisableTiming);
+    if (!getenv("B200_NET_NO_FIN")) {
+      cudaStreamCreateWithFlags(&net->fin, cudaStreamNonBlocking);
+      cudaEventCreateWithFlags(&net->ev_fin_fork, cudaEventDisableTiming);
+      cudaEventCreateWithFlags(&net->ev_fin_join, cudaEventDisableTiming);
+    }
   }
   size_t off = 0;
   size_t prev_out = 0;
@@ -643,6 +666,9 @@ int b200_net_destroy(b200_net *net) {
   if (net->ev_comm_side) cudaEventDestroy(net->ev_comm_side);
   if (net->ev_comm_done) cudaEventDestroy(net->ev_comm_done);
   if (net->side) cudaStreamDestroy(net->side);
+  if (net->fin) cudaStreamDestroy(net->fin);
+  if (net->ev_fin_fork) cudaEventDestroy(net->ev_fin_fork);
+  if (net->ev_fin_join) cudaEventDestroy(net->ev_fin_join);
   if (net->ev_fork) cudaEventDestroy(net->ev_fork);
   if (net->ev_join) cudaEventDestroy(net->ev_join);
   cudaFree(net->x_dev);
@@ -782,6 +808,39 @@ int b200_net_update(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
   B200_REQUIRE(h != nullptr, "net_update: hyper-parameters are NULL");
   B200_TRY(ensure_powers(net, opt_kind, h));
   return net_update_impl(net, opt_kind, h);
+}
+
+int b200_net_set_adam_powers(b200_net *net, float b1, float b2, float b1_t, float b2_t) {
+  B200_TRY(check_net(net));
+  return net_init_powers(net, b1, b2, b1_t, b2_t);
+}
+
+static int opt_state_ptr(b200_net *net, int which, float **p) {
+  B200_REQUIRE(which == 0 || which == 1, "optimizer state %d: there are two state buffers, 0 and 1", which);
+  *p = which == 0 ? net->state0 : net->state1;
+  return 0;
+}
+
+int b200_net_get_opt_state(b200_net *net, int which, float *host_state) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(host_state != nullptr, "net_get_opt_state: NULL buffer");
+  float *src = nullptr;
+  B200_TRY(opt_state_ptr(net, which, &src));
+  B200_CUDA(cudaMemcpyAsync(host_state, src, net->n_params * sizeof(float), cudaMemcpyDeviceToHost,
+                            net->ctx->stream));
+  B200_CUDA(cudaStreamSynchronize(net->ctx->stream));
+  return 0;
+}
+
+int b200_net_set_opt_state(b200_net *net, int which, const float *host_state) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(host_state != nullptr, "net_set_opt_state: NULL buffer");
+  float *dst = nullptr;
+  B200_TRY(opt_state_ptr(net, which, &dst));
+  B200_CUDA(cudaMemcpyAsync(dst, host_state, net->n_params * sizeof(float), cudaMemcpyHostToDevice,
+                            net->ctx->stream));
+  B200_CUDA(cudaStreamSynchronize(net->ctx->stream));
+  return 0;
 }
 
 int b200_net_adam_powers(const b200_net *net, float *b1_t, float *b2_t) {

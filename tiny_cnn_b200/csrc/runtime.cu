@@ -242,6 +242,16 @@ int b200_ctx_sync(b200_ctx *ctx) {
   return 0;
 }
 
+int b200_host_alloc(size_t bytes, void **out) {
+  B200_REQUIRE(out != nullptr, "b200_host_alloc: NULL argument");
+  B200_CUDA(cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocPortable));
+  return 0;
+}
+int b200_host_free(void *ptr) {
+  if (ptr) B200_CUDA(cudaFreeHost(ptr));
+  return 0;
+}
+
 int b200_malloc(b200_ctx *ctx, size_t bytes, void **out) {
   B200_REQUIRE(ctx != nullptr && out != nullptr, "b200_malloc: NULL argument");
   B200_CUDA(cudaSetDevice(ctx->device));

@@ -12,8 +12,14 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <string>
 #include <vector>
 
+#include "tiny_dnn/core/params/conv_params.h"
+#include "tiny_dnn/core/params/fully_params.h"
+#include "tiny_dnn/core/params/maxpool_params.h"
+#include "tiny_dnn/util/nn_error.h"
+#include "tiny_dnn/util/util.h"
 #include "tinycnn_b200.h"
 
 namespace tiny_dnn {
@@ -169,6 +175,56 @@ inline void maxpool_grad_op(tensor_t &prev_delta, const tensor_t &curr_delta,
   for (size_t s = 0; s < B; ++s)
     for (size_t i = 0; i < n_out; ++i) arg[s * n_out + i] = static_cast<int32_t>(params.out2inmax[s][i]);
   check(b200_maxpool_bwd_host(ctx(), &d, dy.data(), arg.data(), dx.data(), static_cast<int>(B)));
+  unpack(dx, prev_delta);
+}
+
+// activation_layer::forward_propagation / back_propagation branch
+// (tiny_dnn/activations/activation_layer.h:74-91).  `type` is the layer's layer_type() string;
+// returns false for an activation that is not on the path (the caller then runs its own loop).
+inline int activation_kind(const std::string &type) {
+  if (type == "relu-activation") return B200_ACT_RELU;
+  if (type == "tanh-activation") return B200_ACT_TANH;
+  if (type == "softmax-activation") return B200_ACT_SOFTMAX;
+  return B200_ACT_NONE;
+}
+
+inline bool activation_op(const std::string &type, const tensor_t &x, tensor_t &y) {
+  const int kind = activation_kind(type);
+  if (kind == B200_ACT_NONE || x.empty()) return false;
+  std::vector<float> in = pack(x), out(in.size());
+  check(b200_act_fwd_host(ctx(), kind, in.data(), out.data(), static_cast<int>(x[0].size()),
+                          static_cast<int>(x.size())));
+  unpack(out, y);
+  return true;
+}
+
+inline bool activation_grad_op(const std::string &type, const tensor_t &y, const tensor_t &dy, tensor_t &dx) {
+  const int kind = activation_kind(type);
+  if (kind == B200_ACT_NONE || y.empty()) return false;
+  std::vector<float> fy = pack(y), fdy = pack(dy), fdx(fy.size());
+  check(b200_act_bwd_host(ctx(), kind, fy.data(), fdy.data(), fdx.data(), static_cast<int>(y[0].size()),
+                          static_cast<int>(y.size())));
+  unpack(fdx, dx);
+  return true;
+}
+
+// average_pooling_layer::forward_propagation branch: replaces tiny_average_pooling_kernel
+// (tiny_dnn/layers/average_pooling_layer.h:25-55)
+inline void average_pooling_op(const b200_pool_desc &d, const tensor_t &in_data, const vec_t &W, const vec_t &bias,
+                               tensor_t &out_data) {
+  std::vector<float> in = pack(in_data), out(out_data.size() * out_data[0].size());
+  check(b200_avgpool_fwd_host(ctx(), &d, in.data(), W.data(), bias.data(), out.data(),
+                              static_cast<int>(in_data.size())));
+  unpack(out, out_data);
+}
+
+// average_pooling_layer::back_propagation branch: replaces tiny_average_pooling_back_kernel
+// (average_pooling_layer.h:58-106); the batch sums of dW / db are added to row 0
+inline void average_pooling_grad_op(const b200_pool_desc &d, const tensor_t &prev_out, const vec_t &W, tensor_t &dW,
+                                    tensor_t &db, const tensor_t &curr_delta, tensor_t &prev_delta) {
+  std::vector<float> x = pack(prev_out), dy = pack(curr_delta), dx(prev_delta.size() * prev_delta[0].size());
+  check(b200_avgpool_bwd_host(ctx(), &d, x.data(), W.data(), dy.data(), dx.data(), dW[0].data(), db[0].data(),
+                              /*accumulate=*/1, static_cast<int>(prev_out.size())));
   unpack(dx, prev_delta);
 }
 

@@ -1,0 +1,362 @@
+// b200_net.h -- network<sequential>::fit on the device-resident step.
+//
+// The patched network.h (make_overlay.py) calls b200_fit_hook from network::fit
+// (tiny_dnn/network.h:840-879) right after the set-up that fit itself does
+// (set_netphase, net_.setup, optimizer.reset).  When every layer of the network
+// is on the path -- convolutional / fully-connected / max-pooling layers with
+// engine backend_t::b200, average pooling, relu / tanh / softmax in between --
+// the loss is mse / cross_entropy / cross_entropy_multiclass and the optimizer
+// is adagrad / adam / momentum, the hook replaces the loop over mini-batches:
+//
+//   layers   -> b200_layer_spec[]            (b200_net_create, cached in the network object)
+//   weights  -> flat parameter buffer        (layer::weights(): W before b, layer order)
+//   adam     -> b200_net_set_adam_powers     (continues from the object's b1_t / b2_t)
+//   batches  -> b200_net_fit_host, one call per epoch from page-locked staging
+//              (replaces train_once / train_onebatch, network.h:883-926)
+//   weights, optimizer state and adam's powers go back into the host objects after every
+//   epoch, before on_epoch_enumerate runs (which typically calls net.test()).
+//
+// Otherwise the hook returns false and fit carries on with the reference's own loop,
+// whose b200 layers then run operator by operator through b200_glue.h.
+//
+// Differences from the reference's loop, by construction: on_batch_enumerate is called
+// once per mini-batch AFTER the epoch's mini-batches have run (the device does not stop
+// between them), and stop_ongoing_training() takes effect at the next epoch boundary.
+#pragma once
+
+#include <cstring>
+#include <memory>
+#include <thread>
+#include <type_traits>
+#include <vector>
+
+#include "tiny_dnn/activations/relu_layer.h"
+#include "tiny_dnn/activations/softmax_layer.h"
+#include "tiny_dnn/activations/tanh_layer.h"
+#include "tiny_dnn/core/kernels/b200_glue.h"
+#include "tiny_dnn/layers/average_pooling_layer.h"
+#include "tiny_dnn/layers/convolutional_layer.h"
+#include "tiny_dnn/layers/fully_connected_layer.h"
+#include "tiny_dnn/layers/max_pooling_layer.h"
+#include "tiny_dnn/lossfunctions/loss_function.h"
+#include "tiny_dnn/optimizers/optimizer.h"
+
+namespace tiny_dnn {
+namespace b200 {
+
+template <typename E>
+struct loss_kind {
+  static const int value = -1;
+};
+template <>
+struct loss_kind<mse> {
+  static const int value = B200_LOSS_MSE;
+};
+template <>
+struct loss_kind<cross_entropy> {
+  static const int value = B200_LOSS_CROSS_ENTROPY;
+};
+template <>
+struct loss_kind<cross_entropy_multiclass> {
+  static const int value = B200_LOSS_CROSS_ENTROPY_MULTICLASS;
+};
+
+// how often the hook took a fit (tests and benchmarks read it)
+inline unsigned long long &device_fit_count() {
+  static unsigned long long n = 0;
+  return n;
+}
+
+// page-locked staging buffer
+struct pinned_buffer {
+  float *p = nullptr;
+  size_t n = 0;
+  void reserve(size_t floats) {
+    if (floats <= n) return;
+    release();
+    void *q = nullptr;
+    check(b200_host_alloc(floats * sizeof(float), &q));
+    p = static_cast<float *>(q);
+    n = floats;
+  }
+  void release() {
+    if (p) b200_host_free(p);
+    p = nullptr;
+    n = 0;
+  }
+  ~pinned_buffer() { release(); }
+};
+
+// the device twin of one network<sequential>, kept in the network object
+struct device_twin {
+  b200_net *net = nullptr;
+  std::vector<const layer *> layers;          // identity of the network it was built for
+  std::vector<std::vector<size_t>> shapes;    // weight tensor lengths per layer
+  int max_batch = 0;
+  std::vector<std::vector<uint8_t>> tables;   // connection tables the specs point into
+  pinned_buffer x, t;
+  ~device_twin() {
+    if (net) b200_net_destroy(net);
+  }
+};
+
+// b200_layer_spec of one layer, or false when the layer is not on the path
+inline bool spec_of(layer *l, b200_layer_spec &s, std::vector<uint8_t> &tbl) {
+  std::memset(&s, 0, sizeof(s));
+  if (auto *c = dynamic_cast<convolutional_layer *>(l)) {
+    if (c->engine() != core::backend_t::b200) return false;
+    s.kind = B200_LAYER_CONV;
+    s.conv = conv_desc(c->b200_params(), tbl);
+    s.conv.input_is_padded = 0;  // the net pads on the device
+    return true;
+  }
+  if (auto *f = dynamic_cast<fully_connected_layer *>(l)) {
+    if (f->engine() != core::backend_t::b200) return false;
+    const core::fully_params &p = f->b200_params();
+    s.kind = B200_LAYER_FC;
+    s.fc_in = static_cast<int32_t>(p.in_size_);
+    s.fc_out = static_cast<int32_t>(p.out_size_);
+    s.fc_has_bias = p.has_bias_ ? 1 : 0;
+    return true;
+  }
+  if (auto *m = dynamic_cast<max_pooling_layer *>(l)) {
+    if (m->engine() != core::backend_t::b200) return false;
+    s.kind = B200_LAYER_MAXPOOL;
+    s.pool = pool_desc(m->b200_params());
+    return true;
+  }
+  if (auto *a = dynamic_cast<average_pooling_layer *>(l)) {
+    s.kind = B200_LAYER_AVGPOOL;
+    s.pool = a->b200_pool_desc();
+    return true;
+  }
+  if (dynamic_cast<relu_layer *>(l)) {
+    s.kind = B200_LAYER_RELU;
+    return true;
+  }
+  if (dynamic_cast<tanh_layer *>(l)) {
+    s.kind = B200_LAYER_TANH;
+    return true;
+  }
+  if (dynamic_cast<softmax_layer *>(l)) {
+    s.kind = B200_LAYER_SOFTMAX;
+    return true;
+  }
+  return false;
+}
+
+struct opt_choice {
+  int kind = -1;
+  b200_opt_hyper h{};
+  int n_state = 0;  // state buffers the optimizer keeps per weight tensor
+  adam *as_adam = nullptr;
+  std::unordered_map<const vec_t *, vec_t> *maps = nullptr;
+};
+
+// adagrad / adam / momentum by RTTI (the reference identifies node types the same way,
+// nodes.h:134-146); eps is private in the reference and constant 1e-8 (optimizer.h:58,110)
+inline opt_choice choose_optimizer(optimizer *o) {
+  opt_choice c;
+  c.h.eps = 1e-8f;
+  if (auto *a = dynamic_cast<adagrad *>(o)) {
+    c.kind = B200_OPT_ADAGRAD;
+    c.h.alpha = a->alpha;
+    c.n_state = 1;
+    c.maps = a->b200_maps();
+  } else if (auto *a = dynamic_cast<adam *>(o)) {
+    c.kind = B200_OPT_ADAM;
+    c.h.alpha = a->alpha;
+    c.h.b1 = a->b1;
+    c.h.b2 = a->b2;
+    c.h.b1_t = a->b1_t;
+    c.h.b2_t = a->b2_t;
+    c.n_state = 2;
+    c.as_adam = a;
+    c.maps = a->b200_maps();
+  } else if (auto *m = dynamic_cast<momentum *>(o)) {
+    c.kind = B200_OPT_MOMENTUM;
+    c.h.alpha = m->alpha;
+    c.h.mu = m->mu;
+    c.h.lambda = m->lambda;
+    c.n_state = 1;
+    c.maps = m->b200_maps();
+  }
+  return c;
+}
+
+template <typename Net>
+std::shared_ptr<device_twin> twin_for(Net &nn, int batch) {
+  const size_t depth = nn.depth();
+  std::vector<const layer *> ids(depth);
+  std::vector<std::vector<size_t>> shapes(depth);
+  for (size_t i = 0; i < depth; ++i) {
+    ids[i] = nn[i];
+    for (auto *w : nn[i]->weights()) shapes[i].push_back(w->size());
+  }
+  auto cached = std::static_pointer_cast<device_twin>(nn.b200_twin_);
+  if (cached && cached->layers == ids && cached->shapes == shapes && cached->max_batch >= batch) return cached;
+  auto tw = std::make_shared<device_twin>();
+  std::vector<b200_layer_spec> specs(depth);
+  tw->tables.resize(depth);
+  for (size_t i = 0; i < depth; ++i)
+    if (!spec_of(nn[i], specs[i], tw->tables[i])) return nullptr;
+  for (size_t i = 0; i < depth; ++i)  // the tables moved with the vector of vectors: point again
+    if (specs[i].kind == B200_LAYER_CONV && specs[i].conv.tbl) specs[i].conv.tbl = tw->tables[i].data();
+  // a shape the library declines (b200_net_create says why) leaves the reference loop in charge
+  if (b200_net_create(ctx(), specs.data(), static_cast<int>(depth), batch, &tw->net) != 0) return nullptr;
+  tw->layers = ids;
+  tw->shapes = shapes;
+  tw->max_batch = batch;
+  nn.b200_twin_ = tw;
+  return tw;
+}
+
+template <typename Net>
+void weights_to_device(Net &nn, device_twin &tw) {
+  std::vector<float> flat(b200_net_param_count(tw.net));
+  size_t off = 0;
+  for (size_t i = 0; i < nn.depth(); ++i)
+    for (auto *w : nn[i]->weights()) {
+      std::copy(w->begin(), w->end(), flat.begin() + off);
+      off += w->size();
+    }
+  check(b200_net_set_params(tw.net, flat.data()));
+}
+
+// weights, optimizer state (stateful_optimizer::E_, keyed by the weight vector's address) and
+// adam's powers back into the host objects
+template <typename Net>
+void state_to_host(Net &nn, device_twin &tw, opt_choice &oc, long long steps_done) {
+  const size_t n = b200_net_param_count(tw.net);
+  std::vector<float> flat(n);
+  check(b200_net_get_params(tw.net, flat.data()));
+  size_t off = 0;
+  for (size_t i = 0; i < nn.depth(); ++i)
+    for (auto *w : nn[i]->weights()) {
+      std::copy(flat.begin() + off, flat.begin() + off + w->size(), w->begin());
+      off += w->size();
+    }
+  for (int k = 0; k < oc.n_state; ++k) {
+    check(b200_net_get_opt_state(tw.net, k, flat.data()));
+    off = 0;
+    for (size_t i = 0; i < nn.depth(); ++i)
+      for (auto *w : nn[i]->weights()) {
+        vec_t &e = oc.maps[k][w];
+        e.assign(flat.begin() + off, flat.begin() + off + w->size());
+        off += w->size();
+      }
+  }
+  if (oc.as_adam) {
+    // adam::update multiplies the powers once per call: tensors x steps sequential float products
+    // (optimizer.h:125-126); the device table did the same multiplications
+    const long long calls = steps_done * static_cast<long long>(b200_net_tensor_count(tw.net));
+    for (long long c = 0; c < calls; ++c) {
+      oc.as_adam->b1_t *= oc.as_adam->b1;
+      oc.as_adam->b2_t *= oc.as_adam->b2;
+    }
+  }
+}
+
+template <typename Error, typename Optimizer, typename OnBatch, typename OnEpoch>
+bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<tensor_t> &inputs,
+                    const std::vector<tensor_t> &desired_outputs, size_t batch_size, int epoch,
+                    OnBatch on_batch_enumerate, OnEpoch on_epoch_enumerate,
+                    const std::vector<tensor_t> &t_cost, const bool *stop) {
+  const int loss = loss_kind<Error>::value;
+  if (loss < 0 || !t_cost.empty() || inputs.empty() || batch_size == 0 || nn.depth() == 0) return false;
+  if (inputs[0].size() != 1 || desired_outputs.size() != inputs.size() || desired_outputs[0].size() != 1)
+    return false;
+  opt_choice oc = choose_optimizer(static_cast<optimizer *>(&opt));
+  if (oc.kind < 0) return false;
+  bool any_b200 = false;
+  for (size_t i = 0; i < nn.depth(); ++i) any_b200 = any_b200 || nn[i]->engine() == core::backend_t::b200;
+  if (!any_b200) return false;
+  const int batch = static_cast<int>(std::min(batch_size, inputs.size()));
+  std::shared_ptr<device_twin> tw = twin_for(nn, batch);
+  if (!tw) return false;
+  const size_t in_dim = static_cast<size_t>(b200_net_in_dim(tw->net));
+  const size_t out_dim = static_cast<size_t>(b200_net_out_dim(tw->net));
+  if (inputs[0][0].size() != in_dim || desired_outputs[0][0].size() != out_dim) return false;
+
+  const size_t N = inputs.size();
+  tw->x.reserve(N * in_dim);
+  tw->t.reserve(N * out_dim);
+  // The reference keeps one heap vector per sample; the device wants rows back to back in
+  // page-locked memory.  Rows [s0, s1) are packed by a few threads, and during the first epoch the
+  // packing of the next run of mini-batches overlaps the device's work on the current one.
+  float *xp = tw->x.p, *tp = tw->t.p;
+  auto pack = [&inputs, &desired_outputs, xp, tp, in_dim, out_dim](size_t s0, size_t s1) {
+    unsigned nt = std::thread::hardware_concurrency();
+    nt = nt == 0 ? 1 : nt > 4 ? 4 : nt;
+    if (s1 - s0 < 64) nt = 1;
+    auto part = [&](size_t a, size_t b) {
+      for (size_t s = a; s < b; ++s) {
+        std::copy(inputs[s][0].begin(), inputs[s][0].end(), xp + s * in_dim);
+        std::copy(desired_outputs[s][0].begin(), desired_outputs[s][0].end(), tp + s * out_dim);
+      }
+    };
+    std::vector<std::thread> helpers;
+    const size_t per = (s1 - s0 + nt - 1) / nt;
+    for (unsigned k = 1; k < nt; ++k) {
+      const size_t a = s0 + k * per, b = std::min(s1, a + per);
+      if (a < b) helpers.emplace_back(part, a, b);
+    }
+    part(s0, std::min(s1, s0 + per));
+    for (auto &h : helpers) h.join();
+  };
+  weights_to_device(nn, *tw);
+  // fit() has just called optimizer.reset(): the state maps are empty, adam's powers carry on
+  check(b200_net_opt_reset(tw->net, 1));
+  if (oc.as_adam) check(b200_net_set_adam_powers(tw->net, oc.h.b1, oc.h.b2, oc.as_adam->b1_t, oc.as_adam->b2_t));
+  const long long steps_per_epoch = static_cast<long long>((N + batch - 1) / batch);
+  const size_t run = static_cast<size_t>(batch) * 16;  // mini-batches per library call in the first epoch
+  for (int iter = 0; iter < epoch && !*stop; ++iter) {
+    if (iter == 0) {
+      pack(0, std::min(N, run));
+      for (size_t s0 = 0; s0 < N; s0 += run) {
+        const size_t s1 = std::min(N, s0 + run), s2 = std::min(N, s1 + run);
+        std::thread ahead;
+        if (s1 < N) ahead = std::thread(pack, s1, s2);
+        const int rc = b200_net_fit_host(tw->net, xp + s0 * in_dim, tp + s0 * out_dim, static_cast<long long>(s1 - s0),
+                                         batch, 1, loss, oc.kind, &oc.h, nullptr);
+        if (ahead.joinable()) ahead.join();
+        check(rc);
+      }
+    } else {
+      check(b200_net_fit_host(tw->net, xp, tp, static_cast<long long>(N), batch, 1, loss, oc.kind, &oc.h, nullptr));
+    }
+    check(b200_ctx_sync(ctx()));
+    state_to_host(nn, *tw, oc, steps_per_epoch);
+    for (long long b = 0; b < steps_per_epoch; ++b) on_batch_enumerate();
+    on_epoch_enumerate();
+  }
+  nn.set_netphase(net_phase::test);
+  ++device_fit_count();
+  return true;
+}
+
+template <typename Error, typename Net, typename Optimizer, typename OnBatch, typename OnEpoch>
+bool fit_dispatch(std::false_type, Net &, Optimizer &, const std::vector<tensor_t> &, const std::vector<tensor_t> &,
+                  size_t, int, OnBatch, OnEpoch, const std::vector<tensor_t> &, const bool *) {
+  return false;  // graph networks keep the reference loop
+}
+template <typename Error, typename Net, typename Optimizer, typename OnBatch, typename OnEpoch>
+bool fit_dispatch(std::true_type, Net &nn, Optimizer &opt, const std::vector<tensor_t> &inputs,
+                  const std::vector<tensor_t> &desired_outputs, size_t batch_size, int epoch, OnBatch on_batch,
+                  OnEpoch on_epoch, const std::vector<tensor_t> &t_cost, const bool *stop) {
+  return fit_sequential<Error>(nn, opt, inputs, desired_outputs, batch_size, epoch, on_batch, on_epoch, t_cost,
+                               stop);
+}
+
+}  // namespace b200
+
+// declared in the patched network.h, called from network::fit
+template <typename Error, typename Net, typename Optimizer, typename OnBatch, typename OnEpoch>
+bool b200_fit_hook(Net &nn, Optimizer &opt, const std::vector<tensor_t> &inputs,
+                   const std::vector<tensor_t> &desired_outputs, size_t batch_size, int epoch, OnBatch on_batch,
+                   OnEpoch on_epoch, const std::vector<tensor_t> &t_cost, const bool *stop) {
+  return b200::fit_dispatch<Error>(std::is_same<Net, network<sequential>>(), nn, opt, inputs,
+                                   desired_outputs, batch_size, epoch, on_batch, on_epoch, t_cost, stop);
+}
+
+}  // namespace tiny_dnn

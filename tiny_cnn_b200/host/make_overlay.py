@@ -8,9 +8,9 @@ placed BEFORE the tiny-dnn tree on the compiler's include path:
 
 The overlay holds patched copies of exactly the headers that carry the backend
 switch, produced here from the user's own tiny-dnn tree by anchored text edits
-(nothing of tiny-dnn is stored in this repository), plus the two headers of this
-directory (b200_glue.h, b200_backend.h) under tiny_dnn/core/kernels/ and
-tiny_dnn/core/.  Every edit asserts that its anchor is present, so a tiny-dnn
+(nothing of tiny-dnn is stored in this repository), plus the three headers of this
+directory (b200_glue.h, b200_backend.h, b200_net.h) under tiny_dnn/core/kernels/
+and tiny_dnn/core/.  Every edit asserts that its anchor is present, so a tiny-dnn
 version the patches do not fit fails loudly instead of silently mis-patching.
 
     python -m tiny_cnn_b200.host.make_overlay --reference /path/to/tiny-dnn --out build/overlay
@@ -99,9 +99,16 @@ def patch_maxpool_grad_op(t, p):
     return t
 
 
+def _params_accessor(t, p, anchor, type_name):
+    """public read access to the layer's private params_ (the device twin of a network is
+    described from them)"""
+    return _edit(t, anchor, anchor + f"  const {type_name} &b200_params() const {{ return params_; }}\n\n", p)
+
+
 def patch_conv_layer(t, p):
     # the same Conv2dOp / Conv2dGradOp objects serve the new engine, so that
     # layer::set_backend_type() can switch engines at run time
+    t = _params_accessor(t, p, "class convolutional_layer : public layer {\n public:\n", "core::conv_params")
     return _edit(t, "    if (backend_type == core::backend_t::internal ||\n"
                     "        backend_type == core::backend_t::nnpack ||\n"
                     "        backend_type == core::backend_t::avx) {\n"
@@ -114,6 +121,7 @@ def patch_conv_layer(t, p):
 
 
 def patch_fc_layer(t, p):
+    t = _params_accessor(t, p, "class fully_connected_layer : public layer {\n public:\n", "core::fully_params")
     return _edit(t, "    if (backend_type == core::backend_t::internal ||\n"
                     "        backend_type == core::backend_t::avx ||",
                  "    if (backend_type == core::backend_t::internal ||\n"
@@ -122,6 +130,7 @@ def patch_fc_layer(t, p):
 
 
 def patch_maxpool_layer(t, p):
+    t = _params_accessor(t, p, "class max_pooling_layer : public layer {\n public:\n", "core::maxpool_params")
     return _edit(t, "    if (backend_type == core::backend_t::internal ||\n"
                     "        backend_type == core::backend_t::nnpack ||\n"
                     "        backend_type == core::backend_t::avx) {\n"
@@ -146,6 +155,99 @@ def patch_qconv_layer(t, p):
     return t
 
 
+def patch_avgpool_layer(t, p):
+    """average_pooling_layer has no engine argument; layer::set_backend_type(b200) selects the
+    device kernels (average_pooling_layer.h:186-221)."""
+    t = _edit(t, '#include "tiny_dnn/util/util.h"\n', '#include "tiny_dnn/util/util.h"\n' + GLUE_INCLUDE, p)
+    t = _edit(t, "    tiny_average_pooling_kernel(parallelize_, in_data, out_data, out_,\n"
+                 "                                Base::scale_factor_, Base::out2wi_);",
+              "    if (layer::engine() == core::backend_t::b200) {\n"
+              "      b200::average_pooling_op(b200_pool_desc(), *in_data[0], (*in_data[1])[0], (*in_data[2])[0],\n"
+              "                               *out_data[0]);\n"
+              "      return;\n"
+              "    }\n"
+              "    tiny_average_pooling_kernel(parallelize_, in_data, out_data, out_,\n"
+              "                                Base::scale_factor_, Base::out2wi_);", p)
+    t = _edit(t, "    tiny_average_pooling_back_kernel(\n      parallelize_, in_data, out_data, out_grad, in_grad, in_,",
+              "    if (layer::engine() == core::backend_t::b200) {\n"
+              "      b200::average_pooling_grad_op(b200_pool_desc(), *in_data[0], (*in_data[1])[0], *in_grad[1],\n"
+              "                                    *in_grad[2], *out_grad[0], *in_grad[0]);\n"
+              "      return;\n"
+              "    }\n"
+              "    tiny_average_pooling_back_kernel(\n      parallelize_, in_data, out_data, out_grad, in_grad, in_,", p)
+    t = _edit(t, "  std::pair<size_t, size_t> pool_size() const {\n",
+              "  ::b200_pool_desc b200_pool_desc() const {\n"
+              "    ::b200_pool_desc d{};\n"
+              "    d.in_w = static_cast<int32_t>(in_.width_);\n"
+              "    d.in_h = static_cast<int32_t>(in_.height_);\n"
+              "    d.in_c = static_cast<int32_t>(in_.depth_);\n"
+              "    d.out_w = static_cast<int32_t>(out_.width_);\n"
+              "    d.out_h = static_cast<int32_t>(out_.height_);\n"
+              "    d.pool_w = static_cast<int32_t>(pool_size_x_);\n"
+              "    d.pool_h = static_cast<int32_t>(pool_size_y_);\n"
+              "    d.stride_w = static_cast<int32_t>(stride_x_);\n"
+              "    d.stride_h = static_cast<int32_t>(stride_y_);\n"
+              "    return d;\n"
+              "  }\n\n"
+              "  std::pair<size_t, size_t> pool_size() const {\n", p)
+    return t
+
+
+def patch_activation_layer(t, p):
+    """relu / tanh / softmax under layer::set_backend_type(b200) (activation_layer.h:74-91); the
+    other activations keep their own loops."""
+    t = _edit(t, "namespace tiny_dnn {\n", GLUE_INCLUDE + "\nnamespace tiny_dnn {\n", p)
+    t = _edit(t, "    const tensor_t &x = *in_data[0];\n    tensor_t &y       = *out_data[0];\n",
+              "    const tensor_t &x = *in_data[0];\n    tensor_t &y       = *out_data[0];\n"
+              "    if (layer::engine() == core::backend_t::b200 && b200::activation_op(layer_type(), x, y)) return;\n", p)
+    t = _edit(t, "    const tensor_t &y  = *out_data[0];\n",
+              "    const tensor_t &y  = *out_data[0];\n"
+              "    if (layer::engine() == core::backend_t::b200 && b200::activation_grad_op(layer_type(), y, dy, dx))\n"
+              "      return;\n", p)
+    return t
+
+
+def patch_layer_h(t, p):
+    """layer::set_sample_count (layer.h:699-718) grows every gradient tensor to one row per sample.
+    The device kernels return the batch sum of a weight gradient in row 0, so under engine b200
+    the weight-gradient tensors stay as they are (one row for a fresh layer): edge::merge_grads
+    (node.h:89-103) then reads len(W) floats instead of B x len(W)."""
+    return _edit(t, "      resize(ith_in_node(i)->get_gradient());\n    }\n\n    for (size_t i = 0; i < out_channels_; i++) {",
+                 "      if (backend_type_ == core::backend_t::b200 && is_trainable_weight(in_type_[i])) continue;\n"
+                 "      resize(ith_in_node(i)->get_gradient());\n    }\n\n    for (size_t i = 0; i < out_channels_; i++) {", p)
+
+
+def patch_optimizer_h(t, p):
+    """public access to the per-weight state of adagrad / adam / momentum (stateful_optimizer::E_,
+    optimizer.h:34-48): the device-resident fit writes its optimizer state back into these maps."""
+    return _edit(t, " protected:\n  template <int Index>\n  vec_t &get(const vec_t &key) {",
+                 "  std::unordered_map<const vec_t *, vec_t> *b200_maps() { return E_; }\n\n"
+                 " protected:\n  template <int Index>\n  vec_t &get(const vec_t &key) {", p)
+
+
+def patch_network_h(t, p):
+    """network::fit (network.h:840-879) hands the loop over mini-batches to the device-resident step
+    when the whole network is on the path (b200_net.h); otherwise nothing changes."""
+    t = _edit(t, "template <typename NetType>\nclass network;\n",
+              "template <typename NetType>\nclass network;\n\n"
+              "// defined in tiny_dnn/core/b200_net.h (included at the end of this file)\n"
+              "template <typename Error, typename Net, typename Optimizer, typename OnBatch, typename OnEpoch>\n"
+              "bool b200_fit_hook(Net &nn, Optimizer &optimizer, const std::vector<tensor_t> &inputs,\n"
+              "                   const std::vector<tensor_t> &desired_outputs, size_t batch_size, int epoch,\n"
+              "                   OnBatch on_batch, OnEpoch on_epoch, const std::vector<tensor_t> &t_cost,\n"
+              "                   const bool *stop);\n", p)
+    t = _edit(t, "    optimizer.reset();\n    stop_training_ = false;\n",
+              "    optimizer.reset();\n    stop_training_ = false;\n"
+              "    if (b200_fit_hook<Error>(*this, optimizer, inputs, desired_outputs, batch_size, epoch,\n"
+              "                             on_batch_enumerate, on_epoch_enumerate, t_cost, &stop_training_))\n"
+              "      return true;\n", p)
+    t = _edit(t, "  void stop_ongoing_training() { stop_training_ = true; }\n",
+              "  void stop_ongoing_training() { stop_training_ = true; }\n\n"
+              "  // device twin of this network under engine backend_t::b200 (tiny_dnn/core/b200_net.h)\n"
+              "  std::shared_ptr<void> b200_twin_;\n", p)
+    return t + '\n#include "tiny_dnn/core/b200_net.h"\n'
+
+
 PATCHES = {
     "tiny_dnn/core/backend.h": patch_backend_h,
     "tiny_dnn/core/kernels/conv2d_op.h": patch_conv2d_op,
@@ -158,6 +260,11 @@ PATCHES = {
     "tiny_dnn/layers/fully_connected_layer.h": patch_fc_layer,
     "tiny_dnn/layers/max_pooling_layer.h": patch_maxpool_layer,
     "tiny_dnn/layers/quantized_convolutional_layer.h": patch_qconv_layer,
+    "tiny_dnn/layers/average_pooling_layer.h": patch_avgpool_layer,
+    "tiny_dnn/activations/activation_layer.h": patch_activation_layer,
+    "tiny_dnn/layers/layer.h": patch_layer_h,
+    "tiny_dnn/optimizers/optimizer.h": patch_optimizer_h,
+    "tiny_dnn/network.h": patch_network_h,
 }
 
 
@@ -173,6 +280,7 @@ def make_overlay(reference: Path, out: Path) -> Path:
     (out / "tiny_dnn/core/kernels").mkdir(parents=True, exist_ok=True)
     shutil.copyfile(HERE / "b200_glue.h", out / "tiny_dnn/core/kernels/b200_glue.h")
     shutil.copyfile(HERE / "b200_backend.h", out / "tiny_dnn/core/b200_backend.h")
+    shutil.copyfile(HERE / "b200_net.h", out / "tiny_dnn/core/b200_net.h")
     return out
 
 
