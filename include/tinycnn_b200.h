@@ -356,18 +356,28 @@ B200_API int b200_loss_value(b200_ctx *ctx, int kind, const float *y, const floa
 /* Gradient merge + optimizer  (a10-a11)                                       */
 /* ------------------------------------------------------------------------- */
 
-enum { B200_OPT_ADAGRAD = 0, B200_OPT_ADAM = 1, B200_OPT_MOMENTUM = 2 };
+/* every optimizer of tiny_dnn/optimizers/optimizer.h: adagrad :57-71, adam :103-137,
+ * momentum :201-218, RMSprop :79-95, adamax :145-175, gradient_descent :182-193,
+ * nesterov_momentum :227-245 */
+enum {
+  B200_OPT_ADAGRAD = 0,
+  B200_OPT_ADAM = 1,
+  B200_OPT_MOMENTUM = 2,
+  B200_OPT_RMSPROP = 3,
+  B200_OPT_ADAMAX = 4,
+  B200_OPT_GRADIENT_DESCENT = 5,
+  B200_OPT_NESTEROV_MOMENTUM = 6
+};
 
-/* Public hyper-parameters of the reference optimizers
- * (tiny_dnn/optimizers/optimizer.h:57-71,103-137,201-218). */
+/* Public hyper-parameters of the reference optimizers. */
 typedef struct b200_opt_hyper {
-  float alpha;   /* learning rate (all three)                    */
-  float b1, b2;  /* adam decay terms                             */
-  float b1_t;    /* adam b1^t for THIS update call (per tensor)  */
-  float b2_t;    /* adam b2^t for THIS update call               */
-  float mu;      /* momentum                                     */
-  float lambda;  /* momentum weight decay                        */
-  float eps;     /* 1e-8 in the reference (private member)       */
+  float alpha;   /* learning rate (all)                                  */
+  float b1, b2;  /* adam / adamax decay terms                            */
+  float b1_t;    /* adam / adamax b1^t for THIS update call (per tensor) */
+  float b2_t;    /* adam b2^t for THIS update call                       */
+  float mu;      /* momentum, nesterov_momentum; RMSprop's decay term    */
+  float lambda;  /* weight decay of the three SGD forms                  */
+  float eps;     /* 1e-8 in the reference (private member)               */
 } b200_opt_hyper;
 
 /*
@@ -379,9 +389,12 @@ B200_API int b200_merge_grads(b200_ctx *ctx, const float *grads, int rows, size_
 
 /*
  * One optimizer::update call on one parameter tensor
- * (adagrad optimizer.h:60-66, adam :112-127, momentum :205-213).  state0 is g
- * (adagrad), mt (adam) or dWprev (momentum); state1 is vt (adam only).  The
- * caller advances b1_t/b2_t after each call as adam::update does (:125-126).
+ * (adagrad optimizer.h:60-66, adam :112-127, momentum :205-213, RMSprop :82-89,
+ * adamax :153-166, gradient_descent :185-188, nesterov_momentum :233-240).  state0 is g
+ * (adagrad, RMSprop), mt (adam, adamax) or dWprev (momentum, nesterov_momentum); state1 is
+ * vt (adam) or ut (adamax); gradient_descent keeps none.  The caller advances b1_t / b2_t
+ * after each call as adam::update and adamax::update do (:125-126, :165).  adamax's step
+ * size alpha / (1.0 - b1_t) is formed in double precision, as the reference's literal does.
  */
 B200_API int b200_opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper *h, const float *dW,
                              float *W, float *state0, float *state1, size_t len);
@@ -560,16 +573,64 @@ B200_API int b200_net_train_step_host(b200_net *net, const float *x_host, const 
 /*
  * network::fit over HOST arrays (tiny_dnn/network.h:840-879): `epochs` passes
  * over n_samples rows of x_host [n_samples][in_dim] / t_host [n_samples][out_dim]
- * in mini-batches of `batch` (the last one of a pass may be smaller, as in the
- * reference), one training step each.  The upload of the next mini-batch runs
+ * in mini-batches of `batch`, one training step each.  A last mini-batch with fewer
+ * samples runs as the reference runs it (network.h:883-926): the new samples replace the
+ * first rows of the batch buffers and the step still covers all `batch` rows, the rest
+ * being the previous step's; exactly one left-over sample is a one-sample step.  (So
+ * n_samples must be at least `batch`, or 1.)  The upload of the next mini-batch runs
  * on a second stream while the current step computes (pinned host memory makes
  * that overlap real).  With `out_host` [n_samples][out_dim] not NULL the
- * forward output of every step is copied back to its rows (the last epoch's
- * values remain).  Returns after everything has finished.
+ * forward output of every step's NEW samples is copied back to their rows (the last
+ * epoch's values remain).  Returns after everything has finished.
  */
 B200_API int b200_net_fit_host(b200_net *net, const float *x_host, const float *t_host,
                                long long n_samples, int batch, int epochs, int loss_kind,
                                int opt_kind, const b200_opt_hyper *h, float *out_host);
+
+/* ------------------------------------------------------------------------- */
+/* The callers' data formats: raw dataset bytes to device batches              */
+/* ------------------------------------------------------------------------- */
+
+enum { B200_IMAGE_CIFAR10 = 0, B200_IMAGE_MNIST = 1 };
+
+/*
+ * How uint8 pixels become the floats of the first layer's input rows.  `mode` selects the
+ * reference parser whose arithmetic is reproduced bit for bit:
+ *   B200_IMAGE_CIFAR10  parse_cifar10 (tiny_dnn/io/cifar10_parser.h:26-86):
+ *                       scale_min + (scale_max - scale_min) * c / 255
+ *   B200_IMAGE_MNIST    parse_mnist_images (tiny_dnn/io/mnist_parser.h:43-68,130-157):
+ *                       (c / 255) * (scale_max - scale_min) + scale_min
+ * Images are planar [channels][height][width] bytes (a CIFAR-10 record without its label byte, the
+ * pixels of an idx3 file); the output rows are [channels][height + 2*y_padding][width +
+ * 2*x_padding] floats with the border filled with scale_min, as both parsers do.
+ */
+typedef struct b200_image_desc {
+  int32_t mode;
+  int32_t channels, height, width;
+  int32_t x_padding, y_padding;
+  float scale_min, scale_max;
+} b200_image_desc;
+
+/* n images of DEVICE bytes -> n DEVICE float rows. */
+B200_API int b200_images_u8_to_float(b200_ctx *ctx, const b200_image_desc *d, const uint8_t *src,
+                                     long long n, float *dst);
+/*
+ * n DEVICE class labels -> n DEVICE target rows of out_dim floats: target_min everywhere,
+ * target_max at the label (nodes::label2vec, tiny_dnn/nodes.h:180-189; the two values are the
+ * output range of the network's last layer, nodes.h:147-156).
+ */
+B200_API int b200_labels_to_targets(b200_ctx *ctx, const uint8_t *labels, long long n, int out_dim,
+                                    float target_min, float target_max, float *dst);
+/*
+ * network::train (network.h:268-307) from the dataset's own bytes: like b200_net_fit_host, but
+ * every mini-batch is uploaded as uint8 images + uint8 labels (HOST memory, page-locked for
+ * overlap) and converted on the device by the two functions above before its step.  The net's
+ * input size must equal the padded image size and its output size must exceed every label.
+ */
+B200_API int b200_net_fit_u8_host(b200_net *net, const b200_image_desc *d, const uint8_t *images_host,
+                                  const uint8_t *labels_host, long long n_samples, int batch, int epochs,
+                                  float target_min, float target_max, int loss_kind, int opt_kind,
+                                  const b200_opt_hyper *h, float *out_host);
 
 /* Adam powers currently held by the net: what the next update of the FIRST tensor will use,
  * i.e. the b1_t / b2_t members of the reference's adam object at that moment (optimizer.h:129-133). */

@@ -530,9 +530,22 @@ ORC_API void orc_opt_update(int kind, const b200_opt_hyper *h, const float *dW, 
       s0[i] = h->b1 * s0[i] + (1.f - h->b1) * dW[i];
       s1[i] = h->b2 * s1[i] + (1.f - h->b2) * dW[i] * dW[i];
       W[i] -= h->alpha * (s0[i] / (1.f - h->b1_t)) / sqrtf((s1[i] / (1.f - h->b2_t)) + h->eps);
-    } else {
+    } else if (kind == B200_OPT_MOMENTUM) {
       float V = h->mu * s0[i] - h->alpha * (dW[i] + W[i] * h->lambda);
       W[i] += V;
+      s0[i] = V;
+    } else if (kind == B200_OPT_RMSPROP) { /* optimizer.h:82-89 */
+      s0[i] = h->mu * s0[i] + (1 - h->mu) * dW[i] * dW[i];
+      W[i] -= h->alpha * dW[i] / sqrtf(s0[i] + h->eps);
+    } else if (kind == B200_OPT_ADAMAX) { /* optimizer.h:153-166; the literal 1.0 makes the step size a double */
+      s0[i] = h->b1 * s0[i] + (1.f - h->b1) * dW[i];
+      s1[i] = fmaxf(h->b2 * s1[i], fabsf(dW[i]));
+      W[i] -= (h->alpha / (1.0 - h->b1_t)) * (s0[i] / (s1[i] + h->eps));
+    } else if (kind == B200_OPT_GRADIENT_DESCENT) { /* optimizer.h:185-188 */
+      W[i] = W[i] - h->alpha * (dW[i] + h->lambda * W[i]);
+    } else { /* nesterov_momentum, optimizer.h:233-240 */
+      float V = h->mu * s0[i] - h->alpha * (dW[i] + W[i] * h->lambda);
+      W[i] += (-h->mu) * s0[i] + (1 + h->mu) * V;
       s0[i] = V;
     }
   }
@@ -1005,7 +1018,7 @@ ORC_API void orc_net_backward(orc_net *net, const float *x, const float *t, int 
  * order; adam's powers advance after every call (optimizer.h:125-126). */
 ORC_API void orc_net_update(orc_net *net, int opt_kind, const b200_opt_hyper *h) {
   b200_opt_hyper hh = *h;
-  if (opt_kind == B200_OPT_ADAM && !net->powers_init) {
+  if ((opt_kind == B200_OPT_ADAM || opt_kind == B200_OPT_ADAMAX) && !net->powers_init) {
     net->b1_t = h->b1;
     net->b2_t = h->b2;
     net->powers_init = 1;
@@ -1015,10 +1028,73 @@ ORC_API void orc_net_update(orc_net *net, int opt_kind, const b200_opt_hyper *h)
     hh.b2_t = net->b2_t;
     orc_opt_update(opt_kind, &hh, net->grads + net->t_off[k], net->params + net->t_off[k],
                    net->s0 + net->t_off[k], net->s1 + net->t_off[k], net->t_len[k]);
-    if (opt_kind == B200_OPT_ADAM) {
+    if (opt_kind == B200_OPT_ADAM || opt_kind == B200_OPT_ADAMAX) {
       net->b1_t *= h->b1;
-      net->b2_t *= h->b2;
+      net->b2_t *= h->b2; /* adamax has no b2_t; the value is unused there */
     }
+  }
+}
+
+/* network::fit (tiny_dnn/network.h:840-926) for `epochs` passes over n samples: the loop over
+ * mini-batches with the reference's batch buffers.  in_batch_ / t_batch_ are sized to the
+ * mini-batch once (:858-859); train_onebatch copies the step's `size` samples over their first
+ * rows and runs fprop / bprop on the whole buffers (:918-924), so a last mini-batch of
+ * 1 < size < batch samples is a full step whose remaining rows are the previous step's; a single
+ * left-over sample takes train_once's one-sample branch (:893-895). */
+ORC_API void orc_net_train_step(orc_net *net, const float *x, const float *t, int B, int loss_kind,
+                                int opt_kind, const b200_opt_hyper *h);
+
+ORC_API int orc_net_fit(orc_net *net, const float *x, const float *t, long long n, int batch, int epochs,
+                        int loss_kind, int opt_kind, const b200_opt_hyper *h) {
+  const size_t in_dim = net->L[0].in_dim, out_dim = net->L[net->n_layers - 1].out_dim;
+  if (batch < 1 || batch > net->max_batch) return 1;
+  float *xb = (float *)calloc((size_t)batch * in_dim, sizeof(float));
+  float *tb = (float *)calloc((size_t)batch * out_dim, sizeof(float));
+  for (int e = 0; e < epochs; ++e)
+    for (long long i = 0; i < n; i += batch) {
+      const int size = (int)((n - i) < batch ? (n - i) : batch);
+      if (size == 1) {
+        orc_net_train_step(net, x + (size_t)i * in_dim, t + (size_t)i * out_dim, 1, loss_kind, opt_kind, h);
+      } else {
+        memcpy(xb, x + (size_t)i * in_dim, (size_t)size * in_dim * sizeof(float));
+        memcpy(tb, t + (size_t)i * out_dim, (size_t)size * out_dim * sizeof(float));
+        orc_net_train_step(net, xb, tb, batch, loss_kind, opt_kind, h);
+      }
+    }
+  free(xb);
+  free(tb);
+  return 0;
+}
+
+/* ---- the callers' data formats ------------------------------------------------------------- */
+/* parse_cifar10 (tiny_dnn/io/cifar10_parser.h:47-85, mode 0) and detail::parse_mnist_image
+ * (tiny_dnn/io/mnist_parser.h:43-68, mode 1): n planar uint8 images [c][h][w] -> float rows
+ * [c][h + 2*y_pad][w + 2*x_pad], border filled with scale_min. */
+ORC_API void orc_images_u8_to_float(const b200_image_desc *d, const uint8_t *src, long long n, float *dst) {
+  const int W = d->width, H = d->height, Wo = W + 2 * d->x_padding, Ho = H + 2 * d->y_padding;
+  const float smin = d->scale_min, smax = d->scale_max;
+  for (long long p = 0; p < n * d->channels; ++p) {
+    float *o = dst + (size_t)p * Wo * Ho;
+    for (int i = 0; i < Wo * Ho; ++i) o[i] = smin;
+    for (int y = 0; y < H; ++y)
+      for (int x = 0; x < W; ++x) {
+        const uint8_t c = src[(size_t)p * W * H + (size_t)y * W + x];
+        float v;
+        if (d->mode == B200_IMAGE_CIFAR10)
+          v = smin + (smax - smin) * c / 255;
+        else
+          v = (c / 255.0f) * (smax - smin) + smin;
+        o[(size_t)(y + d->y_padding) * Wo + x + d->x_padding] = v;
+      }
+  }
+}
+
+/* nodes::label2vec (tiny_dnn/nodes.h:180-189) */
+ORC_API void orc_labels_to_targets(const uint8_t *labels, long long n, int out_dim, float tmin, float tmax,
+                                   float *dst) {
+  for (long long s = 0; s < n; ++s) {
+    for (int j = 0; j < out_dim; ++j) dst[s * out_dim + j] = tmin;
+    dst[s * out_dim + labels[s]] = tmax;
   }
 }
 

@@ -290,12 +290,37 @@ REF_API int ref_opt_steps(int kind, const b200_opt_hyper *h, const float *dW, fl
     o.b1_t = h->b1_t;
     o.b2_t = h->b2_t;
     for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
-  } else {
+  } else if (kind == B200_OPT_MOMENTUM) {
     momentum o;
     o.alpha = h->alpha;
     o.mu = h->mu;
     o.lambda = h->lambda;
     for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
+  } else if (kind == B200_OPT_RMSPROP) {
+    RMSprop o;
+    o.alpha = h->alpha;
+    o.mu = h->mu;
+    for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
+  } else if (kind == B200_OPT_ADAMAX) {
+    adamax o;
+    o.alpha = h->alpha;
+    o.b1 = h->b1;
+    o.b2 = h->b2;
+    o.b1_t = h->b1_t;
+    for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
+  } else if (kind == B200_OPT_GRADIENT_DESCENT) {
+    gradient_descent o;
+    o.alpha = h->alpha;
+    o.lambda = h->lambda;
+    for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
+  } else if (kind == B200_OPT_NESTEROV_MOMENTUM) {
+    nesterov_momentum o;
+    o.alpha = h->alpha;
+    o.mu = h->mu;
+    o.lambda = h->lambda;
+    for (int s = 0; s < steps; ++s) o.update(vdW, vW, false);
+  } else {
+    return 1;
   }
   std::copy(vW.begin(), vW.end(), W);
   return 0;
@@ -475,10 +500,19 @@ REF_API int ref_net_predict(void *h, const float *x, float *out, int B) {
 // mini-batches of `batch` samples (x holds steps*batch rows).  Optimizer
 // objects persist across calls (state and Adam powers carry on).  Returns the
 // seconds spent inside fit().
+REF_API double ref_net_fit_n(void *h, const float *x, const float *t, long long n_samples, int batch, int epochs,
+                             int loss_kind, int opt_kind, const b200_opt_hyper *hy);
+
 REF_API double ref_net_fit(void *h, const float *x, const float *t, int batch, int steps,
                            int loss_kind, int opt_kind, const b200_opt_hyper *hy) {
+  return ref_net_fit_n(h, x, t, (long long)batch * steps, batch, 1, loss_kind, opt_kind, hy);
+}
+
+// the general form: n_samples rows (the last mini-batch of a pass may be ragged), `epochs` passes
+REF_API double ref_net_fit_n(void *h, const float *x, const float *t, long long n_samples, int batch, int epochs,
+                             int loss_kind, int opt_kind, const b200_opt_hyper *hy) {
   RefNet *r = static_cast<RefNet *>(h);
-  size_t N = (size_t)batch * steps;
+  size_t N = (size_t)n_samples;
   std::vector<vec_t> in(N), tgt(N);
   for (size_t n = 0; n < N; ++n) {
     in[n].assign(x + n * r->in_dim, x + (n + 1) * r->in_dim);
@@ -498,25 +532,25 @@ REF_API double ref_net_fit(void *h, const float *x, const float *t, int batch, i
     // maps but not Adam's powers (optimizer.h:36-38)
     if (opt_kind == B200_OPT_ADAGRAD) {
       if (loss_kind == B200_LOSS_MSE)
-        r->net.fit<mse>(r->o_adagrad, in, tgt, batch, 1, nop, nop);
+        r->net.fit<mse>(r->o_adagrad, in, tgt, batch, epochs, nop, nop);
       else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
-        r->net.fit<cross_entropy>(r->o_adagrad, in, tgt, batch, 1, nop, nop);
+        r->net.fit<cross_entropy>(r->o_adagrad, in, tgt, batch, epochs, nop, nop);
       else
-        r->net.fit<cross_entropy_multiclass>(r->o_adagrad, in, tgt, batch, 1, nop, nop);
+        r->net.fit<cross_entropy_multiclass>(r->o_adagrad, in, tgt, batch, epochs, nop, nop);
     } else if (opt_kind == B200_OPT_ADAM) {
       if (loss_kind == B200_LOSS_MSE)
-        r->net.fit<mse>(r->o_adam, in, tgt, batch, 1, nop, nop);
+        r->net.fit<mse>(r->o_adam, in, tgt, batch, epochs, nop, nop);
       else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
-        r->net.fit<cross_entropy>(r->o_adam, in, tgt, batch, 1, nop, nop);
+        r->net.fit<cross_entropy>(r->o_adam, in, tgt, batch, epochs, nop, nop);
       else
-        r->net.fit<cross_entropy_multiclass>(r->o_adam, in, tgt, batch, 1, nop, nop);
+        r->net.fit<cross_entropy_multiclass>(r->o_adam, in, tgt, batch, epochs, nop, nop);
     } else {
       if (loss_kind == B200_LOSS_MSE)
-        r->net.fit<mse>(r->o_momentum, in, tgt, batch, 1, nop, nop);
+        r->net.fit<mse>(r->o_momentum, in, tgt, batch, epochs, nop, nop);
       else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
-        r->net.fit<cross_entropy>(r->o_momentum, in, tgt, batch, 1, nop, nop);
+        r->net.fit<cross_entropy>(r->o_momentum, in, tgt, batch, epochs, nop, nop);
       else
-        r->net.fit<cross_entropy_multiclass>(r->o_momentum, in, tgt, batch, 1, nop, nop);
+        r->net.fit<cross_entropy_multiclass>(r->o_momentum, in, tgt, batch, epochs, nop, nop);
     }
   } catch (const std::exception &e) {
     fprintf(stderr, "ref_net_fit: %s\n", e.what());
@@ -611,6 +645,58 @@ REF_API int ref_net_apply_update(void *h, const float *grads, int opt_kind, cons
       o->update(g, *w, w->size() >= 512);  // layer.h:676
       grads += w->size();
     }
+  return 0;
+}
+
+// ---------------------------------------------------------------- dataset parsers
+// parse_cifar10 (io/cifar10_parser.h:36-86) on a file in the CIFAR-10 binary format; returns the
+// number of records, images as rows of 3 * (32 + 2*y_pad) * (32 + 2*x_pad) floats.
+REF_API long long ref_parse_cifar10(const char *filename, float scale_min, float scale_max, int x_padding,
+                                    int y_padding, float *images, unsigned char *labels, long long max_records) {
+  try {
+    std::vector<vec_t> img;
+    std::vector<label_t> lab;
+    parse_cifar10(filename, &img, &lab, scale_min, scale_max, x_padding, y_padding);
+    long long n = std::min<long long>((long long)img.size(), max_records);
+    for (long long i = 0; i < n; ++i) {
+      std::copy(img[i].begin(), img[i].end(), images + (size_t)i * img[i].size());
+      labels[i] = (unsigned char)lab[i];
+    }
+    return (long long)img.size();
+  } catch (const std::exception &e) {
+    fprintf(stderr, "ref_parse_cifar10: %s\n", e.what());
+    return -1;
+  }
+}
+
+// parse_mnist_images (io/mnist_parser.h:130-157) on an idx3-ubyte file
+REF_API long long ref_parse_mnist_images(const char *filename, float scale_min, float scale_max, int x_padding,
+                                         int y_padding, float *images, long long max_records) {
+  try {
+    std::vector<vec_t> img;
+    parse_mnist_images(filename, &img, scale_min, scale_max, x_padding, y_padding);
+    long long n = std::min<long long>((long long)img.size(), max_records);
+    for (long long i = 0; i < n; ++i) std::copy(img[i].begin(), img[i].end(), images + (size_t)i * img[i].size());
+    return (long long)img.size();
+  } catch (const std::exception &e) {
+    fprintf(stderr, "ref_parse_mnist_images: %s\n", e.what());
+    return -1;
+  }
+}
+
+// network::train's label conversion: nodes::label2vec through normalize_tensor (network.h:268-307,
+// 983-1000) for the net's own target value range
+REF_API int ref_net_label_targets(void *h, const unsigned char *labels, long long n, float *targets, float *range) {
+  RefNet *r = static_cast<RefNet *>(h);
+  // nodes::target_value_min / max (nodes.h:147-156): the output range of the last layer
+  const std::pair<float_t, float_t> rg = r->net[r->net.depth() - 1]->out_value_range();
+  range[0] = rg.first;
+  range[1] = rg.second;
+  for (long long i = 0; i < n; ++i) {  // nodes::label2vec (nodes.h:180-189)
+    vec_t v(r->out_dim, rg.first);
+    v[labels[i]] = rg.second;
+    std::copy(v.begin(), v.end(), targets + (size_t)i * r->out_dim);
+  }
   return 0;
 }
 

@@ -188,7 +188,18 @@ def hyper_for(kind: int) -> OptHyper:
         return hyper(alpha=0.01)
     if kind == 1:
         return hyper(alpha=0.001, b1=0.9, b2=0.999, b1_t=0.9, b2_t=0.999)
+    if kind == 3:  # RMSprop (optimizer.h:80)
+        return hyper(alpha=0.0001, mu=0.99)
+    if kind == 4:  # adamax (optimizer.h:146-151)
+        return hyper(alpha=0.002, b1=0.9, b2=0.999, b1_t=0.9)
+    if kind == 5:  # gradient_descent; a weight decay so that the lambda term is exercised
+        return hyper(alpha=0.01, lambda_=0.001)
+    if kind == 6:  # nesterov_momentum, with weight decay
+        return hyper(alpha=0.01, mu=0.9, lambda_=0.001)
     return hyper(alpha=0.01, mu=0.9, lambda_=0.0)
+
+
+OPT_KINDS = (0, 1, 2, 3, 4, 5, 6)
 
 
 # ---- networks ------------------------------------------------------------------------------
@@ -402,3 +413,127 @@ def check_digest(got, gold, key, tol, stride=101):
         bad = np.abs(g64.sum(axis=1) - rows) > tol * np.maximum(row_abs, 1e-30)
         assert not bad.any(), f"{key}: {int(bad.sum())} row sums differ beyond {tol:g}"
     return worst / max(mx, 1e-30)
+
+
+# ---- dataset formats ---------------------------------------------------------------------------
+# synthetic files in the CIFAR-10 binary format (records of 1 label byte + 3 x 32 x 32 pixel bytes)
+# and in the MNIST idx3-ubyte format; every byte value occurs
+DATA_CASES = {
+    "cifar_m1p1": dict(mode=0, n=4, c=3, h=32, w=32, xp=0, yp=0, smin=-1.0, smax=1.0, seed=81),
+    "cifar_0_1_pad": dict(mode=0, n=3, c=3, h=32, w=32, xp=2, yp=1, smin=0.0, smax=1.0, seed=82),
+    "cifar_odd_range": dict(mode=0, n=2, c=3, h=32, w=32, xp=0, yp=0, smin=-0.3, smax=2.7, seed=83),
+    "mnist_m1p1_pad2": dict(mode=1, n=5, c=1, h=28, w=28, xp=2, yp=2, smin=-1.0, smax=1.0, seed=84),
+    "mnist_0_1": dict(mode=1, n=3, c=1, h=28, w=28, xp=0, yp=0, smin=0.0, smax=1.0, seed=85),
+}
+
+
+def gen_dataset_bytes(c):
+    """(images uint8 [n][c*h*w], labels uint8 [n]) of a dataset case; the first 256 pixels run
+    through every byte value."""
+    rng = np.random.default_rng(c["seed"])
+    img = rng.integers(0, 256, (c["n"], c["c"] * c["h"] * c["w"]), dtype=np.uint8)
+    img[0, :256] = np.arange(256, dtype=np.uint8)
+    labels = rng.integers(0, 10, c["n"], dtype=np.uint8)
+    return img, labels
+
+
+def dataset_file_bytes(c, img, labels):
+    """The file the reference's parser reads for a dataset case."""
+    if c["mode"] == 0:  # CIFAR-10 binary: label byte, then the planar image
+        return b"".join(bytes([int(labels[i])]) + img[i].tobytes() for i in range(c["n"]))
+    header = (0x00000803).to_bytes(4, "big") + c["n"].to_bytes(4, "big") + c["h"].to_bytes(4, "big") + \
+        c["w"].to_bytes(4, "big")
+    return header + img.tobytes()
+
+
+def image_desc(c):
+    from tiny_cnn_b200._lib import ImageDesc
+    return ImageDesc(c["mode"], c["c"], c["h"], c["w"], c["xp"], c["yp"], c["smin"], c["smax"])
+
+
+# network::fit over data whose size is not a multiple of the mini-batch: (net case, samples,
+# mini-batch, epochs).  The reference completes a short last mini-batch with the previous step's rows
+# (its batch buffers keep them); one left-over sample becomes a one-sample step.
+RAGGED_FIT_CASES = {
+    "lenet_165_b16_e2": ("lenet_adagrad", 165, 16, 2),
+    "cifar_28_b8_e2": ("cifar_adam", 28, 8, 2),
+    "lenet_33_b16_e1": ("lenet_adagrad", 33, 16, 1),   # one sample left over
+    "tiny_23_b5_e3": ("tiny_conv_adam", 23, 5, 3),
+}
+
+
+def gen_ragged_fit_data(name):
+    case, n, B, epochs = RAGGED_FIT_CASES[name]
+    c = NET_CASES[case]
+    rng = np.random.default_rng(c["seed"] + 2000)
+    x = c["xgen"](rng, (n, c["in_dim"])).astype(np.float32)
+    t = np.full((n, c["out_dim"]), c["t_lo"], dtype=np.float32)
+    t[np.arange(n), rng.integers(0, c["out_dim"], n)] = c["t_hi"]
+    return c, x, t, n, B, epochs
+
+
+# ---- discrete decisions --------------------------------------------------------------------------
+# Two fp32 evaluations of the same network that differ only in summation order agree on the
+# forward outputs to ~1e-6, but a relu whose input is that close to zero, or a max-pooling window
+# whose two largest values are that close, can be DECIDED differently -- and then the whole
+# gradient contribution of that position is routed differently (one position's dY * x is not
+# small against a tolerance of 1e-3 of the tensor's largest entry).  The functions below find the
+# decisions on which two forward passes differ, per output unit (channel / neuron) of the layer
+# that owns the gradient, so that a comparison can hold every other unit to the strict tolerance.
+def _pool_winners(a, c, h, w):
+    """argmax of every 2x2/2 window in window-scan order (first maximum wins, as strict '>' does)."""
+    v = a.reshape(-1, c, h // 2, 2, w // 2, 2).transpose(0, 1, 2, 4, 3, 5).reshape(-1, c, h // 2, w // 2, 4)
+    return v.argmax(axis=-1)
+
+
+def decision_mismatch(specs, outs_a, outs_b):
+    """{index of a conv / fc layer: bool[out units]} -- units for which the relu gates or the
+    2x2 max-pooling winners behind that layer differ between two forward passes; outs_x[i] is
+    layer i's output [B][dim] (None where it is not available)."""
+    res = {}
+    owner = None
+    for i, sp in enumerate(specs):
+        if sp.kind == LAYER_CONV:
+            owner = (i, sp.conv.out_c, sp.conv.out_h, sp.conv.out_w)
+            res[i] = np.zeros(sp.conv.out_c, bool)
+        elif sp.kind == LAYER_FC:
+            owner = (i, sp.fc_out, 1, 1)
+            res[i] = np.zeros(sp.fc_out, bool)
+        elif sp.kind == LAYER_RELU and owner is not None:
+            li, c, h, w = owner
+            ga = (outs_a[i] > 0).reshape(-1, c, h * w)
+            gb = (outs_b[i] > 0).reshape(-1, c, h * w)
+            res[li] |= (ga != gb).any(axis=(0, 2))
+        elif sp.kind == LAYER_MAXPOOL and owner is not None:
+            li, c, h, w = owner
+            if (sp.pool.pool_w, sp.pool.pool_h, sp.pool.stride_w, sp.pool.stride_h) == (2, 2, 2, 2) and \
+                    outs_a[i - 1] is not None and outs_b[i - 1] is not None:
+                wa, wb = _pool_winners(outs_a[i - 1], c, h, w), _pool_winners(outs_b[i - 1], c, h, w)
+                res[li] |= (wa != wb).any(axis=(0, 2, 3))
+            owner = None
+        elif sp.kind in (LAYER_TANH, LAYER_SOFTMAX, LAYER_AVGPOOL):
+            pass
+    return res
+
+
+def entry_units(spec, is_weight, length):
+    """output unit (channel / neuron) each entry of a conv / fc parameter tensor belongs to"""
+    idx = np.arange(length)
+    if not is_weight:
+        return idx
+    if spec.kind == LAYER_CONV:
+        return idx // (spec.conv.in_c * spec.conv.k_h * spec.conv.k_w)
+    return idx % spec.fc_out   # fully connected: W[in][out]
+
+
+def param_layers(specs):
+    """layer index of every trainable tensor in update order (as net_layout lists them)"""
+    out = []
+    for i, sp in enumerate(specs):
+        if sp.kind == LAYER_CONV:
+            out += [i] * (2 if sp.conv.has_bias else 1)
+        elif sp.kind == LAYER_FC:
+            out += [i] * (2 if sp.fc_has_bias else 1)
+        elif sp.kind == LAYER_AVGPOOL:
+            out += [i, i]
+    return out

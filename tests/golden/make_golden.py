@@ -22,9 +22,10 @@ sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 
 import oracle_lib as o  # noqa: E402
-from cases import (ACT_CASES, AVGPOOL_CASES, CONV_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,  # noqa: E402
-                   QCONV_CASES, QFC_CASES, build_net_specs, conv_desc, gen_conv_inputs, gen_net_data,
-                   hyper_for, merge_rows_np, pool_desc, xavier_params)
+from cases import (ACT_CASES, AVGPOOL_CASES, CONV_CASES, DATA_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,  # noqa: E402
+                   QCONV_CASES, QFC_CASES, build_net_specs, conv_desc, dataset_file_bytes, gen_conv_inputs,
+                   gen_dataset_bytes, gen_net_data, hyper_for, merge_rows_np, pool_desc, xavier_params, OPT_KINDS,
+                   RAGGED_FIT_CASES, gen_ragged_fit_data)
 
 ROWS_LIMIT = 4096  # per-sample gradient rows are stored only when this small
 
@@ -121,7 +122,7 @@ def main():
     g0 = rng.standard_normal(1000).astype(np.float32)
     g0[::7] = 0.0  # exact zeros must give exactly zero update
     out["opt/W0"], out["opt/g"] = W0, g0
-    for kind in (0, 1, 2):
+    for kind in OPT_KINDS:
         W = W0.copy()
         h = hyper_for(kind)
         assert ref.ref_opt_steps(kind, C.byref(h), o.p(g0), o.p(W), W.size, 5) == 0
@@ -168,6 +169,52 @@ def main():
             a, b2 = C.c_float(), C.c_float()
             ref.ref_net_adam_powers(h, C.byref(a), C.byref(b2))
             out[f"net/{name}/adam_powers"] = np.array([a.value, b2.value], dtype=np.float32)
+        ref.ref_net_destroy(h)
+
+    # network::fit with a ragged last mini-batch
+    for name in RAGGED_FIT_CASES:
+        c, x, t, n_samples, B, epochs = gen_ragged_fit_data(name)
+        specs, keep = build_net_specs(c["net"])
+        arr = (type(specs[0]) * len(specs))(*specs)
+        h = ref.ref_net_create(arr, len(specs), c["seed"])
+        p0 = xavier_params(specs, c["seed"])
+        ref.ref_net_set_params(h, o.p(p0))
+        hy = hyper_for(c["opt"])
+        assert ref.ref_net_fit_n(h, o.p(x), o.p(t), n_samples, B, epochs, c["loss"], c["opt"], C.byref(hy)) >= 0
+        p1 = o.f32(p0.size)
+        ref.ref_net_get_params(h, o.p(p1))
+        out[f"fit_ragged/{name}/p1"] = p1
+        ref.ref_net_destroy(h)
+
+    # dataset parsers on synthetic files in the datasets' own formats
+    import tempfile
+    for name, c in DATA_CASES.items():
+        img, labels = gen_dataset_bytes(c)
+        out_len = c["c"] * (c["h"] + 2 * c["yp"]) * (c["w"] + 2 * c["xp"])
+        rows = o.f32(c["n"], out_len)
+        with tempfile.NamedTemporaryFile(suffix=".bin") as f:
+            f.write(dataset_file_bytes(c, img, labels))
+            f.flush()
+            if c["mode"] == 0:
+                lab = np.zeros(c["n"], np.uint8)
+                n = ref.ref_parse_cifar10(f.name.encode(), c["smin"], c["smax"], c["xp"], c["yp"], o.p(rows),
+                                          o.p(lab), c["n"])
+                assert np.array_equal(lab, labels)
+            else:
+                n = ref.ref_parse_mnist_images(f.name.encode(), c["smin"], c["smax"], c["xp"], c["yp"], o.p(rows),
+                                               c["n"])
+        assert n == c["n"], (name, n)
+        out[f"data/{name}/rows"] = rows
+    # network::train's targets for class labels: the output range of the net's last layer
+    for net_name in ("lenet", "cifar"):
+        specs, keep = build_net_specs(net_name)
+        arr = (type(specs[0]) * len(specs))(*specs)
+        h = ref.ref_net_create(arr, len(specs), 1)
+        labels = np.arange(10, dtype=np.uint8)
+        tg, rg = o.f32(10, 10), o.f32(2)
+        assert ref.ref_net_label_targets(h, o.p(labels), 10, o.p(tg), o.p(rg)) == 0
+        out[f"data/targets/{net_name}"] = tg
+        out[f"data/target_range/{net_name}"] = rg
         ref.ref_net_destroy(h)
 
     path = HERE / "ref_outputs.npz"

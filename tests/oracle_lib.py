@@ -12,7 +12,7 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-from tiny_cnn_b200._lib import ConvDesc, LayerSpec, OptHyper, PoolDesc  # noqa: E402
+from tiny_cnn_b200._lib import ConvDesc, ImageDesc, LayerSpec, OptHyper, PoolDesc  # noqa: E402
 
 _vp, _i, _sz, _f = C.c_void_p, C.c_int, C.c_size_t, C.c_float
 _cd, _pd, _oh = C.POINTER(ConvDesc), C.POINTER(PoolDesc), C.POINTER(OptHyper)
@@ -57,6 +57,9 @@ ORACLE_SIGS = {
     "orc_net_update": (None, [_vp, _i, _oh]),
     "orc_net_adam_powers": (None, [_vp, _fp, _fp]),
     "orc_net_opt_reset": (None, [_vp, _i]),
+    "orc_net_fit": (_i, [_vp, _vp, _vp, C.c_longlong, _i, _i, _i, _i, _oh]),
+    "orc_images_u8_to_float": (None, [C.POINTER(ImageDesc), _vp, C.c_longlong, _vp]),
+    "orc_labels_to_targets": (None, [_vp, C.c_longlong, _i, _f, _f, _vp]),
     "orc_net_train_step": (None, [_vp, _vp, _vp, _i, _i, _i, _oh]),
 }
 
@@ -87,7 +90,11 @@ REF_SIGS = {
     "ref_net_set_params": (None, [_vp, _vp]),
     "ref_net_predict": (_i, [_vp, _vp, _vp, _i]),
     "ref_net_fit": (C.c_double, [_vp, _vp, _vp, _i, _i, _i, _i, _oh]),
+    "ref_net_fit_n": (C.c_double, [_vp, _vp, _vp, C.c_longlong, _i, _i, _i, _i, _oh]),
     "ref_net_adam_powers": (None, [_vp, _fp, _fp]),
+    "ref_parse_cifar10": (C.c_longlong, [C.c_char_p, _f, _f, _i, _i, _vp, _vp, C.c_longlong]),
+    "ref_parse_mnist_images": (C.c_longlong, [C.c_char_p, _f, _f, _i, _i, _vp, C.c_longlong]),
+    "ref_net_label_targets": (_i, [_vp, _vp, C.c_longlong, _vp, _vp]),
     "ref_net_grads_chunked": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "ref_net_apply_update": (_i, [_vp, _vp, _i, _oh]),
     "ref_time_conv": (C.c_double, [_cd, _vp, _vp, _vp, _vp, _i, _i, _i]),

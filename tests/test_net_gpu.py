@@ -196,11 +196,12 @@ def test_sequential_mirror_lenet_100_steps(ctx, oracle):
 
 
 def test_fit_host_equals_step_by_step(ctx):
-    """b200_net_fit_host (uploads overlapped with the steps, ragged last mini-batch, two epochs)
-    ends with exactly the weights of one b200_net_train_step_host call per mini-batch, and
-    returns every step's forward output."""
+    """b200_net_fit_host (uploads overlapped with the steps, two epochs, a last mini-batch of 4 new
+    samples completed with the previous step's rows as network::fit does) ends with exactly the
+    weights of one b200_net_train_step_host call per mini-batch on explicitly assembled rows, and
+    returns the forward output of every step's new samples."""
     specs, keep = build_net_specs("cifar")
-    B, n = 8, 28  # 3 full mini-batches and one of 4 per epoch
+    B, n = 8, 28  # 3 full mini-batches and one of 4 new samples per epoch
     rng = np.random.default_rng(5)
     x = rng.standard_normal((n, 3072)).astype(np.float32)
     t = np.zeros((n, 10), np.float32)
@@ -214,18 +215,49 @@ def test_fit_host_equals_step_by_step(ctx):
     outs_b = np.zeros((n, 10), np.float32)
     xp, tp = torch.from_numpy(x).pin_memory(), torch.from_numpy(t).pin_memory()
     check(a.lib.b200_net_fit_host(a.h, ptr(xp), ptr(tp), n, B, 2, 1, 1, C.byref(h), ptr(outs_a)))
+    xb, tb = np.zeros((B, 3072), np.float32), np.zeros((B, 10), np.float32)  # in_batch_ / t_batch_
     for epoch in range(2):
         for i in range(0, n, B):
             nb = min(B, n - i)
-            out = np.empty((nb, 10), np.float32)
-            check(b.lib.b200_net_train_step_host(b.h, ptr(np.ascontiguousarray(x[i:i + nb])),
-                                                 ptr(np.ascontiguousarray(t[i:i + nb])), nb, 1, 1, C.byref(h),
-                                                 ptr(out)))
-            outs_b[i:i + nb] = out
+            xb[:nb], tb[:nb] = x[i:i + nb], t[i:i + nb]
+            out = np.empty((B, 10), np.float32)
+            check(b.lib.b200_net_train_step_host(b.h, ptr(xb), ptr(tb), B, 1, 1, C.byref(h), ptr(out)))
+            outs_b[i:i + nb] = out[:nb]
     assert np.array_equal(a.params(), b.params())
     assert np.array_equal(outs_a, outs_b)
     a.close()
     b.close()
+
+
+@pytest.mark.parametrize("name", ["lenet_165_b16_e2", "cifar_28_b8_e2", "lenet_33_b16_e1", "tiny_23_b5_e3"])
+def test_fit_host_ragged_last_batch_vs_reference(ctx, gold, name):
+    """network::fit over a sample count that is not a multiple of the mini-batch (short last step
+    completed with the previous step's rows; a single left-over sample as a one-sample step):
+    b200_net_fit_host against the weights the reference ends with."""
+    from cases import gen_ragged_fit_data
+    c, x, t, n_samples, B, epochs = gen_ragged_fit_data(name)
+    specs, keep = build_net_specs(c["net"])
+    dnet = DeviceNet(ctx, specs, B)
+    dnet.set_params(xavier_params(specs, c["seed"]))
+    h = hyper_for(c["opt"])
+    check(dnet.lib.b200_net_fit_host(dnet.h, ptr(x), ptr(t), n_samples, B, epochs, c["loss"], c["opt"], C.byref(h),
+                                     None))
+    p, p1 = dnet.params(), gold[f"fit_ragged/{name}/p1"]
+    for off, ln, _, _, _ in net_layout(specs)[0]:
+        assert_close(p[off:off + ln], p1[off:off + ln], GRAD_TOL, f"{name} weights@{off} vs reference")
+    dnet.close()
+
+
+def test_fit_host_refuses_a_short_first_batch(ctx):
+    """Fewer samples than one mini-batch (and more than one): the reference would read rows of its
+    batch buffers that were never set; the library says so instead."""
+    specs, keep = build_net_specs("tiny_conv")
+    dnet = DeviceNet(ctx, specs, 8)
+    x, t = np.zeros((3, 288), np.float32), np.zeros((3, 6), np.float32)
+    h = hyper_for(0)
+    assert dnet.lib.b200_net_fit_host(dnet.h, ptr(x), ptr(t), 3, 8, 1, 2, 0, C.byref(h), None) != 0
+    assert b"no earlier full mini-batch" in dnet.lib.b200_last_error()
+    dnet.close()
 
 
 def test_net_rejects_bad_input(ctx):

@@ -51,6 +51,19 @@ class OptHyper(C.Structure):
     ]
 
 
+class ImageDesc(C.Structure):
+    """b200_image_desc: how uint8 pixels become the first layer's float rows
+    (tiny_dnn/io/cifar10_parser.h:26-86, tiny_dnn/io/mnist_parser.h:43-68)."""
+    _fields_ = [
+        ("mode", C.c_int32), ("channels", C.c_int32), ("height", C.c_int32), ("width", C.c_int32),
+        ("x_padding", C.c_int32), ("y_padding", C.c_int32),
+        ("scale_min", C.c_float), ("scale_max", C.c_float),
+    ]
+
+
+IMAGE_CIFAR10, IMAGE_MNIST = 0, 1
+
+
 class LayerSpec(C.Structure):
     """b200_layer_spec: one layer of a network<sequential>."""
     _fields_ = [
@@ -64,7 +77,7 @@ class LayerSpec(C.Structure):
 # enums of the header
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_SOFTMAX = 0, 1, 2, 3
 LOSS_MSE, LOSS_CROSS_ENTROPY, LOSS_CROSS_ENTROPY_MULTICLASS = 0, 1, 2
-OPT_ADAGRAD, OPT_ADAM, OPT_MOMENTUM = 0, 1, 2
+OPT_ADAGRAD, OPT_ADAM, OPT_MOMENTUM, OPT_RMSPROP, OPT_ADAMAX, OPT_GRADIENT_DESCENT, OPT_NESTEROV_MOMENTUM = range(7)
 LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_AVGPOOL, LAYER_RELU, LAYER_TANH, LAYER_SOFTMAX = range(1, 8)
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
@@ -150,6 +163,10 @@ SIGNATURES = {
     "b200_net_peer_sum": (_i, [_vp]),
     "b200_net_train_step_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _oh, _vp]),
     "b200_net_fit_host": (_i, [_vp, _vp, _vp, C.c_longlong, _i, _i, _i, _i, _oh, _vp]),
+    "b200_images_u8_to_float": (_i, [_vp, C.POINTER(ImageDesc), _vp, C.c_longlong, _vp]),
+    "b200_labels_to_targets": (_i, [_vp, _vp, C.c_longlong, _i, C.c_float, C.c_float, _vp]),
+    "b200_net_fit_u8_host": (_i, [_vp, C.POINTER(ImageDesc), _vp, _vp, C.c_longlong, _i, _i, C.c_float, C.c_float,
+                                  _i, _i, _oh, _vp]),
     "b200_net_adam_powers": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "b200_net_get_opt_state": (_i, [_vp, _i, _vp]),
     "b200_net_set_opt_state": (_i, [_vp, _i, _vp]),

@@ -291,6 +291,14 @@ int opt_update_segments(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const 
 int opt_advance_powers(b200_ctx *ctx, float *pow_tab, int n_tensors, float b1, float b2,
                        const int *skip_if = nullptr);
 
+// raw dataset bytes -> the first layer's float rows and the target rows (data.cu)
+int check_image_desc(const b200_image_desc *d);
+size_t image_in_len(const b200_image_desc *d);
+size_t image_out_len(const b200_image_desc *d);
+int images_u8_to_float(b200_ctx *ctx, const b200_image_desc *d, const uint8_t *src, long long n, float *dst);
+int labels_to_targets(b200_ctx *ctx, const uint8_t *labels, long long n, int out_dim, float tmin, float tmax,
+                      float *dst);
+
 int qconv_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
               const float *bias, float *out, int B);
 int qfc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,

@@ -70,17 +70,16 @@ struct b200_net {
   // FFMA dX use different units of the SM and share it)
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
-  // third stream for the short kernels that finish a tensor-core weight gradient (fixed-order sum of
-  // the partial rows, reorder, bias gradient): the next layer's weight-gradient kernel on the side
-  // stream does not queue behind them
-  cudaStream_t fin = nullptr;
-  cudaEvent_t ev_fin_fork = nullptr, ev_fin_join = nullptr;
   // b200_net_fit_host: uploads of the next mini-batch overlap the step of the current one
   cudaStream_t copy_stream = nullptr;
   float *x_stage[2] = {nullptr, nullptr}, *t_stage[2] = {nullptr, nullptr};
+  // b200_net_fit_u8_host: raw image bytes and labels of a mini-batch
+  uint8_t *u8_stage[2] = {nullptr, nullptr}, *label_stage[2] = {nullptr, nullptr};
+  size_t u8_stage_bytes = 0;
   cudaEvent_t up_done[2] = {nullptr, nullptr}, stage_free[2] = {nullptr, nullptr};
   int cur_batch = 0;
   const float *cur_x = nullptr;
+  int fit_rows = 0;  // rows of x_dev / t_dev the last step of a fit call ran on
   bool fuse = true;
   bool input_grad = true;
   PeerReduce peer;  // data-parallel replicas: the gradient bucket is summed over the ranks inside the step
@@ -220,7 +219,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
   // reads them.  They go to the side stream, so the chain of dX kernels -- the critical path --
   // does not wait for them, and kernels that leave SMs idle overlap.  One join at the end.
   cudaStream_t main_stream = ctx->stream;
-  bool side_used = false, comm_used = false, fin_used = false;
+  bool side_used = false, comm_used = false;
   int rc_side = 0;
   // One side branch, not one per layer: the large kernels of both branches each fill the SMs, so
   // more branches only interleave them and delay the dX chain (measured: two branches 0.387 ms
@@ -254,18 +253,8 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
           if (!L.tc.fwd && !L.xs_from_pool) rc_side = conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs);
           int splits = 0;
           if (!rc_side) rc_side = conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits);
-          if (!rc_side && forked && net->fin) {
-            // the finishing launch leaves the side stream, whose next kernel is the next layer's dW
-            B200_CUDA(cudaEventRecord(net->ev_fin_fork, net->side));
-            B200_CUDA(cudaStreamWaitEvent(net->fin, net->ev_fin_fork, 0));
-            ctx->stream = net->fin;
+          if (!rc_side)
             rc_side = conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db);
-            ctx->stream = net->side;
-            B200_CUDA(cudaEventRecord(net->ev_fin_join, net->fin));
-            fin_used = true;
-          } else if (!rc_side) {
-            rc_side = conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db);
-          }
         } else if (L.tc.dw_small) {
           rc_side = conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0);
         } else if (tiled_bwd) {
@@ -344,7 +333,6 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
         B200_CUDA(cudaEventRecord(net->ev_comm_side, net->side));
         B200_CUDA(cudaStreamWaitEvent(net->comm, net->ev_comm_side, 0));
       }
-      if (fin_used) B200_CUDA(cudaStreamWaitEvent(net->comm, net->ev_fin_join, 0));
       ctx->stream = net->comm;
       int rc = peer_reduce_push_early(ctx, &net->peer, net->grads);
       ctx->stream = main_stream;
@@ -358,7 +346,6 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
     B200_CUDA(cudaEventRecord(net->ev_join, net->side));
     B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_join, 0));
   }
-  if (fin_used) B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_fin_join, 0));
   if (comm_used) B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_comm_done, 0));
 
   return rc_side;
@@ -393,12 +380,15 @@ int net_update_impl(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
   const int *skip_if = net->peer.world > 1 ? ctx->dev_err : nullptr;
   B200_TRY(opt_update_segments(ctx, opt_kind, *h, net->grads, net->params, net->state0,
                                net->state1, net->segs_dev, T, net->n_params, net->pow_tab, skip_if));
-  if (opt_kind == B200_OPT_ADAM) B200_TRY(opt_advance_powers(ctx, net->pow_tab, T, h->b1, h->b2, skip_if));
+  // adam and adamax advance their powers once per update call (optimizer.h:125-126, :165)
+  if (opt_kind == B200_OPT_ADAM || opt_kind == B200_OPT_ADAMAX)
+    B200_TRY(opt_advance_powers(ctx, net->pow_tab, T, h->b1, h->b2, skip_if));
   return 0;
 }
 
 int ensure_powers(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
-  if (opt_kind == B200_OPT_ADAM && !net->pow_init) B200_TRY(net_init_powers(net, h->b1, h->b2, h->b1, h->b2));
+  if ((opt_kind == B200_OPT_ADAM || opt_kind == B200_OPT_ADAMAX) && !net->pow_init)
+    B200_TRY(net_init_powers(net, h->b1, h->b2, h->b1, h->b2));
   return 0;
 }
 
@@ -439,11 +429,6 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
     cudaStreamCreateWithFlags(&net->side, cudaStreamNonBlocking);
     cudaEventCreateWithFlags(&net->ev_fork, cudaEventDisableTiming);
     cudaEventCreateWithFlags(&net->ev_join, cudaEventDisableTiming);
-    if (!getenv("B200_NET_NO_FIN")) {
-      cudaStreamCreateWithFlags(&net->fin, cudaStreamNonBlocking);
-      cudaEventCreateWithFlags(&net->ev_fin_fork, cudaEventDisableTiming);
-      cudaEventCreateWithFlags(&net->ev_fin_join, cudaEventDisableTiming);
-    }
   }
   size_t off = 0;
   size_t prev_out = 0;
@@ -656,6 +641,8 @@ int b200_net_destroy(b200_net *net) {
   for (int i = 0; i < 2; ++i) {
     cudaFree(net->x_stage[i]);
     cudaFree(net->t_stage[i]);
+    cudaFree(net->u8_stage[i]);
+    cudaFree(net->label_stage[i]);
     if (net->up_done[i]) cudaEventDestroy(net->up_done[i]);
     if (net->stage_free[i]) cudaEventDestroy(net->stage_free[i]);
   }
@@ -666,9 +653,6 @@ int b200_net_destroy(b200_net *net) {
   if (net->ev_comm_side) cudaEventDestroy(net->ev_comm_side);
   if (net->ev_comm_done) cudaEventDestroy(net->ev_comm_done);
   if (net->side) cudaStreamDestroy(net->side);
-  if (net->fin) cudaStreamDestroy(net->fin);
-  if (net->ev_fin_fork) cudaEventDestroy(net->ev_fin_fork);
-  if (net->ev_fin_join) cudaEventDestroy(net->ev_fin_join);
   if (net->ev_fork) cudaEventDestroy(net->ev_fork);
   if (net->ev_join) cudaEventDestroy(net->ev_join);
   cudaFree(net->x_dev);
@@ -919,6 +903,25 @@ static std::string step_key(const float *x, const float *t, int batch, int loss_
   return key;
 }
 
+// Rows a step of network::fit runs on when `nb` new samples are left (network.h:883-926).  The
+// reference copies the new samples over the first rows of its batch buffers in_batch_ / t_batch_
+// (members sized to the mini-batch once per fit) and then runs forward / backward on the WHOLE
+// buffers, so a last mini-batch of 1 < nb < batch samples is a full step whose rows nb.. are
+// still the previous step's rows nb..; a single left-over sample takes train_once's one-sample
+// branch instead.  The device keeps the same rows in x_dev / t_dev between steps (and between fit
+// calls, like the members), so copying only the new rows reproduces it.
+static int fit_step_rows(b200_net *net, int nb, int batch, int *rows) {
+  if (nb == batch || nb == 1) {
+    *rows = nb;
+    return 0;
+  }
+  B200_REQUIRE(net->fit_rows == batch,
+               "fit: %d samples for mini-batches of %d and no earlier full mini-batch to complete the step from "
+               "(the reference reads unset rows of its batch buffers in this case)", nb, batch);
+  *rows = batch;
+  return 0;
+}
+
 extern "C" {
 
 int b200_net_train_step(b200_net *net, const float *x, const float *t, int batch, int loss_kind,
@@ -965,6 +968,7 @@ int b200_net_train_step_host(b200_net *net, const float *x_host, const float *t_
   B200_CUDA(cudaMemcpyAsync(net->t_dev, t_host, out_dim * batch * sizeof(float),
                             cudaMemcpyHostToDevice, st));
   B200_TRY(b200_net_train_step(net, net->x_dev, net->t_dev, batch, loss_kind, opt_kind, h));
+  net->fit_rows = batch;
   if (out_host)
     B200_CUDA(cudaMemcpyAsync(out_host, net->layers.back().out, out_dim * batch * sizeof(float),
                               cudaMemcpyDeviceToHost, st));
@@ -996,7 +1000,9 @@ int b200_net_fit_host(b200_net *net, const float *x_host, const float *t_host, l
   long long step = 0;
   for (int e = 0; e < epochs; ++e) {
     for (long long i = 0; i < n_samples; i += batch, ++step) {
-      const int nb = (int)((n_samples - i) < batch ? (n_samples - i) : batch);  // ragged last batch
+      const int nb = (int)((n_samples - i) < batch ? (n_samples - i) : batch);  // new rows of this step
+      int run_nb = 0;
+      B200_TRY(fit_step_rows(net, nb, batch, &run_nb));
       const int buf = (int)(step & 1);
       if (step >= 2) B200_CUDA(cudaStreamWaitEvent(net->copy_stream, net->stage_free[buf], 0));
       B200_CUDA(cudaMemcpyAsync(net->x_stage[buf], x_host + (size_t)i * in_dim, in_dim * nb * sizeof(float),
@@ -1011,7 +1017,76 @@ int b200_net_fit_host(b200_net *net, const float *x_host, const float *t_host, l
       B200_CUDA(cudaMemcpyAsync(net->t_dev, net->t_stage[buf], out_dim * nb * sizeof(float),
                                 cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaEventRecord(net->stage_free[buf], st));
-      B200_TRY(b200_net_train_step(net, net->x_dev, net->t_dev, nb, loss_kind, opt_kind, h));
+      B200_TRY(b200_net_train_step(net, net->x_dev, net->t_dev, run_nb, loss_kind, opt_kind, h));
+      net->fit_rows = run_nb;
+      if (out_host)
+        B200_CUDA(cudaMemcpyAsync(out_host + (size_t)i * out_dim, net->layers.back().out,
+                                  out_dim * nb * sizeof(float), cudaMemcpyDeviceToHost, st));
+    }
+  }
+  B200_CUDA(cudaStreamSynchronize(net->copy_stream));
+  B200_CUDA(cudaStreamSynchronize(st));
+  return 0;
+}
+
+int b200_net_fit_u8_host(b200_net *net, const b200_image_desc *d, const uint8_t *images_host,
+                         const uint8_t *labels_host, long long n_samples, int batch, int epochs, float target_min,
+                         float target_max, int loss_kind, int opt_kind, const b200_opt_hyper *h, float *out_host) {
+  B200_TRY(check_net(net));
+  B200_TRY(check_image_desc(d));
+  B200_REQUIRE(images_host && labels_host && h, "net_fit_u8_host: NULL argument");
+  B200_REQUIRE(batch >= 1 && batch <= net->max_batch, "net_fit_u8_host: batch %d outside 1..%d", batch,
+               net->max_batch);
+  B200_REQUIRE(n_samples >= 0 && epochs >= 0, "net_fit_u8_host: negative count");
+  const size_t in_dim = net->layers.front().in_dim, out_dim = net->layers.back().out_dim;
+  const size_t img_bytes = image_in_len(d);
+  B200_REQUIRE(image_out_len(d) == in_dim, "net_fit_u8_host: padded images have %zu values, the network reads %zu",
+               image_out_len(d), in_dim);
+  for (long long i = 0; i < n_samples; ++i)
+    B200_REQUIRE(labels_host[i] < out_dim, "net_fit_u8_host: label %d of sample %lld outside the %zu network outputs",
+                 (int)labels_host[i], i, out_dim);
+  cudaStream_t st = net->ctx->stream;
+  if (!net->copy_stream) {
+    B200_CUDA(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      B200_TRY(net_alloc((void **)&net->x_stage[i], in_dim * net->max_batch * sizeof(float)));
+      B200_TRY(net_alloc((void **)&net->t_stage[i], out_dim * net->max_batch * sizeof(float)));
+      B200_CUDA(cudaEventCreateWithFlags(&net->up_done[i], cudaEventDisableTiming));
+      B200_CUDA(cudaEventCreateWithFlags(&net->stage_free[i], cudaEventDisableTiming));
+    }
+  }
+  if (net->u8_stage_bytes < img_bytes * net->max_batch) {
+    B200_CUDA(cudaStreamSynchronize(st));
+    for (int i = 0; i < 2; ++i) {
+      cudaFree(net->u8_stage[i]);
+      cudaFree(net->label_stage[i]);
+      net->u8_stage[i] = net->label_stage[i] = nullptr;
+      B200_TRY(net_alloc((void **)&net->u8_stage[i], img_bytes * net->max_batch));
+      B200_TRY(net_alloc((void **)&net->label_stage[i], (size_t)net->max_batch));
+    }
+    net->u8_stage_bytes = img_bytes * net->max_batch;
+  }
+  long long step = 0;
+  for (int e = 0; e < epochs; ++e) {
+    for (long long i = 0; i < n_samples; i += batch, ++step) {
+      const int nb = (int)((n_samples - i) < batch ? (n_samples - i) : batch);
+      int run_nb = 0;
+      B200_TRY(fit_step_rows(net, nb, batch, &run_nb));
+      const int buf = (int)(step & 1);
+      if (step >= 2) B200_CUDA(cudaStreamWaitEvent(net->copy_stream, net->stage_free[buf], 0));
+      B200_CUDA(cudaMemcpyAsync(net->u8_stage[buf], images_host + (size_t)i * img_bytes, img_bytes * nb,
+                                cudaMemcpyHostToDevice, net->copy_stream));
+      B200_CUDA(cudaMemcpyAsync(net->label_stage[buf], labels_host + i, (size_t)nb, cudaMemcpyHostToDevice,
+                                net->copy_stream));
+      B200_CUDA(cudaEventRecord(net->up_done[buf], net->copy_stream));
+      B200_CUDA(cudaStreamWaitEvent(st, net->up_done[buf], 0));
+      // scale / pad the bytes into the step's fixed input rows, labels into its target rows
+      B200_TRY(images_u8_to_float(net->ctx, d, net->u8_stage[buf], nb, net->x_dev));
+      B200_TRY(labels_to_targets(net->ctx, net->label_stage[buf], nb, (int)out_dim, target_min, target_max,
+                                 net->t_dev));
+      B200_CUDA(cudaEventRecord(net->stage_free[buf], st));
+      B200_TRY(b200_net_train_step(net, net->x_dev, net->t_dev, run_nb, loss_kind, opt_kind, h));
+      net->fit_rows = run_nb;
       if (out_host)
         B200_CUDA(cudaMemcpyAsync(out_host + (size_t)i * out_dim, net->layers.back().out,
                                   out_dim * nb * sizeof(float), cudaMemcpyDeviceToHost, st));

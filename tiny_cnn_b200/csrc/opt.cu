@@ -31,14 +31,40 @@ __device__ __forceinline__ void opt_apply(int kind, const OptParams &h, float g,
     float mhat = __fdiv_rn(s0, __fsub_rn(1.f, h.b1_t));
     float vhat = __fdiv_rn(s1, __fsub_rn(1.f, h.b2_t));
     w = __fsub_rn(w, __fdiv_rn(__fmul_rn(h.alpha, mhat), __fsqrt_rn(__fadd_rn(vhat, h.eps))));
-  } else {
+  } else if (kind == B200_OPT_MOMENTUM) {
     // V = mu*dWprev - alpha*(dW + W*lambda) ; W += V ; dWprev = V
     float v = __fsub_rn(__fmul_rn(h.mu, s0),
                         __fmul_rn(h.alpha, __fadd_rn(g, __fmul_rn(w, h.lambda))));
     w = __fadd_rn(w, v);
     s0 = v;
+  } else if (kind == B200_OPT_RMSPROP) {
+    // g = mu*g + (1-mu)*dW*dW ; W -= alpha*dW/sqrt(g+eps)   (optimizer.h:82-89)
+    s0 = __fadd_rn(__fmul_rn(h.mu, s0), __fmul_rn(__fmul_rn(__fsub_rn(1.f, h.mu), g), g));
+    w = __fsub_rn(w, __fdiv_rn(__fmul_rn(h.alpha, g), __fsqrt_rn(__fadd_rn(s0, h.eps))));
+  } else if (kind == B200_OPT_ADAMAX) {
+    // mt = b1*mt + (1-b1)*dW ; ut = max(b2*ut, |dW|) ; W -= (alpha/(1.0-b1_t)) * (mt/(ut+eps))
+    // (optimizer.h:153-166).  The literal 1.0 is a double: the step size, its product with the
+    // float quotient and the subtraction from W are double operations rounded to float once.
+    s0 = __fadd_rn(__fmul_rn(h.b1, s0), __fmul_rn(__fsub_rn(1.f, h.b1), g));
+    s1 = fmaxf(__fmul_rn(h.b2, s1), fabsf(g));
+    const double step = __ddiv_rn((double)h.alpha, __dsub_rn(1.0, (double)h.b1_t));
+    const float q = __fdiv_rn(s0, __fadd_rn(s1, h.eps));
+    w = (float)__dsub_rn((double)w, __dmul_rn(step, (double)q));
+  } else if (kind == B200_OPT_GRADIENT_DESCENT) {
+    // W = W - alpha*(dW + lambda*W)   (optimizer.h:185-188)
+    w = __fsub_rn(w, __fmul_rn(h.alpha, __fadd_rn(g, __fmul_rn(h.lambda, w))));
+  } else {
+    // nesterov: V = mu*dWprev - alpha*(dW + W*lambda) ; W += (-mu)*dWprev + (1+mu)*V ; dWprev = V
+    // (optimizer.h:233-240)
+    float v = __fsub_rn(__fmul_rn(h.mu, s0),
+                        __fmul_rn(h.alpha, __fadd_rn(g, __fmul_rn(w, h.lambda))));
+    w = __fadd_rn(w, __fadd_rn(__fmul_rn(-h.mu, s0), __fmul_rn(__fadd_rn(1.f, h.mu), v)));
+    s0 = v;
   }
 }
+
+// optimizers that keep a second state vector / per-tensor powers
+__host__ __device__ __forceinline__ bool opt_two_states(int kind) { return kind == B200_OPT_ADAM || kind == B200_OPT_ADAMAX; }
 
 __global__ void opt_update_kernel(int kind, OptParams h, const float *__restrict__ grads, int rows,
                                   size_t stride, float *__restrict__ merged, float *__restrict__ W,
@@ -49,11 +75,11 @@ __global__ void opt_update_kernel(int kind, OptParams h, const float *__restrict
     float g = grads[i];
     for (int r = 1; r < rows; ++r) g = __fadd_rn(g, grads[(size_t)r * stride + i]);
     if (merged) merged[i] = g;
-    float w = W[i], a = s0[i], b = (kind == B200_OPT_ADAM) ? s1[i] : 0.f;
+    float w = W[i], a = s0 ? s0[i] : 0.f, b = opt_two_states(kind) ? s1[i] : 0.f;
     opt_apply(kind, h, g, w, a, b);
     W[i] = w;
-    s0[i] = a;
-    if (kind == B200_OPT_ADAM) s1[i] = b;
+    if (s0) s0[i] = a;
+    if (opt_two_states(kind)) s1[i] = b;
   }
 }
 
@@ -71,7 +97,7 @@ __global__ void opt_update_segments_kernel(int kind, OptParams h, const float *_
   size_t step = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += step) {
     OptParams hp = h;
-    if (kind == B200_OPT_ADAM) {
+    if (opt_two_states(kind)) {
       // binary search of the segment containing i
       int lo = 0, hi = n_segs - 1;
       while (lo < hi) {
@@ -85,11 +111,11 @@ __global__ void opt_update_segments_kernel(int kind, OptParams h, const float *_
       hp.b2_t = pow_tab[2 * lo + 1];
     }
     float g = grads[i];
-    float w = W[i], a = s0[i], b = (kind == B200_OPT_ADAM) ? s1[i] : 0.f;
+    float w = W[i], a = s0[i], b = opt_two_states(kind) ? s1[i] : 0.f;
     opt_apply(kind, hp, g, w, a, b);
     W[i] = w;
     s0[i] = a;
-    if (kind == B200_OPT_ADAM) s1[i] = b;
+    if (opt_two_states(kind)) s1[i] = b;
   }
 }
 
@@ -134,9 +160,9 @@ static int grid_for(size_t total, int block, int sm_count) {
 
 int opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *grads, int rows,
                size_t stride, float *merged, float *W, float *s0, float *s1, size_t len) {
-  B200_REQUIRE(kind >= B200_OPT_ADAGRAD && kind <= B200_OPT_MOMENTUM, "unknown optimizer %d", kind);
+  B200_REQUIRE(kind >= B200_OPT_ADAGRAD && kind <= B200_OPT_NESTEROV_MOMENTUM, "unknown optimizer %d", kind);
   B200_REQUIRE(rows >= 1, "opt_update: rows must be >= 1");
-  B200_REQUIRE(s0 != nullptr && (kind != B200_OPT_ADAM || s1 != nullptr),
+  B200_REQUIRE((s0 != nullptr || kind == B200_OPT_GRADIENT_DESCENT) && (!opt_two_states(kind) || s1 != nullptr),
                "opt_update: optimizer state buffer is NULL");
   if (len == 0) return 0;
   opt_update_kernel<<<grid_for(len, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
@@ -148,7 +174,7 @@ int opt_update(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *gr
 int opt_update_segments(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const float *grads,
                         float *W, float *s0, float *s1, const OptSegment *segs_dev, int n_segs,
                         size_t total, float *pow_tab, const int *skip_if) {
-  B200_REQUIRE(kind >= B200_OPT_ADAGRAD && kind <= B200_OPT_MOMENTUM, "unknown optimizer %d", kind);
+  B200_REQUIRE(kind >= B200_OPT_ADAGRAD && kind <= B200_OPT_NESTEROV_MOMENTUM, "unknown optimizer %d", kind);
   if (total == 0) return 0;
   opt_update_segments_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
     kind, to_params(h), grads, W, s0, s1, segs_dev, n_segs, total, pow_tab, skip_if);

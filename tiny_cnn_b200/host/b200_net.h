@@ -8,6 +8,9 @@
 // the loss is mse / cross_entropy / cross_entropy_multiclass and the optimizer
 // is adagrad / adam / momentum, the hook replaces the loop over mini-batches:
 //
+// (the public fit / train overloads call b200_fit_hook_rows even earlier, before they copy the
+// whole data set into tensors)
+//
 //   layers   -> b200_layer_spec[]            (b200_net_create, cached in the network object)
 //   weights  -> flat parameter buffer        (layer::weights(): W before b, layer order)
 //   adam     -> b200_net_set_adam_powers     (continues from the object's b1_t / b2_t)
@@ -24,8 +27,11 @@
 // between them), and stop_ongoing_training() takes effect at the next epoch boundary.
 #pragma once
 
+#include <atomic>
 #include <cstring>
+#include <fstream>
 #include <memory>
+#include <string>
 #include <thread>
 #include <type_traits>
 #include <vector>
@@ -257,42 +263,82 @@ void state_to_host(Net &nn, device_twin &tw, opt_choice &oc, long long steps_don
   }
 }
 
-template <typename Error, typename Optimizer, typename OnBatch, typename OnEpoch>
-bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<tensor_t> &inputs,
-                    const std::vector<tensor_t> &desired_outputs, size_t batch_size, int epoch,
-                    OnBatch on_batch_enumerate, OnEpoch on_epoch_enumerate,
-                    const std::vector<tensor_t> &t_cost, const bool *stop) {
+// rows of the reference's containers: a sample is a vec_t, or a tensor_t holding one vec_t
+inline const vec_t *input_row(const vec_t &v) { return &v; }
+inline const vec_t *input_row(const tensor_t &t) { return t.size() == 1 ? &t[0] : nullptr; }
+
+// writes one target row; class labels become nodes::label2vec rows (nodes.h:180-189) in the output
+// range of the network's last layer (nodes.h:147-156)
+struct target_writer {
+  size_t out_dim;
+  float lo, hi;
+  bool write(const vec_t &v, float *dst) const {
+    if (v.size() != out_dim) return false;
+    std::copy(v.begin(), v.end(), dst);
+    return true;
+  }
+  bool write(const tensor_t &t, float *dst) const { return t.size() == 1 && write(t[0], dst); }
+  bool write(label_t l, float *dst) const {
+    if (static_cast<size_t>(l) >= out_dim) return false;
+    std::fill(dst, dst + out_dim, lo);
+    dst[l] = hi;
+    return true;
+  }
+};
+
+// The loop over mini-batches of network::fit on the device.  `preamble`: also do what fit does
+// before its loop (network.h:852-857) -- for the hooks that run before fit's own set-up; nothing
+// of the network or the optimizer is touched until the whole fit is known to be on the path.
+template <typename Error, typename Optimizer, typename In, typename Tg, typename OnBatch, typename OnEpoch>
+bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<In> &inputs,
+                    const std::vector<Tg> &targets, size_t batch_size, int epoch, OnBatch on_batch_enumerate,
+                    OnEpoch on_epoch_enumerate, bool preamble, bool reset_weights, bool *stop) {
   const int loss = loss_kind<Error>::value;
-  if (loss < 0 || !t_cost.empty() || inputs.empty() || batch_size == 0 || nn.depth() == 0) return false;
-  if (inputs[0].size() != 1 || desired_outputs.size() != inputs.size() || desired_outputs[0].size() != 1)
-    return false;
+  if (loss < 0 || inputs.empty() || batch_size == 0 || nn.depth() == 0 || targets.size() != inputs.size()) return false;
   opt_choice oc = choose_optimizer(static_cast<optimizer *>(&opt));
   if (oc.kind < 0) return false;
   bool any_b200 = false;
   for (size_t i = 0; i < nn.depth(); ++i) any_b200 = any_b200 || nn[i]->engine() == core::backend_t::b200;
   if (!any_b200) return false;
-  const int batch = static_cast<int>(std::min(batch_size, inputs.size()));
+  const size_t N = inputs.size();
+  if (N < batch_size && N != 1) return false;  // the reference's batch buffers would hold unset rows
+  const int batch = static_cast<int>(std::min(batch_size, N));
   std::shared_ptr<device_twin> tw = twin_for(nn, batch);
   if (!tw) return false;
   const size_t in_dim = static_cast<size_t>(b200_net_in_dim(tw->net));
   const size_t out_dim = static_cast<size_t>(b200_net_out_dim(tw->net));
-  if (inputs[0][0].size() != in_dim || desired_outputs[0][0].size() != out_dim) return false;
+  const std::pair<float_t, float_t> range = nn[nn.depth() - 1]->out_value_range();
+  const target_writer tgt{out_dim, static_cast<float>(range.first), static_cast<float>(range.second)};
+  std::vector<float> probe(out_dim);
+  for (size_t s = 0; s < N; ++s) {
+    const vec_t *r = input_row(inputs[s]);
+    if (!r || r->size() != in_dim) return false;
+  }
+  if (!tgt.write(targets[0], probe.data())) return false;
 
-  const size_t N = inputs.size();
+  if (preamble) {
+    nn.set_netphase(net_phase::train);
+    for (size_t i = 0; i < nn.depth(); ++i) nn[i]->setup(reset_weights);
+    for (size_t i = 0; i < nn.depth(); ++i) nn[i]->set_parallelize(true);
+    opt.reset();
+    *stop = false;
+  }
   tw->x.reserve(N * in_dim);
   tw->t.reserve(N * out_dim);
   // The reference keeps one heap vector per sample; the device wants rows back to back in
   // page-locked memory.  Rows [s0, s1) are packed by a few threads, and during the first epoch the
   // packing of the next run of mini-batches overlaps the device's work on the current one.
   float *xp = tw->x.p, *tp = tw->t.p;
-  auto pack = [&inputs, &desired_outputs, xp, tp, in_dim, out_dim](size_t s0, size_t s1) {
+  std::atomic<bool> bad_row(false);
+  auto pack = [&inputs, &targets, &tgt, &bad_row, xp, tp, in_dim, out_dim](size_t s0, size_t s1) {
     unsigned nt = std::thread::hardware_concurrency();
     nt = nt == 0 ? 1 : nt > 4 ? 4 : nt;
     if (s1 - s0 < 64) nt = 1;
     auto part = [&](size_t a, size_t b) {
       for (size_t s = a; s < b; ++s) {
-        std::copy(inputs[s][0].begin(), inputs[s][0].end(), xp + s * in_dim);
-        std::copy(desired_outputs[s][0].begin(), desired_outputs[s][0].end(), tp + s * out_dim);
+        const vec_t *r = input_row(inputs[s]);
+        std::copy(r->begin(), r->end(), xp + s * in_dim);
+        if (!tgt.write(targets[s], tp + s * out_dim)) bad_row = true;
       }
     };
     std::vector<std::thread> helpers;
@@ -305,7 +351,7 @@ bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<t
     for (auto &h : helpers) h.join();
   };
   weights_to_device(nn, *tw);
-  // fit() has just called optimizer.reset(): the state maps are empty, adam's powers carry on
+  // fit() calls optimizer.reset() before its loop: the state maps are empty, adam's powers carry on
   check(b200_net_opt_reset(tw->net, 1));
   if (oc.as_adam) check(b200_net_set_adam_powers(tw->net, oc.h.b1, oc.h.b2, oc.as_adam->b1_t, oc.as_adam->b2_t));
   const long long steps_per_epoch = static_cast<long long>((N + batch - 1) / batch);
@@ -317,9 +363,11 @@ bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<t
         const size_t s1 = std::min(N, s0 + run), s2 = std::min(N, s1 + run);
         std::thread ahead;
         if (s1 < N) ahead = std::thread(pack, s1, s2);
-        const int rc = b200_net_fit_host(tw->net, xp + s0 * in_dim, tp + s0 * out_dim, static_cast<long long>(s1 - s0),
-                                         batch, 1, loss, oc.kind, &oc.h, nullptr);
+        const int rc = bad_row ? 0
+                               : b200_net_fit_host(tw->net, xp + s0 * in_dim, tp + s0 * out_dim,
+                                                   static_cast<long long>(s1 - s0), batch, 1, loss, oc.kind, &oc.h, nullptr);
         if (ahead.joinable()) ahead.join();
+        if (bad_row) throw nn_error("b200: a target row does not fit the network's output (size or class id)");
         check(rc);
       }
     } else {
@@ -335,28 +383,166 @@ bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<t
   return true;
 }
 
-template <typename Error, typename Net, typename Optimizer, typename OnBatch, typename OnEpoch>
-bool fit_dispatch(std::false_type, Net &, Optimizer &, const std::vector<tensor_t> &, const std::vector<tensor_t> &,
-                  size_t, int, OnBatch, OnEpoch, const std::vector<tensor_t> &, const bool *) {
+// ---- training straight from the dataset's bytes ----------------------------------------------
+//
+// parse_cifar10 / parse_mnist_images (tiny_dnn/io/cifar10_parser.h, mnist_parser.h) turn every
+// pixel byte into a float on the host, and network::train then uploads 4 bytes per pixel.  The
+// loaders below keep the bytes; train_u8 uploads them as they are and the device applies the
+// parser's own scaling (bit for bit) and builds the target rows (nodes::label2vec) per mini-batch.
+struct u8_dataset {
+  std::vector<uint8_t> images;  // n records of channels * height * width bytes, planar
+  std::vector<uint8_t> labels;  // n class ids
+  b200_image_desc desc{};
+  size_t size() const { return labels.size(); }
+};
+
+// the records of a CIFAR-10 binary file (1 label byte + 3 x 32 x 32 pixel bytes each), appended to
+// `data`; scale / padding as parse_cifar10's arguments (cifar10_parser.h:36-46)
+inline void load_cifar10_u8(const std::string &filename, u8_dataset *data, float_t scale_min, float_t scale_max,
+                            int x_padding, int y_padding) {
+  if (x_padding < 0 || y_padding < 0) throw nn_error("padding size must not be negative");
+  if (scale_min >= scale_max) throw nn_error("scale_max must be greater than scale_min");
+  std::ifstream ifs(filename.c_str(), std::ios::in | std::ios::binary);
+  if (ifs.fail() || ifs.bad()) throw nn_error("failed to open file:" + filename);
+  data->desc.mode = B200_IMAGE_CIFAR10;
+  data->desc.channels = 3;
+  data->desc.height = data->desc.width = 32;
+  data->desc.x_padding = x_padding;
+  data->desc.y_padding = y_padding;
+  data->desc.scale_min = scale_min;
+  data->desc.scale_max = scale_max;
+  uint8_t label;
+  std::vector<char> buf(3 * 32 * 32);
+  while (ifs.read(reinterpret_cast<char *>(&label), 1)) {
+    if (!ifs.read(buf.data(), buf.size())) break;
+    data->labels.push_back(label);
+    data->images.insert(data->images.end(), buf.begin(), buf.end());
+  }
+}
+
+// the images of an MNIST idx3-ubyte file and the labels of the matching idx1-ubyte file
+// (mnist_parser.h:88-157: big-endian headers, magic numbers 0x803 / 0x801)
+inline void load_mnist_u8(const std::string &image_file, const std::string &label_file, u8_dataset *data,
+                          float_t scale_min, float_t scale_max, int x_padding, int y_padding) {
+  if (x_padding < 0 || y_padding < 0) throw nn_error("padding size must not be negative");
+  if (scale_min >= scale_max) throw nn_error("scale_max must be greater than scale_min");
+  auto be32 = [](std::ifstream &f) {
+    unsigned char b[4] = {0, 0, 0, 0};
+    f.read(reinterpret_cast<char *>(b), 4);
+    return (uint32_t(b[0]) << 24) | (uint32_t(b[1]) << 16) | (uint32_t(b[2]) << 8) | uint32_t(b[3]);
+  };
+  std::ifstream fi(image_file.c_str(), std::ios::in | std::ios::binary);
+  if (fi.bad() || fi.fail()) throw nn_error("failed to open file:" + image_file);
+  const uint32_t magic = be32(fi), n = be32(fi), rows = be32(fi), cols = be32(fi);
+  if (magic != 0x00000803 || n == 0) throw nn_error("MNIST label-file format error");
+  if (fi.fail() || fi.bad()) throw nn_error("file error");
+  std::ifstream fl(label_file.c_str(), std::ios::in | std::ios::binary);
+  if (fl.bad() || fl.fail()) throw nn_error("failed to open file:" + label_file);
+  const uint32_t lmagic = be32(fl), ln = be32(fl);
+  if (lmagic != 0x00000801 || ln != n) throw nn_error("MNIST label-file format error");
+  data->desc.mode = B200_IMAGE_MNIST;
+  data->desc.channels = 1;
+  data->desc.height = static_cast<int32_t>(rows);
+  data->desc.width = static_cast<int32_t>(cols);
+  data->desc.x_padding = x_padding;
+  data->desc.y_padding = y_padding;
+  data->desc.scale_min = scale_min;
+  data->desc.scale_max = scale_max;
+  const size_t off = data->images.size(), loff = data->labels.size();
+  data->images.resize(off + size_t(n) * rows * cols);
+  fi.read(reinterpret_cast<char *>(data->images.data() + off), std::streamsize(size_t(n) * rows * cols));
+  data->labels.resize(loff + n);
+  fl.read(reinterpret_cast<char *>(data->labels.data() + loff), n);
+  if (fi.fail() || fl.fail()) throw nn_error("file error");
+}
+
+// network::train<Error>(optimizer, images, labels, batch, epochs, callbacks) (network.h:268-307)
+// from the raw bytes.  Throws when the network is not wholly on the path: this entry has no host
+// form to fall back to (parse with the reference's parsers and call nn.train for that).
+template <typename Error, typename Optimizer, typename OnBatch, typename OnEpoch>
+bool train_u8(network<sequential> &nn, Optimizer &opt, const u8_dataset &data, size_t batch_size, int epoch,
+              OnBatch on_batch_enumerate, OnEpoch on_epoch_enumerate, bool reset_weights = false) {
+  const int loss = loss_kind<Error>::value;
+  if (loss < 0) throw nn_error("b200::train_u8: loss function is not on the path");
+  opt_choice oc = choose_optimizer(static_cast<optimizer *>(&opt));
+  if (oc.kind < 0) throw nn_error("b200::train_u8: optimizer is not adagrad, adam or momentum");
+  const size_t N = data.size();
+  if (N < batch_size || batch_size == 0) return false;  // as network::train (network.h:297-299)
+  // what fit() does before its loop (network.h:852-857)
+  nn.set_netphase(net_phase::train);
+  for (size_t i = 0; i < nn.depth(); ++i) nn[i]->setup(reset_weights);
+  for (size_t i = 0; i < nn.depth(); ++i) nn[i]->set_parallelize(true);
+  opt.reset();
+  const int batch = static_cast<int>(batch_size);
+  std::shared_ptr<device_twin> tw = twin_for(nn, batch);
+  if (!tw) throw nn_error(std::string("b200::train_u8: the network is not wholly on the B200 path: ") + b200_last_error());
+  const std::pair<float_t, float_t> range = nn[nn.depth() - 1]->out_value_range();  // nodes.h:147-156
+  // page-locked copies of the bytes, so that uploads overlap the steps
+  const size_t img_bytes = data.images.size();
+  tw->x.reserve((img_bytes + 3) / 4);
+  tw->t.reserve((N + 3) / 4);
+  uint8_t *ip = reinterpret_cast<uint8_t *>(tw->x.p), *lp = reinterpret_cast<uint8_t *>(tw->t.p);
+  std::memcpy(ip, data.images.data(), img_bytes);
+  std::memcpy(lp, data.labels.data(), N);
+  weights_to_device(nn, *tw);
+  check(b200_net_opt_reset(tw->net, 1));
+  if (oc.as_adam) check(b200_net_set_adam_powers(tw->net, oc.h.b1, oc.h.b2, oc.as_adam->b1_t, oc.as_adam->b2_t));
+  const long long steps_per_epoch = static_cast<long long>((N + batch - 1) / batch);
+  for (int iter = 0; iter < epoch; ++iter) {
+    check(b200_net_fit_u8_host(tw->net, &data.desc, ip, lp, static_cast<long long>(N), batch, 1, range.first,
+                               range.second, loss, oc.kind, &oc.h, nullptr));
+    check(b200_ctx_sync(ctx()));
+    state_to_host(nn, *tw, oc, steps_per_epoch);
+    for (long long b = 0; b < steps_per_epoch; ++b) on_batch_enumerate();
+    on_epoch_enumerate();
+  }
+  nn.set_netphase(net_phase::test);
+  ++device_fit_count();
+  return true;
+}
+
+template <typename Error, typename Optimizer>
+bool train_u8(network<sequential> &nn, Optimizer &opt, const u8_dataset &data, size_t batch_size = 1, int epoch = 1) {
+  return train_u8<Error>(nn, opt, data, batch_size, epoch, nop, nop);
+}
+
+template <typename Error, typename Net, typename Optimizer, typename In, typename Tg, typename OnBatch,
+          typename OnEpoch>
+bool fit_dispatch(std::false_type, Net &, Optimizer &, const std::vector<In> &, const std::vector<Tg> &, size_t, int,
+                  OnBatch, OnEpoch, bool, bool, bool *) {
   return false;  // graph networks keep the reference loop
 }
-template <typename Error, typename Net, typename Optimizer, typename OnBatch, typename OnEpoch>
-bool fit_dispatch(std::true_type, Net &nn, Optimizer &opt, const std::vector<tensor_t> &inputs,
-                  const std::vector<tensor_t> &desired_outputs, size_t batch_size, int epoch, OnBatch on_batch,
-                  OnEpoch on_epoch, const std::vector<tensor_t> &t_cost, const bool *stop) {
-  return fit_sequential<Error>(nn, opt, inputs, desired_outputs, batch_size, epoch, on_batch, on_epoch, t_cost,
-                               stop);
+template <typename Error, typename Net, typename Optimizer, typename In, typename Tg, typename OnBatch,
+          typename OnEpoch>
+bool fit_dispatch(std::true_type, Net &nn, Optimizer &opt, const std::vector<In> &inputs,
+                  const std::vector<Tg> &targets, size_t batch_size, int epoch, OnBatch on_batch, OnEpoch on_epoch,
+                  bool preamble, bool reset_weights, bool *stop) {
+  return fit_sequential<Error>(nn, opt, inputs, targets, batch_size, epoch, on_batch, on_epoch, preamble,
+                               reset_weights, stop);
 }
 
 }  // namespace b200
 
-// declared in the patched network.h, called from network::fit
+// Declared in the patched network.h.  b200_fit_hook is called from the private network::fit after
+// its own set-up (for callers that hand over std::vector<tensor_t>); b200_fit_hook_rows from the
+// public fit / train overloads before they copy the whole data set into tensors
+// (normalize_tensor, network.h:1085-1098), which the device path has no use for.
 template <typename Error, typename Net, typename Optimizer, typename OnBatch, typename OnEpoch>
 bool b200_fit_hook(Net &nn, Optimizer &opt, const std::vector<tensor_t> &inputs,
                    const std::vector<tensor_t> &desired_outputs, size_t batch_size, int epoch, OnBatch on_batch,
-                   OnEpoch on_epoch, const std::vector<tensor_t> &t_cost, const bool *stop) {
-  return b200::fit_dispatch<Error>(std::is_same<Net, network<sequential>>(), nn, opt, inputs,
-                                   desired_outputs, batch_size, epoch, on_batch, on_epoch, t_cost, stop);
+                   OnEpoch on_epoch, const std::vector<tensor_t> &t_cost, bool *stop) {
+  if (!t_cost.empty()) return false;
+  return b200::fit_dispatch<Error>(std::is_same<Net, network<sequential>>(), nn, opt, inputs, desired_outputs,
+                                   batch_size, epoch, on_batch, on_epoch, false, false, stop);
+}
+
+template <typename Error, typename Net, typename Optimizer, typename In, typename Tg, typename OnBatch,
+          typename OnEpoch>
+bool b200_fit_hook_rows(Net &nn, Optimizer &opt, const std::vector<In> &inputs, const std::vector<Tg> &targets,
+                        size_t batch_size, int epoch, OnBatch on_batch, OnEpoch on_epoch, bool reset_weights,
+                        bool *stop) {
+  return b200::fit_dispatch<Error>(std::is_same<Net, network<sequential>>(), nn, opt, inputs, targets, batch_size,
+                                   epoch, on_batch, on_epoch, true, reset_weights, stop);
 }
 
 }  // namespace tiny_dnn

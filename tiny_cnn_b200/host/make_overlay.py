@@ -235,7 +235,33 @@ def patch_network_h(t, p):
               "bool b200_fit_hook(Net &nn, Optimizer &optimizer, const std::vector<tensor_t> &inputs,\n"
               "                   const std::vector<tensor_t> &desired_outputs, size_t batch_size, int epoch,\n"
               "                   OnBatch on_batch, OnEpoch on_epoch, const std::vector<tensor_t> &t_cost,\n"
-              "                   const bool *stop);\n", p)
+              "                   bool *stop);\n"
+              "template <typename Error, typename Net, typename Optimizer, typename In, typename Tg, typename OnBatch,\n"
+              "          typename OnEpoch>\n"
+              "bool b200_fit_hook_rows(Net &nn, Optimizer &optimizer, const std::vector<In> &inputs,\n"
+              "                        const std::vector<Tg> &targets, size_t batch_size, int epoch, OnBatch on_batch,\n"
+              "                        OnEpoch on_epoch, bool reset_weights, bool *stop);\n", p)
+    # the public train (class labels) and fit (target vectors) overloads, before normalize_tensor
+    t = _edit(t, "    std::vector<tensor_t> input_tensor, output_tensor, t_cost_tensor;\n"
+                 "    normalize_tensor(inputs, input_tensor);\n"
+                 "    normalize_tensor(class_labels, output_tensor);\n",
+              "    if (t_cost.empty() &&\n"
+              "        b200_fit_hook_rows<Error>(*this, optimizer, inputs, class_labels, batch_size, epoch,\n"
+              "                                  on_batch_enumerate, on_epoch_enumerate, reset_weights, &stop_training_))\n"
+              "      return true;\n"
+              "    std::vector<tensor_t> input_tensor, output_tensor, t_cost_tensor;\n"
+              "    normalize_tensor(inputs, input_tensor);\n"
+              "    normalize_tensor(class_labels, output_tensor);\n", p)
+    t = _edit(t, "    std::vector<tensor_t> input_tensor, output_tensor, t_cost_tensor;\n"
+                 "    normalize_tensor(inputs, input_tensor);\n"
+                 "    normalize_tensor(desired_outputs, output_tensor);\n",
+              "    if (t_cost.empty() &&\n"
+              "        b200_fit_hook_rows<Error>(*this, optimizer, inputs, desired_outputs, batch_size, epoch,\n"
+              "                                  on_batch_enumerate, on_epoch_enumerate, reset_weights, &stop_training_))\n"
+              "      return true;\n"
+              "    std::vector<tensor_t> input_tensor, output_tensor, t_cost_tensor;\n"
+              "    normalize_tensor(inputs, input_tensor);\n"
+              "    normalize_tensor(desired_outputs, output_tensor);\n", p)
     t = _edit(t, "    optimizer.reset();\n    stop_training_ = false;\n",
               "    optimizer.reset();\n    stop_training_ = false;\n"
               "    if (b200_fit_hook<Error>(*this, optimizer, inputs, desired_outputs, batch_size, epoch,\n"

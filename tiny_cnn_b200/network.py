@@ -16,7 +16,8 @@ import torch
 
 from . import _lib as L
 from ._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_RELU, LAYER_SOFTMAX,
-                   LAYER_TANH, LOSS_CROSS_ENTROPY, LOSS_MSE, OPT_ADAGRAD, OPT_ADAM, OPT_MOMENTUM,
+                   LAYER_TANH, LOSS_CROSS_ENTROPY, LOSS_MSE, OPT_ADAGRAD, OPT_ADAM, OPT_ADAMAX, OPT_GRADIENT_DESCENT,
+                   OPT_MOMENTUM, OPT_NESTEROV_MOMENTUM, OPT_RMSPROP,
                    LayerSpec, OptHyper, check, ptr)
 from .ops import Context, conv_params, hyper, maxpool_params
 
@@ -56,6 +57,50 @@ class adam:
 class momentum:
     """tiny_dnn/optimizers/optimizer.h:201-218"""
     kind = OPT_MOMENTUM
+
+    def __init__(self, alpha=0.01, mu=0.9, lambda_=0.0):
+        self.alpha, self.mu, self.lambda_ = alpha, mu, lambda_
+
+    def hyper(self) -> OptHyper:
+        return hyper(alpha=self.alpha, mu=self.mu, lambda_=self.lambda_)
+
+
+class RMSprop:
+    """tiny_dnn/optimizers/optimizer.h:79-95"""
+    kind = OPT_RMSPROP
+
+    def __init__(self, alpha=0.0001, mu=0.99):
+        self.alpha, self.mu = alpha, mu
+
+    def hyper(self) -> OptHyper:
+        return hyper(alpha=self.alpha, mu=self.mu)
+
+
+class adamax:
+    """tiny_dnn/optimizers/optimizer.h:145-175"""
+    kind = OPT_ADAMAX
+
+    def __init__(self, alpha=0.002, b1=0.9, b2=0.999):
+        self.alpha, self.b1, self.b2 = alpha, b1, b2
+
+    def hyper(self) -> OptHyper:
+        return hyper(alpha=self.alpha, b1=self.b1, b2=self.b2)
+
+
+class gradient_descent:
+    """tiny_dnn/optimizers/optimizer.h:182-193"""
+    kind = OPT_GRADIENT_DESCENT
+
+    def __init__(self, alpha=0.01, lambda_=0.0):
+        self.alpha, self.lambda_ = alpha, lambda_
+
+    def hyper(self) -> OptHyper:
+        return hyper(alpha=self.alpha, lambda_=self.lambda_)
+
+
+class nesterov_momentum:
+    """tiny_dnn/optimizers/optimizer.h:227-245"""
+    kind = OPT_NESTEROV_MOMENTUM
 
     def __init__(self, alpha=0.01, mu=0.9, lambda_=0.0):
         self.alpha, self.mu, self.lambda_ = alpha, mu, lambda_
@@ -266,7 +311,8 @@ class Sequential:
     def fit(self, opt, inputs, targets, batch_size: int, epochs: int, loss: int, outputs=None):
         """network::fit (tiny_dnn/network.h:840-879) over HOST arrays [N][dim]: one library call,
         uploads overlapped with the steps.  `outputs` [N][out_dim] receives every step's forward
-        output."""
+        output.  When N is not a multiple of the mini-batch, the short last step is completed with
+        the previous step's rows, as the reference's batch buffers do (network.h:911-926)."""
         h = opt.hyper()
         check(self.lib.b200_net_fit_host(self.handle, ptr(inputs), ptr(targets), inputs.shape[0],
                                          batch_size, epochs, loss, opt.kind, C.byref(h), ptr(outputs)))
