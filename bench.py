@@ -374,7 +374,8 @@ def run_b200(args, rank, world, local_rank):
         """Repeat the block until MIN_TIMED_MS have been timed (every rank sees the same max-reduced
         times, so every rank stops after the same block)."""
         times, launches = [], 0
-        while (sum(times) < MIN_TIMED_MS or len(times) < 3) and len(times) < MAX_BLOCKS:
+        min_ms, min_blocks = (0.0, 1) if args.profile else (MIN_TIMED_MS, 3)
+        while (sum(times) < min_ms or len(times) < min_blocks) and len(times) < MAX_BLOCKS:
             ms, launches = timed_block(run_steps, steps)
             times.append(ms)
         return times, launches
@@ -438,14 +439,14 @@ def run_b200(args, rank, world, local_rank):
     line = None
     if rank == 0:
         # per-kernel roofline of the convolution kernels, timed alone with CUDA events
-        kt = time_kernels(ctx, torch, ops)
+        kt = time_kernels(ctx, torch, ops, reps=2 if args.profile else 20)
         peaks = {}
         mp = ROOT / "MEASURED_PEAKS.json"
         if mp.exists():
             peaks = json.loads(mp.read_text())
         kernels, roofline = conv_rooflines(kt, peaks)
-        cpu = cpu_baseline() if world == 1 else None
-        cpp = e2e_cpp(max(4 * args.steps, 200)) if world == 1 else None
+        cpu = cpu_baseline() if world == 1 and not args.profile else None
+        cpp = e2e_cpp(max(4 * args.steps, 200)) if world == 1 and not args.profile else None
         per = 1.0 / args.steps
         line = {
             "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
@@ -625,6 +626,8 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for a profiler: one timed block per leg, no CPU baseline, no per-kernel timing")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -489,7 +489,11 @@ B200_API int b200_net_get_grads(b200_net *net, float *host_grads);
 B200_API float *b200_net_params_ptr(b200_net *net);
 B200_API float *b200_net_grads_ptr(b200_net *net);
 B200_API float *b200_net_output_ptr(b200_net *net);
-/* Device pointer to the output of layer `i` / its gradient (tests). */
+/* Device pointer to the output of layer `i` / its gradient dE/d out, [batch][dim] CHW rows
+ * (tests).  A layer whose activation was folded into its producer has no output of its own
+ * (NULL).  The gradient of a convolution whose backward kernels all read the pixel-major copy
+ * is kept in that form only, and this buffer is then not written; set the environment variable
+ * B200_NET_KEEP_GRADS=1 before b200_net_create to have every gradient here as well. */
 B200_API float *b200_net_layer_out_ptr(b200_net *net, int i);
 B200_API float *b200_net_layer_grad_ptr(b200_net *net, int i);
 

@@ -208,11 +208,15 @@ static void compare_nets(network<sequential> &a, network<sequential> &c, double 
 // Whole-net comparison at a large batch under adam.  Two fp32 evaluation orders agree on the forward
 // pass to ~1e-6, which is enough for a relu gate or a max-pooling winner to be decided differently
 // once in a few million positions; the gradient of that output channel then differs by that
-// position's whole contribution, and adam turns any gradient difference into a weight difference of
-// up to one learning rate per step.  So: the bulk of every tensor within 1e-3, and no entry further
-// away than adam can move it.
+// position's whole contribution, adam turns any gradient difference into a weight difference of
+// up to one learning rate per step, and from the next step on that channel's activations differ at
+// the 1e-3 level and many more decisions with them: the two trajectories separate the way the
+// reference's own internal and AVX engines separate from each other on such a run (after six adam
+// steps at batch 256 only ~65 % of their first-layer weights still agree to 1e-3, the worst by
+// 1.6e-2 of the largest; after three steps all do).  So: at least `min_frac` of every tensor within
+// 1e-3, and no entry further away than a quarter of what adam can have moved it.
 static void compare_nets_large_batch(network<sequential> &a, network<sequential> &c, double alpha, int steps,
-                                     const char *label) {
+                                     double min_frac, const char *label) {
   for (size_t i = 0; i < a.depth(); ++i) {
     auto wa = a[i]->weights();
     auto wc = c[i]->weights();
@@ -228,9 +232,10 @@ static void compare_nets_large_batch(network<sequential> &a, network<sequential>
       }
       const double frac = (double)within / (double)y.size();
       char what[200];
-      snprintf(what, sizeof(what), "%s: layer %zu tensor %zu: %.1f%% within 1e-3, largest difference %.2e (adam bound %.2e)",
-               label, i, k, 100.0 * frac, worst, 2.0 * alpha * steps);
-      expect(frac >= 0.80 && worst <= 2.0 * alpha * steps, what);
+      const double bound = 0.25 * alpha * steps;
+      snprintf(what, sizeof(what), "%s: layer %zu tensor %zu: %.1f%% within 1e-3, largest difference %.2e (bound %.2e)",
+               label, i, k, 100.0 * frac, worst, bound);
+      expect(frac >= min_frac && worst <= bound, what);
     }
   }
 }
@@ -288,7 +293,7 @@ static void ab_cifar_fit(size_t B, bool strict) {
     compare_nets(a, c, 1e-3, label);
     compare_state(a, c, oa, oc, 2, label);
   } else {
-    compare_nets_large_batch(a, c, oa.alpha, (int)steps, label);
+    compare_nets_large_batch(a, c, oa.alpha, (int)steps, 0.95, label);
   }
   expect(oa.b1_t == oc.b1_t && oa.b2_t == oc.b2_t, "CIFAR net: adam powers written back equal the CPU object's");
   // a second fit continues from the written-back powers (fit resets the state maps, not the powers)
@@ -298,10 +303,10 @@ static void ab_cifar_fit(size_t B, bool strict) {
   if (strict)
     compare_nets(a, c, 1e-3, label);
   else
-    compare_nets_large_batch(a, c, oa.alpha, 2 * (int)steps, label);
+    compare_nets_large_batch(a, c, oa.alpha, 2 * (int)steps, 0.0, label);
   expect(oa.b1_t == oc.b1_t && oa.b2_t == oc.b2_t, "CIFAR net: adam powers after the second fit");
   vec_t pa = a.predict(x[0]), pc = c.predict(x[0]);
-  close_vec(pc, pa, strict ? 1e-4 : 5e-3, "CIFAR net predict after fit");
+  close_vec(pc, pa, strict ? 1e-4 : 2e-2, "CIFAR net predict after fit");
 }
 
 // BASELINE configuration 1: LeNet-5 (average pooling with trainable scale, tanh, connection table),

@@ -116,6 +116,45 @@ def main():
             assert np.array_equal(p_fit, p_manual), "fprop/bprop/merge/update by hand differs from network::fit"
             print(f"net {name}: network::fit gives the same weights bit for bit", flush=True)
 
+    # ---- how far two fp32 evaluation orders drift apart: the reference against itself ---------
+    # The CIFAR-10 net at batch 256 trained by the reference twice from the same weights on the same
+    # data: engine backend_t::internal, and the reference's own AVX kernels (backend_t::avx, built
+    # from the same sources with -DCNN_USE_AVX).  Recorded after one fit of three adam steps and
+    # after a second one: per parameter tensor the share of entries that agree to 1e-3 of the
+    # largest magnitude and the worst difference.  This is the yardstick for what "the same result"
+    # can mean for whole-net weights at this size (see tests/test_oracle_fullsize.py).
+    if want("divergence"):
+        avx = o.load_reference_avx()
+        if avx is None:
+            raise SystemExit("oracle/_ref/libtinydnn_ref_avx.so is missing")
+        c = FULL_NET_CASES["cifar_adam_b256"]
+        specs, keep = build_net_specs(c["net"])
+        arr = (type(specs[0]) * len(specs))(*specs)
+        layout, n = net_layout(specs)
+        x, t = gen_net_data(c)
+        hy = hyper_for(c["opt"])
+        p0 = xavier_params(specs, c["seed"])
+        runs = {}
+        for label, lib in (("internal", ref), ("avx", avx)):
+            h = lib.ref_net_create(arr, len(specs), 1)
+            lib.ref_net_set_params(h, o.p(p0))
+            runs[label] = []
+            for fit in range(2):
+                assert lib.ref_net_fit(h, o.p(x), o.p(t), c["B"], c["steps"], c["loss"], c["opt"], C.byref(hy)) >= 0
+                p = o.f32(n)
+                lib.ref_net_get_params(h, o.p(p))
+                runs[label].append(p)
+            lib.ref_net_destroy(h)
+        table = np.zeros((2, len(layout), 2))
+        for fit in range(2):
+            for ti, (off, ln, _, _, _) in enumerate(layout):
+                a, b = runs["internal"][fit][off:off + ln], runs["avx"][fit][off:off + ln]
+                d, mx = np.abs(a.astype(np.float64) - b), float(np.abs(a).max())
+                table[fit, ti] = [(d <= 1e-3 * mx).mean(), d.max() / mx]
+        out["divergence/internal_vs_avx"] = table
+        print("reference internal vs AVX engine, [fit][tensor](share within 1e-3, worst / max):")
+        print(np.array2string(table, precision=4, suppress_small=True), flush=True)
+
     # ---- quantized inference ----------------------------------------------------------------
     if want("quant"):
         t0 = time.time()

@@ -6,8 +6,9 @@ inside the library instead of a buffer grown with cudaMalloc.
 
 It is called through the C ABI twice in a row, with different layer shapes so the
 second call finds the first call's partial sums still in the array, and each
-result is compared with the regular entry point b200_conv2d_bwd within the
-gradient tolerance of the other GPU tests.  The file sorts last so that a run
+result is compared with the regular entry point b200_conv2d_bwd -- and, for the
+calls that start from zero, with the CPU oracle's batch-summed weight gradient --
+within the gradient tolerance of the other GPU tests.  The file sorts last so that a run
 stopping at the first failure has already run every other test."""
 import ctypes as C
 
@@ -27,6 +28,19 @@ def close(got, want, tol, what):
     scale = max(float(np.abs(want).max()), 1e-30)
     err = np.abs(got - want)
     assert (err <= tol * (np.abs(want) + scale)).all(), f"{what}: max err {err.max():g} (scale {scale:g})"
+
+
+def oracle_dw(d, x, W, dy, batch):
+    """batch-summed dW / db of the CPU restatement (oracle.c: conv2d_op_internal.h:130-179)."""
+    import oracle_lib as o
+    orc = o.load_oracle()
+    xh, dyh = x.cpu().numpy(), dy.cpu().numpy()
+    xp = o.f32(batch, d.in_c * d.inp_h * d.inp_w)
+    orc.orc_conv_pad(C.byref(d), o.p(xh), o.p(xp), batch)
+    dxp, dW, db = o.f32(*xp.shape), o.f32(W.numel()), o.f32(d.out_c)
+    Wh = W.cpu().numpy()
+    orc.orc_conv2d_bwd(C.byref(d), o.p(xp), o.p(Wh), o.p(dyh), o.p(dxp), o.p(dW), o.p(db), 0, batch)
+    return torch.from_numpy(dW), torch.from_numpy(db)
 
 
 def run_pair(ctx, lib, w, c, oc, k, batch, same, accumulate, seed):
@@ -49,6 +63,10 @@ def run_pair(ctx, lib, w, c, oc, k, batch, same, accumulate, seed):
     torch.cuda.synchronize()
     close(dW, dW_ref, GRAD_TOL, f"dW {w}x{w}x{c}->{oc} k{k}")
     close(db, db_ref, GRAD_TOL, f"db {w}x{w}x{c}->{oc} k{k}")
+    if not accumulate:
+        dW_orc, db_orc = oracle_dw(d, x, W, dy, batch)
+        close(dW.cpu(), dW_orc, GRAD_TOL, f"dW {w}x{w}x{c}->{oc} k{k} vs oracle")
+        close(db.cpu(), db_orc, GRAD_TOL, f"db {w}x{w}x{c}->{oc} k{k} vs oracle")
 
 
 def test_noalloc_weight_gradient_matches_regular_entry_point(ctx):

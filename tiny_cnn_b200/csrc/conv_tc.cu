@@ -173,7 +173,57 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
     // argmax names.  (channel, pixel) pairs are spread over the whole block, so that narrow images
     // (a handful of pooled pixels per chunk) still fill the lanes; consecutive threads read
     // consecutive pooled pixels, and consecutive channel planes are neighbours in memory.
-    const int pw = W >> 1, ph = H >> 1, nq = ((nr + 1) >> 1) * pw;
+    const int pw = W >> 1, ph = H >> 1;
+    if ((W & 3) == 0) {
+      // two pooled pixels of one channel per thread: 8-byte loads of the pooled gradient and the
+      // winners, 16-byte loads / stores of the two input rows they cover
+      const int pw2 = pw >> 1, nq = ((nr + 1) >> 1) * pw2;
+      const int pws = (pw2 & (pw2 - 1)) == 0 ? 31 - __clz(pw2) : -1;
+      for (int it = threadIdx.x; it < C * nq; it += 256) {
+        const int c = it / nq, q = it - c * nq;
+        const int pry = pws >= 0 ? q >> pws : q / pw2, prx = (q - pry * pw2) * 2, ry = 2 * pry, x = 2 * prx,
+                  y = r0 + ry;
+        const int pp = ry * W + x;
+        float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+        if (y < H) {
+          const size_t po = ((size_t)b * C + c) * ph * pw + (size_t)(y >> 1) * pw + prx;
+          const size_t o = ((size_t)b * C + c) * plane + (size_t)y * W + x;
+          const float2 gv = *reinterpret_cast<const float2 *>(src.a + po);
+          const int2 am = *reinterpret_cast<const int2 *>(src.am + po);
+          const int base0 = (H * c + y) * W + x;
+          const int a0 = am.x - base0, a1 = am.y - (base0 + 2);  // offset inside the window: 0, 1, W, W+1
+          float4 ra = make_float4(1.f, 1.f, 1.f, 1.f), rb2 = ra;
+          if (src.relu_y != nullptr) {
+            ra = *reinterpret_cast<const float4 *>(src.relu_y + o);
+            rb2 = *reinterpret_cast<const float4 *>(src.relu_y + o + W);
+          }
+          v0.x = (a0 == 0 && ra.x > 0.f) ? gv.x : 0.f;
+          v0.y = (a0 == 1 && ra.y > 0.f) ? gv.x : 0.f;
+          v0.z = (a1 == 0 && ra.z > 0.f) ? gv.y : 0.f;
+          v0.w = (a1 == 1 && ra.w > 0.f) ? gv.y : 0.f;
+          v1.x = (a0 == W && rb2.x > 0.f) ? gv.x : 0.f;
+          v1.y = (a0 == W + 1 && rb2.y > 0.f) ? gv.x : 0.f;
+          v1.z = (a1 == W && rb2.z > 0.f) ? gv.y : 0.f;
+          v1.w = (a1 == W + 1 && rb2.w > 0.f) ? gv.y : 0.f;
+          if (src.out_chw != nullptr) {
+            *reinterpret_cast<float4 *>(src.out_chw + o) = v0;
+            *reinterpret_cast<float4 *>(src.out_chw + o + W) = v1;
+          }
+        }
+        float *trow = tile + c * pitch + pp;
+        trow[0] = v0.x;
+        trow[1] = v0.y;
+        trow[2] = v0.z;
+        trow[3] = v0.w;
+        if (ry + 1 < nr) {
+          trow[W] = v1.x;
+          trow[W + 1] = v1.y;
+          trow[W + 2] = v1.z;
+          trow[W + 3] = v1.w;
+        }
+      }
+    } else {
+    const int nq = ((nr + 1) >> 1) * pw;
     const int pws = (pw & (pw - 1)) == 0 ? 31 - __clz(pw) : -1;
     for (int it = threadIdx.x; it < C * nq; it += 256) {
       const int c = it / nq, q = it - c * nq;
@@ -206,6 +256,7 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
         trow[pp + W] = v2;
         trow[pp + W + 1] = v3;
       }
+    }
     }
   }
   __syncthreads();

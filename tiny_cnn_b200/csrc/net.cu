@@ -82,6 +82,7 @@ struct b200_net {
   int fit_rows = 0;  // rows of x_dev / t_dev the last step of a fit call ran on
   bool fuse = true;
   bool input_grad = true;
+  bool keep_layer_grads = false;  // B200_NET_KEEP_GRADS=1: every layer's dE/d out also in CHW form
   PeerReduce peer;  // data-parallel replicas: the gradient bucket is summed over the ranks inside the step
   // the layers after `peer_early_layer` (inclusive) own bucket entries [peer.split, n): once their weight
   // gradients exist they are pushed to the peers from `comm`, beside the rest of the backward pass
@@ -300,9 +301,14 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
           // gradient of this layer (and of the relu before it) written straight into the forms the
           // tensor-core convolution reads: tall split copy, CHW gradient, bias partials
           Layer &Cv = net->layers[L.grad_to_conv];
+          // the CHW form of the convolution's dY is written only when one of its backward kernels
+          // reads it (the tensor-core dW and dX passes read the tall copy)
+          const bool cv_din = L.grad_to_conv > 0 || net->input_grad;
+          const bool chw_read = !Cv.tc.dw || (cv_din && !Cv.tc.dx) || net->keep_layer_grads;
           B200_TRY(conv_tc_tall_dy_unpool(ctx, Cv.g, L.grad, L.argmax,
-                                          L.relu_bwd_fused ? net->layers[i - 1].out : nullptr, Cv.grad, B,
-                                          Cv.tc_dys, Cv.tc.dw && Cv.b_len ? Cv.tc_bsum : nullptr));
+                                          L.relu_bwd_fused ? net->layers[i - 1].out : nullptr,
+                                          chw_read ? Cv.grad : nullptr, B, Cv.tc_dys,
+                                          Cv.tc.dw && Cv.b_len ? Cv.tc_bsum : nullptr));
         } else if (L.relu_bwd_fused) {
           // the relu before this layer was folded into the producer's epilogue: apply
           // its gradient mask here and write straight into the producer's gradient
@@ -425,6 +431,7 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
   net->layers.resize(n_layers);
   if (const char *e = getenv("B200_NET_NO_FUSE")) net->fuse = !(e[0] == '1');
   if (const char *e = getenv("B200_NET_NO_GRAPH")) net->use_graph = !(e[0] == '1');
+  if (const char *e = getenv("B200_NET_KEEP_GRADS")) net->keep_layer_grads = e[0] == '1';
   if (!getenv("B200_NET_NO_SIDE")) {
     cudaStreamCreateWithFlags(&net->side, cudaStreamNonBlocking);
     cudaEventCreateWithFlags(&net->ev_fork, cudaEventDisableTiming);
