@@ -19,6 +19,12 @@ using namespace tiny_dnn;
 
 static int g_fail = 0;
 
+static unsigned long long device_fit_count_now() { return b200::device_fit_count(); }
+static void expect_ok(bool ok, const char *what) {
+  printf(ok ? "ok   %s\n" : "FAIL %s\n", what);
+  if (!ok) ++g_fail;
+}
+
 static double max_abs(const vec_t &v) {
   double m = 0;
   for (auto x : v) m = std::max(m, (double)std::fabs(x));
@@ -135,6 +141,45 @@ static void build_net(network<sequential> &nn, core::backend_t e) {
      << pool(6, 6, 12, 2, false, e) << fc(3 * 3 * 12, 10, true, e) << softmax_layer(10);
 }
 
+// the remaining optimizers through the device-resident fit: same small network, a few steps each
+template <typename Opt>
+static void ab_optimizer(const char *name, int n_state) {
+  network<sequential> a, c;
+  build_net(a, core::backend_t::internal);
+  build_net(c, core::backend_t::b200);
+  set_random_seed(7);
+  a.init_weight();
+  c.init_weight();
+  for (size_t i = 0; i < a.depth(); ++i) {
+    auto wa = a[i]->weights();
+    auto wc = c[i]->weights();
+    for (size_t k = 0; k < wa.size(); ++k) *wc[k] = *wa[k];
+  }
+  std::mt19937 g(13);
+  const size_t B = 8, steps = 4;
+  std::vector<vec_t> x(B * steps, vec_t(16 * 16 * 3)), t(B * steps, vec_t(10, 0.f));
+  std::normal_distribution<float> nd(0.f, 1.f);
+  for (auto &v : x)
+    for (auto &e : v) e = nd(g);
+  for (auto &v : t) v[g() % 10] = 1.f;
+  Opt oa, oc;
+  const unsigned long long fits = device_fit_count_now();
+  a.fit<cross_entropy>(oa, x, t, B, 1);
+  c.fit<cross_entropy>(oc, x, t, B, 1);
+  char what[160];
+  snprintf(what, sizeof(what), "%s: network::fit ran as the device-resident step", name);
+  expect_ok(device_fit_count_now() == fits + 1, what);
+  for (size_t i = 0; i < a.depth(); ++i) {
+    auto wa = a[i]->weights();
+    auto wc = c[i]->weights();
+    for (size_t k = 0; k < wa.size(); ++k) {
+      snprintf(what, sizeof(what), "%s fit: layer %zu tensor %zu after %zu steps", name, i, k, steps);
+      close_vec(*wc[k], *wa[k], 1e-3, what);
+    }
+  }
+  (void)n_state;
+}
+
 static void ab_network() {
   network<sequential> a, c;
   build_net(a, core::backend_t::internal);
@@ -214,7 +259,10 @@ static void compare_nets(network<sequential> &a, network<sequential> &c, double 
 // reference's own internal and AVX engines separate from each other on such a run (after six adam
 // steps at batch 256 only ~65 % of their first-layer weights still agree to 1e-3, the worst by
 // 1.6e-2 of the largest; after three steps all do).  So: at least `min_frac` of every tensor within
-// 1e-3, and no entry further away than a quarter of what adam can have moved it.
+// 1e-3, and no entry further away than half of what adam can have moved it (one adam step moves a
+// weight by up to alpha in the direction of its gradient's sign, so two runs whose gradients for a
+// weight differ in sign separate by up to 2*alpha a step; the reference's own two CPU engines end
+// 1.6e-2 of the largest weight apart on this case).
 static void compare_nets_large_batch(network<sequential> &a, network<sequential> &c, double alpha, int steps,
                                      double min_frac, const char *label) {
   for (size_t i = 0; i < a.depth(); ++i) {
@@ -232,7 +280,7 @@ static void compare_nets_large_batch(network<sequential> &a, network<sequential>
       }
       const double frac = (double)within / (double)y.size();
       char what[200];
-      const double bound = 0.25 * alpha * steps;
+      const double bound = 0.5 * alpha * steps;
       snprintf(what, sizeof(what), "%s: layer %zu tensor %zu: %.1f%% within 1e-3, largest difference %.2e (bound %.2e)",
                label, i, k, 100.0 * frac, worst, bound);
       expect(frac >= min_frac && worst <= bound, what);
@@ -485,6 +533,12 @@ int main() {
       ab_layer("average pooling 2x2 (set_backend_type)", l, 4, true, 10);
     }
     ab_network();
+    ab_optimizer<RMSprop>("RMSprop", 1);
+    ab_optimizer<adamax>("adamax", 2);
+    ab_optimizer<gradient_descent>("gradient_descent", 0);
+    ab_optimizer<nesterov_momentum>("nesterov_momentum", 1);
+    ab_optimizer<momentum>("momentum", 1);
+    ab_optimizer<adagrad>("adagrad", 1);
     ab_operator_path();
     ab_lenet_fit();
     ab_cifar_fit(16, true);    // optimizer hand-off held to 1e-3 where decision flips are improbable

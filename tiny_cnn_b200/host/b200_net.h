@@ -6,7 +6,8 @@
 // is on the path -- convolutional / fully-connected / max-pooling layers with
 // engine backend_t::b200, average pooling, relu / tanh / softmax in between --
 // the loss is mse / cross_entropy / cross_entropy_multiclass and the optimizer
-// is adagrad / adam / momentum, the hook replaces the loop over mini-batches:
+// is one of the reference's seven (adagrad, adam, momentum, RMSprop, adamax,
+// gradient_descent, nesterov_momentum), the hook replaces the loop over mini-batches:
 //
 // (the public fit / train overloads call b200_fit_hook_rows even earlier, before they copy the
 // whole data set into tensors)
@@ -154,13 +155,14 @@ inline bool spec_of(layer *l, b200_layer_spec &s, std::vector<uint8_t> &tbl) {
 struct opt_choice {
   int kind = -1;
   b200_opt_hyper h{};
-  int n_state = 0;  // state buffers the optimizer keeps per weight tensor
-  adam *as_adam = nullptr;
+  int n_state = 0;  // state vectors the optimizer keeps per weight tensor
+  // adam / adamax: the object's running powers b1_t (and b2_t), advanced once per update call
+  float_t *pow1 = nullptr, *pow2 = nullptr;
   std::unordered_map<const vec_t *, vec_t> *maps = nullptr;
 };
 
-// adagrad / adam / momentum by RTTI (the reference identifies node types the same way,
-// nodes.h:134-146); eps is private in the reference and constant 1e-8 (optimizer.h:58,110)
+// The reference's optimizers by RTTI (it identifies node types the same way, nodes.h:134-146);
+// eps is a private member there and constant 1e-8 (optimizer.h:58,83,110,151)
 inline opt_choice choose_optimizer(optimizer *o) {
   opt_choice c;
   c.h.eps = 1e-8f;
@@ -177,8 +179,26 @@ inline opt_choice choose_optimizer(optimizer *o) {
     c.h.b1_t = a->b1_t;
     c.h.b2_t = a->b2_t;
     c.n_state = 2;
-    c.as_adam = a;
+    c.pow1 = &a->b1_t;
+    c.pow2 = &a->b2_t;
     c.maps = a->b200_maps();
+  } else if (auto *a = dynamic_cast<adamax *>(o)) {
+    c.kind = B200_OPT_ADAMAX;
+    c.h.alpha = a->alpha;
+    c.h.b1 = a->b1;
+    c.h.b2 = a->b2;
+    c.h.b1_t = a->b1_t;
+    c.h.b2_t = a->b2;  // adamax keeps no second power
+    c.n_state = 2;
+    c.pow1 = &a->b1_t;
+    c.maps = a->b200_maps();
+  } else if (auto *m = dynamic_cast<nesterov_momentum *>(o)) {
+    c.kind = B200_OPT_NESTEROV_MOMENTUM;
+    c.h.alpha = m->alpha;
+    c.h.mu = m->mu;
+    c.h.lambda = m->lambda;
+    c.n_state = 1;
+    c.maps = m->b200_maps();
   } else if (auto *m = dynamic_cast<momentum *>(o)) {
     c.kind = B200_OPT_MOMENTUM;
     c.h.alpha = m->alpha;
@@ -186,6 +206,16 @@ inline opt_choice choose_optimizer(optimizer *o) {
     c.h.lambda = m->lambda;
     c.n_state = 1;
     c.maps = m->b200_maps();
+  } else if (auto *r = dynamic_cast<RMSprop *>(o)) {
+    c.kind = B200_OPT_RMSPROP;
+    c.h.alpha = r->alpha;
+    c.h.mu = r->mu;
+    c.n_state = 1;
+    c.maps = r->b200_maps();
+  } else if (auto *g = dynamic_cast<gradient_descent *>(o)) {
+    c.kind = B200_OPT_GRADIENT_DESCENT;
+    c.h.alpha = g->alpha;
+    c.h.lambda = g->lambda;
   }
   return c;
 }
@@ -252,13 +282,13 @@ void state_to_host(Net &nn, device_twin &tw, opt_choice &oc, long long steps_don
         off += w->size();
       }
   }
-  if (oc.as_adam) {
-    // adam::update multiplies the powers once per call: tensors x steps sequential float products
-    // (optimizer.h:125-126); the device table did the same multiplications
+  if (oc.pow1) {
+    // adam::update / adamax::update multiply the powers once per call: tensors x steps sequential
+    // float products (optimizer.h:125-126,165); the device table did the same multiplications
     const long long calls = steps_done * static_cast<long long>(b200_net_tensor_count(tw.net));
     for (long long c = 0; c < calls; ++c) {
-      oc.as_adam->b1_t *= oc.as_adam->b1;
-      oc.as_adam->b2_t *= oc.as_adam->b2;
+      *oc.pow1 *= oc.h.b1;
+      if (oc.pow2) *oc.pow2 *= oc.h.b2;
     }
   }
 }
@@ -353,7 +383,7 @@ bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<I
   weights_to_device(nn, *tw);
   // fit() calls optimizer.reset() before its loop: the state maps are empty, adam's powers carry on
   check(b200_net_opt_reset(tw->net, 1));
-  if (oc.as_adam) check(b200_net_set_adam_powers(tw->net, oc.h.b1, oc.h.b2, oc.as_adam->b1_t, oc.as_adam->b2_t));
+  if (oc.pow1) check(b200_net_set_adam_powers(tw->net, oc.h.b1, oc.h.b2, *oc.pow1, oc.pow2 ? *oc.pow2 : oc.h.b2));
   const long long steps_per_epoch = static_cast<long long>((N + batch - 1) / batch);
   const size_t run = static_cast<size_t>(batch) * 16;  // mini-batches per library call in the first epoch
   for (int iter = 0; iter < epoch && !*stop; ++iter) {
@@ -486,7 +516,7 @@ bool train_u8(network<sequential> &nn, Optimizer &opt, const u8_dataset &data, s
   std::memcpy(lp, data.labels.data(), N);
   weights_to_device(nn, *tw);
   check(b200_net_opt_reset(tw->net, 1));
-  if (oc.as_adam) check(b200_net_set_adam_powers(tw->net, oc.h.b1, oc.h.b2, oc.as_adam->b1_t, oc.as_adam->b2_t));
+  if (oc.pow1) check(b200_net_set_adam_powers(tw->net, oc.h.b1, oc.h.b2, *oc.pow1, oc.pow2 ? *oc.pow2 : oc.h.b2));
   const long long steps_per_epoch = static_cast<long long>((N + batch - 1) / batch);
   for (int iter = 0; iter < epoch; ++iter) {
     check(b200_net_fit_u8_host(tw->net, &data.desc, ip, lp, static_cast<long long>(N), batch, 1, range.first,
