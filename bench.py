@@ -359,8 +359,17 @@ def run_b200(args, rank, world, local_rank):
             ms = float(tms[0])
         return ms
 
+    def restart():
+        """Every timed block starts from the initial weights with a fresh optimizer (outside the timed
+        region): thousands of adam steps on eight fixed mini-batches of random labels memorise them
+        until a softmax output rounds to exactly 1, where the reference's cross_entropy::df
+        (y - t) / (y (1 - y)) is 0/0 -- on the CPU as much as here -- and the weights turn to NaN."""
+        net.set_params(p0)
+        check(lib.b200_net_opt_reset(net.handle, 1))
+
     def timed_block(run_steps, steps):
         """barrier, event, `steps` steps, event, barrier; device time, max over ranks."""
+        restart()
         barrier()
         l0 = lib.b200_launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -501,10 +510,18 @@ def dp_parity(torch, dist, np, nw, ops, net, opt, dp_step, p0, rank, world, loca
     two steps of a single GPU (rank 0) on the concatenated mini-batch of world x BATCH samples:
     largest difference of any parameter tensor relative to its largest magnitude."""
     from tiny_cnn_b200._lib import check
-    p_mine = torch.from_numpy(net.get_params()).cuda()
-    gathered = [torch.empty_like(p_mine) for _ in range(world)]
-    dist.all_gather(gathered, p_mine)
-    identical = all(torch.equal(gathered[0], g) for g in gathered)
+    def replicas_differ():
+        """number of parameters that are not bit-equal on every rank, and the largest difference"""
+        mine = torch.from_numpy(net.get_params()).cuda()
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        n_bad, worst_d = 0, 0.0
+        for g in gathered[1:]:
+            n_bad = max(n_bad, int((gathered[0].view(torch.int32) != g.view(torch.int32)).sum()))  # bit patterns
+            worst_d = max(worst_d, float(torch.nan_to_num((gathered[0] - g).abs(), nan=float("inf")).max()))
+        return n_bad, worst_d, bool(torch.isfinite(mine).all())
+
+    bad_timed, diff_timed, finite_timed = replicas_differ()
     # (b) restart every replica from the initial weights with a fresh optimizer
     steps = 2
     net.set_params(p0)
@@ -518,10 +535,8 @@ def dp_parity(torch, dist, np, nw, ops, net, opt, dp_step, p0, rank, world, loca
         dp_step(x_buf, t_buf)
     ctx.sync()
     p_dp = net.get_params()
-    p_all = torch.from_numpy(p_dp).cuda()
-    gathered = [torch.empty_like(p_all) for _ in range(world)]
-    dist.all_gather(gathered, p_all)
-    identical = identical and all(torch.equal(gathered[0], g) for g in gathered)
+    bad_steps, diff_steps, finite_steps = replicas_differ()
+    identical = bad_timed == 0 and bad_steps == 0
     worst = None
     if rank == 0:
         big = nw.cifar10_net(local_rank).build(BATCH * world, ctx)
@@ -539,7 +554,11 @@ def dp_parity(torch, dist, np, nw, ops, net, opt, dp_step, p0, rank, world, loca
             worst = max(worst, float(np.abs(a - b).max() / max(float(np.abs(b).max()), 1e-30)))
         big.close()
     dist.barrier()
-    return {"replicas_identical": bool(identical), "vs_single_gpu": worst, "vs_single_gpu_tol": 1e-3,
+    return {"replicas_identical": bool(identical),
+            "replica_mismatches": {"after_timed_steps": [bad_timed, diff_timed], "after_parity_steps": [bad_steps, diff_steps],
+                                   "what": "[parameters whose bit patterns differ between ranks, largest |difference|]"},
+            "weights_finite": finite_timed and finite_steps,
+            "vs_single_gpu": worst, "vs_single_gpu_tol": 1e-3,
             "steps": steps,
             "how": f"{steps} data-parallel adam steps from the initial weights on {world} x {BATCH} samples against "
                    f"the same steps of one GPU on the concatenated {world * BATCH}-sample mini-batch: largest "

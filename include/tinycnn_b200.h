@@ -309,7 +309,15 @@ B200_API int b200_avgpool_bwd_host(b200_ctx *ctx, const b200_pool_desc *d, const
 /* Activations and loss gradients  (a8-a9)                                     */
 /* ------------------------------------------------------------------------- */
 
-enum { B200_ACT_NONE = 0, B200_ACT_RELU = 1, B200_ACT_TANH = 2, B200_ACT_SOFTMAX = 3 };
+enum {
+  B200_ACT_NONE = 0,
+  B200_ACT_RELU = 1,
+  B200_ACT_TANH = 2,
+  B200_ACT_SOFTMAX = 3,
+  B200_ACT_SIGMOID = 4,    /* tiny_dnn/activations/sigmoid_layer.h:24-39                        */
+  B200_ACT_LEAKY_RELU = 5, /* leaky_relu_layer.h:74-90; parameter = epsilon (0.01 by default)    */
+  B200_ACT_ELU = 6         /* elu_layer.h:38-57; parameter = alpha (1 by default)                */
+};
 
 /*
  * y = f(x) row by row (`dim` elements per row).  Replaces
@@ -328,6 +336,24 @@ B200_API int b200_act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int
  */
 B200_API int b200_act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx,
                           int dim, int batch);
+
+/*
+ * The same two calls for the activations that carry a constructor parameter:
+ * sigmoid y = 1/(1+exp(-x)), dx = dy*y*(1-y) (parameter unused); leaky relu
+ * y = x > 0 ? x : epsilon*x, dx = dy*(y > 0 ? 1 : epsilon)
+ * (leaky_relu_layer.h:74-90, `epsilon_`); elu y = x < 0 ? alpha*(exp(x)-1) : x,
+ * dx = dy*(y > 0 ? 1 : alpha + y) (elu_layer.h:38-57, `alpha_`).  The
+ * parameterless calls above run these kinds with the reference's default
+ * parameters (0.01, 1).
+ */
+B200_API int b200_act_param_fwd(b200_ctx *ctx, int kind, float param, const float *x, float *y,
+                                int dim, int batch);
+B200_API int b200_act_param_bwd(b200_ctx *ctx, int kind, float param, const float *y,
+                                const float *dy, float *dx, int dim, int batch);
+B200_API int b200_act_param_fwd_host(b200_ctx *ctx, int kind, float param, const float *x,
+                                     float *y, int dim, int batch);
+B200_API int b200_act_param_bwd_host(b200_ctx *ctx, int kind, float param, const float *y,
+                                     const float *dy, float *dx, int dim, int batch);
 
 B200_API int b200_act_fwd_host(b200_ctx *ctx, int kind, const float *x, float *y, int dim,
                                int batch);
@@ -450,7 +476,10 @@ enum {
   B200_LAYER_AVGPOOL = 4,
   B200_LAYER_RELU = 5,
   B200_LAYER_TANH = 6,
-  B200_LAYER_SOFTMAX = 7
+  B200_LAYER_SOFTMAX = 7,
+  B200_LAYER_SIGMOID = 8,
+  B200_LAYER_LEAKY_RELU = 9, /* act_param = epsilon */
+  B200_LAYER_ELU = 10        /* act_param = alpha   */
 };
 
 /* One layer of a network<sequential> (tiny_dnn/nodes.h:268-360). */
@@ -459,6 +488,7 @@ typedef struct b200_layer_spec {
   b200_conv_desc conv;   /* B200_LAYER_CONV                                   */
   b200_pool_desc pool;   /* B200_LAYER_MAXPOOL / B200_LAYER_AVGPOOL           */
   int32_t fc_in, fc_out, fc_has_bias; /* B200_LAYER_FC                        */
+  float act_param;       /* B200_LAYER_LEAKY_RELU / B200_LAYER_ELU            */
 } b200_layer_spec;
 
 typedef struct b200_net b200_net;

@@ -425,8 +425,13 @@ ORC_API void orc_avgpool_bwd(const b200_pool_desc *d, const float *prev_out, con
 /* activations and losses                                                      */
 /* ------------------------------------------------------------------------- */
 
-/* relu_layer.h:25-29, tanh_layer.h:24-28, softmax_layer.h:24-34 */
-ORC_API void orc_act_fwd(int kind, const float *x, float *y, int dim, int B) {
+static float act_default_param(int kind) {
+  return kind == B200_ACT_LEAKY_RELU ? 0.01f : kind == B200_ACT_ELU ? 1.f : 0.f;
+}
+
+/* relu_layer.h:25-29, tanh_layer.h:24-28, softmax_layer.h:24-34, sigmoid_layer.h:26-30,
+   leaky_relu_layer.h:74-78 (param = epsilon_), elu_layer.h:38-42 (param = alpha_) */
+ORC_API void orc_act_param_fwd(int kind, float param, const float *x, float *y, int dim, int B) {
   for (int n = 0; n < B; ++n) {
     const float *xr = x + (size_t)n * dim;
     float *yr = y + (size_t)n * dim;
@@ -434,6 +439,12 @@ ORC_API void orc_act_fwd(int kind, const float *x, float *y, int dim, int B) {
       for (int j = 0; j < dim; ++j) yr[j] = xr[j] > 0.f ? xr[j] : 0.f;
     } else if (kind == B200_ACT_TANH) {
       for (int j = 0; j < dim; ++j) yr[j] = tanhf(xr[j]);
+    } else if (kind == B200_ACT_SIGMOID) {
+      for (int j = 0; j < dim; ++j) yr[j] = 1.f / (1.f + expf(-xr[j]));
+    } else if (kind == B200_ACT_LEAKY_RELU) {
+      for (int j = 0; j < dim; ++j) yr[j] = xr[j] > 0.f ? xr[j] : param * xr[j];
+    } else if (kind == B200_ACT_ELU) {
+      for (int j = 0; j < dim; ++j) yr[j] = xr[j] < 0.f ? param * (expf(xr[j]) - 1.f) : xr[j];
     } else if (kind == B200_ACT_SOFTMAX) {
       float alpha = xr[0];
       for (int j = 1; j < dim; ++j) alpha = xr[j] > alpha ? xr[j] : alpha;
@@ -449,8 +460,10 @@ ORC_API void orc_act_fwd(int kind, const float *x, float *y, int dim, int B) {
   }
 }
 
-/* relu_layer.h:31-39, tanh_layer.h:30-38, softmax_layer.h:36-55 */
-ORC_API void orc_act_bwd(int kind, const float *y, const float *dy, float *dx, int dim, int B) {
+/* relu_layer.h:31-39, tanh_layer.h:30-38, softmax_layer.h:36-55, sigmoid_layer.h:32-39,
+   leaky_relu_layer.h:80-88, elu_layer.h:44-54 */
+ORC_API void orc_act_param_bwd(int kind, float param, const float *y, const float *dy, float *dx, int dim,
+                               int B) {
   for (int n = 0; n < B; ++n) {
     const float *yr = y + (size_t)n * dim, *gr = dy + (size_t)n * dim;
     float *dr = dx + (size_t)n * dim;
@@ -458,6 +471,12 @@ ORC_API void orc_act_bwd(int kind, const float *y, const float *dy, float *dx, i
       for (int j = 0; j < dim; ++j) dr[j] = gr[j] * (yr[j] > 0.f ? 1.f : 0.f);
     } else if (kind == B200_ACT_TANH) {
       for (int j = 0; j < dim; ++j) dr[j] = gr[j] * (1.f - yr[j] * yr[j]);
+    } else if (kind == B200_ACT_SIGMOID) {
+      for (int j = 0; j < dim; ++j) dr[j] = gr[j] * yr[j] * (1.f - yr[j]);
+    } else if (kind == B200_ACT_LEAKY_RELU) {
+      for (int j = 0; j < dim; ++j) dr[j] = gr[j] * (yr[j] > 0.f ? 1.f : param);
+    } else if (kind == B200_ACT_ELU) {
+      for (int j = 0; j < dim; ++j) dr[j] = gr[j] * (yr[j] > 0.f ? 1.f : (param + yr[j]));
     } else if (kind == B200_ACT_SOFTMAX) {
       float *df = (float *)malloc(sizeof(float) * dim);
       for (int j = 0; j < dim; ++j) {
@@ -470,6 +489,14 @@ ORC_API void orc_act_bwd(int kind, const float *y, const float *dy, float *dx, i
       memcpy(dr, gr, sizeof(float) * dim);
     }
   }
+}
+
+/* the reference's default constructor arguments */
+ORC_API void orc_act_fwd(int kind, const float *x, float *y, int dim, int B) {
+  orc_act_param_fwd(kind, act_default_param(kind), x, y, dim, B);
+}
+ORC_API void orc_act_bwd(int kind, const float *y, const float *dy, float *dx, int dim, int B) {
+  orc_act_param_bwd(kind, act_default_param(kind), y, dy, dx, dim, B);
 }
 
 /* mse::df, cross_entropy::df, cross_entropy_multiclass::df
@@ -955,9 +982,12 @@ ORC_API float *orc_net_layer_out(orc_net *net, int i) { return net->L[i].out; }
 ORC_API float *orc_net_layer_grad(orc_net *net, int i) { return i < 0 ? net->in_grad : net->L[i].grad; }
 
 static int act_kind(int layer_kind) {
-  return layer_kind == B200_LAYER_RELU ? B200_ACT_RELU
-       : layer_kind == B200_LAYER_TANH ? B200_ACT_TANH
-                                       : B200_ACT_SOFTMAX;
+  return layer_kind == B200_LAYER_RELU         ? B200_ACT_RELU
+         : layer_kind == B200_LAYER_TANH       ? B200_ACT_TANH
+         : layer_kind == B200_LAYER_SIGMOID    ? B200_ACT_SIGMOID
+         : layer_kind == B200_LAYER_LEAKY_RELU ? B200_ACT_LEAKY_RELU
+         : layer_kind == B200_LAYER_ELU        ? B200_ACT_ELU
+                                               : B200_ACT_SOFTMAX;
 }
 
 /* sequential::forward (tiny_dnn/nodes.h:288-303) */
@@ -975,7 +1005,7 @@ ORC_API void orc_net_forward(orc_net *net, const float *x, int B) {
       case B200_LAYER_FC: orc_fc_fwd(L->s.fc_in, L->s.fc_out, in, W, b, L->out, B); break;
       case B200_LAYER_MAXPOOL: orc_maxpool_fwd(&L->s.pool, in, L->out, L->argmax, B); break;
       case B200_LAYER_AVGPOOL: orc_avgpool_fwd(&L->s.pool, in, W, b, L->out, B); break;
-      default: orc_act_fwd(act_kind(L->s.kind), in, L->out, (int)L->out_dim, B); break;
+      default: orc_act_param_fwd(act_kind(L->s.kind), L->s.act_param, in, L->out, (int)L->out_dim, B); break;
     }
     in = L->out;
   }
@@ -1008,7 +1038,7 @@ ORC_API void orc_net_backward(orc_net *net, const float *x, const float *t, int 
       case B200_LAYER_AVGPOOL:
         orc_avgpool_bwd(&L->s.pool, in, W, L->grad, din, dW, db, 0, B);
         break;
-      default: orc_act_bwd(act_kind(L->s.kind), L->out, L->grad, din, (int)L->out_dim, B); break;
+      default: orc_act_param_bwd(act_kind(L->s.kind), L->s.act_param, L->out, L->grad, din, (int)L->out_dim, B); break;
     }
   }
 }

@@ -237,16 +237,19 @@ REF_API int ref_avgpool_fwd_bwd(const b200_pool_desc *d, const float *in, const 
 
 // ---------------------------------------------------------------- activations / loss
 namespace {
-std::unique_ptr<activation_layer> make_act(int kind, size_t dim) {
+std::unique_ptr<activation_layer> make_act(int kind, size_t dim, float param) {
   if (kind == B200_ACT_RELU) return std::unique_ptr<activation_layer>(new relu_layer(dim));
   if (kind == B200_ACT_TANH) return std::unique_ptr<activation_layer>(new tanh_layer(dim));
+  if (kind == B200_ACT_SIGMOID) return std::unique_ptr<activation_layer>(new sigmoid_layer(dim));
+  if (kind == B200_ACT_LEAKY_RELU) return std::unique_ptr<activation_layer>(new leaky_relu_layer(dim, param));
+  if (kind == B200_ACT_ELU) return std::unique_ptr<activation_layer>(new elu_layer(dim, param));
   return std::unique_ptr<activation_layer>(new softmax_layer(dim));
 }
 }  // namespace
 
-REF_API int ref_act_fwd_bwd(int kind, const float *x, float *y, const float *dy, float *dx,
-                            int dim, int B) {
-  auto l = make_act(kind, dim);
+REF_API int ref_act_param_fwd_bwd(int kind, float param, const float *x, float *y, const float *dy, float *dx,
+                                  int dim, int B) {
+  auto l = make_act(kind, dim, param);
   tensor_t tx = to_tensor(x, B, dim), ty(B, vec_t(dim));
   std::vector<tensor_t *> ins = {&tx}, outs = {&ty};
   l->forward_propagation(ins, outs);
@@ -258,6 +261,11 @@ REF_API int ref_act_fwd_bwd(int kind, const float *x, float *y, const float *dy,
     from_tensor(gx, dx, dim);
   }
   return 0;
+}
+
+// the layers' default constructor arguments
+REF_API int ref_act_fwd_bwd(int kind, const float *x, float *y, const float *dy, float *dx, int dim, int B) {
+  return ref_act_param_fwd_bwd(kind, kind == B200_ACT_LEAKY_RELU ? 0.01f : 1.f, x, y, dy, dx, dim, B);
 }
 
 REF_API int ref_loss_grad(int kind, const float *y, const float *t, float *dy, int dim, int B) {
@@ -387,8 +395,60 @@ struct RefNet {
   adagrad o_adagrad;
   adam o_adam;
   momentum o_momentum;
+  RMSprop o_rmsprop;
+  adamax o_adamax;
+  gradient_descent o_sgd;
+  nesterov_momentum o_nesterov;
   size_t in_dim = 0, out_dim = 0, n_params = 0;
+
+  // the net's persistent optimizer object of a kind, with the caller's hyper-parameters
+  optimizer *opt(int kind, const b200_opt_hyper *hy) {
+    switch (kind) {
+      case B200_OPT_ADAGRAD: o_adagrad.alpha = hy->alpha; return &o_adagrad;
+      case B200_OPT_ADAM:
+        o_adam.alpha = hy->alpha;
+        o_adam.b1 = hy->b1;
+        o_adam.b2 = hy->b2;
+        return &o_adam;
+      case B200_OPT_MOMENTUM:
+        o_momentum.alpha = hy->alpha;
+        o_momentum.mu = hy->mu;
+        o_momentum.lambda = hy->lambda;
+        return &o_momentum;
+      case B200_OPT_RMSPROP:
+        o_rmsprop.alpha = hy->alpha;
+        o_rmsprop.mu = hy->mu;
+        return &o_rmsprop;
+      case B200_OPT_ADAMAX:
+        o_adamax.alpha = hy->alpha;
+        o_adamax.b1 = hy->b1;
+        o_adamax.b2 = hy->b2;
+        return &o_adamax;
+      case B200_OPT_GRADIENT_DESCENT:
+        o_sgd.alpha = hy->alpha;
+        o_sgd.lambda = hy->lambda;
+        return &o_sgd;
+      case B200_OPT_NESTEROV_MOMENTUM:
+        o_nesterov.alpha = hy->alpha;
+        o_nesterov.mu = hy->mu;
+        o_nesterov.lambda = hy->lambda;
+        return &o_nesterov;
+    }
+    return nullptr;
+  }
 };
+
+template <typename Opt>
+void fit_loss(RefNet *r, Opt &o, int loss_kind, const std::vector<vec_t> &in, const std::vector<vec_t> &tgt, int batch,
+              int epochs) {
+  auto nop = []() {};
+  if (loss_kind == B200_LOSS_MSE)
+    r->net.fit<mse>(o, in, tgt, batch, epochs, nop, nop);
+  else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
+    r->net.fit<cross_entropy>(o, in, tgt, batch, epochs, nop, nop);
+  else
+    r->net.fit<cross_entropy_multiclass>(o, in, tgt, batch, epochs, nop, nop);
+}
 
 void add_layer(RefNet *r, const b200_layer_spec &s, size_t prev_dim) {
   switch (s.kind) {
@@ -417,6 +477,9 @@ void add_layer(RefNet *r, const b200_layer_spec &s, size_t prev_dim) {
     case B200_LAYER_RELU: r->net << relu_layer(prev_dim); break;
     case B200_LAYER_TANH: r->net << tanh_layer(prev_dim); break;
     case B200_LAYER_SOFTMAX: r->net << softmax_layer(prev_dim); break;
+    case B200_LAYER_SIGMOID: r->net << sigmoid_layer(prev_dim); break;
+    case B200_LAYER_LEAKY_RELU: r->net << leaky_relu_layer(prev_dim, s.act_param); break;
+    case B200_LAYER_ELU: r->net << elu_layer(prev_dim, s.act_param); break;
     default: throw nn_error("unknown layer kind");
   }
 }
@@ -518,39 +581,19 @@ REF_API double ref_net_fit_n(void *h, const float *x, const float *t, long long 
     in[n].assign(x + n * r->in_dim, x + (n + 1) * r->in_dim);
     tgt[n].assign(t + n * r->out_dim, t + (n + 1) * r->out_dim);
   }
-  r->o_adagrad.alpha = hy->alpha;
-  r->o_adam.alpha = hy->alpha;
-  r->o_adam.b1 = hy->b1;
-  r->o_adam.b2 = hy->b2;
-  r->o_momentum.alpha = hy->alpha;
-  r->o_momentum.mu = hy->mu;
-  r->o_momentum.lambda = hy->lambda;
+  if (!r->opt(opt_kind, hy)) return -1.0;
   auto t0 = std::chrono::steady_clock::now();
   try {
-    auto nop = []() {};
     // fit() calls optimizer.reset() (network.h:856), which clears the state
     // maps but not Adam's powers (optimizer.h:36-38)
-    if (opt_kind == B200_OPT_ADAGRAD) {
-      if (loss_kind == B200_LOSS_MSE)
-        r->net.fit<mse>(r->o_adagrad, in, tgt, batch, epochs, nop, nop);
-      else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
-        r->net.fit<cross_entropy>(r->o_adagrad, in, tgt, batch, epochs, nop, nop);
-      else
-        r->net.fit<cross_entropy_multiclass>(r->o_adagrad, in, tgt, batch, epochs, nop, nop);
-    } else if (opt_kind == B200_OPT_ADAM) {
-      if (loss_kind == B200_LOSS_MSE)
-        r->net.fit<mse>(r->o_adam, in, tgt, batch, epochs, nop, nop);
-      else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
-        r->net.fit<cross_entropy>(r->o_adam, in, tgt, batch, epochs, nop, nop);
-      else
-        r->net.fit<cross_entropy_multiclass>(r->o_adam, in, tgt, batch, epochs, nop, nop);
-    } else {
-      if (loss_kind == B200_LOSS_MSE)
-        r->net.fit<mse>(r->o_momentum, in, tgt, batch, epochs, nop, nop);
-      else if (loss_kind == B200_LOSS_CROSS_ENTROPY)
-        r->net.fit<cross_entropy>(r->o_momentum, in, tgt, batch, epochs, nop, nop);
-      else
-        r->net.fit<cross_entropy_multiclass>(r->o_momentum, in, tgt, batch, epochs, nop, nop);
+    switch (opt_kind) {
+      case B200_OPT_ADAGRAD: fit_loss(r, r->o_adagrad, loss_kind, in, tgt, batch, epochs); break;
+      case B200_OPT_ADAM: fit_loss(r, r->o_adam, loss_kind, in, tgt, batch, epochs); break;
+      case B200_OPT_MOMENTUM: fit_loss(r, r->o_momentum, loss_kind, in, tgt, batch, epochs); break;
+      case B200_OPT_RMSPROP: fit_loss(r, r->o_rmsprop, loss_kind, in, tgt, batch, epochs); break;
+      case B200_OPT_ADAMAX: fit_loss(r, r->o_adamax, loss_kind, in, tgt, batch, epochs); break;
+      case B200_OPT_GRADIENT_DESCENT: fit_loss(r, r->o_sgd, loss_kind, in, tgt, batch, epochs); break;
+      default: fit_loss(r, r->o_nesterov, loss_kind, in, tgt, batch, epochs); break;
     }
   } catch (const std::exception &e) {
     fprintf(stderr, "ref_net_fit: %s\n", e.what());
@@ -629,16 +672,8 @@ REF_API int ref_net_grads_chunked(void *h, const float *x, const float *t, int n
 // The optimizer objects are the net's persistent ones (state carries on).
 REF_API int ref_net_apply_update(void *h, const float *grads, int opt_kind, const b200_opt_hyper *hy) {
   RefNet *r = static_cast<RefNet *>(h);
-  r->o_adagrad.alpha = hy->alpha;
-  r->o_adam.alpha = hy->alpha;
-  r->o_adam.b1 = hy->b1;
-  r->o_adam.b2 = hy->b2;
-  r->o_momentum.alpha = hy->alpha;
-  r->o_momentum.mu = hy->mu;
-  r->o_momentum.lambda = hy->lambda;
-  optimizer *o = opt_kind == B200_OPT_ADAGRAD ? static_cast<optimizer *>(&r->o_adagrad)
-                 : opt_kind == B200_OPT_ADAM  ? static_cast<optimizer *>(&r->o_adam)
-                                              : static_cast<optimizer *>(&r->o_momentum);
+  optimizer *o = r->opt(opt_kind, hy);
+  if (!o) return 1;
   for (size_t i = 0; i < r->net.depth(); ++i)
     for (auto *w : r->net[i]->weights()) {
       vec_t g(grads, grads + w->size());

@@ -7,8 +7,8 @@ import ctypes as C
 
 import numpy as np
 
-from tiny_cnn_b200._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_RELU,
-                                LAYER_SOFTMAX, LAYER_TANH, LayerSpec, OptHyper)
+from tiny_cnn_b200._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_ELU, LAYER_FC, LAYER_LEAKY_RELU, LAYER_MAXPOOL,
+                                LAYER_RELU, LAYER_SIGMOID, LAYER_SOFTMAX, LAYER_TANH, LayerSpec, OptHyper)
 from tiny_cnn_b200._lib import ConvDesc, PoolDesc
 from tiny_cnn_b200.network import LENET_TABLE
 
@@ -152,6 +152,12 @@ ACT_CASES = {
     "tanh": dict(kind=2, B=4, dim=37, seed=52, scale=2.0),
     "softmax": dict(kind=3, B=6, dim=10, seed=53, scale=3.0),
     "softmax_wide": dict(kind=3, B=3, dim=33, seed=54, scale=5.0),
+    # sigmoid / leaky relu / elu with the reference's default parameter and with another one
+    "sigmoid": dict(kind=4, B=4, dim=37, seed=55, scale=3.0),
+    "leaky_relu": dict(kind=5, B=4, dim=37, seed=56),
+    "leaky_relu_0.2": dict(kind=5, B=3, dim=41, seed=57, param=0.2),
+    "elu": dict(kind=6, B=4, dim=37, seed=58, scale=2.0),
+    "elu_0.7": dict(kind=6, B=3, dim=41, seed=59, scale=2.0, param=0.7),
 }
 
 # quantized forward: x ~ U[-1, 1], W ~ U[-0.5, 0.5] as the benchmark configuration states
@@ -224,9 +230,10 @@ def _pool(kind, w, h, c, p):
     return s, None
 
 
-def _act(kind):
+def _act(kind, param=0.0):
     s = LayerSpec()
     s.kind = kind
+    s.act_param = param
     return s, None
 
 
@@ -251,6 +258,10 @@ def build_net_specs(name):
     elif name == "tiny_conv":
         L = [_conv(12, 12, 3, 2, 4, True), _act(LAYER_RELU), _pool(LAYER_MAXPOOL, 12, 12, 4, 2),
              _conv(6, 6, 3, 4, 5), _act(LAYER_TANH), _fc(80, 6), _act(LAYER_SOFTMAX)]
+    elif name == "tiny_conv_acts":
+        # the activations with a constructor parameter between the hot operators
+        L = [_conv(12, 12, 3, 2, 4, True), _act(LAYER_LEAKY_RELU, 0.1), _pool(LAYER_MAXPOOL, 12, 12, 4, 2),
+             _conv(6, 6, 3, 4, 5), _act(LAYER_ELU, 0.8), _fc(80, 6), _act(LAYER_SIGMOID)]
     else:
         raise KeyError(name)
     return [s for s, _ in L], [k for _, k in L]
@@ -268,6 +279,9 @@ NET_CASES = {
                          t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.uniform(0, 1, s)),
     "tiny_conv_adam": dict(net="tiny_conv", B=5, steps=4, seed=104, in_dim=288, out_dim=6, loss=2, opt=1,
                            t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.standard_normal(s)),
+    # leaky relu / elu / sigmoid, mse, RMSprop
+    "tiny_conv_acts_rmsprop": dict(net="tiny_conv_acts", B=6, steps=4, seed=105, in_dim=288, out_dim=6, loss=0, opt=3,
+                                   t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.standard_normal(s)),
 }
 
 

@@ -397,11 +397,11 @@ static void ab_lenet_fit() {
   compare_state(a, c, oa, oc, 1, "LeNet-5");
 }
 
-// a layer that is not on the path (sigmoid) keeps the reference's loop: its b200 layers then run
+// a layer that is not on the path (softsign) keeps the reference's loop: its b200 layers then run
 // operator by operator; momentum
 static void ab_operator_path() {
   auto build = [](network<sequential> &nn, core::backend_t e) {
-    nn << convolutional_layer(12, 12, 3, 2, 4, padding::same, true, 1, 1, 1, 1, e) << sigmoid_layer()
+    nn << convolutional_layer(12, 12, 3, 2, 4, padding::same, true, 1, 1, 1, 1, e) << softsign_layer()
        << max_pooling_layer(12, 12, 4, 2, false, e) << fully_connected_layer(6 * 6 * 4, 5, true, e) << softmax_layer(5);
   };
   network<sequential> a, c;
@@ -420,10 +420,37 @@ static void ab_operator_path() {
   a.fit<cross_entropy_multiclass>(oa, x, t, B, 1);
   c.fit<cross_entropy_multiclass>(oc, x, t, B, 1);
   expect(b200::device_fit_count() == fits, "a network with a layer off the path keeps the reference's loop");
-  compare_nets(a, c, 1e-3, "operator-by-operator fit (sigmoid in the net), 3 momentum steps");
+  compare_nets(a, c, 1e-3, "operator-by-operator fit (softsign in the net), 3 momentum steps");
   // under engine b200 the weight-gradient tensors are not grown to one row per sample
   expect(c[0]->weights_grads()[0]->size() == 1 && a[0]->weights_grads()[0]->size() == B,
          "weight-gradient tensors stay at one row under engine b200 (B rows under internal)");
+}
+
+// leaky relu / elu / sigmoid (constructor parameters other than the defaults) between the hot
+// operators: the whole fit runs as the device-resident step; RMSprop, mse
+static void ab_parameter_activations_fit() {
+  auto build = [](network<sequential> &nn, core::backend_t e) {
+    nn << convolutional_layer(12, 12, 3, 2, 4, padding::same, true, 1, 1, 1, 1, e) << leaky_relu_layer(float_t(0.1))
+       << max_pooling_layer(12, 12, 4, 2, false, e) << convolutional_layer(6, 6, 3, 4, 5, padding::valid, true, 1, 1, 1, 1, e)
+       << elu_layer(float_t(0.8)) << fully_connected_layer(80, 6, true, e) << sigmoid_layer();
+  };
+  network<sequential> a, c;
+  build(a, core::backend_t::internal);
+  build(c, core::backend_t::b200);
+  same_weights(a, c, 31);
+  std::mt19937 g(32);
+  const size_t B = 6, steps = 4;
+  std::vector<vec_t> x(B * steps, vec_t(12 * 12 * 2)), t(B * steps, vec_t(6, 0.f));
+  std::normal_distribution<float> nd(0.f, 1.f);
+  for (auto &v : x)
+    for (auto &e : v) e = nd(g);
+  for (auto &v : t) v[g() % 6] = 1.f;
+  RMSprop oa, oc;
+  const unsigned long long fits = b200::device_fit_count();
+  a.fit<mse>(oa, x, t, B, 1);
+  c.fit<mse>(oc, x, t, B, 1);
+  expect(b200::device_fit_count() == fits + 1, "leaky relu / elu / sigmoid net trains as the device-resident step");
+  compare_nets(a, c, 1e-3, "leaky relu(0.1) / elu(0.8) / sigmoid net, 4 RMSprop steps");
 }
 
 // examples/cifar10/train.cpp's data path: parse_cifar10 -> train<cross_entropy> on the CPU against
@@ -529,6 +556,18 @@ int main() {
       ab_layer("softmax (set_backend_type)", l, 6, false, 9);
     }
     {
+      sigmoid_layer l(37);
+      ab_layer("sigmoid (set_backend_type)", l, 4, false, 11);
+    }
+    {
+      leaky_relu_layer l(37, float_t(0.2));
+      ab_layer("leaky relu 0.2 (set_backend_type)", l, 4, false, 12);
+    }
+    {
+      elu_layer l(37, float_t(0.7));
+      ab_layer("elu 0.7 (set_backend_type)", l, 4, false, 13);
+    }
+    {
       average_pooling_layer l(28, 28, 6, 2);
       ab_layer("average pooling 2x2 (set_backend_type)", l, 4, true, 10);
     }
@@ -540,6 +579,7 @@ int main() {
     ab_optimizer<momentum>("momentum", 1);
     ab_optimizer<adagrad>("adagrad", 1);
     ab_operator_path();
+    ab_parameter_activations_fit();
     ab_lenet_fit();
     ab_cifar_fit(16, true);    // optimizer hand-off held to 1e-3 where decision flips are improbable
     ab_cifar_fit(256, false);  // the benchmarked batch

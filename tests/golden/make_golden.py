@@ -107,7 +107,10 @@ def main():
         x = (rng.standard_normal((B, dim)) * c.get("scale", 1.0)).astype(np.float32)
         dy = rng.standard_normal((B, dim)).astype(np.float32)
         y, dx = o.f32(B, dim), o.f32(B, dim)
-        assert ref.ref_act_fwd_bwd(c["kind"], o.p(x), o.p(y), o.p(dy), o.p(dx), dim, B) == 0
+        if "param" in c:
+            assert ref.ref_act_param_fwd_bwd(c["kind"], c["param"], o.p(x), o.p(y), o.p(dy), o.p(dx), dim, B) == 0
+        else:  # the layer's default constructor argument
+            assert ref.ref_act_fwd_bwd(c["kind"], o.p(x), o.p(y), o.p(dy), o.p(dx), dim, B) == 0
         out[f"act/{name}/y"], out[f"act/{name}/dx"] = y, dx
         for loss in (0, 1, 2):
             yy = rng.uniform(0.05, 0.95, (B, dim)).astype(np.float32)

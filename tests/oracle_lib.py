@@ -29,6 +29,8 @@ ORACLE_SIGS = {
     "orc_maxpool_bwd": (None, [_pd, _vp, _vp, _vp, _i]),
     "orc_avgpool_fwd": (None, [_pd, _vp, _vp, _vp, _vp, _i]),
     "orc_avgpool_bwd": (None, [_pd, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "orc_act_param_fwd": (None, [_i, C.c_float, _vp, _vp, _i, _i]),
+    "orc_act_param_bwd": (None, [_i, C.c_float, _vp, _vp, _vp, _i, _i]),
     "orc_act_fwd": (None, [_i, _vp, _vp, _i, _i]),
     "orc_act_bwd": (None, [_i, _vp, _vp, _vp, _i, _i]),
     "orc_loss_grad": (None, [_i, _vp, _vp, _vp, _i, _i]),
@@ -74,6 +76,7 @@ REF_SIGS = {
     "ref_maxpool_fwd_bwd": (_i, [_pd, _i, _i, _vp, _vp, _vp, _vp, _i]),
     "ref_avgpool_fwd_bwd": (_i, [_pd, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "ref_act_fwd_bwd": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i]),
+    "ref_act_param_fwd_bwd": (_i, [_i, C.c_float, _vp, _vp, _vp, _vp, _i, _i]),
     "ref_loss_grad": (_i, [_i, _vp, _vp, _vp, _i, _i]),
     "ref_opt_steps": (_i, [_i, _oh, _vp, _vp, _sz, _i]),
     "ref_f2q_unclamped": (C.c_int64, [_i, _f, _f, _f]),

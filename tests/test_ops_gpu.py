@@ -310,9 +310,9 @@ def test_activation_and_loss(ctx, gold, name):
     B, dim = c["B"], c["dim"]
     x = (rng.standard_normal((B, dim)) * c.get("scale", 1.0)).astype(np.float32)
     dy = rng.standard_normal((B, dim)).astype(np.float32)
-    y = ops.forward_activation(ctx, c["kind"], dev(x))
+    y = ops.forward_activation(ctx, c["kind"], dev(x), c.get("param"))
     assert_close(host(y), gold[f"act/{name}/y"], FWD_TOL, f"{name} fwd")
-    dx = ops.backward_activation(ctx, c["kind"], dev(gold[f"act/{name}/y"]), dev(dy))
+    dx = ops.backward_activation(ctx, c["kind"], dev(gold[f"act/{name}/y"]), dev(dy), c.get("param"))
     assert_close(host(dx), gold[f"act/{name}/dx"], GRAD_TOL, f"{name} bwd")
     for loss in (0, 1, 2):
         yy, tt = gold[f"loss/{name}/{loss}/y"], gold[f"loss/{name}/{loss}/t"]

@@ -260,8 +260,12 @@ def test_gold_act_and_loss(oracle, gold, name):
     x = (rng.standard_normal((B, dim)) * c.get("scale", 1.0)).astype(np.float32)
     dy = rng.standard_normal((B, dim)).astype(np.float32)
     y, dx = o.f32(B, dim), o.f32(B, dim)
-    oracle.orc_act_fwd(c["kind"], o.p(x), o.p(y), dim, B)
-    oracle.orc_act_bwd(c["kind"], o.p(y), o.p(dy), o.p(dx), dim, B)
+    if "param" in c:
+        oracle.orc_act_param_fwd(c["kind"], c["param"], o.p(x), o.p(y), dim, B)
+        oracle.orc_act_param_bwd(c["kind"], c["param"], o.p(y), o.p(dy), o.p(dx), dim, B)
+    else:
+        oracle.orc_act_fwd(c["kind"], o.p(x), o.p(y), dim, B)
+        oracle.orc_act_bwd(c["kind"], o.p(y), o.p(dy), o.p(dx), dim, B)
     assert np.array_equal(y, gold[f"act/{name}/y"])
     assert np.array_equal(dx, gold[f"act/{name}/dx"])
     for loss in (0, 1, 2):

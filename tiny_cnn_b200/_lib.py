@@ -71,14 +71,16 @@ class LayerSpec(C.Structure):
         ("conv", ConvDesc),
         ("pool", PoolDesc),
         ("fc_in", C.c_int32), ("fc_out", C.c_int32), ("fc_has_bias", C.c_int32),
+        ("act_param", C.c_float),
     ]
 
 
 # enums of the header
-ACT_NONE, ACT_RELU, ACT_TANH, ACT_SOFTMAX = 0, 1, 2, 3
+ACT_NONE, ACT_RELU, ACT_TANH, ACT_SOFTMAX, ACT_SIGMOID, ACT_LEAKY_RELU, ACT_ELU = range(7)
 LOSS_MSE, LOSS_CROSS_ENTROPY, LOSS_CROSS_ENTROPY_MULTICLASS = 0, 1, 2
 OPT_ADAGRAD, OPT_ADAM, OPT_MOMENTUM, OPT_RMSPROP, OPT_ADAMAX, OPT_GRADIENT_DESCENT, OPT_NESTEROV_MOMENTUM = range(7)
-LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_AVGPOOL, LAYER_RELU, LAYER_TANH, LAYER_SOFTMAX = range(1, 8)
+(LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_AVGPOOL, LAYER_RELU, LAYER_TANH, LAYER_SOFTMAX, LAYER_SIGMOID,
+ LAYER_LEAKY_RELU, LAYER_ELU) = range(1, 11)
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 _cd, _pd, _oh = C.POINTER(ConvDesc), C.POINTER(PoolDesc), C.POINTER(OptHyper)
@@ -124,6 +126,10 @@ SIGNATURES = {
     "b200_avgpool_bwd_host": (_i, [_vp, _pd, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "b200_act_fwd": (_i, [_vp, _i, _vp, _vp, _i, _i]),
     "b200_act_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i]),
+    "b200_act_param_fwd": (_i, [_vp, _i, C.c_float, _vp, _vp, _i, _i]),
+    "b200_act_param_bwd": (_i, [_vp, _i, C.c_float, _vp, _vp, _vp, _i, _i]),
+    "b200_act_param_fwd_host": (_i, [_vp, _i, C.c_float, _vp, _vp, _i, _i]),
+    "b200_act_param_bwd_host": (_i, [_vp, _i, C.c_float, _vp, _vp, _vp, _i, _i]),
     "b200_act_fwd_host": (_i, [_vp, _i, _vp, _vp, _i, _i]),
     "b200_act_bwd_host": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i]),
     "b200_loss_grad": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i]),

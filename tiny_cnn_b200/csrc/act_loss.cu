@@ -8,7 +8,7 @@
 namespace b200 {
 
 // relu_layer.h:25-29, tanh_layer.h:24-28 -- elementwise, float4 where aligned
-__global__ void act_fwd_kernel(int kind, const float *__restrict__ x, float *__restrict__ y,
+__global__ void act_fwd_kernel(int kind, float param, const float *__restrict__ x, float *__restrict__ y,
                                size_t n4, size_t n) {
   size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   size_t step = (size_t)gridDim.x * blockDim.x;
@@ -16,23 +16,28 @@ __global__ void act_fwd_kernel(int kind, const float *__restrict__ x, float *__r
   float4 *y4 = reinterpret_cast<float4 *>(y);
   for (size_t j = i; j < n4; j += step) {
     float4 v = x4[j];
-    v.x = apply_act(v.x, kind);
-    v.y = apply_act(v.y, kind);
-    v.z = apply_act(v.z, kind);
-    v.w = apply_act(v.w, kind);
+    v.x = apply_act_p(v.x, kind, param);
+    v.y = apply_act_p(v.y, kind, param);
+    v.z = apply_act_p(v.z, kind, param);
+    v.w = apply_act_p(v.w, kind, param);
     y4[j] = v;
   }
-  for (size_t j = n4 * 4 + i; j < n; j += step) y[j] = apply_act(x[j], kind);
+  for (size_t j = n4 * 4 + i; j < n; j += step) y[j] = apply_act_p(x[j], kind, param);
 }
 
 // relu_layer.h:31-39 dx = dy*(y>0); tanh_layer.h:30-38 dx = dy*(1-y*y)
-__device__ __forceinline__ float act_grad(int kind, float y, float dy) {
+// sigmoid_layer.h:32-39 dx = dy*y*(1-y); leaky_relu_layer.h:80-88 dx = dy*(y>0 ? 1 : epsilon);
+// elu_layer.h:44-54 dx = dy*(y>0 ? 1 : alpha+y)
+__device__ __forceinline__ float act_grad(int kind, float param, float y, float dy) {
   if (kind == B200_ACT_RELU) return dy * (y > 0.f ? 1.f : 0.f);
   if (kind == B200_ACT_TANH) return __fmul_rn(dy, __fsub_rn(1.f, __fmul_rn(y, y)));
+  if (kind == B200_ACT_SIGMOID) return __fmul_rn(__fmul_rn(dy, y), __fsub_rn(1.f, y));
+  if (kind == B200_ACT_LEAKY_RELU) return __fmul_rn(dy, y > 0.f ? 1.f : param);
+  if (kind == B200_ACT_ELU) return __fmul_rn(dy, y > 0.f ? 1.f : __fadd_rn(param, y));
   return dy;
 }
 
-__global__ void act_bwd_kernel(int kind, const float *__restrict__ y, const float *__restrict__ dy,
+__global__ void act_bwd_kernel(int kind, float param, const float *__restrict__ y, const float *__restrict__ dy,
                                float *__restrict__ dx, size_t n4, size_t n) {
   size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   size_t step = (size_t)gridDim.x * blockDim.x;
@@ -41,13 +46,13 @@ __global__ void act_bwd_kernel(int kind, const float *__restrict__ y, const floa
   float4 *o4 = reinterpret_cast<float4 *>(dx);
   for (size_t j = i; j < n4; j += step) {
     float4 a = y4[j], g = d4[j], o;
-    o.x = act_grad(kind, a.x, g.x);
-    o.y = act_grad(kind, a.y, g.y);
-    o.z = act_grad(kind, a.z, g.z);
-    o.w = act_grad(kind, a.w, g.w);
+    o.x = act_grad(kind, param, a.x, g.x);
+    o.y = act_grad(kind, param, a.y, g.y);
+    o.z = act_grad(kind, param, a.z, g.z);
+    o.w = act_grad(kind, param, a.w, g.w);
     o4[j] = o;
   }
-  for (size_t j = n4 * 4 + i; j < n; j += step) dx[j] = act_grad(kind, y[j], dy[j]);
+  for (size_t j = n4 * 4 + i; j < n; j += step) dx[j] = act_grad(kind, param, y[j], dy[j]);
 }
 
 // softmax_layer.h:24-34: subtract the row max, exponentiate, divide by the sum
@@ -244,10 +249,8 @@ static int grid_for(size_t total, int block, int sm_count) {
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B) {
-  B200_REQUIRE(kind == B200_ACT_RELU || kind == B200_ACT_TANH || kind == B200_ACT_SOFTMAX ||
-                 kind == B200_ACT_NONE,
-               "act_fwd: unknown activation %d", kind);
+int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B, float param) {
+  B200_REQUIRE(kind >= B200_ACT_NONE && kind <= B200_ACT_ELU, "act_fwd: unknown activation %d", kind);
   size_t n = (size_t)dim * B;
   if (n == 0) return 0;
   if (kind == B200_ACT_SOFTMAX) {
@@ -257,17 +260,15 @@ int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B) {
       softmax_fwd_kernel<<<ceil_div(B, 32), 32, 0, ctx->stream>>>(x, y, dim, B);
   } else {
     size_t n4 = (aligned16(x) && aligned16(y)) ? n / 4 : 0;
-    act_fwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(kind, x, y,
-                                                                                      n4, n);
+    act_fwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(kind, param, x,
+                                                                                      y, n4, n);
   }
   B200_LAUNCHED();
   return 0;
 }
 
-int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int B) {
-  B200_REQUIRE(kind == B200_ACT_RELU || kind == B200_ACT_TANH || kind == B200_ACT_SOFTMAX ||
-                 kind == B200_ACT_NONE,
-               "act_bwd: unknown activation %d", kind);
+int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int B, float param) {
+  B200_REQUIRE(kind >= B200_ACT_NONE && kind <= B200_ACT_ELU, "act_bwd: unknown activation %d", kind);
   size_t n = (size_t)dim * B;
   if (n == 0) return 0;
   if (kind == B200_ACT_SOFTMAX) {
@@ -279,7 +280,7 @@ int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx,
   } else {
     size_t n4 = (aligned16(y) && aligned16(dy) && aligned16(dx)) ? n / 4 : 0;
     act_bwd_kernel<<<grid_for(n4 ? n4 : n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
-      kind, y, dy, dx, n4, n);
+      kind, param, y, dy, dx, n4, n);
   }
   B200_LAUNCHED();
   return 0;

@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "device_utils.cuh"
 
 using namespace b200;
 
@@ -440,36 +441,49 @@ int b200_avgpool_bwd_host(b200_ctx *ctx, const b200_pool_desc *d, const float *i
 }
 
 // ---------------------------------------------------------------- activations / loss
-int b200_act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int batch) {
+int b200_act_param_fwd(b200_ctx *ctx, int kind, float param, const float *x, float *y, int dim, int batch) {
   B200_TRY(check_ctx(ctx));
   B200_REQUIRE(x && y && dim > 0 && batch >= 0, "act_fwd: bad argument");
-  return act_fwd(ctx, kind, x, y, dim, batch);
+  return act_fwd(ctx, kind, x, y, dim, batch, param);
 }
-int b200_act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim,
-                 int batch) {
+int b200_act_param_bwd(b200_ctx *ctx, int kind, float param, const float *y, const float *dy, float *dx, int dim,
+                       int batch) {
   B200_TRY(check_ctx(ctx));
   B200_REQUIRE(y && dy && dx && dim > 0 && batch >= 0, "act_bwd: bad argument");
-  return act_bwd(ctx, kind, y, dy, dx, dim, batch);
+  return act_bwd(ctx, kind, y, dy, dx, dim, batch, param);
 }
-int b200_act_fwd_host(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int batch) {
+int b200_act_param_fwd_host(b200_ctx *ctx, int kind, float param, const float *x, float *y, int dim, int batch) {
   B200_TRY(check_ctx(ctx));
   B200_REQUIRE(dim > 0 && batch >= 0, "act_fwd_host: bad argument");
   size_t n = (size_t)dim * batch * 4;
   HostBuf b[2] = {{x, nullptr, n, nullptr}, {nullptr, y, n, nullptr}};
   B200_TRY(stage_in(ctx, b, 2));
-  B200_TRY(act_fwd(ctx, kind, (const float *)b[0].dev, (float *)b[1].dev, dim, batch));
+  B200_TRY(act_fwd(ctx, kind, (const float *)b[0].dev, (float *)b[1].dev, dim, batch, param));
   return stage_out(ctx, b, 2);
 }
-int b200_act_bwd_host(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim,
-                      int batch) {
+int b200_act_param_bwd_host(b200_ctx *ctx, int kind, float param, const float *y, const float *dy, float *dx,
+                            int dim, int batch) {
   B200_TRY(check_ctx(ctx));
   B200_REQUIRE(dim > 0 && batch >= 0, "act_bwd_host: bad argument");
   size_t n = (size_t)dim * batch * 4;
   HostBuf b[3] = {{y, nullptr, n, nullptr}, {dy, nullptr, n, nullptr}, {nullptr, dx, n, nullptr}};
   B200_TRY(stage_in(ctx, b, 3));
-  B200_TRY(act_bwd(ctx, kind, (const float *)b[0].dev, (const float *)b[1].dev, (float *)b[2].dev,
-                   dim, batch));
+  B200_TRY(act_bwd(ctx, kind, (const float *)b[0].dev, (const float *)b[1].dev, (float *)b[2].dev, dim, batch,
+                   param));
   return stage_out(ctx, b, 3);
+}
+// the parameterless forms: the reference's default constructor arguments
+int b200_act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int batch) {
+  return b200_act_param_fwd(ctx, kind, act_default_param(kind), x, y, dim, batch);
+}
+int b200_act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int batch) {
+  return b200_act_param_bwd(ctx, kind, act_default_param(kind), y, dy, dx, dim, batch);
+}
+int b200_act_fwd_host(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int batch) {
+  return b200_act_param_fwd_host(ctx, kind, act_default_param(kind), x, y, dim, batch);
+}
+int b200_act_bwd_host(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int batch) {
+  return b200_act_param_bwd_host(ctx, kind, act_default_param(kind), y, dy, dx, dim, batch);
 }
 
 int b200_loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy, int dim,

@@ -263,8 +263,10 @@ int avgpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const f
 int avgpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const float *W,
                 const float *dout, float *din, float *dW, float *db, int accumulate, int B);
 
-int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B);
-int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int B);
+// `param`: epsilon of leaky relu / alpha of elu (ignored by the other kinds)
+int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B, float param = 0.f);
+int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int B,
+            float param = 0.f);
 int loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy, int dim, int B);
 // loss gradient (into dy) and the gradient of a softmax layer whose output is y (into dx) in one launch
 int softmax_loss_bwd(b200_ctx *ctx, int loss_kind, const float *y, const float *t, float *dy, float *dx, int dim,

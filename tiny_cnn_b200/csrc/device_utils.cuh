@@ -14,6 +14,21 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return v;
 }
 
+// the default constructor parameters of leaky_relu_layer (epsilon) and elu_layer (alpha)
+__host__ __device__ __forceinline__ float act_default_param(int act) {
+  return act == B200_ACT_LEAKY_RELU ? 0.01f : act == B200_ACT_ELU ? 1.f : 0.f;
+}
+
+// relu / tanh as above; sigmoid_layer.h:26-30, leaky_relu_layer.h:74-78, elu_layer.h:38-42
+__device__ __forceinline__ float apply_act_p(float v, int act, float param) {
+  if (act == B200_ACT_RELU) return fmaxf(0.f, v);
+  if (act == B200_ACT_TANH) return tanhf(v);
+  if (act == B200_ACT_SIGMOID) return __fdiv_rn(1.f, __fadd_rn(1.f, expf(-v)));
+  if (act == B200_ACT_LEAKY_RELU) return v > 0.f ? v : __fmul_rn(param, v);
+  if (act == B200_ACT_ELU) return v < 0.f ? __fmul_rn(param, __fsub_rn(expf(v), 1.f)) : v;
+  return v;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

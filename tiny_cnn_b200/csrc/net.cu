@@ -38,6 +38,7 @@ struct Layer {
   float *tc_wt_fwd = nullptr, *tc_wt_dx = nullptr, *tc_part = nullptr, *tc_small_part = nullptr;
   float *fc_scratch = nullptr;  // k-slice partial sums of the small GEMMs
   float *fc_scratch_side = nullptr;  // the same for the dW GEMM when it runs on the side stream
+  float act_param = 0.f;  // leaky relu: epsilon; elu: alpha
   int fused_act = 0;      // activation of the NEXT layer folded into this epilogue
   bool skipped = false;   // activation layer folded into the previous layer
   bool relu_bwd_fused = false;   // max-pool: also applies the gradient of the relu before it
@@ -124,6 +125,9 @@ int act_of_layer(int kind) {
   if (kind == B200_LAYER_RELU) return B200_ACT_RELU;
   if (kind == B200_LAYER_TANH) return B200_ACT_TANH;
   if (kind == B200_LAYER_SOFTMAX) return B200_ACT_SOFTMAX;
+  if (kind == B200_LAYER_SIGMOID) return B200_ACT_SIGMOID;
+  if (kind == B200_LAYER_LEAKY_RELU) return B200_ACT_LEAKY_RELU;
+  if (kind == B200_LAYER_ELU) return B200_ACT_ELU;
   return B200_ACT_NONE;
 }
 
@@ -194,7 +198,10 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
       case B200_LAYER_RELU:
       case B200_LAYER_TANH:
       case B200_LAYER_SOFTMAX:
-        B200_TRY(act_fwd(ctx, act_of_layer(L.kind), in, dst, (int)L.out_dim, B));
+      case B200_LAYER_SIGMOID:
+      case B200_LAYER_LEAKY_RELU:
+      case B200_LAYER_ELU:
+        B200_TRY(act_fwd(ctx, act_of_layer(L.kind), in, dst, (int)L.out_dim, B, L.act_param));
         break;
       default: B200_REQUIRE(false, "net_forward: unknown layer kind %d", L.kind);
     }
@@ -324,9 +331,12 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
       case B200_LAYER_RELU:
       case B200_LAYER_TANH:
       case B200_LAYER_SOFTMAX:
+      case B200_LAYER_SIGMOID:
+      case B200_LAYER_LEAKY_RELU:
+      case B200_LAYER_ELU:
         if (L.bwd_done_by_next) break;  // the pooling layer after it already wrote din
         if (din)
-          B200_TRY(act_bwd(ctx, act_of_layer(L.kind), L.out, L.grad, din, (int)L.out_dim, B));
+          B200_TRY(act_bwd(ctx, act_of_layer(L.kind), L.out, L.grad, din, (int)L.out_dim, B, L.act_param));
         break;
       default: B200_REQUIRE(false, "net_backward: unknown layer kind %d", L.kind);
     }
@@ -482,7 +492,11 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
       case B200_LAYER_RELU:
       case B200_LAYER_TANH:
       case B200_LAYER_SOFTMAX:
+      case B200_LAYER_SIGMOID:
+      case B200_LAYER_LEAKY_RELU:
+      case B200_LAYER_ELU:
         L.in_dim = L.out_dim = prev_out;
+        L.act_param = S.act_param;
         break;
       default:
         set_error("net_create: unknown layer kind %d at %d", S.kind, i);

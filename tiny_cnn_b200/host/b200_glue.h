@@ -180,29 +180,34 @@ inline void maxpool_grad_op(tensor_t &prev_delta, const tensor_t &curr_delta,
 
 // activation_layer::forward_propagation / back_propagation branch
 // (tiny_dnn/activations/activation_layer.h:74-91).  `type` is the layer's layer_type() string;
+// `param` the activation's constructor parameter (leaky relu: epsilon, elu: alpha);
 // returns false for an activation that is not on the path (the caller then runs its own loop).
 inline int activation_kind(const std::string &type) {
   if (type == "relu-activation") return B200_ACT_RELU;
   if (type == "tanh-activation") return B200_ACT_TANH;
   if (type == "softmax-activation") return B200_ACT_SOFTMAX;
+  if (type == "sigmoid-activation") return B200_ACT_SIGMOID;
+  if (type == "leaky-relu-activation") return B200_ACT_LEAKY_RELU;
+  if (type == "elu-activation") return B200_ACT_ELU;
   return B200_ACT_NONE;
 }
 
-inline bool activation_op(const std::string &type, const tensor_t &x, tensor_t &y) {
+inline bool activation_op(const std::string &type, float param, const tensor_t &x, tensor_t &y) {
   const int kind = activation_kind(type);
   if (kind == B200_ACT_NONE || x.empty()) return false;
   std::vector<float> in = pack(x), out(in.size());
-  check(b200_act_fwd_host(ctx(), kind, in.data(), out.data(), static_cast<int>(x[0].size()),
+  check(b200_act_param_fwd_host(ctx(), kind, param, in.data(), out.data(), static_cast<int>(x[0].size()),
                           static_cast<int>(x.size())));
   unpack(out, y);
   return true;
 }
 
-inline bool activation_grad_op(const std::string &type, const tensor_t &y, const tensor_t &dy, tensor_t &dx) {
+inline bool activation_grad_op(const std::string &type, float param, const tensor_t &y, const tensor_t &dy,
+                               tensor_t &dx) {
   const int kind = activation_kind(type);
   if (kind == B200_ACT_NONE || y.empty()) return false;
   std::vector<float> fy = pack(y), fdy = pack(dy), fdx(fy.size());
-  check(b200_act_bwd_host(ctx(), kind, fy.data(), fdy.data(), fdx.data(), static_cast<int>(y[0].size()),
+  check(b200_act_param_bwd_host(ctx(), kind, param, fy.data(), fdy.data(), fdx.data(), static_cast<int>(y[0].size()),
                           static_cast<int>(y.size())));
   unpack(fdx, dx);
   return true;

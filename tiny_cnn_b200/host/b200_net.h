@@ -37,7 +37,10 @@
 #include <type_traits>
 #include <vector>
 
+#include "tiny_dnn/activations/elu_layer.h"
+#include "tiny_dnn/activations/leaky_relu_layer.h"
 #include "tiny_dnn/activations/relu_layer.h"
+#include "tiny_dnn/activations/sigmoid_layer.h"
 #include "tiny_dnn/activations/softmax_layer.h"
 #include "tiny_dnn/activations/tanh_layer.h"
 #include "tiny_dnn/core/kernels/b200_glue.h"
@@ -147,6 +150,20 @@ inline bool spec_of(layer *l, b200_layer_spec &s, std::vector<uint8_t> &tbl) {
   }
   if (dynamic_cast<softmax_layer *>(l)) {
     s.kind = B200_LAYER_SOFTMAX;
+    return true;
+  }
+  if (dynamic_cast<sigmoid_layer *>(l)) {
+    s.kind = B200_LAYER_SIGMOID;
+    return true;
+  }
+  if (auto *k = dynamic_cast<leaky_relu_layer *>(l)) {
+    s.kind = B200_LAYER_LEAKY_RELU;
+    s.act_param = static_cast<float>(k->epsilon_);
+    return true;
+  }
+  if (auto *e = dynamic_cast<elu_layer *>(l)) {
+    s.kind = B200_LAYER_ELU;
+    s.act_param = static_cast<float>(e->alpha_);
     return true;
   }
   return false;

@@ -194,17 +194,38 @@ def patch_avgpool_layer(t, p):
 
 
 def patch_activation_layer(t, p):
-    """relu / tanh / softmax under layer::set_backend_type(b200) (activation_layer.h:74-91); the
-    other activations keep their own loops."""
+    """relu / tanh / softmax / sigmoid / leaky relu / elu under layer::set_backend_type(b200)
+    (activation_layer.h:74-91); the other activations keep their own loops.  The constructor
+    parameter of leaky relu (epsilon) and elu (alpha) reaches the base class through a virtual
+    that the two derived headers override."""
     t = _edit(t, "namespace tiny_dnn {\n", GLUE_INCLUDE + "\nnamespace tiny_dnn {\n", p)
     t = _edit(t, "    const tensor_t &x = *in_data[0];\n    tensor_t &y       = *out_data[0];\n",
               "    const tensor_t &x = *in_data[0];\n    tensor_t &y       = *out_data[0];\n"
-              "    if (layer::engine() == core::backend_t::b200 && b200::activation_op(layer_type(), x, y)) return;\n", p)
+              "    if (layer::engine() == core::backend_t::b200 &&\n"
+              "        b200::activation_op(layer_type(), static_cast<float>(b200_act_param()), x, y))\n"
+              "      return;\n", p)
     t = _edit(t, "    const tensor_t &y  = *out_data[0];\n",
               "    const tensor_t &y  = *out_data[0];\n"
-              "    if (layer::engine() == core::backend_t::b200 && b200::activation_grad_op(layer_type(), y, dy, dx))\n"
+              "    if (layer::engine() == core::backend_t::b200 &&\n"
+              "        b200::activation_grad_op(layer_type(), static_cast<float>(b200_act_param()), y, dy, dx))\n"
               "      return;\n", p)
+    t = _edit(t, "  std::string layer_type() const override = 0;\n",
+              "  std::string layer_type() const override = 0;\n\n"
+              "  // constructor parameter of the activation (leaky relu: epsilon, elu: alpha)\n"
+              "  virtual float_t b200_act_param() const { return float_t(0); }\n", p)
     return t
+
+
+def patch_leaky_relu_layer(t, p):
+    return _edit(t, "  float_t epsilon_value() const { return epsilon_; }\n",
+                 "  float_t epsilon_value() const { return epsilon_; }\n\n"
+                 "  float_t b200_act_param() const override { return epsilon_; }\n", p)
+
+
+def patch_elu_layer(t, p):
+    return _edit(t, '  std::string layer_type() const override { return "elu-activation"; }\n',
+                 '  std::string layer_type() const override { return "elu-activation"; }\n\n'
+                 "  float_t b200_act_param() const override { return alpha_; }\n", p)
 
 
 def patch_layer_h(t, p):
@@ -288,6 +309,8 @@ PATCHES = {
     "tiny_dnn/layers/quantized_convolutional_layer.h": patch_qconv_layer,
     "tiny_dnn/layers/average_pooling_layer.h": patch_avgpool_layer,
     "tiny_dnn/activations/activation_layer.h": patch_activation_layer,
+    "tiny_dnn/activations/leaky_relu_layer.h": patch_leaky_relu_layer,
+    "tiny_dnn/activations/elu_layer.h": patch_elu_layer,
     "tiny_dnn/layers/layer.h": patch_layer_h,
     "tiny_dnn/optimizers/optimizer.h": patch_optimizer_h,
     "tiny_dnn/network.h": patch_network_h,

@@ -15,7 +15,8 @@ import numpy as np
 import torch
 
 from . import _lib as L
-from ._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_RELU, LAYER_SOFTMAX,
+from ._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_ELU, LAYER_FC, LAYER_LEAKY_RELU, LAYER_MAXPOOL, LAYER_RELU,
+                   LAYER_SIGMOID, LAYER_SOFTMAX,
                    LAYER_TANH, LOSS_CROSS_ENTROPY, LOSS_MSE, OPT_ADAGRAD, OPT_ADAM, OPT_ADAMAX, OPT_GRADIENT_DESCENT,
                    OPT_MOMENTUM, OPT_NESTEROV_MOMENTUM, OPT_RMSPROP,
                    LayerSpec, OptHyper, check, ptr)
@@ -161,9 +162,10 @@ class Sequential:
         self._out_dim = d.in_c * d.out_h * d.out_w
         return self
 
-    def _act(self, kind):
+    def _act(self, kind, param=0.0):
         s = LayerSpec()
         s.kind = kind
+        s.act_param = param
         self.specs.append(s)
         return self
 
@@ -175,6 +177,15 @@ class Sequential:
 
     def softmax_layer(self):
         return self._act(LAYER_SOFTMAX)
+
+    def sigmoid_layer(self):
+        return self._act(LAYER_SIGMOID)
+
+    def leaky_relu_layer(self, epsilon=0.01):
+        return self._act(LAYER_LEAKY_RELU, epsilon)
+
+    def elu_layer(self, alpha=1.0):
+        return self._act(LAYER_ELU, alpha)
 
     # ---- device twin ---------------------------------------------------------------------
     def spec_array(self):

@@ -200,17 +200,25 @@ def average_pooling_backward(ctx: Context, d: PoolDesc, x, W, dout, need_dx=True
 
 
 # --------------------------------------------------------------------------- activations / loss
-def forward_activation(ctx: Context, kind: int, x):
-    """activation_layer::forward_propagation (tiny_dnn/activations/activation_layer.h:74-79)."""
+def forward_activation(ctx: Context, kind: int, x, param=None):
+    """activation_layer::forward_propagation (tiny_dnn/activations/activation_layer.h:74-79).
+    `param`: epsilon of leaky_relu_layer / alpha of elu_layer (None: the reference's default)."""
     y = torch.empty_like(x)
-    check(ctx.lib.b200_act_fwd(ctx.handle, kind, ptr(x), ptr(y), x.shape[1], x.shape[0]))
+    if param is None:
+        check(ctx.lib.b200_act_fwd(ctx.handle, kind, ptr(x), ptr(y), x.shape[1], x.shape[0]))
+    else:
+        check(ctx.lib.b200_act_param_fwd(ctx.handle, kind, float(param), ptr(x), ptr(y), x.shape[1], x.shape[0]))
     return y
 
 
-def backward_activation(ctx: Context, kind: int, y, dy):
+def backward_activation(ctx: Context, kind: int, y, dy, param=None):
     """activation_layer::back_propagation (activation_layer.h:81-91)."""
     dx = torch.empty_like(y)
-    check(ctx.lib.b200_act_bwd(ctx.handle, kind, ptr(y), ptr(dy), ptr(dx), y.shape[1], y.shape[0]))
+    if param is None:
+        check(ctx.lib.b200_act_bwd(ctx.handle, kind, ptr(y), ptr(dy), ptr(dx), y.shape[1], y.shape[0]))
+    else:
+        check(ctx.lib.b200_act_param_bwd(ctx.handle, kind, float(param), ptr(y), ptr(dy), ptr(dx), y.shape[1],
+                                         y.shape[0]))
     return dx
 
 
