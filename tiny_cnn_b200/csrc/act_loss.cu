@@ -311,6 +311,114 @@ int softmax_loss_bwd(b200_ctx *ctx, int loss_kind, const float *y, const float *
   return 0;
 }
 
+// ---- a narrow fully-connected layer followed by a softmax output layer ---------------------
+// (the classifier's last two layers: 64 -> 10 in the CIFAR-10 net).  Sixteen lanes per sample as in
+// the softmax kernels above; the weights (K x N floats, N <= 16) sit in shared memory.
+constexpr int FCS_THREADS = 64;  // four samples per block: enough blocks to spread a small batch
+
+// z = x W + b (fully_connected_op_internal.h:15-36: products added in input order, then the bias),
+// y = softmax(z) (softmax_layer.h:24-34)
+__global__ void __launch_bounds__(FCS_THREADS) fc_softmax_fwd16_kernel(const float *__restrict__ x,
+                                                                       const float *__restrict__ W,
+                                                                       const float *__restrict__ bias,
+                                                                       float *__restrict__ z, float *__restrict__ y,
+                                                                       int K, int N, int B) {
+  extern __shared__ float fcs_w[];  // [K][N]
+  for (int i = threadIdx.x; i < K * N; i += FCS_THREADS) fcs_w[i] = W[i];
+  __syncthreads();
+  const int n = (blockIdx.x * FCS_THREADS + threadIdx.x) >> 4, j = threadIdx.x & 15;
+  const int base = threadIdx.x & 16;
+  const bool row = n < B, live = row && j < N;
+  const float *xr = x + (size_t)(row ? n : 0) * K;
+  float acc = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    const float xv = (row && k0 + j < K) ? xr[k0 + j] : 0.f;  // lane j holds x[k0 + j]
+    const int kn = min(16, K - k0);
+    for (int k = 0; k < kn; ++k) {
+      const float xk = __shfl_sync(0xffffffffu, xv, base + k);
+      if (j < N) acc = fmaf(xk, fcs_w[(k0 + k) * N + j], acc);
+    }
+  }
+  const float zj = (bias != nullptr && j < N) ? acc + bias[j] : acc;
+  if (live) z[(size_t)n * N + j] = zj;
+  float alpha = __shfl_sync(0xffffffffu, zj, base);
+  for (int k = 1; k < N; ++k) alpha = fmaxf(alpha, __shfl_sync(0xffffffffu, zj, base + k));
+  const float ej = expf(zj - alpha);
+  float denom = 0.f;
+  for (int k = 0; k < N; ++k) denom += __shfl_sync(0xffffffffu, ej, base + k);
+  if (live) y[(size_t)n * N + j] = ej / denom;
+}
+
+// dy = loss gradient of (y, t); dz = softmax gradient (as softmax_bwd16_kernel); dx = dz W^T
+// (fully_connected_op_internal.h:45-50), multiplied by the gradient of a relu in front of the layer when
+// `relu_x` (that relu's output = this layer's input) is given (relu_layer.h:31-39)
+__global__ void __launch_bounds__(FCS_THREADS) fc_softmax_bwd16_kernel(const float *__restrict__ y,
+                                                                       const float *__restrict__ t, int loss_kind,
+                                                                       const float *__restrict__ W,
+                                                                       const float *__restrict__ relu_x,
+                                                                       float *__restrict__ dy, float *__restrict__ dz,
+                                                                       float *__restrict__ dx, int K, int N, int B) {
+  extern __shared__ float fcs_w[];  // [K][N]
+  for (int i = threadIdx.x; i < K * N; i += FCS_THREADS) fcs_w[i] = W[i];
+  __syncthreads();
+  const int n = (blockIdx.x * FCS_THREADS + threadIdx.x) >> 4, j = threadIdx.x & 15;
+  const int base = threadIdx.x & 16;
+  const bool row = n < B, live = row && j < N;
+  const float factor = 2.0f / (float)N;
+  float yj = 0.f, gj = 0.f;
+  if (live) {
+    yj = y[(size_t)n * N + j];
+    gj = loss_grad_one(loss_kind, yj, t[(size_t)n * N + j], factor);
+    dy[(size_t)n * N + j] = gj;
+  }
+  float s = 0.f;
+  for (int k = 0; k < N; ++k) {
+    const float yk = __shfl_sync(0xffffffffu, yj, base + k);
+    const float gk = __shfl_sync(0xffffffffu, gj, base + k);
+    const float df = (k == j) ? __fmul_rn(yj, __fsub_rn(1.f, yj)) : __fmul_rn(-yk, yj);
+    s = __fadd_rn(s, __fmul_rn(gk, df));
+  }
+  if (live) dz[(size_t)n * N + j] = s;
+  if (dx == nullptr) return;
+  // lane j owns inputs c = j, j + 16, ...: dx_c = sum_i dz_i W[c][i]
+  for (int c0 = 0; c0 < K; c0 += 16) {
+    const int c = c0 + j;
+    float a = 0.f;
+    for (int i = 0; i < N; ++i) {
+      const float di = __shfl_sync(0xffffffffu, s, base + i);
+      if (c < K) a = fmaf(di, fcs_w[c * N + i], a);
+    }
+    if (row && c < K) {
+      if (relu_x != nullptr && !(relu_x[(size_t)n * K + c] > 0.f)) a = 0.f;
+      dx[(size_t)n * K + c] = a;
+    }
+  }
+}
+
+bool fc_softmax_fusable(int K, int N) { return N >= 1 && N <= 16 && K >= 1 && (size_t)K * N * sizeof(float) <= 32 * 1024; }
+
+int fc_softmax_fwd(b200_ctx *ctx, int K, int N, const float *x, const float *W, const float *bias, float *z, float *y,
+                   int B) {
+  B200_REQUIRE(fc_softmax_fusable(K, N), "fc_softmax_fwd: shape %d x %d not supported", K, N);
+  if (B == 0) return 0;
+  fc_softmax_fwd16_kernel<<<ceil_div(B * 16, FCS_THREADS), FCS_THREADS, (size_t)K * N * sizeof(float), ctx->stream>>>(
+    x, W, bias, z, y, K, N, B);
+  B200_LAUNCHED();
+  return 0;
+}
+
+int fc_softmax_loss_bwd(b200_ctx *ctx, int loss_kind, int K, int N, const float *y, const float *t, const float *W,
+                        const float *relu_x, float *dy, float *dz, float *dx, int B) {
+  B200_REQUIRE(fc_softmax_fusable(K, N), "fc_softmax_loss_bwd: shape %d x %d not supported", K, N);
+  B200_REQUIRE(loss_kind >= B200_LOSS_MSE && loss_kind <= B200_LOSS_CROSS_ENTROPY_MULTICLASS,
+               "fc_softmax_loss_bwd: unknown loss %d", loss_kind);
+  if (B == 0) return 0;
+  fc_softmax_bwd16_kernel<<<ceil_div(B * 16, FCS_THREADS), FCS_THREADS, (size_t)K * N * sizeof(float), ctx->stream>>>(
+    y, t, loss_kind, W, relu_x, dy, dz, dx, K, N, B);
+  B200_LAUNCHED();
+  return 0;
+}
+
 int loss_value(b200_ctx *ctx, int kind, const float *y, const float *t, float *loss_sum, int dim,
                int B) {
   B200_REQUIRE(kind >= B200_LOSS_MSE && kind <= B200_LOSS_CROSS_ENTROPY_MULTICLASS,

@@ -148,8 +148,9 @@ int conv_general_dw(b200_ctx *ctx, const ConvGeom &g, const float *in, const flo
 // tiled kernels; `scratch` must hold the matching conv_tiled_*_scratch floats
 int conv_tiled_fwd(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *W,
                    const float *bias, float *out, int B, int act, float *scratch);
+int conv_tiled_dx_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, float *scratch);
 int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float *dout,
-                  float *din, int B, float *scratch);
+                  float *din, int B, float *scratch, int prep = 1);
 // Writes `*splits` partial sums of [dW | db] (row length conv_weight_len + OC)
 // into scratch; the caller merges them in row order.
 int conv_tiled_dw_partials(b200_ctx *ctx, const ConvGeom &g, const float *in,
@@ -182,7 +183,7 @@ int conv_tc_tall_dy(b200_ctx *ctx, const ConvGeom &g, const float *dout, int B, 
 int conv_tc_tall_x_pool(b200_ctx *ctx, const ConvGeom &g, const float *in, float *pooled, int32_t *argmax, int B,
                         float *xs);
 int conv_tc_tall_dy_unpool(b200_ctx *ctx, const ConvGeom &g, const float *gpool, const int32_t *argmax,
-                           const float *relu_y, float *dout_chw, int B, float *dys, float *bsum);
+                           const float *pooled_y, float *dout_chw, int B, float *dys, float *bsum);
 // filter matrices of the forward and / or dX pass (either may be nullptr) in one launch
 int conv_tc_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, float *wt_fwd, float *wt_dx);
 // `prep` = 0 reuses the filter matrices an earlier call left in `wt` (same weights)
@@ -192,15 +193,38 @@ int conv_tc_dx(b200_ctx *ctx, const ConvGeom &g, const float *dys, const float *
                float *wt, int prep = 1);
 int conv_tc_dw(b200_ctx *ctx, const ConvGeom &g, const float *xs, const float *dys, int B, float *part,
                int *splits);
-// finish: fixed-order sum of the partial rows into the reference layout, and (with bsum / db) the bias gradient
+// Arguments of one finishing pass of a tensor-core dW kernel: sums the partial rows in fixed order
+// and stores the totals in the reference layout.  Elements [0, row_w) are weight-gradient entries in
+// the producing kernel's own order; `layout` says which: 0 = [unit][j][ky][inc][o] of
+// conv_dw_tc_kernel (kx = KW-1-j), 1 = [k][o] of conv_dw_small_tc_kernel.  Elements
+// [row_w, row_w + OC) are bias-gradient sums taken from `bsrc` (bs_rows rows of bs_stride floats,
+// entry bs_off + o of each).  Unconnected pairs get no gradient.
+struct DwFinishArgs {
+  const float *part;
+  long long part_stride;
+  int splits;
+  const float *bsrc;
+  long long bs_stride, bs_off;
+  int bs_rows;
+  float *dW, *db;
+  int layout, row_w;
+  int C, OC, OCp, KH, KW, ic_slabs;
+  const uint8_t *tbl;
+  int accumulate;
+};
+constexpr int DW_FINISH_MAX = 4;  // layers per launch of dw_finish_many
+// finish: fixed-order sum of the partial rows into the reference layout, and (with bsum / db) the bias
+// gradient.  With `defer` the pass is not launched but described there, for dw_finish_many.
 int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate,
-                      const float *bsum, int B, float *db);
+                      const float *bsum, int B, float *db, DwFinishArgs *defer = nullptr);
+// the finishing passes of several layers in one launch (same sums, element by element)
+int dw_finish_many(b200_ctx *ctx, const DwFinishArgs *list, int n);
 
 // dW of stride-1 layers with in_c*KH*KW <= 128 on the tensor cores, straight from the CHW tensors
 bool conv_dw_small_ok(const b200_ctx *ctx, const ConvGeom &g);
 size_t conv_dw_small_floats(const b200_ctx *ctx, const ConvGeom &g, int B);
 int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout, int B, float *part,
-                  float *dW, float *db, int accumulate);
+                  float *dW, float *db, int accumulate, DwFinishArgs *defer = nullptr);
 
 // dst (+)= sum_r src[r*stride + i], rows summed in order; optional connection
 // mask for convolution weights (entries of unconnected pairs are left alone
@@ -234,7 +258,7 @@ struct PeerReduce {
   long long split = 0;           // [split, n) is pushed early, [0, split) by the summing kernel
   unsigned long long timeout_ns = 0;
   float **bases_dev = nullptr;   // [world] every rank's buffer as mapped in this process
-  unsigned *step_dev = nullptr;  // reductions done so far
+  unsigned *step_dev = nullptr;  // [0] reductions done so far, [1] blocks of the running sum that ended
 };
 size_t peer_reduce_bytes(long long n, int world);
 // `timeout_ms` bounds every wait of the summing kernel (0 = 10 s)
@@ -252,11 +276,11 @@ int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const floa
 
 int maxpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, float *out,
                 int32_t *argmax, int B);
-// `relu_y` (optional): output of a relu layer feeding this pooling layer; its
-// gradient mask is applied to din on the way (2x2/2 aligned layers only, see
-// maxpool_can_fuse_relu).
+// `pooled_y` (optional): this layer's forward output, given when a relu layer feeds the pooling
+// layer; the relu's gradient mask (its output at a window's winner is the pooled value) is applied
+// to din on the way (2x2/2 aligned layers only, see maxpool_can_fuse_relu).
 int maxpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *dout, const int32_t *argmax,
-                float *din, int B, const float *relu_y = nullptr);
+                float *din, int B, const float *pooled_y = nullptr);
 bool maxpool_can_fuse_relu(const b200_pool_desc &d);
 int avgpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const float *W,
                 const float *bias, float *out, int B);
@@ -271,6 +295,15 @@ int loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy
 // loss gradient (into dy) and the gradient of a softmax layer whose output is y (into dx) in one launch
 int softmax_loss_bwd(b200_ctx *ctx, int loss_kind, const float *y, const float *t, float *dy, float *dx, int dim,
                      int B);
+// a fully-connected layer of at most 16 outputs followed by a softmax output layer, as one kernel
+// per direction: forward z = x W + b, y = softmax(z); backward dy = loss gradient, dz = softmax
+// gradient, dx = dz W^T (times the gradient of the relu whose output `relu_x` is the layer's input,
+// when given; dx may be nullptr)
+bool fc_softmax_fusable(int K, int N);
+int fc_softmax_fwd(b200_ctx *ctx, int K, int N, const float *x, const float *W, const float *bias, float *z, float *y,
+                   int B);
+int fc_softmax_loss_bwd(b200_ctx *ctx, int loss_kind, int K, int N, const float *y, const float *t, const float *W,
+                        const float *relu_x, float *dy, float *dz, float *dx, int B);
 int loss_value(b200_ctx *ctx, int kind, const float *y, const float *t, float *loss_sum, int dim,
                int B);
 

@@ -75,13 +75,14 @@ int dy_period(const ConvGeom &g) {
 // Where the CHW values to convert come from.  mode 0: a CHW tensor.  mode 1: the 2x2/2 max-pool of
 // `a` (planes in_h x in_w = 2H x 2W): the pooled values and their argmax are also written, CHW, as
 // maxpool2x2_fwd_kernel would (strict '>' in window order).  mode 2: the gradient of a 2x2/2
-// max-pool (pooled gradient `a`, argmax `am`), masked by the relu whose output is `relu_y` when
+// max-pool (pooled gradient `a`, argmax `am`), masked by the relu before the pooling layer when
+// `pooled_y` (the pooling layer's forward output: the relu's output at each window's winner) is
 // given; the CHW gradient is also written to `out_chw`.
 struct TallSrc {
   int mode;
   const float *a;
   const int32_t *am;
-  const float *relu_y;
+  const float *pooled_y;
   float *out_chw;
   int32_t *out_am;
 };
@@ -104,7 +105,8 @@ __device__ __forceinline__ void pool_window(float a, float b, float c, float d, 
 // writes the per-channel sum of what it read (bias gradient partials, fixed order).
 // Shared tile [c][pixel] with an odd pitch: scalar, coalesced loads along x; 16-byte
 // stores of four channels of one pixel.
-__global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, int H, int W, int Cp, int period,
+template <int MODE>
+__global__ void __launch_bounds__(256, MODE == 1 ? 1 : 6) to_tall_kernel(const TallSrc src, int C, int H, int W, int Cp, int period,
                                                       int rb, int pitch, float *__restrict__ hi,
                                                       float *__restrict__ lo, float *__restrict__ bsum) {
   extern __shared__ float tile[];  // [C][pitch]
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
   const size_t plane = (size_t)H * W;
   // phase 1: one warp per channel (channels w, w+8, ...), lanes along the pixels of the chunk
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (src.mode == 0) {
+  if (MODE == 0) {
     const float *img = src.a + ((size_t)b * C * H + r0) * W;
     for (int c = warp; c < C; c += 8) {
       const float *ch = img + c * plane;
@@ -124,7 +126,7 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
 #pragma unroll 4
       for (int p = lane; p < npx; p += 32) trow[p] = p < valid_px ? ch[p] : 0.f;
     }
-  } else if (src.mode == 1) {
+  } else if (MODE == 1) {
     // two pooled pixels per lane: 16-byte loads of the two input rows, 8-byte stores.  Two channels
     // per pass, so that four loads are in flight per lane; the pair's place in the chunk does not
     // depend on the channel.
@@ -188,23 +190,23 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
         if (y < H) {
           const size_t po = ((size_t)b * C + c) * ph * pw + (size_t)(y >> 1) * pw + prx;
           const size_t o = ((size_t)b * C + c) * plane + (size_t)y * W + x;
-          const float2 gv = *reinterpret_cast<const float2 *>(src.a + po);
+          float2 gv = *reinterpret_cast<const float2 *>(src.a + po);
           const int2 am = *reinterpret_cast<const int2 *>(src.am + po);
+          if (src.pooled_y != nullptr) {  // relu mask: the relu's output at a winner is the pooled value
+            const float2 py = *reinterpret_cast<const float2 *>(src.pooled_y + po);
+            gv.x = py.x > 0.f ? gv.x : 0.f;
+            gv.y = py.y > 0.f ? gv.y : 0.f;
+          }
           const int base0 = (H * c + y) * W + x;
           const int a0 = am.x - base0, a1 = am.y - (base0 + 2);  // offset inside the window: 0, 1, W, W+1
-          float4 ra = make_float4(1.f, 1.f, 1.f, 1.f), rb2 = ra;
-          if (src.relu_y != nullptr) {
-            ra = *reinterpret_cast<const float4 *>(src.relu_y + o);
-            rb2 = *reinterpret_cast<const float4 *>(src.relu_y + o + W);
-          }
-          v0.x = (a0 == 0 && ra.x > 0.f) ? gv.x : 0.f;
-          v0.y = (a0 == 1 && ra.y > 0.f) ? gv.x : 0.f;
-          v0.z = (a1 == 0 && ra.z > 0.f) ? gv.y : 0.f;
-          v0.w = (a1 == 1 && ra.w > 0.f) ? gv.y : 0.f;
-          v1.x = (a0 == W && rb2.x > 0.f) ? gv.x : 0.f;
-          v1.y = (a0 == W + 1 && rb2.y > 0.f) ? gv.x : 0.f;
-          v1.z = (a1 == W && rb2.z > 0.f) ? gv.y : 0.f;
-          v1.w = (a1 == W + 1 && rb2.w > 0.f) ? gv.y : 0.f;
+          v0.x = a0 == 0 ? gv.x : 0.f;
+          v0.y = a0 == 1 ? gv.x : 0.f;
+          v0.z = a1 == 0 ? gv.y : 0.f;
+          v0.w = a1 == 1 ? gv.y : 0.f;
+          v1.x = a0 == W ? gv.x : 0.f;
+          v1.y = a0 == W + 1 ? gv.x : 0.f;
+          v1.z = a1 == W ? gv.y : 0.f;
+          v1.w = a1 == W + 1 ? gv.y : 0.f;
           if (src.out_chw != nullptr) {
             *reinterpret_cast<float4 *>(src.out_chw + o) = v0;
             *reinterpret_cast<float4 *>(src.out_chw + o + W) = v1;
@@ -233,17 +235,13 @@ __global__ void __launch_bounds__(256) to_tall_kernel(const TallSrc src, int C, 
       if (y < H) {
         const size_t po = ((size_t)b * C + c) * ph * pw + (size_t)(y >> 1) * pw + prx;
         const size_t o = ((size_t)b * C + c) * plane + (size_t)y * W + x;
-        const float gval = src.a[po];
+        float gval = src.a[po];
         const int am = src.am[po] - ((H * c + y) * W + x);  // offset inside the window: 0, 1, W, W+1
-        float2 ra = make_float2(1.f, 1.f), rb2 = make_float2(1.f, 1.f);
-        if (src.relu_y != nullptr) {
-          ra = *reinterpret_cast<const float2 *>(src.relu_y + o);
-          rb2 = *reinterpret_cast<const float2 *>(src.relu_y + o + W);
-        }
-        v0 = (am == 0 && ra.x > 0.f) ? gval : 0.f;
-        v1 = (am == 1 && ra.y > 0.f) ? gval : 0.f;
-        v2 = (am == W && rb2.x > 0.f) ? gval : 0.f;
-        v3 = (am == W + 1 && rb2.y > 0.f) ? gval : 0.f;
+        if (src.pooled_y != nullptr && !(src.pooled_y[po] > 0.f)) gval = 0.f;
+        v0 = am == 0 ? gval : 0.f;
+        v1 = am == 1 ? gval : 0.f;
+        v2 = am == W ? gval : 0.f;
+        v3 = am == W + 1 ? gval : 0.f;
         if (src.out_chw != nullptr) {
           *reinterpret_cast<float2 *>(src.out_chw + o) = make_float2(v0, v1);
           *reinterpret_cast<float2 *>(src.out_chw + o + W) = make_float2(v2, v3);
@@ -891,14 +889,20 @@ int to_tall(b200_ctx *ctx, const TallSrc &src, int C, int H, int W, int Cp, int 
                "tall conversion: the pooling gradient needs even row counts");
   const int pitch = ((rb * W + 7) & ~7) + 1;
   size_t smem = (size_t)C * pitch * sizeof(float);
-  if (smem > 48 * 1024)
-    B200_CUDA(cudaFuncSetAttribute(to_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int chunks = ceil_div(period, rb);
   size_t one = (size_t)B * period * W * Cp;
-  to_tall_kernel<<<B * chunks, 256, smem, ctx->stream>>>(src, C, H, W, Cp, period, rb, pitch, dst, dst + one,
-                                                         bsum);
-  B200_LAUNCHED();
-  return 0;
+  // one instantiation per source, so that the plain and the pooling-gradient conversions do not
+  // carry the registers of the pooling one
+  auto launch = [&](auto kernel) -> int {
+    if (smem > 48 * 1024)
+      B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<B * chunks, 256, smem, ctx->stream>>>(src, C, H, W, Cp, period, rb, pitch, dst, dst + one, bsum);
+    B200_LAUNCHED();
+    return 0;
+  };
+  if (src.mode == 0) return launch(to_tall_kernel<0>);
+  if (src.mode == 1) return launch(to_tall_kernel<1>);
+  return launch(to_tall_kernel<2>);
 }
 
 // shared launcher of the forward and dX passes
@@ -1021,37 +1025,18 @@ int conv_tc_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, float *wt_fwd
 
 namespace {
 
-// One launch that finishes a tensor-core dW pass: sums the partial rows in fixed order (8 row
-// lanes per element, lane k adds rows k, k+8, ... in order, lanes combined in order) and stores
-// the totals in the reference layout.  Elements [0, row_w) are weight-gradient entries in the
-// producing kernel's own order; `layout` says which: 0 = [unit][j][ky][inc][o] of
-// conv_dw_tc_kernel (kx = KW-1-j), 1 = [k][o] of conv_dw_small_tc_kernel.  Elements
-// [row_w, row_w + OC) are bias-gradient sums taken from `bsrc` (bs_rows rows of bs_stride floats,
-// entry bs_off + o of each).  Unconnected pairs get no gradient.
-struct DwFinishArgs {
-  const float *part;
-  long long part_stride;
-  int splits;
-  const float *bsrc;
-  long long bs_stride, bs_off;
-  int bs_rows;
-  float *dW, *db;
-  int layout, row_w;
-  int C, OC, OCp, KH, KW, ic_slabs;
-  const uint8_t *tbl;
-  int accumulate;
-};
-
-__global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) {
+// One block of the finishing pass of a tensor-core dW kernel (DwFinishArgs): 8 row lanes per
+// element, lane k adds rows k, k+8, ... in order, lanes combined in order.
+__device__ __forceinline__ void dw_finish_block(const DwFinishArgs &a, const int block) {
   constexpr int RL = 8;  // row lanes
   __shared__ float lanes[RL][33];
   __shared__ float tree[256];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int wblocks = (a.row_w + 31) / 32;
-  if ((int)blockIdx.x >= wblocks) {
+  if (block >= wblocks) {
     // bias gradient: one block per output channel; its many short partial rows are spread over
     // all 256 threads (thread k adds rows k, k+256, ... in order), combined by a fixed tree
-    const int o = blockIdx.x - wblocks, t = ty * 32 + tx;
+    const int o = block - wblocks, t = ty * 32 + tx;
     if (a.db == nullptr || o >= a.OC) return;
     const float *src = a.bsrc + a.bs_off + o;
     float s = 0.f;
@@ -1066,7 +1051,7 @@ __global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) {
     if (t == 0) a.db[o] = a.accumulate ? a.db[o] + tree[0] : tree[0];
     return;
   }
-  const int e = blockIdx.x * 32 + tx;
+  const int e = block * 32 + tx;
   float s0 = 0.f, s1 = 0.f;
   if (e < a.row_w) {
     const float *src = a.part + e;
@@ -1112,9 +1097,25 @@ __global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) {
   }
 }
 
+__global__ void __launch_bounds__(256) dw_finish_kernel(const DwFinishArgs a) { dw_finish_block(a, (int)blockIdx.x); }
+
+// several layers' finishing passes as one launch: block ranges [first[i], first[i + 1]) belong to layer i
+struct DwFinishBatch {
+  int n;
+  int first[DW_FINISH_MAX + 1];
+  DwFinishArgs a[DW_FINISH_MAX];
+};
+
+__global__ void __launch_bounds__(256) dw_finish_multi_kernel(const DwFinishBatch b) {
+  int i = 0;
+  while (i + 1 < b.n && (int)blockIdx.x >= b.first[i + 1]) ++i;
+  dw_finish_block(b.a[i], (int)blockIdx.x - b.first[i]);
+}
+
+int dw_finish_blocks(const DwFinishArgs &a) { return (a.row_w + 31) / 32 + (a.db != nullptr ? a.OC : 0); }
+
 int launch_dw_finish(b200_ctx *ctx, const DwFinishArgs &a) {
-  const int blocks = (a.row_w + 31) / 32 + (a.db != nullptr ? a.OC : 0);
-  dw_finish_kernel<<<blocks, dim3(32, 8), 0, ctx->stream>>>(a);
+  dw_finish_kernel<<<dw_finish_blocks(a), dim3(32, 8), 0, ctx->stream>>>(a);
   B200_LAUNCHED();
   return 0;
 }
@@ -1218,8 +1219,28 @@ size_t conv_tc_dw_floats(const b200_ctx *ctx, const ConvGeom &g, int B) {
 
 // sum the partial rows conv_tc_dw wrote (fixed order) and store them in the reference layout; with
 // `bsum` (the per-block channel sums of conv_tc_tall_dy) and `db` also the bias gradient
+int dw_finish_many(b200_ctx *ctx, const DwFinishArgs *list, int n) {
+  for (int i0 = 0; i0 < n; i0 += DW_FINISH_MAX) {
+    const int m = n - i0 < DW_FINISH_MAX ? n - i0 : DW_FINISH_MAX;
+    if (m == 1) {
+      B200_TRY(launch_dw_finish(ctx, list[i0]));
+      continue;
+    }
+    DwFinishBatch b;
+    b.n = m;
+    b.first[0] = 0;
+    for (int i = 0; i < m; ++i) {
+      b.a[i] = list[i0 + i];
+      b.first[i + 1] = b.first[i] + dw_finish_blocks(list[i0 + i]);
+    }
+    dw_finish_multi_kernel<<<b.first[m], dim3(32, 8), 0, ctx->stream>>>(b);
+    B200_LAUNCHED();
+  }
+  return 0;
+}
+
 int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits, float *dW, int accumulate,
-                      const float *bsum, int B, float *db) {
+                      const float *bsum, int B, float *db, DwFinishArgs *defer) {
   TallGeom t = tall_geom(g, 1);
   DwFinishArgs a;
   a.part = part;
@@ -1241,6 +1262,10 @@ int conv_tc_dw_finish(b200_ctx *ctx, const ConvGeom &g, float *part, int splits,
   a.ic_slabs = t.Cp / 32;
   a.tbl = g.tbl;
   a.accumulate = accumulate;
+  if (defer != nullptr) {  // the caller launches it later, with other layers' (dw_finish_many)
+    *defer = a;
+    return 0;
+  }
   return launch_dw_finish(ctx, a);
 }
 
@@ -1268,12 +1293,13 @@ int conv_tc_tall_x_pool(b200_ctx *ctx, const ConvGeom &g, const float *in, float
 }
 
 // gradient of a 2x2/2 max-pooling layer (pooled gradient `gpool`, its `argmax`) that follows this
-// convolution -- through the relu in between when `relu_y` (the relu's output) is given -- written as
+// convolution -- through the relu in between when `pooled_y` (the pooling layer's forward output) is
+// given -- written as
 // the tall split copy of dY, as the CHW gradient `dout_chw` (may be nullptr) and as bias partials
 int conv_tc_tall_dy_unpool(b200_ctx *ctx, const ConvGeom &g, const float *gpool, const int32_t *argmax,
-                           const float *relu_y, float *dout_chw, int B, float *dys, float *bsum) {
+                           const float *pooled_y, float *dout_chw, int B, float *dys, float *bsum) {
   TallGeom t = tall_geom(g, B);
-  const TallSrc src = {2, gpool, argmax, relu_y, dout_chw, nullptr};
+  const TallSrc src = {2, gpool, argmax, pooled_y, dout_chw, nullptr};
   return to_tall(ctx, src, g.OC, g.OH, g.OW, t.OCp, dy_period(g), B, dys, bsum);
 }
 
@@ -1661,7 +1687,7 @@ size_t conv_dw_small_floats(const b200_ctx *ctx, const ConvGeom &g, int B) {
 
 // dW (+ db when the layer has a bias) from the CHW input and gradient; `part` holds conv_dw_small_floats
 int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float *dout, int B, float *part,
-                  float *dW, float *db, int accumulate) {
+                  float *dW, float *db, int accumulate, DwFinishArgs *defer) {
   const int OCp = (g.OC + 15) / 16 * 16, bw = dw_small_bw(g);
   EncodeTiledFn fn = encode_fn();
   B200_REQUIRE(fn != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
@@ -1752,6 +1778,10 @@ int conv_dw_small(b200_ctx *ctx, const ConvGeom &g, const float *in, const float
   f.ic_slabs = 1;
   f.tbl = g.tbl;
   f.accumulate = accumulate;
+  if (defer != nullptr) {
+    *defer = f;
+    return 0;
+  }
   B200_TRY(launch_dw_finish(ctx, f));
   return 0;
 }

@@ -887,15 +887,23 @@ static int launch_fewout(b200_ctx *ctx, const FewOutCfg &p, int B) {
   return 0;
 }
 
-int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float *dout,
-                  float *din, int B, float *scratch) {
-  if (B == 0) return 0;
+// the flipped, transposed filter copy the dX kernels read; depends on the weights only
+int conv_tiled_dx_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, float *scratch) {
   int KK = g.KH * g.KW;
   int Cp = padded_channels(g.C);
   int total = g.OC * KK * Cp;
   conv_prep_wt_dx_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(W, scratch, g.C, g.OC, Cp,
                                                                        g.KH, g.KW, g.tbl);
   B200_LAUNCHED();
+  return 0;
+}
+
+// `prep` = 0: `scratch` already holds the filter copy of these weights (conv_tiled_dx_prep)
+int conv_tiled_dx(b200_ctx *ctx, const ConvGeom &g, const float *W, const float *dout,
+                  float *din, int B, float *scratch, int prep) {
+  if (B == 0) return 0;
+  int Cp = padded_channels(g.C);
+  if (prep) B200_TRY(conv_tiled_dx_prep(ctx, g, W, scratch));
   if (g.C <= 4 && Cp == 4 && fewout_smem(g.OC, g.KH, g.KW) <= ctx->smem_optin) {
     // few input channels: dX is a convolution with few OUTPUT channels
     FewOutCfg f{};

@@ -45,7 +45,8 @@ struct Layer {
   bool bwd_done_by_next = false; // relu: its gradient is produced by the pooling layer after it
   // 2x2 max-pool next to a tensor-core convolution: the pooling kernels also write the tall split
   // copies that convolution reads (its input in the forward pass, its dY in the backward pass)
-  cudaEvent_t ev_prep = nullptr;  // tensor-core convolution: its filter matrices are ready (side stream)
+  cudaEvent_t ev_prep = nullptr;  // convolution: its filter matrices / copies are ready (side stream)
+  bool dx_prep_side = false;      // the FFMA dX filter copy of this step was made beside the forward pass
   int feeds_conv = -1;     // max-pool: convolution layer whose input copy it writes
   int grad_to_conv = -1;   // max-pool: convolution layer whose dY copy it writes
   bool xs_from_pool = false, dys_from_pool = false;  // convolution: copies come from the pooling layers
@@ -57,6 +58,10 @@ struct b200_net {
   b200_ctx *ctx = nullptr;
   int max_batch = 0;
   std::vector<Layer> layers;
+  // a narrow fully-connected layer + softmax output layer run as one kernel per direction:
+  // index of that fully-connected layer (-1: none) and of a relu directly before it (-1: none)
+  int head_fc = -1, head_relu = -1;
+  bool batch_finishes = false;  // B200_NET_BATCH_FINISH=1
   std::vector<OptSegment> segs;  // trainable tensors in update order
   size_t n_params = 0;
   float *params = nullptr, *grads = nullptr, *state0 = nullptr, *state1 = nullptr;
@@ -140,25 +145,38 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
   bool prep_on_side = false;
   if (net->side) {
     cudaStream_t main_stream = ctx->stream;
-    for (size_t i = 0; i < n; ++i) {
-      Layer &L = net->layers[i];
-      if (L.kind != B200_LAYER_CONV || !L.tc.fwd || !L.ev_prep) continue;
-      if (!prep_on_side) {
-        B200_CUDA(cudaEventRecord(net->ev_fork, main_stream));
-        B200_CUDA(cudaStreamWaitEvent(net->side, net->ev_fork, 0));
-        prep_on_side = true;
+    // first what the forward pass waits for (the tensor-core layers' filter matrices), then the
+    // flipped filter copies of FFMA dX passes, which only the backward pass reads
+    for (int pass = 0; pass < 2; ++pass) {
+      for (size_t i = 0; i < n; ++i) {
+        Layer &L = net->layers[i];
+        if (L.kind != B200_LAYER_CONV || !L.ev_prep) continue;
+        const bool dx_copy = L.tiled && !L.tc.dx && L.g.OW <= 64 && L.wt_dx && (i > 0 || net->input_grad);
+        if (pass == 0) L.dx_prep_side = false;
+        if (pass == 0 ? !L.tc.fwd : !dx_copy) continue;
+        if (!prep_on_side) {
+          B200_CUDA(cudaEventRecord(net->ev_fork, main_stream));
+          B200_CUDA(cudaStreamWaitEvent(net->side, net->ev_fork, 0));
+          prep_on_side = true;
+        }
+        ctx->stream = net->side;
+        int rc;
+        if (pass == 0) {
+          rc = conv_tc_prep(ctx, L.g, net->params + L.w_off, L.tc_wt_fwd, L.tc.dx ? L.tc_wt_dx : nullptr);
+        } else {
+          rc = conv_tiled_dx_prep(ctx, L.g, net->params + L.w_off, L.wt_dx);
+          L.dx_prep_side = rc == 0;
+        }
+        ctx->stream = main_stream;
+        B200_TRY(rc);
+        B200_CUDA(cudaEventRecord(L.ev_prep, net->side));
       }
-      ctx->stream = net->side;
-      int rc = conv_tc_prep(ctx, L.g, net->params + L.w_off, L.tc_wt_fwd, L.tc.dx ? L.tc_wt_dx : nullptr);
-      ctx->stream = main_stream;
-      B200_TRY(rc);
-      B200_CUDA(cudaEventRecord(L.ev_prep, net->side));
     }
   }
   for (size_t i = 0; i < n; ++i) {
     Layer &L = net->layers[i];
-    if (L.skipped) {
-      in = L.out;  // already written by the previous layer's epilogue
+    if (L.skipped || (net->head_fc >= 0 && i == n - 1)) {
+      in = L.out;  // already written by the previous layer's kernel
       continue;
     }
     float *dst = L.fused_act ? net->layers[i + 1].out : L.out;
@@ -169,7 +187,7 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
         if (L.tc.fwd) {
           if (!L.xs_from_pool) B200_TRY(conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs));
           // the dX pass of this step reads the same weights: both filter matrices in one launch
-          if (prep_on_side && L.ev_prep)
+          if (prep_on_side && L.ev_prep && L.tc.fwd)
             B200_CUDA(cudaStreamWaitEvent(ctx->stream, L.ev_prep, 0));
           else
             B200_TRY(conv_tc_prep(ctx, L.g, W, L.tc_wt_fwd, L.tc.dx ? L.tc_wt_dx : nullptr));
@@ -182,7 +200,10 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
           B200_TRY(conv_general_fwd(ctx, L.g, in, W, b, dst, B, L.fused_act));
         break;
       case B200_LAYER_FC:
-        B200_TRY(fc_fwd(ctx, L.fc_in, L.fc_out, in, W, b, dst, B, L.fused_act, L.fc_scratch));
+        if ((int)i == net->head_fc)
+          B200_TRY(fc_softmax_fwd(ctx, L.fc_in, L.fc_out, in, W, b, dst, net->layers[n - 1].out, B));
+        else
+          B200_TRY(fc_fwd(ctx, L.fc_in, L.fc_out, in, W, b, dst, B, L.fused_act, L.fc_scratch));
         break;
       case B200_LAYER_MAXPOOL:
         if (L.feeds_conv >= 0) {
@@ -207,6 +228,12 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
     }
     in = dst;
   }
+  if (prep_on_side) {
+    // everything the side stream was given in this pass ends here (a filter copy made for the
+    // backward pass has no reader in the forward pass), so a forward pass alone leaves no open branch
+    B200_CUDA(cudaEventRecord(net->ev_join, net->side));
+    B200_CUDA(cudaStreamWaitEvent(ctx->stream, net->ev_join, 0));
+  }
   net->cur_batch = B;
   net->cur_x = x;
   return 0;
@@ -219,7 +246,16 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
   Layer &last = net->layers[n - 1];
   // a softmax output layer: loss gradient and softmax gradient in one launch
   const bool tail_fused = net->fuse && last.kind == B200_LAYER_SOFTMAX && n >= 2;
-  if (tail_fused)
+  if (net->head_fc >= 0) {
+    // loss gradient, softmax gradient, the narrow layer's dX and the gradient of a relu in front of
+    // it in one launch; the layer's dW / db follow in the loop below
+    Layer &F = net->layers[net->head_fc];
+    const int first = net->head_relu >= 0 ? net->head_relu : net->head_fc;  // first layer the kernel covers
+    float *target = first == 0 ? (net->input_grad ? net->in_grad : nullptr) : net->layers[first - 1].grad;
+    B200_TRY(fc_softmax_loss_bwd(ctx, loss_kind, F.fc_in, F.fc_out, last.out, t, net->params + F.w_off,
+                                 net->head_relu >= 0 ? net->layers[net->head_relu].out : nullptr, last.grad, F.grad,
+                                 target, B));
+  } else if (tail_fused)
     B200_TRY(softmax_loss_bwd(ctx, loss_kind, last.out, t, last.grad, net->layers[n - 2].grad, (int)last.out_dim, B));
   else
     B200_TRY(loss_grad(ctx, loss_kind, last.out, t, last.grad, (int)last.out_dim, B));
@@ -239,6 +275,20 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
     side_used = true;
     return 0;
   };
+  // The finishing passes of the tensor-core dW kernels (partial rows -> gradient in the reference
+  // layout) can be collected and launched together (before the gradients leave for the other
+  // replicas, and at the end of the pass) instead of after each dW kernel: B200_NET_BATCH_FINISH=1.
+  // Measured slower on the benchmark step (0.335 against 0.323 ms: the one launch then shares the SMs
+  // with the first layer's dX), so each pass follows its kernel by default.
+  std::vector<DwFinishArgs> finishes;
+  auto flush_finishes = [&]() -> int {
+    if (finishes.empty()) return 0;
+    ctx->stream = net->side;  // they were produced there (fork() ran)
+    int rc = dw_finish_many(ctx, finishes.data(), (int)finishes.size());
+    ctx->stream = main_stream;
+    finishes.clear();
+    return rc;
+  };
   for (int i = tail_fused ? n - 2 : n - 1; i >= 0 && rc_side == 0; --i) {
     Layer &L = net->layers[i];
     const float *in = i == 0 ? net->cur_x : net->layers[i - 1].out;
@@ -246,7 +296,10 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
     const float *W = net->params + L.w_off;
     float *dW = net->grads + L.w_off;
     float *db = L.b_len ? net->grads + L.b_off : nullptr;
-    const bool can_fork = net->side != nullptr && din != nullptr;
+    if (net->head_fc >= 0 && i == net->head_relu) continue;  // its gradient came with the head kernel
+    const bool head = i == net->head_fc && net->head_fc >= 0;
+    if (head) din = nullptr;                                  // so did this layer's dX
+    const bool can_fork = net->side != nullptr && (din != nullptr || head);
     switch (L.kind) {
       case B200_LAYER_CONV: {
         bool tiled_bwd = L.tiled && L.g.OW <= 64;
@@ -256,15 +309,21 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
         // dW first: its launch precedes the dX launch, so a one-block-per-SM dW kernel is resident
         // when the small blocks of an FFMA dX arrive and both share the SMs
         const bool forked = can_fork && (L.tc.dw || L.tc.dw_small);
+        const bool batch_fin = forked && net->batch_finishes;
         if (forked) B200_TRY(fork());
         if (L.tc.dw) {
           if (!L.tc.fwd && !L.xs_from_pool) rc_side = conv_tc_tall_x(ctx, L.g, in, B, L.tc_xs);
           int splits = 0;
           if (!rc_side) rc_side = conv_tc_dw(ctx, L.g, L.tc_xs, L.tc_dys, B, L.tc_part, &splits);
+          DwFinishArgs later;
           if (!rc_side)
-            rc_side = conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db);
+            rc_side = conv_tc_dw_finish(ctx, L.g, L.tc_part, splits, dW, 0, db ? L.tc_bsum : nullptr, B, db,
+                                        batch_fin ? &later : nullptr);
+          if (!rc_side && batch_fin) finishes.push_back(later);
         } else if (L.tc.dw_small) {
-          rc_side = conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0);
+          DwFinishArgs later;
+          rc_side = conv_dw_small(ctx, L.g, in, L.grad, B, L.tc_small_part, dW, db, 0, batch_fin ? &later : nullptr);
+          if (!rc_side && batch_fin) finishes.push_back(later);
         } else if (tiled_bwd) {
           int splits = 0;
           rc_side = conv_tiled_dw_partials(ctx, L.g, in, L.grad, B, L.dw_part, &splits);
@@ -285,8 +344,12 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
         if (din) {
           if (tc_dx)
             B200_TRY(conv_tc_dx(ctx, L.g, L.tc_dys, W, din, B, L.tc_wt_dx, L.tc.fwd ? 0 : 1));
-          else if (tiled_bwd)
-            B200_TRY(conv_tiled_dx(ctx, L.g, W, L.grad, din, B, L.wt_dx));
+          else if (tiled_bwd) {
+            // the filter copy was made beside the forward pass (same weights: nothing updates
+            // them between the two passes of a step)
+            if (L.dx_prep_side) B200_CUDA(cudaStreamWaitEvent(ctx->stream, L.ev_prep, 0));
+            B200_TRY(conv_tiled_dx(ctx, L.g, W, L.grad, din, B, L.wt_dx, L.dx_prep_side ? 0 : 1));
+          }
           else
             B200_TRY(conv_general_dx(ctx, L.g, W, L.grad, din, B));
         }
@@ -313,14 +376,13 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
           const bool cv_din = L.grad_to_conv > 0 || net->input_grad;
           const bool chw_read = !Cv.tc.dw || (cv_din && !Cv.tc.dx) || net->keep_layer_grads;
           B200_TRY(conv_tc_tall_dy_unpool(ctx, Cv.g, L.grad, L.argmax,
-                                          L.relu_bwd_fused ? net->layers[i - 1].out : nullptr,
+                                          L.relu_bwd_fused ? L.out : nullptr,
                                           chw_read ? Cv.grad : nullptr, B, Cv.tc_dys,
                                           Cv.tc.dw && Cv.b_len ? Cv.tc_bsum : nullptr));
         } else if (L.relu_bwd_fused) {
           // the relu before this layer was folded into the producer's epilogue: apply
           // its gradient mask here and write straight into the producer's gradient
-          B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, net->layers[i - 2].grad, B,
-                               net->layers[i - 1].out));
+          B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, net->layers[i - 2].grad, B, L.out));
         } else if (din) {
           B200_TRY(maxpool_bwd(ctx, L.pd, L.grad, L.argmax, din, B));
         }
@@ -341,6 +403,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
       default: B200_REQUIRE(false, "net_backward: unknown layer kind %d", L.kind);
     }
     if (peer_in_step && i == net->peer_early_layer && rc_side == 0 && net->comm) {
+      B200_TRY(flush_finishes());
       // every weight gradient of layers i.. has been issued (main or side stream): send them to
       // the peers now, from a third stream, while the remaining layers still compute
       B200_CUDA(cudaEventRecord(net->ev_comm_main, main_stream));
@@ -358,6 +421,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
     }
   }
   ctx->stream = main_stream;
+  if (rc_side == 0) B200_TRY(flush_finishes());
   if (side_used) {  // the optimizer (or the caller's all-reduce) follows on the main stream
     B200_CUDA(cudaEventRecord(net->ev_join, net->side));
     B200_CUDA(cudaStreamWaitEvent(main_stream, net->ev_join, 0));
@@ -440,6 +504,7 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
   net->max_batch = max_batch;
   net->layers.resize(n_layers);
   if (const char *e = getenv("B200_NET_NO_FUSE")) net->fuse = !(e[0] == '1');
+  if (const char *e = getenv("B200_NET_BATCH_FINISH")) net->batch_finishes = e[0] == '1';
   if (const char *e = getenv("B200_NET_NO_GRAPH")) net->use_graph = !(e[0] == '1');
   if (const char *e = getenv("B200_NET_KEEP_GRADS")) net->keep_layer_grads = e[0] == '1';
   if (!getenv("B200_NET_NO_SIDE")) {
@@ -550,6 +615,15 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
       }
     }
   }
+  // narrow fully-connected layer -> softmax output layer: one kernel per direction
+  if (net->fuse && n_layers >= 2) {
+    Layer &S = net->layers[n_layers - 1];
+    Layer &F = net->layers[n_layers - 2];
+    if (S.kind == B200_LAYER_SOFTMAX && F.kind == B200_LAYER_FC && fc_softmax_fusable(F.fc_in, F.fc_out)) {
+      net->head_fc = n_layers - 2;
+      if (n_layers >= 3 && net->layers[n_layers - 3].kind == B200_LAYER_RELU) net->head_relu = n_layers - 3;
+    }
+  }
   // 2x2 max-pool beside a tensor-core convolution: fuse the tall conversions into the pooling kernels
   if (net->fuse) {
     for (int i = 0; i < n_layers; ++i) {
@@ -610,7 +684,7 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
     }
     if (L.kind == B200_LAYER_CONV && L.tc.dw_small)
       B200_TRY(net_alloc((void **)&L.tc_small_part, conv_dw_small_floats(ctx, L.g, max_batch) * f));
-    if (L.kind == B200_LAYER_CONV && L.tc.fwd && net->side)
+    if (L.kind == B200_LAYER_CONV && (L.tc.fwd || L.tiled) && net->side)
       B200_CUDA(cudaEventCreateWithFlags(&L.ev_prep, cudaEventDisableTiming));
     if (L.kind == B200_LAYER_CONV && (L.tc.fwd || L.tc.dx || L.tc.dw)) {
       if (L.tc.fwd || L.tc.dw)

@@ -45,7 +45,7 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
 struct PeerArgs {
   float *grads;              // local bucket, n floats: read, then overwritten with the sum
   float *const *bases;       // [world] base of every rank's buffer as mapped here
-  const unsigned *step;      // number of reductions done so far
+  unsigned *step;            // [0] number of reductions done so far, [1] blocks of the summing kernel that ended
   int *err;
   int rank, world;
   long long n, npad;         // floats; npad is a multiple of 4
@@ -104,6 +104,20 @@ __global__ void __launch_bounds__(PR_THREADS) peer_push_kernel(const PeerArgs a,
   if (regions & 1) push_and_signal(a, 0, half, b);
 }
 
+// the last block of the summing kernel to end closes this use of the buffer half: every block has
+// read the step number by then
+__device__ __forceinline__ void sum_block_done(const PeerArgs &a) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.step + 1, 1u) == gridDim.x - 1) {
+      a.step[1] = 0u;
+      __threadfence();
+      a.step[0] += 1u;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(PR_THREADS) peer_sum_kernel(const PeerArgs a, int push_late) {
   __shared__ int s_fail;
   const int tid = threadIdx.x, b = blockIdx.x;
@@ -141,6 +155,7 @@ __global__ void __launch_bounds__(PR_THREADS) peer_sum_kernel(const PeerArgs a, 
   __syncthreads();
   if (s_fail) {
     if (tid == 0 && a.err) atomicExch(a.err, 7);
+    sum_block_done(a);
     return;
   }
   // sum the slots in rank order; the peers' stores sit in this GPU's memory / L2, not in this SM's L1
@@ -166,9 +181,8 @@ __global__ void __launch_bounds__(PR_THREADS) peer_sum_kernel(const PeerArgs a, 
       }
     }
   }
+  sum_block_done(a);
 }
-
-__global__ void peer_advance_kernel(unsigned *step) { *step += 1u; }
 
 long long pr_npad(long long n) { return (n + 3) / 4 * 4; }
 
@@ -225,8 +239,8 @@ int peer_reduce_init(b200_ctx *ctx, PeerReduce *pr, long long n, long long split
   pr->timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1000000ull;
   B200_CUDA(cudaMalloc(&pr->bases_dev, sizeof(float *) * world));
   B200_CUDA(cudaMemcpy(pr->bases_dev, bases, sizeof(float *) * world, cudaMemcpyHostToDevice));
-  B200_CUDA(cudaMalloc(&pr->step_dev, sizeof(unsigned)));
-  B200_CUDA(cudaMemset(pr->step_dev, 0, sizeof(unsigned)));
+  B200_CUDA(cudaMalloc(&pr->step_dev, 2 * sizeof(unsigned)));
+  B200_CUDA(cudaMemset(pr->step_dev, 0, 2 * sizeof(unsigned)));
   (void)ctx;
   return 0;
 }
@@ -262,8 +276,6 @@ int peer_reduce_push_all(b200_ctx *ctx, const PeerReduce *pr, float *grads) {
 int peer_reduce_finish(b200_ctx *ctx, const PeerReduce *pr, float *grads, int late_pushed) {
   B200_TRY(check_run(pr, grads));
   peer_sum_kernel<<<PR_CHUNKS, PR_THREADS, 0, ctx->stream>>>(make_args(ctx, pr, grads), late_pushed ? 0 : 1);
-  B200_LAUNCHED();
-  peer_advance_kernel<<<1, 1, 0, ctx->stream>>>(pr->step_dev);
   B200_LAUNCHED();
   return 0;
 }

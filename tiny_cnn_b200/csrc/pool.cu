@@ -110,16 +110,18 @@ __global__ void maxpool2x2_fwd_kernel(int in_w, int in_h, int out_w, int out_h, 
   }
 }
 
-// Gradient of the same layer; with `relu_y` != nullptr the gradient of a relu
-// that precedes the pooling layer is applied on the way (relu_y is that relu's
-// output, i.e. this layer's input): din = (y > 0) ? pooled gradient : 0.
+// Gradient of the same layer; with `pooled_y` != nullptr (this layer's forward output) the
+// gradient of a relu that precedes the pooling layer is applied on the way:
+// din = (y > 0) ? pooled gradient : 0 at the window's winner, where the relu's output y equals the
+// pooled value, and 0 at the other three positions either way -- so the mask needs one pooled
+// value per window instead of the relu's whole output.
 // I = unsigned when every index fits 32 bits (the usual case: the 64-bit divisions of the general
 // form cost more than the memory traffic of this kernel), long long otherwise.
 template <typename I>
 __global__ void maxpool2x2_bwd_kernel(int in_w, int in_h, int out_w, int out_h, long long planes,
                                       const float *__restrict__ dout,
                                       const int32_t *__restrict__ argmax,
-                                      const float *__restrict__ relu_y, float *__restrict__ din,
+                                      const float *__restrict__ pooled_y, float *__restrict__ din,
                                       int in_c) {
   const I ow2 = (I)(out_w >> 1), oh = (I)out_h, ic = (I)in_c;
   const I total = (I)planes * oh * ow2;
@@ -134,6 +136,11 @@ __global__ void maxpool2x2_bwd_kernel(int in_w, int in_h, int out_w, int out_h, 
     const I o = (plane * oh + oy) * (I)out_w + 2 * xp;
     float2 g = *reinterpret_cast<const float2 *>(dout + o);
     int2 am = *reinterpret_cast<const int2 *>(argmax + o);
+    if (pooled_y) {
+      const float2 py = *reinterpret_cast<const float2 *>(pooled_y + o);
+      g.x = py.x > 0.f ? g.x : 0.f;
+      g.y = py.y > 0.f ? g.y : 0.f;
+    }
     int base = (in_h * c + 2 * (int)oy) * in_w + 4 * (int)xp;
     float4 a, b;
     a.x = am.x == base ? g.x : 0.f;
@@ -145,18 +152,6 @@ __global__ void maxpool2x2_bwd_kernel(int in_w, int in_h, int out_w, int out_h, 
     b.z = am.y == base + in_w + 2 ? g.y : 0.f;
     b.w = am.y == base + in_w + 3 ? g.y : 0.f;
     const I ioff = (plane * (I)in_h + 2 * oy) * (I)in_w + 4 * xp;
-    if (relu_y) {
-      float4 ya = *reinterpret_cast<const float4 *>(relu_y + ioff);
-      float4 yb = *reinterpret_cast<const float4 *>(relu_y + ioff + in_w);
-      a.x = ya.x > 0.f ? a.x : 0.f;
-      a.y = ya.y > 0.f ? a.y : 0.f;
-      a.z = ya.z > 0.f ? a.z : 0.f;
-      a.w = ya.w > 0.f ? a.w : 0.f;
-      b.x = yb.x > 0.f ? b.x : 0.f;
-      b.y = yb.y > 0.f ? b.y : 0.f;
-      b.z = yb.z > 0.f ? b.z : 0.f;
-      b.w = yb.w > 0.f ? b.w : 0.f;
-    }
     *reinterpret_cast<float4 *>(din + ioff) = a;
     *reinterpret_cast<float4 *>(din + ioff + in_w) = b;
   }
@@ -312,22 +307,22 @@ int maxpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, float *
 bool maxpool_can_fuse_relu(const b200_pool_desc &d) { return pool2x2_fast(d); }
 
 int maxpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *dout, const int32_t *argmax,
-                float *din, int B, const float *relu_y) {
+                float *din, int B, const float *pooled_y) {
   B200_TRY(check_pool(d));
   long long total = (long long)B * d.in_c * d.in_h * d.in_w;
   if (total == 0) return 0;
   bool fast = pool2x2_fast(d) && aligned16(dout) && aligned16(din) && aligned16(argmax) &&
-              (!relu_y || aligned16(relu_y));
-  B200_REQUIRE(fast || !relu_y, "maxpool_bwd: relu fusion needs the 2x2/2 aligned path");
+              (!pooled_y || aligned16(pooled_y));
+  B200_REQUIRE(fast || !pooled_y, "maxpool_bwd: relu fusion needs the 2x2/2 aligned path");
   if (fast) {
     long long planes = (long long)B * d.in_c;
     long long work = planes * d.out_h * (d.out_w / 2);
     if (planes * d.in_h * d.in_w < (1LL << 31))
       maxpool2x2_bwd_kernel<unsigned><<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
-        d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, relu_y, din, d.in_c);
+        d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, pooled_y, din, d.in_c);
     else
       maxpool2x2_bwd_kernel<long long><<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
-        d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, relu_y, din, d.in_c);
+        d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, pooled_y, din, d.in_c);
     B200_LAUNCHED();
     return 0;
   }
