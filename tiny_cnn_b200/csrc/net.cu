@@ -113,7 +113,7 @@ struct b200_net {
       entries.clear();
     }
   } slots[2];
-  static constexpr size_t kGraphsPerSlot = 4;
+  static constexpr size_t kGraphsPerSlot = 8;
   bool use_graph = true;
 };
 
