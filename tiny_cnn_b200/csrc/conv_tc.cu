@@ -395,6 +395,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   conv_tc_kernel(const __grid_constant__ CUtensorMap in_hi, const __grid_constant__ CUtensorMap in_lo,
                  const __grid_constant__ CUtensorMap f_hi, const __grid_constant__ CUtensorMap f_lo,
                  const TcConvArgs a) {
+  const long long t_entry = tc_clock();  // 0 unless built with -DB200_TC_TIMING
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   constexpr uint32_t HB = TCV_HALO_W * TCV_TILE_ROWS * 128u;  // one haloed tile (hi or lo): 32 KiB
@@ -473,7 +474,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
     // ---- MMA issuer -----------------------------------------------------------------------
     const uint32_t idesc = umma_idesc_tf32(128, Ng);
     uint32_t u = 0, f = 0, it = 0;
-    long long w_acc = 0, w_halo = 0, w_filt = 0, t_begin = tc_clock(), tq;
+    long long w_acc = 0, w_halo = 0, w_filt = 0, t_begin = tc_clock(), tq, t_first = 0;
     for (int unit = blockIdx.x; unit < nunits && !failed; unit += gridDim.x, ++it) {
       const uint32_t ab = it % a.nb, ause = it / a.nb;
       tq = tc_clock();
@@ -492,6 +493,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
           break;
         }
         w_halo += tc_clock() - tq;
+        if (t_first == 0) t_first = tc_clock() - t_entry;  // kernel entry -> first operand tile in place
         tc_fence_after();
         const uint32_t hbase = smem_u32(halo + (size_t)hb * 2 * HB);
         for (int kx = 0; kx < a.KW && !failed; ++kx) {
@@ -535,6 +537,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
       d[1] = w_acc;
       d[2] = w_halo;
       d[3] = w_filt;
+      d[6] = t_first;
     }
   } else if (warp < 4) {
     // ---- epilogue: sum the KH row-shifted column blocks, bias, activation, store -------------
@@ -644,6 +647,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
       long long *d = a.dbg + (size_t)blockIdx.x * 8;
       d[4] = tc_clock() - t_begin;
       d[5] = w_full;
+      d[7] = tc_clock() - t_entry;  // kernel entry -> end of the last epilogue
     }
   }
   if (failed && a.err) atomicExch(a.err, 3);
@@ -981,8 +985,8 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, int Hin, l
       for (int k = 0; k < 8; ++k) s[k] += (double)h[(size_t)i * 8 + k] / grid;
     fprintf(stderr,
             "[tc-timing] tiles %d grid %d N %d: mma total %.0f clk, waits acc %.0f halo %.0f filt %.0f | "
-            "epilogue total %.0f, wait full %.0f\n",
-            a.ntiles, grid, KH * p.gs, s[0], s[1], s[2], s[3], s[4], s[5]);
+            "epilogue total %.0f, wait full %.0f | entry -> first tile in place %.0f, entry -> last epilogue done %.0f\n",
+            a.ntiles, grid, KH * p.gs, s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7]);
   }
 #endif
   return 0;
