@@ -38,7 +38,7 @@ namespace {
 constexpr int TCV_THREADS = 192;
 constexpr int TCV_TILE_ROWS = 16;  // tall rows per output tile
 constexpr int TCV_TILE_COLS = 8;   // columns per output tile (one group of 8 MMA rows)
-constexpr int TCV_HALO_W = 16;     // columns of the haloed tile in shared memory
+constexpr int TCV_HALO_W = 16;     // most columns a haloed tile has in shared memory (8 + KW - 1, KW <= 8 ... 9)
 
 // geometry of the tall tensors of one convolution
 struct TallGeom {
@@ -377,6 +377,7 @@ struct TcConvArgs {
   int KH, KW, pad_t, pad_l;
   int tiles_x, ntiles;
   int act;
+  int hw;              // columns of the haloed tile in shared memory: 8 + KW - 1
   int nh;              // haloed-tile buffers (1 or 2)
   int nf;              // filter ring stages
   int nb;              // accumulator buffers in tensor memory (1 or 2)
@@ -398,7 +399,7 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
   const long long t_entry = tc_clock();  // 0 unless built with -DB200_TC_TIMING
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  constexpr uint32_t HB = TCV_HALO_W * TCV_TILE_ROWS * 128u;  // one haloed tile (hi or lo): 32 KiB
+  const uint32_t HB = (uint32_t)a.hw * TCV_TILE_ROWS * 128u;  // one haloed tile (hi or lo): 24 KiB for a 5-wide window
   const int Ng = a.KH * a.gs;                                 // MMA width
   const uint32_t FB = (uint32_t)Ng * 128u;                    // one filter tile (hi or lo)
   const int CB = Ng;                                          // accumulator columns per buffer
@@ -513,10 +514,10 @@ __global__ void __launch_bounds__(TCV_THREADS, 1)
               const uint32_t bbase = smem_u32(filt + (size_t)fs * FB);
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) {
-                const uint64_t ahi = umma_desc(abase + k4 * 32, 16, TCV_HALO_W * 128, 2);
+                const uint64_t ahi = umma_desc(abase + k4 * 32, 16, a.hw * 128, 2);
                 const uint64_t b = umma_desc(bbase + k4 * 32, 16, 1024, 2);
                 if (part == 0) {
-                  const uint64_t alo = umma_desc(abase + HB + k4 * 32, 16, TCV_HALO_W * 128, 2);
+                  const uint64_t alo = umma_desc(abase + HB + k4 * 32, 16, a.hw * 128, 2);
                   umma_tf32(d, alo, b, idesc, (slab | kx | k4) != 0);
                   umma_tf32(d, ahi, b, idesc, 1);
                 } else {
@@ -831,12 +832,15 @@ struct TcPlan {
   bool ok;
   int groups, gs;   // output-channel groups and channels per group
   int nh, nf, nb;   // haloed-tile buffers, filter ring stages, accumulator buffers
+  int hw;           // columns of the haloed tile in shared memory
   int tmem_cols;
   size_t smem;
 };
 
-TcPlan conv_tc_plan(const b200_ctx *ctx, int KH, int n_out) {
+// `KW` decides how wide the haloed tile is (8 output columns + KW - 1); groups / gs do not depend on it
+TcPlan conv_tc_plan(const b200_ctx *ctx, int KH, int n_out, int KW = 8) {
   TcPlan p = {};
+  p.hw = 8 + KW - 1 < TCV_HALO_W ? 8 + KW - 1 : TCV_HALO_W;
   const int c16 = pad16(n_out);
   const int gmax = 256 / KH / 16 * 16;
   if (gmax < 16) return p;
@@ -845,13 +849,13 @@ TcPlan conv_tc_plan(const b200_ctx *ctx, int KH, int n_out) {
   const int CB = KH * p.gs;  // accumulator columns of one (tile, group) unit
   p.nb = 2 * CB <= 512 ? 2 : 1;
   p.tmem_cols = pow2_at_least(p.nb * CB);
-  const size_t HB = (size_t)TCV_HALO_W * TCV_TILE_ROWS * 128, stage = (size_t)KH * p.gs * 128;
+  const size_t HB = (size_t)p.hw * TCV_TILE_ROWS * 128, stage = (size_t)KH * p.gs * 128;
   const size_t fixed = 1024 + (size_t)TCV_EPI_FLOATS * 4 + 512;
   for (p.nh = 2; p.nh >= 1; --p.nh) {
     size_t need = fixed + (size_t)p.nh * 2 * HB;
     if (ctx->smem_optin < need + 2 * stage) continue;
     size_t nf = (ctx->smem_optin - need) / stage;
-    p.nf = (int)(nf > 12 ? 12 : nf);
+    p.nf = (int)(nf > 12 ? 12 : nf);  // measured on the CIFAR layers: 3, 4 and 5 stages run the same
     p.smem = need + (size_t)p.nf * stage;
     p.ok = true;
     return p;
@@ -916,7 +920,7 @@ int to_tall(b200_ctx *ctx, const TallSrc &src, int C, int H, int W, int Cp, int 
 int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, int Hin, long long rows, int period,
                    const float *wt, int KH, int KW, int pad_t, int pad_l, int N, float *out, int OH, int OW,
                    const float *bias, int act, int B) {
-  const TcPlan p = conv_tc_plan(ctx, KH, N);
+  const TcPlan p = conv_tc_plan(ctx, KH, N, KW);
   B200_REQUIRE(p.ok, "tensor-core convolution: tiles do not fit (window height %d, %d channels)", KH, N);
   const int slabs = Cp / 32, Ng = KH * p.gs;
   CUtensorMap in_hi, in_lo, f_hi, f_lo;
@@ -926,14 +930,14 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, int Hin, l
   const bool aligned = !no_aligned && Hin == OH && Hin >= 1 && TCV_TILE_ROWS % Hin == 0 && pad_t <= KH - 1;
   const int ipt = aligned ? TCV_TILE_ROWS / Hin : 1;
   if (aligned) {
-    B200_TRY(make_map_4d(&in_hi, tall, Cp, Win, Hin, B, (uint64_t)period * Win * Cp, 32, TCV_HALO_W, Hin, ipt,
+    B200_TRY(make_map_4d(&in_hi, tall, Cp, Win, Hin, B, (uint64_t)period * Win * Cp, 32, p.hw, Hin, ipt,
                          CU_TENSOR_MAP_SWIZZLE_128B));
-    B200_TRY(make_map_4d(&in_lo, tall + one, Cp, Win, Hin, B, (uint64_t)period * Win * Cp, 32, TCV_HALO_W, Hin,
+    B200_TRY(make_map_4d(&in_lo, tall + one, Cp, Win, Hin, B, (uint64_t)period * Win * Cp, 32, p.hw, Hin,
                          ipt, CU_TENSOR_MAP_SWIZZLE_128B));
   } else {
-    B200_TRY(make_map_3d(&in_hi, tall, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS,
+    B200_TRY(make_map_3d(&in_hi, tall, Cp, Win, rows, 32, p.hw, TCV_TILE_ROWS,
                          CU_TENSOR_MAP_SWIZZLE_128B));
-    B200_TRY(make_map_3d(&in_lo, tall + one, Cp, Win, rows, 32, TCV_HALO_W, TCV_TILE_ROWS,
+    B200_TRY(make_map_3d(&in_lo, tall + one, Cp, Win, rows, 32, p.hw, TCV_TILE_ROWS,
                          CU_TENSOR_MAP_SWIZZLE_128B));
   }
   const size_t frows = (size_t)slabs * KW * p.groups * Ng;
@@ -965,6 +969,7 @@ int launch_conv_tc(b200_ctx *ctx, const float *tall, int Cp, int Win, int Hin, l
   a.nh = p.nh;
   a.nf = p.nf;
   a.nb = p.nb;
+  a.hw = p.hw;
   a.tmem_cols = p.tmem_cols;
   a.dbg = nullptr;
   B200_CUDA(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
