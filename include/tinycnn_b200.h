@@ -362,6 +362,69 @@ B200_API int b200_act_bwd_host(b200_ctx *ctx, int kind, const float *y, const fl
 
 enum { B200_LOSS_MSE = 0, B200_LOSS_CROSS_ENTROPY = 1, B200_LOSS_CROSS_ENTROPY_MULTICLASS = 2 };
 
+/* ------------------------------------------------------------------------- */
+/* Layers between the hot operators: batch normalization, dropout, LRN         */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * batch_normalization_layer::forward_propagation
+ * (tiny_dnn/layers/batch_normalization_layer.h:136-168) on rows of
+ * `channels` x `spatial` values.  train != 0 (net_phase::train): `mean` and
+ * `variance` receive this mini-batch's moments (moments(),
+ * tiny_dnn/util/math_functions.h:25-96: mean = sum / (batch*spatial),
+ * variance = sum (x-mean)^2 / max(1, batch*spatial - 1)); train == 0: they
+ * are read (the layer's moving averages).  `stddev` always receives
+ * sqrt(variance + eps), and y = (x - mean) / stddev.  The sums are formed by
+ * a fixed tree, not in the reference's sample-by-sample order: results agree
+ * with the reference to rounding, not bit for bit.
+ */
+B200_API int b200_batchnorm_fwd(b200_ctx *ctx, int channels, int spatial, float eps, const float *x,
+                                float *mean, float *variance, float *stddev, float *y, int batch,
+                                int train);
+/*
+ * batch_normalization_layer::back_propagation (:94-134):
+ * dx = (dy - mean(dy) - mean(dy*y) * y) / stddev, the means per channel over
+ * batch x spatial; `stddev` as the forward pass left it.
+ */
+B200_API int b200_batchnorm_bwd(b200_ctx *ctx, int channels, int spatial, const float *y,
+                                const float *dy, const float *stddev, float *dx, int batch);
+/* batch_normalization_layer::post_update (:174-180):
+ * mean = momentum*mean + (1-momentum)*mean_cur, the same for the variance. */
+B200_API int b200_batchnorm_post_update(b200_ctx *ctx, int channels, float momentum, float *mean,
+                                        float *variance, const float *mean_cur,
+                                        const float *var_cur);
+B200_API int b200_batchnorm_fwd_host(b200_ctx *ctx, int channels, int spatial, float eps,
+                                     const float *x, float *mean, float *variance, float *stddev,
+                                     float *y, int batch, int train);
+B200_API int b200_batchnorm_bwd_host(b200_ctx *ctx, int channels, int spatial, const float *y,
+                                     const float *dy, const float *stddev, float *dx, int batch);
+
+/*
+ * dropout_layer in the train phase with the mask the caller drew
+ * (tiny_dnn/layers/dropout_layer.h:95-115: the reference draws it from its
+ * host generator inside a parallel loop, so only a mask handed over can
+ * reproduce a run): out = mask * scale * in with scale = 1 / (1 - rate).
+ * The backward pass (:66-84) is the same call on dy with scale = 1 -- the
+ * reference does not scale the gradient.  `n` values, one mask byte each.
+ */
+B200_API int b200_dropout(b200_ctx *ctx, const float *in, const uint8_t *mask, float scale,
+                          float *out, long long n);
+B200_API int b200_dropout_host(b200_ctx *ctx, const float *in, const uint8_t *mask, float scale,
+                               float *out, long long n);
+
+/*
+ * lrn_layer::forward_propagation, norm_region::across_channels
+ * (tiny_dnn/layers/lrn_layer.h:82-143): out = in * (1 + alpha/size * S)^-beta
+ * with S the running sum of squares over a window of `size` channels, updated
+ * in the reference's order.  The reference has no backward pass for this
+ * layer (:96-104 throws "not implemented") and no within-channel form
+ * (:145-149 throws), so neither exists here.
+ */
+B200_API int b200_lrn_fwd(b200_ctx *ctx, const float *in, float *out, int channels, int area, int size,
+                          float alpha, float beta, int batch);
+B200_API int b200_lrn_fwd_host(b200_ctx *ctx, const float *in, float *out, int channels, int area,
+                               int size, float alpha, float beta, int batch);
+
 /*
  * Per-sample loss gradient dE/dy: mse 2/dim*(y-t), cross_entropy
  * (y-t)/(y*(1-y)), multiclass -t/y.  Replaces mse::df / cross_entropy::df /
@@ -479,7 +542,8 @@ enum {
   B200_LAYER_SOFTMAX = 7,
   B200_LAYER_SIGMOID = 8,
   B200_LAYER_LEAKY_RELU = 9, /* act_param = epsilon */
-  B200_LAYER_ELU = 10        /* act_param = alpha   */
+  B200_LAYER_ELU = 10,       /* act_param = alpha   */
+  B200_LAYER_BATCHNORM = 11  /* bn_* fields         */
 };
 
 /* One layer of a network<sequential> (tiny_dnn/nodes.h:268-360). */
@@ -489,6 +553,10 @@ typedef struct b200_layer_spec {
   b200_pool_desc pool;   /* B200_LAYER_MAXPOOL / B200_LAYER_AVGPOOL           */
   int32_t fc_in, fc_out, fc_has_bias; /* B200_LAYER_FC                        */
   float act_param;       /* B200_LAYER_LEAKY_RELU / B200_LAYER_ELU            */
+  /* B200_LAYER_BATCHNORM: batch_normalization_layer(in_spatial_size, in_channels, epsilon,
+   * momentum) (tiny_dnn/layers/batch_normalization_layer.h:59-72) */
+  int32_t bn_channels, bn_spatial;
+  float bn_eps, bn_momentum;
 } b200_layer_spec;
 
 typedef struct b200_net b200_net;
@@ -526,6 +594,20 @@ B200_API float *b200_net_output_ptr(b200_net *net);
  * B200_NET_KEEP_GRADS=1 before b200_net_create to have every gradient here as well. */
 B200_API float *b200_net_layer_out_ptr(b200_net *net, int i);
 B200_API float *b200_net_layer_grad_ptr(b200_net *net, int i);
+
+/*
+ * network::set_netphase (tiny_dnn/network.h:438-442): train != 0 is net_phase::train (batch
+ * normalization layers use the mini-batch's moments and, after every update, move their averages
+ * toward them), 0 is net_phase::test (they use the moving averages).  A new net is in the train
+ * phase, as a new layer object is.  Only batch normalization layers look at it.
+ */
+B200_API int b200_net_set_phase(b200_net *net, int train);
+/*
+ * The moving averages of batch normalization layer `layer` (index into the layer list):
+ * mean_ and variance_ of the reference object, `channels` floats each, host memory.
+ * set != 0 writes them to the device, 0 reads them back.
+ */
+B200_API int b200_net_bn_stats(b200_net *net, int layer, float *mean, float *variance, int set);
 
 /* network::fprop (tiny_dnn/network.h:911-926 -> nodes.h:288-303). */
 B200_API int b200_net_forward(b200_net *net, const float *x, int batch);

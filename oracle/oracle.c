@@ -499,6 +499,119 @@ ORC_API void orc_act_bwd(int kind, const float *y, const float *dy, float *dx, i
   orc_act_param_bwd(kind, act_default_param(kind), y, dy, dx, dim, B);
 }
 
+/* ------------------------------------------------------------------------- */
+/* batch normalization, dropout, local response normalization                  */
+/* ------------------------------------------------------------------------- */
+
+/* moments() (tiny_dnn/util/math_functions.h:25-96): per channel, samples in order, std::accumulate
+   over the spatial positions of each; then the division */
+static void moments_mean(const float *x, int C, int S, int B, float *mean) {
+  for (int j = 0; j < C; ++j) mean[j] = 0.f;
+  for (int i = 0; i < B; ++i)
+    for (int j = 0; j < C; ++j) {
+      float r = mean[j];
+      const float *it = x + ((size_t)i * C + j) * S;
+      for (int k = 0; k < S; ++k) r = r + it[k];
+      mean[j] = r;
+    }
+  const float div = (float)B * S;
+  for (int j = 0; j < C; ++j) mean[j] = mean[j] / div;
+}
+
+static void moments_variance(const float *x, int C, int S, int B, const float *mean, float *var) {
+  for (int j = 0; j < C; ++j) var[j] = 0.f;
+  for (int i = 0; i < B; ++i)
+    for (int j = 0; j < C; ++j) {
+      float r = var[j];
+      const float ex = mean[j];
+      const float *it = x + ((size_t)i * C + j) * S;
+      /* `current + pow(x - ex, float_t{2.0})`: x - ex is formed in float, the square and the addition
+         in double (the C library's pow(double, double) is the overload that unqualified call finds),
+         and std::accumulate stores the sum back into its float accumulator */
+      for (int k = 0; k < S; ++k) r = (float)((double)r + pow((double)(it[k] - ex), 2.0));
+      var[j] = r;
+    }
+  float div = (float)((size_t)B * S) - 1.0f;
+  if (div < 1.0f) div = 1.0f;
+  for (int j = 0; j < C; ++j) var[j] = var[j] / div;
+}
+
+/* batch_normalization_layer::forward_propagation (batch_normalization_layer.h:136-168) */
+ORC_API void orc_batchnorm_fwd(int C, int S, float eps, const float *x, float *mean, float *variance, float *stddev,
+                               float *y, int B, int train) {
+  if (train) {
+    moments_mean(x, C, S, B, mean);
+    moments_variance(x, C, S, B, mean, variance);
+  }
+  for (int j = 0; j < C; ++j) stddev[j] = sqrtf(variance[j] + eps);
+  for (int i = 0; i < B; ++i)
+    for (int j = 0; j < C; ++j) {
+      const float m = mean[j];
+      const float *ip = x + ((size_t)i * C + j) * S;
+      float *op = y + ((size_t)i * C + j) * S;
+      for (int k = 0; k < S; ++k) op[k] = (ip[k] - m) / stddev[j];
+    }
+}
+
+/* batch_normalization_layer::back_propagation (:94-134) */
+ORC_API void orc_batchnorm_bwd(int C, int S, const float *y, const float *dy, const float *stddev, float *dx, int B) {
+  const size_t n = (size_t)B * C * S;
+  float *ddy = (float *)malloc(sizeof(float) * (n ? n : 1));
+  float *mean_ddy = (float *)malloc(sizeof(float) * C), *mean_d = (float *)malloc(sizeof(float) * C);
+  for (size_t i = 0; i < n; ++i) ddy[i] = y[i] * dy[i];
+  moments_mean(ddy, C, S, B, mean_ddy);
+  moments_mean(dy, C, S, B, mean_d);
+  for (int i = 0; i < B; ++i)
+    for (int j = 0; j < C; ++j)
+      for (int k = 0; k < S; ++k) {
+        const size_t idx = ((size_t)i * C + j) * S + k;
+        float v = dy[idx] - mean_d[j] - mean_ddy[j] * y[idx];
+        dx[idx] = v / stddev[j];
+      }
+  free(ddy);
+  free(mean_ddy);
+  free(mean_d);
+}
+
+/* batch_normalization_layer::post_update (:174-180) */
+ORC_API void orc_batchnorm_post_update(int C, float momentum, float *mean, float *variance, const float *mean_cur,
+                                       const float *var_cur) {
+  for (int i = 0; i < C; ++i) {
+    mean[i] = momentum * mean[i] + (1 - momentum) * mean_cur[i];
+    variance[i] = momentum * variance[i] + (1 - momentum) * var_cur[i];
+  }
+}
+
+/* dropout_layer in the train phase with a given mask (dropout_layer.h:95-115); with scale 1 on a
+   gradient it is the backward pass (:66-84) */
+ORC_API void orc_dropout(const float *in, const uint8_t *mask, float scale, float *out, long long n) {
+  for (long long i = 0; i < n; ++i) out[i] = mask[i] * scale * in[i];
+}
+
+/* lrn_layer::forward_across (lrn_layer.h:110-143) */
+ORC_API void orc_lrn_fwd(const float *in, float *out, int C, int area, int size, float alpha, float beta, int B) {
+  float *sq = (float *)malloc(sizeof(float) * area);
+  const float alpha_div_size = alpha / size;
+  for (int n = 0; n < B; ++n) {
+    const float *ip = in + (size_t)n * C * area;
+    float *op = out + (size_t)n * C * area;
+    for (int j = 0; j < area; ++j) sq[j] = 0.f;
+    for (int i = 0; i < size / 2 && i < C; ++i)
+      for (int j = 0; j < area; ++j) sq[j] += ip[(size_t)i * area + j] * ip[(size_t)i * area + j];
+    int head = size / 2;
+    long tail = (long)head - (long)size;
+    for (int i = 0; i < C; ++i, ++head, ++tail) {
+      if (head < C)
+        for (int j = 0; j < area; ++j) sq[j] += ip[(size_t)head * area + j] * ip[(size_t)head * area + j];
+      if (tail >= 0)
+        for (int j = 0; j < area; ++j) sq[j] -= ip[(size_t)tail * area + j] * ip[(size_t)tail * area + j];
+      for (int j = 0; j < area; ++j)
+        op[(size_t)i * area + j] = ip[(size_t)i * area + j] * powf(1.f + alpha_div_size * sq[j], -beta);
+    }
+  }
+  free(sq);
+}
+
 /* mse::df, cross_entropy::df, cross_entropy_multiclass::df
  * (tiny_dnn/lossfunctions/loss_function.h:28-36,120-128,143-150) */
 ORC_API void orc_loss_grad(int kind, const float *y, const float *t, float *dy, int dim, int B) {

@@ -263,6 +263,69 @@ REF_API int ref_act_param_fwd_bwd(int kind, float param, const float *x, float *
   return 0;
 }
 
+// batch_normalization_layer forward (train != 0: this batch's moments come back in mean / variance;
+// else they are the layer's moving averages) and backward; stddev_ is private, so it is returned as
+// sqrt(variance + eps) the way calc_stddev computes it
+REF_API int ref_batchnorm_fwd_bwd(int C, int S, float eps, const float *x, float *mean, float *variance,
+                                  float *stddev, float *y, const float *dy, float *dx, int B, int train) {
+  batch_normalization_layer l(S, C, eps, float_t(0.999), train ? net_phase::train : net_phase::test);
+  if (!train) {
+    l.set_mean(vec_t(mean, mean + C));
+    l.set_variance(vec_t(variance, variance + C));
+  } else {
+    l.update_immidiately(true);  // mean_ / variance_ = this batch's moments, readable through save()
+  }
+  tensor_t tx = to_tensor(x, B, (size_t)C * S), ty(B, vec_t((size_t)C * S));
+  std::vector<tensor_t *> ins = {&tx}, outs = {&ty};
+  l.forward_propagation(ins, outs);
+  from_tensor(ty, y, (size_t)C * S);
+  if (train) {
+    std::ostringstream os;
+    l.save(os, 9);
+    std::istringstream is(os.str());
+    for (int j = 0; j < C; ++j) is >> mean[j];
+    for (int j = 0; j < C; ++j) is >> variance[j];
+  }
+  for (int j = 0; j < C; ++j) stddev[j] = std::sqrt(variance[j] + eps);
+  if (dy && dx) {
+    tensor_t gy = to_tensor(dy, B, (size_t)C * S), gx(B, vec_t((size_t)C * S));
+    std::vector<tensor_t *> gouts = {&gy}, gins = {&gx};
+    l.back_propagation(ins, outs, gouts, gins);
+    from_tensor(gx, dx, (size_t)C * S);
+  }
+  return 0;
+}
+
+// lrn_layer forward, across channels
+REF_API int ref_lrn_fwd(const float *in, float *out, int C, int w, int h, int size, float alpha, float beta, int B) {
+  lrn_layer l(w, h, size, C, alpha, beta, norm_region::across_channels);
+  tensor_t tx = to_tensor(in, B, (size_t)C * w * h), ty(B, vec_t((size_t)C * w * h));
+  std::vector<tensor_t *> ins = {&tx}, outs = {&ty};
+  l.forward_propagation(ins, outs);
+  from_tensor(ty, out, (size_t)C * w * h);
+  return 0;
+}
+
+// dropout_layer forward in the train phase: the mask it drew comes back with the output; then its
+// backward pass on dy
+REF_API int ref_dropout_fwd_bwd(int dim, float rate, const float *in, float *out, uint8_t *mask, const float *dy,
+                                float *dx, int B) {
+  dropout_layer l(dim, rate, net_phase::train);
+  tensor_t tx = to_tensor(in, B, dim), ty(B, vec_t(dim));
+  std::vector<tensor_t *> ins = {&tx}, outs = {&ty};
+  l.forward_propagation(ins, outs);
+  from_tensor(ty, out, dim);
+  for (int n = 0; n < B; ++n) {
+    const std::vector<uint8_t> &m = l.get_mask(n);
+    std::copy(m.begin(), m.end(), mask + (size_t)n * dim);
+  }
+  tensor_t gy = to_tensor(dy, B, dim), gx(B, vec_t(dim));
+  std::vector<tensor_t *> gouts = {&gy}, gins = {&gx};
+  l.back_propagation(ins, outs, gouts, gins);
+  from_tensor(gx, dx, dim);
+  return 0;
+}
+
 // the layers' default constructor arguments
 REF_API int ref_act_fwd_bwd(int kind, const float *x, float *y, const float *dy, float *dx, int dim, int B) {
   return ref_act_param_fwd_bwd(kind, kind == B200_ACT_LEAKY_RELU ? 0.01f : 1.f, x, y, dy, dx, dim, B);

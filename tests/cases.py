@@ -160,6 +160,34 @@ ACT_CASES = {
     "elu_0.7": dict(kind=6, B=3, dim=41, seed=59, scale=2.0, param=0.7),
 }
 
+# batch normalization (channels x spatial rows), local response normalization, dropout
+BATCHNORM_CASES = {
+    "conv_like": dict(C=6, S=49, B=5, eps=1e-5, seed=71, shift=0.7, scale=2.0),
+    "fc_like": dict(C=33, S=1, B=16, eps=1e-3, seed=72, shift=-0.3, scale=0.5),
+    "one_sample": dict(C=4, S=25, B=1, eps=1e-5, seed=73, shift=0.0, scale=1.0),
+    "wide": dict(C=3, S=1024, B=12, eps=1e-5, seed=74, shift=5.0, scale=3.0),
+}
+LRN_CASES = {
+    "alexnet_like": dict(C=8, w=6, h=5, size=5, alpha=1e-4, beta=0.75, B=3, seed=75),
+    "default_params": dict(C=5, w=4, h=4, size=3, alpha=1.0, beta=5.0, B=2, seed=76),
+    "window_wider_than_channels": dict(C=3, w=3, h=3, size=5, alpha=0.5, beta=2.0, B=2, seed=77),
+}
+DROPOUT_CASES = {
+    "half": dict(dim=101, rate=0.5, B=4, seed=78),
+    "light": dict(dim=64, rate=0.2, B=3, seed=79),
+}
+
+
+def gen_batchnorm_inputs(c):
+    rng = np.random.default_rng(c["seed"])
+    n = c["C"] * c["S"]
+    x = (rng.standard_normal((c["B"], n)) * c["scale"] + c["shift"]).astype(np.float32)
+    dy = rng.standard_normal((c["B"], n)).astype(np.float32)
+    run_mean = rng.uniform(-1, 1, c["C"]).astype(np.float32)
+    run_var = rng.uniform(0.5, 2.0, c["C"]).astype(np.float32)
+    return x, dy, run_mean, run_var
+
+
 # quantized forward: x ~ U[-1, 1], W ~ U[-0.5, 0.5] as the benchmark configuration states
 QCONV_CASES = {
     "valid5x5": dict(w=12, h=12, c=4, kw=5, kh=5, oc=6, same=False, bias=True, B=3, seed=61,

@@ -131,6 +131,41 @@ static void ab_layer(const char *name, L &l, size_t B, bool has_weights, unsigne
   }
 }
 
+// lrn_layer has no backward pass in the reference (it throws): forward only
+static void ab_lrn() {
+  std::mt19937 g(41);
+  const size_t B = 3;
+  lrn_layer l(6, 5, 5, 8, float_t(1e-4), float_t(0.75));
+  tensor_t x(B, vec_t(6 * 5 * 8)), ya(B, vec_t(6 * 5 * 8)), yc = ya;
+  fill_normal(x, g);
+  std::vector<tensor_t *> ins = {&x}, outs_a = {&ya}, outs_c = {&yc};
+  l.set_backend_type(core::backend_t::internal);
+  l.forward_propagation(ins, outs_a);
+  l.set_backend_type(core::backend_t::b200);
+  l.forward_propagation(ins, outs_c);
+  close_vec(flat(yc), flat(ya), 1e-4, "lrn across channels forward (set_backend_type)");
+}
+
+// batch normalization in the test phase: the moving averages are read, not this batch's moments
+static void ab_batchnorm_test_phase() {
+  std::mt19937 g(42);
+  const size_t B = 4, C = 5, S = 9;
+  batch_normalization_layer l(S, C, float_t(1e-5), float_t(0.999), net_phase::test);
+  vec_t m(C), v(C);
+  fill_uniform(m, g, -1.f, 1.f);
+  fill_uniform(v, g, 0.5f, 2.f);
+  l.set_mean(m);
+  l.set_variance(v);
+  tensor_t x(B, vec_t(C * S)), ya(B, vec_t(C * S)), yc = ya;
+  fill_normal(x, g);
+  std::vector<tensor_t *> ins = {&x}, outs_a = {&ya}, outs_c = {&yc};
+  l.set_backend_type(core::backend_t::internal);
+  l.forward_propagation(ins, outs_a);
+  l.set_backend_type(core::backend_t::b200);
+  l.forward_propagation(ins, outs_c);
+  close_vec(flat(yc), flat(ya), 1e-4, "batch normalization, test phase forward (set_backend_type)");
+}
+
 static void build_net(network<sequential> &nn, core::backend_t e) {
   using conv = convolutional_layer;
   using pool = max_pooling_layer;
@@ -567,6 +602,12 @@ int main() {
       elu_layer l(37, float_t(0.7));
       ab_layer("elu 0.7 (set_backend_type)", l, 4, false, 13);
     }
+    {
+      batch_normalization_layer l(49, 6);
+      ab_layer("batch normalization, train phase (set_backend_type)", l, 5, false, 14);
+    }
+    ab_batchnorm_test_phase();
+    ab_lrn();
     {
       average_pooling_layer l(28, 28, 6, 2);
       ab_layer("average pooling 2x2 (set_backend_type)", l, 4, true, 10);

@@ -22,7 +22,8 @@ sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 
 import oracle_lib as o  # noqa: E402
-from cases import (ACT_CASES, AVGPOOL_CASES, CONV_CASES, DATA_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,  # noqa: E402
+from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, gen_batchnorm_inputs,  # noqa: E402
+                   ACT_CASES, AVGPOOL_CASES, CONV_CASES, DATA_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,  # noqa: E402
                    QCONV_CASES, QFC_CASES, build_net_specs, conv_desc, dataset_file_bytes, gen_conv_inputs,
                    gen_dataset_bytes, gen_net_data, hyper_for, merge_rows_np, pool_desc, xavier_params, OPT_KINDS,
                    RAGGED_FIT_CASES, gen_ragged_fit_data)
@@ -100,6 +101,38 @@ def main():
                                        o.p(dW), o.p(db), B) == 0
         out[f"avgpool/{name}/y"], out[f"avgpool/{name}/dx"] = y, dx
         put_grads(out, f"avgpool/{name}", dW, db)
+
+    for name, c in BATCHNORM_CASES.items():
+        x, dy, run_mean, run_var = gen_batchnorm_inputs(c)
+        Cn, S, B = c["C"], c["S"], c["B"]
+        y, dx = o.f32(*x.shape), o.f32(*x.shape)
+        mean, var, sd = o.f32(Cn), o.f32(Cn), o.f32(Cn)
+        assert ref.ref_batchnorm_fwd_bwd(Cn, S, c["eps"], o.p(x), o.p(mean), o.p(var), o.p(sd), o.p(y), o.p(dy), o.p(dx),
+                                         B, 1) == 0
+        for k, v in (("y", y), ("dx", dx), ("mean", mean), ("var", var), ("stddev", sd)):
+            out[f"batchnorm/{name}/train/{k}"] = v
+        y2, dx2, sd2 = o.f32(*x.shape), o.f32(*x.shape), o.f32(Cn)
+        m2, v2 = run_mean.copy(), run_var.copy()
+        assert ref.ref_batchnorm_fwd_bwd(Cn, S, c["eps"], o.p(x), o.p(m2), o.p(v2), o.p(sd2), o.p(y2), o.p(dy), o.p(dx2),
+                                         B, 0) == 0
+        for k, v in (("y", y2), ("dx", dx2), ("stddev", sd2)):
+            out[f"batchnorm/{name}/test/{k}"] = v
+
+    for name, c in LRN_CASES.items():
+        rng = np.random.default_rng(c["seed"])
+        x = rng.standard_normal((c["B"], c["C"] * c["w"] * c["h"])).astype(np.float32)
+        y = o.f32(*x.shape)
+        assert ref.ref_lrn_fwd(o.p(x), o.p(y), c["C"], c["w"], c["h"], c["size"], c["alpha"], c["beta"], c["B"]) == 0
+        out[f"lrn/{name}/y"] = y
+
+    for name, c in DROPOUT_CASES.items():
+        rng = np.random.default_rng(c["seed"])
+        x = rng.standard_normal((c["B"], c["dim"])).astype(np.float32)
+        dy = rng.standard_normal((c["B"], c["dim"])).astype(np.float32)
+        y, dx = o.f32(*x.shape), o.f32(*x.shape)
+        mask = np.zeros(x.shape, np.uint8)
+        assert ref.ref_dropout_fwd_bwd(c["dim"], c["rate"], o.p(x), o.p(y), o.p(mask), o.p(dy), o.p(dx), c["B"]) == 0
+        out[f"dropout/{name}/mask"], out[f"dropout/{name}/y"], out[f"dropout/{name}/dx"] = mask, y, dx
 
     for name, c in ACT_CASES.items():
         rng = np.random.default_rng(c["seed"])

@@ -29,6 +29,11 @@ ORACLE_SIGS = {
     "orc_maxpool_bwd": (None, [_pd, _vp, _vp, _vp, _i]),
     "orc_avgpool_fwd": (None, [_pd, _vp, _vp, _vp, _vp, _i]),
     "orc_avgpool_bwd": (None, [_pd, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "orc_batchnorm_fwd": (None, [_i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "orc_batchnorm_bwd": (None, [_i, _i, _vp, _vp, _vp, _vp, _i]),
+    "orc_batchnorm_post_update": (None, [_i, C.c_float, _vp, _vp, _vp, _vp]),
+    "orc_dropout": (None, [_vp, _vp, C.c_float, _vp, C.c_longlong]),
+    "orc_lrn_fwd": (None, [_vp, _vp, _i, _i, _i, C.c_float, C.c_float, _i]),
     "orc_act_param_fwd": (None, [_i, C.c_float, _vp, _vp, _i, _i]),
     "orc_act_param_bwd": (None, [_i, C.c_float, _vp, _vp, _vp, _i, _i]),
     "orc_act_fwd": (None, [_i, _vp, _vp, _i, _i]),
@@ -76,6 +81,9 @@ REF_SIGS = {
     "ref_maxpool_fwd_bwd": (_i, [_pd, _i, _i, _vp, _vp, _vp, _vp, _i]),
     "ref_avgpool_fwd_bwd": (_i, [_pd, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "ref_act_fwd_bwd": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i]),
+    "ref_batchnorm_fwd_bwd": (_i, [_i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "ref_lrn_fwd": (_i, [_vp, _vp, _i, _i, _i, _i, C.c_float, C.c_float, _i]),
+    "ref_dropout_fwd_bwd": (_i, [_i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i]),
     "ref_act_param_fwd_bwd": (_i, [_i, C.c_float, _vp, _vp, _vp, _vp, _i, _i]),
     "ref_loss_grad": (_i, [_i, _vp, _vp, _vp, _i, _i]),
     "ref_opt_steps": (_i, [_i, _oh, _vp, _vp, _sz, _i]),

@@ -13,7 +13,8 @@ import pytest
 import torch
 
 import oracle_lib as o
-from cases import (ACT_CASES, AVGPOOL_CASES, CONV_CASES, FC_CASES, MAXPOOL_CASES, conv_desc,
+from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, gen_batchnorm_inputs,
+                   ACT_CASES, AVGPOOL_CASES, CONV_CASES, FC_CASES, MAXPOOL_CASES, conv_desc,
                    gen_conv_inputs, hyper_for, merge_rows_np, pool_desc)
 from test_oracle import orc_conv
 from tiny_cnn_b200 import ops
@@ -318,6 +319,76 @@ def test_activation_and_loss(ctx, gold, name):
         yy, tt = gold[f"loss/{name}/{loss}/y"], gold[f"loss/{name}/{loss}/t"]
         g = ops.gradient(ctx, loss, dev(yy), dev(tt))
         assert_close(host(g), gold[f"loss/{name}/{loss}/g"], 1e-6, f"{name} loss {loss}")
+
+
+# --------------------------------------------------------------------------- batch norm / lrn / dropout
+@pytest.mark.parametrize("name", list(BATCHNORM_CASES))
+def test_batchnorm(ctx, gold, name):
+    """Forward (train and test phase) and backward against the reference's recorded outputs: 1e-4 / 1e-3
+    (the per-channel sums are formed by a tree here, sample by sample in the reference)."""
+    c = BATCHNORM_CASES[name]
+    x, dy, run_mean, run_var = gen_batchnorm_inputs(c)
+    Cn, S = c["C"], c["S"]
+    y, mean, var, sd = ops.batch_normalization_forward(ctx, Cn, S, c["eps"], dev(x), train=True)
+    assert_close(host(y), gold[f"batchnorm/{name}/train/y"], FWD_TOL, f"{name} train y")
+    assert_close(host(mean), gold[f"batchnorm/{name}/train/mean"], FWD_TOL, f"{name} mean")
+    assert_close(host(var), gold[f"batchnorm/{name}/train/var"], FWD_TOL, f"{name} variance")
+    assert_close(host(sd), gold[f"batchnorm/{name}/train/stddev"], FWD_TOL, f"{name} stddev")
+    dx = ops.batch_normalization_backward(ctx, Cn, S, dev(gold[f"batchnorm/{name}/train/y"]), dev(dy),
+                                          dev(gold[f"batchnorm/{name}/train/stddev"]))
+    assert_close(host(dx), gold[f"batchnorm/{name}/train/dx"], GRAD_TOL, f"{name} train dx")
+    y2, _, _, sd2 = ops.batch_normalization_forward(ctx, Cn, S, c["eps"], dev(x), dev(run_mean), dev(run_var),
+                                                    train=False)
+    assert_close(host(y2), gold[f"batchnorm/{name}/test/y"], FWD_TOL, f"{name} test y")
+    assert np.array_equal(host(sd2), gold[f"batchnorm/{name}/test/stddev"])
+    # host-row entry points give the device entry points' bits
+    yh, mh, vh, sh = (np.empty_like(x), np.empty(Cn, np.float32), np.empty(Cn, np.float32), np.empty(Cn, np.float32))
+    check(ctx.lib.b200_batchnorm_fwd_host(ctx.handle, Cn, S, c["eps"], ptr(x), ptr(mh), ptr(vh), ptr(sh), ptr(yh),
+                                          c["B"], 1))
+    assert np.array_equal(yh, host(y)) and np.array_equal(mh, host(mean)) and np.array_equal(sh, host(sd))
+    dxh = np.empty_like(x)
+    yg, sg = gold[f"batchnorm/{name}/train/y"], gold[f"batchnorm/{name}/train/stddev"]
+    check(ctx.lib.b200_batchnorm_bwd_host(ctx.handle, Cn, S, ptr(yg), ptr(dy), ptr(sg), ptr(dxh), c["B"]))
+    assert np.array_equal(dxh, host(dx))
+
+
+def test_batchnorm_post_update(ctx, oracle):
+    rng = np.random.default_rng(5)
+    mean, var, mc, vc = (rng.standard_normal(7).astype(np.float32) for _ in range(4))
+    dm, dv, dmc, dvc = dev(mean), dev(var), dev(mc), dev(vc)
+    check(ctx.lib.b200_batchnorm_post_update(ctx.handle, 7, 0.999, ptr(dm), ptr(dv), ptr(dmc), ptr(dvc)))
+    oracle.orc_batchnorm_post_update(7, 0.999, o.p(mean), o.p(var), o.p(mc), o.p(vc))
+    assert np.array_equal(host(dm), mean) and np.array_equal(host(dv), var)
+
+
+@pytest.mark.parametrize("name", list(LRN_CASES))
+def test_lrn_forward(ctx, gold, name):
+    c = LRN_CASES[name]
+    rng = np.random.default_rng(c["seed"])
+    x = rng.standard_normal((c["B"], c["C"] * c["w"] * c["h"])).astype(np.float32)
+    y = ops.lrn_forward(ctx, dev(x), c["C"], c["w"] * c["h"], c["size"], c["alpha"], c["beta"])
+    assert_close(host(y), gold[f"lrn/{name}/y"], FWD_TOL, f"lrn {name}")
+    yh = np.empty_like(x)
+    check(ctx.lib.b200_lrn_fwd_host(ctx.handle, ptr(x), ptr(yh), c["C"], c["w"] * c["h"], c["size"], c["alpha"],
+                                    c["beta"], c["B"]))
+    assert np.array_equal(yh, host(y))
+
+
+@pytest.mark.parametrize("name", list(DROPOUT_CASES))
+def test_dropout_with_the_reference_mask(ctx, gold, name):
+    """Bit for bit given the mask the reference drew."""
+    c = DROPOUT_CASES[name]
+    rng = np.random.default_rng(c["seed"])
+    x = rng.standard_normal((c["B"], c["dim"])).astype(np.float32)
+    dy = rng.standard_normal((c["B"], c["dim"])).astype(np.float32)
+    mask = gold[f"dropout/{name}/mask"]
+    scale = float(np.float32(1) / (np.float32(1) - np.float32(c["rate"])))
+    dm = torch.from_numpy(np.ascontiguousarray(mask)).cuda()
+    assert np.array_equal(host(ops.dropout(ctx, dev(x), dm, scale)), gold[f"dropout/{name}/y"])
+    assert np.array_equal(host(ops.dropout(ctx, dev(dy), dm, 1.0)), gold[f"dropout/{name}/dx"])
+    yh = np.empty_like(x)
+    check(ctx.lib.b200_dropout_host(ctx.handle, ptr(x), ptr(np.ascontiguousarray(mask)), scale, ptr(yh), x.size))
+    assert np.array_equal(yh, gold[f"dropout/{name}/y"])
 
 
 def test_loss_value(ctx, oracle):

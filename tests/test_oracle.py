@@ -14,7 +14,8 @@ import numpy as np
 import pytest
 
 import oracle_lib as o
-from cases import (ACT_CASES, AVGPOOL_CASES, CONV_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,
+from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, gen_batchnorm_inputs,
+                   ACT_CASES, AVGPOOL_CASES, CONV_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,
                    QCONV_CASES, QFC_CASES, build_net_specs, conv_desc, gen_conv_inputs, gen_net_data,
                    hyper_for, merge_rows_np, pool_desc, xavier_params)
 from tiny_cnn_b200.ops import conv_params, hyper, maxpool_params
@@ -273,6 +274,62 @@ def test_gold_act_and_loss(oracle, gold, name):
         g = o.f32(B, dim)
         oracle.orc_loss_grad(loss, o.p(yy), o.p(tt), o.p(g), dim, B)
         assert np.array_equal(g, gold[f"loss/{name}/{loss}/g"])
+
+
+@pytest.mark.parametrize("name", list(BATCHNORM_CASES))
+def test_gold_batchnorm(oracle, gold, name):
+    """batch_normalization_layer forward (both phases) and backward: bit for bit."""
+    c = BATCHNORM_CASES[name]
+    x, dy, run_mean, run_var = gen_batchnorm_inputs(c)
+    Cn, S, B = c["C"], c["S"], c["B"]
+    for phase, train in (("train", 1), ("test", 0)):
+        mean, var = (o.f32(Cn), o.f32(Cn)) if train else (run_mean.copy(), run_var.copy())
+        sd, y, dx = o.f32(Cn), o.f32(*x.shape), o.f32(*x.shape)
+        oracle.orc_batchnorm_fwd(Cn, S, c["eps"], o.p(x), o.p(mean), o.p(var), o.p(sd), o.p(y), B, train)
+        oracle.orc_batchnorm_bwd(Cn, S, o.p(y), o.p(dy), o.p(sd), o.p(dx), B)
+        assert np.array_equal(y, gold[f"batchnorm/{name}/{phase}/y"])
+        assert np.array_equal(sd, gold[f"batchnorm/{name}/{phase}/stddev"])
+        assert np.array_equal(dx, gold[f"batchnorm/{name}/{phase}/dx"])
+        if train:
+            assert np.array_equal(mean, gold[f"batchnorm/{name}/train/mean"])
+            assert np.array_equal(var, gold[f"batchnorm/{name}/train/var"])
+
+
+def test_batchnorm_post_update(oracle):
+    """mean = m*mean + (1-m)*mean_cur (batch_normalization_layer.h:174-180)."""
+    rng = np.random.default_rng(5)
+    mean, var, mc, vc = (rng.standard_normal(7).astype(np.float32) for _ in range(4))
+    want_m = np.float32(0.999) * mean + (np.float32(1) - np.float32(0.999)) * mc
+    want_v = np.float32(0.999) * var + (np.float32(1) - np.float32(0.999)) * vc
+    oracle.orc_batchnorm_post_update(7, 0.999, o.p(mean), o.p(var), o.p(mc), o.p(vc))
+    assert np.array_equal(mean, want_m) and np.array_equal(var, want_v)
+
+
+@pytest.mark.parametrize("name", list(LRN_CASES))
+def test_gold_lrn(oracle, gold, name):
+    c = LRN_CASES[name]
+    rng = np.random.default_rng(c["seed"])
+    x = rng.standard_normal((c["B"], c["C"] * c["w"] * c["h"])).astype(np.float32)
+    y = o.f32(*x.shape)
+    oracle.orc_lrn_fwd(o.p(x), o.p(y), c["C"], c["w"] * c["h"], c["size"], c["alpha"], c["beta"], c["B"])
+    assert np.array_equal(y, gold[f"lrn/{name}/y"])
+
+
+@pytest.mark.parametrize("name", list(DROPOUT_CASES))
+def test_gold_dropout(oracle, gold, name):
+    """With the mask the reference drew: forward mask*scale*x, backward mask*dy."""
+    c = DROPOUT_CASES[name]
+    rng = np.random.default_rng(c["seed"])
+    x = rng.standard_normal((c["B"], c["dim"])).astype(np.float32)
+    dy = rng.standard_normal((c["B"], c["dim"])).astype(np.float32)
+    mask = gold[f"dropout/{name}/mask"]
+    assert 0 < mask.mean() < 1
+    scale = np.float32(1) / (np.float32(1) - np.float32(c["rate"]))
+    y, dx = o.f32(*x.shape), o.f32(*x.shape)
+    oracle.orc_dropout(o.p(x), o.p(mask), scale, o.p(y), x.size)
+    oracle.orc_dropout(o.p(dy), o.p(mask), 1.0, o.p(dx), x.size)
+    assert np.array_equal(y, gold[f"dropout/{name}/y"])
+    assert np.array_equal(dx, gold[f"dropout/{name}/dx"])
 
 
 @pytest.mark.parametrize("kind", [0, 1, 2, 3, 4, 5, 6])

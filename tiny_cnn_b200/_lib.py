@@ -132,6 +132,15 @@ SIGNATURES = {
     "b200_act_param_bwd_host": (_i, [_vp, _i, C.c_float, _vp, _vp, _vp, _i, _i]),
     "b200_act_fwd_host": (_i, [_vp, _i, _vp, _vp, _i, _i]),
     "b200_act_bwd_host": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i]),
+    "b200_batchnorm_fwd": (_i, [_vp, _i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "b200_batchnorm_bwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i]),
+    "b200_batchnorm_post_update": (_i, [_vp, _i, C.c_float, _vp, _vp, _vp, _vp]),
+    "b200_batchnorm_fwd_host": (_i, [_vp, _i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "b200_batchnorm_bwd_host": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i]),
+    "b200_dropout": (_i, [_vp, _vp, _vp, C.c_float, _vp, C.c_longlong]),
+    "b200_dropout_host": (_i, [_vp, _vp, _vp, C.c_float, _vp, C.c_longlong]),
+    "b200_lrn_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, C.c_float, C.c_float, _i]),
+    "b200_lrn_fwd_host": (_i, [_vp, _vp, _vp, _i, _i, _i, C.c_float, C.c_float, _i]),
     "b200_loss_grad": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i]),
     "b200_loss_value": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i]),
     "b200_merge_grads": (_i, [_vp, _vp, _i, _sz, _vp]),

@@ -486,6 +486,100 @@ int b200_act_bwd_host(b200_ctx *ctx, int kind, const float *y, const float *dy, 
   return b200_act_param_bwd_host(ctx, kind, act_default_param(kind), y, dy, dx, dim, batch);
 }
 
+// ---- batch normalization / dropout / LRN ------------------------------------------------------
+static int bn_check(b200_ctx *ctx, int channels, int spatial, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(channels > 0 && spatial > 0 && batch >= 0, "batchnorm: bad shape %d x %d, batch %d", channels, spatial,
+               batch);
+  return 0;
+}
+
+int b200_batchnorm_fwd(b200_ctx *ctx, int channels, int spatial, float eps, const float *x, float *mean,
+                       float *variance, float *stddev, float *y, int batch, int train) {
+  B200_TRY(bn_check(ctx, channels, spatial, batch));
+  B200_REQUIRE(x && mean && variance && stddev && y, "batchnorm_fwd: NULL argument");
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, batchnorm_scratch_floats(ctx, channels, batch) * sizeof(float), &scratch));
+  return batchnorm_fwd(ctx, channels, spatial, eps, x, mean, variance, stddev, y, batch, train,
+                       static_cast<float *>(scratch));
+}
+int b200_batchnorm_bwd(b200_ctx *ctx, int channels, int spatial, const float *y, const float *dy,
+                       const float *stddev, float *dx, int batch) {
+  B200_TRY(bn_check(ctx, channels, spatial, batch));
+  B200_REQUIRE(y && dy && stddev && dx, "batchnorm_bwd: NULL argument");
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, batchnorm_scratch_floats(ctx, channels, batch) * sizeof(float), &scratch));
+  return batchnorm_bwd(ctx, channels, spatial, y, dy, stddev, dx, batch, static_cast<float *>(scratch));
+}
+int b200_batchnorm_post_update(b200_ctx *ctx, int channels, float momentum, float *mean, float *variance,
+                               const float *mean_cur, const float *var_cur) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(channels > 0 && mean && variance && mean_cur && var_cur, "batchnorm_post_update: bad argument");
+  return batchnorm_post_update(ctx, channels, momentum, mean, variance, mean_cur, var_cur, nullptr);
+}
+int b200_batchnorm_fwd_host(b200_ctx *ctx, int channels, int spatial, float eps, const float *x, float *mean,
+                            float *variance, float *stddev, float *y, int batch, int train) {
+  B200_TRY(bn_check(ctx, channels, spatial, batch));
+  const size_t n = (size_t)channels * spatial * batch * 4, c = (size_t)channels * 4;
+  // the moments go in (test phase) or come out (train phase); stddev and y always come out
+  HostBuf b[5] = {{x, nullptr, n, nullptr},
+                  {train ? nullptr : mean, train ? mean : nullptr, c, nullptr},
+                  {train ? nullptr : variance, train ? variance : nullptr, c, nullptr},
+                  {nullptr, stddev, c, nullptr},
+                  {nullptr, y, n, nullptr}};
+  B200_TRY(stage_in(ctx, b, 5));
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, batchnorm_scratch_floats(ctx, channels, batch) * sizeof(float), &scratch));
+  B200_TRY(batchnorm_fwd(ctx, channels, spatial, eps, (const float *)b[0].dev, (float *)b[1].dev, (float *)b[2].dev,
+                         (float *)b[3].dev, (float *)b[4].dev, batch, train, static_cast<float *>(scratch)));
+  return stage_out(ctx, b, 5);
+}
+int b200_batchnorm_bwd_host(b200_ctx *ctx, int channels, int spatial, const float *y, const float *dy,
+                            const float *stddev, float *dx, int batch) {
+  B200_TRY(bn_check(ctx, channels, spatial, batch));
+  const size_t n = (size_t)channels * spatial * batch * 4, c = (size_t)channels * 4;
+  HostBuf b[4] = {{y, nullptr, n, nullptr}, {dy, nullptr, n, nullptr}, {stddev, nullptr, c, nullptr},
+                  {nullptr, dx, n, nullptr}};
+  B200_TRY(stage_in(ctx, b, 4));
+  void *scratch = nullptr;
+  B200_TRY(ctx_scratch(ctx, batchnorm_scratch_floats(ctx, channels, batch) * sizeof(float), &scratch));
+  B200_TRY(batchnorm_bwd(ctx, channels, spatial, (const float *)b[0].dev, (const float *)b[1].dev,
+                         (const float *)b[2].dev, (float *)b[3].dev, batch, static_cast<float *>(scratch)));
+  return stage_out(ctx, b, 4);
+}
+
+int b200_dropout(b200_ctx *ctx, const float *in, const uint8_t *mask, float scale, float *out, long long n) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in && mask && out && n >= 0, "dropout: bad argument");
+  return dropout_apply(ctx, in, mask, scale, out, (size_t)n);
+}
+int b200_dropout_host(b200_ctx *ctx, const float *in, const uint8_t *mask, float scale, float *out, long long n) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(n >= 0, "dropout_host: bad argument");
+  HostBuf b[3] = {{in, nullptr, (size_t)n * 4, nullptr}, {mask, nullptr, (size_t)n, nullptr},
+                  {nullptr, out, (size_t)n * 4, nullptr}};
+  B200_TRY(stage_in(ctx, b, 3));
+  B200_TRY(dropout_apply(ctx, (const float *)b[0].dev, (const uint8_t *)b[1].dev, scale, (float *)b[2].dev, (size_t)n));
+  return stage_out(ctx, b, 3);
+}
+
+int b200_lrn_fwd(b200_ctx *ctx, const float *in, float *out, int channels, int area, int size, float alpha, float beta,
+                 int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in && out && channels > 0 && area > 0 && size > 0 && batch >= 0, "lrn_fwd: bad argument");
+  return lrn_across_fwd(ctx, in, out, channels, area, size, alpha, beta, batch);
+}
+int b200_lrn_fwd_host(b200_ctx *ctx, const float *in, float *out, int channels, int area, int size, float alpha,
+                      float beta, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(channels > 0 && area > 0 && size > 0 && batch >= 0, "lrn_fwd_host: bad argument");
+  const size_t n = (size_t)channels * area * batch * 4;
+  HostBuf b[2] = {{in, nullptr, n, nullptr}, {nullptr, out, n, nullptr}};
+  B200_TRY(stage_in(ctx, b, 2));
+  B200_TRY(lrn_across_fwd(ctx, (const float *)b[0].dev, (float *)b[1].dev, channels, area, size, alpha, beta, batch));
+  return stage_out(ctx, b, 2);
+}
+
 int b200_loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy, int dim,
                    int batch) {
   B200_TRY(check_ctx(ctx));

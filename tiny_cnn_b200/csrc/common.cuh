@@ -291,6 +291,18 @@ int avgpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, const f
 int act_fwd(b200_ctx *ctx, int kind, const float *x, float *y, int dim, int B, float param = 0.f);
 int act_bwd(b200_ctx *ctx, int kind, const float *y, const float *dy, float *dx, int dim, int B,
             float param = 0.f);
+// batch normalization, dropout with a host-made mask, local response normalization (norm.cu)
+size_t batchnorm_scratch_floats(const b200_ctx *ctx, int channels, int B);
+int batchnorm_fwd(b200_ctx *ctx, int channels, int spatial, float eps, const float *x, float *mean, float *variance,
+                  float *stddev, float *y, int B, int train, float *scratch);
+int batchnorm_bwd(b200_ctx *ctx, int channels, int spatial, const float *y, const float *dy, const float *stddev,
+                  float *dx, int B, float *scratch);
+int batchnorm_post_update(b200_ctx *ctx, int channels, float momentum, float *mean, float *variance,
+                          const float *mean_cur, const float *var_cur, const int *skip_if);
+int dropout_apply(b200_ctx *ctx, const float *in, const uint8_t *mask, float scale, float *out, size_t n);
+int lrn_across_fwd(b200_ctx *ctx, const float *in, float *out, int channels, int area, int size, float alpha,
+                   float beta, int B);
+
 int loss_grad(b200_ctx *ctx, int kind, const float *y, const float *t, float *dy, int dim, int B);
 // loss gradient (into dy) and the gradient of a softmax layer whose output is y (into dx) in one launch
 int softmax_loss_bwd(b200_ctx *ctx, int loss_kind, const float *y, const float *t, float *dy, float *dx, int dim,

@@ -39,6 +39,11 @@ struct Layer {
   float *fc_scratch = nullptr;  // k-slice partial sums of the small GEMMs
   float *fc_scratch_side = nullptr;  // the same for the dW GEMM when it runs on the side stream
   float act_param = 0.f;  // leaky relu: epsilon; elu: alpha
+  // batch normalization: shape, constants, this batch's moments, stddev, moving averages, slice sums
+  int bn_c = 0, bn_s = 0;
+  float bn_eps = 0.f, bn_momentum = 0.f;
+  float *bn_mean_cur = nullptr, *bn_var_cur = nullptr, *bn_stddev = nullptr, *bn_mean = nullptr, *bn_var = nullptr,
+        *bn_scratch = nullptr;
   int fused_act = 0;      // activation of the NEXT layer folded into this epilogue
   bool skipped = false;   // activation layer folded into the previous layer
   bool relu_bwd_fused = false;   // max-pool: also applies the gradient of the relu before it
@@ -61,6 +66,7 @@ struct b200_net {
   // a narrow fully-connected layer + softmax output layer run as one kernel per direction:
   // index of that fully-connected layer (-1: none) and of a relu directly before it (-1: none)
   int head_fc = -1, head_relu = -1;
+  bool train_phase = true;  // net_phase::train (b200_net_set_phase)
   bool batch_finishes = false;  // B200_NET_BATCH_FINISH=1
   std::vector<OptSegment> segs;  // trainable tensors in update order
   size_t n_params = 0;
@@ -215,6 +221,11 @@ int net_forward_impl(b200_net *net, const float *x, int B) {
         break;
       case B200_LAYER_AVGPOOL:
         B200_TRY(avgpool_fwd(ctx, L.pd, in, W, b, dst, B));
+        break;
+      case B200_LAYER_BATCHNORM:
+        B200_TRY(batchnorm_fwd(ctx, L.bn_c, L.bn_s, L.bn_eps, in, net->train_phase ? L.bn_mean_cur : L.bn_mean,
+                               net->train_phase ? L.bn_var_cur : L.bn_var, L.bn_stddev, dst, B, net->train_phase ? 1 : 0,
+                               L.bn_scratch));
         break;
       case B200_LAYER_RELU:
       case B200_LAYER_TANH:
@@ -390,6 +401,9 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
       case B200_LAYER_AVGPOOL:
         B200_TRY(avgpool_bwd(ctx, L.pd, in, W, L.grad, din, dW, db, 0, B));
         break;
+      case B200_LAYER_BATCHNORM:
+        if (din) B200_TRY(batchnorm_bwd(ctx, L.bn_c, L.bn_s, L.out, L.grad, L.bn_stddev, din, B, L.bn_scratch));
+        break;
       case B200_LAYER_RELU:
       case B200_LAYER_TANH:
       case B200_LAYER_SOFTMAX:
@@ -463,6 +477,11 @@ int net_update_impl(b200_net *net, int opt_kind, const b200_opt_hyper *h) {
   // adam and adamax advance their powers once per update call (optimizer.h:125-126, :165)
   if (opt_kind == B200_OPT_ADAM || opt_kind == B200_OPT_ADAMAX)
     B200_TRY(opt_advance_powers(ctx, net->pow_tab, T, h->b1, h->b2, skip_if));
+  // layer::update_weight ends with post_update() (layer.h:681): batch normalization moves its averages
+  for (Layer &L : net->layers)
+    if (L.kind == B200_LAYER_BATCHNORM)
+      B200_TRY(batchnorm_post_update(ctx, L.bn_c, L.bn_momentum, L.bn_mean, L.bn_var, L.bn_mean_cur, L.bn_var_cur,
+                                     skip_if));
   return 0;
 }
 
@@ -562,6 +581,18 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
       case B200_LAYER_ELU:
         L.in_dim = L.out_dim = prev_out;
         L.act_param = S.act_param;
+        break;
+      case B200_LAYER_BATCHNORM:
+        L.bn_c = S.bn_channels;
+        L.bn_s = S.bn_spatial;
+        L.bn_eps = S.bn_eps;
+        L.bn_momentum = S.bn_momentum;
+        if (L.bn_c <= 0 || L.bn_s <= 0) {
+          set_error("net_create: batch normalization layer %d has shape %d x %d", i, L.bn_c, L.bn_s);
+          delete net;
+          return 2;
+        }
+        L.in_dim = L.out_dim = (size_t)L.bn_c * L.bn_s;
         break;
       default:
         set_error("net_create: unknown layer kind %d at %d", S.kind, i);
@@ -666,6 +697,14 @@ int b200_net_create(b200_ctx *ctx, const b200_layer_spec *specs, int n_layers, i
   for (int i = 0; i < n_layers; ++i) {
     Layer &L = net->layers[i];
     B200_TRY(net_alloc((void **)&L.out, L.out_dim * max_batch * f));
+    if (L.kind == B200_LAYER_BATCHNORM) {
+      float **bufs[5] = {&L.bn_mean_cur, &L.bn_var_cur, &L.bn_stddev, &L.bn_mean, &L.bn_var};
+      for (float **b : bufs) {  // the reference's init(): all zeros
+        B200_TRY(net_alloc((void **)b, (size_t)L.bn_c * f));
+        B200_CUDA(cudaMemset(*b, 0, (size_t)L.bn_c * f));
+      }
+      B200_TRY(net_alloc((void **)&L.bn_scratch, batchnorm_scratch_floats(ctx, L.bn_c, max_batch) * f));
+    }
     B200_TRY(net_alloc((void **)&L.grad, L.out_dim * max_batch * f));
     if (L.kind == B200_LAYER_MAXPOOL)
       B200_TRY(net_alloc((void **)&L.argmax, L.out_dim * max_batch * sizeof(int32_t)));
@@ -712,6 +751,12 @@ int b200_net_destroy(b200_net *net) {
     cudaFree(L.out);
     cudaFree(L.grad);
     cudaFree(L.argmax);
+    cudaFree(L.bn_mean_cur);
+    cudaFree(L.bn_var_cur);
+    cudaFree(L.bn_stddev);
+    cudaFree(L.bn_mean);
+    cudaFree(L.bn_var);
+    cudaFree(L.bn_scratch);
     cudaFree(L.wt_fwd);
     cudaFree(L.wt_dx);
     if (L.ev_prep) cudaEventDestroy(L.ev_prep);
@@ -817,6 +862,31 @@ int b200_net_backward(b200_net *net, const float *t, int loss_kind) {
   B200_REQUIRE(t != nullptr, "net_backward: t is NULL");
   B200_REQUIRE(net->cur_batch > 0, "net_backward: no forward pass to differentiate");
   return net_backward_impl(net, t, loss_kind);
+}
+
+int b200_net_set_phase(b200_net *net, int train) {
+  B200_TRY(check_net(net));
+  net->train_phase = train != 0;
+  return 0;
+}
+
+int b200_net_bn_stats(b200_net *net, int layer, float *mean, float *variance, int set) {
+  B200_TRY(check_net(net));
+  B200_REQUIRE(layer >= 0 && layer < (int)net->layers.size() && net->layers[layer].kind == B200_LAYER_BATCHNORM,
+               "net_bn_stats: layer %d is not a batch normalization layer", layer);
+  B200_REQUIRE(mean && variance, "net_bn_stats: NULL argument");
+  Layer &L = net->layers[layer];
+  const size_t bytes = (size_t)L.bn_c * sizeof(float);
+  cudaStream_t st = net->ctx->stream;
+  if (set) {
+    B200_CUDA(cudaMemcpyAsync(L.bn_mean, mean, bytes, cudaMemcpyHostToDevice, st));
+    B200_CUDA(cudaMemcpyAsync(L.bn_var, variance, bytes, cudaMemcpyHostToDevice, st));
+  } else {
+    B200_CUDA(cudaMemcpyAsync(mean, L.bn_mean, bytes, cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaMemcpyAsync(variance, L.bn_var, bytes, cudaMemcpyDeviceToHost, st));
+  }
+  B200_CUDA(cudaStreamSynchronize(st));
+  return 0;
 }
 
 int b200_net_opt_reset(b200_net *net, int reset_powers) {
@@ -997,6 +1067,13 @@ static std::string step_key(const float *x, const float *t, int batch, int loss_
   if (h) key.append(reinterpret_cast<const char *>(h), sizeof(*h));
   return key;
 }
+// the phase decides which kernels a batch normalization layer launches
+static std::string step_key(const b200_net *net, const float *x, const float *t, int batch, int loss_kind,
+                            int opt_kind, const b200_opt_hyper *h) {
+  std::string key = step_key(x, t, batch, loss_kind, opt_kind, h);
+  key.push_back(net->train_phase ? 't' : 'e');
+  return key;
+}
 
 // Rows a step of network::fit runs on when `nb` new samples are left (network.h:883-926).  The
 // reference copies the new samples over the first rows of its batch buffers in_batch_ / t_batch_
@@ -1026,7 +1103,7 @@ int b200_net_train_step(b200_net *net, const float *x, const float *t, int batch
   B200_REQUIRE(batch >= 1 && batch <= net->max_batch, "net_train_step: batch %d outside 1..%d",
                batch, net->max_batch);
   B200_TRY(ensure_powers(net, opt_kind, h));
-  int r = run_captured(net, 0, step_key(x, t, batch, loss_kind, opt_kind, h), [&]() {
+  int r = run_captured(net, 0, step_key(net, x, t, batch, loss_kind, opt_kind, h), [&]() {
     return step_eager(net, x, t, batch, loss_kind, opt_kind, h);
   });
   net->cur_batch = batch;
@@ -1040,7 +1117,7 @@ int b200_net_forward_backward(b200_net *net, const float *x, const float *t, int
   B200_REQUIRE(x && t, "net_forward_backward: NULL argument");
   B200_REQUIRE(batch >= 1 && batch <= net->max_batch,
                "net_forward_backward: batch %d outside 1..%d", batch, net->max_batch);
-  int r = run_captured(net, 1, step_key(x, t, batch, loss_kind, -1, nullptr), [&]() {
+  int r = run_captured(net, 1, step_key(net, x, t, batch, loss_kind, -1, nullptr), [&]() {
     B200_TRY(net_forward_impl(net, x, batch));
     return net_backward_impl(net, t, loss_kind);
   });

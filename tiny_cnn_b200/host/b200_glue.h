@@ -213,6 +213,48 @@ inline bool activation_grad_op(const std::string &type, float param, const tenso
   return true;
 }
 
+// batch_normalization_layer::forward_propagation / back_propagation branches
+// (tiny_dnn/layers/batch_normalization_layer.h:94-168).  Train phase: `mean` / `variance` (the layer's
+// mean_current_ / variance_current_) receive this mini-batch's moments; test phase: they are the moving
+// averages.  `stddev` is the layer's stddev_, which the backward pass reads.
+inline void batch_normalization_op(size_t channels, size_t spatial, float_t eps, bool train, const tensor_t &x,
+                                   vec_t &mean, vec_t &variance, vec_t &stddev, tensor_t &y) {
+  if (x.empty()) return;
+  std::vector<float> in = pack(x), out(in.size());
+  std::vector<float> m(mean.begin(), mean.end()), v(variance.begin(), variance.end()), sd(channels);
+  m.resize(channels);
+  v.resize(channels);
+  check(b200_batchnorm_fwd_host(ctx(), static_cast<int>(channels), static_cast<int>(spatial), static_cast<float>(eps),
+                                in.data(), m.data(), v.data(), sd.data(), out.data(), static_cast<int>(x.size()),
+                                train ? 1 : 0));
+  if (train) {
+    mean.assign(m.begin(), m.end());
+    variance.assign(v.begin(), v.end());
+  }
+  stddev.assign(sd.begin(), sd.end());
+  unpack(out, y);
+}
+
+inline void batch_normalization_grad_op(size_t channels, size_t spatial, const tensor_t &y, const tensor_t &dy,
+                                        const vec_t &stddev, tensor_t &dx) {
+  if (y.empty()) return;
+  std::vector<float> fy = pack(y), fdy = pack(dy), fdx(fy.size()), sd(stddev.begin(), stddev.end());
+  check(b200_batchnorm_bwd_host(ctx(), static_cast<int>(channels), static_cast<int>(spatial), fy.data(), fdy.data(),
+                                sd.data(), fdx.data(), static_cast<int>(y.size())));
+  unpack(fdx, dx);
+}
+
+// lrn_layer::forward_propagation branch, norm_region::across_channels (tiny_dnn/layers/lrn_layer.h:82-143)
+inline void lrn_op(size_t channels, size_t area, size_t size, float_t alpha, float_t beta, const tensor_t &x,
+                   tensor_t &y) {
+  if (x.empty()) return;
+  std::vector<float> in = pack(x), out(in.size());
+  check(b200_lrn_fwd_host(ctx(), in.data(), out.data(), static_cast<int>(channels), static_cast<int>(area),
+                          static_cast<int>(size), static_cast<float>(alpha), static_cast<float>(beta),
+                          static_cast<int>(x.size())));
+  unpack(out, y);
+}
+
 // average_pooling_layer::forward_propagation branch: replaces tiny_average_pooling_kernel
 // (tiny_dnn/layers/average_pooling_layer.h:25-55)
 inline void average_pooling_op(const b200_pool_desc &d, const tensor_t &in_data, const vec_t &W, const vec_t &bias,

@@ -228,6 +228,53 @@ def patch_elu_layer(t, p):
                  "  float_t b200_act_param() const override { return alpha_; }\n", p)
 
 
+def patch_batchnorm_layer(t, p):
+    """batch_normalization_layer has no engine argument; layer::set_backend_type(b200) selects the device
+    kernels (batch_normalization_layer.h:94-168).  Accessors give the fit hook the moving averages."""
+    t = _edit(t, '#include "tiny_dnn/util/util.h"\n', '#include "tiny_dnn/util/util.h"\n' + GLUE_INCLUDE, p)
+    t = _edit(t, "    tensor_t &in  = *in_data[0];\n    tensor_t &out = *out_data[0];\n",
+              "    tensor_t &in  = *in_data[0];\n    tensor_t &out = *out_data[0];\n"
+              "    if (layer::engine() == core::backend_t::b200) {\n"
+              "      b200::batch_normalization_op(in_channels_, in_spatial_size_, eps_, phase_ == net_phase::train, in,\n"
+              "                                   mean, variance, stddev_, out);\n"
+              "      if (phase_ == net_phase::train && update_immidiately_) {\n"
+              "        mean_     = mean_current_;\n"
+              "        variance_ = variance_current_;\n"
+              "      }\n"
+              "      return;\n"
+              "    }\n", p)
+    t = _edit(t, "    tensor_t delta_dot_y = curr_out;\n",
+              "    if (layer::engine() == core::backend_t::b200) {\n"
+              "      b200::batch_normalization_grad_op(in_channels_, in_spatial_size_, curr_out, curr_delta, stddev_,\n"
+              "                                        prev_delta);\n"
+              "      return;\n"
+              "    }\n"
+              "    tensor_t delta_dot_y = curr_out;\n", p)
+    t = _edit(t, "  float_t epsilon() const { return eps_; }\n",
+              "  float_t epsilon() const { return eps_; }\n\n"
+              "  size_t b200_channels() const { return in_channels_; }\n"
+              "  size_t b200_spatial() const { return in_spatial_size_; }\n"
+              "  vec_t &b200_mean() { return mean_; }\n"
+              "  vec_t &b200_variance() { return variance_; }\n"
+              "  vec_t &b200_mean_current() { return mean_current_; }\n"
+              "  vec_t &b200_variance_current() { return variance_current_; }\n"
+              "  vec_t &b200_stddev() { return stddev_; }\n"
+              "  net_phase b200_phase() const { return phase_; }\n", p)
+    return t
+
+
+def patch_lrn_layer(t, p):
+    """lrn_layer across channels under layer::set_backend_type(b200) (lrn_layer.h:82-95)."""
+    t = _edit(t, '#include "tiny_dnn/util/util.h"\n', '#include "tiny_dnn/util/util.h"\n' + GLUE_INCLUDE, p)
+    t = _edit(t, "    // @todo revise the parallelism strategy\n",
+              "    if (layer::engine() == core::backend_t::b200 && region_ == norm_region::across_channels) {\n"
+              "      b200::lrn_op(in_shape_.depth_, in_shape_.area(), size_, alpha_, beta_, *in_data[0], *out_data[0]);\n"
+              "      return;\n"
+              "    }\n"
+              "    // @todo revise the parallelism strategy\n", p)
+    return t
+
+
 def patch_layer_h(t, p):
     """layer::set_sample_count (layer.h:699-718) grows every gradient tensor to one row per sample.
     The device kernels return the batch sum of a weight gradient in row 0, so under engine b200
@@ -311,6 +358,8 @@ PATCHES = {
     "tiny_dnn/activations/activation_layer.h": patch_activation_layer,
     "tiny_dnn/activations/leaky_relu_layer.h": patch_leaky_relu_layer,
     "tiny_dnn/activations/elu_layer.h": patch_elu_layer,
+    "tiny_dnn/layers/batch_normalization_layer.h": patch_batchnorm_layer,
+    "tiny_dnn/layers/lrn_layer.h": patch_lrn_layer,
     "tiny_dnn/layers/layer.h": patch_layer_h,
     "tiny_dnn/optimizers/optimizer.h": patch_optimizer_h,
     "tiny_dnn/network.h": patch_network_h,

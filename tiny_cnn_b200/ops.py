@@ -222,6 +222,45 @@ def backward_activation(ctx: Context, kind: int, y, dy, param=None):
     return dx
 
 
+# --------------------------------------------------------------------------- batch norm / dropout / lrn
+def batch_normalization_forward(ctx: Context, channels: int, spatial: int, eps: float, x, mean=None, variance=None,
+                                train=True):
+    """batch_normalization_layer::forward_propagation (tiny_dnn/layers/batch_normalization_layer.h:136-168).
+    Train phase: returns (y, mean, variance, stddev) of this mini-batch; test phase: `mean` / `variance`
+    are the layer's moving averages."""
+    B = x.shape[0]
+    y = torch.empty_like(x)
+    if train:
+        mean = torch.empty(channels, device=x.device)
+        variance = torch.empty(channels, device=x.device)
+    stddev = torch.empty(channels, device=x.device)
+    check(ctx.lib.b200_batchnorm_fwd(ctx.handle, channels, spatial, float(eps), ptr(x), ptr(mean), ptr(variance),
+                                     ptr(stddev), ptr(y), B, int(train)))
+    return y, mean, variance, stddev
+
+
+def batch_normalization_backward(ctx: Context, channels: int, spatial: int, y, dy, stddev):
+    """batch_normalization_layer::back_propagation (batch_normalization_layer.h:94-134)."""
+    dx = torch.empty_like(y)
+    check(ctx.lib.b200_batchnorm_bwd(ctx.handle, channels, spatial, ptr(y), ptr(dy), ptr(stddev), ptr(dx), y.shape[0]))
+    return dx
+
+
+def dropout(ctx: Context, x, mask, scale: float):
+    """dropout_layer with the caller's mask (tiny_dnn/layers/dropout_layer.h:66-115): mask * scale * x."""
+    out = torch.empty_like(x)
+    check(ctx.lib.b200_dropout(ctx.handle, ptr(x), ptr(mask), float(scale), ptr(out), x.numel()))
+    return out
+
+
+def lrn_forward(ctx: Context, x, channels: int, area: int, size: int, alpha: float, beta: float):
+    """lrn_layer::forward_propagation across channels (tiny_dnn/layers/lrn_layer.h:82-143)."""
+    out = torch.empty_like(x)
+    check(ctx.lib.b200_lrn_fwd(ctx.handle, ptr(x), ptr(out), channels, area, size, float(alpha), float(beta),
+                               x.shape[0]))
+    return out
+
+
 def gradient(ctx: Context, loss: int, y, t):
     """gradient<E>(y, t) for a mini-batch (tiny_dnn/lossfunctions/loss_function.h:190-218)."""
     dy = torch.empty_like(y)
