@@ -983,6 +983,8 @@ typedef struct {
   float *out, *grad;   /* [B][out_dim] */
   float *padded, *padded_grad; /* conv: padded input / padded prev_delta */
   int32_t *argmax;
+  /* batch normalization: this batch's moments, stddev_, the moving averages (5 x channels floats) */
+  float *bn_mean_cur, *bn_var_cur, *bn_stddev, *bn_mean, *bn_var;
 } orc_layer;
 
 typedef struct orc_net {
@@ -994,6 +996,7 @@ typedef struct orc_net {
   float *params, *grads, *s0, *s1, *in_grad;
   float b1_t, b2_t; /* adam powers, advanced once per update call */
   int powers_init;
+  int test_phase;   /* net_phase::test: batch normalization reads its moving averages */
 } orc_net;
 
 static size_t layer_dims(const b200_layer_spec *s, size_t prev, size_t *in_dim, size_t *w_len,
@@ -1018,6 +1021,9 @@ static size_t layer_dims(const b200_layer_spec *s, size_t prev, size_t *in_dim, 
         *b_len = s->pool.in_c;
       }
       return (size_t)s->pool.in_c * s->pool.out_h * s->pool.out_w;
+    case B200_LAYER_BATCHNORM:
+      *in_dim = (size_t)s->bn_channels * s->bn_spatial;
+      return *in_dim;
     default: *in_dim = prev; return prev;
   }
 }
@@ -1057,6 +1063,14 @@ ORC_API orc_net *orc_net_create(const b200_layer_spec *specs, int n_layers, int 
     }
     if (specs[i].kind == B200_LAYER_MAXPOOL)
       L->argmax = (int32_t *)calloc(L->out_dim * max_batch, sizeof(int32_t));
+    if (specs[i].kind == B200_LAYER_BATCHNORM) {
+      const size_t c = specs[i].bn_channels;
+      L->bn_mean_cur = (float *)calloc(5 * c, sizeof(float));  /* init(): zeros */
+      L->bn_var_cur = L->bn_mean_cur + c;
+      L->bn_stddev = L->bn_mean_cur + 2 * c;
+      L->bn_mean = L->bn_mean_cur + 3 * c;
+      L->bn_var = L->bn_mean_cur + 4 * c;
+    }
   }
   net->n_params = off;
   net->params = (float *)calloc(off ? off : 1, sizeof(float));
@@ -1075,6 +1089,7 @@ ORC_API void orc_net_destroy(orc_net *net) {
     free(net->L[i].padded);
     free(net->L[i].padded_grad);
     free(net->L[i].argmax);
+    free(net->L[i].bn_mean_cur);
   }
   free(net->L);
   free(net->t_off);
@@ -1093,6 +1108,11 @@ ORC_API float *orc_net_grads(orc_net *net) { return net->grads; }
 ORC_API float *orc_net_output(orc_net *net) { return net->L[net->n_layers - 1].out; }
 ORC_API float *orc_net_layer_out(orc_net *net, int i) { return net->L[i].out; }
 ORC_API float *orc_net_layer_grad(orc_net *net, int i) { return i < 0 ? net->in_grad : net->L[i].grad; }
+/* network::set_netphase (network.h:438-442) */
+ORC_API void orc_net_set_phase(orc_net *net, int train) { net->test_phase = !train; }
+/* moving averages of batch normalization layer i: mean_ then variance_ */
+ORC_API float *orc_net_bn_mean(orc_net *net, int i) { return net->L[i].bn_mean; }
+ORC_API float *orc_net_bn_var(orc_net *net, int i) { return net->L[i].bn_var; }
 
 static int act_kind(int layer_kind) {
   return layer_kind == B200_LAYER_RELU         ? B200_ACT_RELU
@@ -1118,6 +1138,11 @@ ORC_API void orc_net_forward(orc_net *net, const float *x, int B) {
       case B200_LAYER_FC: orc_fc_fwd(L->s.fc_in, L->s.fc_out, in, W, b, L->out, B); break;
       case B200_LAYER_MAXPOOL: orc_maxpool_fwd(&L->s.pool, in, L->out, L->argmax, B); break;
       case B200_LAYER_AVGPOOL: orc_avgpool_fwd(&L->s.pool, in, W, b, L->out, B); break;
+      case B200_LAYER_BATCHNORM:
+        orc_batchnorm_fwd(L->s.bn_channels, L->s.bn_spatial, L->s.bn_eps, in,
+                          net->test_phase ? L->bn_mean : L->bn_mean_cur, net->test_phase ? L->bn_var : L->bn_var_cur,
+                          L->bn_stddev, L->out, B, !net->test_phase);
+        break;
       default: orc_act_param_fwd(act_kind(L->s.kind), L->s.act_param, in, L->out, (int)L->out_dim, B); break;
     }
     in = L->out;
@@ -1151,6 +1176,9 @@ ORC_API void orc_net_backward(orc_net *net, const float *x, const float *t, int 
       case B200_LAYER_AVGPOOL:
         orc_avgpool_bwd(&L->s.pool, in, W, L->grad, din, dW, db, 0, B);
         break;
+      case B200_LAYER_BATCHNORM:
+        orc_batchnorm_bwd(L->s.bn_channels, L->s.bn_spatial, L->out, L->grad, L->bn_stddev, din, B);
+        break;
       default: orc_act_param_bwd(act_kind(L->s.kind), L->s.act_param, L->out, L->grad, din, (int)L->out_dim, B); break;
     }
   }
@@ -1175,6 +1203,13 @@ ORC_API void orc_net_update(orc_net *net, int opt_kind, const b200_opt_hyper *h)
       net->b1_t *= h->b1;
       net->b2_t *= h->b2; /* adamax has no b2_t; the value is unused there */
     }
+  }
+  /* layer::update_weight ends with post_update() (layer.h:681) */
+  for (int i = 0; i < net->n_layers; ++i) {
+    orc_layer *L = &net->L[i];
+    if (L->s.kind == B200_LAYER_BATCHNORM)
+      orc_batchnorm_post_update(L->s.bn_channels, L->s.bn_momentum, L->bn_mean, L->bn_var, L->bn_mean_cur,
+                                L->bn_var_cur);
   }
 }
 

@@ -543,6 +543,9 @@ void add_layer(RefNet *r, const b200_layer_spec &s, size_t prev_dim) {
     case B200_LAYER_SIGMOID: r->net << sigmoid_layer(prev_dim); break;
     case B200_LAYER_LEAKY_RELU: r->net << leaky_relu_layer(prev_dim, s.act_param); break;
     case B200_LAYER_ELU: r->net << elu_layer(prev_dim, s.act_param); break;
+    case B200_LAYER_BATCHNORM:
+      r->net << batch_normalization_layer(s.bn_spatial, s.bn_channels, s.bn_eps, s.bn_momentum);
+      break;
     default: throw nn_error("unknown layer kind");
   }
 }
@@ -632,6 +635,21 @@ REF_API double ref_net_fit_n(void *h, const float *x, const float *t, long long 
 REF_API double ref_net_fit(void *h, const float *x, const float *t, int batch, int steps,
                            int loss_kind, int opt_kind, const b200_opt_hyper *hy) {
   return ref_net_fit_n(h, x, t, (long long)batch * steps, batch, 1, loss_kind, opt_kind, hy);
+}
+
+// moving averages of batch normalization layer `layer` (mean_ then variance_), read through the
+// layer's own save() since the members are private
+REF_API int ref_net_bn_stats(void *h, int layer, float *mean, float *variance) {
+  RefNet *r = static_cast<RefNet *>(h);
+  auto *bn = dynamic_cast<batch_normalization_layer *>(r->net[layer]);
+  if (!bn) return 1;
+  const size_t C = bn->in_shape()[0].depth_;
+  std::ostringstream os;
+  bn->save(os, 9);
+  std::istringstream is(os.str());
+  for (size_t j = 0; j < C; ++j) is >> mean[j];
+  for (size_t j = 0; j < C; ++j) is >> variance[j];
+  return 0;
 }
 
 // the general form: n_samples rows (the last mini-batch of a pass may be ragged), `epochs` passes

@@ -7,7 +7,7 @@ import ctypes as C
 
 import numpy as np
 
-from tiny_cnn_b200._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_ELU, LAYER_FC, LAYER_LEAKY_RELU, LAYER_MAXPOOL,
+from tiny_cnn_b200._lib import (LAYER_AVGPOOL, LAYER_BATCHNORM, LAYER_CONV, LAYER_ELU, LAYER_FC, LAYER_LEAKY_RELU, LAYER_MAXPOOL,
                                 LAYER_RELU, LAYER_SIGMOID, LAYER_SOFTMAX, LAYER_TANH, LayerSpec, OptHyper)
 from tiny_cnn_b200._lib import ConvDesc, PoolDesc
 from tiny_cnn_b200.network import LENET_TABLE
@@ -265,6 +265,13 @@ def _act(kind, param=0.0):
     return s, None
 
 
+def _bn(spatial, channels, eps=1e-5, momentum=0.999):
+    s = LayerSpec()
+    s.kind = LAYER_BATCHNORM
+    s.bn_spatial, s.bn_channels, s.bn_eps, s.bn_momentum = spatial, channels, eps, momentum
+    return s, None
+
+
 def build_net_specs(name):
     """Layer specs of a named network; returns (specs, keepalive)."""
     if name == "lenet":
@@ -286,6 +293,10 @@ def build_net_specs(name):
     elif name == "tiny_conv":
         L = [_conv(12, 12, 3, 2, 4, True), _act(LAYER_RELU), _pool(LAYER_MAXPOOL, 12, 12, 4, 2),
              _conv(6, 6, 3, 4, 5), _act(LAYER_TANH), _fc(80, 6), _act(LAYER_SOFTMAX)]
+    elif name == "tiny_conv_bn":
+        # batch normalization between a convolution and its relu, and before the classifier
+        L = [_conv(12, 12, 3, 2, 4, True), _bn(144, 4), _act(LAYER_RELU), _pool(LAYER_MAXPOOL, 12, 12, 4, 2),
+             _conv(6, 6, 3, 4, 5), _bn(16, 5, 1e-3, 0.9), _act(LAYER_TANH), _fc(80, 6), _act(LAYER_SOFTMAX)]
     elif name == "tiny_conv_acts":
         # the activations with a constructor parameter between the hot operators
         L = [_conv(12, 12, 3, 2, 4, True), _act(LAYER_LEAKY_RELU, 0.1), _pool(LAYER_MAXPOOL, 12, 12, 4, 2),
@@ -307,10 +318,40 @@ NET_CASES = {
                          t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.uniform(0, 1, s)),
     "tiny_conv_adam": dict(net="tiny_conv", B=5, steps=4, seed=104, in_dim=288, out_dim=6, loss=2, opt=1,
                            t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.standard_normal(s)),
+    # batch normalization layers (train phase while fitting, moving averages for predict), adam
+    "tiny_conv_bn_adam": dict(net="tiny_conv_bn", B=6, steps=4, seed=106, in_dim=288, out_dim=6, loss=1, opt=1,
+                              t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.standard_normal(s)),
     # leaky relu / elu / sigmoid, mse, RMSprop
     "tiny_conv_acts_rmsprop": dict(net="tiny_conv_acts", B=6, steps=4, seed=105, in_dim=288, out_dim=6, loss=0, opt=3,
                                    t_lo=0.0, t_hi=1.0, xgen=lambda r, s: r.standard_normal(s)),
 }
+
+
+def bn_layers(specs):
+    """indices of the batch normalization layers"""
+    return [i for i, s in enumerate(specs) if s.kind == LAYER_BATCHNORM]
+
+
+def null_gradient_biases(specs):
+    """Offsets (into the flat parameter buffer) of the biases of layers that feed a batch normalization
+    layer.  Their gradient is exactly zero in exact arithmetic (the normalization subtracts the channel
+    mean), so what any implementation holds there is the rounding noise of its sums: such a tensor is
+    checked to be noise, not to match the other side's noise."""
+    offs, off = set(), 0
+    for i, s in enumerate(specs):
+        if s.kind == LAYER_CONV:
+            d = s.conv
+            w, b = d.out_c * d.in_c * d.k_h * d.k_w, (d.out_c if d.has_bias else 0)
+        elif s.kind == LAYER_FC:
+            w, b = s.fc_in * s.fc_out, (s.fc_out if s.fc_has_bias else 0)
+        elif s.kind == LAYER_AVGPOOL:
+            w, b = s.pool.pool_w * s.pool.pool_h * s.pool.in_c, s.pool.in_c
+        else:
+            continue
+        if b and i + 1 < len(specs) and specs[i + 1].kind == LAYER_BATCHNORM:
+            offs.add(off + w)
+        off += w + b
+    return offs
 
 
 def net_layout(specs):

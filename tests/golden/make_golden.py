@@ -22,7 +22,7 @@ sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 
 import oracle_lib as o  # noqa: E402
-from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, gen_batchnorm_inputs,  # noqa: E402
+from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, bn_layers, gen_batchnorm_inputs,  # noqa: E402
                    ACT_CASES, AVGPOOL_CASES, CONV_CASES, DATA_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,  # noqa: E402
                    QCONV_CASES, QFC_CASES, build_net_specs, conv_desc, dataset_file_bytes, gen_conv_inputs,
                    gen_dataset_bytes, gen_net_data, hyper_for, merge_rows_np, pool_desc, xavier_params, OPT_KINDS,
@@ -201,6 +201,10 @@ def main():
         yp = o.f32(B, c["out_dim"])
         assert ref.ref_net_predict(h, o.p(x[:B]), o.p(yp), B) == 0
         out[f"net/{name}/p1"], out[f"net/{name}/predict"] = p1, yp
+        for li in bn_layers(specs):  # moving averages after the fit (predict above ran in the test phase)
+            m, v = o.f32(specs[li].bn_channels), o.f32(specs[li].bn_channels)
+            assert ref.ref_net_bn_stats(h, li, o.p(m), o.p(v)) == 0
+            out[f"net/{name}/bn{li}/mean"], out[f"net/{name}/bn{li}/var"] = m, v
         if c["opt"] == 1:
             a, b2 = C.c_float(), C.c_float()
             ref.ref_net_adam_powers(h, C.byref(a), C.byref(b2))

@@ -29,6 +29,9 @@ ORACLE_SIGS = {
     "orc_maxpool_bwd": (None, [_pd, _vp, _vp, _vp, _i]),
     "orc_avgpool_fwd": (None, [_pd, _vp, _vp, _vp, _vp, _i]),
     "orc_avgpool_bwd": (None, [_pd, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "orc_net_set_phase": (None, [_vp, _i]),
+    "orc_net_bn_mean": (C.POINTER(C.c_float), [_vp, _i]),
+    "orc_net_bn_var": (C.POINTER(C.c_float), [_vp, _i]),
     "orc_batchnorm_fwd": (None, [_i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "orc_batchnorm_bwd": (None, [_i, _i, _vp, _vp, _vp, _vp, _i]),
     "orc_batchnorm_post_update": (None, [_i, C.c_float, _vp, _vp, _vp, _vp]),
@@ -81,6 +84,7 @@ REF_SIGS = {
     "ref_maxpool_fwd_bwd": (_i, [_pd, _i, _i, _vp, _vp, _vp, _vp, _i]),
     "ref_avgpool_fwd_bwd": (_i, [_pd, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "ref_act_fwd_bwd": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i]),
+    "ref_net_bn_stats": (_i, [_vp, _i, _vp, _vp]),
     "ref_batchnorm_fwd_bwd": (_i, [_i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "ref_lrn_fwd": (_i, [_vp, _vp, _i, _i, _i, _i, C.c_float, C.c_float, _i]),
     "ref_dropout_fwd_bwd": (_i, [_i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i]),

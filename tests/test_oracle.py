@@ -14,7 +14,7 @@ import numpy as np
 import pytest
 
 import oracle_lib as o
-from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, gen_batchnorm_inputs,
+from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, bn_layers, gen_batchnorm_inputs,
                    ACT_CASES, AVGPOOL_CASES, CONV_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,
                    QCONV_CASES, QFC_CASES, build_net_specs, conv_desc, gen_conv_inputs, gen_net_data,
                    hyper_for, merge_rows_np, pool_desc, xavier_params)
@@ -395,6 +395,13 @@ def test_gold_net_training(oracle, gold, name):
         oracle.orc_net_train_step(net, o.p(xs), o.p(ts), B, c["loss"], c["opt"], C.byref(h))
     p1 = gold[f"net/{name}/p1"]
     assert np.array_equal(params, p1), float(np.abs(params - p1).max())
+    for li in bn_layers(specs):  # the moving averages post_update kept
+        cn = specs[li].bn_channels
+        assert np.array_equal(np.ctypeslib.as_array(oracle.orc_net_bn_mean(net, li), shape=(cn,)),
+                              gold[f"net/{name}/bn{li}/mean"])
+        assert np.array_equal(np.ctypeslib.as_array(oracle.orc_net_bn_var(net, li), shape=(cn,)),
+                              gold[f"net/{name}/bn{li}/var"])
+    oracle.orc_net_set_phase(net, 0)  # network::predict runs in the test phase
     oracle.orc_net_forward(net, o.p(x[:B]), B)
     out = np.ctypeslib.as_array(oracle.orc_net_output(net), shape=(B, c["out_dim"]))
     assert np.array_equal(out, gold[f"net/{name}/predict"])

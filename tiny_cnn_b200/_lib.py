@@ -72,6 +72,8 @@ class LayerSpec(C.Structure):
         ("pool", PoolDesc),
         ("fc_in", C.c_int32), ("fc_out", C.c_int32), ("fc_has_bias", C.c_int32),
         ("act_param", C.c_float),
+        ("bn_channels", C.c_int32), ("bn_spatial", C.c_int32),
+        ("bn_eps", C.c_float), ("bn_momentum", C.c_float),
     ]
 
 
@@ -80,7 +82,7 @@ ACT_NONE, ACT_RELU, ACT_TANH, ACT_SOFTMAX, ACT_SIGMOID, ACT_LEAKY_RELU, ACT_ELU 
 LOSS_MSE, LOSS_CROSS_ENTROPY, LOSS_CROSS_ENTROPY_MULTICLASS = 0, 1, 2
 OPT_ADAGRAD, OPT_ADAM, OPT_MOMENTUM, OPT_RMSPROP, OPT_ADAMAX, OPT_GRADIENT_DESCENT, OPT_NESTEROV_MOMENTUM = range(7)
 (LAYER_CONV, LAYER_FC, LAYER_MAXPOOL, LAYER_AVGPOOL, LAYER_RELU, LAYER_TANH, LAYER_SOFTMAX, LAYER_SIGMOID,
- LAYER_LEAKY_RELU, LAYER_ELU) = range(1, 11)
+ LAYER_LEAKY_RELU, LAYER_ELU, LAYER_BATCHNORM) = range(1, 12)
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 _cd, _pd, _oh = C.POINTER(ConvDesc), C.POINTER(PoolDesc), C.POINTER(OptHyper)
@@ -132,6 +134,8 @@ SIGNATURES = {
     "b200_act_param_bwd_host": (_i, [_vp, _i, C.c_float, _vp, _vp, _vp, _i, _i]),
     "b200_act_fwd_host": (_i, [_vp, _i, _vp, _vp, _i, _i]),
     "b200_act_bwd_host": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i]),
+    "b200_net_set_phase": (_i, [_vp, _i]),
+    "b200_net_bn_stats": (_i, [_vp, _i, _vp, _vp, _i]),
     "b200_batchnorm_fwd": (_i, [_vp, _i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "b200_batchnorm_bwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i]),
     "b200_batchnorm_post_update": (_i, [_vp, _i, C.c_float, _vp, _vp, _vp, _vp]),

@@ -45,6 +45,7 @@
 #include "tiny_dnn/activations/tanh_layer.h"
 #include "tiny_dnn/core/kernels/b200_glue.h"
 #include "tiny_dnn/layers/average_pooling_layer.h"
+#include "tiny_dnn/layers/batch_normalization_layer.h"
 #include "tiny_dnn/layers/convolutional_layer.h"
 #include "tiny_dnn/layers/fully_connected_layer.h"
 #include "tiny_dnn/layers/max_pooling_layer.h"
@@ -166,6 +167,14 @@ inline bool spec_of(layer *l, b200_layer_spec &s, std::vector<uint8_t> &tbl) {
     s.act_param = static_cast<float>(e->alpha_);
     return true;
   }
+  if (auto *bn = dynamic_cast<batch_normalization_layer *>(l)) {
+    s.kind = B200_LAYER_BATCHNORM;
+    s.bn_channels = static_cast<int32_t>(bn->b200_channels());
+    s.bn_spatial = static_cast<int32_t>(bn->b200_spatial());
+    s.bn_eps = static_cast<float>(bn->epsilon());
+    s.bn_momentum = static_cast<float>(bn->momentum());
+    return true;
+  }
   return false;
 }
 
@@ -274,6 +283,14 @@ void weights_to_device(Net &nn, device_twin &tw) {
       off += w->size();
     }
   check(b200_net_set_params(tw.net, flat.data()));
+  // batch normalization: the layers' moving averages; the fit runs in the train phase
+  for (size_t i = 0; i < nn.depth(); ++i)
+    if (auto *bn = dynamic_cast<batch_normalization_layer *>(nn[i])) {
+      std::vector<float> m(bn->b200_mean().begin(), bn->b200_mean().end()),
+        v(bn->b200_variance().begin(), bn->b200_variance().end());
+      check(b200_net_bn_stats(tw.net, static_cast<int>(i), m.data(), v.data(), 1));
+    }
+  check(b200_net_set_phase(tw.net, 1));
 }
 
 // weights, optimizer state (stateful_optimizer::E_, keyed by the weight vector's address) and
@@ -288,6 +305,13 @@ void state_to_host(Net &nn, device_twin &tw, opt_choice &oc, long long steps_don
     for (auto *w : nn[i]->weights()) {
       std::copy(flat.begin() + off, flat.begin() + off + w->size(), w->begin());
       off += w->size();
+    }
+  for (size_t i = 0; i < nn.depth(); ++i)
+    if (auto *bn = dynamic_cast<batch_normalization_layer *>(nn[i])) {
+      std::vector<float> m(bn->b200_channels()), v(bn->b200_channels());
+      check(b200_net_bn_stats(tw.net, static_cast<int>(i), m.data(), v.data(), 0));
+      bn->b200_mean().assign(m.begin(), m.end());
+      bn->b200_variance().assign(v.begin(), v.end());
     }
   for (int k = 0; k < oc.n_state; ++k) {
     check(b200_net_get_opt_state(tw.net, k, flat.data()));

@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from . import _lib as L
-from ._lib import (LAYER_AVGPOOL, LAYER_CONV, LAYER_ELU, LAYER_FC, LAYER_LEAKY_RELU, LAYER_MAXPOOL, LAYER_RELU,
+from ._lib import (LAYER_AVGPOOL, LAYER_BATCHNORM, LAYER_CONV, LAYER_ELU, LAYER_FC, LAYER_LEAKY_RELU, LAYER_MAXPOOL, LAYER_RELU,
                    LAYER_SIGMOID, LAYER_SOFTMAX,
                    LAYER_TANH, LOSS_CROSS_ENTROPY, LOSS_MSE, OPT_ADAGRAD, OPT_ADAM, OPT_ADAMAX, OPT_GRADIENT_DESCENT,
                    OPT_MOMENTUM, OPT_NESTEROV_MOMENTUM, OPT_RMSPROP,
@@ -186,6 +186,16 @@ class Sequential:
 
     def elu_layer(self, alpha=1.0):
         return self._act(LAYER_ELU, alpha)
+
+    def batch_normalization_layer(self, in_spatial_size, in_channels, epsilon=1e-5, momentum=0.999):
+        """batch_normalization_layer(in_spatial_size, in_channels, epsilon, momentum)
+        (tiny_dnn/layers/batch_normalization_layer.h:59-72)."""
+        s = LayerSpec()
+        s.kind = LAYER_BATCHNORM
+        s.bn_spatial, s.bn_channels, s.bn_eps, s.bn_momentum = in_spatial_size, in_channels, epsilon, momentum
+        self.specs.append(s)
+        self._out_dim = in_spatial_size * in_channels
+        return self
 
     # ---- device twin ---------------------------------------------------------------------
     def spec_array(self):
