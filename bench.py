@@ -250,7 +250,9 @@ def time_kernels(ctx, torch, ops, reps=20):
 
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None where no capture of that launch exists
-NCU_DRAM_BYTES = {"conv2_fwd": 19.13e6}
+# (profiles/conv_tc_kernel_conv2_fwd_b256_ncu_full.md; conv2's dX launch is the same kernel on
+# tensors of the same sizes -- 32 -> 32 channels, the same 512 tiles -- so the figure stands for both)
+NCU_DRAM_BYTES = {"conv2_fwd": 17.04e6, "conv2_dx": 17.04e6}
 
 
 def conv_rooflines(kt, peaks):

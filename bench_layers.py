@@ -70,6 +70,25 @@ def other_layers(args, ctx):
         ms = timed(lambda: ops.quantized_conv2d(ctx, d, x, W, b), args.reps, args.warmup)
         macs = B * 64 * d.out_w * d.out_h * 32 * 25
         out["fwd"] = {"ms": round(ms, 4), "int_tops": round(2.0 * macs / ms / 1e9, 3)}
+    elif args.layer == "bn":  # batch normalization, 64 channels x 32 x 32 (an HBM-bound layer: bytes, not flops)
+        Cn, S = 64, 1024
+        x = torch.randn(B, Cn * S, device="cuda", generator=g)
+        dy = torch.randn(B, Cn * S, device="cuda", generator=g)
+        y, mean, var, sd = ops.batch_normalization_forward(ctx, Cn, S, 1e-5, x)
+        nbytes = 4.0 * B * Cn * S
+        ms = timed(lambda: ops.batch_normalization_forward(ctx, Cn, S, 1e-5, x), args.reps, args.warmup)
+        # two reduction passes and the normalising pass read x; one write
+        out["fwd"] = {"ms": round(ms, 4), "algorithmic_gbs": round(2 * nbytes / ms / 1e6, 1),
+                      "touched_gbs": round(4 * nbytes / ms / 1e6, 1)}
+        ms = timed(lambda: ops.batch_normalization_backward(ctx, Cn, S, y, dy, sd), args.reps, args.warmup)
+        out["bwd"] = {"ms": round(ms, 4), "algorithmic_gbs": round(3 * nbytes / ms / 1e6, 1),
+                      "touched_gbs": round(5 * nbytes / ms / 1e6, 1)}
+    elif args.layer == "lrn":  # across 64 channels of 32 x 32, window 5
+        Cn, area = 64, 1024
+        x = torch.randn(B, Cn * area, device="cuda", generator=g)
+        nbytes = 4.0 * B * Cn * area
+        ms = timed(lambda: ops.lrn_forward(ctx, x, Cn, area, 5, 1e-4, 0.75), args.reps, args.warmup)
+        out["fwd"] = {"ms": round(ms, 4), "algorithmic_gbs": round(2 * nbytes / ms / 1e6, 1)}
     else:  # qfc 9216 -> 256
         x = torch.rand(B, 9216, device="cuda", generator=g) * 2 - 1
         W = torch.rand(9216 * 256, device="cuda", generator=g) - 0.5
@@ -81,7 +100,7 @@ def other_layers(args, ctx):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--layer", default="conv2", choices=sorted(LAYERS) + sorted(FC_LAYERS) + ["qconv", "qfc"])
+    ap.add_argument("--layer", default="conv2", choices=sorted(LAYERS) + sorted(FC_LAYERS) + ["qconv", "qfc", "bn", "lrn"])
     ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--reps", type=int, default=5)
