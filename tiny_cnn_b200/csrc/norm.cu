@@ -43,16 +43,32 @@ __device__ __forceinline__ float add_slices(const float *part, int c, int slices
 // (two inputs: also the sum of x*y, for the backward pass)
 __global__ void __launch_bounds__(BN_THREADS) bn_sum_kernel(const float *__restrict__ x, const float *__restrict__ y,
                                                             int S, int B, float *__restrict__ part_x,
-                                                            float *__restrict__ part_xy) {
+                                                            float *__restrict__ part_xy, int vec4) {
   const int c = blockIdx.x, C = gridDim.x, z = blockIdx.y, Z = gridDim.y;
   const int n0 = (int)((long long)B * z / Z), n1 = (int)((long long)B * (z + 1) / Z);
   float sx = 0.f, sxy = 0.f;
-  for (int n = n0; n < n1; ++n) {
-    const size_t base = ((size_t)n * C + c) * S;
-    for (int k = threadIdx.x; k < S; k += BN_THREADS) {
-      const float v = x[base + k];
-      sx += v;
-      if (y != nullptr) sxy += v * y[base + k];
+  if (vec4) {  // 16-byte loads: S a multiple of 4 and the tensors 16-byte aligned (checked by the launcher)
+    for (int n = n0; n < n1; ++n) {
+      const size_t base = ((size_t)n * C + c) * S;
+      const float4 *x4 = reinterpret_cast<const float4 *>(x + base);
+      const float4 *y4 = y != nullptr ? reinterpret_cast<const float4 *>(y + base) : nullptr;
+      for (int k = threadIdx.x; k < S / 4; k += BN_THREADS) {
+        const float4 v = x4[k];
+        sx += (v.x + v.y) + (v.z + v.w);
+        if (y4 != nullptr) {
+          const float4 w = y4[k];
+          sxy += (v.x * w.x + v.y * w.y) + (v.z * w.z + v.w * w.w);
+        }
+      }
+    }
+  } else {
+    for (int n = n0; n < n1; ++n) {
+      const size_t base = ((size_t)n * C + c) * S;
+      for (int k = threadIdx.x; k < S; k += BN_THREADS) {
+        const float v = x[base + k];
+        sx += v;
+        if (y != nullptr) sxy += v * y[base + k];
+      }
     }
   }
   sx = block_sum_all(sx);
@@ -66,16 +82,27 @@ __global__ void __launch_bounds__(BN_THREADS) bn_sum_kernel(const float *__restr
 // pass 2 (math_functions.h:39-61): per (channel, batch slice) the sum of (x - mean)^2
 __global__ void __launch_bounds__(BN_THREADS) bn_var_kernel(const float *__restrict__ x, int S, int B, int slices,
                                                             const float *__restrict__ part_x,
-                                                            float *__restrict__ part_v) {
+                                                            float *__restrict__ part_v, int vec4) {
   const int c = blockIdx.x, C = gridDim.x, z = blockIdx.y, Z = gridDim.y;
   const float mean = __fdiv_rn(add_slices(part_x, c, slices), (float)B * (float)S);
   const int n0 = (int)((long long)B * z / Z), n1 = (int)((long long)B * (z + 1) / Z);
   float sv = 0.f;
-  for (int n = n0; n < n1; ++n) {
-    const size_t base = ((size_t)n * C + c) * S;
-    for (int k = threadIdx.x; k < S; k += BN_THREADS) {
-      const float d = __fsub_rn(x[base + k], mean);
-      sv += __fmul_rn(d, d);
+  if (vec4) {
+    for (int n = n0; n < n1; ++n) {
+      const float4 *x4 = reinterpret_cast<const float4 *>(x + ((size_t)n * C + c) * S);
+      for (int k = threadIdx.x; k < S / 4; k += BN_THREADS) {
+        const float4 v = x4[k];
+        const float a = v.x - mean, b = v.y - mean, e = v.z - mean, f = v.w - mean;
+        sv += (a * a + b * b) + (e * e + f * f);
+      }
+    }
+  } else {
+    for (int n = n0; n < n1; ++n) {
+      const size_t base = ((size_t)n * C + c) * S;
+      for (int k = threadIdx.x; k < S; k += BN_THREADS) {
+        const float d = __fsub_rn(x[base + k], mean);
+        sv += __fmul_rn(d, d);
+      }
     }
   }
   sv = block_sum_all(sv);
@@ -89,7 +116,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_apply_kernel(const float *__res
                                                               int B, float eps, int slices,
                                                               const float *__restrict__ part_x,
                                                               const float *__restrict__ part_v, float *mean_io,
-                                                              float *var_io, float *__restrict__ stddev) {
+                                                              float *var_io, float *__restrict__ stddev, int vec4) {
   const int c = blockIdx.x, C = gridDim.x, z = blockIdx.y, Z = gridDim.y;
   float mean, var;
   if (part_x != nullptr) {
@@ -108,6 +135,22 @@ __global__ void __launch_bounds__(BN_THREADS) bn_apply_kernel(const float *__res
     stddev[c] = sd;
   }
   const int n0 = (int)((long long)B * z / Z), n1 = (int)((long long)B * (z + 1) / Z);
+  if (vec4) {
+    for (int n = n0; n < n1; ++n) {
+      const size_t base = ((size_t)n * C + c) * S;
+      const float4 *x4 = reinterpret_cast<const float4 *>(x + base);
+      float4 *y4 = reinterpret_cast<float4 *>(y + base);
+      for (int k = threadIdx.x; k < S / 4; k += BN_THREADS) {
+        float4 v = x4[k];
+        v.x = __fdiv_rn(__fsub_rn(v.x, mean), sd);
+        v.y = __fdiv_rn(__fsub_rn(v.y, mean), sd);
+        v.z = __fdiv_rn(__fsub_rn(v.z, mean), sd);
+        v.w = __fdiv_rn(__fsub_rn(v.w, mean), sd);
+        y4[k] = v;
+      }
+    }
+    return;
+  }
   for (int n = n0; n < n1; ++n) {
     const size_t base = ((size_t)n * C + c) * S;
     for (int k = threadIdx.x; k < S; k += BN_THREADS) y[base + k] = __fdiv_rn(__fsub_rn(x[base + k], mean), sd);
@@ -119,13 +162,30 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_kernel(const float *__restr
                                                             float *__restrict__ dx, int S, int B, int slices,
                                                             const float *__restrict__ part_d,
                                                             const float *__restrict__ part_dy,
-                                                            const float *__restrict__ stddev) {
+                                                            const float *__restrict__ stddev, int vec4) {
   const int c = blockIdx.x, C = gridDim.x, z = blockIdx.y, Z = gridDim.y;
   const float count = (float)B * (float)S;
   const float mean_d = __fdiv_rn(add_slices(part_d, c, slices), count);
   const float mean_dy = __fdiv_rn(add_slices(part_dy, c, slices), count);
   const float sd = stddev[c];
   const int n0 = (int)((long long)B * z / Z), n1 = (int)((long long)B * (z + 1) / Z);
+  if (vec4) {
+    for (int n = n0; n < n1; ++n) {
+      const size_t base = ((size_t)n * C + c) * S;
+      const float4 *y4 = reinterpret_cast<const float4 *>(y + base), *g4 = reinterpret_cast<const float4 *>(dy + base);
+      float4 *d4 = reinterpret_cast<float4 *>(dx + base);
+      for (int k = threadIdx.x; k < S / 4; k += BN_THREADS) {
+        const float4 a = y4[k], g = g4[k];
+        float4 o;
+        o.x = __fdiv_rn(__fsub_rn(__fsub_rn(g.x, mean_d), __fmul_rn(mean_dy, a.x)), sd);
+        o.y = __fdiv_rn(__fsub_rn(__fsub_rn(g.y, mean_d), __fmul_rn(mean_dy, a.y)), sd);
+        o.z = __fdiv_rn(__fsub_rn(__fsub_rn(g.z, mean_d), __fmul_rn(mean_dy, a.z)), sd);
+        o.w = __fdiv_rn(__fsub_rn(__fsub_rn(g.w, mean_d), __fmul_rn(mean_dy, a.w)), sd);
+        d4[k] = o;
+      }
+    }
+    return;
+  }
   for (int n = n0; n < n1; ++n) {
     const size_t base = ((size_t)n * C + c) * S;
     for (int k = threadIdx.x; k < S; k += BN_THREADS) {
@@ -189,6 +249,8 @@ __global__ void lrn_across_fwd_kernel(const float *__restrict__ in, float *__res
   }
 }
 
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 int elementwise_grid(size_t n, int sm_count) {
   size_t blocks = (n + 255) / 256, cap = (size_t)sm_count * 16;
   if (blocks > cap) blocks = cap;
@@ -209,14 +271,15 @@ int batchnorm_fwd(b200_ctx *ctx, int channels, int spatial, float eps, const flo
   const int Z = bn_slices(B, channels, ctx->sm_count);
   const dim3 grid(channels, Z);
   float *part_x = scratch, *part_v = scratch + (size_t)Z * channels;
+  const int vec4 = spatial % 4 == 0 && aligned16(x) && aligned16(y);
   if (train) {
-    bn_sum_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(x, nullptr, spatial, B, part_x, nullptr);
+    bn_sum_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(x, nullptr, spatial, B, part_x, nullptr, vec4);
     B200_LAUNCHED();
-    bn_var_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(x, spatial, B, Z, part_x, part_v);
+    bn_var_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(x, spatial, B, Z, part_x, part_v, vec4);
     B200_LAUNCHED();
   }
   bn_apply_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(x, y, spatial, B, eps, Z, train ? part_x : nullptr,
-                                                        train ? part_v : nullptr, mean, variance, stddev);
+                                                        train ? part_v : nullptr, mean, variance, stddev, vec4);
   B200_LAUNCHED();
   return 0;
 }
@@ -227,9 +290,10 @@ int batchnorm_bwd(b200_ctx *ctx, int channels, int spatial, const float *y, cons
   const int Z = bn_slices(B, channels, ctx->sm_count);
   const dim3 grid(channels, Z);
   float *part_d = scratch, *part_dy = scratch + (size_t)Z * channels;
-  bn_sum_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(dy, y, spatial, B, part_d, part_dy);
+  const int vec4 = spatial % 4 == 0 && aligned16(y) && aligned16(dy) && aligned16(dx);
+  bn_sum_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(dy, y, spatial, B, part_d, part_dy, vec4);
   B200_LAUNCHED();
-  bn_bwd_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(y, dy, dx, spatial, B, Z, part_d, part_dy, stddev);
+  bn_bwd_kernel<<<grid, BN_THREADS, 0, ctx->stream>>>(y, dy, dx, spatial, B, Z, part_d, part_dy, stddev, vec4);
   B200_LAUNCHED();
   return 0;
 }
