@@ -479,7 +479,9 @@ def run_b200(args, rank, world, local_rank):
                          "rank-ordered sum (the library's peer-memory kernels), update" if peer else
                          "CUDA graph of forward+backward, NCCL sum all-reduce of the gradient bucket, update")
                         + "; inside the graph the weight-gradient kernels and the filter matrices run on a "
-                          "side branch beside the forward / dX chain"},
+                          "side branch beside the forward / dX chain",
+                "peer_rendezvous": ({"ipc": "b200_peer_buffer_create/_open (the library's inter-process handles)",
+                                     "symm": "torch symmetric memory"}.get(dp.rendezvous) if peer else None)},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": ms_e2e * per,
                     "ms_per_step_min": min(blocks_e2e) * per, "ms_per_step_max": max(blocks_e2e) * per,
@@ -585,6 +587,8 @@ def dp_parity(torch, dist, np, nw, ops, net, opt, dp, dp_step, p0, rank, world, 
             "replica_mismatches": {"after_timed_steps": [bad_timed, diff_timed], "after_parity_steps": [bad_steps, diff_steps],
                                    "what": "[parameters whose bit patterns differ between ranks, largest |difference|]"},
             "weights_finite": finite_timed and finite_steps,
+            # the sum over the replicas against one GPU on the concatenated mini-batch: the gradient bucket
+            "vs_single_gpu": worst_grad, "vs_single_gpu_tol": 1e-3,
             "grads_vs_single_gpu": worst_grad, "grads_tol": 1e-3,
             "weights_vs_single_gpu": {"worst": worst, "share_within_1e-3": share, "worst_abs": worst_abs,
                                       "adam_reach": 2 * steps * opt.alpha, "steps": steps},

@@ -523,6 +523,36 @@ B200_API int b200_qconv2d_fwd(b200_ctx *ctx, const b200_conv_desc *d, const floa
 B200_API int b200_qfc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in,
                           const float *W, const float *bias, float *out, int batch);
 
+/*
+ * The forms for quantized layers chained without dequantizing in between
+ * (tiny_backend::conv2d_eq / fully_eq, tiny_dnn/core/backend_tiny.h:115-135,321-345, over
+ * the nine- / eleven-argument overloads of tiny_quantized_conv2d_kernel
+ * (tiny_quantized_conv2d_kernel.h:353-466) and tiny_quantized_fully_connected_kernel
+ * (tiny_quantized_fully_connected_kernel.h:269-370)): `in`, `W` and `bias` hold uint8 values
+ * in floats, `in_r` (2 floats per sample), `W_r`, `b_r` (2 floats each) their ranges; `out`
+ * receives the requantized uint8 values in floats and `out_r` (2 floats per sample) their
+ * range.  Bit for bit with the reference kernels, including the convolution's bias term
+ * formed in float.  The convolution input rows are the PADDED rows, as for b200_qconv2d_fwd.
+ * In the reference nothing constructs a layer with the six inputs that select these forms,
+ * so only a caller of the backend interface reaches them.
+ */
+B200_API int b200_qconv2d_eq_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                                 const float *W, const float *bias, const float *in_r,
+                                 const float *W_r, const float *b_r, float *out, float *out_r,
+                                 int batch);
+B200_API int b200_qfc_eq_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in,
+                             const float *W, const float *bias, const float *in_r,
+                             const float *W_r, const float *b_r, float *out, float *out_r,
+                             int batch);
+B200_API int b200_qconv2d_eq_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
+                                      const float *W, const float *bias, const float *in_r,
+                                      const float *W_r, const float *b_r, float *out,
+                                      float *out_r, int batch);
+B200_API int b200_qfc_eq_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in,
+                                  const float *W, const float *bias, const float *in_r,
+                                  const float *W_r, const float *b_r, float *out, float *out_r,
+                                  int batch);
+
 B200_API int b200_qconv2d_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in,
                                    const float *W, const float *bias, float *out, int batch);
 B200_API int b200_qfc_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in,
@@ -674,6 +704,27 @@ B200_API int b200_net_peer_reduce_init(b200_net *net, int rank, int world,
 B200_API int b200_net_peer_reduce(b200_net *net);
 B200_API int b200_net_peer_push(b200_net *net);
 B200_API int b200_net_peer_sum(b200_net *net);
+
+/*
+ * The rendezvous of those exchange buffers between the processes of one box, for a host
+ * that has no framework to do it (a multi-process C++ launcher around network::fit):
+ * b200_peer_buffer_create allocates `bytes` of zero-filled device memory on the context's
+ * GPU and writes an opaque B200_PEER_HANDLE_BYTES-byte handle that the caller sends to the
+ * other processes by any means (a pipe, a file, MPI, a torch.distributed object gather);
+ * b200_peer_buffer_open maps the buffer behind another process's handle into this process
+ * (peer access between the two GPUs is enabled on first use) and returns its address here.
+ * The addresses -- the own buffer at index `rank` -- are what b200_net_peer_reduce_init
+ * takes.  b200_peer_buffer_close unmaps an opened buffer; b200_peer_buffer_destroy frees a
+ * created one, after every other process has closed it.  A handle is only meaningful on
+ * the box and during the life of the process that created it.
+ */
+#define B200_PEER_HANDLE_BYTES 64
+B200_API int b200_peer_buffer_create(b200_ctx *ctx, size_t bytes, void **dev,
+                                     unsigned char handle[B200_PEER_HANDLE_BYTES]);
+B200_API int b200_peer_buffer_open(b200_ctx *ctx, const unsigned char handle[B200_PEER_HANDLE_BYTES],
+                                   void **dev);
+B200_API int b200_peer_buffer_close(b200_ctx *ctx, void *dev);
+B200_API int b200_peer_buffer_destroy(b200_ctx *ctx, void *dev);
 
 /*
  * The same step from HOST buffers (what network::train_onebatch does,

@@ -973,6 +973,136 @@ ORC_API int orc_qfc_fwd(int in_size, int out_size, const float *in, const float 
   return 0;
 }
 
+/* The "efficient" forms for chained quantized layers: operands arrive as uint8 values held in
+   floats with their ranges, results leave the same way (no quantize at the input, no dequantize at
+   the output).  tiny_quantized_conv2d_kernel, nine-argument overload
+   (tiny_quantized_conv2d_kernel.h:353-466), per sample as tiny_backend::conv2d_eq calls it
+   (backend_tiny.h:115-135): in [B][in_len] (padded), in_r [B][2], W_r / b_r [2], out [B][out_len],
+   out_r [B][2]. */
+ORC_API int orc_qconv2d_eq_fwd(const b200_conv_desc *p, const float *in, const float *W, const float *bias,
+                               const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r,
+                               int B) {
+  (void)b_r; /* the kernel takes the bias range and never reads it */
+  size_t iw = p->inp_w, ih = p->inp_h, id = p->in_c;
+  size_t ow = p->out_w, oh = p->out_h, od = p->out_c;
+  size_t kw = p->k_w, kh = p->k_h;
+  size_t in_len = iw * ih * id, out_len = ow * oh * od, lenW = kw * kh * id * od;
+  uint8_t *in_q = (uint8_t *)malloc(in_len);
+  uint8_t *W_q = (uint8_t *)malloc(lenW);
+  int32_t *a_q = (int32_t *)malloc(sizeof(int32_t) * out_len);
+  uint8_t *a_rq = (uint8_t *)malloc(out_len);
+  for (size_t i = 0; i < lenW; ++i) W_q[i] = (uint8_t)W[i];
+  for (int n = 0; n < B; ++n) {
+    const float *x = in + n * in_len;
+    float min_filter = W_r[0], max_filter = W_r[1];
+    if (W_r[0] == W_r[1]) {
+      max_filter = W_r[1] + 1e-3f;
+      min_filter = W_r[0] - 1e-3f;
+    }
+    const float min_input = in_r[2 * n], max_input = in_r[2 * n + 1];
+    float min_output_value, max_output_value;
+    orc_range_for_multiplication(min_input, max_input, min_filter, max_filter, &min_output_value,
+                                 &max_output_value);
+    for (size_t i = 0; i < in_len; ++i) in_q[i] = (uint8_t)x[i];
+    const int32_t offset_input = (int32_t)orc_f2q_unclamped(8, 0.0f, min_input, max_input);
+    const int32_t offset_filter = (int32_t)orc_f2q_unclamped(8, 0.0f, min_filter, max_filter);
+    const int32_t zero_in_total_space = (int32_t)orc_f2q(32, 0.0f, min_output_value, max_output_value);
+    memset(a_q, 0, sizeof(int32_t) * out_len);
+    for (size_t o = 0; o < od; ++o) {
+      for (size_t inc = 0; inc < id; ++inc) {
+        if (!tbl_connected(p, (int)o, (int)inc)) continue;
+        const uint8_t *pw = W_q + kw * kh * (id * o + inc);
+        const uint8_t *pi = in_q + iw * ih * inc;
+        int32_t *pa = a_q + ow * oh * o;
+        for (size_t y = 0; y < oh; ++y)
+          for (size_t xx = 0; xx < ow; ++xx) {
+            const uint8_t *ppw = pw;
+            const uint8_t *ppi = pi + iw * (y * p->stride_h) + xx * p->stride_w;
+            int32_t sum = 0;
+            for (size_t wy = 0; wy < kh; ++wy)
+              for (size_t wx = 0; wx < kw; ++wx)
+                sum += ((int32_t)(*ppw++) - offset_filter) * ((int32_t)ppi[wy * iw + wx] - offset_input);
+            pa[y * ow + xx] += sum;
+          }
+      }
+      if (p->has_bias) {
+        /* `bias[o] - zero_in_total_space`: the FLOAT bias entry minus the int, formed in float, then
+           cast to int32 (:436-441) -- not the integer form of the plain kernel */
+        int32_t *pa = a_q + ow * oh * o;
+        const int32_t add = (int32_t)(bias[o] - (float)zero_in_total_space);
+        for (size_t i = 0; i < ow * oh; ++i) pa[i] += add;
+      }
+    }
+    float min_rq, max_rq;
+    orc_quantize_down_and_shrink_range(a_q, out_len, min_output_value, max_output_value, &min_rq, &max_rq, a_rq);
+    for (size_t i = 0; i < out_len; ++i) out[n * out_len + i] = (float)a_rq[i];
+    out_r[2 * n] = min_rq;
+    out_r[2 * n + 1] = max_rq;
+  }
+  free(in_q);
+  free(W_q);
+  free(a_q);
+  free(a_rq);
+  return 0;
+}
+
+/* tiny_quantized_fully_connected_kernel, eleven-argument overload
+   (tiny_quantized_fully_connected_kernel.h:269-370), per sample as tiny_backend::fully_eq would
+   (backend_tiny.h:321-345) */
+ORC_API int orc_qfc_eq_fwd(int in_size, int out_size, const float *in, const float *W, const float *bias,
+                           const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r, int B) {
+  const int has_bias = bias != NULL;
+  uint8_t *in_q = (uint8_t *)malloc(in_size ? in_size : 1);
+  uint8_t *W_q = (uint8_t *)malloc((size_t)in_size * out_size + 1);
+  uint8_t *b_q = (uint8_t *)malloc(out_size ? out_size : 1);
+  int32_t *o_q = (int32_t *)malloc(sizeof(int32_t) * (out_size ? out_size : 1));
+  uint8_t *o_rq = (uint8_t *)malloc(out_size ? out_size : 1);
+  for (size_t i = 0; i < (size_t)in_size * out_size; ++i) W_q[i] = (uint8_t)W[i];
+  if (has_bias)
+    for (int i = 0; i < out_size; ++i) b_q[i] = (uint8_t)bias[i];
+  for (int n = 0; n < B; ++n) {
+    const float *x = in + (size_t)n * in_size;
+    float min_filter = W_r[0], max_filter = W_r[1];
+    if (min_filter == max_filter) {
+      max_filter = W_r[1] + 1e-3f;
+      min_filter = W_r[0] - 1e-3f;
+    }
+    float min_bias = b_r[0], max_bias = b_r[1];
+    if (has_bias && min_bias == max_bias) {
+      max_bias = b_r[1] + 1e-3f;
+      min_bias = b_r[0] - 1e-3f;
+    }
+    const float min_input = in_r[2 * n], max_input = in_r[2 * n + 1];
+    float min_output_value, max_output_value;
+    orc_range_for_multiplication(min_input, max_input, min_filter, max_filter, &min_output_value,
+                                 &max_output_value);
+    for (int i = 0; i < in_size; ++i) in_q[i] = (uint8_t)x[i];
+    min_output_value += min_bias;
+    max_output_value += max_bias;
+    const int32_t offset_input = (int32_t)orc_f2q_unclamped(8, 0.0f, min_input, max_input);
+    const int32_t offset_filter = (int32_t)orc_f2q_unclamped(8, 0.0f, min_filter, max_filter);
+    const int32_t zero_in_total_space = (int32_t)orc_f2q(32, 0.0f, min_output_value, max_output_value);
+    for (int i = 0; i < out_size; ++i) {
+      int32_t acc = 0;
+      for (int c = 0; c < in_size; ++c)
+        acc += ((int32_t)W_q[(size_t)c * out_size + i] - offset_filter) * ((int32_t)in_q[c] - offset_input);
+      if (has_bias) acc += (b_q[i] - zero_in_total_space);
+      o_q[i] = acc;
+    }
+    float min_rq, max_rq;
+    orc_quantize_down_and_shrink_range(o_q, out_size, min_output_value, max_output_value, &min_rq, &max_rq, o_rq);
+    for (int i = 0; i < out_size; ++i) out[(size_t)n * out_size + i] = (float)o_rq[i];
+    out_r[2 * n] = min_rq;
+    out_r[2 * n + 1] = max_rq;
+  }
+  free(in_q);
+  free(W_q);
+  free(b_q);
+  free(o_q);
+  free(o_rq);
+  return 0;
+}
+
 /* ------------------------------------------------------------------------- */
 /* one training step of a sequential network                                   */
 /* ------------------------------------------------------------------------- */

@@ -449,6 +449,37 @@ REF_API int ref_qconv2d_fwd(const b200_conv_desc *d, const float *in, const floa
   return 0;
 }
 
+// tiny_quantized_conv2d_kernel, the nine-argument overload for chained quantized layers
+// (tiny_quantized_conv2d_kernel.h:353-466), once per sample as tiny_backend::conv2d_eq calls it
+// (backend_tiny.h:115-135).  `in`: PADDED rows of uint8 values held in floats.
+REF_API int ref_qconv2d_eq_fwd(const b200_conv_desc *d, const float *in, const float *W, const float *bias,
+                               const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r,
+                               int B) {
+  core::conv_params p;
+  p.in = shape3d(d->in_w, d->in_h, d->in_c);
+  p.in_padded = shape3d(d->inp_w, d->inp_h, d->in_c);
+  p.out = shape3d(d->out_w, d->out_h, d->out_c);
+  p.weight = shape3d(d->k_w, d->k_h, (size_t)d->in_c * d->out_c);
+  p.has_bias = d->has_bias != 0;
+  p.pad_type = d->pad_same ? padding::same : padding::valid;
+  p.w_stride = d->stride_w;
+  p.h_stride = d->stride_h;
+  p.w_dilation = p.h_dilation = 1;
+  p.tbl = make_table(d);
+  const size_t in_len = p.in_padded.size(), out_len = p.out.size(), lenW = p.weight.size();
+  vec_t vW(W, W + lenW), vb(d->out_c, 0.f), vWr(W_r, W_r + 2), vbr(b_r, b_r + 2);
+  if (d->has_bias) vb.assign(bias, bias + d->out_c);
+  for (int n = 0; n < B; ++n) {
+    vec_t vin(in + (size_t)n * in_len, in + (size_t)(n + 1) * in_len), vinr(in_r + 2 * n, in_r + 2 * n + 2);
+    vec_t va(out_len, 0.f), var(2, 0.f);
+    core::kernels::tiny_quantized_conv2d_kernel(p, vin, vW, vb, vinr, vWr, vbr, va, var, true);
+    std::copy(va.begin(), va.end(), out + (size_t)n * out_len);
+    out_r[2 * n] = var[0];
+    out_r[2 * n + 1] = var[1];
+  }
+  return 0;
+}
+
 // ---------------------------------------------------------------- whole network
 namespace {
 

@@ -216,6 +216,40 @@ QFC_CASES = {
 }
 
 
+# the forms for chained quantized layers: operands are uint8 values held in floats, with ranges
+QEQ_CONV_CASES = {"valid5x5": dict(seed=81), "stride2": dict(seed=82), "zero_bias": dict(seed=83, flat_filter_range=True)}
+QEQ_FC_CASES = {"small": dict(seed=84), "nobias": dict(seed=85), "wide": dict(seed=86, flat_ranges=True)}
+
+
+def gen_qeq_conv_inputs(name):
+    """(desc, x, W, bias, in_r, W_r, b_r) for QEQ_CONV_CASES[name] on the geometry of QCONV_CASES[name]."""
+    c, e = QCONV_CASES[name], QEQ_CONV_CASES[name]
+    d = conv_desc(c)
+    rng = np.random.default_rng(e["seed"])
+    B = c["B"]
+    x = rng.integers(0, 256, (B, d.in_c * d.inp_h * d.inp_w)).astype(np.float32)
+    W = rng.integers(0, 256, d.out_c * d.in_c * d.k_h * d.k_w).astype(np.float32)
+    bias = rng.integers(0, 256, d.out_c).astype(np.float32)
+    in_r = np.stack([np.array([-1.0 - 0.25 * n, 1.0 + 0.125 * n], np.float32) for n in range(B)])
+    W_r = np.array([0.25, 0.25] if e.get("flat_filter_range") else [-0.5, 0.5], np.float32)
+    b_r = np.array([-0.1, 0.1], np.float32)
+    return d, x, W, bias, np.ascontiguousarray(in_r), W_r, b_r
+
+
+def gen_qeq_fc_inputs(name):
+    c, e = QFC_CASES[name], QEQ_FC_CASES[name]
+    rng = np.random.default_rng(e["seed"])
+    B, I, O = c["B"], c["in"], c["out"]
+    x = rng.integers(0, 256, (B, I)).astype(np.float32)
+    W = rng.integers(0, 256, I * O).astype(np.float32)
+    bias = rng.integers(0, 256, O).astype(np.float32) if c["bias"] else None
+    in_r = np.stack([np.array([-1.0 - 0.25 * n, 1.0 + 0.125 * n], np.float32) for n in range(B)])
+    flat = e.get("flat_ranges")
+    W_r = np.array([0.25, 0.25] if flat else [-0.5, 0.5], np.float32)
+    b_r = np.array([0.05, 0.05] if flat else [-0.1, 0.1], np.float32)
+    return I, O, x, W, bias, np.ascontiguousarray(in_r), W_r, b_r
+
+
 def hyper_for(kind: int) -> OptHyper:
     """Default hyper-parameters of the reference optimizers (optimizer.h:57-58,104-110,203)."""
     if kind == 0:

@@ -602,6 +602,73 @@ static void ab_quantized() {
   }
 }
 
+// conv2d_eq / fully_eq of core::backend, called on the backend objects themselves: every constructor of
+// the quantized layers declares three inputs, so no layer of the tree reaches the six-input forms
+static void ab_quantized_eq() {
+  std::mt19937 g(5);
+  const size_t B = 3;
+  quantized_convolutional_layer owner(12, 12, 5, 5, 4, 6, padding::valid, true, 1, 1, core::backend_t::internal);
+  owner.set_parallelize(true);
+  core::conv_params p;
+  p.in = shape3d(12, 12, 4);
+  p.in_padded = p.in;
+  p.out = shape3d(8, 8, 6);
+  p.weight = shape3d(5, 5, 4 * 6);
+  p.has_bias = true;
+  p.pad_type = padding::valid;
+  p.w_stride = p.h_stride = 1;
+  p.w_dilation = p.h_dilation = 1;
+  core::conv_layer_worker_specific_storage store;
+  auto pad = [&](const tensor_t &in) {
+    store.prev_out_padded_.resize(in.size());
+    for (size_t s = 0; s < in.size(); ++s) store.prev_out_padded_[s] = &in[s];
+  };
+  core::tiny_backend cpu(&p, pad, [](const tensor_t &, tensor_t &) {},
+                         [](const tensor_t &, const tensor_t &, tensor_t &) {}, &store);
+  cpu.set_layer(&owner);
+  core::b200_backend dev(&p, pad, &store);
+  std::uniform_int_distribution<int> u8(0, 255);
+  tensor_t x(B, vec_t(p.in.size())), W(1, vec_t(p.weight.size())), b(1, vec_t(6)), xr(B, vec_t(2));
+  tensor_t Wr(1, vec_t{-0.5f, 0.5f}), br(1, vec_t{-0.1f, 0.1f});
+  for (size_t s = 0; s < B; ++s) {
+    for (auto &v : x[s]) v = static_cast<float>(u8(g));
+    xr[s][0] = -1.f - 0.25f * s;
+    xr[s][1] = 1.f + 0.125f * s;
+  }
+  for (auto &v : W[0]) v = static_cast<float>(u8(g));
+  for (auto &v : b[0]) v = static_cast<float>(u8(g));
+  tensor_t oa(B, vec_t(p.out.size())), oc(B, vec_t(p.out.size())), ra(B, vec_t(2)), rc(B, vec_t(2));
+  std::vector<tensor_t *> ins = {&x, &W, &b, &xr, &Wr, &br}, outa = {&oa, &ra}, outc = {&oc, &rc};
+  cpu.conv2d_eq(ins, outa);
+  dev.conv2d_eq(ins, outc);
+  bool same = true;
+  for (size_t s = 0; s < B; ++s)
+    same = same && std::memcmp(oa[s].data(), oc[s].data(), oa[s].size() * sizeof(float)) == 0 &&
+           std::memcmp(ra[s].data(), rc[s].data(), 2 * sizeof(float)) == 0;
+  expect(same, "conv2d_eq (uint8 values and ranges in and out) bit-exact against tiny_backend");
+
+  // fully_eq: tiny_backend's needs gemmlowp (backend_tiny.h:321-345), so only the call shape is
+  // exercised here; the values are pinned bit for bit by the library's own tests
+  core::fully_params fp;
+  fp.in_size_ = 40;
+  fp.out_size_ = 7;
+  fp.has_bias_ = true;
+  core::b200_backend devf(&fp);
+  tensor_t fx(B, vec_t(40)), fW(1, vec_t(40 * 7)), fb(1, vec_t(7)), fo(B, vec_t(7)), fr(B, vec_t(2));
+  for (auto &r : fx)
+    for (auto &v : r) v = static_cast<float>(u8(g));
+  for (auto &v : fW[0]) v = static_cast<float>(u8(g));
+  for (auto &v : fb[0]) v = static_cast<float>(u8(g));
+  std::vector<tensor_t *> fins = {&fx, &fW, &fb, &xr, &Wr, &br}, fouts = {&fo, &fr};
+  devf.fully_eq(fins, fouts);
+  bool sane = true;
+  for (size_t s = 0; s < B; ++s) {
+    sane = sane && fr[s][0] < fr[s][1];
+    for (float v : fo[s]) sane = sane && v >= 0.f && v <= 255.f && v == std::floor(v);
+  }
+  expect(sane, "fully_eq returns uint8 values and an ordered range");
+}
+
 int main() {
   try {
     {
@@ -679,6 +746,7 @@ int main() {
     ab_cifar_fit(256, false);  // the benchmarked batch
     ab_train_from_dataset_bytes();
     ab_quantized();
+    ab_quantized_eq();
     std::ostringstream os;
     os << core::backend_t::b200;
     if (os.str() != "B200") {

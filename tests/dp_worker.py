@@ -57,7 +57,8 @@ def run(rank, world, local, use_peer, steps, B):
     opt = nw.adam(1e-3)
     dp = DataParallel(net)
     if use_peer:
-        assert dp.enable_peer_reduce(), "peer mapping unavailable"
+        assert dp.enable_peer_reduce(rendezvous=use_peer), f"peer mapping by {use_peer} unavailable"
+        assert dp.rendezvous == use_peer
     for s in range(steps):
         xh, th = batch_of(rank, s, B)
         x, t = torch.from_numpy(xh).cuda(), torch.from_numpy(th).cuda()
@@ -73,11 +74,13 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     steps, B = 4, 16  # step 1 eager, step 2 captured, steps 3-4 replayed; both halves of the buffer twice
-    p_peer, p0 = run(rank, world, local, True, steps, B)
-    p_nccl, _ = run(rank, world, local, False, steps, B)
+    # the exchange buffers mapped by the library's own inter-process handles, then by torch symmetric memory
+    p_peer, p0 = run(rank, world, local, "ipc", steps, B)
+    p_symm, _ = run(rank, world, local, "symm", steps, B)
+    p_nccl, _ = run(rank, world, local, None, steps, B)
     gathered = [torch.empty_like(p_peer) for _ in range(world)]
     dist.all_gather(gathered, p_peer)
-    ok = all(torch.equal(gathered[0], g) for g in gathered)
+    ok = all(torch.equal(gathered[0], g) for g in gathered) and torch.equal(p_peer, p_symm)
     if world == 2:
         ok = ok and torch.equal(p_peer, p_nccl)
     else:

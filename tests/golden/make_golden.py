@@ -22,7 +22,8 @@ sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 
 import oracle_lib as o  # noqa: E402
-from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, bn_layers, gen_batchnorm_inputs,  # noqa: E402
+from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, QEQ_CONV_CASES, QEQ_FC_CASES,  # noqa: E402
+                   bn_layers, gen_batchnorm_inputs, gen_qeq_conv_inputs, gen_qeq_fc_inputs,
                    ACT_CASES, AVGPOOL_CASES, CONV_CASES, DATA_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,  # noqa: E402
                    QCONV_CASES, QFC_CASES, build_net_specs, conv_desc, dataset_file_bytes, gen_conv_inputs,
                    gen_dataset_bytes, gen_net_data, hyper_for, merge_rows_np, pool_desc, xavier_params, OPT_KINDS,
@@ -101,6 +102,22 @@ def main():
                                        o.p(dW), o.p(db), B) == 0
         out[f"avgpool/{name}/y"], out[f"avgpool/{name}/dx"] = y, dx
         put_grads(out, f"avgpool/{name}", dW, db)
+
+    # quantized layers chained without dequantizing: the reference's nine- / eleven-argument kernels
+    for name in QEQ_CONV_CASES:
+        d, x, W, bias, in_r, W_r, b_r = gen_qeq_conv_inputs(name)
+        B = x.shape[0]
+        y, yr = o.f32(B, d.out_c * d.out_h * d.out_w), o.f32(B, 2)
+        assert ref.ref_qconv2d_eq_fwd(C.byref(d), o.p(x), o.p(W), o.p(bias), o.p(in_r), o.p(W_r), o.p(b_r), o.p(y),
+                                      o.p(yr), B) == 0
+        out[f"qconv_eq/{name}/y"], out[f"qconv_eq/{name}/range"] = y, yr
+    for name in QEQ_FC_CASES:
+        I, O, x, W, bias, in_r, W_r, b_r = gen_qeq_fc_inputs(name)
+        B = x.shape[0]
+        y, yr = o.f32(B, O), o.f32(B, 2)
+        assert ref.ref_qfc_eq_fwd(I, O, o.p(x), o.p(W), o.p(bias), o.p(in_r), o.p(W_r), o.p(b_r), o.p(y), o.p(yr),
+                                  B) == 0
+        out[f"qfc_eq/{name}/y"], out[f"qfc_eq/{name}/range"] = y, yr
 
     for name, c in BATCHNORM_CASES.items():
         x, dy, run_mean, run_var = gen_batchnorm_inputs(c)

@@ -29,6 +29,8 @@ ORACLE_SIGS = {
     "orc_maxpool_bwd": (None, [_pd, _vp, _vp, _vp, _i]),
     "orc_avgpool_fwd": (None, [_pd, _vp, _vp, _vp, _vp, _i]),
     "orc_avgpool_bwd": (None, [_pd, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "orc_qconv2d_eq_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "orc_qfc_eq_fwd": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "orc_net_set_phase": (None, [_vp, _i]),
     "orc_net_bn_mean": (C.POINTER(C.c_float), [_vp, _i]),
     "orc_net_bn_var": (C.POINTER(C.c_float), [_vp, _i]),
@@ -84,6 +86,8 @@ REF_SIGS = {
     "ref_maxpool_fwd_bwd": (_i, [_pd, _i, _i, _vp, _vp, _vp, _vp, _i]),
     "ref_avgpool_fwd_bwd": (_i, [_pd, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "ref_act_fwd_bwd": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i]),
+    "ref_qconv2d_eq_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "ref_qfc_eq_fwd": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "ref_net_bn_stats": (_i, [_vp, _i, _vp, _vp]),
     "ref_batchnorm_fwd_bwd": (_i, [_i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "ref_lrn_fwd": (_i, [_vp, _vp, _i, _i, _i, _i, C.c_float, C.c_float, _i]),
@@ -162,7 +166,7 @@ def load_reference_avx():
         path = ROOT / "oracle" / "_ref" / "libtinydnn_ref_avx.so"
         if not path.exists():
             return None
-        sigs = {k: v for k, v in REF_SIGS.items() if k != "ref_qfc_fwd"}
+        sigs = {k: v for k, v in REF_SIGS.items() if k not in ("ref_qfc_fwd", "ref_qfc_eq_fwd")}
         _ref_avx = _bind(path, sigs)
     return _ref_avx
 

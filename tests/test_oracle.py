@@ -14,7 +14,8 @@ import numpy as np
 import pytest
 
 import oracle_lib as o
-from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, bn_layers, gen_batchnorm_inputs,
+from cases import (BATCHNORM_CASES, DROPOUT_CASES, LRN_CASES, QEQ_CONV_CASES, QEQ_FC_CASES, bn_layers,
+                   gen_batchnorm_inputs, gen_qeq_conv_inputs, gen_qeq_fc_inputs,
                    ACT_CASES, AVGPOOL_CASES, CONV_CASES, FC_CASES, MAXPOOL_CASES, NET_CASES,
                    QCONV_CASES, QFC_CASES, build_net_specs, conv_desc, gen_conv_inputs, gen_net_data,
                    hyper_for, merge_rows_np, pool_desc, xavier_params)
@@ -372,6 +373,29 @@ def test_gold_qfc(oracle, gold, name):
     y = o.f32(B, O)
     assert oracle.orc_qfc_fwd(I, O, o.p(x), o.p(W), o.p(b), o.p(y), B) == 0
     assert y.tobytes() == gold[f"qfc/{name}/y"].tobytes()
+
+
+@pytest.mark.parametrize("name", list(QEQ_CONV_CASES))
+def test_gold_qconv_eq(oracle, gold, name):
+    """The nine-argument quantized convolution kernel (uint8 values and ranges in and out): bit for bit."""
+    d, x, W, bias, in_r, W_r, b_r = gen_qeq_conv_inputs(name)
+    B = x.shape[0]
+    y, yr = o.f32(B, d.out_c * d.out_h * d.out_w), o.f32(B, 2)
+    assert oracle.orc_qconv2d_eq_fwd(C.byref(d), o.p(x), o.p(W), o.p(bias), o.p(in_r), o.p(W_r), o.p(b_r), o.p(y),
+                                     o.p(yr), B) == 0
+    assert y.tobytes() == gold[f"qconv_eq/{name}/y"].tobytes()
+    assert yr.tobytes() == gold[f"qconv_eq/{name}/range"].tobytes()
+    assert len(np.unique(y)) > 8  # the case exercises the requantizer, not a constant output
+
+
+@pytest.mark.parametrize("name", list(QEQ_FC_CASES))
+def test_gold_qfc_eq(oracle, gold, name):
+    I, O, x, W, bias, in_r, W_r, b_r = gen_qeq_fc_inputs(name)
+    B = x.shape[0]
+    y, yr = o.f32(B, O), o.f32(B, 2)
+    assert oracle.orc_qfc_eq_fwd(I, O, o.p(x), o.p(W), o.p(bias), o.p(in_r), o.p(W_r), o.p(b_r), o.p(y), o.p(yr), B) == 0
+    assert y.tobytes() == gold[f"qfc_eq/{name}/y"].tobytes()
+    assert yr.tobytes() == gold[f"qfc_eq/{name}/range"].tobytes()
 
 
 @pytest.mark.parametrize("name", list(NET_CASES))

@@ -9,7 +9,9 @@ import pytest
 import torch
 
 import oracle_lib as o
-from cases import QCONV_CASES, QCONV_ORACLE_ONLY, QFC_CASES, conv_desc, gen_conv_inputs
+from cases import (QCONV_CASES, QCONV_ORACLE_ONLY, QEQ_CONV_CASES, QEQ_FC_CASES, QFC_CASES, conv_desc, gen_conv_inputs,
+                   gen_qeq_conv_inputs, gen_qeq_fc_inputs)
+from tiny_cnn_b200._lib import check, ptr
 from test_ops_gpu import dev, host
 from tiny_cnn_b200 import ops
 
@@ -63,6 +65,40 @@ def test_qfc_bit_exact(ctx, oracle, gold, name):
     b = rng.uniform(-0.1, 0.1, O).astype(np.float32) if c["bias"] else None
     y = ops.quantized_fully_connected(ctx, I, O, dev(x), dev(W), dev(b))
     bit_equal(host(y), gold[f"qfc/{name}/y"], f"{name} vs reference")
+
+
+@pytest.mark.parametrize("name", list(QEQ_CONV_CASES))
+def test_qconv_eq_bit_exact(ctx, oracle, gold, name):
+    """tiny_backend::conv2d_eq's kernel: uint8 values held in floats and their ranges in and out."""
+    d, x, W, bias, in_r, W_r, b_r = gen_qeq_conv_inputs(name)
+    B = x.shape[0]
+    y = torch.empty(B, d.out_c * d.out_h * d.out_w, device="cuda")
+    yr = torch.empty(B, 2, device="cuda")
+    t = [dev(a) for a in (x, W, bias, in_r, W_r, b_r)]
+    check(ctx.lib.b200_qconv2d_eq_fwd(ctx.handle, C.byref(d), *[ptr(a) for a in t], ptr(y), ptr(yr), B))
+    bit_equal(host(y), gold[f"qconv_eq/{name}/y"], f"{name} values vs reference")
+    bit_equal(host(yr), gold[f"qconv_eq/{name}/range"], f"{name} range vs reference")
+    yh, yrh = np.empty((B, y.shape[1]), np.float32), np.empty((B, 2), np.float32)
+    check(ctx.lib.b200_qconv2d_eq_fwd_host(ctx.handle, C.byref(d), ptr(x), ptr(W), ptr(bias), ptr(in_r), ptr(W_r),
+                                           ptr(b_r), ptr(yh), ptr(yrh), B))
+    bit_equal(yh, gold[f"qconv_eq/{name}/y"], f"{name} host entry point")
+    bit_equal(yrh, gold[f"qconv_eq/{name}/range"], f"{name} host entry point range")
+
+
+@pytest.mark.parametrize("name", list(QEQ_FC_CASES))
+def test_qfc_eq_bit_exact(ctx, oracle, gold, name):
+    I, O, x, W, bias, in_r, W_r, b_r = gen_qeq_fc_inputs(name)
+    B = x.shape[0]
+    y, yr = torch.empty(B, O, device="cuda"), torch.empty(B, 2, device="cuda")
+    t = [dev(a) for a in (x, W, bias, in_r, W_r, b_r)]
+    check(ctx.lib.b200_qfc_eq_fwd(ctx.handle, I, O, *[ptr(a) for a in t], ptr(y), ptr(yr), B))
+    bit_equal(host(y), gold[f"qfc_eq/{name}/y"], f"{name} values vs reference")
+    bit_equal(host(yr), gold[f"qfc_eq/{name}/range"], f"{name} range vs reference")
+    yh, yrh = np.empty((B, O), np.float32), np.empty((B, 2), np.float32)
+    check(ctx.lib.b200_qfc_eq_fwd_host(ctx.handle, I, O, ptr(x), ptr(W), ptr(bias), ptr(in_r), ptr(W_r), ptr(b_r),
+                                       ptr(yh), ptr(yrh), B))
+    bit_equal(yh, gold[f"qfc_eq/{name}/y"], f"{name} host entry point")
+    bit_equal(yrh, gold[f"qfc_eq/{name}/range"], f"{name} host entry point range")
 
 
 def test_quantized_pipeline_config5(ctx, oracle):

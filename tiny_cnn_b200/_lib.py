@@ -134,6 +134,10 @@ SIGNATURES = {
     "b200_act_param_bwd_host": (_i, [_vp, _i, C.c_float, _vp, _vp, _vp, _i, _i]),
     "b200_act_fwd_host": (_i, [_vp, _i, _vp, _vp, _i, _i]),
     "b200_act_bwd_host": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i]),
+    "b200_qconv2d_eq_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "b200_qfc_eq_fwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "b200_qconv2d_eq_fwd_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "b200_qfc_eq_fwd_host": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "b200_net_set_phase": (_i, [_vp, _i]),
     "b200_net_bn_stats": (_i, [_vp, _i, _vp, _vp, _i]),
     "b200_batchnorm_fwd": (_i, [_vp, _i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i, _i]),
@@ -180,6 +184,10 @@ SIGNATURES = {
     "b200_net_peer_reduce": (_i, [_vp]),
     "b200_net_peer_push": (_i, [_vp]),
     "b200_net_peer_sum": (_i, [_vp]),
+    "b200_peer_buffer_create": (_i, [_vp, _sz, _vp, _vp]),
+    "b200_peer_buffer_open": (_i, [_vp, _vp, _vp]),
+    "b200_peer_buffer_close": (_i, [_vp, _vp]),
+    "b200_peer_buffer_destroy": (_i, [_vp, _vp]),
     "b200_net_train_step_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _oh, _vp]),
     "b200_net_fit_host": (_i, [_vp, _vp, _vp, C.c_longlong, _i, _i, _i, _i, _oh, _vp]),
     "b200_images_u8_to_float": (_i, [_vp, C.POINTER(ImageDesc), _vp, C.c_longlong, _vp]),

@@ -658,4 +658,59 @@ int b200_qfc_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in,
   return stage_out(ctx, b, 4);
 }
 
+// ---- quantized layers chained without dequantizing ("eq") --------------------------------------
+int b200_qconv2d_eq_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W, const float *bias,
+                        const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && in && W && in_r && W_r && b_r && out && out_r && batch >= 0, "qconv2d_eq_fwd: bad argument");
+  B200_REQUIRE(!d->has_bias || bias, "qconv2d_eq_fwd: the layer has a bias but none was given");
+  return qconv_eq_fwd(ctx, d, in, W, bias, in_r, W_r, b_r, out, out_r, batch);
+}
+int b200_qfc_eq_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W, const float *bias,
+                    const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in_size > 0 && out_size > 0 && in && W && in_r && W_r && b_r && out && out_r && batch >= 0,
+               "qfc_eq_fwd: bad argument");
+  return qfc_eq_fwd(ctx, in_size, out_size, in, W, bias, in_r, W_r, b_r, out, out_r, batch);
+}
+int b200_qconv2d_eq_fwd_host(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W,
+                             const float *bias, const float *in_r, const float *W_r, const float *b_r, float *out,
+                             float *out_r, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(d && batch >= 0, "qconv2d_eq_fwd_host: bad argument");
+  const size_t f = sizeof(float), in_len = (size_t)d->in_c * d->inp_h * d->inp_w;
+  HostBuf b[8] = {{in, nullptr, in_len * batch * f, nullptr},
+                  {W, nullptr, conv_w_len(d) * f, nullptr},
+                  {d->has_bias ? bias : nullptr, nullptr, d->has_bias ? d->out_c * f : 0, nullptr},
+                  {in_r, nullptr, (size_t)2 * batch * f, nullptr},
+                  {W_r, nullptr, 2 * f, nullptr},
+                  {b_r, nullptr, 2 * f, nullptr},
+                  {nullptr, out, conv_out_len(d) * batch * f, nullptr},
+                  {nullptr, out_r, (size_t)2 * batch * f, nullptr}};
+  B200_TRY(stage_in(ctx, b, 8));
+  B200_TRY(qconv_eq_fwd(ctx, d, (const float *)b[0].dev, (const float *)b[1].dev,
+                        d->has_bias ? (const float *)b[2].dev : nullptr, (const float *)b[3].dev,
+                        (const float *)b[4].dev, (const float *)b[5].dev, (float *)b[6].dev, (float *)b[7].dev, batch));
+  return stage_out(ctx, b, 8);
+}
+int b200_qfc_eq_fwd_host(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W, const float *bias,
+                         const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r, int batch) {
+  B200_TRY(check_ctx(ctx));
+  B200_REQUIRE(in_size > 0 && out_size > 0 && batch >= 0, "qfc_eq_fwd_host: bad argument");
+  const size_t f = sizeof(float);
+  HostBuf b[8] = {{in, nullptr, (size_t)in_size * batch * f, nullptr},
+                  {W, nullptr, (size_t)in_size * out_size * f, nullptr},
+                  {bias, nullptr, bias ? out_size * f : 0, nullptr},
+                  {in_r, nullptr, (size_t)2 * batch * f, nullptr},
+                  {W_r, nullptr, 2 * f, nullptr},
+                  {b_r, nullptr, 2 * f, nullptr},
+                  {nullptr, out, (size_t)out_size * batch * f, nullptr},
+                  {nullptr, out_r, (size_t)2 * batch * f, nullptr}};
+  B200_TRY(stage_in(ctx, b, 8));
+  B200_TRY(qfc_eq_fwd(ctx, in_size, out_size, (const float *)b[0].dev, (const float *)b[1].dev,
+                      bias ? (const float *)b[2].dev : nullptr, (const float *)b[3].dev, (const float *)b[4].dev,
+                      (const float *)b[5].dev, (float *)b[6].dev, (float *)b[7].dev, batch));
+  return stage_out(ctx, b, 8);
+}
+
 }  // extern "C"

@@ -350,5 +350,10 @@ int qconv_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const flo
               const float *bias, float *out, int B);
 int qfc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
             const float *bias, float *out, int B);
+// the forms for chained quantized layers: uint8 values held in floats with their ranges in and out
+int qconv_eq_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W, const float *bias,
+                 const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r, int B);
+int qfc_eq_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W, const float *bias,
+               const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r, int B);
 
 }  // namespace b200

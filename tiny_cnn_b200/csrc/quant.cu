@@ -265,10 +265,12 @@ __device__ __forceinline__ void block_minmax_atomic(int mn, int mx, int *gmin, i
 }
 
 // conv :89-133.  grid = (blocks per sample, B); one thread per output element.
+// `bias_f` != nullptr: the nine-argument kernel's bias term, `bias[o] - zero_in_total_space` formed
+// in FLOAT from the float-held bias entry and cast to int32 (tiny_quantized_conv2d_kernel.h:436-441)
 __global__ void q_conv_acc_kernel(ConvGeom g, const uint8_t *__restrict__ inq,
                                   const uint8_t *__restrict__ Wq, const uint8_t *__restrict__ bq,
                                   const QGlobal *__restrict__ qg, QSample *qs,
-                                  int *__restrict__ acc) {
+                                  int *__restrict__ acc, const float *__restrict__ bias_f) {
   const int n = blockIdx.y;
   const int out_len = g.OC * g.OH * g.OW;
   const int in_len = g.C * g.HI * g.WI;
@@ -292,7 +294,8 @@ __global__ void q_conv_acc_kernel(ConvGeom g, const uint8_t *__restrict__ inq,
         for (int wx = 0; wx < g.KW; ++wx)
           sum += ((int)w[wy * g.KW + wx] - off_f) * ((int)ip[wy * g.WI + wx] - off_in);
     }
-    if (g.has_bias) sum += (int)bq[o] - zero_total;
+    if (g.has_bias)
+      sum += bias_f != nullptr ? (int)__fsub_rn(bias_f[o], (float)zero_total) : (int)bq[o] - zero_total;
     acc[(size_t)n * out_len + idx] = sum;
     mn = min(mn, sum);
     mx = max(mx, sum);
@@ -654,6 +657,107 @@ __global__ void q_requant_dequant_kernel(const int *__restrict__ acc, size_t out
   }
 }
 
+// ---- 7. the forms for chained quantized layers ("eq") -----------------------------------------
+// Operands are uint8 values held in floats, with their ranges; the result leaves the same way
+// (tiny_quantized_conv2d_kernel.h:353-466, tiny_quantized_fully_connected_kernel.h:269-370).
+
+// ranges, offsets and the accumulator range of every sample from the supplied ranges
+__global__ void q_eq_params_kernel(QSample *qs, QGlobal *qg, const float *__restrict__ in_r,
+                                   const float *__restrict__ W_r, const float *__restrict__ b_r, int B, int fc,
+                                   int has_bias) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= B) return;
+  float min_f = W_r[0], max_f = W_r[1];
+  if (min_f == max_f) {
+    max_f = __fadd_rn(W_r[1], 1e-3f);
+    min_f = __fsub_rn(W_r[0], 1e-3f);
+  }
+  float min_b = 0.f, max_b = 0.f;
+  if (fc) {  // only the fully-connected kernel reads the bias range (:286-293, :313-314)
+    min_b = b_r[0];
+    max_b = b_r[1];
+    if (has_bias && min_b == max_b) {
+      max_b = __fadd_rn(b_r[1], 1e-3f);
+      min_b = __fsub_rn(b_r[0], 1e-3f);
+    }
+  }
+  QSample s = qs[n];
+  s.min_in = in_r[2 * n];
+  s.max_in = in_r[2 * n + 1];
+  const float c_level = __fmul_rn(one_level_u8(s.min_in, s.max_in), one_level_u8(min_f, max_f));
+  float mn = __fmul_rn(c_level, (float)(-(1LL << 31)));
+  float mx = __fmul_rn(c_level, (float)((1LL << 31) - 1));
+  if (fc) {
+    mn = __fadd_rn(mn, min_b);
+    mx = __fadd_rn(mx, max_b);
+  }
+  s.min_out = mn;
+  s.max_out = mx;
+  s.off_in = (int)f2q_unclamped<8>(0.0f, s.min_in, s.max_in);
+  s.zero_total = (int)f2q<32>(0.0f, mn, mx);
+  s.acc_min = INT_MAX;
+  s.acc_max = INT_MIN;
+  s.sum_in = 0;
+  qs[n] = s;
+  if (n == 0) {
+    qg->min_f = min_f;
+    qg->max_f = max_f;
+    qg->min_b = min_b;
+    qg->max_b = max_b;
+    qg->off_f = (int)f2q_unclamped<8>(0.0f, min_f, max_f);
+  }
+}
+
+// static_cast<uint8_t>(float) of values that are uint8 already
+__global__ void q_cast_u8_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst, size_t n) {
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) dst[i] = (uint8_t)__float2int_rz(src[i]);
+}
+
+// fully-connected accumulate on the reference's [in][out] byte filter: one thread per (sample, output)
+__global__ void q_fc_acc_kernel(int in_size, int out_size, int has_bias, const uint8_t *__restrict__ inq,
+                                const uint8_t *__restrict__ Wq, const uint8_t *__restrict__ bq,
+                                const QGlobal *__restrict__ qg, QSample *qs, int *__restrict__ acc) {
+  const int n = blockIdx.y;
+  const int off_f = qg->off_f, off_in = qs[n].off_in, zero_total = qs[n].zero_total;
+  const uint8_t *x = inq + (size_t)n * in_size;
+  int mn = INT_MAX, mx = INT_MIN;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < out_size; i += gridDim.x * blockDim.x) {
+    int sum = 0;
+    for (int c = 0; c < in_size; ++c) sum += ((int)Wq[(size_t)c * out_size + i] - off_f) * ((int)x[c] - off_in);
+    if (has_bias) sum += (int)bq[i] - zero_total;
+    acc[(size_t)n * out_size + i] = sum;
+    mn = min(mn, sum);
+    mx = max(mx, sum);
+  }
+  block_minmax_atomic(mn, mx, &qs[n].acc_min, &qs[n].acc_max);
+}
+
+// requantize to uint8 held in floats, and hand the shrunk range out (:455-465 / :358-369)
+__global__ void q_requant_u8_kernel(const int *__restrict__ acc, size_t out_len, const QSample *__restrict__ qs,
+                                    float *__restrict__ out, float *__restrict__ out_r) {
+  const int n = blockIdx.y;
+  const QSample s = qs[n];
+  const int *a = acc + (size_t)n * out_len;
+  float *o = out + (size_t)n * out_len;
+  const long long rounding_delta = 1LL << 15;
+  size_t step = (size_t)gridDim.x * blockDim.x;
+  for (size_t j = blockIdx.x * (size_t)blockDim.x + threadIdx.x; j < out_len; j += step) {
+    long long v = (long long)a[j];
+    long long fp_value = ((v * s.range_scale_fp) >> 32) + s.input_offset_fp;
+    long long ri = ((fp_value >= 0) ? (fp_value + rounding_delta) : (fp_value - rounding_delta)) >> 16;
+    long long q = ri - s.output_offset_fp;
+    q = q > 0 ? q : 0;
+    q = q < 255 ? q : 255;
+    o[j] = (float)q;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    out_r[2 * n] = s.min_new;
+    out_r[2 * n + 1] = s.max_new;
+  }
+}
+
 // ---- host side -------------------------------------------------------------------------
 
 static int blocks_for(size_t n, int block) {
@@ -766,7 +870,7 @@ int qconv_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const flo
                                                                              s.inq);
     B200_LAUNCHED();
     q_conv_acc_kernel<<<dim3(blocks_for(out_len, 256), B), 256, 0, st>>>(g, s.inq, s.Wq, s.bq,
-                                                                        s.qg, s.qs, s.acc);
+                                                                        s.qg, s.qs, s.acc, nullptr);
   }
   B200_LAUNCHED();
   q_requant_params_kernel<<<ceil_div(B, 128), 128, 0, st>>>(s.qs, B);
@@ -810,6 +914,65 @@ int qfc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const flo
   B200_LAUNCHED();
   q_requant_dequant_kernel<<<dim3(blocks_for(out_size, 256), B), 256, 0, st>>>(s.acc, out_size,
                                                                               s.qs, out);
+  B200_LAUNCHED();
+  return 0;
+}
+
+// tiny_backend::conv2d_eq (backend_tiny.h:115-135): padded rows of uint8 values held in floats
+int qconv_eq_fwd(b200_ctx *ctx, const b200_conv_desc *d, const float *in, const float *W, const float *bias,
+                 const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r, int B) {
+  b200_conv_desc dd = *d;
+  dd.input_is_padded = 1;
+  ConvGeom g;
+  B200_TRY(conv_geom_from_desc(ctx, &dd, &g));
+  B200_REQUIRE(g.DH == 1 && g.DW == 1, "quantized convolution has no dilation");
+  if (B == 0) return 0;
+  const size_t in_len = (size_t)g.HI * g.WI * g.C, out_len = (size_t)g.OC * g.OH * g.OW;
+  const size_t lenW = conv_weight_len(g);
+  QScratch s;
+  B200_TRY(q_carve(ctx, B, in_len, lenW, g.OC, out_len, &s));
+  cudaStream_t st = ctx->stream;
+  q_eq_params_kernel<<<ceil_div(B, 128), 128, 0, st>>>(s.qs, s.qg, in_r, W_r, b_r, B, 0, g.has_bias);
+  B200_LAUNCHED();
+  q_cast_u8_kernel<<<blocks_for(in_len * B, 256), 256, 0, st>>>(in, s.inq, in_len * B);
+  B200_LAUNCHED();
+  q_cast_u8_kernel<<<blocks_for(lenW, 256), 256, 0, st>>>(W, s.Wq, lenW);
+  B200_LAUNCHED();
+  q_conv_acc_kernel<<<dim3(blocks_for(out_len, 256), B), 256, 0, st>>>(g, s.inq, s.Wq, s.bq, s.qg, s.qs, s.acc,
+                                                                      g.has_bias ? bias : nullptr);
+  B200_LAUNCHED();
+  q_requant_params_kernel<<<ceil_div(B, 128), 128, 0, st>>>(s.qs, B);
+  B200_LAUNCHED();
+  q_requant_u8_kernel<<<dim3(blocks_for(out_len, 256), B), 256, 0, st>>>(s.acc, out_len, s.qs, out, out_r);
+  B200_LAUNCHED();
+  return 0;
+}
+
+// tiny_backend::fully_eq (backend_tiny.h:321-345)
+int qfc_eq_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W, const float *bias,
+               const float *in_r, const float *W_r, const float *b_r, float *out, float *out_r, int B) {
+  if (B == 0) return 0;
+  const size_t lenW = (size_t)in_size * out_size;
+  QScratch s;
+  B200_TRY(q_carve(ctx, B, in_size, lenW, out_size, out_size, &s));
+  cudaStream_t st = ctx->stream;
+  const int has_bias = bias != nullptr;
+  q_eq_params_kernel<<<ceil_div(B, 128), 128, 0, st>>>(s.qs, s.qg, in_r, W_r, b_r, B, 1, has_bias);
+  B200_LAUNCHED();
+  q_cast_u8_kernel<<<blocks_for((size_t)in_size * B, 256), 256, 0, st>>>(in, s.inq, (size_t)in_size * B);
+  B200_LAUNCHED();
+  q_cast_u8_kernel<<<blocks_for(lenW, 256), 256, 0, st>>>(W, s.Wq, lenW);
+  B200_LAUNCHED();
+  if (has_bias) {
+    q_cast_u8_kernel<<<blocks_for(out_size, 256), 256, 0, st>>>(bias, s.bq, out_size);
+    B200_LAUNCHED();
+  }
+  q_fc_acc_kernel<<<dim3(blocks_for(out_size, 128), B), 128, 0, st>>>(in_size, out_size, has_bias, s.inq, s.Wq, s.bq,
+                                                                     s.qg, s.qs, s.acc);
+  B200_LAUNCHED();
+  q_requant_params_kernel<<<ceil_div(B, 128), 128, 0, st>>>(s.qs, B);
+  B200_LAUNCHED();
+  q_requant_u8_kernel<<<dim3(blocks_for(out_size, 256), B), 256, 0, st>>>(s.acc, out_size, s.qs, out, out_r);
   B200_LAUNCHED();
   return 0;
 }

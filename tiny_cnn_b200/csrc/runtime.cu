@@ -182,6 +182,57 @@ int b200_ctx_create(int device, void *stream, b200_ctx **out) {
   return 0;
 }
 
+// ---------------------------------------------------------------- exchange buffers across processes
+static_assert(sizeof(cudaIpcMemHandle_t) <= B200_PEER_HANDLE_BYTES, "handle does not fit its ABI size");
+
+int b200_peer_buffer_create(b200_ctx *ctx, size_t bytes, void **dev, unsigned char *handle) {
+  B200_REQUIRE(ctx && dev && handle, "peer_buffer_create: NULL argument");
+  B200_REQUIRE(bytes > 0, "peer_buffer_create: empty buffer");
+  B200_CUDA(cudaSetDevice(ctx->device));
+  void *p = nullptr;
+  // a plain cudaMalloc: memory of a stream-ordered pool cannot be exported
+  B200_CUDA(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    B200_CUDA(e);
+  }
+  memset(handle, 0, B200_PEER_HANDLE_BYTES);
+  memcpy(handle, &h, sizeof(h));
+  *dev = p;
+  return 0;
+}
+
+int b200_peer_buffer_open(b200_ctx *ctx, const unsigned char *handle, void **dev) {
+  B200_REQUIRE(ctx && dev && handle, "peer_buffer_open: NULL argument");
+  B200_CUDA(cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void *p = nullptr;
+  B200_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *dev = p;
+  return 0;
+}
+
+int b200_peer_buffer_close(b200_ctx *ctx, void *dev) {
+  B200_REQUIRE(ctx != nullptr, "peer_buffer_close: NULL context");
+  if (!dev) return 0;
+  B200_CUDA(cudaSetDevice(ctx->device));
+  B200_CUDA(cudaIpcCloseMemHandle(dev));
+  return 0;
+}
+
+int b200_peer_buffer_destroy(b200_ctx *ctx, void *dev) {
+  B200_REQUIRE(ctx != nullptr, "peer_buffer_destroy: NULL context");
+  if (!dev) return 0;
+  B200_CUDA(cudaSetDevice(ctx->device));
+  B200_CUDA(cudaFree(dev));
+  return 0;
+}
+
 int b200_ctx_destroy(b200_ctx *ctx) {
   if (!ctx) return 0;
   cudaSetDevice(ctx->device);

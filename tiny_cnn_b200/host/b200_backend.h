@@ -65,7 +65,41 @@ class b200_backend : public backend {
     tiny_dnn::b200::unpack(y, out);
   }
 
-  void conv2d_eq(const std::vector<tensor_t *> &, std::vector<tensor_t *> &) override { na(); }
+  // tiny_backend::conv2d_eq (backend_tiny.h:115-135): in_data = data, W, bias, data range (2 floats
+  // per sample), W range, bias range; out_data = uint8 values held in floats, their range per sample
+  void conv2d_eq(const std::vector<tensor_t *> &in_data, std::vector<tensor_t *> &out_data) override {
+    pad_(*in_data[0]);
+    const std::vector<const vec_t *> &in = cws_->prev_out_padded_;
+    const vec_t &W = (*in_data[1])[0];
+    const vec_t &bias = (*in_data[2])[0];
+    const tensor_t &in_r = *in_data[3];
+    const vec_t &W_r = (*in_data[4])[0];
+    const vec_t &b_r = (*in_data[5])[0];
+    std::vector<uint8_t> tbl;
+    b200_conv_desc d = tiny_dnn::b200::conv_desc(*params_c_, tbl);
+    d.tbl = nullptr;
+    d.dil_w = d.dil_h = 1;
+    const size_t n_in = params_c_->in_padded.size(), n_out = params_c_->out.size(), B = in.size();
+    std::vector<float> x(B * n_in), y(B * n_out), xr(2 * B), yr(2 * B);
+    for (size_t s = 0; s < B; ++s) {
+      std::copy(in[s]->begin(), in[s]->begin() + n_in, x.begin() + s * n_in);
+      xr[2 * s] = in_r[s][0];
+      xr[2 * s + 1] = in_r[s][1];
+    }
+    if (!params_c_->tbl.is_empty()) {
+      tbl.assign(params_c_->tbl.connected_.begin(), params_c_->tbl.connected_.end());
+      d.tbl = tbl.data();
+    }
+    tiny_dnn::b200::check(b200_qconv2d_eq_fwd_host(tiny_dnn::b200::ctx(), &d, x.data(), W.data(),
+                                                   params_c_->has_bias ? bias.data() : nullptr, xr.data(), W_r.data(),
+                                                   b_r.data(), y.data(), yr.data(), static_cast<int>(B)));
+    tiny_dnn::b200::unpack(y, *out_data[0]);
+    tensor_t &out_r = *out_data[1];
+    for (size_t s = 0; s < B; ++s) {
+      out_r[s][0] = yr[2 * s];
+      out_r[s][1] = yr[2 * s + 1];
+    }
+  }
   void conv2d_q(const std::vector<tensor_t *> &, const std::vector<tensor_t *> &,
                 std::vector<tensor_t *> &, std::vector<tensor_t *> &) override { na(); }
   void deconv2d(const std::vector<tensor_t *> &, std::vector<tensor_t *> &) override { na(); }
@@ -75,7 +109,30 @@ class b200_backend : public backend {
                 std::vector<tensor_t *> &, std::vector<tensor_t *> &) override { na(); }
   void deconv2d_q(const std::vector<tensor_t *> &, const std::vector<tensor_t *> &,
                   std::vector<tensor_t *> &, std::vector<tensor_t *> &) override { na(); }
-  void fully_eq(const std::vector<tensor_t *> &, std::vector<tensor_t *> &) override { na(); }
+  // tiny_backend::fully_eq (backend_tiny.h:321-345)
+  void fully_eq(const std::vector<tensor_t *> &in_data, std::vector<tensor_t *> &out_data) override {
+    const tensor_t &in = *in_data[0];
+    const vec_t &W = (*in_data[1])[0];
+    const tensor_t &in_r = *in_data[3];
+    const vec_t &W_r = (*in_data[4])[0];
+    const vec_t &b_r = (*in_data[5])[0];
+    const size_t B = in.size();
+    std::vector<float> x = tiny_dnn::b200::pack(in), y(B * params_f_->out_size_), xr(2 * B), yr(2 * B);
+    for (size_t s = 0; s < B; ++s) {
+      xr[2 * s] = in_r[s][0];
+      xr[2 * s + 1] = in_r[s][1];
+    }
+    tiny_dnn::b200::check(b200_qfc_eq_fwd_host(
+      tiny_dnn::b200::ctx(), static_cast<int>(params_f_->in_size_), static_cast<int>(params_f_->out_size_), x.data(),
+      W.data(), params_f_->has_bias_ ? (*in_data[2])[0].data() : nullptr, xr.data(), W_r.data(), b_r.data(), y.data(),
+      yr.data(), static_cast<int>(B)));
+    tiny_dnn::b200::unpack(y, *out_data[0]);
+    tensor_t &out_r = *out_data[1];
+    for (size_t s = 0; s < B; ++s) {
+      out_r[s][0] = yr[2 * s];
+      out_r[s][1] = yr[2 * s + 1];
+    }
+  }
   void fully_q(const std::vector<tensor_t *> &, const std::vector<tensor_t *> &,
                std::vector<tensor_t *> &, std::vector<tensor_t *> &) override { na(); }
 
