@@ -251,23 +251,34 @@ int gemm_tc(b200_ctx *ctx, int M, int N, int K, const float *src_a, long long ld
 size_t fc_scratch_floats(const b200_ctx *ctx, int in_size, int out_size, int B);
 int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
            const float *bias, float *out, int B, int act, float *scratch);
+// A kernel that runs beside the persistent tensor-core kernels asks for their shared-memory carve-out
+// (the largest): an SM whose carve-out has to change between two kernels must drain first.
+int carveout_once(const void *kernel);
+#define B200_CARVEOUT(kernel)                                                          \
+  do {                                                                                 \
+    static const int b200_carveout_done_ = ::b200::carveout_once((const void *)(kernel)); \
+    (void)b200_carveout_done_;                                                         \
+  } while (0)
+
 // sum of a bucket over the ranks of a data-parallel job through peer memory (peer_reduce.cu)
 struct PeerReduce {
   int rank = 0, world = 0;
   long long n = 0;
   long long split = 0;           // [split, n) is pushed early, [0, split) by the summing kernel
+  long long ll_n = 0;            // words per rank and half when the late region travels as flagged 8-byte words
   unsigned long long timeout_ns = 0;
   float **bases_dev = nullptr;   // [world] every rank's buffer as mapped in this process
   unsigned *step_dev = nullptr;  // [0] reductions done so far, [1] blocks of the running sum that ended
 };
-size_t peer_reduce_bytes(long long n, int world);
+size_t peer_reduce_bytes(long long n, long long split, int world);
 // `timeout_ms` bounds every wait of the summing kernel (0 = 10 s)
 int peer_reduce_init(b200_ctx *ctx, PeerReduce *pr, long long n, long long split, int rank, int world,
                      const unsigned long long *bases, int timeout_ms);
 void peer_reduce_free(PeerReduce *pr);
 int peer_reduce_push_early(b200_ctx *ctx, const PeerReduce *pr, float *grads);
 int peer_reduce_push_all(b200_ctx *ctx, const PeerReduce *pr, float *grads);
-int peer_reduce_finish(b200_ctx *ctx, const PeerReduce *pr, float *grads, int late_pushed);
+int peer_reduce_sum_early(b200_ctx *ctx, const PeerReduce *pr, float *grads);
+int peer_reduce_finish(b200_ctx *ctx, const PeerReduce *pr, float *grads, int late_pushed, int early_summed);
 int peer_reduce_run(b200_ctx *ctx, const PeerReduce *pr, float *grads);
 
 int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,

@@ -101,6 +101,8 @@ struct b200_net {
   int peer_early_layer = -1;
   cudaStream_t comm = nullptr;
   cudaEvent_t ev_comm_main = nullptr, ev_comm_side = nullptr, ev_comm_done = nullptr;
+  bool peer_early_sum = true;   // sum the early region on the communication stream (B200_PEER_EARLY_SUM=0: in the last kernel)
+  bool early_summed = false;    // the backward pass just issued did so
   // captured launch sequences: slot 0 = whole step, slot 1 = forward + backward.  A slot keeps
   // the graphs of the last few configurations (buffers, batch size, hyper-parameters), so the
   // ragged last mini-batch of an epoch does not evict the graph of the full ones.
@@ -276,6 +278,7 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
   cudaStream_t main_stream = ctx->stream;
   bool side_used = false, comm_used = false;
   int rc_side = 0;
+  net->early_summed = false;
   // One side branch, not one per layer: the large kernels of both branches each fill the SMs, so
   // more branches only interleave them and delay the dX chain (measured: two branches 0.387 ms
   // against 0.374 ms with one).
@@ -428,6 +431,11 @@ int net_backward_impl(b200_net *net, const float *t, int loss_kind, bool peer_in
       }
       ctx->stream = net->comm;
       int rc = peer_reduce_push_early(ctx, &net->peer, net->grads);
+      // ... and add the other ranks' copies as they arrive, still beside the remaining layers
+      if (rc == 0 && net->peer_early_sum) {
+        rc = peer_reduce_sum_early(ctx, &net->peer, net->grads);
+        net->early_summed = rc == 0;
+      }
       ctx->stream = main_stream;
       B200_TRY(rc);
       B200_CUDA(cudaEventRecord(net->ev_comm_done, net->comm));
@@ -505,7 +513,7 @@ int step_eager(b200_net *net, const float *x, const float *t, int B, int loss_ki
   B200_TRY(net_backward_impl(net, t, loss_kind, early));
   if (peer) {
     if (!early) B200_TRY(peer_reduce_push_early(net->ctx, &net->peer, net->grads));
-    B200_TRY(peer_reduce_finish(net->ctx, &net->peer, net->grads, 0));
+    B200_TRY(peer_reduce_finish(net->ctx, &net->peer, net->grads, 0, early && net->early_summed));
   }
   return net_update_impl(net, opt_kind, h);
 }
@@ -898,17 +906,10 @@ int b200_net_opt_reset(b200_net *net, int reset_powers) {
   return 0;
 }
 
-size_t b200_net_peer_reduce_bytes(b200_net *net, int world) {
-  if (!net || world < 2) return 0;
-  return peer_reduce_bytes((long long)net->n_params, world);
-}
-
-int b200_net_peer_reduce_init(b200_net *net, int rank, int world, const unsigned long long *buffers,
-                              int timeout_ms) {
-  B200_TRY(check_net(net));
-  // The first layer with parameters finishes its gradients last; everything after it in the
-  // bucket can leave early.  The boundary is rounded up to 16 bytes (entries below it that are
-  // ready early simply travel with the late part).
+// The first layer with parameters finishes its gradients last; everything after it in the
+// bucket can leave early.  The boundary is rounded up to 16 bytes (entries below it that are
+// ready early simply travel with the late part).
+static long long peer_split_of(const b200_net *net, int *early_layer) {
   int first = -1, second = -1;
   for (int i = 0; i < (int)net->layers.size(); ++i) {
     if (net->layers[i].w_len == 0 && net->layers[i].b_len == 0) continue;
@@ -921,8 +922,22 @@ int b200_net_peer_reduce_init(b200_net *net, int rank, int world, const unsigned
     split = (long long)((L.w_len ? L.w_off : L.b_off) + 3) / 4 * 4;
     if (split > n) split = n;
   }
-  net->peer_early_layer = split < n ? second : -1;
+  if (early_layer) *early_layer = split < n ? second : -1;
+  return split;
+}
+
+size_t b200_net_peer_reduce_bytes(b200_net *net, int world) {
+  if (!net || world < 2) return 0;
+  return peer_reduce_bytes((long long)net->n_params, peer_split_of(net, nullptr), world);
+}
+
+int b200_net_peer_reduce_init(b200_net *net, int rank, int world, const unsigned long long *buffers,
+                              int timeout_ms) {
+  B200_TRY(check_net(net));
+  const long long n = (long long)net->n_params;
+  const long long split = peer_split_of(net, &net->peer_early_layer);
   B200_TRY(peer_reduce_init(net->ctx, &net->peer, n, split, rank, world, buffers, timeout_ms));
+  if (const char *e = getenv("B200_PEER_EARLY_SUM")) net->peer_early_sum = atoi(e) != 0;
   if (!net->comm) {
     B200_CUDA(cudaStreamCreateWithFlags(&net->comm, cudaStreamNonBlocking));
     B200_CUDA(cudaEventCreateWithFlags(&net->ev_comm_main, cudaEventDisableTiming));
@@ -949,7 +964,7 @@ int b200_net_peer_push(b200_net *net) {
 int b200_net_peer_sum(b200_net *net) {
   B200_TRY(check_net(net));
   B200_REQUIRE(net->peer.world > 1, "net_peer_sum: b200_net_peer_reduce_init was not called");
-  return peer_reduce_finish(net->ctx, &net->peer, net->grads, 1);
+  return peer_reduce_finish(net->ctx, &net->peer, net->grads, 1, 0);
 }
 
 int b200_net_update(b200_net *net, int opt_kind, const b200_opt_hyper *h) {

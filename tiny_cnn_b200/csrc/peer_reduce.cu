@@ -5,7 +5,8 @@
 // per-sample gradients of ONE mini-batch; replicas extend that sum across GPUs, with no 1/N).
 //
 // Every rank owns a buffer that all ranks have mapped ("symmetric" memory):
-//   slots[2][world][npad] floats, then flags[2][2][PR_CHUNKS] counters
+//   slots[2][world][npad] floats, then flags[2][2][PR_CHUNKS] counters, then words[2][world][ll_n]
+//   8-byte words (only when the late region is small, see below)
 // A step uses the half `step & 1`.  The bucket has two regions:
 //   early = [split, n)  gradients that are final long before the backward pass ends (every layer
 //                       but the first one with parameters); pushed from a side branch of the step
@@ -26,6 +27,12 @@
 // ranks (restart from a checkpoint).  A half is reused only two steps later, after every rank has
 // passed the step in between.  Every load is CTA-local or a plain load of this GPU's own memory;
 // the peers are only written.
+// A SMALL late region (at most PR_LL_MAX floats -- the first layer of a convolutional net) travels as
+// flagged words instead: every float is stored to the peers as ONE aligned 8-byte scalar
+// {value, step + 1}, which arrives whole, and the summing thread polls the word in its own memory
+// until the flag is this step's.  No fence, no counter, no second trip over NVLink: the late
+// region sits on the critical path of the step (it leaves when the backward pass has ended), and
+// store -> fence -> counter -> poll costs three NVLink traversals where this costs one.
 #include "common.cuh"
 #include "device_utils.cuh"
 
@@ -35,6 +42,19 @@ namespace {
 
 constexpr int PR_CHUNKS = 128;   // blocks: all resident at once on 148 SMs
 constexpr int PR_THREADS = 256;
+constexpr long long PR_LL_MAX = 65536;  // floats: above this, bandwidth matters more than latency
+
+// one float and the flag of its step as a single 8-byte scalar store / load: single-copy atomic
+__device__ __forceinline__ void st_word_sys(unsigned long long *dst, float v, unsigned flag) {
+  const unsigned long long w = ((unsigned long long)flag << 32) | (unsigned long long)__float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(w) : "memory");
+}
+__device__ __forceinline__ bool ld_word_sys(const unsigned long long *src, unsigned flag, float *v) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];\n" : "=l"(w) : "l"(src) : "memory");
+  *v = __uint_as_float((unsigned)(w & 0xffffffffull));
+  return (unsigned)(w >> 32) == flag;
+}
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
   unsigned v;
@@ -51,6 +71,7 @@ struct PeerArgs {
   long long n, npad;         // floats; npad is a multiple of 4
   long long lo[2], chunk[2]; // region r = [lo[r], hi[r]) cut into PR_CHUNKS chunks of chunk[r] floats
   long long hi[2];           // lo, chunk multiples of 4
+  long long ll_n;            // words per rank and half of the flagged-word area; 0 = the late region uses slots + counters
   unsigned long long timeout_ns;
 };
 
@@ -96,12 +117,34 @@ __device__ __forceinline__ void push_and_signal(const PeerArgs &a, int region, i
   }
 }
 
+// the flagged-word area of rank p's buffer: words[half][source rank][ll_n]
+__device__ __forceinline__ unsigned long long *words_of(const PeerArgs &a, int p, int half, int src) {
+  const size_t before = ((size_t)2 * a.world * a.npad + (size_t)4 * PR_CHUNKS) * sizeof(float);  // bytes, a multiple of 16
+  return reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(a.bases[p]) + before) +
+         ((size_t)half * a.world + src) * a.ll_n;
+}
+
+// late chunk b as flagged words into every other rank's buffer; waits for nothing, signals nothing
+__device__ __forceinline__ void push_words(const PeerArgs &a, int half, unsigned flag, int b) {
+  long long c0, c1;
+  chunk_range(a, 0, b, &c0, &c1);
+  for (long long i = c0 + threadIdx.x; i < c1; i += PR_THREADS) {
+    const float v = a.grads[i];
+    for (int p = 0; p < a.world; ++p)
+      if (p != a.rank) st_word_sys(words_of(a, p, half, a.rank) + i, v, flag);
+  }
+}
+
 // regions: bit 0 = late [0, split), bit 1 = early [split, n)
 __global__ void __launch_bounds__(PR_THREADS) peer_push_kernel(const PeerArgs a, int regions) {
   const int b = blockIdx.x;
-  const int half = (int)(*a.step & 1u);
+  const unsigned step = *a.step;
+  const int half = (int)(step & 1u);
   if (regions & 2) push_and_signal(a, 1, half, b);
-  if (regions & 1) push_and_signal(a, 0, half, b);
+  if (regions & 1) {
+    if (a.ll_n) push_words(a, half, step + 1u, b);
+    else push_and_signal(a, 0, half, b);
+  }
 }
 
 // the last block of the summing kernel to end closes this use of the buffer half: every block has
@@ -118,14 +161,21 @@ __device__ __forceinline__ void sum_block_done(const PeerArgs &a) {
   }
 }
 
-__global__ void __launch_bounds__(PR_THREADS) peer_sum_kernel(const PeerArgs a, int push_late) {
+// regions: bit 0 = late, bit 1 = early -- the regions this launch waits for and sums; `advance`: this
+// launch is the last one of the step that uses the buffer half
+__global__ void __launch_bounds__(PR_THREADS) peer_sum_kernel(const PeerArgs a, int push_late, int regions,
+                                                              int advance) {
   __shared__ int s_fail;
   const int tid = threadIdx.x, b = blockIdx.x;
   const unsigned step = *a.step;
   const int half = (int)(step & 1u);
   const unsigned target = (step / 2u + 1u) * (unsigned)a.world;  // additions a flag has seen after this use
   const size_t flag_off = (size_t)2 * a.world * a.npad;
-  if (push_late) push_and_signal(a, 0, half, b);
+  const bool words = a.ll_n != 0;  // the late region travels as flagged words
+  if (push_late) {
+    if (words) push_words(a, half, step + 1u, b);
+    else push_and_signal(a, 0, half, b);
+  }
   long long c0[2], c1[2];
   chunk_range(a, 0, b, &c0[0], &c1[0]);
   chunk_range(a, 1, b, &c0[1], &c1[1]);
@@ -135,7 +185,7 @@ __global__ void __launch_bounds__(PR_THREADS) peer_sum_kernel(const PeerArgs a, 
     int fail = 0;
     unsigned long long t0 = 0, t1;
     for (int region = 0; region < 2 && !fail; ++region) {
-      if (c0[region] >= c1[region]) continue;
+      if (!(regions >> region & 1) || c0[region] >= c1[region] || (region == 0 && words)) continue;
       const unsigned *mine = flags + region * PR_CHUNKS;
       if (ld_acquire_sys(mine) >= target) continue;
       if (!t0) asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
@@ -155,12 +205,44 @@ __global__ void __launch_bounds__(PR_THREADS) peer_sum_kernel(const PeerArgs a, 
   __syncthreads();
   if (s_fail) {
     if (tid == 0 && a.err) atomicExch(a.err, 7);
-    sum_block_done(a);
+    if (advance) sum_block_done(a);
     return;
   }
   // sum the slots in rank order; the peers' stores sit in this GPU's memory / L2, not in this SM's L1
   const float *slots = a.bases[a.rank] + (size_t)half * a.world * a.npad;
-  for (int region = 0; region < 2; ++region) {
+  if (words && (regions & 1)) {
+    // every thread polls the words of its own floats, rank by rank: the sum keeps the rank order
+    const unsigned flag = step + 1u;
+    unsigned long long t0 = 0, t1;
+    bool fail = false;
+    for (long long i = c0[0] + tid; i < c1[0] && !fail; i += PR_THREADS) {
+      float sum = 0.f;
+      for (int r = 0; r < a.world && !fail; ++r) {
+        float v;
+        if (r == a.rank) {
+          v = a.grads[i];
+        } else {
+          const unsigned long long *w = words_of(a, a.rank, half, r) + i;
+          while (!ld_word_sys(w, flag, &v)) {
+            bool done = false;
+            for (int k = 0; k < 64 && !done; ++k) done = ld_word_sys(w, flag, &v);
+            if (done) break;
+            if (!t0) asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
+            if (t1 - t0 > a.timeout_ns) {
+              fail = true;
+              break;
+            }
+          }
+        }
+        sum = r == 0 ? v : __fadd_rn(sum, v);
+      }
+      if (!fail) a.grads[i] = sum;
+    }
+    if (fail && a.err) atomicExch(a.err, 7);
+  }
+  for (int region = words ? 1 : 0; region < 2; ++region) {
+    if (!(regions >> region & 1)) continue;
     for (long long i = c0[region] + 4 * tid; i < c1[region]; i += 4 * PR_THREADS) {
       if (i + 4 <= c1[region]) {
         float4 s = __ldcg(reinterpret_cast<const float4 *>(slots + i));
@@ -181,7 +263,7 @@ __global__ void __launch_bounds__(PR_THREADS) peer_sum_kernel(const PeerArgs a, 
       }
     }
   }
-  sum_block_done(a);
+  if (advance) sum_block_done(a);
 }
 
 long long pr_npad(long long n) { return (n + 3) / 4 * 4; }
@@ -205,6 +287,7 @@ PeerArgs make_args(b200_ctx *ctx, const PeerReduce *pr, float *grads) {
     long long c = (len + PR_CHUNKS - 1) / PR_CHUNKS;
     a.chunk[r] = (c + 3) / 4 * 4;
   }
+  a.ll_n = pr->ll_n;
   a.timeout_ns = pr->timeout_ns;
   return a;
 }
@@ -218,8 +301,11 @@ int check_run(const PeerReduce *pr, const float *grads) {
 }  // namespace
 
 // bytes of the buffer every rank must provide (zero-filled, mapped by all ranks)
-size_t peer_reduce_bytes(long long n, int world) {
-  return ((size_t)2 * world * pr_npad(n)) * sizeof(float) + (size_t)4 * PR_CHUNKS * sizeof(unsigned);
+long long peer_reduce_words(long long split) { return split > 0 && split <= PR_LL_MAX ? pr_npad(split) : 0; }
+
+size_t peer_reduce_bytes(long long n, long long split, int world) {
+  return ((size_t)2 * world * pr_npad(n)) * sizeof(float) + (size_t)4 * PR_CHUNKS * sizeof(unsigned) +
+         (size_t)2 * world * peer_reduce_words(split) * sizeof(unsigned long long);
 }
 
 int peer_reduce_init(b200_ctx *ctx, PeerReduce *pr, long long n, long long split, int rank, int world,
@@ -236,12 +322,22 @@ int peer_reduce_init(b200_ctx *ctx, PeerReduce *pr, long long n, long long split
   pr->world = world;
   pr->n = n;
   pr->split = split;
+  pr->ll_n = peer_reduce_words(split);
+  if (const char *e = getenv("B200_PEER_WORDS"))
+    if (atoi(e) == 0) pr->ll_n = 0;  // the buffer has room for the words either way
   pr->timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1000000ull;
   B200_CUDA(cudaMalloc(&pr->bases_dev, sizeof(float *) * world));
   B200_CUDA(cudaMemcpy(pr->bases_dev, bases, sizeof(float *) * world, cudaMemcpyHostToDevice));
   B200_CUDA(cudaMalloc(&pr->step_dev, 2 * sizeof(unsigned)));
   B200_CUDA(cudaMemset(pr->step_dev, 0, 2 * sizeof(unsigned)));
   (void)ctx;
+  // these kernels run beside the persistent tensor-core kernels, which hold the largest shared-memory
+  // carve-out of an SM; asking for the same carve-out keeps an SM from being reconfigured between them
+  const char *co = getenv("B200_PEER_CARVEOUT");
+  if (!co || atoi(co) != 0) {
+    cudaFuncSetAttribute(peer_push_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(peer_sum_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  }
   return 0;
 }
 
@@ -271,11 +367,22 @@ int peer_reduce_push_all(b200_ctx *ctx, const PeerReduce *pr, float *grads) {
   return 0;
 }
 
-// (push the late region unless `late_pushed`,) wait for every rank's regions and replace `grads`
-// by the sum over the ranks; ends this use of the buffer half
-int peer_reduce_finish(b200_ctx *ctx, const PeerReduce *pr, float *grads, int late_pushed) {
+// wait for every rank's early region and sum it, on the stream the early push went to: by the end of
+// the backward pass only the late region is left.  Does not end the use of the buffer half.
+int peer_reduce_sum_early(b200_ctx *ctx, const PeerReduce *pr, float *grads) {
   B200_TRY(check_run(pr, grads));
-  peer_sum_kernel<<<PR_CHUNKS, PR_THREADS, 0, ctx->stream>>>(make_args(ctx, pr, grads), late_pushed ? 0 : 1);
+  if (pr->split >= pr->n) return 0;
+  peer_sum_kernel<<<PR_CHUNKS, PR_THREADS, 0, ctx->stream>>>(make_args(ctx, pr, grads), 0, 2, 0);
+  B200_LAUNCHED();
+  return 0;
+}
+
+// (push the late region unless `late_pushed`,) wait for every rank's regions -- the late one only when
+// `early_summed` -- and replace `grads` by the sum over the ranks; ends this use of the buffer half
+int peer_reduce_finish(b200_ctx *ctx, const PeerReduce *pr, float *grads, int late_pushed, int early_summed) {
+  B200_TRY(check_run(pr, grads));
+  peer_sum_kernel<<<PR_CHUNKS, PR_THREADS, 0, ctx->stream>>>(make_args(ctx, pr, grads), late_pushed ? 0 : 1,
+                                                            early_summed ? 1 : 3, 1);
   B200_LAUNCHED();
   return 0;
 }
@@ -283,7 +390,7 @@ int peer_reduce_finish(b200_ctx *ctx, const PeerReduce *pr, float *grads, int la
 // the whole reduction on one stream: early push, then late push + wait + sum
 int peer_reduce_run(b200_ctx *ctx, const PeerReduce *pr, float *grads) {
   B200_TRY(peer_reduce_push_early(ctx, pr, grads));
-  return peer_reduce_finish(ctx, pr, grads, 0);
+  return peer_reduce_finish(ctx, pr, grads, 0, 0);
 }
 
 }  // namespace b200
