@@ -401,7 +401,6 @@ int fc_softmax_fwd(b200_ctx *ctx, int K, int N, const float *x, const float *W, 
                    int B) {
   B200_REQUIRE(fc_softmax_fusable(K, N), "fc_softmax_fwd: shape %d x %d not supported", K, N);
   if (B == 0) return 0;
-  B200_CARVEOUT((fc_softmax_fwd16_kernel));
   fc_softmax_fwd16_kernel<<<ceil_div(B * 16, FCS_THREADS), FCS_THREADS, (size_t)K * N * sizeof(float), ctx->stream>>>(
     x, W, bias, z, y, K, N, B);
   B200_LAUNCHED();
@@ -414,7 +413,6 @@ int fc_softmax_loss_bwd(b200_ctx *ctx, int loss_kind, int K, int N, const float 
   B200_REQUIRE(loss_kind >= B200_LOSS_MSE && loss_kind <= B200_LOSS_CROSS_ENTROPY_MULTICLASS,
                "fc_softmax_loss_bwd: unknown loss %d", loss_kind);
   if (B == 0) return 0;
-  B200_CARVEOUT((fc_softmax_bwd16_kernel));
   fc_softmax_bwd16_kernel<<<ceil_div(B * 16, FCS_THREADS), FCS_THREADS, (size_t)K * N * sizeof(float), ctx->stream>>>(
     y, t, loss_kind, W, relu_x, dy, dz, dx, K, N, B);
   B200_LAUNCHED();

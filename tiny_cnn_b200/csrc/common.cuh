@@ -251,15 +251,6 @@ int gemm_tc(b200_ctx *ctx, int M, int N, int K, const float *src_a, long long ld
 size_t fc_scratch_floats(const b200_ctx *ctx, int in_size, int out_size, int B);
 int fc_fwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const float *W,
            const float *bias, float *out, int B, int act, float *scratch);
-// A kernel that runs beside the persistent tensor-core kernels asks for their shared-memory carve-out
-// (the largest): an SM whose carve-out has to change between two kernels must drain first.
-int carveout_once(const void *kernel);
-#define B200_CARVEOUT(kernel)                                                          \
-  do {                                                                                 \
-    static const int b200_carveout_done_ = ::b200::carveout_once((const void *)(kernel)); \
-    (void)b200_carveout_done_;                                                         \
-  } while (0)
-
 // sum of a bucket over the ranks of a data-parallel job through peer memory (peer_reduce.cu)
 struct PeerReduce {
   int rank = 0, world = 0;

@@ -904,7 +904,6 @@ int to_tall(b200_ctx *ctx, const TallSrc &src, int C, int H, int W, int Cp, int 
   auto launch = [&](auto kernel) -> int {
     if (smem > 48 * 1024)
       B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    carveout_once((const void *)kernel);  // every instantiation shares this lambda: no once-flag here
     kernel<<<B * chunks, 256, smem, ctx->stream>>>(src, C, H, W, Cp, period, rb, pitch, dst, dst + one, bsum);
     B200_LAUNCHED();
     return 0;
@@ -1030,7 +1029,6 @@ int conv_tc_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, float *wt_fwd
   long long total = t0 > t1 ? t0 : t1;
   int blocks = (int)((total + 255) / 256);
   if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-  B200_CARVEOUT((tc_filter_prep_kernel));
   tc_filter_prep_kernel<<<dim3(blocks, sets), 256, 0, ctx->stream>>>(W, g.tbl, g.C, g.OC, g.KH, g.KW, m0, m1);
   B200_LAUNCHED();
   return 0;
@@ -1128,7 +1126,6 @@ __global__ void __launch_bounds__(256) dw_finish_multi_kernel(const DwFinishBatc
 int dw_finish_blocks(const DwFinishArgs &a) { return (a.row_w + 31) / 32 + (a.db != nullptr ? a.OC : 0); }
 
 int launch_dw_finish(b200_ctx *ctx, const DwFinishArgs &a) {
-  B200_CARVEOUT((dw_finish_kernel));
   dw_finish_kernel<<<dw_finish_blocks(a), dim3(32, 8), 0, ctx->stream>>>(a);
   B200_LAUNCHED();
   return 0;
@@ -1247,7 +1244,6 @@ int dw_finish_many(b200_ctx *ctx, const DwFinishArgs *list, int n) {
       b.a[i] = list[i0 + i];
       b.first[i + 1] = b.first[i] + dw_finish_blocks(list[i0 + i]);
     }
-    B200_CARVEOUT((dw_finish_multi_kernel));
     dw_finish_multi_kernel<<<b.first[m], dim3(32, 8), 0, ctx->stream>>>(b);
     B200_LAUNCHED();
   }

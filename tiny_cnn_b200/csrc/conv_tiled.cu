@@ -876,7 +876,6 @@ static int launch_fewout(b200_ctx *ctx, const FewOutCfg &p, int B) {
   do {                                                                                                   \
     B200_CUDA(cudaFuncSetAttribute(conv_fewout_kernel<KH, KW, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                    (int)smem));                                                          \
-    B200_CARVEOUT((conv_fewout_kernel<KH, KW, N>));                                                      \
     conv_fewout_kernel<KH, KW, N><<<grid, FO_THREADS, smem, ctx->stream>>>(p);                           \
   } while (0)
   if (p.CO == 1) B200_FEWOUT(1);
@@ -893,7 +892,6 @@ int conv_tiled_dx_prep(b200_ctx *ctx, const ConvGeom &g, const float *W, float *
   int KK = g.KH * g.KW;
   int Cp = padded_channels(g.C);
   int total = g.OC * KK * Cp;
-  B200_CARVEOUT((conv_prep_wt_dx_kernel));
   conv_prep_wt_dx_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(W, scratch, g.C, g.OC, Cp,
                                                                        g.KH, g.KW, g.tbl);
   B200_LAUNCHED();

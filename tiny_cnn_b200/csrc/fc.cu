@@ -211,11 +211,9 @@ static int run_gemm(b200_ctx *ctx, int M, int N, int K, const float *A, long lon
   }
   dim3 grid(ceil_div(N, p.tile), ceil_div(M, p.tile), p.slices);
   if (p.tile == 64) {
-    B200_CARVEOUT((sgemm_kernel<64, 4, A_KFAST, B_NFAST>));
     sgemm_kernel<64, 4, A_KFAST, B_NFAST><<<grid, 256, 0, ctx->stream>>>(
       M, N, K, A, a_m, a_k, Bm, b_k, b_n, C, bias, accumulate, act, p.k_per, scratch);
   } else {
-    B200_CARVEOUT((sgemm_kernel<32, 2, A_KFAST, B_NFAST>));
     sgemm_kernel<32, 2, A_KFAST, B_NFAST><<<grid, 256, 0, ctx->stream>>>(
       M, N, K, A, a_m, a_k, Bm, b_k, b_n, C, bias, accumulate, act, p.k_per, scratch);
   }
@@ -224,7 +222,6 @@ static int run_gemm(b200_ctx *ctx, int M, int N, int K, const float *A, long lon
     size_t MN = (size_t)M * N;
     size_t blocks = ceil_div_sz(MN, 256);
     if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
-    B200_CARVEOUT((gemm_reduce_kernel));
     gemm_reduce_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(scratch, p.slices, MN, N, C, bias,
                                                                  accumulate, act);
     B200_LAUNCHED();
@@ -267,7 +264,6 @@ int fc_bwd(b200_ctx *ctx, int in_size, int out_size, const float *in, const floa
                                     dW, nullptr, accumulate, 0, scratch)));
   }
   if (db) {
-    B200_CARVEOUT((col_sum_kernel));
     col_sum_kernel<<<ceil_div(out_size, 32), dim3(32, 8), 0, ctx->stream>>>(dout, db, B, out_size,
                                                                            accumulate);
     B200_LAUNCHED();

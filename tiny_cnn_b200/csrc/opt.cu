@@ -176,7 +176,6 @@ int opt_update_segments(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const 
                         size_t total, float *pow_tab, const int *skip_if) {
   B200_REQUIRE(kind >= B200_OPT_ADAGRAD && kind <= B200_OPT_NESTEROV_MOMENTUM, "unknown optimizer %d", kind);
   if (total == 0) return 0;
-  B200_CARVEOUT((opt_update_segments_kernel));
   opt_update_segments_kernel<<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
     kind, to_params(h), grads, W, s0, s1, segs_dev, n_segs, total, pow_tab, skip_if);
   B200_LAUNCHED();
@@ -186,7 +185,6 @@ int opt_update_segments(b200_ctx *ctx, int kind, const b200_opt_hyper &h, const 
 int opt_advance_powers(b200_ctx *ctx, float *pow_tab, int n_tensors, float b1, float b2,
                        const int *skip_if) {
   if (n_tensors == 0) return 0;
-  B200_CARVEOUT((opt_advance_powers_kernel));
   opt_advance_powers_kernel<<<ceil_div(n_tensors, 64), 64, 0, ctx->stream>>>(pow_tab, n_tensors, b1,
                                                                             b2, skip_if);
   B200_LAUNCHED();

@@ -293,7 +293,6 @@ int maxpool_fwd(b200_ctx *ctx, const b200_pool_desc &d, const float *in, float *
   if (total == 0) return 0;
   if (pool2x2_fast(d) && aligned16(in) && aligned16(out) && aligned16(argmax)) {
     long long planes = (long long)B * d.in_c;
-    B200_CARVEOUT((maxpool2x2_fwd_kernel));
     maxpool2x2_fwd_kernel<<<grid_for(total / 2, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
       d.in_w, d.in_h, d.out_w, d.out_h, planes, in, out, argmax, d.in_c);
     B200_LAUNCHED();
@@ -319,11 +318,9 @@ int maxpool_bwd(b200_ctx *ctx, const b200_pool_desc &d, const float *dout, const
     long long planes = (long long)B * d.in_c;
     long long work = planes * d.out_h * (d.out_w / 2);
     if (planes * d.in_h * d.in_w < (1LL << 31)) {
-      B200_CARVEOUT((maxpool2x2_bwd_kernel<unsigned>));
       maxpool2x2_bwd_kernel<unsigned><<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
         d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, pooled_y, din, d.in_c);
     } else {
-      B200_CARVEOUT((maxpool2x2_bwd_kernel<long long>));
       maxpool2x2_bwd_kernel<long long><<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
         d.in_w, d.in_h, d.out_w, d.out_h, planes, dout, argmax, pooled_y, din, d.in_c);
     }

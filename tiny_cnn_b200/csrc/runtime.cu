@@ -176,25 +176,11 @@ int b200_ctx_create(int device, void *stream, b200_ctx **out) {
     c->own_stream = true;
   }
   ctx_load_tiles(c);
-  // experiment: every kernel without a preference of its own asks for the largest shared-memory carve-out
-  if (const char *e = getenv("B200_PREFER_SHARED"))
-    if (atoi(e) != 0) cudaDeviceSetCacheConfig(cudaFuncCachePreferShared);
   B200_CUDA(cudaMalloc(&c->dev_err, sizeof(int)));
   B200_CUDA(cudaMemset(c->dev_err, 0, sizeof(int)));
   *out = c;
   return 0;
 }
-
-namespace b200 {
-int carveout_once(const void *kernel) {
-  static const int on = [] {
-    const char *e = getenv("B200_SMALL_CARVEOUT");
-    return e ? atoi(e) : 0;
-  }();
-  if (on) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  return on;
-}
-}  // namespace b200
 
 // ---------------------------------------------------------------- exchange buffers across processes
 static_assert(sizeof(cudaIpcMemHandle_t) <= B200_PEER_HANDLE_BYTES, "handle does not fit its ABI size");
