@@ -680,9 +680,12 @@ B200_API int b200_net_forward_backward(b200_net *net, const float *x, const floa
  * process, to b200_net_peer_reduce_init.  From then on b200_net_train_step sums the
  * gradient bucket over the ranks inside its captured graph: the gradients of every layer
  * but the first one with parameters are pushed into every rank's buffer over NVLink from a
- * side branch as soon as the backward pass has produced them; after the backward pass one
- * kernel per GPU pushes the first layer's, waits (bounded) for the other ranks' pushes and
- * adds the `world` copies in rank order, so the replicas stay bit-identical.  No 1/world
+ * side branch as soon as the backward pass has produced them, and summed there (bounded wait
+ * for the other ranks' pushes, the `world` copies added in rank order); after the backward
+ * pass one kernel per GPU sends the first layer's gradients -- as 8-byte words {value, step
+ * number} that need neither fence nor counter when there are at most 65 536 of them -- waits
+ * (bounded) for the other ranks' and adds them in rank order, so the replicas stay
+ * bit-identical.  No 1/world
  * factor.  Every rank must call the step the same number of times.
  *
  * `timeout_ms` bounds every wait for another rank (0 = 10 s).  A wait that runs out sets the

@@ -95,6 +95,7 @@ def build_reference(force: bool = False) -> Path | None:
 OVERLAY_DIR = REF_DIR / "overlay"
 BACKEND_TEST = REF_DIR / "bin" / "test_backend_b200"
 FIT_BENCH = REF_DIR / "bin" / "bench_fit_b200"
+DP_TEST = REF_DIR / "bin" / "test_dp_b200"
 
 
 def build_backend_test(force: bool = False) -> Path | None:
@@ -107,17 +108,18 @@ def build_backend_test(force: bool = False) -> Path | None:
     _sys.path.insert(0, str(ROOT))
     from tiny_cnn_b200.host.make_overlay import make_overlay
     src = ROOT / "tests" / "cpp" / "test_backend_b200.cpp"
+    dp_src = ROOT / "tests" / "cpp" / "test_dp_b200.cpp"  # data-parallel fit, one process per GPU
     host = ROOT / "tiny_cnn_b200" / "host"
     bench_src = host / "bench_fit.cpp"
-    deps = [src, bench_src, host / "b200_glue.h", host / "b200_backend.h", host / "b200_net.h",
+    deps = [src, dp_src, bench_src, host / "b200_glue.h", host / "b200_backend.h", host / "b200_net.h",
             host / "make_overlay.py", ROOT / "include" / "tinycnn_b200.h"]
-    if not (force or _stale(BACKEND_TEST, deps) or _stale(FIT_BENCH, deps)):
+    if not (force or _stale(BACKEND_TEST, deps) or _stale(FIT_BENCH, deps) or _stale(DP_TEST, deps)):
         return BACKEND_TEST
     make_overlay(REF_ROOT, OVERLAY_DIR)
     BACKEND_TEST.parent.mkdir(parents=True, exist_ok=True)
     libdir = ROOT / "tiny_cnn_b200" / "csrc"
     procs = []
-    for s, out in ((src, BACKEND_TEST), (bench_src, FIT_BENCH)):  # the A/B test, and the timed fit bench.py runs
+    for s, out in ((src, BACKEND_TEST), (bench_src, FIT_BENCH), (dp_src, DP_TEST)):  # the A/B test, and the timed fit bench.py runs
         procs.append(subprocess.Popen(
             ["g++", "-std=c++14", "-O2", "-fopenmp", "-DCNN_USE_OMP", "-w", f"-I{OVERLAY_DIR}", f"-I{REF_ROOT}",
              f"-I{ROOT / 'include'}", str(s), "-o", str(out), f"-L{libdir}", "-ltinycnn_b200",

@@ -12,6 +12,7 @@ import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 BIN = ROOT / "oracle" / "_ref" / "bin" / "test_backend_b200"
+DP_BIN = ROOT / "oracle" / "_ref" / "bin" / "test_dp_b200"
 
 
 @pytest.mark.gpu
@@ -19,6 +20,22 @@ def test_backend_b200_inside_tiny_dnn():
     if not BIN.exists():
         pytest.skip("the C++ A/B binary has not been built (reference tree absent at build time)")
     res = subprocess.run([str(BIN)], capture_output=True, text=True, timeout=600)
+    print(res.stdout)
+    print(res.stderr)
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]
+    assert "RESULT: all passed" in res.stdout
+
+
+@pytest.mark.gpu
+def test_data_parallel_fit_from_cpp_on_two_gpus():
+    """tests/cpp/test_dp_b200.cpp: two processes, one GPU each, network<sequential>::fit on backend_t::b200 with
+    the gradients summed over the processes (buffer handles exchanged over pipes, no framework)."""
+    import torch
+    if not DP_BIN.exists():
+        pytest.skip("the C++ data-parallel binary has not been built (reference tree absent at build time)")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = subprocess.run([str(DP_BIN), "2"], capture_output=True, text=True, timeout=600)
     print(res.stdout)
     print(res.stderr)
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]

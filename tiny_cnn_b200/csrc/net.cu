@@ -89,6 +89,16 @@ struct b200_net {
   uint8_t *u8_stage[2] = {nullptr, nullptr}, *label_stage[2] = {nullptr, nullptr};
   size_t u8_stage_bytes = 0;
   cudaEvent_t up_done[2] = {nullptr, nullptr}, stage_free[2] = {nullptr, nullptr};
+  // a full mini-batch of b200_net_fit_host is read where the upload left it, and its forward output
+  // leaves through a copy the step itself makes, fetched by a third stream: between two steps the
+  // compute stream has nothing but the next graph
+  cudaStream_t d2h_stream = nullptr;
+  float *out_stage[2] = {nullptr, nullptr};
+  cudaEvent_t step_done[2] = {nullptr, nullptr}, d2h_done[2] = {nullptr, nullptr};
+  bool stage_used[2] = {false, false}, out_stage_used[2] = {false, false};
+  unsigned fit_toggle = 0;        // staging buffer of the next step (persists across fit calls)
+  int fit_last = -1;              // staging buffer holding the latest full mini-batch; -1: x_dev / t_dev do
+  float *fit_out_copy = nullptr;  // where the step being issued leaves a copy of its forward output
   int cur_batch = 0;
   const float *cur_x = nullptr;
   int fit_rows = 0;  // rows of x_dev / t_dev the last step of a fit call ran on
@@ -515,7 +525,13 @@ int step_eager(b200_net *net, const float *x, const float *t, int B, int loss_ki
     if (!early) B200_TRY(peer_reduce_push_early(net->ctx, &net->peer, net->grads));
     B200_TRY(peer_reduce_finish(net->ctx, &net->peer, net->grads, 0, early && net->early_summed));
   }
-  return net_update_impl(net, opt_kind, h);
+  B200_TRY(net_update_impl(net, opt_kind, h));
+  if (net->fit_out_copy) {  // fit from host buffers: the forward output of this step, for the stream that fetches it
+    const Layer &last = net->layers.back();
+    B200_CUDA(cudaMemcpyAsync(net->fit_out_copy, last.out, (size_t)B * last.out_dim * sizeof(float),
+                              cudaMemcpyDeviceToDevice, net->ctx->stream));
+  }
+  return 0;
 }
 
 }  // namespace
@@ -793,8 +809,12 @@ int b200_net_destroy(b200_net *net) {
     cudaFree(net->label_stage[i]);
     if (net->up_done[i]) cudaEventDestroy(net->up_done[i]);
     if (net->stage_free[i]) cudaEventDestroy(net->stage_free[i]);
+    cudaFree(net->out_stage[i]);
+    if (net->step_done[i]) cudaEventDestroy(net->step_done[i]);
+    if (net->d2h_done[i]) cudaEventDestroy(net->d2h_done[i]);
   }
   if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+  if (net->d2h_stream) cudaStreamDestroy(net->d2h_stream);
   peer_reduce_free(&net->peer);
   if (net->comm) cudaStreamDestroy(net->comm);
   if (net->ev_comm_main) cudaEventDestroy(net->ev_comm_main);
@@ -1087,6 +1107,7 @@ static std::string step_key(const b200_net *net, const float *x, const float *t,
                             int opt_kind, const b200_opt_hyper *h) {
   std::string key = step_key(x, t, batch, loss_kind, opt_kind, h);
   key.push_back(net->train_phase ? 't' : 'e');
+  key.append(reinterpret_cast<const char *>(&net->fit_out_copy), sizeof(net->fit_out_copy));
   return key;
 }
 
@@ -1106,6 +1127,22 @@ static int fit_step_rows(b200_net *net, int nb, int batch, int *rows) {
                "fit: %d samples for mini-batches of %d and no earlier full mini-batch to complete the step from "
                "(the reference reads unset rows of its batch buffers in this case)", nb, batch);
   *rows = batch;
+  return 0;
+}
+
+// x_dev / t_dev receive the rows of the latest full mini-batch when a staging buffer holds them
+static int fit_rows_to_fixed(b200_net *net) {
+  if (net->fit_last < 0) return 0;
+  const int batch = net->fit_rows;  // a staging buffer only ever holds a full mini-batch of the last step
+  const size_t in_dim = net->layers.front().in_dim, out_dim = net->layers.back().out_dim;
+  cudaStream_t st = net->ctx->stream;
+  B200_CUDA(cudaMemcpyAsync(net->x_dev, net->x_stage[net->fit_last], in_dim * batch * sizeof(float),
+                            cudaMemcpyDeviceToDevice, st));
+  B200_CUDA(cudaMemcpyAsync(net->t_dev, net->t_stage[net->fit_last], out_dim * batch * sizeof(float),
+                            cudaMemcpyDeviceToDevice, st));
+  // the next upload into that staging buffer must come after these copies, not only after its step
+  B200_CUDA(cudaEventRecord(net->stage_free[net->fit_last], st));
+  net->fit_last = -1;
   return 0;
 }
 
@@ -1182,37 +1219,65 @@ int b200_net_fit_host(b200_net *net, const float *x_host, const float *t_host, l
       B200_CUDA(cudaEventCreateWithFlags(&net->stage_free[i], cudaEventDisableTiming));
     }
   }
-  // whatever the compute stream has queued so far must not be overtaken by the first upload's
-  // consumer; the staging buffers themselves are free (every earlier fit ended with a sync)
-  long long step = 0;
+  if (!net->d2h_stream) {
+    B200_CUDA(cudaStreamCreateWithFlags(&net->d2h_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      B200_TRY(net_alloc((void **)&net->out_stage[i], out_dim * net->max_batch * sizeof(float)));
+      B200_CUDA(cudaEventCreateWithFlags(&net->step_done[i], cudaEventDisableTiming));
+      B200_CUDA(cudaEventCreateWithFlags(&net->d2h_done[i], cudaEventDisableTiming));
+    }
+  }
+  // A full mini-batch runs where its upload left it (the library keeps one captured step per input
+  // address, so two staging buffers mean two graphs) and its output is fetched by a third stream
+  // from a copy the step makes: the compute stream carries graph after graph.  A short last
+  // mini-batch goes through x_dev / t_dev, which first receive the rows of the latest full one.
   for (int e = 0; e < epochs; ++e) {
-    for (long long i = 0; i < n_samples; i += batch, ++step) {
+    for (long long i = 0; i < n_samples; i += batch) {
       const int nb = (int)((n_samples - i) < batch ? (n_samples - i) : batch);  // new rows of this step
       int run_nb = 0;
       B200_TRY(fit_step_rows(net, nb, batch, &run_nb));
-      const int buf = (int)(step & 1);
-      if (step >= 2) B200_CUDA(cudaStreamWaitEvent(net->copy_stream, net->stage_free[buf], 0));
+      const int buf = (int)(net->fit_toggle++ & 1u);
+      if (net->stage_used[buf]) B200_CUDA(cudaStreamWaitEvent(net->copy_stream, net->stage_free[buf], 0));
+      net->stage_used[buf] = true;
       B200_CUDA(cudaMemcpyAsync(net->x_stage[buf], x_host + (size_t)i * in_dim, in_dim * nb * sizeof(float),
                                 cudaMemcpyHostToDevice, net->copy_stream));
       B200_CUDA(cudaMemcpyAsync(net->t_stage[buf], t_host + (size_t)i * out_dim, out_dim * nb * sizeof(float),
                                 cudaMemcpyHostToDevice, net->copy_stream));
       B200_CUDA(cudaEventRecord(net->up_done[buf], net->copy_stream));
       B200_CUDA(cudaStreamWaitEvent(st, net->up_done[buf], 0));
-      // the captured step reads fixed buffers: hand the mini-batch over with a device copy
-      B200_CUDA(cudaMemcpyAsync(net->x_dev, net->x_stage[buf], in_dim * nb * sizeof(float),
-                                cudaMemcpyDeviceToDevice, st));
-      B200_CUDA(cudaMemcpyAsync(net->t_dev, net->t_stage[buf], out_dim * nb * sizeof(float),
-                                cudaMemcpyDeviceToDevice, st));
-      B200_CUDA(cudaEventRecord(net->stage_free[buf], st));
-      B200_TRY(b200_net_train_step(net, net->x_dev, net->t_dev, run_nb, loss_kind, opt_kind, h));
+      if (nb == batch) {
+        if (out_host && net->out_stage_used[buf]) B200_CUDA(cudaStreamWaitEvent(st, net->d2h_done[buf], 0));
+        net->fit_out_copy = out_host ? net->out_stage[buf] : nullptr;
+        int rc = b200_net_train_step(net, net->x_stage[buf], net->t_stage[buf], batch, loss_kind, opt_kind, h);
+        net->fit_out_copy = nullptr;
+        B200_TRY(rc);
+        B200_CUDA(cudaEventRecord(net->stage_free[buf], st));  // the step reads its input to the end (first layer's dW)
+        if (out_host) {
+          net->out_stage_used[buf] = true;
+          B200_CUDA(cudaStreamWaitEvent(net->d2h_stream, net->stage_free[buf], 0));
+          B200_CUDA(cudaMemcpyAsync(out_host + (size_t)i * out_dim, net->out_stage[buf], out_dim * nb * sizeof(float),
+                                    cudaMemcpyDeviceToHost, net->d2h_stream));
+          B200_CUDA(cudaEventRecord(net->d2h_done[buf], net->d2h_stream));
+        }
+        net->fit_last = buf;
+      } else {
+        B200_TRY(fit_rows_to_fixed(net));
+        B200_CUDA(cudaMemcpyAsync(net->x_dev, net->x_stage[buf], in_dim * nb * sizeof(float),
+                                  cudaMemcpyDeviceToDevice, st));
+        B200_CUDA(cudaMemcpyAsync(net->t_dev, net->t_stage[buf], out_dim * nb * sizeof(float),
+                                  cudaMemcpyDeviceToDevice, st));
+        B200_CUDA(cudaEventRecord(net->stage_free[buf], st));
+        B200_TRY(b200_net_train_step(net, net->x_dev, net->t_dev, run_nb, loss_kind, opt_kind, h));
+        if (out_host)
+          B200_CUDA(cudaMemcpyAsync(out_host + (size_t)i * out_dim, net->layers.back().out,
+                                    out_dim * nb * sizeof(float), cudaMemcpyDeviceToHost, st));
+      }
       net->fit_rows = run_nb;
-      if (out_host)
-        B200_CUDA(cudaMemcpyAsync(out_host + (size_t)i * out_dim, net->layers.back().out,
-                                  out_dim * nb * sizeof(float), cudaMemcpyDeviceToHost, st));
     }
   }
   B200_CUDA(cudaStreamSynchronize(net->copy_stream));
   B200_CUDA(cudaStreamSynchronize(st));
+  B200_CUDA(cudaStreamSynchronize(net->d2h_stream));
   return 0;
 }
 
@@ -1267,6 +1332,7 @@ int b200_net_fit_u8_host(b200_net *net, const b200_image_desc *d, const uint8_t 
                                 net->copy_stream));
       B200_CUDA(cudaEventRecord(net->up_done[buf], net->copy_stream));
       B200_CUDA(cudaStreamWaitEvent(st, net->up_done[buf], 0));
+      B200_TRY(fit_rows_to_fixed(net));
       // scale / pad the bytes into the step's fixed input rows, labels into its target rows
       B200_TRY(images_u8_to_float(net->ctx, d, net->u8_stage[buf], nb, net->x_dev));
       B200_TRY(labels_to_targets(net->ctx, net->label_stage[buf], nb, (int)out_dim, target_min, target_max,

@@ -12,6 +12,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -29,11 +30,14 @@ inline void check(int status) {
   if (status != 0) throw nn_error(std::string("b200: ") + b200_last_error());
 }
 
-// one context per process: device 0, its own stream
+// one context per process, with its own stream, on device 0 -- or on the device the environment
+// variable B200_DEVICE names (a launcher that starts one process per GPU sets it per process; the
+// other GPUs must stay visible to the process for the peer mapping of data-parallel replicas)
 inline b200_ctx *ctx() {
   static b200_ctx *c = [] {
     b200_ctx *p = nullptr;
-    check(b200_ctx_create(0, nullptr, &p));
+    const char *dev = std::getenv("B200_DEVICE");
+    check(b200_ctx_create(dev ? std::atoi(dev) : 0, nullptr, &p));
     return p;
   }();
   return c;

@@ -31,6 +31,7 @@
 #include <atomic>
 #include <cstring>
 #include <fstream>
+#include <functional>
 #include <memory>
 #include <string>
 #include <thread>
@@ -98,8 +99,28 @@ struct pinned_buffer {
   ~pinned_buffer() { release(); }
 };
 
+// Data-parallel replicas of a C++ program: one process per GPU (B200_DEVICE selects it), every process
+// builds the same network from the same seed and calls fit() on its own shard of the data with the
+// per-GPU batch size; the device-resident step then sums the gradients over the processes (no 1/N,
+// as edge::merge_grads sums the samples of one mini-batch) before every update, so the replicas stay
+// bit-identical and equal one process training on the concatenated mini-batches.  The launcher fills
+// this in before the first fit: its rank, the number of processes, and `exchange`, which sends this
+// process's 64-byte buffer handle and returns every process's, in rank order, over whatever channel
+// the launcher has (pipes, MPI, a file).  Every process must make the same number of steps.
+struct replica_group {
+  int rank = 0, world = 1;
+  std::function<void(const unsigned char *own, unsigned char *all)> exchange;
+  int timeout_ms = 0;  // bound of every wait for another process (0: the library's 10 s)
+};
+inline replica_group &replicas() {
+  static replica_group g;
+  return g;
+}
+
 // the device twin of one network<sequential>, kept in the network object
 struct device_twin {
+  void *peer_own = nullptr;            // this process's exchange buffer
+  std::vector<void *> peer_opened;     // the other processes' buffers as mapped here
   b200_net *net = nullptr;
   std::vector<const layer *> layers;          // identity of the network it was built for
   std::vector<std::vector<size_t>> shapes;    // weight tensor lengths per layer
@@ -108,8 +129,34 @@ struct device_twin {
   pinned_buffer x, t;
   ~device_twin() {
     if (net) b200_net_destroy(net);
+    for (void *q : peer_opened) b200_peer_buffer_close(ctx(), q);
+    // peer_own stays allocated: another process may still have it mapped; it goes with the process
   }
 };
+
+// maps every replica's exchange buffer and switches the twin's step to the summed gradients
+inline void join_replicas(device_twin &tw) {
+  replica_group &g = replicas();
+  if (g.world <= 1) return;
+  if (!g.exchange) throw nn_error("b200: replicas().exchange is not set");
+  const size_t bytes = b200_net_peer_reduce_bytes(tw.net, g.world);
+  unsigned char own[B200_PEER_HANDLE_BYTES];
+  check(b200_peer_buffer_create(ctx(), bytes, &tw.peer_own, own));
+  std::vector<unsigned char> all(static_cast<size_t>(g.world) * B200_PEER_HANDLE_BYTES);
+  g.exchange(own, all.data());
+  std::vector<unsigned long long> bases(g.world);
+  for (int r = 0; r < g.world; ++r) {
+    if (r == g.rank) {
+      bases[r] = reinterpret_cast<unsigned long long>(tw.peer_own);
+      continue;
+    }
+    void *q = nullptr;
+    check(b200_peer_buffer_open(ctx(), all.data() + static_cast<size_t>(r) * B200_PEER_HANDLE_BYTES, &q));
+    tw.peer_opened.push_back(q);
+    bases[r] = reinterpret_cast<unsigned long long>(q);
+  }
+  check(b200_net_peer_reduce_init(tw.net, g.rank, g.world, bases.data(), g.timeout_ms));
+}
 
 // b200_layer_spec of one layer, or false when the layer is not on the path
 inline bool spec_of(layer *l, b200_layer_spec &s, std::vector<uint8_t> &tbl) {
@@ -266,6 +313,7 @@ std::shared_ptr<device_twin> twin_for(Net &nn, int batch) {
     if (specs[i].kind == B200_LAYER_CONV && specs[i].conv.tbl) specs[i].conv.tbl = tw->tables[i].data();
   // a shape the library declines (b200_net_create says why) leaves the reference loop in charge
   if (b200_net_create(ctx(), specs.data(), static_cast<int>(depth), batch, &tw->net) != 0) return nullptr;
+  join_replicas(*tw);
   tw->layers = ids;
   tw->shapes = shapes;
   tw->max_batch = batch;
