@@ -757,6 +757,18 @@ B200_API int b200_net_fit_host(b200_net *net, const float *x_host, const float *
                                long long n_samples, int batch, int epochs, int loss_kind,
                                int opt_kind, const b200_opt_hyper *h, float *out_host);
 
+/*
+ * The same, returning as soon as the steps are queued: for a host that prepares its rows in
+ * runs (tiny-dnn keeps one heap vector per sample; the fit hook packs them into page-locked
+ * memory while the device trains on the rows packed before) and wants the device to go from
+ * one run to the next without draining.  The arrays of every queued call must stay valid and
+ * unchanged, and `out_host` unread, until b200_net_fit_host_wait has returned.
+ */
+B200_API int b200_net_fit_host_enqueue(b200_net *net, const float *x_host, const float *t_host,
+                               long long n_samples, int batch, int epochs, int loss_kind,
+                               int opt_kind, const b200_opt_hyper *h, float *out_host);
+B200_API int b200_net_fit_host_wait(b200_net *net);
+
 /* ------------------------------------------------------------------------- */
 /* The callers' data formats: raw dataset bytes to device batches              */
 /* ------------------------------------------------------------------------- */

@@ -190,6 +190,8 @@ SIGNATURES = {
     "b200_peer_buffer_destroy": (_i, [_vp, _vp]),
     "b200_net_train_step_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _oh, _vp]),
     "b200_net_fit_host": (_i, [_vp, _vp, _vp, C.c_longlong, _i, _i, _i, _i, _oh, _vp]),
+    "b200_net_fit_host_enqueue": (_i, [_vp, _vp, _vp, C.c_longlong, _i, _i, _i, _i, _oh, _vp]),
+    "b200_net_fit_host_wait": (_i, [_vp]),
     "b200_images_u8_to_float": (_i, [_vp, C.POINTER(ImageDesc), _vp, C.c_longlong, _vp]),
     "b200_labels_to_targets": (_i, [_vp, _vp, C.c_longlong, _i, C.c_float, C.c_float, _vp]),
     "b200_net_fit_u8_host": (_i, [_vp, C.POINTER(ImageDesc), _vp, _vp, C.c_longlong, _i, _i, C.c_float, C.c_float,

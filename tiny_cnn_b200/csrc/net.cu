@@ -1200,9 +1200,28 @@ int b200_net_train_step_host(b200_net *net, const float *x_host, const float *t_
   return 0;
 }
 
+int b200_net_fit_host_wait(b200_net *net) {
+  B200_TRY(check_net(net));
+  if (net->copy_stream) B200_CUDA(cudaStreamSynchronize(net->copy_stream));
+  B200_CUDA(cudaStreamSynchronize(net->ctx->stream));
+  if (net->d2h_stream) B200_CUDA(cudaStreamSynchronize(net->d2h_stream));
+  return 0;
+}
+
 int b200_net_fit_host(b200_net *net, const float *x_host, const float *t_host, long long n_samples,
                       int batch, int epochs, int loss_kind, int opt_kind, const b200_opt_hyper *h,
                       float *out_host) {
+  const int rc = b200_net_fit_host_enqueue(net, x_host, t_host, n_samples, batch, epochs, loss_kind, opt_kind, h, out_host);
+  if (rc != 0) {  // what was queued before the failure still reads the caller's arrays
+    if (net && net->ctx) cudaStreamSynchronize(net->ctx->stream);
+    return rc;
+  }
+  return b200_net_fit_host_wait(net);
+}
+
+int b200_net_fit_host_enqueue(b200_net *net, const float *x_host, const float *t_host, long long n_samples,
+                              int batch, int epochs, int loss_kind, int opt_kind, const b200_opt_hyper *h,
+                              float *out_host) {
   B200_TRY(check_net(net));
   B200_REQUIRE(x_host && t_host && h, "net_fit_host: NULL argument");
   B200_REQUIRE(batch >= 1 && batch <= net->max_batch, "net_fit_host: batch %d outside 1..%d", batch,
@@ -1275,9 +1294,6 @@ int b200_net_fit_host(b200_net *net, const float *x_host, const float *t_host, l
       net->fit_rows = run_nb;
     }
   }
-  B200_CUDA(cudaStreamSynchronize(net->copy_stream));
-  B200_CUDA(cudaStreamSynchronize(st));
-  B200_CUDA(cudaStreamSynchronize(net->d2h_stream));
   return 0;
 }
 

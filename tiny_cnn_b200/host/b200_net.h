@@ -452,6 +452,7 @@ bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<I
   auto pack = [&inputs, &targets, &tgt, &bad_row, xp, tp, in_dim, out_dim](size_t s0, size_t s1) {
     unsigned nt = std::thread::hardware_concurrency();
     nt = nt == 0 ? 1 : nt > 4 ? 4 : nt;
+    if (const char *e = std::getenv("B200_PACK_THREADS")) nt = std::max(1, std::atoi(e));
     if (s1 - s0 < 64) nt = 1;
     auto part = [&](size_t a, size_t b) {
       for (size_t s = a; s < b; ++s) {
@@ -474,21 +475,37 @@ bool fit_sequential(network<sequential> &nn, Optimizer &opt, const std::vector<I
   check(b200_net_opt_reset(tw->net, 1));
   if (oc.pow1) check(b200_net_set_adam_powers(tw->net, oc.h.b1, oc.h.b2, *oc.pow1, oc.pow2 ? *oc.pow2 : oc.h.b2));
   const long long steps_per_epoch = static_cast<long long>((N + batch - 1) / batch);
-  const size_t run = static_cast<size_t>(batch) * 16;  // mini-batches per library call in the first epoch
   for (int iter = 0; iter < epoch && !*stop; ++iter) {
     if (iter == 0) {
-      pack(0, std::min(N, run));
-      for (size_t s0 = 0; s0 < N; s0 += run) {
-        const size_t s1 = std::min(N, s0 + run), s2 = std::min(N, s1 + run);
-        std::thread ahead;
-        if (s1 < N) ahead = std::thread(pack, s1, s2);
-        const int rc = bad_row ? 0
-                               : b200_net_fit_host(tw->net, xp + s0 * in_dim, tp + s0 * out_dim,
-                                                   static_cast<long long>(s1 - s0), batch, 1, loss, oc.kind, &oc.h, nullptr);
-        if (ahead.joinable()) ahead.join();
-        if (bad_row) throw nn_error("b200: a target row does not fit the network's output (size or class id)");
-        check(rc);
+      // a packer thread runs ahead mini-batch by mini-batch and publishes how far it is; every library
+      // call takes the whole mini-batches packed so far, so the device starts after one of them and the
+      // calls grow as the packer gains on it
+      std::atomic<size_t> packed(0);
+      std::thread packer([&] {
+        for (size_t s = 0; s < N && !bad_row; s += static_cast<size_t>(batch)) {
+          const size_t e = std::min(N, s + static_cast<size_t>(batch));
+          pack(s, e);
+          packed.store(e, std::memory_order_release);
+        }
+        packed.store(N, std::memory_order_release);  // also ends the wait below after a bad row
+      });
+      int rc = 0;
+      for (size_t s0 = 0; s0 < N && rc == 0 && !bad_row;) {
+        const size_t want = std::min(N, s0 + static_cast<size_t>(batch));
+        size_t have;
+        while ((have = packed.load(std::memory_order_acquire)) < want) std::this_thread::yield();
+        if (bad_row) break;
+        const size_t s1 = have == N ? N : s0 + (have - s0) / batch * batch;
+        // queued, not waited for: the device goes from one run to the next without draining
+        rc = b200_net_fit_host_enqueue(tw->net, xp + s0 * in_dim, tp + s0 * out_dim, static_cast<long long>(s1 - s0),
+                                       batch, 1, loss, oc.kind, &oc.h, nullptr);
+        s0 = s1;
       }
+      packer.join();
+      const int rc_wait = b200_net_fit_host_wait(tw->net);
+      if (rc == 0) rc = rc_wait;
+      if (bad_row) throw nn_error("b200: a target row does not fit the network's output (size or class id)");
+      check(rc);
     } else {
       check(b200_net_fit_host(tw->net, xp, tp, static_cast<long long>(N), batch, 1, loss, oc.kind, &oc.h, nullptr));
     }
