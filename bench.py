@@ -303,6 +303,37 @@ def conv_rooflines(kt, peaks):
     return kernels, roofline
 
 
+def kernel_timeline(torch, path, rank, world, some_steps):
+    """Start and duration of every kernel of one replayed step on rank 0, as text.  Not a bench
+    number: the profiler's own overhead is in it; it shows which kernels overlap which."""
+    import re
+
+    from torch.profiler import ProfilerActivity, profile
+    if rank != 0:
+        some_steps()
+        torch.cuda.synchronize()
+        return
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        some_steps()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    evs.sort(key=lambda e: e.time_range.start)
+    marks = [i for i, e in enumerate(evs) if "opt_advance_powers" in e.name]  # the last kernel of a step
+    if len(marks) < 4:
+        return
+    a, b = marks[-3] + 1, marks[-2] + 1
+    t0 = evs[a].time_range.start
+    rows = [f"# one replayed step of {world} replica(s), rank 0: {len(evs[a:b])} kernels / copies, "
+            f"{evs[b - 1].time_range.end - t0:.1f} us from the first start to the last end",
+            "# start_us  duration_us  kernel"]
+    for e in evs[a:b]:
+        m = re.search(r"(\w+_kernel)", e.name)
+        rows.append(f"{e.time_range.start - t0:9.1f} {e.time_range.end - e.time_range.start:11.1f}  "
+                    f"{m.group(1) if m else e.name[:60]}")
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    Path(path).write_text("\n".join(rows) + "\n")
+
+
 def run_b200(args, rank, world, local_rank):
     import numpy as np
     import torch
@@ -437,6 +468,14 @@ def run_b200(args, rank, world, local_rank):
     blocks_e2e, _ = repeat_blocks(run_e2e, args.steps)
     ctx.sync()
     ms_e2e = statistics.median(blocks_e2e)
+
+    # ---- optional: kernel timeline of one replayed step (CUPTI through torch.profiler, rank 0) ----
+    if args.timeline:
+        restart()
+        barrier()
+        # every resident mini-batch has its own captured graph: each one replays under the profiler before the step that is kept
+        kernel_timeline(torch, args.timeline, rank, world, lambda: run_device(3 * NB))
+        barrier()
 
     # ---- replicas against each other and against one GPU on the concatenated mini-batch ----
     parity = None
@@ -681,6 +720,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: one timed block per leg, no CPU baseline, no per-kernel timing")
+    ap.add_argument("--timeline", default=None, metavar="FILE",
+                    help="also write the kernel timeline of one replayed step (rank 0, torch.profiler) to FILE")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
