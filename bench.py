@@ -440,6 +440,16 @@ def run_b200(args, rank, world, local_rank):
     ctx.sync()  # raises if a kernel gave up a bounded wait (a peer reduction that timed out)
     ms = statistics.median(blocks)
 
+    # informational, never the reported value: the same step without the gradient with respect to the
+    # input images, which the reference computes and network::fit never reads (weights bit-identical)
+    ms_no_input_grad = None
+    if world == 1 and not args.profile:
+        check(lib.b200_net_set_input_grad(net.handle, 0))
+        run_device(3 * NB)
+        ms_no_input_grad = statistics.median(timed_block(run_device, args.steps)[0] for _ in range(5))
+        check(lib.b200_net_set_input_grad(net.handle, 1))
+        run_device(3 * NB)
+
     # ---- end to end: every step's inputs from pinned host memory, its output back to the host ----
     fit_ok = world == 1 or peer
 
@@ -519,6 +529,11 @@ def run_b200(args, rank, world, local_rank):
                          "CUDA graph of forward+backward, NCCL sum all-reduce of the gradient bucket, update")
                         + "; inside the graph the weight-gradient kernels and the filter matrices run on a "
                           "side branch beside the forward / dX chain",
+                "without_input_gradient": (None if ms_no_input_grad is None else {
+                    "ms_per_step": ms_no_input_grad / args.steps,
+                    "samples_per_s": BATCH * args.steps / (ms_no_input_grad * 1e-3),
+                    "what": "informational: b200_net_set_input_grad(net, 0) drops the first layer's dX, a tensor the "
+                            "reference computes and network::fit never reads; weights bit-identical; `value` keeps it"}),
                 "peer_rendezvous": ({"ipc": "b200_peer_buffer_create/_open (the library's inter-process handles)",
                                      "symm": "torch symmetric memory"}.get(dp.rendezvous) if peer else None)},
             "clocks": clocks,

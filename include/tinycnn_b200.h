@@ -632,6 +632,15 @@ B200_API float *b200_net_layer_grad_ptr(b200_net *net, int i);
  * phase, as a new layer object is.  Only batch normalization layers look at it.
  */
 B200_API int b200_net_set_phase(b200_net *net, int train);
+
+/*
+ * The gradient with respect to the network's INPUT (prev_delta of the first layer).  The
+ * reference's backward pass computes it for every layer (layers/layer.h back_propagation) and
+ * network::fit never reads it; a new net computes it as well (b200_net_layer_grad_ptr(net, -1)).
+ * on = 0 drops the first layer's dX kernel from the following steps -- the weights come out bit
+ * for bit the same -- and rebuilds the captured graphs.
+ */
+B200_API int b200_net_set_input_grad(b200_net *net, int on);
 /*
  * The moving averages of batch normalization layer `layer` (index into the layer list):
  * mean_ and variance_ of the reference object, `channels` floats each, host memory.

@@ -192,6 +192,35 @@ def test_train_step_graph_and_host_path(ctx, oracle, gold, name, monkeypatch):
         dnet.close()
 
 
+@pytest.mark.parametrize("graph", ["0", "1"])
+def test_without_the_input_gradient_the_weights_are_the_same_bits(ctx, graph, monkeypatch):
+    """b200_net_set_input_grad(net, 0) drops the first layer's dX (which network::fit never reads):
+    four adam steps of the CIFAR net end in bit-identical weights, and turning it back on works."""
+    monkeypatch.setenv("B200_NET_NO_GRAPH", "0" if graph == "1" else "1")
+    specs, keep = build_net_specs("cifar")
+    B = 16
+    p0 = xavier_params(specs, 11)
+    rng = np.random.default_rng(12)
+    x = torch.from_numpy(rng.standard_normal((B, 3072)).astype(np.float32)).cuda()
+    t = torch.zeros(B, 10, device="cuda")
+    t[torch.arange(B), torch.from_numpy(rng.integers(0, 10, B)).cuda()] = 1.0
+    h = hyper_for(1)
+    results = []
+    for on in (1, 0):
+        dnet = DeviceNet(ctx, specs, B)
+        dnet.set_params(p0)
+        check(ctx.lib.b200_net_set_input_grad(dnet.h, on))
+        for s in range(4):
+            if s == 3:  # back on for the last step: the graphs are rebuilt
+                check(ctx.lib.b200_net_set_input_grad(dnet.h, 1))
+            check(ctx.lib.b200_net_train_step(dnet.h, ptr(x), ptr(t), B, 1, 1, C.byref(h)))
+        ctx.sync()
+        results.append(dnet.params())
+        dnet.close()
+    assert not np.array_equal(results[0], p0)
+    assert results[0].tobytes() == results[1].tobytes()
+
+
 def test_sequential_mirror_lenet_100_steps(ctx, oracle):
     """Benchmark configuration 1 through the Python mirror of network<sequential>:
     LeNet-5, batch 16, 100 adagrad steps on +-1 targets; weights within 1e-3 of the oracle."""

@@ -139,6 +139,7 @@ SIGNATURES = {
     "b200_qconv2d_eq_fwd_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "b200_qfc_eq_fwd_host": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "b200_net_set_phase": (_i, [_vp, _i]),
+    "b200_net_set_input_grad": (_i, [_vp, _i]),
     "b200_net_bn_stats": (_i, [_vp, _i, _vp, _vp, _i]),
     "b200_batchnorm_fwd": (_i, [_vp, _i, _i, C.c_float, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "b200_batchnorm_bwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i]),

@@ -898,6 +898,15 @@ int b200_net_set_phase(b200_net *net, int train) {
   return 0;
 }
 
+int b200_net_set_input_grad(b200_net *net, int on) {
+  B200_TRY(check_net(net));
+  if (net->input_grad != (on != 0)) {
+    net->input_grad = on != 0;
+    for (auto &slot : net->slots) slot.clear();  // the step's launch sequence changes
+  }
+  return 0;
+}
+
 int b200_net_bn_stats(b200_net *net, int layer, float *mean, float *variance, int set) {
   B200_TRY(check_net(net));
   B200_REQUIRE(layer >= 0 && layer < (int)net->layers.size() && net->layers[layer].kind == B200_LAYER_BATCHNORM,

@@ -338,6 +338,12 @@ class Sequential:
         check(self.lib.b200_net_fit_host(self.handle, ptr(inputs), ptr(targets), inputs.shape[0],
                                          batch_size, epochs, loss, opt.kind, C.byref(h), ptr(outputs)))
 
+    def set_input_grad(self, on: bool):
+        """Whether the backward pass also produces the gradient with respect to the input rows (the
+        first layer's prev_delta: the reference computes it, network::fit never reads it).  Off drops
+        that kernel; the weights come out bit for bit the same."""
+        check(self.lib.b200_net_set_input_grad(self.handle, 1 if on else 0))
+
     def adam_powers(self):
         a, b = C.c_float(), C.c_float()
         check(self.lib.b200_net_adam_powers(self.handle, C.byref(a), C.byref(b)))
