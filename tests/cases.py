@@ -122,6 +122,8 @@ FC_CASES = {
     "lenet_f6": dict(B=16, **{"in": 120, "out": 10}, bias=True, seed=23),
     "cifar_fc1": dict(B=8, **{"in": 1024, "out": 64}, bias=True, seed=24),
     "ragged": dict(B=5, **{"in": 130, "out": 67}, bias=True, seed=25),
+    # long inner dimension, few outputs, an odd batch, no bias: the split-k path of the small GEMM
+    "skinny_tail": dict(B=11, **{"in": 576, "out": 48}, bias=False, seed=26),
 }
 
 MAXPOOL_CASES = {
